@@ -1,0 +1,262 @@
+"""ctypes binding of the CPU restatement (oracle/tfr_oracle.c).
+
+Test infrastructure only: imported by tests/, by the smoke check and by the CPU-baseline
+legs of bench.py.  The product package never imports this module.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+LIB_PATH = HERE / "liboracle.so"
+
+Q4_K, Q6_K = 12, 14
+BLOCK_BYTES = {Q4_K: 144, Q6_K: 210}
+
+
+def build(force: bool = False) -> None:
+    """Compile liboracle.so (and the reference cubin when the reference checkout exists)."""
+    srcs = [HERE / "tfr_oracle.c", HERE / "tfr_oracle_gdn.c"]
+    stale = force or not LIB_PATH.exists() or any(s.stat().st_mtime > LIB_PATH.stat().st_mtime for s in srcs)
+    if stale:
+        subprocess.run(["make", "-C", str(HERE), str(LIB_PATH)], check=True, capture_output=True)
+
+
+class Mat(C.Structure):
+    _fields_ = [("type", C.c_int32), ("K", C.c_int32), ("N", C.c_int32), ("pad_", C.c_int32),
+                ("data", C.c_void_p)]
+
+
+class Layer(C.Structure):
+    _fields_ = [(n, Mat) for n in ("wq", "wk", "wv", "wo", "gate", "up", "down")] + \
+               [(n, C.c_void_p) for n in ("bq", "bk", "bv", "attn_norm", "ffn_norm")]
+
+
+class Model(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n_layer", "n_embd", "n_head", "n_kv", "head_dim", "n_ff",
+                                         "n_vocab", "max_seq")] + \
+               [("rope_theta", C.c_float), ("eps", C.c_float),
+                ("token_embd", Mat), ("output", Mat), ("output_norm", C.c_void_p),
+                ("layers", C.POINTER(Layer))]
+
+
+class Taps(C.Structure):
+    _fields_ = [("x_final", C.c_void_p), ("xn_final", C.c_void_p)]
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        _lib = C.CDLL(str(LIB_PATH))
+        _lib.tfo_half_to_float.restype = C.c_float
+        _lib.tfo_half_to_float.argtypes = [C.c_uint16]
+        _lib.tfo_float_to_half_bits.restype = C.c_uint16
+        _lib.tfo_float_to_half_bits.argtypes = [C.c_float]
+        for name in ("tfo_dot_q4k_q8", "tfo_dot_q6k_q8"):
+            f = getattr(_lib, name)
+            f.restype = C.c_float
+            f.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+        for name in ("tfo_dot_q6k_f32", "tfo_dot_q4k_f32"):
+            f = getattr(_lib, name)
+            f.restype = C.c_float
+            f.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        _lib.tfo_gemv.argtypes = [C.POINTER(Mat), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]
+        _lib.tfo_ffn_gate_up.argtypes = [C.POINTER(Mat), C.POINTER(Mat), C.c_void_p, C.c_void_p]
+        _lib.tfo_decode_token.argtypes = [C.POINTER(Model), C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                          C.c_void_p, C.POINTER(Taps), C.c_int]
+        _lib.tfo_decode_greedy.argtypes = [C.POINTER(Model), C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                           C.c_void_p, C.c_void_p, C.c_void_p]
+        _lib.tfo_rms_norm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_float]
+        _lib.tfo_rope_neox.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float]
+        _lib.tfo_attention.argtypes = [C.c_void_p] * 4 + [C.c_int] * 4 + [C.c_float]
+        _lib.tfo_quantize_q8.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+        _lib.tfo_dequant_row.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_void_p]
+        _lib.tfo_q4k_subdots.argtypes = [C.c_void_p] * 4
+        _lib.tfo_q6k_groupdots.argtypes = [C.c_void_p] * 3
+        _lib.tfo_copy_kv_f16.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int]
+        _lib.tfo_argmax.argtypes = [C.c_void_p, C.c_int]
+        _lib.tfo_set_threads.argtypes = [C.c_int]
+        _gdn_bind(_lib)
+    return _lib
+
+
+def _gdn_bind(l) -> None:
+    if hasattr(l, "tfo_gdn_step"):
+        l.tfo_gdn_step.argtypes = [C.c_void_p] * 11 + [C.c_int] * 4 + [C.c_float]
+
+
+def _p(a: np.ndarray) -> int:
+    return a.ctypes.data
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def set_threads(n: int) -> None:
+    lib().tfo_set_threads(int(n))
+
+
+def max_threads() -> int:
+    return int(lib().tfo_max_threads())
+
+
+def half_to_float(bits: np.ndarray) -> np.ndarray:
+    """Exact f16 -> f32 widening (numpy's own conversion is the same IEEE operation)."""
+    return np.asarray(bits, dtype=np.uint16).view(np.float16).astype(np.float32)
+
+
+def float_to_half_bits(x) -> np.ndarray:
+    x = _f32(x).ravel()
+    out = np.empty(x.size, np.uint16)
+    f = lib().tfo_float_to_half_bits
+    for i, v in enumerate(x):
+        out[i] = f(float(v))
+    return out
+
+
+def quantize_q8(x) -> tuple[np.ndarray, np.ndarray]:
+    x = _f32(x)
+    q = np.zeros(x.size, np.int8)
+    d = np.zeros(x.size // 32, np.float32)
+    lib().tfo_quantize_q8(_p(x), x.size, _p(q), _p(d))
+    return q, d
+
+
+def mat(wtype: int, data: np.ndarray, K: int, N: int) -> Mat:
+    """Wrap raw GGUF bytes (uint8 array that the caller keeps alive) as a matrix."""
+    assert data.dtype == np.uint8 and data.flags["C_CONTIGUOUS"]
+    assert data.size == N * (K // 256) * BLOCK_BYTES[wtype], (data.size, N, K, wtype)
+    return Mat(wtype, K, N, 0, _p(data))
+
+
+def dequant_rows(wtype: int, data: np.ndarray, K: int, N: int) -> np.ndarray:
+    out = np.empty((N, K), np.float32)
+    rb = (K // 256) * BLOCK_BYTES[wtype]
+    flat = np.ascontiguousarray(data).ravel()
+    for j in range(N):
+        rc = lib().tfo_dequant_row(wtype, _p(flat) + j * rb, K, _p(out) + j * K * 4)
+        assert rc == 0
+    return out
+
+
+def gemv(m: Mat, x, out=None, bias=None, use_res: int = 0, act_mode: int = 0) -> np.ndarray:
+    x = _f32(x)
+    if out is None:
+        out = np.zeros(m.N, np.float32)
+    b = _f32(bias) if bias is not None else None
+    rc = lib().tfo_gemv(C.byref(m), _p(x), _p(out), _p(b) if b is not None else None, use_res, act_mode)
+    assert rc == 0
+    return out
+
+
+def ffn_gate_up(gate: Mat, up: Mat, x) -> np.ndarray:
+    x = _f32(x)
+    out = np.zeros(gate.N, np.float32)
+    assert lib().tfo_ffn_gate_up(C.byref(gate), C.byref(up), _p(x), _p(out)) == 0
+    return out
+
+
+def q4k_subdots(block: np.ndarray, q8: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
+    I = np.zeros(8, np.int32)
+    S = np.zeros(8, np.int32)
+    lib().tfo_q4k_subdots(_p(block), _p(q8), _p(I), _p(S))
+    return I, S
+
+
+def q6k_groupdots(block: np.ndarray, q8: np.ndarray) -> np.ndarray:
+    J = np.zeros(16, np.int32)
+    lib().tfo_q6k_groupdots(_p(block), _p(q8), _p(J))
+    return J
+
+
+def rms_norm(x, w, eps: float) -> np.ndarray:
+    x, w = _f32(x), _f32(w)
+    out = np.empty_like(x)
+    lib().tfo_rms_norm(_p(x), _p(w), _p(out), x.size, eps)
+    return out
+
+
+def rope_neox(x, n_heads: int, head_dim: int, pos: int, theta: float) -> np.ndarray:
+    x = _f32(x).copy()
+    lib().tfo_rope_neox(_p(x), n_heads, head_dim, pos, theta)
+    return x
+
+
+def attention(q, kc: np.ndarray, vc: np.ndarray, n_head: int, n_kv: int, hd: int, pos: int) -> np.ndarray:
+    q = _f32(q)
+    out = np.zeros(n_head * hd, np.float32)
+    lib().tfo_attention(_p(q), _p(kc), _p(vc), _p(out), n_head, n_kv, hd, pos, float(1.0 / np.sqrt(np.float32(hd))))
+    return out
+
+
+class OracleModel:
+    """Dense decoder held as raw GGUF tensors (dict name -> (ggml_type, K, N, uint8 array) for
+    matrices, name -> float32 array for vectors), with the names of cuda/load.rs:280-417."""
+
+    def __init__(self, cfg: dict, tensors: dict, max_seq: int):
+        self.cfg, self.tensors, self.max_seq = cfg, tensors, max_seq
+        L = cfg["n_layer"]
+        self._keep = []
+        self._layers = (Layer * L)()
+
+        def m(name):
+            t, K, N, data = tensors[name]
+            return mat(t, data, K, N)
+
+        def v(name):
+            if name not in tensors:
+                return None
+            a = _f32(tensors[name])
+            self._keep.append(a)
+            return _p(a)
+
+        for i in range(L):
+            p = f"blk.{i}."
+            ly = self._layers[i]
+            ly.wq, ly.wk, ly.wv, ly.wo = (m(p + n + ".weight") for n in ("attn_q", "attn_k", "attn_v", "attn_output"))
+            ly.gate, ly.up, ly.down = (m(p + n + ".weight") for n in ("ffn_gate", "ffn_up", "ffn_down"))
+            ly.bq, ly.bk, ly.bv = v(p + "attn_q.bias"), v(p + "attn_k.bias"), v(p + "attn_v.bias")
+            ly.attn_norm, ly.ffn_norm = v(p + "attn_norm.weight"), v(p + "ffn_norm.weight")
+        self.m = Model()
+        for k in ("n_layer", "n_embd", "n_head", "n_kv", "head_dim", "n_ff", "n_vocab"):
+            setattr(self.m, k, cfg[k])
+        self.m.max_seq = max_seq
+        self.m.rope_theta, self.m.eps = cfg["rope_theta"], cfg["eps"]
+        self.m.token_embd = m("token_embd.weight")
+        if "output.weight" in tensors:
+            self.m.output = m("output.weight")
+        self.m.output_norm = v("output_norm.weight")
+        self.m.layers = self._layers
+        kvn = cfg["n_kv"] * cfg["head_dim"]
+        self.kc = np.zeros((L, max_seq, kvn), np.uint16)
+        self.vc = np.zeros((L, max_seq, kvn), np.uint16)
+
+    def decode_token(self, pos: int, token: int, act_f32: bool = False, want_taps: bool = False):
+        logits = np.zeros(self.cfg["n_vocab"], np.float32)
+        taps = Taps()
+        xf = np.zeros(self.cfg["n_embd"], np.float32)
+        xn = np.zeros(self.cfg["n_embd"], np.float32)
+        taps.x_final, taps.xn_final = _p(xf), _p(xn)
+        rc = lib().tfo_decode_token(C.byref(self.m), _p(self.kc), _p(self.vc), pos, token, _p(logits),
+                                    C.byref(taps), int(act_f32))
+        assert rc == 0, rc
+        return (logits, xf, xn) if want_taps else logits
+
+    def decode_greedy(self, pos0: int, first: int, n: int):
+        toks = np.zeros(n, np.int32)
+        margins = np.zeros(n, np.float32)
+        last = np.zeros(self.cfg["n_vocab"], np.float32)
+        rc = lib().tfo_decode_greedy(C.byref(self.m), _p(self.kc), _p(self.vc), pos0, first, n, _p(toks),
+                                     _p(margins), _p(last))
+        assert rc == 0, rc
+        return toks, margins, last

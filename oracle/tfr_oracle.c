@@ -1,0 +1,545 @@
+/*
+ * CPU restatement of taraference's batch-1 decode math.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file is the checker for the CUDA library: it is
+ * linked or called from tests/, from the smoke check and from the CPU-baseline legs of
+ * bench.py, never from the product path.  It restates, in plain C with IEEE fp32
+ * arithmetic, what the reference's device code computes; every function cites the
+ * reference lines it follows (paths are relative to the reference project root).
+ *
+ * Pinning: the reference's own tests hold no golden vectors for this path (they never
+ * launch a kernel).  The pins are (1) gguf-py's `quants.dequantize` for block decoding,
+ * and (2) outputs of the reference's own .cu kernels, compiled unmodified and run on a
+ * B200, stored under tests/golden/ together with the script that produced them.
+ *
+ * Known, intended difference from the reference build: the reference is compiled with
+ * fast-math (approximate division, ex2/sin/cos approximations).  This file uses exact
+ * IEEE operations, so the int8 activation quantiser can differ by one unit on a few
+ * elements in 1e5 and transcendental results differ in the last bits.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define TFO_Q4_K 12 /* ggml type ids, crates/gguf/src/types.rs:7-60 */
+#define TFO_Q6_K 14
+#define TFO_Q4_K_BYTES 144
+#define TFO_Q6_K_BYTES 210
+
+static int g_threads = 1;
+
+void tfo_set_threads(int n) {
+    g_threads = n < 1 ? 1 : n;
+#ifdef _OPENMP
+    omp_set_num_threads(g_threads);
+#endif
+}
+
+int tfo_get_threads(void) { return g_threads; }
+
+int tfo_max_threads(void) {
+#ifdef _OPENMP
+    return omp_get_num_procs();
+#else
+    return 1;
+#endif
+}
+
+/* ---------------------------------------------------------------- fp16 ---------- */
+
+/* kernels/common.cu:2-6 — cvt.f32.f16 is an exact widening, subnormals included. */
+float tfo_half_to_float(uint16_t h) {
+    uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    uint32_t exp = (h >> 10) & 0x1fu;
+    uint32_t man = h & 0x3ffu;
+    uint32_t bits;
+    if (exp == 0) {
+        if (man == 0) {
+            bits = sign;
+        } else {
+            int e = -1;
+            do {
+                man <<= 1;
+                e++;
+            } while (!(man & 0x400u));
+            bits = sign | ((uint32_t)(127 - 15 - e) << 23) | ((man & 0x3ffu) << 13);
+        }
+    } else if (exp == 31) {
+        bits = sign | 0x7f800000u | (man << 13);
+    } else {
+        bits = sign | ((exp + 127 - 15) << 23) | (man << 13);
+    }
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+/* kernels/common.cu:9-38 — the KV-store rounding: add one when the highest dropped bit
+ * is set (round half up in magnitude), flush below 2^-25, saturate to inf at 65536. */
+uint16_t tfo_float_to_half_bits(float f) {
+    uint32_t x;
+    memcpy(&x, &f, 4);
+    uint32_t sign = (x >> 16) & 0x8000u;
+    uint32_t absx = x & 0x7fffffffu;
+    if (absx == 0u) return (uint16_t)sign;
+    if (absx >= 0x7f800000u) return (uint16_t)(sign | (absx == 0x7f800000u ? 0x7c00u : 0x7e00u));
+    if (absx < 0x33000000u) return (uint16_t)sign;
+    if (absx >= 0x47800000u) return (uint16_t)(sign | 0x7c00u);
+    int e = (int)((absx >> 23) & 0xff) - 127 + 15;
+    uint32_t mant = absx & 0x7fffffu;
+    if (e <= 0) {
+        if (e < -10) return (uint16_t)sign;
+        mant |= 0x800000u;
+        uint32_t shift = (uint32_t)(14 - e);
+        uint32_t hm = mant >> shift;
+        if ((mant >> (shift - 1)) & 1u) hm += 1u;
+        return (uint16_t)(sign | hm);
+    }
+    uint32_t half = ((uint32_t)e << 10) | (mant >> 13);
+    if (mant & 0x1000u) half += 1u;
+    return (uint16_t)(sign | half);
+}
+
+static inline uint16_t rd16(const uint8_t* p) { return (uint16_t)(p[0] | (p[1] << 8)); }
+
+/* ---------------------------------------------------------------- blocks -------- */
+
+/* kernels/common.cu:40-50 — 6-bit scale / min of sub-block j from the 12 packed bytes. */
+void tfo_scale_min_k4(int j, const uint8_t* q, uint8_t* sc, uint8_t* m) {
+    if (j < 4) {
+        *sc = q[j] & 63;
+        *m = q[j + 4] & 63;
+    } else {
+        *sc = (uint8_t)((q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4));
+        *m = (uint8_t)((q[j + 4] >> 4) | ((q[j] >> 6) << 4));
+    }
+}
+
+/* kernels/common.cu:64-84 — one 144-byte Q4_K super-block to 256 floats. */
+void tfo_dequant_q4_k(const uint8_t* b, float* out) {
+    float d = tfo_half_to_float(rd16(b));
+    float dmin = tfo_half_to_float(rd16(b + 2));
+    const uint8_t* scales = b + 4;
+    const uint8_t* qs = b + 16;
+    for (int t = 0; t < 4; t++) {
+        uint8_t sc, m;
+        tfo_scale_min_k4(2 * t, scales, &sc, &m);
+        float d1 = d * (float)sc, m1 = dmin * (float)m;
+        tfo_scale_min_k4(2 * t + 1, scales, &sc, &m);
+        float d2 = d * (float)sc, m2 = dmin * (float)m;
+        for (int l = 0; l < 32; l++) {
+            out[64 * t + l] = d1 * (float)(qs[32 * t + l] & 0xF) - m1;
+            out[64 * t + 32 + l] = d2 * (float)(qs[32 * t + l] >> 4) - m2;
+        }
+    }
+}
+
+/* Signed 6-bit value (already minus 32) of element e (0..255) of a Q6_K block;
+ * kernels/common.cu:164-186. */
+static inline int q6_value(const uint8_t* b, int e) {
+    int n = e >> 7, r = e & 127, j = r >> 5, l = r & 31;
+    const uint8_t* ql = b + 64 * n;
+    const uint8_t* qh = b + 128 + 32 * n;
+    int lo = (j & 1) ? ql[32 + l] : ql[l];
+    lo = (j & 2) ? (lo >> 4) : (lo & 0xF);
+    int hi = (qh[l] >> (2 * j)) & 3;
+    return (lo | (hi << 4)) - 32;
+}
+
+/* Scale index of element e; kernels/common.cu:176-184 (sc_i + is + {0,2,4,6}). */
+static inline int q6_scale_index(int e) {
+    int n = e >> 7, r = e & 127, j = r >> 5, l = r & 31;
+    return 8 * n + (l >> 4) + 2 * j;
+}
+
+/* kernels/common.cu:164-186 — one 210-byte Q6_K block to 256 floats. */
+void tfo_dequant_q6_k(const uint8_t* b, float* out) {
+    const int8_t* sc = (const int8_t*)(b + 192);
+    float d = tfo_half_to_float(rd16(b + 208));
+    for (int e = 0; e < 256; e++)
+        out[e] = d * (float)sc[q6_scale_index(e)] * (float)q6_value(b, e);
+}
+
+static int blk_bytes(int type) { return type == TFO_Q4_K ? TFO_Q4_K_BYTES : (type == TFO_Q6_K ? TFO_Q6_K_BYTES : 0); }
+
+/* One weight row (K elements, GGUF bytes) to floats.  kernels/embed.cu:71-131 is this
+ * applied to the row of a token id. */
+int tfo_dequant_row(int type, const uint8_t* row, int K, float* out) {
+    int bb = blk_bytes(type);
+    if (!bb || K % 256) return -1;
+    for (int b = 0; b < K / 256; b++) {
+        if (type == TFO_Q4_K) tfo_dequant_q4_k(row + (size_t)b * bb, out + 256 * b);
+        else tfo_dequant_q6_k(row + (size_t)b * bb, out + 256 * b);
+    }
+    return 0;
+}
+
+/* ---------------------------------------------------------------- quantiser ----- */
+
+/* kernels/gemv.cu:43-65 (same body at gemv.cu:16-40 and ops.cu:66-83): per 32 values
+ * d = amax * (1/127) in fp32, q = round-to-nearest-even(x / d), all-zero group -> 0.
+ * Groups beyond n/32 whole groups are not written (n_rows >> 5). */
+void tfo_quantize_q8(const float* x, int n, int8_t* q, float* d8) {
+    int nb = n >> 5;
+    for (int b = 0; b < nb; b++) {
+        float amax = 0.f;
+        for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(x[32 * b + i]));
+        float d = amax * (1.0f / 127.0f);
+        for (int i = 0; i < 32; i++)
+            q[32 * b + i] = amax == 0.f ? 0 : (int8_t)(int)nearbyintf(x[32 * b + i] / d);
+        d8[b] = d;
+    }
+}
+
+/* ---------------------------------------------------------------- dots ---------- */
+
+/* Integer contract of kernels/gemv.cu:71-130: for sub-block j of one super-block,
+ * I[j] = sum over its 32 elements of nibble * q8, S[j] = sum of q8.  The reference
+ * builds these from four 8-element dp4a partials per lane; integer addition is exact,
+ * so the totals are what matters. */
+void tfo_q4k_subdots(const uint8_t* b, const int8_t* q8, int32_t* I, int32_t* S) {
+    const uint8_t* qs = b + 16;
+    for (int t = 0; t < 4; t++) {
+        int32_t i0 = 0, i1 = 0, s0 = 0, s1 = 0;
+        for (int l = 0; l < 32; l++) {
+            int a0 = q8[64 * t + l], a1 = q8[64 * t + 32 + l];
+            i0 += (qs[32 * t + l] & 0xF) * a0;
+            i1 += (qs[32 * t + l] >> 4) * a1;
+            s0 += a0;
+            s1 += a1;
+        }
+        I[2 * t] = i0;
+        I[2 * t + 1] = i1;
+        S[2 * t] = s0;
+        S[2 * t + 1] = s1;
+    }
+}
+
+/* kernels/gemv.cu:71-130 — Q4_K row times Q8 activation.  Per super-block
+ * d * sum_j d8*(float)(I_j*sc_j) - dmin * sum_j d8*(float)(S_j*m_j). */
+float tfo_dot_q4k_q8(const uint8_t* row, int nb, const int8_t* q8, const float* d8) {
+    float acc = 0.f;
+    for (int b = 0; b < nb; b++) {
+        const uint8_t* blk = row + (size_t)b * TFO_Q4_K_BYTES;
+        float d = tfo_half_to_float(rd16(blk));
+        float dmin = tfo_half_to_float(rd16(blk + 2));
+        int32_t I[8], S[8];
+        tfo_q4k_subdots(blk, q8 + 256 * b, I, S);
+        float pos = 0.f, neg = 0.f;
+        for (int j = 0; j < 8; j++) {
+            uint8_t sc, m;
+            tfo_scale_min_k4(j, blk + 4, &sc, &m);
+            pos += d8[8 * b + j] * (float)(I[j] * (int)sc);
+            neg += d8[8 * b + j] * (float)(S[j] * (int)m);
+        }
+        acc += d * pos;
+        acc -= dmin * neg;
+    }
+    return acc;
+}
+
+/* Integer contract of kernels/gemv.cu:302-337: for each of the 16 scale groups g of a
+ * block (16 consecutive elements 16g..16g+15) J[g] = sum (q6 - 32) * q8. */
+void tfo_q6k_groupdots(const uint8_t* b, const int8_t* q8, int32_t* J) {
+    for (int g = 0; g < 16; g++) J[g] = 0;
+    for (int e = 0; e < 256; e++) J[e >> 4] += q6_value(b, e) * (int)q8[e];
+}
+
+/* kernels/gemv.cu:302-337 — Q6_K row times Q8 activation: d * scale_g * d8 * J. */
+float tfo_dot_q6k_q8(const uint8_t* row, int nb, const int8_t* q8, const float* d8) {
+    float acc = 0.f;
+    for (int b = 0; b < nb; b++) {
+        const uint8_t* blk = row + (size_t)b * TFO_Q6_K_BYTES;
+        const int8_t* sc = (const int8_t*)(blk + 192);
+        float d = tfo_half_to_float(rd16(blk + 208));
+        int32_t J[16];
+        tfo_q6k_groupdots(blk, q8 + 256 * b, J);
+        /* element group 16g sits in 32-group (16g)/32 of this block */
+        for (int g = 0; g < 16; g++) {
+            /* scale index of elements 16g.. is q6_scale_index(16g) */
+            acc += d * (float)sc[q6_scale_index(16 * g)] * d8[8 * b + (g >> 1)] * (float)J[g];
+        }
+    }
+    return acc;
+}
+
+/* kernels/gemv.cu:233-264 — Q6_K row times UNQUANTISED fp32 activation (the route the
+ * reference takes for a Q6_K attn_v: layer.rs:265-275 -> matmul.rs:346-412). */
+float tfo_dot_q6k_f32(const uint8_t* row, int nb, const float* x) {
+    float acc = 0.f;
+    for (int b = 0; b < nb; b++) {
+        const uint8_t* blk = row + (size_t)b * TFO_Q6_K_BYTES;
+        const int8_t* sc = (const int8_t*)(blk + 192);
+        float d = tfo_half_to_float(rd16(blk + 208));
+        for (int e = 0; e < 256; e++)
+            acc += d * (float)sc[q6_scale_index(e)] * (float)q6_value(blk, e) * x[256 * b + e];
+    }
+    return acc;
+}
+
+/* kernels/gemv.cu:193-231 shape — Q4_K row times fp32 activation (prefill GEMM math,
+ * kernels/gemm.cu:6-67: dequantise then fp32 multiply-add). */
+float tfo_dot_q4k_f32(const uint8_t* row, int nb, const float* x) {
+    float acc = 0.f, w[256];
+    for (int b = 0; b < nb; b++) {
+        tfo_dequant_q4_k(row + (size_t)b * TFO_Q4_K_BYTES, w);
+        for (int e = 0; e < 256; e++) acc += w[e] * x[256 * b + e];
+    }
+    return acc;
+}
+
+/* ---------------------------------------------------------------- GEMV ---------- */
+
+typedef struct {
+    int32_t type; /* TFO_Q4_K or TFO_Q6_K */
+    int32_t K;    /* input features, contiguous (GGUF dims[0]) */
+    int32_t N;    /* output rows (GGUF dims[1]) */
+    int32_t pad_;
+    const uint8_t* data; /* raw GGUF bytes, N rows of K/256 blocks */
+} tfo_mat;
+
+static size_t row_bytes(const tfo_mat* m) { return (size_t)(m->K / 256) * blk_bytes(m->type); }
+
+/* y = W x (+bias) (+y).  act_mode 0: x is quantised to Q8 first (gemv.cu:377-403,
+ * 469-490, 515-536, 2081-2115); act_mode 1: fp32 activation (gemv.cu:405-438, only
+ * defined by the reference for Q6_K; Q4_K accepted here for the prefill restatement).
+ * use_res 0/2 as gemv.cu:367-373 (2 = accumulate into out). */
+int tfo_gemv(const tfo_mat* w, const float* x, float* out, const float* bias, int use_res, int act_mode) {
+    int K = w->K, N = w->N, nb = K / 256;
+    if (K % 256 || !blk_bytes(w->type)) return -1;
+    int8_t* q8 = NULL;
+    float* d8 = NULL;
+    if (act_mode == 0) {
+        q8 = (int8_t*)malloc((size_t)K);
+        d8 = (float*)malloc(sizeof(float) * (size_t)(K / 32));
+        tfo_quantize_q8(x, K, q8, d8);
+    }
+    size_t rb = row_bytes(w);
+#pragma omp parallel for schedule(static) if (g_threads > 1)
+    for (int j = 0; j < N; j++) {
+        const uint8_t* row = w->data + (size_t)j * rb;
+        float acc;
+        if (act_mode == 0)
+            acc = w->type == TFO_Q4_K ? tfo_dot_q4k_q8(row, nb, q8, d8) : tfo_dot_q6k_q8(row, nb, q8, d8);
+        else
+            acc = w->type == TFO_Q4_K ? tfo_dot_q4k_f32(row, nb, x) : tfo_dot_q6k_f32(row, nb, x);
+        if (use_res == 2) acc += out[j];
+        if (bias) acc += bias[j];
+        out[j] = acc;
+    }
+    free(q8);
+    free(d8);
+    return 0;
+}
+
+/* kernels/gemv.cu:2546-2575 — h[j] = silu(gate_j . x) * (up_j . x), x quantised to Q8
+ * once, silu(g) = g / (1 + exp(-g)). */
+int tfo_ffn_gate_up(const tfo_mat* gate, const tfo_mat* up, const float* x, float* out) {
+    int K = gate->K, N = gate->N, nb = K / 256;
+    if (gate->type != TFO_Q4_K || up->type != TFO_Q4_K || up->K != K || up->N != N || K % 256) return -1;
+    int8_t* q8 = (int8_t*)malloc((size_t)K);
+    float* d8 = (float*)malloc(sizeof(float) * (size_t)(K / 32));
+    tfo_quantize_q8(x, K, q8, d8);
+    size_t rb = row_bytes(gate);
+#pragma omp parallel for schedule(static) if (g_threads > 1)
+    for (int j = 0; j < N; j++) {
+        float g = tfo_dot_q4k_q8(gate->data + (size_t)j * rb, nb, q8, d8);
+        float u = tfo_dot_q4k_q8(up->data + (size_t)j * rb, nb, q8, d8);
+        out[j] = (g / (1.f + expf(-g))) * u;
+    }
+    free(q8);
+    free(d8);
+    return 0;
+}
+
+/* ---------------------------------------------------------------- elementwise --- */
+
+/* kernels/ops.cu:4-34 — y = x * rsqrt(mean(x^2) + eps) * w. */
+void tfo_rms_norm(const float* x, const float* w, float* out, int n, float eps) {
+    float s = 0.f;
+    for (int i = 0; i < n; i++) s += x[i] * x[i];
+    float scale = 1.0f / sqrtf(s / (float)n + eps);
+    for (int i = 0; i < n; i++) out[i] = x[i] * scale * w[i];
+}
+
+/* kernels/ops.cu:348-371 — neox rotation of pairs (i, i + hd/2), fp32 angle. */
+void tfo_rope_neox(float* x, int n_heads, int head_dim, int pos, float theta) {
+    int half = head_dim / 2;
+    for (int h = 0; h < n_heads; h++) {
+        float* base = x + (size_t)h * head_dim;
+        for (int i = 0; i < half; i++) {
+            float freq = powf(theta, -2.f * (float)i / (float)head_dim);
+            float ang = (float)pos * freq;
+            float c = cosf(ang), s = sinf(ang);
+            float x0 = base[i], x1 = base[i + half];
+            base[i] = x0 * c - x1 * s;
+            base[i + half] = x0 * s + x1 * c;
+        }
+    }
+}
+
+/* kernels/ops.cu:471-486 — fp32 -> f16 bits into cache row `pos` of [pos][n_kv*hd]. */
+void tfo_copy_kv_f16(const float* src, uint16_t* cache, int pos, int stride) {
+    for (int d = 0; d < stride; d++) cache[(size_t)pos * stride + d] = tfo_float_to_half_bits(src[d]);
+}
+
+/* kernels/attn/flash.cu:16-116 and 222-255 — softmax(q.K^T * scale) V over positions
+ * 0..pos for every query head; KV head of query head h is h / (n_head / n_kv).  The
+ * reference splits the range in 8 and merges (m, l, O); the merge is exact algebra, so
+ * the restatement is the unsplit softmax in fp32. */
+void tfo_attention(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv,
+                   int hd, int pos, float scale) {
+    int rep = n_head / n_kv, stride = n_kv * hd, T = pos + 1;
+#pragma omp parallel for schedule(static) if (g_threads > 1)
+    for (int h = 0; h < n_head; h++) {
+        int kvh = h / rep;
+        float* sc = (float*)malloc(sizeof(float) * (size_t)T);
+        float m = -1e30f;
+        for (int t = 0; t < T; t++) {
+            const uint16_t* kr = kc + (size_t)t * stride + (size_t)kvh * hd;
+            float dot = 0.f;
+            for (int d = 0; d < hd; d++) dot += q[(size_t)h * hd + d] * tfo_half_to_float(kr[d]);
+            sc[t] = dot * scale;
+            m = fmaxf(m, sc[t]);
+        }
+        float l = 0.f;
+        for (int t = 0; t < T; t++) {
+            sc[t] = expf(sc[t] - m);
+            l += sc[t];
+        }
+        for (int d = 0; d < hd; d++) {
+            float acc = 0.f;
+            for (int t = 0; t < T; t++) acc += sc[t] * tfo_half_to_float(vc[(size_t)t * stride + (size_t)kvh * hd + d]);
+            out[(size_t)h * hd + d] = acc / fmaxf(l, 1e-20f);
+        }
+        free(sc);
+    }
+}
+
+/* kernels/ops.cu:573-599 — index of the maximum; on exact ties the reference's tree can
+ * return any of the tied indices, this returns the lowest. */
+int tfo_argmax(const float* x, int n) {
+    int bi = 0;
+    float bv = -1e30f;
+    for (int i = 0; i < n; i++)
+        if (x[i] > bv) {
+            bv = x[i];
+            bi = i;
+        }
+    return bi;
+}
+
+/* ---------------------------------------------------------------- dense model --- */
+
+typedef struct {
+    tfo_mat wq, wk, wv, wo, gate, up, down;
+    const float *bq, *bk, *bv;   /* may be NULL */
+    const float *attn_norm, *ffn_norm;
+} tfo_layer;
+
+typedef struct {
+    int32_t n_layer, n_embd, n_head, n_kv, head_dim, n_ff, n_vocab, max_seq;
+    float rope_theta, eps;
+    tfo_mat token_embd;
+    tfo_mat output; /* data == NULL: tied to token_embd */
+    const float* output_norm;
+    const tfo_layer* layers;
+} tfo_model;
+
+/* Optional taps of intermediate vectors of the LAST layer processed and of the head,
+ * for stage-by-stage parity tests.  Any pointer may be NULL. */
+typedef struct {
+    float* x_final;  /* [n_embd] residual stream after the last layer */
+    float* xn_final; /* [n_embd] after output_norm */
+} tfo_taps;
+
+/* One batch-1 decode step: layer schedule of layer.rs:142-709 (attention block),
+ * layer.rs:1210-1456 (dense FFN) and layer.rs:2125-2259 (head) at n_tok = 1, with the
+ * BASELINE dispatch: Q4_K matrices take Q8 activations, a Q6_K attn_v takes fp32
+ * activations, o-proj / down / head take Q8 activations.
+ * kcache/vcache: [n_layer][max_seq][n_kv*hd] f16 bits.  Writes row `pos`.
+ * act_f32 != 0 restates the reference's PREFILL arithmetic instead (gemm.cu: every
+ * projection is dequantise-then-fp32; ops.cu silu_mul), used to fill a cache the way
+ * forward.rs:54-65 does. */
+int tfo_decode_token(const tfo_model* M, uint16_t* kcache, uint16_t* vcache, int pos, int token, float* logits,
+                     const tfo_taps* taps, int act_f32) {
+    int K = M->n_embd, H = M->n_head, Hkv = M->n_kv, hd = M->head_dim, FF = M->n_ff;
+    if (pos < 0 || pos >= M->max_seq || token < 0 || token >= M->token_embd.N) return -1;
+    int qn = H * hd, kvn = Hkv * hd;
+    float* x = (float*)malloc(sizeof(float) * (size_t)K);
+    float* xb = (float*)malloc(sizeof(float) * (size_t)(K > qn ? K : qn));
+    float* q = (float*)malloc(sizeof(float) * (size_t)qn);
+    float* kb = (float*)malloc(sizeof(float) * (size_t)kvn);
+    float* vb = (float*)malloc(sizeof(float) * (size_t)kvn);
+    float* h = (float*)malloc(sizeof(float) * (size_t)FF);
+    float* u = (float*)malloc(sizeof(float) * (size_t)FF);
+    int rc = 0;
+    size_t lstride = (size_t)M->max_seq * kvn;
+    /* embed.cu:112-131 */
+    rc |= tfo_dequant_row(M->token_embd.type, M->token_embd.data + (size_t)token * row_bytes(&M->token_embd), K, x);
+    for (int li = 0; li < M->n_layer && rc == 0; li++) {
+        const tfo_layer* L = &M->layers[li];
+        uint16_t* kc = kcache + (size_t)li * lstride;
+        uint16_t* vc = vcache + (size_t)li * lstride;
+        tfo_rms_norm(x, L->attn_norm, xb, K, M->eps);
+        rc |= tfo_gemv(&L->wq, xb, q, L->bq, 0, act_f32);
+        rc |= tfo_gemv(&L->wk, xb, kb, L->bk, 0, act_f32);
+        rc |= tfo_gemv(&L->wv, xb, vb, L->bv, 0, (act_f32 || L->wv.type == TFO_Q6_K) ? 1 : 0);
+        tfo_rope_neox(q, H, hd, pos, M->rope_theta);
+        tfo_rope_neox(kb, Hkv, hd, pos, M->rope_theta);
+        tfo_copy_kv_f16(kb, kc, pos, kvn);
+        tfo_copy_kv_f16(vb, vc, pos, kvn);
+        tfo_attention(q, kc, vc, xb, H, Hkv, hd, pos, 1.0f / sqrtf((float)hd));
+        {
+            tfo_mat wo = L->wo;
+            rc |= tfo_gemv(&wo, xb, x, NULL, 2, act_f32);
+        }
+        tfo_rms_norm(x, L->ffn_norm, xb, K, M->eps);
+        if (!act_f32) {
+            rc |= tfo_ffn_gate_up(&L->gate, &L->up, xb, h);
+        } else {
+            rc |= tfo_gemv(&L->gate, xb, h, NULL, 0, 1);
+            rc |= tfo_gemv(&L->up, xb, u, NULL, 0, 1);
+            for (int j = 0; j < FF; j++) h[j] = (h[j] / (1.f + expf(-h[j]))) * u[j];
+        }
+        rc |= tfo_gemv(&L->down, h, x, NULL, 2, act_f32);
+    }
+    if (rc == 0) {
+        if (taps && taps->x_final) memcpy(taps->x_final, x, sizeof(float) * (size_t)K);
+        tfo_rms_norm(x, M->output_norm, xb, K, M->eps);
+        if (taps && taps->xn_final) memcpy(taps->xn_final, xb, sizeof(float) * (size_t)K);
+        const tfo_mat* head = M->output.data ? &M->output : &M->token_embd;
+        if (logits) rc |= tfo_gemv(head, xb, logits, NULL, 0, 0);
+    }
+    free(x); free(xb); free(q); free(kb); free(vb); free(h); free(u);
+    return rc;
+}
+
+/* Greedy loop over tfo_decode_token (session.rs:288-368 without EOS handling): feeds
+ * `first` at position pos0, then each argmax; writes n tokens and, if margins != NULL,
+ * the top-1 minus top-2 logit gap of every step (for margin-gated token comparison). */
+int tfo_decode_greedy(const tfo_model* M, uint16_t* kcache, uint16_t* vcache, int pos0, int first, int n,
+                      int32_t* out_tokens, float* margins, float* last_logits) {
+    int V = M->output.data ? M->output.N : M->token_embd.N;
+    float* logits = (float*)malloc(sizeof(float) * (size_t)V);
+    int tok = first, rc = 0;
+    for (int s = 0; s < n && rc == 0; s++) {
+        rc = tfo_decode_token(M, kcache, vcache, pos0 + s, tok, logits, NULL, 0);
+        if (rc) break;
+        tok = tfo_argmax(logits, V);
+        out_tokens[s] = tok;
+        if (margins) {
+            float second = -1e30f;
+            for (int i = 0; i < V; i++)
+                if (i != tok && logits[i] > second) second = logits[i];
+            margins[s] = logits[tok] - second;
+        }
+    }
+    if (last_logits && rc == 0) memcpy(last_logits, logits, sizeof(float) * (size_t)V);
+    free(logits);
+    return rc;
+}

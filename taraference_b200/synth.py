@@ -1,0 +1,164 @@
+"""Seeded synthetic GGUF-layout tensors and models (numpy, host side).
+
+No real GGUF files are available to this project, so tests and benchmarks run on tensors
+generated here: random super-blocks with the value distributions of the FFN-block
+configuration, and N(0, 0.02) weights pushed through a small deterministic K-quant
+quantiser for whole models.  The reference has no quantiser (crates/gguf only parses
+files, crates/gguf/src/lib.rs:1-16); parity is defined downstream of the bytes, so this
+one need not reproduce ggml's search — it only has to emit valid blocks
+(layouts: crates/core/src/cuda/kernels/common.cu:40-84 and :164-186).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+Q4_K, Q6_K, F32 = 12, 14, 0
+BLOCK_BYTES = {Q4_K: 144, Q6_K: 210}
+
+
+# ------------------------------------------------------------------ random blocks
+
+def random_q4_k(rng: np.random.Generator, n_blocks: int, d_sigma: float = 0.003) -> np.ndarray:
+    """n_blocks Q4_K super-blocks: fp16 d, dmin ~ |N(0, d_sigma)|, 6-bit scales/mins uniform in
+    [0, 63], uniform 4-bit quants."""
+    out = np.empty((n_blocks, 144), np.uint8)
+    dd = np.abs(rng.normal(0.0, d_sigma, size=(n_blocks, 2))).astype(np.float16)
+    out[:, 0:4] = dd.view(np.uint8).reshape(n_blocks, 4)
+    sc = rng.integers(0, 64, size=(n_blocks, 8), dtype=np.uint8)
+    mn = rng.integers(0, 64, size=(n_blocks, 8), dtype=np.uint8)
+    out[:, 4:16] = pack_scales_k4(sc, mn)
+    out[:, 16:144] = rng.integers(0, 256, size=(n_blocks, 128), dtype=np.uint8)
+    return out
+
+
+def random_q6_k(rng: np.random.Generator, n_blocks: int, d_sigma: float = 0.002) -> np.ndarray:
+    """n_blocks Q6_K blocks: uniform ql/qh bytes, int8 scales uniform in [-32, 31], fp16 d ~ |N(0, d_sigma)|."""
+    out = np.empty((n_blocks, 210), np.uint8)
+    out[:, 0:192] = rng.integers(0, 256, size=(n_blocks, 192), dtype=np.uint8)
+    out[:, 192:208] = rng.integers(-32, 32, size=(n_blocks, 16), dtype=np.int8).view(np.uint8)
+    d = np.abs(rng.normal(0.0, d_sigma, size=(n_blocks, 1))).astype(np.float16)
+    out[:, 208:210] = d.view(np.uint8).reshape(n_blocks, 2)
+    return out
+
+
+def pack_scales_k4(sc: np.ndarray, mn: np.ndarray) -> np.ndarray:
+    """Pack eight 6-bit scales and mins per block into the 12-byte K-quant field."""
+    sc = sc.astype(np.uint8)
+    mn = mn.astype(np.uint8)
+    out = np.empty(sc.shape[:-1] + (12,), np.uint8)
+    out[..., 0:4] = sc[..., 0:4] | ((sc[..., 4:8] >> 4) << 6)
+    out[..., 4:8] = mn[..., 0:4] | ((mn[..., 4:8] >> 4) << 6)
+    out[..., 8:12] = (sc[..., 4:8] & 0xF) | ((mn[..., 4:8] & 0xF) << 4)
+    return out
+
+
+# ------------------------------------------------------------------ quantisers
+
+def quantize_q4_k(w: np.ndarray) -> np.ndarray:
+    """Rows of fp32 weights (N, K) -> uint8 (N, K/256*144).  Asymmetric min/max per 32-element
+    sub-block; not ggml's iterative search."""
+    N, K = w.shape
+    assert K % 256 == 0
+    nb = K // 256
+    x = w.astype(np.float32).reshape(N, nb, 8, 32)
+    lo = np.minimum(x.min(-1), 0.0)
+    hi = np.maximum(x.max(-1), lo)
+    scale = (hi - lo) / 15.0
+    mins = -lo
+    d = (scale.max(-1) / 63.0).astype(np.float16)
+    dmin = (mins.max(-1) / 63.0).astype(np.float16)
+    df, dminf = d.astype(np.float32), dmin.astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        sc = np.where(df[..., None] > 0, np.rint(scale / df[..., None]), 0).clip(0, 63)
+        mn = np.where(dminf[..., None] > 0, np.rint(mins / dminf[..., None]), 0).clip(0, 63)
+        step = df[..., None] * sc
+        q = np.where(step[..., None] > 0, np.rint((x + (dminf[..., None] * mn)[..., None]) / step[..., None]), 0)
+    q = q.clip(0, 15).astype(np.uint8).reshape(N, nb, 4, 2, 32)
+    out = np.empty((N, nb, 144), np.uint8)
+    out[..., 0:2] = d.view(np.uint8).reshape(N, nb, 2)
+    out[..., 2:4] = dmin.view(np.uint8).reshape(N, nb, 2)
+    out[..., 4:16] = pack_scales_k4(sc.astype(np.uint8), mn.astype(np.uint8))
+    out[..., 16:144] = (q[..., 0, :] | (q[..., 1, :] << 4)).reshape(N, nb, 128)
+    return out.reshape(N, nb * 144)
+
+
+def quantize_q6_k(w: np.ndarray) -> np.ndarray:
+    """Rows of fp32 weights (N, K) -> uint8 (N, K/256*210).  Symmetric per 16-element group."""
+    N, K = w.shape
+    assert K % 256 == 0
+    nb = K // 256
+    x = w.astype(np.float32).reshape(N, nb, 16, 16)
+    gscale = np.abs(x).max(-1) / 31.0
+    d = (gscale.max(-1) / 127.0).astype(np.float16)
+    df = d.astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        sc = np.where(df[..., None] > 0, np.rint(gscale / df[..., None]), 0).clip(0, 127)
+        step = df[..., None] * sc
+        q = np.where(step[..., None] > 0, np.rint(x / step[..., None]), 0)
+    L = (q.clip(-32, 31) + 32).astype(np.uint8).reshape(N, nb, 2, 4, 32)  # [half n][run j][l]
+    out = np.empty((N, nb, 210), np.uint8)
+    ql = np.empty((N, nb, 2, 64), np.uint8)
+    ql[..., 0:32] = (L[..., 0, :] & 0xF) | ((L[..., 2, :] & 0xF) << 4)
+    ql[..., 32:64] = (L[..., 1, :] & 0xF) | ((L[..., 3, :] & 0xF) << 4)
+    qh = (L[..., 0, :] >> 4) | ((L[..., 1, :] >> 4) << 2) | ((L[..., 2, :] >> 4) << 4) | ((L[..., 3, :] >> 4) << 6)
+    out[..., 0:128] = ql.reshape(N, nb, 128)
+    out[..., 128:192] = qh.reshape(N, nb, 64)
+    out[..., 192:208] = sc.astype(np.int8).view(np.uint8)
+    out[..., 208:210] = d.view(np.uint8).reshape(N, nb, 2)
+    return out.reshape(N, nb * 210)
+
+
+def quantize(wtype: int, w: np.ndarray) -> np.ndarray:
+    return quantize_q4_k(w) if wtype == Q4_K else quantize_q6_k(w)
+
+
+# ------------------------------------------------------------------ models
+
+QWEN25_3B = dict(arch="qwen2", n_layer=36, n_embd=2048, n_head=16, n_kv=2, head_dim=128, n_ff=11008,
+                 n_vocab=151936, rope_theta=1e6, eps=1e-6, tied=True, qkv_bias=True)
+QWEN25_32B = dict(arch="qwen2", n_layer=64, n_embd=5120, n_head=40, n_kv=8, head_dim=128, n_ff=27648,
+                  n_vocab=152064, rope_theta=1e6, eps=1e-6, tied=False, qkv_bias=True)
+TINY_DENSE = dict(arch="qwen2", n_layer=2, n_embd=256, n_head=4, n_kv=2, head_dim=64, n_ff=512,
+                  n_vocab=320, rope_theta=1e6, eps=1e-6, tied=True, qkv_bias=True)
+
+
+def dense_tensor_plan(cfg: dict) -> list[tuple[str, int, int, int]]:
+    """(name, ggml_type, K, N) of every matrix of a dense decoder in the Q4_K_M mix used by the
+    benchmark configurations: Q6_K for token_embd / output, attn_v and ffn_down, Q4_K elsewhere."""
+    K, H, Hkv, hd, FF, V = (cfg[k] for k in ("n_embd", "n_head", "n_kv", "head_dim", "n_ff", "n_vocab"))
+    plan = [("token_embd.weight", Q6_K, K, V)]
+    if not cfg.get("tied", True):
+        plan.append(("output.weight", Q6_K, K, V))
+    for i in range(cfg["n_layer"]):
+        p = f"blk.{i}."
+        plan += [(p + "attn_q.weight", Q4_K, K, H * hd), (p + "attn_k.weight", Q4_K, K, Hkv * hd),
+                 (p + "attn_v.weight", Q6_K, K, Hkv * hd), (p + "attn_output.weight", Q4_K, H * hd, K),
+                 (p + "ffn_gate.weight", Q4_K, K, FF), (p + "ffn_up.weight", Q4_K, K, FF),
+                 (p + "ffn_down.weight", Q6_K, FF, K)]
+    return plan
+
+
+def dense_vector_plan(cfg: dict) -> list[tuple[str, int, str]]:
+    """(name, length, kind) of every fp32 vector; kind 'norm' -> ones, 'bias' -> N(0, 0.02)."""
+    K, H, Hkv, hd = (cfg[k] for k in ("n_embd", "n_head", "n_kv", "head_dim"))
+    plan = [("output_norm.weight", K, "norm")]
+    for i in range(cfg["n_layer"]):
+        p = f"blk.{i}."
+        plan += [(p + "attn_norm.weight", K, "norm"), (p + "ffn_norm.weight", K, "norm")]
+        if cfg.get("qkv_bias", False):
+            plan += [(p + "attn_q.bias", H * hd, "bias"), (p + "attn_k.bias", Hkv * hd, "bias"),
+                     (p + "attn_v.bias", Hkv * hd, "bias")]
+    return plan
+
+
+def make_dense_model(cfg: dict, seed: int = 0, sigma: float = 0.02) -> dict:
+    """Whole dense model on the host: name -> (type, K, N, uint8 bytes) or fp32 vector.
+    Only for sizes numpy handles in seconds; full-size models are generated on the GPU."""
+    rng = np.random.default_rng(seed)
+    tensors: dict = {}
+    for name, t, K, N in dense_tensor_plan(cfg):
+        w = rng.normal(0.0, sigma, size=(N, K)).astype(np.float32)
+        tensors[name] = (t, K, N, np.ascontiguousarray(quantize(t, w).reshape(-1)))
+    for name, n, kind in dense_vector_plan(cfg):
+        tensors[name] = np.ones(n, np.float32) if kind == "norm" else rng.normal(0, sigma, n).astype(np.float32)
+    return tensors
