@@ -1,0 +1,168 @@
+/*
+ * tarafer_b200 — C ABI of the B200-native batch-1 decode engine.
+ *
+ * The reference has no C ABI: its seam is the Rust-internal API of crates/core/src/cuda
+ * (CudaModel / CudaKv).  Each entry point below names the reference item it stands in for
+ * (paths relative to the reference project root), so that a Rust `extern "C"` module with
+ * the reference's own method signatures can be a thin wrapper over this library.
+ *
+ * Conventions: every call returns 0 on success or a negative TFR_E_* code and never
+ * throws or aborts; tfr_last_error() gives the message of the last failure on that
+ * engine.  An engine is not thread-safe — the caller serialises access exactly as the
+ * reference does (crates/cli/src/serve/mod.rs:28-32).  All device work runs on one CUDA
+ * stream per engine.  After tfr_alloc_kv no call on the decode path allocates device
+ * memory (crates/core/src/cuda/load.rs:547-607, "zero-allocation forward loop").
+ * The library has no CPU fallback: without a usable CUDA device tfr_create fails.
+ */
+#ifndef TARAFER_B200_H
+#define TARAFER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TFR_OK 0
+#define TFR_E_INVALID (-1)  /* bad argument / shape / state */
+#define TFR_E_CUDA (-2)     /* a CUDA call failed */
+#define TFR_E_FULL (-3)     /* "context full", crates/core/src/cuda/forward.rs:46-48 */
+#define TFR_E_EMPTY (-4)    /* "empty tokens", crates/core/src/cuda/forward.rs:43-45 */
+#define TFR_E_UNSUPPORTED (-5)
+
+/* ggml tensor type ids, crates/gguf/src/types.rs:7-60 */
+#define TFR_TYPE_F32 0
+#define TFR_TYPE_Q4_K 12
+#define TFR_TYPE_Q6_K 14
+
+typedef struct tfr_engine tfr_engine;
+typedef struct tfr_kv tfr_kv;
+typedef struct tfr_mat tfr_mat;
+
+/* Fields of ModelConfig, crates/core/src/config.rs:67-104 (GGUF keys: config.rs:107-264). */
+typedef struct {
+    int32_t n_layer;        /* block_count */
+    int32_t n_embd;         /* embedding_length */
+    int32_t n_head;         /* attention.head_count */
+    int32_t n_kv_head;      /* attention.head_count_kv */
+    int32_t head_dim;       /* attention.key_length */
+    int32_t n_ff;           /* feed_forward_length */
+    int32_t n_vocab;        /* vocab_size */
+    int32_t context_length; /* context_length */
+    float rope_theta;       /* rope.freq_base */
+    float rms_eps;          /* attention.layer_norm_rms_epsilon */
+    int32_t hybrid;         /* 0 dense (qwen2), 1 Gated-DeltaNet hybrid (qwen35), backend.rs:19-31 */
+    int32_t rope_dim;       /* rope.dimension_count (hybrid), 0 = head_dim */
+    int32_t ssm_conv_kernel;
+    int32_t ssm_state_size;
+    int32_t ssm_group_count;     /* K/Q heads of the linear layers */
+    int32_t ssm_time_step_rank;  /* V heads of the linear layers */
+    int32_t ssm_inner_size;
+    int32_t full_attention_interval; /* layer i is full attention iff (i+1) % interval == 0 */
+    int32_t tp_rank;        /* tensor-parallel rank of this engine (0 when tp_size == 1) */
+    int32_t tp_size;        /* 1 = single GPU */
+} tfr_model_config;
+
+/* ---- engine lifetime: CudaModel::load_with, crates/core/src/cuda/load.rs:166-609 ---- */
+
+/* init_device (crates/core/src/cuda/device.rs:84-142) without NVRTC: kernels are ahead-of-time sm_100a code. */
+int tfr_create(int device_ordinal, tfr_engine** out);
+void tfr_destroy(tfr_engine* e);
+const char* tfr_last_error(const tfr_engine* e);
+/* gpu_name / compute_major / compute_minor fields of CudaModel, model.rs:19-29 */
+int tfr_device_info(const tfr_engine* e, char* name, size_t name_cap, int* cc_major, int* cc_minor, int* sm_count);
+
+int tfr_set_config(tfr_engine* e, const tfr_model_config* cfg);
+/* upload_mat / upload_vec, load.rs:135-143 and 203-260.  Called once per GGUF tensor with
+ * the tensor's name (load.rs:280-417), ggml type, dims[0] = n_rows (K, contiguous) and
+ * dims[1] = n_cols (N; 1 for vectors) and the raw bytes.  `bytes` may be host or device
+ * memory; the library copies (and re-orders Q6_K rows for aligned loads) — the caller keeps
+ * ownership and may unmap the file after tfr_finalize_load. */
+int tfr_upload_tensor(tfr_engine* e, const char* name, int ggml_type, int64_t n_rows, int64_t n_cols, const void* bytes,
+                      size_t nbytes);
+/* End of load_with: checks every tensor the configuration needs is present, allocates workspaces. */
+int tfr_finalize_load(tfr_engine* e);
+
+/* ---- KV cache: CudaKv, crates/core/src/cuda/kv.rs:6-42; alloc_kv model.rs:114-162 ---- */
+int tfr_alloc_kv(tfr_engine* e, int max_seq, tfr_kv** out);
+void tfr_free_kv(tfr_kv* kv);
+int tfr_kv_len(const tfr_kv* kv);                 /* CudaKv::len */
+int tfr_kv_max_seq(const tfr_kv* kv);             /* CudaKv::max_seq */
+int tfr_kv_set_len(tfr_kv* kv, int len);          /* callers assign cache.len, session.rs:345 */
+int tfr_kv_clear(tfr_kv* kv);                     /* CudaKv::clear */
+int64_t tfr_kv_bytes_per_token(const tfr_kv* kv); /* CudaKv::bytes_per_token */
+int tfr_zero_recurrent(tfr_engine* e, tfr_kv* kv); /* CudaModel::zero_recurrent, model.rs:165-194 */
+
+/* ---- token loop ---- */
+/* CudaModel::forward_greedy, forward.rs:42-71: feeds n tokens at positions kv.len.., returns the
+ * greedy next token, advances kv.len by n.  n == 0 -> TFR_E_EMPTY, overflow -> TFR_E_FULL.
+ * Prompts (n > 1) are fed through the decode kernels one position at a time. */
+int tfr_forward_greedy(tfr_engine* e, tfr_kv* kv, const uint32_t* tokens, int n, uint32_t* next_token);
+/* The on-device loop that replaces the per-token host round-trip of session.rs:288-368 /
+ * forward.rs:73-105: starting from first_token at position kv.len, runs up to max_n decode
+ * steps, each feeding the previous step's argmax, without returning to the host.  Stops
+ * after emitting one of stop_ids (n_stop <= 8) or when the cache is full.  out receives the
+ * emitted tokens, *n_out their count; kv.len advances by *n_out. */
+int tfr_decode_burst(tfr_engine* e, tfr_kv* kv, uint32_t first_token, int max_n, const uint32_t* stop_ids, int n_stop,
+                     uint32_t* out, int* n_out);
+/* CudaModel::current_logits, forward.rs:20-39: logits of the last decoded position. */
+int tfr_current_logits(tfr_engine* e, float* out, int n);
+/* set_cuda_graph / graph_active / invalidate_decode_graph, model.rs:101-112,197 */
+int tfr_set_cuda_graph(tfr_engine* e, int enabled);
+int tfr_graph_active(const tfr_engine* e);
+/* Kernel launches issued by this engine so far (graph replays count their kernel nodes). */
+int64_t tfr_launch_count(const tfr_engine* e);
+/* Device time of the last tfr_decode_burst / tfr_forward_greedy in milliseconds (CUDA events
+ * on the engine's stream, around the kernels only). */
+float tfr_last_device_ms(const tfr_engine* e);
+/* Test tap: copy a named workspace of the last step to the host ("x", "q", "attn", "h", "logits"). */
+int tfr_debug_read(tfr_engine* e, tfr_kv* kv, const char* what, int layer, void* out, size_t nbytes);
+
+/* ---- operator level (device pointers unless stated; stream = cudaStream_t or NULL) ---- */
+
+/* GpuMat, crates/core/src/cuda/types.rs:26-39: a weight matrix resident on the device in
+ * decode layout.  rope_pair_head_dim > 0 re-orders rows so RoPE partners are adjacent. */
+int tfr_mat_create(int ggml_type, int64_t n_rows, int64_t n_cols, const void* bytes, size_t nbytes,
+                   int rope_pair_head_dim, tfr_mat** out);
+void tfr_mat_free(tfr_mat* m);
+int64_t tfr_mat_device_bytes(const tfr_mat* m);
+
+/* quantize_q8_global, kernels/gemv.cu:43-65 */
+int tfr_op_quantize_q8(const float* x, int n, int8_t* q8, float* d8, void* stream);
+/* gemv / try_gemv_global_q8, crates/core/src/cuda/matmul.rs:118-302.  act_mode 0: Q8
+ * activation; 1: fp32 activation (Q6_K only; the reference's attn_v route).  use_res 2:
+ * out += W x.  norm_w != NULL applies RMSNorm (kernels/ops.cu:4-34) to x first. */
+int tfr_op_gemv(const tfr_mat* w, const float* x, float* out, const float* bias, int use_res, int act_mode,
+                const float* norm_w, float eps, void* stream);
+/* gemv_q4_k_ffn_mcol, kernels/gemv.cu:2546-2575 (+ optional RMSNorm in front) */
+int tfr_op_ffn_gate_up(const tfr_mat* gate, const tfr_mat* up, const float* x, const float* norm_w, float eps, float* h,
+                       void* stream);
+/* The FFN block of ffn_block_dense (layer.rs:1210-1456) at n_tok = 1 without the norm:
+ * y (+)= down . Q8(silu(gate . Q8(x)) * (up . Q8(x))).  h_scratch: n_ff floats. */
+int tfr_op_ffn_block(const tfr_mat* gate, const tfr_mat* up, const tfr_mat* down, const float* x, float* h_scratch,
+                     float* y, int use_res, void* stream);
+/* Same with HOST buffers: copies x in, runs the two kernels, copies y out, synchronises. */
+int tfr_ffn_block_host(const tfr_mat* gate, const tfr_mat* up, const tfr_mat* down, const float* x_host, float* y_host);
+/* Integer contract taps (test aid, no reference kernel exposes these): for Q4_K, a = I[N][K/32]
+ * and b = S[N][K/32] of kernels/gemv.cu:71-130; for Q6_K, a = J[N][K/16] of gemv.cu:302-337. */
+int tfr_op_int_dots(const tfr_mat* w, const int8_t* q8, const float* d8, int32_t* a, int32_t* b, void* stream);
+/* attn_flash_partial + attn_flash_reduce, kernels/attn/flash.cu:16-255, for one query token
+ * at position pos over cache rows [0, pos].  kc / vc: [max_seq][n_kv*head_dim] f16 bits. */
+int tfr_op_attention(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv,
+                     int head_dim, int pos, void* stream);
+/* Fused attention front end: RMSNorm + Q8 + Q/K/V projections + bias + RoPE + f16 KV store
+ * (rms_norm_f32, gemv_q4_k_pair, gemv_q6_k, rope_neox_f32, copy_kv_f16; layer.rs:196-600).
+ * wq / wk must have been created with rope_pair_head_dim = head_dim; biases natural order. */
+int tfr_op_qkv_rope_store(const tfr_mat* wq, const tfr_mat* wk, const tfr_mat* wv, const float* bq, const float* bk,
+                          const float* bv, const float* x, const float* norm_w, float eps, float theta, int head_dim,
+                          int pos, float* q_out, uint16_t* kc, uint16_t* vc, void* stream);
+
+/* Synthetic-model aid (no counterpart in the reference, which has no quantiser): quantise
+ * fp32 rows [N][K] on the device into GGUF Q4_K / Q6_K bytes. */
+int tfr_synth_quantize(int ggml_type, const float* w, int64_t n_rows_k, int64_t n_cols_n, void* out_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

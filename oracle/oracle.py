@@ -136,7 +136,9 @@ def mat(wtype: int, data: np.ndarray, K: int, N: int) -> Mat:
     """Wrap raw GGUF bytes (uint8 array that the caller keeps alive) as a matrix."""
     assert data.dtype == np.uint8 and data.flags["C_CONTIGUOUS"]
     assert data.size == N * (K // 256) * BLOCK_BYTES[wtype], (data.size, N, K, wtype)
-    return Mat(wtype, K, N, 0, _p(data))
+    m = Mat(wtype, K, N, 0, _p(data))
+    m._keep = data  # the struct only holds the address
+    return m
 
 
 def dequant_rows(wtype: int, data: np.ndarray, K: int, N: int) -> np.ndarray:

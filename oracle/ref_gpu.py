@@ -1,0 +1,293 @@
+"""Launcher for the reference's own CUDA kernels (test infrastructure, GPU box only).
+
+oracle/Makefile compiles the reference's .cu fragments, unmodified and with the
+reference's NVRTC options, into oracle/_ref/ref_kernels.cubin.  This module loads that
+cubin through the CUDA driver API (ctypes on libcuda) and launches the kernels with the
+reference's grid / block / shared-memory recipes (crates/core/src/cuda/matmul.rs,
+layer.rs; each helper cites its recipe) on torch-allocated device buffers.  It defines
+"what the reference computes" on the very same B200: the bit-exact target for the int8
+activation quantiser and the tolerance target for logits.
+
+Only tests/, the smoke check and bench.py's reference-side measurements may use it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+CUBIN = HERE / "_ref" / "ref_kernels.cubin"
+Q4_K, Q6_K = 12, 14
+
+
+def available() -> bool:
+    return CUBIN.exists() and torch.cuda.is_available()
+
+
+class RefKernels:
+    def __init__(self):
+        if not available():
+            raise RuntimeError("reference cubin or GPU missing")
+        torch.cuda.init()
+        torch.zeros(1, device="cuda")  # make sure the primary context is current
+        self.cu = C.CDLL("libcuda.so.1")
+        self.mod = C.c_void_p()
+        data = CUBIN.read_bytes()
+        self._img = C.create_string_buffer(data, len(data))
+        self._chk(self.cu.cuModuleLoadData(C.byref(self.mod), self._img), "cuModuleLoadData")
+        self._fn = {}
+        self.launches = 0
+
+    def _chk(self, rc, what):
+        if rc != 0:
+            raise RuntimeError(f"{what} failed with CUresult {rc}")
+
+    def fn(self, name: str):
+        if name not in self._fn:
+            f = C.c_void_p()
+            self._chk(self.cu.cuModuleGetFunction(C.byref(f), self.mod, name.encode()), f"cuModuleGetFunction({name})")
+            self._fn[name] = f
+        return self._fn[name]
+
+    def launch(self, name, grid, block, smem, *args):
+        """args: torch tensors (device pointer), python ints (int32) or floats (float32)."""
+        vals = []
+        for a in args:
+            if isinstance(a, torch.Tensor):
+                vals.append(C.c_void_p(a.data_ptr()))
+            elif isinstance(a, float):
+                vals.append(C.c_float(a))
+            else:
+                vals.append(C.c_int(int(a)))
+        arr = (C.c_void_p * len(vals))(*[C.cast(C.pointer(v), C.c_void_p) for v in vals])
+        g = tuple(grid) + (1,) * (3 - len(grid))
+        b = tuple(block) + (1,) * (3 - len(block))
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        self._chk(self.cu.cuLaunchKernel(self.fn(name), *[C.c_uint(x) for x in g], *[C.c_uint(x) for x in b],
+                                         C.c_uint(smem), stream, arr, None), f"cuLaunchKernel({name})")
+        self.launches += 1
+
+
+_K = None
+
+
+def kernels() -> RefKernels:
+    global _K
+    if _K is None:
+        _K = RefKernels()
+    return _K
+
+
+def dev(a, dtype=None) -> torch.Tensor:
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.cuda()
+
+
+def compact_q6(raw: np.ndarray, K: int, N: int) -> np.ndarray:
+    """crates/core/src/cuda/load.rs:145-159: pad every 210-byte block to 212 bytes."""
+    nb = K // 256
+    out = np.zeros((N * nb, 212), np.uint8)
+    out[:, :210] = raw.reshape(N * nb, 210)
+    return out.reshape(-1)
+
+
+class RefMat:
+    """GpuMat as the reference loader holds it (types.rs:26-39): raw bytes, plus the 212-byte
+    compact copy for Q6_K (load.rs:240-259)."""
+
+    def __init__(self, wtype: int, K: int, N: int, raw: np.ndarray):
+        self.type, self.K, self.N = wtype, K, N
+        nb = K // 256
+        self.col_bytes = nb * (144 if wtype == Q4_K else 210)
+        self.data = dev(raw)
+        self.compact = dev(compact_q6(raw, K, N)) if wtype == Q6_K else None
+        self.compact_col_bytes = nb * 212
+
+
+# ------------------------------------------------------------------ single kernels
+
+def quantize_q8(x: torch.Tensor):
+    """quantize_q8, matmul.rs:47-70."""
+    n = x.numel()
+    q = torch.zeros(n, dtype=torch.int8, device="cuda")
+    d = torch.zeros(n // 32, dtype=torch.float32, device="cuda")
+    groups = (n + 31) // 32
+    kernels().launch("quantize_q8_global", ((groups + 7) // 8,), (256,), 0, x, q, d, n)
+    return q, d
+
+
+def rms_norm(x, w, eps):
+    """layer.rs rms_norm launch: grid n_tok x 256 (ops.cu:4-34)."""
+    out = torch.empty_like(x)
+    kernels().launch("rms_norm_f32", (1,), (256,), 0, x, w, out, x.numel(), 1, float(eps))
+    return out
+
+
+def gemv_q8(m: RefMat, x, out=None, bias=None, use_res=0, warps=16):
+    """try_gemv_global_q8, matmul.rs:142-302, for K < 4096 and the tall-K 8-way Q6_K case."""
+    if out is None:
+        out = torch.zeros(m.N, dtype=torch.float32, device="cuda")
+    q, d = quantize_q8(x)
+    b = bias if bias is not None else x
+    smem = m.K + (m.K // 32) * 4
+    if m.type == Q4_K:
+        if m.K >= 4096:
+            raise NotImplementedError("split-K Q4_K route not wired in the harness")
+        kernels().launch("gemv_q4_k_global", ((m.N + warps - 1) // warps,), (warps * 32,), smem, m.data, q, d, out,
+                         m.K, m.N, m.col_bytes, int(bias is not None), b, use_res, x)
+    elif m.K >= 4096:
+        kernels().launch("gemv_q6_k_compact_global_8way", (m.N,), (256,), 0, m.compact, q, d, out, m.K, m.N,
+                         m.compact_col_bytes, int(bias is not None), b, use_res, x)
+    else:
+        kernels().launch("gemv_q6_k_compact_global", ((m.N + warps - 1) // warps,), (warps * 32,), smem, m.compact, q,
+                         d, out, m.K, m.N, m.compact_col_bytes, int(bias is not None), b, use_res, x)
+    return out
+
+
+def gemv_q6_f32(m: RefMat, x, bias=None):
+    """gemv_baseline for Q6_K, matmul.rs:346-412 (lc_q5_gemv): fp32 activations."""
+    assert m.type == Q6_K and m.K < 4096
+    out = torch.zeros(m.N, dtype=torch.float32, device="cuda")
+    b = bias if bias is not None else x
+    kernels().launch("gemv_q6_k", ((m.N + 7) // 8,), (256,), m.K * 4, m.data, x, out, m.K, m.N, m.col_bytes,
+                     int(bias is not None), b, 0, x)
+    return out
+
+
+def gemv_q4_pair(wa: RefMat, wb: RefMat, x, ba=None, bb=None):
+    """try_gemv_q4_pair, matmul.rs:727-784."""
+    q, d = quantize_q8(x)
+    oa = torch.zeros(wa.N, dtype=torch.float32, device="cuda")
+    ob = torch.zeros(wb.N, dtype=torch.float32, device="cuda")
+    both = ba is not None and bb is not None
+    kernels().launch("gemv_q4_k_pair", (wa.N + wb.N,), (64,), 0, wa.data, wb.data, q, d, oa, ob, wa.K, wa.N, wb.N,
+                     wa.col_bytes, int(both), ba if both else x, bb if both else x)
+    return oa, ob
+
+
+def ffn_gate_up(gate: RefMat, up: RefMat, x):
+    """gemv_q4_k_ffn_mcol, matmul.rs:680-725: grid ceil(ff/32) x 1024, smem K + K/8."""
+    out = torch.zeros(gate.N, dtype=torch.float32, device="cuda")
+    kernels().launch("gemv_q4_k_ffn_mcol", ((gate.N + 31) // 32,), (1024,), gate.K + gate.K // 8, gate.data, up.data,
+                     x, out, gate.K, gate.N, gate.col_bytes)
+    return out
+
+
+def rope(x, n_heads, hd, pos, theta):
+    """rope launch, layer.rs:~560-600: grid (heads, n_tok) x 32 (ops.cu:348-371)."""
+    kernels().launch("rope_neox_f32", (n_heads, 1), (32,), 0, x, n_heads, hd, pos, 1, float(theta))
+    return x
+
+
+def copy_kv(src, cache, pos, stride):
+    """copy_kv launch (LaunchConfig::for_num_elems: 1024-thread blocks), ops.cu:471-486."""
+    kernels().launch("copy_kv_f16", ((stride + 1023) // 1024,), (1024,), 0, src, cache, pos, 1, stride)
+
+
+def attention(q, kc, vc, n_head, n_kv, hd, pos):
+    """launch_attn flash route, layer.rs:2040-2121: partial grid (n_head, 8) x 128, smem (hd+64)*4;
+    reduce grid n_head x hd."""
+    partial = torch.zeros(n_head * 8 * (2 + hd), dtype=torch.float32, device="cuda")
+    out = torch.zeros(n_head * hd, dtype=torch.float32, device="cuda")
+    scale = float(1.0 / np.sqrt(np.float32(hd)))
+    kernels().launch("attn_flash_partial", (n_head, 8, 1), (128,), (hd + 64) * 4, q, kc, vc, partial, n_head, n_kv, hd,
+                     pos, 1, 8, scale)
+    kernels().launch("attn_flash_reduce", (n_head, 1), (hd,), 0, partial, out, n_head, hd, 8, 1)
+    return out
+
+
+def argmax(x):
+    out = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kernels().launch("argmax_f32", (1,), (256,), 0, x, x.numel(), out)
+    return out
+
+
+def embed(table: RefMat, token: int):
+    out = torch.zeros(table.K, dtype=torch.float32, device="cuda")
+    name = "embed_q6_k_one" if table.type == Q6_K else "embed_q4_k_one"
+    kernels().launch(name, (1,), (32,), 0, table.data, out, token, table.K, table.col_bytes)
+    return out
+
+
+# ------------------------------------------------------------------ whole dense model
+
+class RefModel:
+    """The reference's n_tok = 1 schedule (layer.rs:142-709, 1210-1456, 2125-2259) assembled
+    from its own kernels, for the BASELINE dense mix at K < 4096."""
+
+    def __init__(self, cfg: dict, tensors: dict, max_seq: int):
+        self.cfg, self.max_seq = cfg, max_seq
+        L = cfg["n_layer"]
+
+        def m(name):
+            t, K, N, data = tensors[name]
+            return RefMat(t, K, N, data)
+
+        def v(name):
+            return dev(tensors[name]) if name in tensors else None
+
+        self.embd = m("token_embd.weight")
+        self.head = m("output.weight") if "output.weight" in tensors else self.embd
+        self.out_norm = v("output_norm.weight")
+        self.layers = []
+        for i in range(L):
+            p = f"blk.{i}."
+            self.layers.append(dict(
+                wq=m(p + "attn_q.weight"), wk=m(p + "attn_k.weight"), wv=m(p + "attn_v.weight"),
+                wo=m(p + "attn_output.weight"), gate=m(p + "ffn_gate.weight"), up=m(p + "ffn_up.weight"),
+                down=m(p + "ffn_down.weight"), bq=v(p + "attn_q.bias"), bk=v(p + "attn_k.bias"),
+                bv=v(p + "attn_v.bias"), an=v(p + "attn_norm.weight"), fn=v(p + "ffn_norm.weight")))
+        kvn = cfg["n_kv"] * cfg["head_dim"]
+        self.kc = [torch.zeros(max_seq * kvn, dtype=torch.int16, device="cuda") for _ in range(L)]
+        self.vc = [torch.zeros(max_seq * kvn, dtype=torch.int16, device="cuda") for _ in range(L)]
+
+    def decode_token(self, pos: int, token: int, taps: dict | None = None) -> torch.Tensor:
+        c = self.cfg
+        H, Hkv, hd = c["n_head"], c["n_kv"], c["head_dim"]
+        kvn = Hkv * hd
+        x = embed(self.embd, token)
+        for li, L in enumerate(self.layers):
+            xb = rms_norm(x, L["an"], c["eps"])
+            q, k = gemv_q4_pair(L["wq"], L["wk"], xb, L["bq"], L["bk"])
+            if L["wv"].type == Q6_K:
+                v = gemv_q6_f32(L["wv"], xb, L["bv"])
+            else:
+                v = gemv_q8(L["wv"], xb, bias=L["bv"])
+            rope(q, H, hd, pos, c["rope_theta"])
+            rope(k, Hkv, hd, pos, c["rope_theta"])
+            copy_kv(k, self.kc[li], pos, kvn)
+            copy_kv(v, self.vc[li], pos, kvn)
+            if taps is not None and li == 0:
+                taps["q0"] = q.clone()
+            att = attention(q, self.kc[li], self.vc[li], H, Hkv, hd, pos)
+            if taps is not None and li == 0:
+                taps["attn0"] = att.clone()
+            gemv_q8(L["wo"], att, out=x, use_res=2)
+            xb = rms_norm(x, L["fn"], c["eps"])
+            h = ffn_gate_up(L["gate"], L["up"], xb)
+            if taps is not None and li == 0:
+                taps["h0"] = h.clone()
+            gemv_q8(L["down"], h, out=x, use_res=2)
+            if taps is not None and li == 0:
+                taps["x0"] = x.clone()
+        xb = rms_norm(x, self.out_norm, c["eps"])
+        logits = gemv_q8(self.head, xb)
+        if taps is not None:
+            taps["x"] = x.clone()
+        return logits
+
+    def decode_greedy(self, pos0: int, first: int, n: int):
+        toks, margins, tok = [], [], first
+        logits = None
+        for s in range(n):
+            logits = self.decode_token(pos0 + s, tok)
+            top2 = torch.topk(logits, 2)
+            tok = int(argmax(logits).item())
+            toks.append(tok)
+            margins.append(float(top2.values[0] - top2.values[1]))
+        return np.array(toks, np.int32), np.array(margins, np.float32), logits.cpu().numpy()

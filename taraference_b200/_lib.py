@@ -1,0 +1,82 @@
+"""ctypes view of libtarafer_b200.so.  There is no fallback: if the library is missing or
+cannot be loaded, importing a symbol raises."""
+from __future__ import annotations
+
+import ctypes as C
+import re
+from pathlib import Path
+
+from .build import LIB, PKG
+
+HEADER = PKG.parent / "include" / "tarafer_b200.h"
+
+
+class ModelConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n_layer", "n_embd", "n_head", "n_kv_head", "head_dim", "n_ff", "n_vocab",
+                                         "context_length")] + \
+               [("rope_theta", C.c_float), ("rms_eps", C.c_float)] + \
+               [(n, C.c_int32) for n in ("hybrid", "rope_dim", "ssm_conv_kernel", "ssm_state_size", "ssm_group_count",
+                                         "ssm_time_step_rank", "ssm_inner_size", "full_attention_interval",
+                                         "tp_rank", "tp_size")]
+
+
+def declared_symbols() -> list[str]:
+    """Every function name the public header declares."""
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(tfr_[a-z0-9_]+)\s*\(", text)))
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB.exists():
+        raise RuntimeError(f"{LIB} is not built; run `python -m taraference_b200.build` (needs nvcc). "
+                           "There is no CPU fallback.")
+    l = C.CDLL(str(LIB))
+    vp, i32, i64, f32, sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
+    sig = {
+        "tfr_create": (i32, [i32, C.POINTER(vp)]),
+        "tfr_destroy": (None, [vp]),
+        "tfr_last_error": (C.c_char_p, [vp]),
+        "tfr_device_info": (i32, [vp, C.c_char_p, sz, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32)]),
+        "tfr_set_config": (i32, [vp, C.POINTER(ModelConfig)]),
+        "tfr_upload_tensor": (i32, [vp, C.c_char_p, i32, i64, i64, vp, sz]),
+        "tfr_finalize_load": (i32, [vp]),
+        "tfr_alloc_kv": (i32, [vp, i32, C.POINTER(vp)]),
+        "tfr_free_kv": (None, [vp]),
+        "tfr_kv_len": (i32, [vp]),
+        "tfr_kv_max_seq": (i32, [vp]),
+        "tfr_kv_set_len": (i32, [vp, i32]),
+        "tfr_kv_clear": (i32, [vp]),
+        "tfr_kv_bytes_per_token": (i64, [vp]),
+        "tfr_zero_recurrent": (i32, [vp, vp]),
+        "tfr_forward_greedy": (i32, [vp, vp, vp, i32, C.POINTER(C.c_uint32)]),
+        "tfr_decode_burst": (i32, [vp, vp, C.c_uint32, i32, vp, i32, vp, C.POINTER(i32)]),
+        "tfr_current_logits": (i32, [vp, vp, i32]),
+        "tfr_set_cuda_graph": (i32, [vp, i32]),
+        "tfr_graph_active": (i32, [vp]),
+        "tfr_launch_count": (i64, [vp]),
+        "tfr_last_device_ms": (f32, [vp]),
+        "tfr_debug_read": (i32, [vp, vp, C.c_char_p, i32, vp, sz]),
+        "tfr_mat_create": (i32, [i32, i64, i64, vp, sz, i32, C.POINTER(vp)]),
+        "tfr_mat_free": (None, [vp]),
+        "tfr_mat_device_bytes": (i64, [vp]),
+        "tfr_op_quantize_q8": (i32, [vp, i32, vp, vp, vp]),
+        "tfr_op_gemv": (i32, [vp, vp, vp, vp, i32, i32, vp, f32, vp]),
+        "tfr_op_ffn_gate_up": (i32, [vp, vp, vp, vp, f32, vp, vp]),
+        "tfr_op_ffn_block": (i32, [vp, vp, vp, vp, vp, vp, i32, vp]),
+        "tfr_ffn_block_host": (i32, [vp, vp, vp, vp, vp]),
+        "tfr_op_int_dots": (i32, [vp, vp, vp, vp, vp, vp]),
+        "tfr_op_attention": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
+        "tfr_op_qkv_rope_store": (i32, [vp] * 8 + [f32, f32, i32, i32, vp, vp, vp, vp]),
+        "tfr_synth_quantize": (i32, [i32, vp, i64, i64, vp, vp]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(l, name)
+        fn.restype, fn.argtypes = res, args
+    _lib = l
+    return l

@@ -1,0 +1,238 @@
+// Split-KV flash-decode over the f16 KV cache, one query token.
+//
+// Reference: kernels/attn/flash.cu:16-116 (partial) and :222-255 (merge).  The reference
+// launches one CTA per (query head, split) with 8 fixed splits, so every query head
+// re-reads the K/V rows of its KV head.  Here one CTA serves ALL query heads that share a
+// KV head (GQA group), so each K/V row is read from HBM once per token; the number of
+// splits is sized to the SM count and shrinks for short contexts, and the CTA that
+// finishes last for a KV head merges the (m, l, O) partials itself (no second launch).
+// Arithmetic is fp32 on f16 data as in the reference; exp is the build's ex2-based expf.
+#pragma once
+#include "tfr_common.cuh"
+
+namespace tfr {
+
+constexpr int ATTN_THREADS = 256;
+constexpr int ATTN_TILE = 64;     // keys per tile
+constexpr int ATTN_REP_MAX = 8;   // query heads per KV head handled by one CTA
+
+struct AttnArgs {
+    const float* q;             // [n_head * hd], RoPE applied
+    const unsigned short* kc;   // layer base, [max_seq][n_kv * hd] f16 bits
+    const unsigned short* vc;
+    float* partial;             // [n_head][S][2 + hd]
+    unsigned int* counters;     // [n_kv], zero between launches
+    float* out;                 // [n_head * hd]
+    const float* gate;          // optional [n_head * hd]: out *= sigmoid(gate) (deltanet.cu:176-186)
+    int n_head, n_kv, S, min_keys;
+    float scale;
+    int pos;                    // used when st == nullptr
+};
+
+// After the five butterfly steps lane L holds the sum over all lanes of v[L].
+__device__ __forceinline__ float warp_transpose_reduce32(float (&v)[32], int lane) {
+#pragma unroll
+    for (int off = 16, n = 32; off >= 1; off >>= 1, n >>= 1) {
+        const bool up = (lane & off) != 0;
+#pragma unroll
+        for (int i = 0; i < n / 2; i++) {
+            const float send = up ? v[i] : v[i + n / 2];
+            const float keep = up ? v[i + n / 2] : v[i];
+            v[i] = keep + __shfl_xor_sync(TFR_FULL_MASK, send, off);
+        }
+    }
+    return v[0];
+}
+
+template <int HD>
+__global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const TokenState* st) {
+    if (st && st->done) return;
+    constexpr int DL = HD / 32;   // dims per lane in the score phase
+    constexpr int DPT = HD / 64;  // dims per thread in the value phase
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = blockIdx.x / a.S, s = blockIdx.x % a.S;
+    const int rep = a.n_head / a.n_kv;
+    const int kvdim = a.n_kv * HD;
+    const int T = (st ? st->pos : a.pos) + 1;
+    int S_eff = (T + a.min_keys - 1) / a.min_keys;
+    S_eff = S_eff < 1 ? 1 : (S_eff > a.S ? a.S : S_eff);
+    if (s >= S_eff) return;
+    const int chunk = (T + S_eff - 1) / S_eff;
+    const int t0 = s * chunk;
+    const int t1 = min(T, t0 + chunk);
+
+    __shared__ float sc[ATTN_REP_MAX][ATTN_TILE];
+    __shared__ float m_s[ATTN_REP_MAX], l_s[ATTN_REP_MAX], alpha_s[ATTN_REP_MAX];
+    __shared__ float ored[4][ATTN_REP_MAX][HD];
+    __shared__ int is_last_s;
+
+    // q fragment of every head of the group: dims lane*DL .. lane*DL+DL-1
+    float qr[ATTN_REP_MAX][DL];
+#pragma unroll
+    for (int h = 0; h < ATTN_REP_MAX; h++)
+#pragma unroll
+        for (int d = 0; d < DL; d++) qr[h][d] = h < rep ? a.q[(g * rep + h) * HD + lane * DL + d] : 0.f;
+    if (tid < ATTN_REP_MAX) {
+        m_s[tid] = -1e30f;
+        l_s[tid] = 0.f;
+    }
+    float o[ATTN_REP_MAX][DPT];
+#pragma unroll
+    for (int h = 0; h < ATTN_REP_MAX; h++)
+#pragma unroll
+        for (int d = 0; d < DPT; d++) o[h][d] = 0.f;
+    __syncthreads();
+
+    const int kg = tid >> 6, dp = tid & 63;
+    for (int tt = t0; tt < t1; tt += ATTN_TILE) {
+        // ---- scores: each warp takes two batches of four keys
+#pragma unroll
+        for (int bt = 0; bt < 2; bt++) {
+            const int kbase = (warp * 2 + bt) * 4;
+            float v[32];
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++) {
+                const int t = tt + kbase + kk;
+                float kf[DL];
+                if (t < t1) {
+                    const unsigned short* kr = a.kc + (size_t)t * kvdim + g * HD + lane * DL;
+                    if constexpr (DL == 4) {
+                        const uint2 raw = *reinterpret_cast<const uint2*>(kr);
+                        kf[0] = f16_to_f32((unsigned short)(raw.x & 0xffff));
+                        kf[1] = f16_to_f32((unsigned short)(raw.x >> 16));
+                        kf[2] = f16_to_f32((unsigned short)(raw.y & 0xffff));
+                        kf[3] = f16_to_f32((unsigned short)(raw.y >> 16));
+                    } else if constexpr (DL == 8) {
+                        const uint4 raw = *reinterpret_cast<const uint4*>(kr);
+                        const unsigned int rw[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                        for (int d = 0; d < 4; d++) {
+                            kf[2 * d] = f16_to_f32((unsigned short)(rw[d] & 0xffff));
+                            kf[2 * d + 1] = f16_to_f32((unsigned short)(rw[d] >> 16));
+                        }
+                    } else {
+#pragma unroll
+                        for (int d = 0; d < DL; d++) kf[d] = f16_to_f32(kr[d]);
+                    }
+                } else {
+#pragma unroll
+                    for (int d = 0; d < DL; d++) kf[d] = 0.f;
+                }
+#pragma unroll
+                for (int h = 0; h < ATTN_REP_MAX; h++) {
+                    float acc = 0.f;
+#pragma unroll
+                    for (int d = 0; d < DL; d++) acc += qr[h][d] * kf[d];
+                    v[kk * 8 + h] = acc;
+                }
+            }
+            const float tot = warp_transpose_reduce32(v, lane);
+            const int kk = lane >> 3, h = lane & 7;
+            const int t = tt + kbase + kk;
+            sc[h][kbase + kk] = (t < t1 && h < rep) ? tot * a.scale : -1e30f;
+        }
+        __syncthreads();
+        // ---- online softmax bookkeeping: warp h owns head h
+        if (warp < rep) {
+            const float s0 = sc[warp][lane], s1 = sc[warp][lane + 32];
+            const float tile_m = warp_max(fmaxf(s0, s1));
+            const float m_old = m_s[warp];
+            const float m_new = fmaxf(m_old, tile_m);
+            const float p0 = (tt + lane < t1) ? expf(s0 - m_new) : 0.f;
+            const float p1 = (tt + lane + 32 < t1) ? expf(s1 - m_new) : 0.f;
+            const float tile_l = warp_sum(p0 + p1);
+            sc[warp][lane] = p0;
+            sc[warp][lane + 32] = p1;
+            if (lane == 0) {
+                const float alpha = expf(m_old - m_new);
+                alpha_s[warp] = alpha;
+                l_s[warp] = l_s[warp] * alpha + tile_l;
+                m_s[warp] = m_new;
+            }
+        }
+        __syncthreads();
+        // ---- values: thread (kg, dp) accumulates keys kg, kg+4, ... for dims dp*DPT..
+#pragma unroll
+        for (int h = 0; h < ATTN_REP_MAX; h++) {
+            const float al = h < rep ? alpha_s[h] : 1.f;
+#pragma unroll
+            for (int d = 0; d < DPT; d++) o[h][d] *= al;
+        }
+        const int tn = min(ATTN_TILE, t1 - tt);
+        for (int k = kg; k < tn; k += 4) {
+            const unsigned short* vr = a.vc + (size_t)(tt + k) * kvdim + g * HD + dp * DPT;
+            float vf[DPT];
+            if constexpr (DPT == 2) {
+                const unsigned int raw = *reinterpret_cast<const unsigned int*>(vr);
+                vf[0] = f16_to_f32((unsigned short)(raw & 0xffff));
+                vf[1] = f16_to_f32((unsigned short)(raw >> 16));
+            } else if constexpr (DPT == 4) {
+                const uint2 raw = *reinterpret_cast<const uint2*>(vr);
+                vf[0] = f16_to_f32((unsigned short)(raw.x & 0xffff));
+                vf[1] = f16_to_f32((unsigned short)(raw.x >> 16));
+                vf[2] = f16_to_f32((unsigned short)(raw.y & 0xffff));
+                vf[3] = f16_to_f32((unsigned short)(raw.y >> 16));
+            } else {
+#pragma unroll
+                for (int d = 0; d < DPT; d++) vf[d] = f16_to_f32(vr[d]);
+            }
+#pragma unroll
+            for (int h = 0; h < ATTN_REP_MAX; h++) {
+                if (h < rep) {
+                    const float p = sc[h][k];
+#pragma unroll
+                    for (int d = 0; d < DPT; d++) o[h][d] += p * vf[d];
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    // ---- combine the four key groups and write this split's (m, l, O)
+#pragma unroll
+    for (int h = 0; h < ATTN_REP_MAX; h++)
+#pragma unroll
+        for (int d = 0; d < DPT; d++) ored[kg][h][dp * DPT + d] = o[h][d];
+    __syncthreads();
+    const int po = 2 + HD;
+    for (int idx = tid; idx < rep * HD; idx += ATTN_THREADS) {
+        const int h = idx / HD, d = idx % HD;
+        const float tot = ored[0][h][d] + ored[1][h][d] + ored[2][h][d] + ored[3][h][d];
+        float* base = a.partial + ((size_t)(g * rep + h) * a.S + s) * po;
+        base[2 + d] = tot;
+        if (d == 0) {
+            base[0] = m_s[h];
+            base[1] = l_s[h];
+        }
+    }
+    // ---- last CTA of this KV head merges (flash.cu:222-255)
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned int old = atomicAdd(&a.counters[g], 1u);
+        is_last_s = (old == (unsigned int)(S_eff - 1));
+        if (is_last_s) a.counters[g] = 0u;
+    }
+    __syncthreads();
+    if (!is_last_s) return;
+    __threadfence();
+    for (int idx = tid; idx < rep * HD; idx += ATTN_THREADS) {
+        const int h = idx / HD, d = idx % HD;
+        const int hg = g * rep + h;
+        const float* hb = a.partial + (size_t)hg * a.S * po;
+        float m = -1e30f;
+        for (int ss = 0; ss < S_eff; ss++) m = fmaxf(m, __ldcg(hb + (size_t)ss * po));
+        float l = 0.f, acc = 0.f;
+        for (int ss = 0; ss < S_eff; ss++) {
+            const float* b = hb + (size_t)ss * po;
+            const float al = expf(__ldcg(b) - m);
+            l += al * __ldcg(b + 1);
+            acc += al * __ldcg(b + 2 + d);
+        }
+        float r = acc / fmaxf(l, 1e-20f);
+        if (a.gate) r *= 1.f / (1.f + expf(-a.gate[hg * HD + d]));
+        a.out[hg * HD + d] = r;
+    }
+}
+
+}  // namespace tfr

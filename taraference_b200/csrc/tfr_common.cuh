@@ -1,0 +1,106 @@
+// Shared device helpers for the sm_100a decode kernels.
+//
+// This translation unit is compiled with --use_fast_math, -ftz=true, -prec-div=false,
+// -prec-sqrt=false, -fmad=true: the options the reference hands NVRTC
+// (crates/core/src/cuda/device.rs:106-120).  Expressions written the same way as in the
+// reference kernels therefore lower to the same approximate instructions (div.approx,
+// ex2.approx, rsqrt.approx, sin/cos.approx), which is what makes the int8 activation
+// quantiser bit-identical to the reference build.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TFR_Q4_K 12
+#define TFR_Q6_K 14
+#define TFR_FULL_MASK 0xffffffffu
+
+namespace tfr {
+
+// kernels/common.cu:2-6
+__device__ __forceinline__ float f16_to_f32(unsigned short h) {
+    float o;
+    asm("cvt.f32.f16 %0, %1;" : "=f"(o) : "h"(h));
+    return o;
+}
+
+// kernels/common.cu:9-38: the KV-store rounding (round half up in magnitude).
+__device__ __forceinline__ unsigned short f32_to_f16_bits_ref(float f) {
+    unsigned int x = __float_as_uint(f);
+    unsigned int sign = (x >> 16) & 0x8000u;
+    unsigned int absx = x & 0x7fffffffu;
+    if (absx == 0u) return (unsigned short)sign;
+    if (absx >= 0x7f800000u) return (unsigned short)(sign | (absx == 0x7f800000u ? 0x7c00u : 0x7e00u));
+    if (absx < 0x33000000u) return (unsigned short)sign;
+    if (absx >= 0x47800000u) return (unsigned short)(sign | 0x7c00u);
+    int e = (int)((absx >> 23) & 0xff) - 127 + 15;
+    unsigned int mant = absx & 0x7fffffu;
+    if (e <= 0) {
+        if (e < -10) return (unsigned short)sign;
+        mant |= 0x800000u;
+        unsigned int shift = (unsigned int)(14 - e);
+        unsigned int hm = mant >> shift;
+        if ((mant >> (shift - 1)) & 1u) hm += 1u;
+        return (unsigned short)(sign | hm);
+    }
+    unsigned int half = ((unsigned int)e << 10) | (mant >> 13);
+    if (mant & 0x1000u) half += 1u;
+    return (unsigned short)(sign | half);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(TFR_FULL_MASK, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(TFR_FULL_MASK, v, o));
+    return v;
+}
+
+// Streaming 16-byte weight load: read-only path, do not keep in L1.
+__device__ __forceinline__ int4 ldg_stream(const void* p) {
+    int4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ int2 ldg_stream8(const void* p) {
+    int2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.s32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+
+// Device-resident decode state shared by every kernel of the token loop.  The host never
+// reads it while a burst is in flight; kernels read pos/token from here so one captured
+// graph serves every position (the reference's `_d` kernel variants do the same with
+// d_pos0 / d_token, crates/core/src/cuda/model.rs:71-73).
+struct TokenState {
+    int pos;        // position of the token being processed (= KV rows already filled)
+    int token;      // id of the token being processed
+    int step;       // tokens emitted so far in this burst
+    int max_steps;  // burst length
+    int done;       // set once a stop id was emitted or max_steps reached
+    int n_stop;
+    int stop_ids[8];
+    int err;                       // non-zero: a kernel saw an impossible state
+    unsigned int head_done;        // CTAs of the vocabulary head that have finished
+    unsigned long long best;       // packed (orderable logit, ~index) running argmax
+    int prompt_left;               // prompt tokens still to be fed (prefill by decode steps)
+    int prompt_idx;
+    int max_seq;                   // KV capacity; reaching it sets done
+    int pad_;
+};
+
+// Orderable 64-bit key: larger logit wins; on equal logits the lower index wins.
+__device__ __forceinline__ unsigned long long argmax_key(float v, int idx) {
+    unsigned int b = __float_as_uint(v);
+    b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    return ((unsigned long long)b << 32) | (unsigned long long)(0xffffffffu - (unsigned int)idx);
+}
+__device__ __forceinline__ int argmax_key_index(unsigned long long k) {
+    return (int)(0xffffffffu - (unsigned int)(k & 0xffffffffull));
+}
+
+}  // namespace tfr

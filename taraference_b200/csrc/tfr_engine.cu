@@ -1,0 +1,972 @@
+// Engine and C ABI of the B200 batch-1 decode library (see include/tarafer_b200.h).
+//
+// The layer schedule follows crates/core/src/cuda/layer.rs:142-709 (attention block),
+// :1210-1456 (dense FFN) and :2125-2259 (vocabulary head) at n_tok = 1, folded from the
+// reference's 16 launches per layer into five:
+//   1. RMSNorm + Q8 + Q/K/V (+bias) + RoPE + f16 KV store
+//   2. split-KV flash-decode with in-kernel merge
+//   3. Q8 + o-proj + residual
+//   4. RMSNorm + Q8 + gate/up + SiLU*mul
+//   5. Q8 + down + residual
+// plus one head kernel per token (RMSNorm + Q8 + lm_head + argmax + state advance); the
+// embedding lookup is folded into layer 0's first kernel.  Position and token live in
+// device memory (TokenState), so one captured CUDA graph per token is replayed back to
+// back for a whole burst without any host round-trip.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/tarafer_b200.h"
+#include "tfr_kernels.cuh"
+
+using namespace tfr;
+
+// ------------------------------------------------------------------ objects
+
+struct tfr_mat {
+    Mat m{};
+    void* dev = nullptr;
+    size_t bytes = 0;
+    int perm_hd = 0;
+};
+
+struct LayerW {
+    tfr_mat *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *gate = nullptr, *up = nullptr, *down = nullptr;
+    float* bias_qkv = nullptr;  // vrow order, or nullptr
+    float *attn_norm = nullptr, *ffn_norm = nullptr;
+};
+
+struct VecT {
+    float* dev = nullptr;
+    int64_t n = 0;
+};
+
+constexpr int TFR_MAX_BURST = 8192;
+constexpr int TFR_MAX_PROMPT = 65536;
+
+struct tfr_engine {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    cudaDeviceProp prop{};
+    std::string err;
+    tfr_model_config cfg{};
+    bool has_cfg = false, finalized = false;
+    std::map<std::string, tfr_mat*> mats;
+    std::map<std::string, VecT> vecs;
+    std::vector<LayerW> layers;
+    tfr_mat *token_embd = nullptr, *head = nullptr;
+    float* output_norm = nullptr;
+    // workspaces
+    float *x = nullptr, *q = nullptr, *attn = nullptr, *h = nullptr, *logits = nullptr, *partial = nullptr;
+    unsigned int* counters = nullptr;
+    TokenState* st = nullptr;
+    TokenState* st_host = nullptr;  // pinned
+    int *out_tokens = nullptr, *out_host = nullptr, *prompt = nullptr;
+    int attn_S = 1, attn_min_keys = 256;
+    // graphs
+    bool use_graph = true;
+    cudaGraphExec_t g_decode = nullptr, g_body = nullptr;
+    const tfr_kv* graph_kv = nullptr;
+    int nodes_decode = 0, nodes_body = 0;
+    int64_t launches = 0;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    float last_ms = 0.f;
+};
+
+struct tfr_kv {
+    tfr_engine* e = nullptr;
+    unsigned short *k = nullptr, *v = nullptr;
+    int len = 0, max_seq = 0;
+    size_t layer_stride = 0;  // elements
+};
+
+static int fail(tfr_engine* e, int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (e) e->err = buf;
+    return code;
+}
+
+#define CU(e, call)                                                                              \
+    do {                                                                                         \
+        cudaError_t _r = (call);                                                                 \
+        if (_r != cudaSuccess) return fail(e, TFR_E_CUDA, "%s: %s", #call, cudaGetErrorString(_r)); \
+    } while (0)
+
+static size_t raw_bytes(int type, int64_t K, int64_t N) {
+    int64_t nb = K / 256;
+    if (type == TFR_Q4_K) return (size_t)(N * nb * 144);
+    if (type == TFR_Q6_K) return (size_t)(N * nb * 210);
+    return 0;
+}
+
+static void configure_kernels_once() {
+    static bool done = false;
+    if (done) return;
+    done = true;
+    const int big = 160 * 1024;
+    cudaFuncSetAttribute(k_gemv<MapStack, EpiQkv>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    cudaFuncSetAttribute(k_gemv<MapSingle, EpiStore>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    cudaFuncSetAttribute(k_gemv<MapPair, EpiSilu>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    cudaFuncSetAttribute(k_gemv<MapSingle, EpiLogits>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    cudaFuncSetAttribute(k_int_dots, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+}
+
+static int sm_count_cached() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+// ------------------------------------------------------------------ matrices
+
+static int mat_create_impl(tfr_engine* e, int type, int64_t K, int64_t N, const void* bytes, size_t nbytes, int perm_hd,
+                           cudaStream_t stream, tfr_mat** out) {
+    if (type != TFR_Q4_K && type != TFR_Q6_K) return fail(e, TFR_E_UNSUPPORTED, "matrix type %d not supported", type);
+    if (K <= 0 || N <= 0 || K % 256) return fail(e, TFR_E_INVALID, "matrix K=%lld must be a positive multiple of 256", (long long)K);
+    if (nbytes != raw_bytes(type, K, N))
+        return fail(e, TFR_E_INVALID, "matrix byte size %zu != expected %zu", nbytes, raw_bytes(type, K, N));
+    if (perm_hd && (N % perm_hd || perm_hd % 2)) return fail(e, TFR_E_INVALID, "rope pairing head_dim %d does not divide N", perm_hd);
+    configure_kernels_once();
+    tfr_mat* m = new tfr_mat();
+    m->m.type = type;
+    m->m.K = (int)K;
+    m->m.N = (int)N;
+    m->m.nb = (int)(K / 256);
+    m->m.row_stride = mat_row_stride(type, (int)K);
+    m->bytes = (size_t)m->m.row_stride * (size_t)N;
+    m->perm_hd = perm_hd;
+    void* staging = nullptr;
+    cudaError_t r = cudaMalloc(&m->dev, m->bytes);
+    if (r == cudaSuccess) r = cudaMalloc(&staging, nbytes);
+    if (r == cudaSuccess) r = cudaMemcpyAsync(staging, bytes, nbytes, cudaMemcpyDefault, stream);
+    if (r == cudaSuccess) {
+        const int grid = sm_count_cached() * 8;
+        if (type == TFR_Q4_K)
+            k_repack_q4k<<<grid, 256, 0, stream>>>((const uint8_t*)staging, (uint8_t*)m->dev, (int)N, m->m.nb, perm_hd);
+        else {
+            cudaMemsetAsync(m->dev, 0, m->bytes, stream);
+            k_repack_q6k<<<grid, 256, 0, stream>>>((const uint8_t*)staging, (uint8_t*)m->dev, (int)N, m->m.nb,
+                                                   m->m.row_stride, perm_hd);
+        }
+        r = cudaGetLastError();
+    }
+    if (r == cudaSuccess) r = cudaStreamSynchronize(stream);
+    if (staging) cudaFree(staging);
+    if (r != cudaSuccess) {
+        if (m->dev) cudaFree(m->dev);
+        delete m;
+        return fail(e, TFR_E_CUDA, "matrix upload: %s", cudaGetErrorString(r));
+    }
+    m->m.data = (const uint8_t*)m->dev;
+    *out = m;
+    return TFR_OK;
+}
+
+extern "C" int tfr_mat_create(int type, int64_t K, int64_t N, const void* bytes, size_t nbytes, int perm_hd, tfr_mat** out) {
+    if (!bytes || !out) return TFR_E_INVALID;
+    return mat_create_impl(nullptr, type, K, N, bytes, nbytes, perm_hd, nullptr, out);
+}
+extern "C" void tfr_mat_free(tfr_mat* m) {
+    if (!m) return;
+    if (m->dev) cudaFree(m->dev);
+    delete m;
+}
+extern "C" int64_t tfr_mat_device_bytes(const tfr_mat* m) { return m ? (int64_t)m->bytes : 0; }
+
+// ------------------------------------------------------------------ engine lifetime
+
+extern "C" int tfr_create(int device, tfr_engine** out) {
+    if (!out) return TFR_E_INVALID;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) return TFR_E_CUDA;
+    if (cudaSetDevice(device) != cudaSuccess) return TFR_E_CUDA;
+    tfr_engine* e = new tfr_engine();
+    e->device = device;
+    if (cudaGetDeviceProperties(&e->prop, device) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreate(&e->ev0) != cudaSuccess || cudaEventCreate(&e->ev1) != cudaSuccess) {
+        delete e;
+        return TFR_E_CUDA;
+    }
+    configure_kernels_once();
+    *out = e;
+    return TFR_OK;
+}
+
+static void drop_graphs(tfr_engine* e) {
+    if (e->g_decode) cudaGraphExecDestroy(e->g_decode);
+    if (e->g_body) cudaGraphExecDestroy(e->g_body);
+    e->g_decode = e->g_body = nullptr;
+    e->graph_kv = nullptr;
+}
+
+extern "C" void tfr_destroy(tfr_engine* e) {
+    if (!e) return;
+    cudaSetDevice(e->device);
+    cudaStreamSynchronize(e->stream);
+    drop_graphs(e);
+    for (auto& kv : e->mats) tfr_mat_free(kv.second);
+    for (auto& kv : e->vecs) cudaFree(kv.second.dev);
+    for (auto& L : e->layers) cudaFree(L.bias_qkv);
+    void* ws[] = {e->x, e->q, e->attn, e->h, e->logits, e->partial, e->counters, e->st, e->out_tokens, e->prompt};
+    for (void* p : ws) cudaFree(p);
+    if (e->st_host) cudaFreeHost(e->st_host);
+    if (e->out_host) cudaFreeHost(e->out_host);
+    cudaEventDestroy(e->ev0);
+    cudaEventDestroy(e->ev1);
+    cudaStreamDestroy(e->stream);
+    delete e;
+}
+
+extern "C" const char* tfr_last_error(const tfr_engine* e) { return e ? e->err.c_str() : "null engine"; }
+
+extern "C" int tfr_device_info(const tfr_engine* e, char* name, size_t cap, int* major, int* minor, int* sms) {
+    if (!e) return TFR_E_INVALID;
+    if (name && cap) snprintf(name, cap, "%s", e->prop.name);
+    if (major) *major = e->prop.major;
+    if (minor) *minor = e->prop.minor;
+    if (sms) *sms = e->prop.multiProcessorCount;
+    return TFR_OK;
+}
+
+extern "C" int tfr_set_config(tfr_engine* e, const tfr_model_config* c) {
+    if (!e || !c) return TFR_E_INVALID;
+    if (e->finalized) return fail(e, TFR_E_INVALID, "config after finalize");
+    if (c->n_layer <= 0 || c->n_embd <= 0 || c->n_embd % 256 || c->n_head <= 0 || c->n_kv_head <= 0 ||
+        c->n_head % c->n_kv_head || c->n_ff <= 0 || c->n_ff % 256 || c->n_vocab <= 0)
+        return fail(e, TFR_E_INVALID, "bad model configuration");
+    if (c->head_dim != 64 && c->head_dim != 128 && c->head_dim != 256)
+        return fail(e, TFR_E_UNSUPPORTED, "head_dim %d (supported: 64, 128, 256)", c->head_dim);
+    if (c->n_head / c->n_kv_head > ATTN_REP_MAX)
+        return fail(e, TFR_E_UNSUPPORTED, "more than %d query heads per KV head", ATTN_REP_MAX);
+    if (c->hybrid) return fail(e, TFR_E_UNSUPPORTED, "hybrid (Gated-DeltaNet) models are not built yet");
+    if (c->tp_size > 1) return fail(e, TFR_E_UNSUPPORTED, "tensor parallelism is not built yet");
+    e->cfg = *c;
+    if (e->cfg.tp_size < 1) e->cfg.tp_size = 1;
+    e->has_cfg = true;
+    return TFR_OK;
+}
+
+static bool ends_with(const std::string& s, const char* suf) {
+    size_t n = strlen(suf);
+    return s.size() >= n && s.compare(s.size() - n, n, suf) == 0;
+}
+
+extern "C" int tfr_upload_tensor(tfr_engine* e, const char* name, int type, int64_t n_rows, int64_t n_cols, const void* bytes,
+                                 size_t nbytes) {
+    if (!e || !name || !bytes) return TFR_E_INVALID;
+    if (!e->has_cfg) return fail(e, TFR_E_INVALID, "tfr_set_config must precede uploads");
+    if (e->finalized) return fail(e, TFR_E_INVALID, "upload after finalize");
+    cudaSetDevice(e->device);
+    std::string nm(name);
+    if (e->mats.count(nm) || e->vecs.count(nm)) return fail(e, TFR_E_INVALID, "tensor %s uploaded twice", name);
+    if (type == TFR_TYPE_F32) {
+        // vectors must be F32 (load.rs:135-143)
+        int64_t n = n_rows * (n_cols > 0 ? n_cols : 1);
+        if (nbytes != (size_t)n * 4) return fail(e, TFR_E_INVALID, "vector %s: %zu bytes for %lld floats", name, nbytes, (long long)n);
+        VecT v;
+        v.n = n;
+        CU(e, cudaMalloc(&v.dev, nbytes));
+        CU(e, cudaMemcpy(v.dev, bytes, nbytes, cudaMemcpyDefault));
+        e->vecs[nm] = v;
+        return TFR_OK;
+    }
+    // F32/F16 matrices are rejected like load.rs:15-28
+    int perm = (ends_with(nm, "attn_q.weight") || ends_with(nm, "attn_k.weight")) ? e->cfg.head_dim : 0;
+    tfr_mat* m = nullptr;
+    int rc = mat_create_impl(e, type, n_rows, n_cols, bytes, nbytes, perm, e->stream, &m);
+    if (rc) return rc;
+    e->mats[nm] = m;
+    return TFR_OK;
+}
+
+static tfr_mat* need_mat(tfr_engine* e, const std::string& n, int K, int N, int& rc) {
+    auto it = e->mats.find(n);
+    if (it == e->mats.end()) {
+        rc = fail(e, TFR_E_INVALID, "missing tensor %s", n.c_str());
+        return nullptr;
+    }
+    if (it->second->m.K != K || it->second->m.N != N) {
+        rc = fail(e, TFR_E_INVALID, "tensor %s is %dx%d, expected %dx%d", n.c_str(), it->second->m.K, it->second->m.N, K, N);
+        return nullptr;
+    }
+    return it->second;
+}
+static float* need_vec(tfr_engine* e, const std::string& n, int len, bool optional, int& rc) {
+    auto it = e->vecs.find(n);
+    if (it == e->vecs.end()) {
+        if (!optional) rc = fail(e, TFR_E_INVALID, "missing tensor %s", n.c_str());
+        return nullptr;
+    }
+    if (it->second.n != len) {
+        rc = fail(e, TFR_E_INVALID, "tensor %s has %lld elements, expected %d", n.c_str(), (long long)it->second.n, len);
+        return nullptr;
+    }
+    return it->second.dev;
+}
+
+extern "C" int tfr_finalize_load(tfr_engine* e) {
+    if (!e || !e->has_cfg) return TFR_E_INVALID;
+    if (e->finalized) return TFR_OK;
+    cudaSetDevice(e->device);
+    const tfr_model_config& c = e->cfg;
+    const int K = c.n_embd, hd = c.head_dim, nq = c.n_head * hd, nkv = c.n_kv_head * hd, FF = c.n_ff, V = c.n_vocab;
+    int rc = TFR_OK;
+    e->token_embd = need_mat(e, "token_embd.weight", K, V, rc);
+    if (rc) return rc;
+    e->head = e->mats.count("output.weight") ? need_mat(e, "output.weight", K, V, rc) : e->token_embd;
+    e->output_norm = need_vec(e, "output_norm.weight", K, false, rc);
+    if (rc) return rc;
+    e->layers.resize(c.n_layer);
+    for (int i = 0; i < c.n_layer; i++) {
+        const std::string p = "blk." + std::to_string(i) + ".";
+        LayerW& L = e->layers[i];
+        L.wq = need_mat(e, p + "attn_q.weight", K, nq, rc);
+        L.wk = need_mat(e, p + "attn_k.weight", K, nkv, rc);
+        L.wv = need_mat(e, p + "attn_v.weight", K, nkv, rc);
+        L.wo = need_mat(e, p + "attn_output.weight", nq, K, rc);
+        L.gate = need_mat(e, p + "ffn_gate.weight", K, FF, rc);
+        L.up = need_mat(e, p + "ffn_up.weight", K, FF, rc);
+        L.down = need_mat(e, p + "ffn_down.weight", FF, K, rc);
+        L.attn_norm = need_vec(e, p + "attn_norm.weight", K, false, rc);
+        L.ffn_norm = need_vec(e, p + "ffn_norm.weight", K, true, rc);
+        if (!L.ffn_norm && !rc) L.ffn_norm = need_vec(e, p + "post_attention_norm.weight", K, false, rc);  // load.rs:280-417
+        if (rc) return rc;
+        if (L.wq->m.type != TFR_Q4_K || L.wk->m.type != TFR_Q4_K)
+            return fail(e, TFR_E_UNSUPPORTED, "layer %d: attn_q / attn_k must be Q4_K", i);
+        if (L.gate->m.type != TFR_Q4_K || L.up->m.type != TFR_Q4_K)
+            return fail(e, TFR_E_UNSUPPORTED, "layer %d: ffn_gate / ffn_up must be Q4_K", i);
+        float* bq = need_vec(e, p + "attn_q.bias", nq, true, rc);
+        float* bk = need_vec(e, p + "attn_k.bias", nkv, true, rc);
+        float* bv = need_vec(e, p + "attn_v.bias", nkv, true, rc);
+        if (rc) return rc;
+        if (bq || bk || bv) {
+            const int tot = nq + 2 * nkv;
+            CU(e, cudaMalloc(&L.bias_qkv, (size_t)tot * 4));
+            CU(e, cudaMemsetAsync(L.bias_qkv, 0, (size_t)tot * 4, e->stream));
+            if (bq) k_permute_f32<<<(nq + 255) / 256, 256, 0, e->stream>>>(bq, L.bias_qkv, nq, hd);
+            if (bk) k_permute_f32<<<(nkv + 255) / 256, 256, 0, e->stream>>>(bk, L.bias_qkv + nq, nkv, hd);
+            if (bv) k_permute_f32<<<(nkv + 255) / 256, 256, 0, e->stream>>>(bv, L.bias_qkv + nq + nkv, nkv, 0);
+            CU(e, cudaGetLastError());
+        }
+    }
+    // workspaces (load.rs:547-607: everything allocated once)
+    const int sms = e->prop.multiProcessorCount;
+    e->attn_S = sms / c.n_kv_head;
+    if (e->attn_S < 1) e->attn_S = 1;
+    CU(e, cudaMalloc(&e->x, (size_t)K * 4));
+    CU(e, cudaMalloc(&e->q, (size_t)nq * 4));
+    CU(e, cudaMalloc(&e->attn, (size_t)nq * 4));
+    CU(e, cudaMalloc(&e->h, (size_t)FF * 4));
+    CU(e, cudaMalloc(&e->logits, (size_t)V * 4));
+    CU(e, cudaMalloc(&e->partial, (size_t)c.n_head * e->attn_S * (2 + hd) * 4));
+    CU(e, cudaMalloc(&e->counters, (size_t)c.n_kv_head * 4));
+    CU(e, cudaMalloc(&e->st, sizeof(TokenState)));
+    CU(e, cudaMalloc(&e->out_tokens, (size_t)TFR_MAX_BURST * 4));
+    CU(e, cudaMalloc(&e->prompt, (size_t)TFR_MAX_PROMPT * 4));
+    CU(e, cudaMallocHost(&e->st_host, sizeof(TokenState)));
+    CU(e, cudaMallocHost(&e->out_host, (size_t)TFR_MAX_BURST * 4));
+    CU(e, cudaMemsetAsync(e->counters, 0, (size_t)c.n_kv_head * 4, e->stream));
+    CU(e, cudaMemsetAsync(e->st, 0, sizeof(TokenState), e->stream));
+    CU(e, cudaMemsetAsync(e->logits, 0, (size_t)V * 4, e->stream));
+    CU(e, cudaStreamSynchronize(e->stream));
+    e->finalized = true;
+    return TFR_OK;
+}
+
+// ------------------------------------------------------------------ KV cache
+
+extern "C" int tfr_alloc_kv(tfr_engine* e, int max_seq, tfr_kv** out) {
+    if (!e || !out || !e->finalized || max_seq <= 0) return e ? fail(e, TFR_E_INVALID, "alloc_kv: bad state or size") : TFR_E_INVALID;
+    cudaSetDevice(e->device);
+    tfr_kv* kv = new tfr_kv();
+    kv->e = e;
+    kv->max_seq = max_seq;
+    kv->layer_stride = (size_t)max_seq * e->cfg.n_kv_head * e->cfg.head_dim;
+    const size_t bytes = kv->layer_stride * e->cfg.n_layer * 2;
+    if (cudaMalloc(&kv->k, bytes) != cudaSuccess || cudaMalloc(&kv->v, bytes) != cudaSuccess) {
+        cudaFree(kv->k);
+        delete kv;
+        cudaGetLastError();
+        return fail(e, TFR_E_CUDA, "alloc_kv: out of device memory (%zu bytes x2)", bytes);
+    }
+    cudaMemsetAsync(kv->k, 0, bytes, e->stream);
+    cudaMemsetAsync(kv->v, 0, bytes, e->stream);
+    cudaStreamSynchronize(e->stream);
+    *out = kv;
+    return TFR_OK;
+}
+extern "C" void tfr_free_kv(tfr_kv* kv) {
+    if (!kv) return;
+    if (kv->e && kv->e->graph_kv == kv) drop_graphs(kv->e);
+    cudaFree(kv->k);
+    cudaFree(kv->v);
+    delete kv;
+}
+extern "C" int tfr_kv_len(const tfr_kv* kv) { return kv ? kv->len : TFR_E_INVALID; }
+extern "C" int tfr_kv_max_seq(const tfr_kv* kv) { return kv ? kv->max_seq : TFR_E_INVALID; }
+extern "C" int tfr_kv_set_len(tfr_kv* kv, int len) {
+    if (!kv || len < 0 || len > kv->max_seq) return TFR_E_INVALID;
+    kv->len = len;
+    return TFR_OK;
+}
+extern "C" int tfr_kv_clear(tfr_kv* kv) { return tfr_kv_set_len(kv, 0); }
+extern "C" int64_t tfr_kv_bytes_per_token(const tfr_kv* kv) {
+    if (!kv) return 0;
+    const tfr_model_config& c = kv->e->cfg;
+    return (int64_t)c.n_layer * c.n_kv_head * c.head_dim * 2 * 2;  // kv.rs:36-41
+}
+extern "C" int tfr_zero_recurrent(tfr_engine* e, tfr_kv* kv) {
+    if (!e || !kv) return TFR_E_INVALID;
+    return TFR_OK;  // dense models carry no recurrent state (model.rs:165-194 is a no-op for them)
+}
+
+// ------------------------------------------------------------------ one token
+
+static cudaError_t launch_attention(cudaStream_t s, const AttnArgs& a, int hd, const TokenState* st) {
+    const int grid = a.n_kv * a.S;
+    if (hd == 64) k_attn_decode<64><<<grid, ATTN_THREADS, 0, s>>>(a, st);
+    else if (hd == 128) k_attn_decode<128><<<grid, ATTN_THREADS, 0, s>>>(a, st);
+    else k_attn_decode<256><<<grid, ATTN_THREADS, 0, s>>>(a, st);
+    return cudaGetLastError();
+}
+
+static int wt_of(const tfr_mat* m) { return m->m.type == TFR_Q4_K ? WT_Q4K : WT_Q6K; }
+static int swz_of(const tfr_mat* m) { return m->m.type == TFR_Q4_K ? SWZ_Q4 : SWZ_Q6; }
+
+// Enqueues the kernels of one decode step; returns the number of launches or a negative error.
+static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
+    const tfr_model_config& c = e->cfg;
+    const int K = c.n_embd, hd = c.head_dim, nq = c.n_head * hd, nkv = c.n_kv_head * hd, FF = c.n_ff, V = c.n_vocab;
+    const int cap = e->prop.multiProcessorCount * 4;
+    cudaStream_t s = e->stream;
+    int n = 0;
+    for (int li = 0; li < c.n_layer; li++) {
+        const LayerW& L = e->layers[li];
+        {  // 1. norm + quant + QKV + rope + KV store
+            PrepArgs pa{};
+            pa.vec = li == 0 ? nullptr : e->x;
+            pa.embed = e->token_embd->m;
+            pa.normw = L.attn_norm;
+            pa.eps = c.rms_eps;
+            pa.swz = SWZ_Q4;
+            pa.want_xf = L.wv->m.type == TFR_Q6_K;
+            pa.raw_out = e->x;
+            MapStack map{};
+            map.m[0] = L.wq->m;
+            map.m[1] = L.wk->m;
+            map.m[2] = L.wv->m;
+            map.wt[0] = map.wt[1] = WT_Q4K;
+            map.wt[2] = L.wv->m.type == TFR_Q6_K ? WT_Q6K_F32 : WT_Q4K;
+            map.start[0] = 0;
+            map.start[1] = nq;
+            map.start[2] = nq + nkv;
+            map.start[3] = map.start[4] = nq + 2 * nkv;
+            map.count = 3;
+            EpiQkv epi{};
+            epi.q_out = e->q;
+            epi.kc = kv->k + (size_t)li * kv->layer_stride;
+            epi.vc = kv->v + (size_t)li * kv->layer_stride;
+            epi.bias = L.bias_qkv;
+            epi.nq = nq;
+            epi.nk = nkv;
+            epi.hd = hd;
+            epi.kvdim = nkv;
+            epi.theta = c.rope_theta;
+            if (launch_gemv(s, cap, pa, map, epi, K, (nq + 2 * nkv) / 2, e->st) != cudaSuccess) return -1;
+            n++;
+        }
+        {  // 2. attention
+            AttnArgs a{};
+            a.q = e->q;
+            a.kc = kv->k + (size_t)li * kv->layer_stride;
+            a.vc = kv->v + (size_t)li * kv->layer_stride;
+            a.partial = e->partial;
+            a.counters = e->counters;
+            a.out = e->attn;
+            a.gate = nullptr;
+            a.n_head = c.n_head;
+            a.n_kv = c.n_kv_head;
+            a.S = e->attn_S;
+            a.min_keys = e->attn_min_keys;
+            a.scale = 1.0f / sqrtf((float)hd);  // forward.rs:389
+            if (launch_attention(s, a, hd, e->st) != cudaSuccess) return -1;
+            n++;
+        }
+        {  // 3. o-proj + residual
+            PrepArgs pa{};
+            pa.vec = e->attn;
+            pa.swz = swz_of(L.wo);
+            MapSingle map{L.wo->m, wt_of(L.wo)};
+            EpiStore epi{e->x, nullptr, 2};
+            if (launch_gemv(s, cap, pa, map, epi, nq, K, e->st) != cudaSuccess) return -1;
+            n++;
+        }
+        {  // 4. norm + quant + gate/up + silu*mul
+            PrepArgs pa{};
+            pa.vec = e->x;
+            pa.normw = L.ffn_norm;
+            pa.eps = c.rms_eps;
+            pa.swz = SWZ_Q4;
+            MapPair map{L.gate->m, L.up->m};
+            EpiSilu epi{e->h};
+            if (launch_gemv(s, cap, pa, map, epi, K, FF, e->st) != cudaSuccess) return -1;
+            n++;
+        }
+        {  // 5. down + residual
+            PrepArgs pa{};
+            pa.vec = e->h;
+            pa.swz = swz_of(L.down);
+            MapSingle map{L.down->m, wt_of(L.down)};
+            EpiStore epi{e->x, nullptr, 2};
+            if (launch_gemv(s, cap, pa, map, epi, FF, K, e->st) != cudaSuccess) return -1;
+            n++;
+        }
+    }
+    if (with_head) {
+        PrepArgs pa{};
+        pa.vec = e->x;
+        pa.normw = e->output_norm;
+        pa.eps = c.rms_eps;
+        pa.swz = swz_of(e->head);
+        MapSingle map{e->head->m, wt_of(e->head)};
+        EpiLogits epi{};
+        epi.logits = e->logits;
+        epi.out_tokens = e->out_tokens;
+        if (launch_gemv(s, cap, pa, map, epi, K, V, e->st) != cudaSuccess) return -1;
+        n++;
+    } else {
+        k_state_next_prompt<<<1, 1, 0, s>>>(e->st, e->prompt);
+        if (cudaGetLastError() != cudaSuccess) return -1;
+        n++;
+    }
+    return n;
+}
+
+static int ensure_graphs(tfr_engine* e, const tfr_kv* kv) {
+    if (e->graph_kv == kv && e->g_decode && e->g_body) return TFR_OK;
+    drop_graphs(e);
+    for (int which = 0; which < 2; which++) {
+        cudaGraph_t g = nullptr;
+        CU(e, cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeRelaxed));
+        int n = record_token(e, kv, which == 0);
+        cudaError_t r = cudaStreamEndCapture(e->stream, &g);
+        if (n < 0 || r != cudaSuccess) {
+            if (g) cudaGraphDestroy(g);
+            cudaGetLastError();
+            return fail(e, TFR_E_CUDA, "graph capture failed: %s", cudaGetErrorString(r));
+        }
+        cudaGraphExec_t ex = nullptr;
+        r = cudaGraphInstantiate(&ex, g, 0);
+        cudaGraphDestroy(g);
+        if (r != cudaSuccess) return fail(e, TFR_E_CUDA, "graph instantiate: %s", cudaGetErrorString(r));
+        if (which == 0) {
+            e->g_decode = ex;
+            e->nodes_decode = n;
+        } else {
+            e->g_body = ex;
+            e->nodes_body = n;
+        }
+    }
+    e->graph_kv = kv;
+    return TFR_OK;
+}
+
+static int run_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
+    if (e->use_graph) {
+        CU(e, cudaGraphLaunch(with_head ? e->g_decode : e->g_body, e->stream));
+        e->launches += with_head ? e->nodes_decode : e->nodes_body;
+        return TFR_OK;
+    }
+    int n = record_token(e, kv, with_head);
+    if (n < 0) return fail(e, TFR_E_CUDA, "kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    e->launches += n;
+    return TFR_OK;
+}
+
+static int begin_state(tfr_engine* e, int token, int pos, int max_steps, int max_seq, const uint32_t* stops, int n_stop) {
+    int s[8] = {-1, -1, -1, -1, -1, -1, -1, -1};
+    for (int i = 0; i < n_stop && i < 8; i++) s[i] = (int)stops[i];
+    k_state_begin<<<1, 1, 0, e->stream>>>(e->st, token, pos, max_steps, max_seq, n_stop, s[0], s[1], s[2], s[3], s[4], s[5],
+                                          s[6], s[7]);
+    CU(e, cudaGetLastError());
+    e->launches += 1;
+    return TFR_OK;
+}
+
+static int finish_state(tfr_engine* e, int n_tokens_out) {
+    CU(e, cudaMemcpyAsync(e->st_host, e->st, sizeof(TokenState), cudaMemcpyDeviceToHost, e->stream));
+    if (n_tokens_out > 0)
+        CU(e, cudaMemcpyAsync(e->out_host, e->out_tokens, (size_t)n_tokens_out * 4, cudaMemcpyDeviceToHost, e->stream));
+    CU(e, cudaStreamSynchronize(e->stream));
+    cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1);
+    if (e->st_host->err) return fail(e, TFR_E_INVALID, "device reported an invalid token id");
+    return TFR_OK;
+}
+
+extern "C" int tfr_forward_greedy(tfr_engine* e, tfr_kv* kv, const uint32_t* tokens, int n, uint32_t* next_token) {
+    if (!e || !kv || kv->e != e || !e->finalized) return e ? fail(e, TFR_E_INVALID, "forward_greedy: bad handle") : TFR_E_INVALID;
+    if (n <= 0 || !tokens) return fail(e, TFR_E_EMPTY, "empty tokens");
+    if (kv->len + n > kv->max_seq) return fail(e, TFR_E_FULL, "context full");
+    if (n > TFR_MAX_PROMPT) return fail(e, TFR_E_INVALID, "more than %d tokens in one call", TFR_MAX_PROMPT);
+    for (int i = 0; i < n; i++)
+        if (tokens[i] >= (uint32_t)e->token_embd->m.N) return fail(e, TFR_E_INVALID, "token id %u out of range", tokens[i]);
+    cudaSetDevice(e->device);
+    if (e->use_graph) {
+        int rc = ensure_graphs(e, kv);
+        if (rc) return rc;
+    }
+    CU(e, cudaMemcpyAsync(e->prompt, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, e->stream));
+    int rc = begin_state(e, (int)tokens[0], kv->len, 1, kv->max_seq + 1, nullptr, 0);
+    if (rc) return rc;
+    CU(e, cudaEventRecord(e->ev0, e->stream));
+    for (int i = 0; i < n && !rc; i++) rc = run_token(e, kv, i == n - 1);
+    if (rc) return rc;
+    CU(e, cudaEventRecord(e->ev1, e->stream));
+    rc = finish_state(e, 1);
+    if (rc) return rc;
+    kv->len += n;
+    if (next_token) *next_token = (uint32_t)e->out_host[0];
+    return TFR_OK;
+}
+
+extern "C" int tfr_decode_burst(tfr_engine* e, tfr_kv* kv, uint32_t first_token, int max_n, const uint32_t* stop_ids, int n_stop,
+                                uint32_t* out, int* n_out) {
+    if (!e || !kv || kv->e != e || !e->finalized || !out || !n_out)
+        return e ? fail(e, TFR_E_INVALID, "decode_burst: bad argument") : TFR_E_INVALID;
+    if (max_n <= 0) return fail(e, TFR_E_EMPTY, "empty tokens");
+    if (n_stop < 0 || n_stop > 8) return fail(e, TFR_E_INVALID, "at most 8 stop ids");
+    if (kv->len + 1 > kv->max_seq) return fail(e, TFR_E_FULL, "context full");
+    if (first_token >= (uint32_t)e->token_embd->m.N) return fail(e, TFR_E_INVALID, "token id %u out of range", first_token);
+    cudaSetDevice(e->device);
+    int n_run = max_n < TFR_MAX_BURST ? max_n : TFR_MAX_BURST;
+    if (n_run > kv->max_seq - kv->len) n_run = kv->max_seq - kv->len;
+    if (e->use_graph) {
+        int rc = ensure_graphs(e, kv);
+        if (rc) return rc;
+    }
+    int rc = begin_state(e, (int)first_token, kv->len, n_run, kv->max_seq + 1, stop_ids, n_stop);
+    if (rc) return rc;
+    CU(e, cudaEventRecord(e->ev0, e->stream));
+    for (int i = 0; i < n_run && !rc; i++) rc = run_token(e, kv, true);
+    if (rc) return rc;
+    CU(e, cudaEventRecord(e->ev1, e->stream));
+    rc = finish_state(e, n_run);
+    if (rc) return rc;
+    const int produced = e->st_host->step;
+    for (int i = 0; i < produced; i++) out[i] = (uint32_t)e->out_host[i];
+    *n_out = produced;
+    kv->len += produced;
+    return TFR_OK;
+}
+
+extern "C" int tfr_current_logits(tfr_engine* e, float* out, int n) {
+    if (!e || !out || !e->finalized || n <= 0 || n > e->cfg.n_vocab) return e ? fail(e, TFR_E_INVALID, "current_logits: bad argument") : TFR_E_INVALID;
+    cudaSetDevice(e->device);
+    CU(e, cudaMemcpyAsync(out, e->logits, (size_t)n * 4, cudaMemcpyDeviceToHost, e->stream));
+    CU(e, cudaStreamSynchronize(e->stream));
+    return TFR_OK;
+}
+
+extern "C" int tfr_set_cuda_graph(tfr_engine* e, int enabled) {
+    if (!e) return TFR_E_INVALID;
+    e->use_graph = enabled != 0;
+    if (!e->use_graph) drop_graphs(e);
+    return TFR_OK;
+}
+extern "C" int tfr_graph_active(const tfr_engine* e) { return e && e->use_graph && e->g_decode ? 1 : 0; }
+extern "C" int64_t tfr_launch_count(const tfr_engine* e) { return e ? e->launches : 0; }
+extern "C" float tfr_last_device_ms(const tfr_engine* e) { return e ? e->last_ms : 0.f; }
+
+extern "C" int tfr_debug_read(tfr_engine* e, tfr_kv* kv, const char* what, int layer, void* out, size_t nbytes) {
+    if (!e || !what || !out || !e->finalized) return TFR_E_INVALID;
+    const tfr_model_config& c = e->cfg;
+    const void* src = nullptr;
+    size_t have = 0;
+    std::string w(what);
+    if (w == "x") src = e->x, have = (size_t)c.n_embd * 4;
+    else if (w == "q") src = e->q, have = (size_t)c.n_head * c.head_dim * 4;
+    else if (w == "attn") src = e->attn, have = (size_t)c.n_head * c.head_dim * 4;
+    else if (w == "h") src = e->h, have = (size_t)c.n_ff * 4;
+    else if (w == "logits") src = e->logits, have = (size_t)c.n_vocab * 4;
+    else if ((w == "k" || w == "v") && kv && layer >= 0 && layer < c.n_layer) {
+        src = (w == "k" ? kv->k : kv->v) + (size_t)layer * kv->layer_stride;
+        have = kv->layer_stride * 2;
+    } else return fail(e, TFR_E_INVALID, "debug_read: unknown tap %s", what);
+    if (nbytes > have) return fail(e, TFR_E_INVALID, "debug_read: %zu bytes requested, %zu available", nbytes, have);
+    cudaSetDevice(e->device);
+    CU(e, cudaStreamSynchronize(e->stream));
+    CU(e, cudaMemcpy(out, src, nbytes, cudaMemcpyDeviceToHost));
+    return TFR_OK;
+}
+
+// ------------------------------------------------------------------ operator level
+
+static int check(cudaError_t r) { return r == cudaSuccess ? TFR_OK : TFR_E_CUDA; }
+
+extern "C" int tfr_op_quantize_q8(const float* x, int n, int8_t* q8, float* d8, void* stream) {
+    if (!x || !q8 || !d8 || n <= 0 || n % 32) return TFR_E_INVALID;
+    const int groups = n / 32;
+    k_quantize_q8<<<(groups + 7) / 8, 256, 0, (cudaStream_t)stream>>>(x, (signed char*)q8, d8, n);
+    return check(cudaGetLastError());
+}
+
+extern "C" int tfr_op_gemv(const tfr_mat* w, const float* x, float* out, const float* bias, int use_res, int act_mode,
+                           const float* norm_w, float eps, void* stream) {
+    if (!w || !x || !out) return TFR_E_INVALID;
+    if (act_mode == 1 && w->m.type != TFR_Q6_K) return TFR_E_UNSUPPORTED;
+    if (w->perm_hd) return TFR_E_INVALID;  // row-permuted matrices only make sense in the fused QKV kernel
+    configure_kernels_once();
+    PrepArgs pa{};
+    pa.vec = x;
+    pa.normw = norm_w;
+    pa.eps = eps;
+    pa.swz = swz_of(w);
+    pa.want_xf = act_mode == 1;
+    MapSingle map{w->m, act_mode == 1 ? WT_Q6K_F32 : wt_of(w)};
+    EpiStore epi{out, bias, use_res};
+    return check(launch_gemv((cudaStream_t)stream, sm_count_cached() * 4, pa, map, epi, w->m.K, w->m.N, nullptr));
+}
+
+extern "C" int tfr_op_ffn_gate_up(const tfr_mat* gate, const tfr_mat* up, const float* x, const float* norm_w, float eps, float* h,
+                                  void* stream) {
+    if (!gate || !up || !x || !h) return TFR_E_INVALID;
+    if (gate->m.type != TFR_Q4_K || up->m.type != TFR_Q4_K || gate->m.K != up->m.K || gate->m.N != up->m.N) return TFR_E_UNSUPPORTED;
+    configure_kernels_once();
+    PrepArgs pa{};
+    pa.vec = x;
+    pa.normw = norm_w;
+    pa.eps = eps;
+    pa.swz = SWZ_Q4;
+    MapPair map{gate->m, up->m};
+    EpiSilu epi{h};
+    return check(launch_gemv((cudaStream_t)stream, sm_count_cached() * 4, pa, map, epi, gate->m.K, gate->m.N, nullptr));
+}
+
+extern "C" int tfr_op_ffn_block(const tfr_mat* gate, const tfr_mat* up, const tfr_mat* down, const float* x, float* h_scratch,
+                                float* y, int use_res, void* stream) {
+    if (!down || !y || !h_scratch || !gate || down->m.K != gate->m.N) return TFR_E_INVALID;
+    int rc = tfr_op_ffn_gate_up(gate, up, x, nullptr, 0.f, h_scratch, stream);
+    if (rc) return rc;
+    return tfr_op_gemv(down, h_scratch, y, nullptr, use_res, 0, nullptr, 0.f, stream);
+}
+
+extern "C" int tfr_ffn_block_host(const tfr_mat* gate, const tfr_mat* up, const tfr_mat* down, const float* x_host, float* y_host) {
+    if (!gate || !up || !down || !x_host || !y_host) return TFR_E_INVALID;
+    const int K = gate->m.K, FF = gate->m.N, N = down->m.N;
+    static float *dx = nullptr, *dh = nullptr, *dy = nullptr;
+    static int cap_k = 0, cap_f = 0, cap_n = 0;
+    if (K > cap_k || FF > cap_f || N > cap_n) {
+        cudaFree(dx), cudaFree(dh), cudaFree(dy);
+        if (cudaMalloc(&dx, (size_t)K * 4) != cudaSuccess || cudaMalloc(&dh, (size_t)FF * 4) != cudaSuccess ||
+            cudaMalloc(&dy, (size_t)N * 4) != cudaSuccess)
+            return TFR_E_CUDA;
+        cap_k = K, cap_f = FF, cap_n = N;
+    }
+    if (cudaMemcpyAsync(dx, x_host, (size_t)K * 4, cudaMemcpyHostToDevice, nullptr) != cudaSuccess) return TFR_E_CUDA;
+    int rc = tfr_op_ffn_block(gate, up, down, dx, dh, dy, 0, nullptr);
+    if (rc) return rc;
+    if (cudaMemcpyAsync(y_host, dy, (size_t)N * 4, cudaMemcpyDeviceToHost, nullptr) != cudaSuccess) return TFR_E_CUDA;
+    return check(cudaStreamSynchronize(nullptr));
+}
+
+extern "C" int tfr_op_int_dots(const tfr_mat* w, const int8_t* q8, const float* d8, int32_t* a, int32_t* b, void* stream) {
+    if (!w || !q8 || !d8 || !a || w->perm_hd) return TFR_E_INVALID;
+    if (w->m.type == TFR_Q4_K && !b) return TFR_E_INVALID;
+    configure_kernels_once();
+    const size_t smem = act_smem_bytes(w->m.K, false);
+    k_int_dots<<<sm_count_cached(), 256, smem, (cudaStream_t)stream>>>(w->m, (const signed char*)q8, d8, a, b);
+    return check(cudaGetLastError());
+}
+
+extern "C" int tfr_op_attention(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv,
+                                int head_dim, int pos, void* stream) {
+    if (!q || !kc || !vc || !out || n_kv <= 0 || n_head % n_kv || n_head / n_kv > ATTN_REP_MAX || pos < 0) return TFR_E_INVALID;
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256) return TFR_E_UNSUPPORTED;
+    if (n_kv > 64) return TFR_E_UNSUPPORTED;
+    // scratch for the stand-alone call: partials + counters, grown on demand and kept
+    static float* partial = nullptr;
+    static unsigned int* counters = nullptr;
+    static size_t cap = 0;
+    AttnArgs a{};
+    a.S = sm_count_cached() / n_kv;
+    if (a.S < 1) a.S = 1;
+    const size_t need = (size_t)n_head * a.S * (2 + head_dim) * 4;
+    if (need > cap || !counters) {
+        cudaFree(partial);
+        if (!counters) {
+            if (cudaMalloc(&counters, 64 * 4) != cudaSuccess) return TFR_E_CUDA;
+            cudaMemset(counters, 0, 64 * 4);
+        }
+        if (cudaMalloc(&partial, need) != cudaSuccess) return TFR_E_CUDA;
+        cap = need;
+    }
+    a.q = q;
+    a.kc = kc;
+    a.vc = vc;
+    a.partial = partial;
+    a.counters = counters;
+    a.out = out;
+    a.n_head = n_head;
+    a.n_kv = n_kv;
+    a.min_keys = 256;
+    a.scale = 1.0f / sqrtf((float)head_dim);
+    a.pos = pos;
+    return check(launch_attention((cudaStream_t)stream, a, head_dim, nullptr));
+}
+
+extern "C" int tfr_op_qkv_rope_store(const tfr_mat* wq, const tfr_mat* wk, const tfr_mat* wv, const float* bq, const float* bk,
+                                     const float* bv, const float* x, const float* norm_w, float eps, float theta, int head_dim,
+                                     int pos, float* q_out, uint16_t* kc, uint16_t* vc, void* stream) {
+    if (!wq || !wk || !wv || !x || !q_out || !kc || !vc) return TFR_E_INVALID;
+    if (wq->perm_hd != head_dim || wk->perm_hd != head_dim || wv->perm_hd) return TFR_E_INVALID;
+    if (wq->m.type != TFR_Q4_K || wk->m.type != TFR_Q4_K) return TFR_E_UNSUPPORTED;
+    configure_kernels_once();
+    cudaStream_t s = (cudaStream_t)stream;
+    const int nq = wq->m.N, nkv = wk->m.N, tot = nq + 2 * nkv;
+    float* bias = nullptr;
+    if (bq || bk || bv) {
+        static float* bias_buf = nullptr;
+        static int bias_cap = 0;
+        if (tot > bias_cap) {
+            cudaFree(bias_buf);
+            if (cudaMalloc(&bias_buf, (size_t)tot * 4) != cudaSuccess) return TFR_E_CUDA;
+            bias_cap = tot;
+        }
+        bias = bias_buf;
+        cudaMemsetAsync(bias, 0, (size_t)tot * 4, s);
+        if (bq) k_permute_f32<<<(nq + 255) / 256, 256, 0, s>>>(bq, bias, nq, head_dim);
+        if (bk) k_permute_f32<<<(nkv + 255) / 256, 256, 0, s>>>(bk, bias + nq, nkv, head_dim);
+        if (bv) k_permute_f32<<<(nkv + 255) / 256, 256, 0, s>>>(bv, bias + nq + nkv, nkv, 0);
+    }
+    PrepArgs pa{};
+    pa.vec = x;
+    pa.normw = norm_w;
+    pa.eps = eps;
+    pa.swz = SWZ_Q4;
+    pa.want_xf = wv->m.type == TFR_Q6_K;
+    MapStack map{};
+    map.m[0] = wq->m;
+    map.m[1] = wk->m;
+    map.m[2] = wv->m;
+    map.wt[0] = map.wt[1] = WT_Q4K;
+    map.wt[2] = wv->m.type == TFR_Q6_K ? WT_Q6K_F32 : WT_Q4K;
+    map.start[0] = 0;
+    map.start[1] = nq;
+    map.start[2] = nq + nkv;
+    map.start[3] = map.start[4] = tot;
+    map.count = 3;
+    EpiQkv epi{};
+    epi.q_out = q_out;
+    epi.kc = kc;
+    epi.vc = vc;
+    epi.bias = bias;
+    epi.nq = nq;
+    epi.nk = nkv;
+    epi.hd = head_dim;
+    epi.kvdim = nkv;
+    epi.theta = theta;
+    epi.pos = pos;
+    return check(launch_gemv(s, sm_count_cached() * 4, pa, map, epi, wq->m.K, tot / 2, nullptr));
+}
+
+// ------------------------------------------------------------------ synthetic quantiser
+
+// One thread per 256-element super-block.  Asymmetric min/max per 32-element sub-block.
+__global__ void k_synth_q4k(const float* __restrict__ w, uint8_t* __restrict__ out, long long n_blocks) {
+    const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    const float* x = w + b * 256;
+    uint8_t* o = out + b * 144;
+    float scale[8], mins[8], smax = 0.f, mmax = 0.f;
+    for (int j = 0; j < 8; j++) {
+        float lo = 0.f, hi = -1e30f;
+        for (int i = 0; i < 32; i++) {
+            lo = fminf(lo, x[32 * j + i]);
+            hi = fmaxf(hi, x[32 * j + i]);
+        }
+        hi = fmaxf(hi, lo);
+        scale[j] = (hi - lo) / 15.f;
+        mins[j] = -lo;
+        smax = fmaxf(smax, scale[j]);
+        mmax = fmaxf(mmax, mins[j]);
+    }
+    const __half dh = __float2half_rn(smax / 63.f), mh = __float2half_rn(mmax / 63.f);
+    const float d = __half2float(dh), dmin = __half2float(mh);
+    int sc[8], mn[8];
+    for (int j = 0; j < 8; j++) {
+        sc[j] = d > 0.f ? min(63, max(0, (int)rintf(scale[j] / d))) : 0;
+        mn[j] = dmin > 0.f ? min(63, max(0, (int)rintf(mins[j] / dmin))) : 0;
+    }
+    *reinterpret_cast<unsigned short*>(o) = __half_as_ushort(dh);
+    *reinterpret_cast<unsigned short*>(o + 2) = __half_as_ushort(mh);
+    for (int j = 0; j < 4; j++) {
+        o[4 + j] = (uint8_t)(sc[j] | ((sc[j + 4] >> 4) << 6));
+        o[8 + j] = (uint8_t)(mn[j] | ((mn[j + 4] >> 4) << 6));
+        o[12 + j] = (uint8_t)((sc[j + 4] & 0xF) | ((mn[j + 4] & 0xF) << 4));
+    }
+    for (int t = 0; t < 4; t++) {
+        const float s0 = d * sc[2 * t], s1 = d * sc[2 * t + 1];
+        const float o0 = dmin * mn[2 * t], o1 = dmin * mn[2 * t + 1];
+        for (int l = 0; l < 32; l++) {
+            const int q0 = s0 > 0.f ? min(15, max(0, (int)rintf((x[64 * t + l] + o0) / s0))) : 0;
+            const int q1 = s1 > 0.f ? min(15, max(0, (int)rintf((x[64 * t + 32 + l] + o1) / s1))) : 0;
+            o[16 + 32 * t + l] = (uint8_t)(q0 | (q1 << 4));
+        }
+    }
+}
+
+// One thread per 256-element block.  Symmetric per 16-element group.
+__global__ void k_synth_q6k(const float* __restrict__ w, uint8_t* __restrict__ out, long long n_blocks) {
+    const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    const float* x = w + b * 256;
+    uint8_t* o = out + b * 210;
+    float gs[16], gmax = 0.f;
+    for (int g = 0; g < 16; g++) {
+        float am = 0.f;
+        for (int i = 0; i < 16; i++) am = fmaxf(am, fabsf(x[16 * g + i]));
+        gs[g] = am / 31.f;
+        gmax = fmaxf(gmax, gs[g]);
+    }
+    const __half dh = __float2half_rn(gmax / 127.f);
+    const float d = __half2float(dh);
+    int sc[16];
+    for (int g = 0; g < 16; g++) sc[g] = d > 0.f ? min(127, max(0, (int)rintf(gs[g] / d))) : 0;
+    for (int i = 0; i < 192; i++) o[i] = 0;
+    for (int e = 0; e < 256; e++) {
+        const float step = d * sc[e >> 4];
+        const int q = (step > 0.f ? min(31, max(-32, (int)rintf(x[e] / step))) : 0) + 32;
+        const int n = e >> 7, r = e & 127, j = r >> 5, l = r & 31;
+        const int qi = 64 * n + ((j & 1) ? 32 : 0) + l;
+        o[qi] |= (uint8_t)((q & 0xF) << ((j & 2) ? 4 : 0));
+        o[128 + 32 * n + l] |= (uint8_t)((q >> 4) << (2 * j));
+    }
+    for (int g = 0; g < 16; g++) o[192 + g] = (uint8_t)(signed char)sc[g];
+    *reinterpret_cast<unsigned short*>(o + 208) = __half_as_ushort(dh);
+}
+
+extern "C" int tfr_synth_quantize(int type, const float* w, int64_t K, int64_t N, void* out, void* stream) {
+    if (!w || !out || K <= 0 || K % 256 || N <= 0) return TFR_E_INVALID;
+    const long long nblk = (long long)N * (K / 256);
+    const int grid = (int)((nblk + 127) / 128);
+    if (type == TFR_Q4_K) k_synth_q4k<<<grid, 128, 0, (cudaStream_t)stream>>>(w, (uint8_t*)out, nblk);
+    else if (type == TFR_Q6_K) k_synth_q6k<<<grid, 128, 0, (cudaStream_t)stream>>>(w, (uint8_t*)out, nblk);
+    else return TFR_E_UNSUPPORTED;
+    return check(cudaGetLastError());
+}

@@ -1,0 +1,254 @@
+"""Host-side mirror of the reference's device-runtime interface over the C ABI.
+
+Names and behaviour follow crates/core/src/cuda: `CudaModel` (model.rs:18-201,
+forward.rs:20-105, load.rs:166) and `CudaKv` (kv.rs:6-42).  Errors surface as
+`TfrError` carrying the reference's messages ("empty tokens", "context full").
+Everything here is plumbing around libtarafer_b200.so; there is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import ModelConfig
+
+TYPE_F32, TYPE_Q4_K, TYPE_Q6_K = 0, 12, 14
+
+
+class TfrError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"[{code}] {msg}")
+        self.code, self.msg = code, msg
+
+
+def _ptr(a) -> int:
+    """Address of a numpy array, a torch tensor (host or device) or a raw integer."""
+    if a is None:
+        return 0
+    if isinstance(a, int):
+        return a
+    if isinstance(a, np.ndarray):
+        return a.ctypes.data
+    return a.data_ptr()
+
+
+def _nbytes(a) -> int:
+    return a.nbytes if isinstance(a, np.ndarray) else a.numel() * a.element_size()
+
+
+def model_config(cfg: dict, context_length: int = 4096) -> ModelConfig:
+    c = ModelConfig()
+    c.n_layer, c.n_embd, c.n_head, c.n_kv_head = cfg["n_layer"], cfg["n_embd"], cfg["n_head"], cfg["n_kv"]
+    c.head_dim, c.n_ff, c.n_vocab = cfg["head_dim"], cfg["n_ff"], cfg["n_vocab"]
+    c.context_length = context_length
+    c.rope_theta, c.rms_eps = cfg["rope_theta"], cfg["eps"]
+    c.hybrid = int(cfg.get("hybrid", 0))
+    for k in ("rope_dim", "ssm_conv_kernel", "ssm_state_size", "ssm_group_count", "ssm_time_step_rank",
+              "ssm_inner_size", "full_attention_interval"):
+        setattr(c, k, int(cfg.get(k, 0)))
+    c.tp_rank, c.tp_size = int(cfg.get("tp_rank", 0)), int(cfg.get("tp_size", 1))
+    return c
+
+
+class CudaKv:
+    """kv.rs:6-42: append-only f16 K/V arena; `len` is assignable by the caller (session.rs:345)."""
+
+    def __init__(self, model: "CudaModel", handle: int):
+        self._model, self._h = model, handle
+
+    @property
+    def len(self) -> int:
+        return _lib.lib().tfr_kv_len(self._h)
+
+    @len.setter
+    def len(self, n: int) -> None:
+        rc = _lib.lib().tfr_kv_set_len(self._h, int(n))
+        if rc:
+            raise TfrError(rc, "kv length out of range")
+
+    @property
+    def max_seq(self) -> int:
+        return _lib.lib().tfr_kv_max_seq(self._h)
+
+    def clear(self) -> None:
+        _lib.lib().tfr_kv_clear(self._h)
+
+    def bytes_per_token(self) -> int:
+        return _lib.lib().tfr_kv_bytes_per_token(self._h)
+
+    def free(self) -> None:
+        if self._h:
+            _lib.lib().tfr_free_kv(self._h)
+            self._h = 0
+
+
+class CudaModel:
+    """model.rs:18-201 / forward.rs: the decode engine for one GPU."""
+
+    def __init__(self, device: int = 0):
+        h = C.c_void_p()
+        rc = _lib.lib().tfr_create(device, C.byref(h))
+        if rc:
+            raise TfrError(rc, "tfr_create failed: no usable CUDA device (this library has no CPU fallback)")
+        self._h = h.value
+        self.cfg: dict | None = None
+        name = C.create_string_buffer(256)
+        maj, mnr, sms = C.c_int(), C.c_int(), C.c_int()
+        _lib.lib().tfr_device_info(self._h, name, 256, C.byref(maj), C.byref(mnr), C.byref(sms))
+        self.gpu_name, self.compute_major, self.compute_minor = name.value.decode(), maj.value, mnr.value
+        self.sm_count = sms.value
+
+    # -- loading (load.rs:166-609) ------------------------------------------------------
+    def _check(self, rc: int) -> None:
+        if rc:
+            raise TfrError(rc, _lib.lib().tfr_last_error(self._h).decode())
+
+    def set_config(self, cfg: dict, context_length: int = 4096) -> None:
+        self.cfg = dict(cfg)
+        c = model_config(cfg, context_length)
+        self._check(_lib.lib().tfr_set_config(self._h, C.byref(c)))
+
+    def upload_tensor(self, name: str, ggml_type: int, n_rows: int, n_cols: int, data) -> None:
+        """`data`: numpy array or torch tensor (host or device) holding the raw GGUF bytes."""
+        self._check(_lib.lib().tfr_upload_tensor(self._h, name.encode(), ggml_type, n_rows, n_cols, _ptr(data),
+                                                 _nbytes(data)))
+
+    def finalize_load(self) -> None:
+        self._check(_lib.lib().tfr_finalize_load(self._h))
+
+    @classmethod
+    def load_with(cls, cfg: dict, tensors: dict, device: int = 0, context_length: int = 4096) -> "CudaModel":
+        """CudaModel::load_with for tensors already in memory: name -> (type, K, N, bytes) for
+        matrices, name -> fp32 array for vectors."""
+        m = cls(device)
+        m.set_config(cfg, context_length)
+        for name, t in tensors.items():
+            if isinstance(t, tuple):
+                wt, K, N, data = t
+                m.upload_tensor(name, wt, K, N, data)
+            else:
+                a = np.ascontiguousarray(t, dtype=np.float32) if isinstance(t, np.ndarray) else t
+                m.upload_tensor(name, TYPE_F32, _nbytes(a) // 4, 1, a)
+        m.finalize_load()
+        return m
+
+    # -- runtime ----------------------------------------------------------------------------
+    def alloc_kv(self, max_seq: int) -> CudaKv:
+        h = C.c_void_p()
+        self._check(_lib.lib().tfr_alloc_kv(self._h, max_seq, C.byref(h)))
+        return CudaKv(self, h.value)
+
+    def zero_recurrent(self, kv: CudaKv) -> None:
+        self._check(_lib.lib().tfr_zero_recurrent(self._h, kv._h))
+
+    def set_cuda_graph(self, enabled: bool) -> None:
+        self._check(_lib.lib().tfr_set_cuda_graph(self._h, int(enabled)))
+
+    def graph_active(self) -> bool:
+        return bool(_lib.lib().tfr_graph_active(self._h))
+
+    def forward_greedy(self, tokens, kv: CudaKv) -> int:
+        t = np.ascontiguousarray(tokens, dtype=np.uint32)
+        out = C.c_uint32()
+        self._check(_lib.lib().tfr_forward_greedy(self._h, kv._h, t.ctypes.data, t.size, C.byref(out)))
+        return int(out.value)
+
+    def decode_burst(self, first_token: int, max_n: int, kv: CudaKv, stop_ids=()) -> np.ndarray:
+        stops = np.ascontiguousarray(stop_ids, dtype=np.uint32)
+        out = np.zeros(max(max_n, 1), np.uint32)
+        n = C.c_int()
+        self._check(_lib.lib().tfr_decode_burst(self._h, kv._h, int(first_token), int(max_n),
+                                                stops.ctypes.data if stops.size else 0, stops.size, out.ctypes.data,
+                                                C.byref(n)))
+        return out[: n.value].copy()
+
+    def current_logits(self) -> np.ndarray:
+        out = np.zeros(self.cfg["n_vocab"], np.float32)
+        self._check(_lib.lib().tfr_current_logits(self._h, out.ctypes.data, out.size))
+        return out
+
+    def launch_count(self) -> int:
+        return int(_lib.lib().tfr_launch_count(self._h))
+
+    def last_device_ms(self) -> float:
+        return float(_lib.lib().tfr_last_device_ms(self._h))
+
+    def debug_read(self, what: str, n: int, dtype=np.float32, kv: CudaKv | None = None, layer: int = 0) -> np.ndarray:
+        out = np.zeros(n, dtype)
+        self._check(_lib.lib().tfr_debug_read(self._h, kv._h if kv else 0, what.encode(), layer, out.ctypes.data,
+                                              out.nbytes))
+        return out
+
+    def destroy(self) -> None:
+        if self._h:
+            _lib.lib().tfr_destroy(self._h)
+            self._h = 0
+
+
+class GpuMat:
+    """types.rs:26-39: one weight matrix in decode layout on the device."""
+
+    def __init__(self, ggml_type: int, K: int, N: int, data, rope_pair_head_dim: int = 0):
+        h = C.c_void_p()
+        rc = _lib.lib().tfr_mat_create(ggml_type, K, N, _ptr(data), _nbytes(data), rope_pair_head_dim, C.byref(h))
+        if rc:
+            raise TfrError(rc, "tfr_mat_create failed")
+        self._h, self.K, self.N, self.type = h.value, K, N, ggml_type
+
+    def free(self) -> None:
+        if self._h:
+            _lib.lib().tfr_mat_free(self._h)
+            self._h = 0
+
+
+def _ok(rc: int, what: str) -> None:
+    if rc:
+        raise TfrError(rc, what)
+
+
+# Operator-level calls on device pointers (torch tensors); thin wrappers used by tests and bench.
+def op_quantize_q8(x, q8, d8, stream: int = 0) -> None:
+    _ok(_lib.lib().tfr_op_quantize_q8(_ptr(x), x.numel(), _ptr(q8), _ptr(d8), stream), "quantize_q8")
+
+
+def op_gemv(w: GpuMat, x, out, bias=None, use_res: int = 0, act_mode: int = 0, norm_w=None, eps: float = 0.0,
+            stream: int = 0) -> None:
+    _ok(_lib.lib().tfr_op_gemv(w._h, _ptr(x), _ptr(out), _ptr(bias), use_res, act_mode, _ptr(norm_w), eps, stream),
+        "gemv")
+
+
+def op_ffn_gate_up(gate: GpuMat, up: GpuMat, x, h, norm_w=None, eps: float = 0.0, stream: int = 0) -> None:
+    _ok(_lib.lib().tfr_op_ffn_gate_up(gate._h, up._h, _ptr(x), _ptr(norm_w), eps, _ptr(h), stream), "ffn_gate_up")
+
+
+def op_ffn_block(gate: GpuMat, up: GpuMat, down: GpuMat, x, h_scratch, y, use_res: int = 0, stream: int = 0) -> None:
+    _ok(_lib.lib().tfr_op_ffn_block(gate._h, up._h, down._h, _ptr(x), _ptr(h_scratch), _ptr(y), use_res, stream),
+        "ffn_block")
+
+
+def ffn_block_host(gate: GpuMat, up: GpuMat, down: GpuMat, x: np.ndarray, y: np.ndarray) -> None:
+    _ok(_lib.lib().tfr_ffn_block_host(gate._h, up._h, down._h, _ptr(x), _ptr(y)), "ffn_block_host")
+
+
+def op_int_dots(w: GpuMat, q8, d8, a, b=None, stream: int = 0) -> None:
+    _ok(_lib.lib().tfr_op_int_dots(w._h, _ptr(q8), _ptr(d8), _ptr(a), _ptr(b), stream), "int_dots")
+
+
+def op_attention(q, kc, vc, out, n_head: int, n_kv: int, head_dim: int, pos: int, stream: int = 0) -> None:
+    _ok(_lib.lib().tfr_op_attention(_ptr(q), _ptr(kc), _ptr(vc), _ptr(out), n_head, n_kv, head_dim, pos, stream),
+        "attention")
+
+
+def op_qkv_rope_store(wq: GpuMat, wk: GpuMat, wv: GpuMat, bq, bk, bv, x, norm_w, eps: float, theta: float,
+                      head_dim: int, pos: int, q_out, kc, vc, stream: int = 0) -> None:
+    _ok(_lib.lib().tfr_op_qkv_rope_store(wq._h, wk._h, wv._h, _ptr(bq), _ptr(bk), _ptr(bv), _ptr(x), _ptr(norm_w),
+                                         eps, theta, head_dim, pos, _ptr(q_out), _ptr(kc), _ptr(vc), stream),
+        "qkv_rope_store")
+
+
+def synth_quantize(ggml_type: int, w, out, stream: int = 0) -> None:
+    """Quantise fp32 device rows w[N][K] into GGUF bytes on the device."""
+    N, K = w.shape
+    _ok(_lib.lib().tfr_synth_quantize(ggml_type, _ptr(w), K, N, _ptr(out), stream), "synth_quantize")
