@@ -1,0 +1,366 @@
+#!/usr/bin/env python
+"""Batch-1 greedy decode benchmark on the Qwen2.5-3B-shaped Q4_K_M model (BASELINE configuration 2).
+
+One step = one pass of the hot path over one batch of synthetic input: starting from a
+32-token prompt already in the KV cache, decode 256 tokens greedily with the on-device
+token loop.  Weights are random N(0, 0.02) quantised on the device (no model files are
+available); norm weights are ones; ctx 4096.  `value` is tokens per second with everything
+resident in HBM (CUDA events around the kernels); `e2e` is the same count of tokens over
+the wall-clock time of the C-ABI call that takes its scalars from host memory and returns
+the tokens to host memory.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+N > 1 runs N independent replicas (one process per GPU under torchrun): the decode loop
+of this model has no unit to shard without a per-layer exchange, which costs more than a
+layer's HBM time at this size.  `--impl reference` times the CPU restatement of the
+reference algorithm (the reference has no CPU path of its own for these kernels) on all
+host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+PROMPT_LEN, N_DECODE, CTX = 32, 256, 4096
+METRIC, UNIT = "batch1_decode_tokens_per_s", "tok/s"
+NOMINAL_HBM_GBS = 8000.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate+up launch, from the ncu capture
+# summarised in profiles/ffn_gate_up_qwen25_3b.md (None until such a capture exists)
+GATE_UP_DRAM_TRAFFIC_BYTES = None
+
+
+def measured_peaks() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle samples taken while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.rows, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.t.join(timeout=2)
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def cpu_port_tokens_per_s(host_tensors, cfg, prompt, first, n_tokens: int, threads: int):
+    """Times the CPU restatement (oracle/) on n_tokens decode steps after the prompt.  Checker code
+    used as a reported baseline only."""
+    from oracle import oracle as O
+    O.set_threads(threads)
+    om = O.OracleModel(cfg, host_tensors, PROMPT_LEN + n_tokens + 1)
+    # fill the prompt rows of the cache cheaply: only what attention needs, one pass per token
+    for i, t in enumerate(prompt):
+        om.decode_token(i, int(t))
+    t0 = time.perf_counter()
+    om.decode_greedy(PROMPT_LEN, int(first), n_tokens)
+    dt = time.perf_counter() - t0
+    O.set_threads(1)
+    return n_tokens / dt, dt
+
+
+def run_reference_arm(args, rank, world):
+    """`--impl reference`: the reference algorithm on the host cores (CPU restatement)."""
+    if rank != 0:
+        return
+    import torch
+    from oracle import oracle as O
+    from taraference_b200 import synth as S
+    cfg = dict(S.QWEN25_3B)
+    threads = O.max_threads()
+    # same model bytes as the GPU arm when a GPU is there (device generator), else a numpy model
+    if torch.cuda.is_available():
+        from taraference_b200 import synth_gpu
+        model, host = synth_gpu.build_dense_model(cfg, seed=0, keep_host=True, context_length=CTX)
+        model.destroy()
+    else:
+        host = S.make_dense_model(cfg, seed=0)
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, cfg["n_vocab"], PROMPT_LEN)
+    O.set_threads(threads)
+    om = O.OracleModel(cfg, host, CTX)
+    sample = 2  # tokens per step: a bounded sample of the 256-token workload
+    pos = 0
+    for t in prompt[:4]:  # short prefix keeps the run within minutes; attention cost is negligible here
+        om.decode_token(pos, int(t))
+        pos += 1
+    tok = int(prompt[4])
+    times = []
+    for step in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        toks, _, _ = om.decode_greedy(pos, tok, sample)
+        dt = time.perf_counter() - t0
+        pos += sample
+        tok = int(toks[-1])
+        if step >= args.warmup:
+            times.append(dt)
+    total = float(np.sum(times))
+    value = sample * len(times) / total
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000 * total / len(times),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
+            "data": "synthetic",
+            "config": {"workload": "qwen2.5-3b-shape Q4_K_M batch-1 greedy decode, CPU restatement of the reference "
+                                   "kernels' arithmetic (the reference has no CPU implementation of this path)",
+                       "prompt_tokens": 4, "decode_tokens_per_step": sample},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                             "sample": f"{sample} decode tokens per step, {len(times)} steps, OpenMP over {threads} threads"},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def reference_kernels_on_gpu(cfg, host, prompt_len: int):
+    """The reference's own kernels (compiled unmodified, its launch shapes) replayed from a CUDA graph of
+    one decode step at a mid-run position: what its token costs on this GPU without its host loop."""
+    import torch
+    try:
+        from oracle import ref_gpu
+        if not ref_gpu.available():
+            return None
+        rm = ref_gpu.RefModel(cfg, host, prompt_len + N_DECODE + 1)
+        pos = prompt_len + N_DECODE // 2
+        rm.decode_token(pos, 17)  # warm-up, loads modules
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        before = ref_gpu.kernels().launches
+        with torch.cuda.graph(g):
+            rm.decode_token(pos, 17)
+        nodes = ref_gpu.kernels().launches - before
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        reps = 32
+        for _ in range(reps):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1000 / reps
+        return {"us_per_token": us, "tokens_per_s": 1e6 / us, "kernel_nodes": nodes,
+                "note": "reference .cu compiled unmodified with its NVRTC options for sm_100, its launch shapes, one "
+                        "CUDA graph per token, no argmax readback"}
+    except Exception as exc:  # the comparison is informative; never fail the bench for it
+        return {"error": repr(exc)[:200]}
+
+
+def gate_up_roofline(E, S, cfg, peak_gbs, peak_kind):
+    """Average duration of the fused gate+up kernel (the largest per-layer read) over distinct weight
+    sets that together exceed L2, with CUDA events on the launching stream."""
+    import torch
+    from taraference_b200 import synth_gpu
+    K, FF = cfg["n_embd"], cfg["n_ff"]
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(123)
+    sets = []
+    for _ in range(10):  # 10 x 25.4 MB = 254 MB > 126 MB L2
+        g = synth_gpu.quantized_matrix(S.Q4_K, K, FF, gen)
+        u = synth_gpu.quantized_matrix(S.Q4_K, K, FF, gen)
+        sets.append((E.GpuMat(S.Q4_K, K, FF, g), E.GpuMat(S.Q4_K, K, FF, u)))
+        del g, u
+    x = torch.randn(K, device="cuda")
+    nw = torch.ones(K, device="cuda")
+    h = torch.zeros(FF, device="cuda")
+    for mg, mu in sets:
+        E.op_ffn_gate_up(mg, mu, x, h, nw, 1e-6)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    rounds = 20
+    a.record()
+    for _ in range(rounds):
+        for mg, mu in sets:
+            E.op_ffn_gate_up(mg, mu, x, h, nw, 1e-6)
+    b.record()
+    torch.cuda.synchronize()
+    us = a.elapsed_time(b) * 1000 / (rounds * len(sets))
+    alg = 2 * FF * (K // 256) * 144 + 2 * K * 4 + FF * 4  # both matrices + x + norm weights + h
+    for mg, mu in sets:
+        mg.free(), mu.free()
+    ach = alg / us * 1e-3
+    return {"bound": "hbm", "kernel": "k_gemv<MapPair,EpiSilu> (RMSNorm+Q8+gate/up+SiLU*mul, 11008x2048 Q4_K x2)",
+            "achieved": ach, "peak": peak_gbs, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": ach / peak_gbs,
+            "traffic": GATE_UP_DRAM_TRAFFIC_BYTES, "algorithmic_bytes_per_launch": alg, "us_per_launch": us,
+            "note": "back-to-back launches on one stream: includes the launch gap"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-reference-gpu", action="store_true")
+    args = ap.parse_args()
+    rank, world, local = dist_env()
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the decode library has no CPU fallback")
+    from taraference_b200 import engine as E, synth as S, synth_gpu
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    warmup = max(args.warmup, 3)
+    cfg = dict(S.QWEN25_3B)
+    want_host = rank == 0 and world == 1 and not (args.skip_cpu_baseline and args.skip_reference_gpu)
+    model, host = synth_gpu.build_dense_model(cfg, seed=0, device=local, context_length=CTX, keep_host=want_host)
+    kv = model.alloc_kv(CTX)
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, cfg["n_vocab"], PROMPT_LEN)
+    first = model.forward_greedy(prompt, kv)  # prefill once; every step restarts from this cache state
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def one_step():
+        kv.len = PROMPT_LEN
+        t0 = time.perf_counter()
+        toks = model.decode_burst(first, N_DECODE, kv)
+        wall = time.perf_counter() - t0
+        assert len(toks) == N_DECODE
+        return model.last_device_ms(), wall, toks
+
+    for _ in range(warmup):
+        one_step()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    launches0 = model.launch_count()
+    dev_ms, walls = [], []
+    t_all = time.perf_counter()
+    for _ in range(args.steps):
+        d, w, toks = one_step()
+        dev_ms.append(d)
+        walls.append(w)
+    barrier()
+    wall_all = time.perf_counter() - t_all
+    clocks = sampler.stop() if rank == 0 else None
+    launches = model.launch_count() - launches0
+    dev_total, wall_total = float(np.sum(dev_ms)), float(np.sum(walls))
+    if world > 1:
+        t = torch.tensor([dev_total, wall_total], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_total, wall_total = float(t[0]), float(t[1])
+    tokens_all = N_DECODE * args.steps * world
+    value = tokens_all / (dev_total / 1000.0)
+    e2e_value = tokens_all / wall_total
+
+    # per-token host round-trip through forward_greedy (the reference's call pattern), rank 0 only
+    per_token_api = None
+    if rank == 0:
+        kv.len = PROMPT_LEN
+        t, t0 = first, time.perf_counter()
+        for _ in range(64):
+            t = model.forward_greedy([t], kv)
+        per_token_api = 64 / (time.perf_counter() - t0)
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        wbytes = synth_gpu.weight_bytes(cfg)
+        kvb = synth_gpu.kv_bytes_per_position(cfg)
+        bytes_per_token = wbytes + kvb * (PROMPT_LEN + N_DECODE / 2)
+        us_tok = dev_total * 1000 / (N_DECODE * args.steps)
+        token_gbs = bytes_per_token / us_tok * 1e-3
+        roof = gate_up_roofline(E, S, cfg, peak, peak_kind) if world == 1 else None
+        cpu = None
+        if want_host and not args.skip_cpu_baseline:
+            from oracle import oracle as O
+            th = O.max_threads()
+            v, dt = cpu_port_tokens_per_s(host, cfg, prompt[:4], int(prompt[4]), 4, th)
+            cpu = {"value": v, "unit": UNIT, "cores": th, "kind": "port",
+                   "sample": f"4 decode tokens after a 4-token prefix ({dt:.1f} s), OpenMP over {th} threads"}
+        ref_gpu_info = None
+        if want_host and not args.skip_reference_gpu:
+            ref_gpu_info = reference_kernels_on_gpu(cfg, host, PROMPT_LEN)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": dev_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8", "data": "synthetic",
+            "config": {"workload": "qwen2.5-3b-shape Q4_K_M, batch-1 greedy decode, 32-token prompt, 256 decoded tokens "
+                                   "per step, ctx 4096 (BASELINE configuration 2)",
+                       "weights": "N(0,0.02) quantised on device; Q6_K token_embd/attn_v/ffn_down, Q4_K elsewhere",
+                       "l2": "each token streams 2.03 GB of weights, far beyond the 126 MB L2",
+                       "parallelism": "replicas" if world > 1 else "single GPU",
+                       "timing": "CUDA events on the engine's stream around each 256-token burst; max over ranks"},
+            "us_per_token": us_tok,
+            "token_roofline": {"bytes_per_token": bytes_per_token, "achieved_gbs": token_gbs,
+                               "frac_of_8TBs_nominal": token_gbs / NOMINAL_HBM_GBS,
+                               f"frac_of_{peak_kind}_copy_peak": token_gbs / peak, "peak_gbs": peak},
+            "roofline": roof, "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 64, "d2h_bytes_per_step": 4 * N_DECODE + 96,
+                    "call": "tfr_decode_burst: scalars from pinned host memory, tokens back to host memory",
+                    "per_token_forward_greedy_tok_s": per_token_api},
+            "gpu_launches": int(launches), "clocks": clocks, "reference_kernels_same_gpu": ref_gpu_info,
+            "wall_s_timed_region": wall_all,
+        }
+        print(json.dumps(line), flush=True)
+    kv.free()
+    model.destroy()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -116,7 +116,9 @@ int64_t tfr_launch_count(const tfr_engine* e);
 /* Device time of the last tfr_decode_burst / tfr_forward_greedy in milliseconds (CUDA events
  * on the engine's stream, around the kernels only). */
 float tfr_last_device_ms(const tfr_engine* e);
-/* Test tap: copy a named workspace of the last step to the host ("x", "q", "attn", "h", "logits"). */
+/* Test tap: copy a named workspace of the last step to the host ("x", "q", "attn", "h", "logits",
+ * "k"/"v" = cache of `layer`, "layer_x" = residual stream after every layer; the first "layer_x"
+ * request switches that tap on for later steps and returns zeros). */
 int tfr_debug_read(tfr_engine* e, tfr_kv* kv, const char* what, int layer, void* out, size_t nbytes);
 
 /* ---- operator level (device pointers unless stated; stream = cudaStream_t or NULL) ---- */

@@ -75,6 +75,9 @@ def lib():
                                           C.c_void_p, C.POINTER(Taps), C.c_int]
         _lib.tfo_decode_greedy.argtypes = [C.POINTER(Model), C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                            C.c_void_p, C.c_void_p, C.c_void_p]
+        _lib.tfo_layer_forward.argtypes = [C.POINTER(Model), C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]
+        _lib.tfo_head_forward.argtypes = [C.POINTER(Model), C.c_void_p, C.c_void_p, C.c_void_p]
+        _lib.tfo_embed.argtypes = [C.POINTER(Model), C.c_int, C.c_void_p]
         _lib.tfo_rms_norm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_float]
         _lib.tfo_rope_neox.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float]
         _lib.tfo_attention.argtypes = [C.c_void_p] * 4 + [C.c_int] * 4 + [C.c_float]
@@ -253,6 +256,24 @@ class OracleModel:
                                     C.byref(taps), int(act_f32))
         assert rc == 0, rc
         return (logits, xf, xn) if want_taps else logits
+
+    def embed(self, token: int) -> np.ndarray:
+        x = np.zeros(self.cfg["n_embd"], np.float32)
+        assert lib().tfo_embed(C.byref(self.m), token, _p(x)) == 0
+        return x
+
+    def layer_forward(self, li: int, x: np.ndarray, pos: int) -> np.ndarray:
+        """One layer applied to a copy of the residual stream x at position pos (writes cache row pos)."""
+        x = _f32(x).copy()
+        rc = lib().tfo_layer_forward(C.byref(self.m), li, _p(x), _p(self.kc[li]), _p(self.vc[li]), pos, 0)
+        assert rc == 0, rc
+        return x
+
+    def head_forward(self, x: np.ndarray) -> np.ndarray:
+        x = _f32(x)
+        logits = np.zeros(self.cfg["n_vocab"], np.float32)
+        assert lib().tfo_head_forward(C.byref(self.m), _p(x), _p(logits), None) == 0
+        return logits
 
     def decode_greedy(self, pos0: int, first: int, n: int):
         toks = np.zeros(n, np.int32)

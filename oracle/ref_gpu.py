@@ -178,6 +178,16 @@ def ffn_gate_up(gate: RefMat, up: RefMat, x):
     return out
 
 
+def ffn_gate_up_8way(gate: RefMat, up: RefMat, x):
+    """gemv_q4_k_ffn_8way, matmul.rs:698-725: the reference's alternative FFN kernel (8 warps split K,
+    pre-quantised activation); same mathematics as the mcol kernel, different summation order."""
+    q, d = quantize_q8(x)
+    out = torch.zeros(gate.N, dtype=torch.float32, device="cuda")
+    kernels().launch("gemv_q4_k_ffn_8way", (gate.N,), (256,), 0, gate.data, up.data, q, d, out, gate.K, gate.N,
+                     gate.col_bytes)
+    return out
+
+
 def rope(x, n_heads, hd, pos, theta):
     """rope launch, layer.rs:~560-600: grid (heads, n_tok) x 32 (ops.cu:348-371)."""
     kernels().launch("rope_neox_f32", (n_heads, 1), (32,), 0, x, n_heads, hd, pos, 1, float(theta))
@@ -220,8 +230,11 @@ class RefModel:
     """The reference's n_tok = 1 schedule (layer.rs:142-709, 1210-1456, 2125-2259) assembled
     from its own kernels, for the BASELINE dense mix at K < 4096."""
 
-    def __init__(self, cfg: dict, tensors: dict, max_seq: int):
-        self.cfg, self.max_seq = cfg, max_seq
+    def __init__(self, cfg: dict, tensors: dict, max_seq: int, alt_ffn: bool = False):
+        """alt_ffn: use the reference's other FFN kernel (gemv_q4_k_ffn_8way).  Both are the
+        reference; they differ only in fp32 summation order, which makes the pair a measure of
+        how far the reference's logits move under reassociation alone."""
+        self.cfg, self.max_seq, self.alt_ffn = cfg, max_seq, alt_ffn
         L = cfg["n_layer"]
 
         def m(name):
@@ -246,40 +259,42 @@ class RefModel:
         self.kc = [torch.zeros(max_seq * kvn, dtype=torch.int16, device="cuda") for _ in range(L)]
         self.vc = [torch.zeros(max_seq * kvn, dtype=torch.int16, device="cuda") for _ in range(L)]
 
-    def decode_token(self, pos: int, token: int, taps: dict | None = None) -> torch.Tensor:
+    def layer_forward(self, li: int, x: torch.Tensor, pos: int, taps: dict | None = None) -> torch.Tensor:
+        """One decoder layer applied in place to the residual stream x at position pos."""
         c = self.cfg
         H, Hkv, hd = c["n_head"], c["n_kv"], c["head_dim"]
         kvn = Hkv * hd
+        L = self.layers[li]
+        xb = rms_norm(x, L["an"], c["eps"])
+        q, k = gemv_q4_pair(L["wq"], L["wk"], xb, L["bq"], L["bk"])
+        if L["wv"].type == Q6_K:
+            v = gemv_q6_f32(L["wv"], xb, L["bv"])
+        else:
+            v = gemv_q8(L["wv"], xb, bias=L["bv"])
+        rope(q, H, hd, pos, c["rope_theta"])
+        rope(k, Hkv, hd, pos, c["rope_theta"])
+        copy_kv(k, self.kc[li], pos, kvn)
+        copy_kv(v, self.vc[li], pos, kvn)
+        att = attention(q, self.kc[li], self.vc[li], H, Hkv, hd, pos)
+        gemv_q8(L["wo"], att, out=x, use_res=2)
+        xb = rms_norm(x, L["fn"], c["eps"])
+        h = (ffn_gate_up_8way if self.alt_ffn else ffn_gate_up)(L["gate"], L["up"], xb)
+        gemv_q8(L["down"], h, out=x, use_res=2)
+        if taps is not None:
+            taps[f"q{li}"], taps[f"attn{li}"], taps[f"h{li}"], taps[f"x{li}"] = q, att, h, x.clone()
+        return x
+
+    def head_forward(self, x: torch.Tensor) -> torch.Tensor:
+        xb = rms_norm(x, self.out_norm, self.cfg["eps"])
+        return gemv_q8(self.head, xb)
+
+    def decode_token(self, pos: int, token: int, taps: dict | None = None) -> torch.Tensor:
         x = embed(self.embd, token)
-        for li, L in enumerate(self.layers):
-            xb = rms_norm(x, L["an"], c["eps"])
-            q, k = gemv_q4_pair(L["wq"], L["wk"], xb, L["bq"], L["bk"])
-            if L["wv"].type == Q6_K:
-                v = gemv_q6_f32(L["wv"], xb, L["bv"])
-            else:
-                v = gemv_q8(L["wv"], xb, bias=L["bv"])
-            rope(q, H, hd, pos, c["rope_theta"])
-            rope(k, Hkv, hd, pos, c["rope_theta"])
-            copy_kv(k, self.kc[li], pos, kvn)
-            copy_kv(v, self.vc[li], pos, kvn)
-            if taps is not None and li == 0:
-                taps["q0"] = q.clone()
-            att = attention(q, self.kc[li], self.vc[li], H, Hkv, hd, pos)
-            if taps is not None and li == 0:
-                taps["attn0"] = att.clone()
-            gemv_q8(L["wo"], att, out=x, use_res=2)
-            xb = rms_norm(x, L["fn"], c["eps"])
-            h = ffn_gate_up(L["gate"], L["up"], xb)
-            if taps is not None and li == 0:
-                taps["h0"] = h.clone()
-            gemv_q8(L["down"], h, out=x, use_res=2)
-            if taps is not None and li == 0:
-                taps["x0"] = x.clone()
-        xb = rms_norm(x, self.out_norm, c["eps"])
-        logits = gemv_q8(self.head, xb)
+        for li in range(len(self.layers)):
+            x = self.layer_forward(li, x, pos, taps)
         if taps is not None:
             taps["x"] = x.clone()
-        return logits
+        return self.head_forward(x)
 
     def decode_greedy(self, pos0: int, first: int, n: int):
         toks, margins, tok = [], [], first

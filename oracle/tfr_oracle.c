@@ -457,20 +457,18 @@ typedef struct {
     float* xn_final; /* [n_embd] after output_norm */
 } tfo_taps;
 
-/* One batch-1 decode step: layer schedule of layer.rs:142-709 (attention block),
- * layer.rs:1210-1456 (dense FFN) and layer.rs:2125-2259 (head) at n_tok = 1, with the
- * BASELINE dispatch: Q4_K matrices take Q8 activations, a Q6_K attn_v takes fp32
- * activations, o-proj / down / head take Q8 activations.
- * kcache/vcache: [n_layer][max_seq][n_kv*hd] f16 bits.  Writes row `pos`.
+/* One decoder layer at n_tok = 1, applied in place to the residual stream x: layer
+ * schedule of layer.rs:142-709 (attention block) and layer.rs:1210-1456 (dense FFN) with
+ * the BASELINE dispatch: Q4_K matrices take Q8 activations, a Q6_K attn_v takes fp32
+ * activations, o-proj and down take Q8 activations.  kc / vc: this layer's cache,
+ * [max_seq][n_kv*hd] f16 bits; row `pos` is written.
  * act_f32 != 0 restates the reference's PREFILL arithmetic instead (gemm.cu: every
- * projection is dequantise-then-fp32; ops.cu silu_mul), used to fill a cache the way
- * forward.rs:54-65 does. */
-int tfo_decode_token(const tfo_model* M, uint16_t* kcache, uint16_t* vcache, int pos, int token, float* logits,
-                     const tfo_taps* taps, int act_f32) {
+ * projection is dequantise-then-fp32; ops.cu silu_mul), as forward.rs:54-65 fills a cache. */
+int tfo_layer_forward(const tfo_model* M, int li, float* x, uint16_t* kc, uint16_t* vc, int pos, int act_f32) {
     int K = M->n_embd, H = M->n_head, Hkv = M->n_kv, hd = M->head_dim, FF = M->n_ff;
-    if (pos < 0 || pos >= M->max_seq || token < 0 || token >= M->token_embd.N) return -1;
+    if (li < 0 || li >= M->n_layer || pos < 0 || pos >= M->max_seq) return -1;
     int qn = H * hd, kvn = Hkv * hd;
-    float* x = (float*)malloc(sizeof(float) * (size_t)K);
+    const tfo_layer* L = &M->layers[li];
     float* xb = (float*)malloc(sizeof(float) * (size_t)(K > qn ? K : qn));
     float* q = (float*)malloc(sizeof(float) * (size_t)qn);
     float* kb = (float*)malloc(sizeof(float) * (size_t)kvn);
@@ -478,44 +476,64 @@ int tfo_decode_token(const tfo_model* M, uint16_t* kcache, uint16_t* vcache, int
     float* h = (float*)malloc(sizeof(float) * (size_t)FF);
     float* u = (float*)malloc(sizeof(float) * (size_t)FF);
     int rc = 0;
-    size_t lstride = (size_t)M->max_seq * kvn;
-    /* embed.cu:112-131 */
-    rc |= tfo_dequant_row(M->token_embd.type, M->token_embd.data + (size_t)token * row_bytes(&M->token_embd), K, x);
-    for (int li = 0; li < M->n_layer && rc == 0; li++) {
-        const tfo_layer* L = &M->layers[li];
-        uint16_t* kc = kcache + (size_t)li * lstride;
-        uint16_t* vc = vcache + (size_t)li * lstride;
-        tfo_rms_norm(x, L->attn_norm, xb, K, M->eps);
-        rc |= tfo_gemv(&L->wq, xb, q, L->bq, 0, act_f32);
-        rc |= tfo_gemv(&L->wk, xb, kb, L->bk, 0, act_f32);
-        rc |= tfo_gemv(&L->wv, xb, vb, L->bv, 0, (act_f32 || L->wv.type == TFO_Q6_K) ? 1 : 0);
-        tfo_rope_neox(q, H, hd, pos, M->rope_theta);
-        tfo_rope_neox(kb, Hkv, hd, pos, M->rope_theta);
-        tfo_copy_kv_f16(kb, kc, pos, kvn);
-        tfo_copy_kv_f16(vb, vc, pos, kvn);
-        tfo_attention(q, kc, vc, xb, H, Hkv, hd, pos, 1.0f / sqrtf((float)hd));
-        {
-            tfo_mat wo = L->wo;
-            rc |= tfo_gemv(&wo, xb, x, NULL, 2, act_f32);
-        }
-        tfo_rms_norm(x, L->ffn_norm, xb, K, M->eps);
-        if (!act_f32) {
-            rc |= tfo_ffn_gate_up(&L->gate, &L->up, xb, h);
-        } else {
-            rc |= tfo_gemv(&L->gate, xb, h, NULL, 0, 1);
-            rc |= tfo_gemv(&L->up, xb, u, NULL, 0, 1);
-            for (int j = 0; j < FF; j++) h[j] = (h[j] / (1.f + expf(-h[j]))) * u[j];
-        }
-        rc |= tfo_gemv(&L->down, h, x, NULL, 2, act_f32);
+    tfo_rms_norm(x, L->attn_norm, xb, K, M->eps);
+    rc |= tfo_gemv(&L->wq, xb, q, L->bq, 0, act_f32);
+    rc |= tfo_gemv(&L->wk, xb, kb, L->bk, 0, act_f32);
+    rc |= tfo_gemv(&L->wv, xb, vb, L->bv, 0, (act_f32 || L->wv.type == TFO_Q6_K) ? 1 : 0);
+    tfo_rope_neox(q, H, hd, pos, M->rope_theta);
+    tfo_rope_neox(kb, Hkv, hd, pos, M->rope_theta);
+    tfo_copy_kv_f16(kb, kc, pos, kvn);
+    tfo_copy_kv_f16(vb, vc, pos, kvn);
+    tfo_attention(q, kc, vc, xb, H, Hkv, hd, pos, 1.0f / sqrtf((float)hd));
+    rc |= tfo_gemv(&L->wo, xb, x, NULL, 2, act_f32);
+    tfo_rms_norm(x, L->ffn_norm, xb, K, M->eps);
+    if (!act_f32) {
+        rc |= tfo_ffn_gate_up(&L->gate, &L->up, xb, h);
+    } else {
+        rc |= tfo_gemv(&L->gate, xb, h, NULL, 0, 1);
+        rc |= tfo_gemv(&L->up, xb, u, NULL, 0, 1);
+        for (int j = 0; j < FF; j++) h[j] = (h[j] / (1.f + expf(-h[j]))) * u[j];
     }
+    rc |= tfo_gemv(&L->down, h, x, NULL, 2, act_f32);
+    free(xb); free(q); free(kb); free(vb); free(h); free(u);
+    return rc;
+}
+
+/* Vocabulary head, layer.rs:2125-2259: logits = E . Q8(RMSNorm(x, output_norm)). */
+int tfo_head_forward(const tfo_model* M, const float* x, float* logits, float* xn_out) {
+    int K = M->n_embd;
+    float* xb = (float*)malloc(sizeof(float) * (size_t)K);
+    tfo_rms_norm(x, M->output_norm, xb, K, M->eps);
+    if (xn_out) memcpy(xn_out, xb, sizeof(float) * (size_t)K);
+    const tfo_mat* head = M->output.data ? &M->output : &M->token_embd;
+    int rc = tfo_gemv(head, xb, logits, NULL, 0, 0);
+    free(xb);
+    return rc;
+}
+
+/* Embedding row of a token, kernels/embed.cu:71-131. */
+int tfo_embed(const tfo_model* M, int token, float* x) {
+    if (token < 0 || token >= M->token_embd.N) return -1;
+    return tfo_dequant_row(M->token_embd.type, M->token_embd.data + (size_t)token * row_bytes(&M->token_embd),
+                           M->n_embd, x);
+}
+
+/* One batch-1 decode step (forward.rs:360-407 at n_tok = 1): embed, every layer, head.
+ * kcache/vcache: [n_layer][max_seq][n_kv*hd] f16 bits. */
+int tfo_decode_token(const tfo_model* M, uint16_t* kcache, uint16_t* vcache, int pos, int token, float* logits,
+                     const tfo_taps* taps, int act_f32) {
+    int K = M->n_embd;
+    if (pos < 0 || pos >= M->max_seq) return -1;
+    float* x = (float*)malloc(sizeof(float) * (size_t)K);
+    size_t lstride = (size_t)M->max_seq * M->n_kv * M->head_dim;
+    int rc = tfo_embed(M, token, x);
+    for (int li = 0; li < M->n_layer && rc == 0; li++)
+        rc = tfo_layer_forward(M, li, x, kcache + (size_t)li * lstride, vcache + (size_t)li * lstride, pos, act_f32);
     if (rc == 0) {
         if (taps && taps->x_final) memcpy(taps->x_final, x, sizeof(float) * (size_t)K);
-        tfo_rms_norm(x, M->output_norm, xb, K, M->eps);
-        if (taps && taps->xn_final) memcpy(taps->xn_final, xb, sizeof(float) * (size_t)K);
-        const tfo_mat* head = M->output.data ? &M->output : &M->token_embd;
-        if (logits) rc |= tfo_gemv(head, xb, logits, NULL, 0, 0);
+        if (logits) rc = tfo_head_forward(M, x, logits, taps ? taps->xn_final : NULL);
     }
-    free(x); free(xb); free(q); free(kb); free(vb); free(h); free(u);
+    free(x);
     return rc;
 }
 

@@ -195,6 +195,18 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
         for (int d = 0; d < DPT; d++) ored[kg][h][dp * DPT + d] = o[h][d];
     __syncthreads();
     const int po = 2 + HD;
+    if (S_eff == 1) {
+        // single split: normalise and store directly (the merge of one partial is the identity)
+        for (int idx = tid; idx < rep * HD; idx += ATTN_THREADS) {
+            const int h = idx / HD, d = idx % HD;
+            const int hg = g * rep + h;
+            const float tot = ored[0][h][d] + ored[1][h][d] + ored[2][h][d] + ored[3][h][d];
+            float r = tot / fmaxf(l_s[h], 1e-20f);
+            if (a.gate) r *= 1.f / (1.f + expf(-a.gate[hg * HD + d]));
+            a.out[hg * HD + d] = r;
+        }
+        return;
+    }
     for (int idx = tid; idx < rep * HD; idx += ATTN_THREADS) {
         const int h = idx / HD, d = idx % HD;
         const float tot = ored[0][h][d] + ored[1][h][d] + ored[2][h][d] + ored[3][h][d];

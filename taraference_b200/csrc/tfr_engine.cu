@@ -68,7 +68,9 @@ struct tfr_engine {
     TokenState* st = nullptr;
     TokenState* st_host = nullptr;  // pinned
     int *out_tokens = nullptr, *out_host = nullptr, *prompt = nullptr;
+    int *args_dev = nullptr, *args_host = nullptr;  // per-call scalars: pinned host -> device
     int attn_S = 1, attn_min_keys = 256;
+    float* layer_taps = nullptr;  // [n_layer][n_embd] residual stream after each layer (test aid)
     // graphs
     bool use_graph = true;
     cudaGraphExec_t g_decode = nullptr, g_body = nullptr;
@@ -113,8 +115,8 @@ static void configure_kernels_once() {
     static bool done = false;
     if (done) return;
     done = true;
-    const int big = 160 * 1024;
-    cudaFuncSetAttribute(k_gemv<MapStack, EpiQkv>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    const int big = 200 * 1024;
+    cudaFuncSetAttribute(k_gemv<MapQK, EpiQkv>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
     cudaFuncSetAttribute(k_gemv<MapSingle, EpiStore>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
     cudaFuncSetAttribute(k_gemv<MapPair, EpiSilu>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
     cudaFuncSetAttribute(k_gemv<MapSingle, EpiLogits>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
@@ -223,10 +225,13 @@ extern "C" void tfr_destroy(tfr_engine* e) {
     for (auto& kv : e->mats) tfr_mat_free(kv.second);
     for (auto& kv : e->vecs) cudaFree(kv.second.dev);
     for (auto& L : e->layers) cudaFree(L.bias_qkv);
-    void* ws[] = {e->x, e->q, e->attn, e->h, e->logits, e->partial, e->counters, e->st, e->out_tokens, e->prompt};
+    void* ws[] = {e->x, e->q, e->attn, e->h, e->logits, e->partial, e->counters, e->st, e->out_tokens, e->prompt,
+                  e->layer_taps};
     for (void* p : ws) cudaFree(p);
     if (e->st_host) cudaFreeHost(e->st_host);
     if (e->out_host) cudaFreeHost(e->out_host);
+    if (e->args_host) cudaFreeHost(e->args_host);
+    cudaFree(e->args_dev);
     cudaEventDestroy(e->ev0);
     cudaEventDestroy(e->ev1);
     cudaStreamDestroy(e->stream);
@@ -381,6 +386,8 @@ extern "C" int tfr_finalize_load(tfr_engine* e) {
     CU(e, cudaMalloc(&e->prompt, (size_t)TFR_MAX_PROMPT * 4));
     CU(e, cudaMallocHost(&e->st_host, sizeof(TokenState)));
     CU(e, cudaMallocHost(&e->out_host, (size_t)TFR_MAX_BURST * 4));
+    CU(e, cudaMalloc(&e->args_dev, 16 * sizeof(int)));
+    CU(e, cudaMallocHost(&e->args_host, 16 * sizeof(int)));
     CU(e, cudaMemsetAsync(e->counters, 0, (size_t)c.n_kv_head * 4, e->stream));
     CU(e, cudaMemsetAsync(e->st, 0, sizeof(TokenState), e->stream));
     CU(e, cudaMemsetAsync(e->logits, 0, (size_t)V * 4, e->stream));
@@ -447,13 +454,12 @@ static cudaError_t launch_attention(cudaStream_t s, const AttnArgs& a, int hd, c
 }
 
 static int wt_of(const tfr_mat* m) { return m->m.type == TFR_Q4_K ? WT_Q4K : WT_Q6K; }
-static int swz_of(const tfr_mat* m) { return m->m.type == TFR_Q4_K ? SWZ_Q4 : SWZ_Q6; }
 
 // Enqueues the kernels of one decode step; returns the number of launches or a negative error.
 static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
     const tfr_model_config& c = e->cfg;
     const int K = c.n_embd, hd = c.head_dim, nq = c.n_head * hd, nkv = c.n_kv_head * hd, FF = c.n_ff, V = c.n_vocab;
-    const int cap = e->prop.multiProcessorCount * 4;
+    const int cap = e->prop.multiProcessorCount;  // one 1024-thread CTA per SM
     cudaStream_t s = e->stream;
     int n = 0;
     for (int li = 0; li < c.n_layer; li++) {
@@ -464,20 +470,22 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
             pa.embed = e->token_embd->m;
             pa.normw = L.attn_norm;
             pa.eps = c.rms_eps;
-            pa.swz = SWZ_Q4;
-            pa.want_xf = L.wv->m.type == TFR_Q6_K;
+            pa.wt = WT_Q4K;
             pa.raw_out = e->x;
-            MapStack map{};
-            map.m[0] = L.wq->m;
-            map.m[1] = L.wk->m;
-            map.m[2] = L.wv->m;
-            map.wt[0] = map.wt[1] = WT_Q4K;
-            map.wt[2] = L.wv->m.type == TFR_Q6_K ? WT_Q6K_F32 : WT_Q4K;
-            map.start[0] = 0;
-            map.start[1] = nq;
-            map.start[2] = nq + nkv;
-            map.start[3] = map.start[4] = nq + 2 * nkv;
-            map.count = 3;
+            const bool v_f32 = L.wv->m.type == TFR_Q6_K;
+            MapQK map{};
+            map.q = L.wq->m;
+            map.k = L.wk->m;
+            map.shq = make_share(nq / 2, cap);
+            map.shk = make_share(nkv / 2, cap);
+            F32Seg fseg{};
+            if (v_f32) {
+                fseg.m = L.wv->m;
+                fseg.sh = make_share(nkv / 2, cap);
+                fseg.id_base = (nq + nkv) / 2;
+            } else {
+                return -2;  // a Q4_K attn_v would join the Q8 route; not wired yet
+            }
             EpiQkv epi{};
             epi.q_out = e->q;
             epi.kc = kv->k + (size_t)li * kv->layer_stride;
@@ -488,7 +496,7 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
             epi.hd = hd;
             epi.kvdim = nkv;
             epi.theta = c.rope_theta;
-            if (launch_gemv(s, cap, pa, map, epi, K, (nq + 2 * nkv) / 2, e->st) != cudaSuccess) return -1;
+            if (launch_gemv(s, cap, pa, map, fseg, epi, K, e->st) != cudaSuccess) return -1;
             n++;
         }
         {  // 2. attention
@@ -511,10 +519,10 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
         {  // 3. o-proj + residual
             PrepArgs pa{};
             pa.vec = e->attn;
-            pa.swz = swz_of(L.wo);
-            MapSingle map{L.wo->m, wt_of(L.wo)};
-            EpiStore epi{e->x, nullptr, 2};
-            if (launch_gemv(s, cap, pa, map, epi, nq, K, e->st) != cudaSuccess) return -1;
+            pa.wt = wt_of(L.wo);
+            MapSingle map{L.wo->m, make_share((K + 1) / 2, cap)};
+            EpiStore epi{e->x, nullptr, 2, K};
+            if (launch_gemv(s, cap, pa, map, F32Seg{}, epi, nq, e->st) != cudaSuccess) return -1;
             n++;
         }
         {  // 4. norm + quant + gate/up + silu*mul
@@ -522,33 +530,37 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
             pa.vec = e->x;
             pa.normw = L.ffn_norm;
             pa.eps = c.rms_eps;
-            pa.swz = SWZ_Q4;
-            MapPair map{L.gate->m, L.up->m};
+            pa.wt = WT_Q4K;
+            MapPair map{L.gate->m, L.up->m, make_share(FF, cap)};
             EpiSilu epi{e->h};
-            if (launch_gemv(s, cap, pa, map, epi, K, FF, e->st) != cudaSuccess) return -1;
+            if (launch_gemv(s, cap, pa, map, F32Seg{}, epi, K, e->st) != cudaSuccess) return -1;
             n++;
         }
         {  // 5. down + residual
             PrepArgs pa{};
             pa.vec = e->h;
-            pa.swz = swz_of(L.down);
-            MapSingle map{L.down->m, wt_of(L.down)};
-            EpiStore epi{e->x, nullptr, 2};
-            if (launch_gemv(s, cap, pa, map, epi, FF, K, e->st) != cudaSuccess) return -1;
+            pa.wt = wt_of(L.down);
+            MapSingle map{L.down->m, make_share((K + 1) / 2, cap)};
+            EpiStore epi{e->x, nullptr, 2, K};
+            if (launch_gemv(s, cap, pa, map, F32Seg{}, epi, FF, e->st) != cudaSuccess) return -1;
             n++;
         }
+        if (e->layer_taps &&
+            cudaMemcpyAsync(e->layer_taps + (size_t)li * K, e->x, (size_t)K * 4, cudaMemcpyDeviceToDevice, s) != cudaSuccess)
+            return -1;
     }
     if (with_head) {
         PrepArgs pa{};
         pa.vec = e->x;
         pa.normw = e->output_norm;
         pa.eps = c.rms_eps;
-        pa.swz = swz_of(e->head);
-        MapSingle map{e->head->m, wt_of(e->head)};
+        pa.wt = wt_of(e->head);
+        MapSingle map{e->head->m, make_share((V + 1) / 2, cap)};
         EpiLogits epi{};
         epi.logits = e->logits;
         epi.out_tokens = e->out_tokens;
-        if (launch_gemv(s, cap, pa, map, epi, K, V, e->st) != cudaSuccess) return -1;
+        epi.n_rows = V;
+        if (launch_gemv(s, cap, pa, map, F32Seg{}, epi, K, e->st) != cudaSuccess) return -1;
         n++;
     } else {
         k_state_next_prompt<<<1, 1, 0, s>>>(e->st, e->prompt);
@@ -600,10 +612,15 @@ static int run_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
 }
 
 static int begin_state(tfr_engine* e, int token, int pos, int max_steps, int max_seq, const uint32_t* stops, int n_stop) {
-    int s[8] = {-1, -1, -1, -1, -1, -1, -1, -1};
-    for (int i = 0; i < n_stop && i < 8; i++) s[i] = (int)stops[i];
-    k_state_begin<<<1, 1, 0, e->stream>>>(e->st, token, pos, max_steps, max_seq, n_stop, s[0], s[1], s[2], s[3], s[4], s[5],
-                                          s[6], s[7]);
+    int* a = e->args_host;
+    a[0] = token;
+    a[1] = pos;
+    a[2] = max_steps;
+    a[3] = max_seq;
+    a[4] = n_stop;
+    for (int i = 0; i < 8; i++) a[5 + i] = i < n_stop ? (int)stops[i] : -1;
+    CU(e, cudaMemcpyAsync(e->args_dev, a, 16 * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    k_state_begin<<<1, 1, 0, e->stream>>>(e->st, e->args_dev);
     CU(e, cudaGetLastError());
     e->launches += 1;
     return TFR_OK;
@@ -704,6 +721,16 @@ extern "C" int tfr_debug_read(tfr_engine* e, tfr_kv* kv, const char* what, int l
     else if (w == "attn") src = e->attn, have = (size_t)c.n_head * c.head_dim * 4;
     else if (w == "h") src = e->h, have = (size_t)c.n_ff * 4;
     else if (w == "logits") src = e->logits, have = (size_t)c.n_vocab * 4;
+    else if (w == "layer_x") {
+        // residual stream after every layer of the last step; the first request switches the taps on
+        if (!e->layer_taps) {
+            cudaSetDevice(e->device);
+            CU(e, cudaMalloc(&e->layer_taps, (size_t)c.n_layer * c.n_embd * 4));
+            CU(e, cudaMemset(e->layer_taps, 0, (size_t)c.n_layer * c.n_embd * 4));
+            drop_graphs(e);
+        }
+        src = e->layer_taps, have = (size_t)c.n_layer * c.n_embd * 4;
+    }
     else if ((w == "k" || w == "v") && kv && layer >= 0 && layer < c.n_layer) {
         src = (w == "k" ? kv->k : kv->v) + (size_t)layer * kv->layer_stride;
         have = kv->layer_stride * 2;
@@ -736,11 +763,17 @@ extern "C" int tfr_op_gemv(const tfr_mat* w, const float* x, float* out, const f
     pa.vec = x;
     pa.normw = norm_w;
     pa.eps = eps;
-    pa.swz = swz_of(w);
-    pa.want_xf = act_mode == 1;
-    MapSingle map{w->m, act_mode == 1 ? WT_Q6K_F32 : wt_of(w)};
-    EpiStore epi{out, bias, use_res};
-    return check(launch_gemv((cudaStream_t)stream, sm_count_cached() * 4, pa, map, epi, w->m.K, w->m.N, nullptr));
+    pa.wt = wt_of(w);
+    const int C = sm_count_cached(), pairs = (w->m.N + 1) / 2;
+    MapSingle map{w->m, make_share(act_mode == 1 ? 0 : pairs, C)};
+    F32Seg fseg{};
+    if (act_mode == 1) {
+        fseg.m = w->m;
+        fseg.sh = make_share(pairs, C);
+        fseg.id_base = 0;
+    }
+    EpiStore epi{out, bias, use_res, w->m.N};
+    return check(launch_gemv((cudaStream_t)stream, C, pa, map, fseg, epi, w->m.K, nullptr));
 }
 
 extern "C" int tfr_op_ffn_gate_up(const tfr_mat* gate, const tfr_mat* up, const float* x, const float* norm_w, float eps, float* h,
@@ -752,10 +785,10 @@ extern "C" int tfr_op_ffn_gate_up(const tfr_mat* gate, const tfr_mat* up, const 
     pa.vec = x;
     pa.normw = norm_w;
     pa.eps = eps;
-    pa.swz = SWZ_Q4;
-    MapPair map{gate->m, up->m};
+    pa.wt = WT_Q4K;
+    MapPair map{gate->m, up->m, make_share(gate->m.N, sm_count_cached())};
     EpiSilu epi{h};
-    return check(launch_gemv((cudaStream_t)stream, sm_count_cached() * 4, pa, map, epi, gate->m.K, gate->m.N, nullptr));
+    return check(launch_gemv((cudaStream_t)stream, sm_count_cached(), pa, map, F32Seg{}, epi, gate->m.K, nullptr));
 }
 
 extern "C" int tfr_op_ffn_block(const tfr_mat* gate, const tfr_mat* up, const tfr_mat* down, const float* x, float* h_scratch,
@@ -789,7 +822,7 @@ extern "C" int tfr_op_int_dots(const tfr_mat* w, const int8_t* q8, const float* 
     if (!w || !q8 || !d8 || !a || w->perm_hd) return TFR_E_INVALID;
     if (w->m.type == TFR_Q4_K && !b) return TFR_E_INVALID;
     configure_kernels_once();
-    const size_t smem = act_smem_bytes(w->m.K, false);
+    const size_t smem = act_smem_bytes(w->m.K, false, false);
     k_int_dots<<<sm_count_cached(), 256, smem, (cudaStream_t)stream>>>(w->m, (const signed char*)q8, d8, a, b);
     return check(cudaGetLastError());
 }
@@ -854,23 +887,22 @@ extern "C" int tfr_op_qkv_rope_store(const tfr_mat* wq, const tfr_mat* wk, const
         if (bk) k_permute_f32<<<(nkv + 255) / 256, 256, 0, s>>>(bk, bias + nq, nkv, head_dim);
         if (bv) k_permute_f32<<<(nkv + 255) / 256, 256, 0, s>>>(bv, bias + nq + nkv, nkv, 0);
     }
+    if (wv->m.type != TFR_Q6_K) return TFR_E_UNSUPPORTED;
     PrepArgs pa{};
     pa.vec = x;
     pa.normw = norm_w;
     pa.eps = eps;
-    pa.swz = SWZ_Q4;
-    pa.want_xf = wv->m.type == TFR_Q6_K;
-    MapStack map{};
-    map.m[0] = wq->m;
-    map.m[1] = wk->m;
-    map.m[2] = wv->m;
-    map.wt[0] = map.wt[1] = WT_Q4K;
-    map.wt[2] = wv->m.type == TFR_Q6_K ? WT_Q6K_F32 : WT_Q4K;
-    map.start[0] = 0;
-    map.start[1] = nq;
-    map.start[2] = nq + nkv;
-    map.start[3] = map.start[4] = tot;
-    map.count = 3;
+    pa.wt = WT_Q4K;
+    const int C = sm_count_cached();
+    MapQK map{};
+    map.q = wq->m;
+    map.k = wk->m;
+    map.shq = make_share(nq / 2, C);
+    map.shk = make_share(nkv / 2, C);
+    F32Seg fseg{};
+    fseg.m = wv->m;
+    fseg.sh = make_share(nkv / 2, C);
+    fseg.id_base = (nq + nkv) / 2;
     EpiQkv epi{};
     epi.q_out = q_out;
     epi.kc = kc;
@@ -882,7 +914,7 @@ extern "C" int tfr_op_qkv_rope_store(const tfr_mat* wq, const tfr_mat* wk, const
     epi.kvdim = nkv;
     epi.theta = theta;
     epi.pos = pos;
-    return check(launch_gemv(s, sm_count_cached() * 4, pa, map, epi, wq->m.K, tot / 2, nullptr));
+    return check(launch_gemv(s, C, pa, map, fseg, epi, wq->m.K, nullptr));
 }
 
 // ------------------------------------------------------------------ synthetic quantiser

@@ -21,12 +21,14 @@
 //         (kernels/gemv.cu:71-130).  Q6_K: sum (q6-32)*q8 over each 16-element scale group
 //         (kernels/gemv.cu:302-337).  Float combination order is not part of the contract.
 #pragma once
+#include <cuda_fp16.h>
+
 #include "tfr_common.cuh"
 
 namespace tfr {
 
-constexpr int GEMV_THREADS = 256;  // also the reduction shape of the reference RMSNorm
-constexpr int GEMV_UNROLL = 2;     // units in flight per thread per pass
+constexpr int GEMV_THREADS = 1024;  // one CTA per SM; every thread keeps GEMV_UNROLL units in flight
+constexpr int GEMV_UNROLL = 2;      // units (16-byte weight loads x3) in flight per thread per tile
 constexpr int GEMV_PT_MIN = GEMV_THREADS * GEMV_UNROLL;
 
 enum { WT_Q4K = 0, WT_Q6K = 1, WT_Q6K_F32 = 2 };
@@ -50,19 +52,28 @@ struct Act {
     int4* q8;    // K/16 chunks of 16 int8, swizzled so that consecutive units hit consecutive banks
     float* d8;   // K/32 scales
     int* ss;     // K/32 packed sums: low 16 bits = sum of the first 16 q8 of the group, high = last 16
-    float* xf;   // K fp32 values (normalised input) when a fp32-activation row type needs them
+    float* xf;   // the staged fp32 vector (normalised in place), padded layout, see xs_idx()
+    float* wf;   // staged RMSNorm weights, same layout (only when a norm is fused)
 };
 
-__host__ __device__ inline size_t act_smem_bytes(int K, bool want_xf) {
-    return (size_t)K + (size_t)(K / 32) * 8 + (want_xf ? (size_t)K * 4 : 0);
+// The fp32 vector is staged with 4 floats of padding after every 32, so that the thread that
+// quantises group g can read its 32 values as float4 without shared-memory bank conflicts.
+__host__ __device__ __forceinline__ int xs_idx(int i) { return i + ((i >> 5) << 2); }
+__host__ __device__ inline size_t xs_floats(int K) { return (size_t)K + (size_t)(K / 32) * 4; }
+
+// Shared-memory bytes of an Act.
+__host__ __device__ inline size_t act_smem_bytes(int K, bool with_xf, bool with_wf) {
+    return (size_t)K + (size_t)(K / 32) * 8 + (with_xf ? xs_floats(K) * 4 : 0) + (with_wf ? xs_floats(K) * 4 : 0);
 }
 
-__device__ __forceinline__ Act act_carve(unsigned char* smem, int K, bool want_xf) {
+__device__ __forceinline__ Act act_carve(unsigned char* smem, int K, bool with_xf, bool with_wf) {
     Act a;
     a.q8 = reinterpret_cast<int4*>(smem);
     a.d8 = reinterpret_cast<float*>(smem + K);
     a.ss = reinterpret_cast<int*>(smem + K + (K / 32) * 4);
-    a.xf = want_xf ? reinterpret_cast<float*>(smem + K + (K / 32) * 8) : nullptr;
+    unsigned char* p = smem + K + (K / 32) * 8;
+    a.xf = with_xf ? reinterpret_cast<float*>(p) : nullptr;
+    a.wf = with_wf ? reinterpret_cast<float*>(p + xs_floats(K) * 4) : nullptr;
     return a;
 }
 
@@ -73,11 +84,6 @@ __device__ __forceinline__ int swz_pos(int c, int G, int mode) {
 }
 
 // ------------------------------------------------------------------ activation sources
-
-struct SrcVec {
-    const float* v;
-    __device__ __forceinline__ float get(int i) const { return v[i]; }
-};
 
 // Row `token` of the embedding table, decoded element by element
 // (kernels/embed.cu:71-131: x = dequant(row), no scaling).
@@ -117,89 +123,146 @@ struct SrcEmbed {
     }
 };
 
-// RMSNorm scale with the reduction shape of kernels/ops.cu:4-34 (256 strided partial sums,
-// then a binary tree), so that the normalised vector — and with it the int8 activation —
-// is bit-identical to the reference's for the same input.  Must be called by all 256 threads.
-template <class Src>
-__device__ float rms_scale_256(const Src& src, int n, float eps, float* red /* 256 floats */) {
-    const int tid = threadIdx.x;
-    float local = 0.f;
-    for (int i = tid; i < n; i += GEMV_THREADS) {
-        float v = src.get(i);
-        local += v * v;
+// RMSNorm scale over the vector staged in shared memory, with the reduction shape of
+// kernels/ops.cu:4-34: 256 strided partial sums, then the binary tree red[t] += red[t + s]
+// for s = 128 .. 1.  One warp replays that tree in registers (lane l holds red[l + 32k]),
+// pairing exactly the operands the reference pairs, so the normalised vector — and with it
+// the int8 activation — is bit-identical to the reference build's for the same input.
+// Called by all threads of the CTA; red: 257 floats of shared memory.
+__device__ float rms_scale_staged(const float* xs, int n, float eps, float* red) {
+    const int tid = threadIdx.x, lane = tid & 31;
+    if (tid < 256) {
+        float local = 0.f;
+        for (int i = tid; i < n; i += 256) {
+            const float v = xs[xs_idx(i)];
+            local += v * v;
+        }
+        red[tid] = local;
     }
-    red[tid] = local;
     __syncthreads();
-    for (int s = GEMV_THREADS / 2; s > 0; s >>= 1) {
-        if (tid < s) red[tid] += red[tid + s];
-        __syncthreads();
+    if (tid < 32) {
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) v[k] = red[lane + 32 * k];
+#pragma unroll
+        for (int k = 0; k < 4; k++) v[k] += v[k + 4];  // s = 128
+        v[0] += v[2];                                  // s = 64
+        v[1] += v[3];
+        v[0] += v[1];                                  // s = 32
+        float t = v[0];
+#pragma unroll
+        for (int sft = 16; sft > 0; sft >>= 1) t += __shfl_down_sync(TFR_FULL_MASK, t, sft);
+        if (lane == 0) red[256] = rsqrtf(t / (float)n + eps);
     }
-    float scale = rsqrtf(red[0] / (float)n + eps);
     __syncthreads();
-    return scale;
+    return red[256];
 }
 
-// Q8 activation quantiser, kernels/gemv.cu:16-65: per 32 values d = amax * (1/127),
-// q = rn(x / d) with the build's approximate division, zero group -> zeros.  Additionally
-// records per-half-group sums of q (pure integer, derived from q).
-template <class Src>
-__device__ void act_prepare(Act& act, const Src& src, const float* __restrict__ normw, float eps, int K, int swz,
-                            float* __restrict__ raw_out, float* red) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+// Q8 activation quantiser over the staged vector, kernels/gemv.cu:16-65: per 32 values
+// d = amax * (1/127), q = rn(x / d) with the build's approximate division, zero group ->
+// zeros.  One THREAD per 32-value group (the reference uses a warp per group; max and the
+// per-element rounding do not depend on that).  With a fused RMSNorm the normalised value
+// x * scale * w is formed in the reference's order and written back for fp32-route rows.
+// Also records per-half-group sums of q (pure integer, derived from q).
+__device__ void act_quantize_staged(Act& act, bool has_norm, float scale, int K, int swz) {
+    const int g = threadIdx.x;
+    if (g >= (K >> 5)) return;
     const int G = K >> 6;
-    float scale = 1.f;
-    if (normw) scale = rms_scale_256(src, K, eps, red);
-    signed char* q8b = reinterpret_cast<signed char*>(act.q8);
-    for (int g = warp; g < (K >> 5); g += GEMV_THREADS / 32) {
-        const int i = (g << 5) + lane;
-        float raw = src.get(i);
-        if (raw_out) raw_out[i] = raw;
-        float xi = normw ? raw * scale * normw[i] : raw;
-        if (act.xf) act.xf[i] = xi;
-        float amax = warp_max(fabsf(xi));
-        const float d = amax * (1.0f / 127.0f);
-        int q = amax == 0.f ? 0 : (int)(signed char)__float2int_rn(xi / d);
-        const int c = i >> 4;
-        q8b[swz_pos(c, G, swz) * 16 + (i & 15)] = (signed char)q;
-        int s = q;
-        s += __shfl_xor_sync(TFR_FULL_MASK, s, 8);
-        s += __shfl_xor_sync(TFR_FULL_MASK, s, 4);
-        s += __shfl_xor_sync(TFR_FULL_MASK, s, 2);
-        s += __shfl_xor_sync(TFR_FULL_MASK, s, 1);
-        int hi = __shfl_sync(TFR_FULL_MASK, s, 16);
-        if (lane == 0) {
-            act.d8[g] = d;
-            act.ss[g] = (s & 0xffff) | (hi << 16);
+    float4* xg = reinterpret_cast<float4*>(act.xf + 36 * g);
+    const float4* wg = reinterpret_cast<const float4*>(act.wf + 36 * g);
+    float amax = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        float4 x = xg[k];
+        if (has_norm) {
+            const float4 w = wg[k];
+            x.x = x.x * scale * w.x;
+            x.y = x.y * scale * w.y;
+            x.z = x.z * scale * w.z;
+            x.w = x.w * scale * w.w;
+            xg[k] = x;
         }
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))));
     }
-    __syncthreads();
+    const float d = amax * (1.0f / 127.0f);
+    int wd[8];
+    int s_lo = 0, s_hi = 0;
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        const float4 x = xg[k];
+        int q0 = 0, q1 = 0, q2 = 0, q3 = 0;
+        if (amax != 0.f) {
+            q0 = (int)(signed char)__float2int_rn(x.x / d);
+            q1 = (int)(signed char)__float2int_rn(x.y / d);
+            q2 = (int)(signed char)__float2int_rn(x.z / d);
+            q3 = (int)(signed char)__float2int_rn(x.w / d);
+        }
+        wd[k] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | ((q3 & 0xff) << 24);
+        if (k < 4) s_lo += q0 + q1 + q2 + q3;
+        else s_hi += q0 + q1 + q2 + q3;
+    }
+    act.q8[swz_pos(2 * g, G, swz)] = make_int4(wd[0], wd[1], wd[2], wd[3]);
+    act.q8[swz_pos(2 * g + 1, G, swz)] = make_int4(wd[4], wd[5], wd[6], wd[7]);
+    act.d8[g] = d;
+    act.ss[g] = (s_lo & 0xffff) | (s_hi << 16);
 }
 
 // ------------------------------------------------------------------ unit loads / dots
 
+// Weight bytes of one unit.  Q4_K: a, b = 32 B of nibbles, c = block header.  Q6_K: a, b = ql
+// pieces, c = qh piece, s = 8 scale bytes of the half block, dbits = fp16 d.
 struct UnitW {
     int4 a, b, c;
     int2 s;
     unsigned int dbits;
 };
 
-__device__ __forceinline__ void load_unit(UnitW& w, int wt, const uint8_t* row, int nb, int u) {
+// Byte offsets of a thread's unit inside a row; a thread keeps the same unit column for the
+// whole kernel, so these are computed once.
+struct UnitOff {
+    int q4_hdr, q4_qs;              // Q4_K
+    int q6_ql, q6_qh, q6_sc, q6_d;  // Q6_K
+};
+
+__device__ __forceinline__ UnitOff unit_offsets(int u, int nb) {
+    UnitOff o;
+    o.q4_hdr = (u >> 2) * 144;
+    o.q4_qs = o.q4_hdr + 16 + 32 * (u & 3);
+    const int b = u >> 2, n = (u >> 1) & 1, is = u & 1;
+    o.q6_ql = b * 128 + 64 * n + 16 * is;
+    o.q6_qh = nb * 128 + b * 64 + 32 * n + 16 * is;
+    o.q6_sc = nb * 192 + b * 16 + 8 * n;
+    o.q6_d = nb * 208 + 2 * b;
+    return o;
+}
+
+__device__ __forceinline__ void load_unit(UnitW& w, int wt, const uint8_t* row, const UnitOff& o) {
     if (wt == WT_Q4K) {
-        const uint8_t* blk = row + (u >> 2) * 144;
-        w.c = ldg_stream(blk);
-        w.a = ldg_stream(blk + 16 + 32 * (u & 3));
-        w.b = ldg_stream(blk + 32 + 32 * (u & 3));
+        w.c = ldg_stream(row + o.q4_hdr);
+        w.a = ldg_stream(row + o.q4_qs);
+        w.b = ldg_stream(row + o.q4_qs + 16);
     } else {
-        const int b = u >> 2, n = (u >> 1) & 1, is = u & 1;
-        const uint8_t* ql = row + b * 128 + 64 * n + 16 * is;
-        w.a = ldg_stream(ql);
-        w.b = ldg_stream(ql + 32);
-        w.c = ldg_stream(row + nb * 128 + b * 64 + 32 * n + 16 * is);
-        w.s = ldg_stream8(row + nb * 192 + b * 16 + 8 * n);
-        w.dbits = __ldg(reinterpret_cast<const unsigned short*>(row + nb * 208 + 2 * b));
+        w.a = ldg_stream(row + o.q6_ql);
+        w.b = ldg_stream(row + o.q6_ql + 32);
+        w.c = ldg_stream(row + o.q6_qh);
+        w.s = ldg_stream8(row + o.q6_sc);
+        w.dbits = __ldg(reinterpret_cast<const unsigned short*>(row + o.q6_d));
     }
 }
 
+// u8 x s8 dot product with 32-bit accumulate (bytes of a are unsigned, bytes of b signed).
+__device__ __forceinline__ int dp4a_us(unsigned int a, int b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dot16_us(const int4& w, unsigned int mask, const int4& a) {
+    int acc = dp4a_us((unsigned)w.x & mask, a.x, 0);
+    acc = dp4a_us((unsigned)w.y & mask, a.y, acc);
+    acc = dp4a_us((unsigned)w.z & mask, a.z, acc);
+    acc = dp4a_us((unsigned)w.w & mask, a.w, acc);
+    return acc;
+}
 __device__ __forceinline__ int dot16(const int4& w, const int4& a, int acc) {
     acc = __dp4a(w.x, a.x, acc);
     acc = __dp4a(w.y, a.y, acc);
@@ -207,29 +270,58 @@ __device__ __forceinline__ int dot16(const int4& w, const int4& a, int acc) {
     acc = __dp4a(w.w, a.w, acc);
     return acc;
 }
-__device__ __forceinline__ int4 and4(const int4& v, int m) { return make_int4(v.x & m, v.y & m, v.z & m, v.w & m); }
-__device__ __forceinline__ int4 shr4(const int4& v, int s) {
-    return make_int4((int)((unsigned)v.x >> s), (int)((unsigned)v.y >> s), (int)((unsigned)v.z >> s),
-                     (int)((unsigned)v.w >> s));
-}
 
-// Integer sub-block results of one Q4_K unit (sub-blocks 2t and 2t+1 of its super-block).
-struct Q4Ints {
-    int I0, I1, S0, S1, sc0, sc1, m0, m1;
+// Exact int -> float for |i| < 2^22 on the FP32 pipe (the conversion instruction runs at a
+// quarter of the rate).  All integers converted here are below 2^22 in magnitude:
+// |I * sc| <= 15*127*32*63 < 2^22, |J| <= 32*127*16 < 2^17.
+__device__ __forceinline__ float i2f_small(int i) { return __int_as_float(0x4B400000 + i) - 12582912.0f; }
+
+// The activation pieces one unit needs, read from shared memory once per pass.
+struct Frag {
+    int4 a0, a1, a2, a3;  // the unit's 64 int8 activations, in the order its weight pieces use them
+    float4 d8;            // Q4_K: (d8 of sub-block 2t, 2t+1, -, -).  Q6_K: d8 of the four runs' groups
+    int4 aux;             // Q4_K: float bits of d8*S of the two sub-blocks.  Q6_K: -32*S16 of the four runs,
+                          // used as the dp4a accumulator start so that sum (q6-32)*q8 stays an exact integer
 };
 
-__device__ __forceinline__ Q4Ints q4k_unit_ints(const UnitW& w, const Act& act, int u, int G) {
-    Q4Ints r;
-    const int4 a0 = act.q8[u], a1 = act.q8[G + u], a2 = act.q8[2 * G + u], a3 = act.q8[3 * G + u];
-    r.I0 = dot16(and4(w.a, 0x0f0f0f0f), a0, 0);
-    r.I0 = dot16(and4(w.b, 0x0f0f0f0f), a1, r.I0);
-    r.I1 = dot16(and4(shr4(w.a, 4), 0x0f0f0f0f), a2, 0);
-    r.I1 = dot16(and4(shr4(w.b, 4), 0x0f0f0f0f), a3, r.I1);
-    const int2 ss = reinterpret_cast<const int2*>(act.ss)[u];
-    r.S0 = (int)(short)(ss.x & 0xffff) + (ss.x >> 16);
-    r.S1 = (int)(short)(ss.y & 0xffff) + (ss.y >> 16);
+__device__ __forceinline__ void frag_load(Frag& f, int wt, const Act& act, int u, int G) {
+    f.a0 = act.q8[u];
+    f.a1 = act.q8[G + u];
+    f.a2 = act.q8[2 * G + u];
+    f.a3 = act.q8[3 * G + u];
+    if (wt == WT_Q4K) {
+        const float2 d = reinterpret_cast<const float2*>(act.d8)[u];
+        const int2 ss = reinterpret_cast<const int2*>(act.ss)[u];
+        const int S0 = (int)(short)(ss.x & 0xffff) + (ss.x >> 16);
+        const int S1 = (int)(short)(ss.y & 0xffff) + (ss.y >> 16);
+        f.d8 = make_float4(d.x, d.y, 0.f, 0.f);
+        f.aux = make_int4(__float_as_int(d.x * i2f_small(S0)), __float_as_int(d.y * i2f_small(S1)), 0, 0);
+    } else {
+        f.d8 = reinterpret_cast<const float4*>(act.d8)[u >> 1];
+        const int4 ss = reinterpret_cast<const int4*>(act.ss)[u >> 1];
+        const int is = u & 1;
+#define TFR_S16(v) (is ? ((v) >> 16) : (int)(short)((v) & 0xffff))
+        f.aux = make_int4(-32 * TFR_S16(ss.x), -32 * TFR_S16(ss.y), -32 * TFR_S16(ss.z), -32 * TFR_S16(ss.w));
+#undef TFR_S16
+    }
+}
+
+// Q4_K unit (sub-blocks 2t and 2t+1 of its super-block, t = u & 3) against the fragment.
+// ints (optional): I0, I1 = sum nibble*q8 of the two sub-blocks — the bit-exact contract of
+// kernels/gemv.cu:71-130; the sums S are the fragment's.  High nibbles are multiplied as
+// (nibble << 4) and the exact factor 16 is shifted out afterwards.
+__device__ __forceinline__ float q4k_dot(const UnitW& w, const Frag& f, int t, int* ints) {
+    int I0 = dot16_us(w.a, 0x0f0f0f0fu, f.a0);
+    I0 += dot16_us(w.b, 0x0f0f0f0fu, f.a1);
+    int I1 = dot16_us(w.a, 0xf0f0f0f0u, f.a2);
+    I1 += dot16_us(w.b, 0xf0f0f0f0u, f.a3);
+    I1 >>= 4;
+    if (ints) {
+        ints[0] = I0;
+        ints[1] = I1;
+    }
     // 6-bit scales / mins, kernels/common.cu:40-50 in the 16-bit form of gemv.cu:94-106.
-    const int t = u & 3, sh = 16 * (t & 1);
+    const int sh = 16 * (t & 1);
     const unsigned y16 = ((unsigned)w.c.y >> sh) & 0xffffu, z16 = ((unsigned)w.c.z >> sh) & 0xffffu,
                    w16 = ((unsigned)w.c.w >> sh) & 0xffffu;
     unsigned aux_sc, aux_m;
@@ -240,204 +332,151 @@ __device__ __forceinline__ Q4Ints q4k_unit_ints(const UnitW& w, const Act& act, 
         aux_sc = (w16 & 0x0f0fu) | ((y16 & 0xc0c0u) >> 2);
         aux_m = ((w16 >> 4) & 0x0f0fu) | ((z16 & 0xc0c0u) >> 2);
     }
-    r.sc0 = aux_sc & 0xff;
-    r.sc1 = aux_sc >> 8;
-    r.m0 = aux_m & 0xff;
-    r.m1 = aux_m >> 8;
-    return r;
+    const int sc0 = aux_sc & 0xff, sc1 = aux_sc >> 8, m0 = aux_m & 0xff, m1 = aux_m >> 8;
+    const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&w.c.x));  // (d, dmin)
+    return dd.x * (f.d8.x * i2f_small(I0 * sc0) + f.d8.y * i2f_small(I1 * sc1)) -
+           dd.y * (__int_as_float(f.aux.x) * i2f_small(m0) + __int_as_float(f.aux.y) * i2f_small(m1));
 }
 
-__device__ __forceinline__ float q4k_unit_dot(const UnitW& w, const Act& act, int u, int G) {
-    const Q4Ints r = q4k_unit_ints(w, act, u, G);
-    const float d = f16_to_f32((unsigned short)(w.c.x & 0xffff));
-    const float dmin = f16_to_f32((unsigned short)((unsigned)w.c.x >> 16));
-    const float2 d8 = reinterpret_cast<const float2*>(act.d8)[u];
-    return d * (d8.x * (float)(r.I0 * r.sc0) + d8.y * (float)(r.I1 * r.sc1)) -
-           dmin * (d8.x * (float)(r.S0 * r.m0) + d8.y * (float)(r.S1 * r.m1));
-}
-
-// The four 16-element scale-group dots sum (q6-32)*q8 of one Q6_K unit: runs j = 0..3 are
-// elements 128n + 32j + 16is + [0,16) of block b, where u = 4b + 2n + is.
-__device__ __forceinline__ void q6k_unit_ints(const UnitW& w, const Act& act, int u, int G, int J[4]) {
-    const int4 a0 = act.q8[u], a1 = act.q8[G + u], a2 = act.q8[2 * G + u], a3 = act.q8[3 * G + u];
+// Q6_K unit: runs j = 0..3 are elements 128n + 32j + 16is + [0,16) of block b (u = 4b+2n+is).
+// ints (optional): the four scale-group dots sum (q6-32)*q8 of kernels/gemv.cu:302-337.
+__device__ __forceinline__ float q6k_dot(const UnitW& w, const Frag& f, int is, int* ints) {
     const int4 h = w.c;
     int4 r0, r1, r2, r3;
-#define TFR_Q6W(f)                                                          \
-    r0.f = (w.a.f & 0x0f0f0f0f) | ((h.f << 4) & 0x30303030);                \
-    r1.f = (w.b.f & 0x0f0f0f0f) | ((h.f << 2) & 0x30303030);                \
-    r2.f = (((unsigned)w.a.f >> 4) & 0x0f0f0f0f) | (h.f & 0x30303030);      \
-    r3.f = (((unsigned)w.b.f >> 4) & 0x0f0f0f0f) | (((unsigned)h.f >> 2) & 0x30303030);
+#define TFR_Q6W(c)                                                          \
+    r0.c = (w.a.c & 0x0f0f0f0f) | ((h.c << 4) & 0x30303030);                \
+    r1.c = (w.b.c & 0x0f0f0f0f) | ((h.c << 2) & 0x30303030);                \
+    r2.c = (((unsigned)w.a.c >> 4) & 0x0f0f0f0f) | (h.c & 0x30303030);      \
+    r3.c = (((unsigned)w.b.c >> 4) & 0x0f0f0f0f) | (((unsigned)h.c >> 2) & 0x30303030);
     TFR_Q6W(x) TFR_Q6W(y) TFR_Q6W(z) TFR_Q6W(w)
 #undef TFR_Q6W
-    const int4 ss = reinterpret_cast<const int4*>(act.ss)[u >> 1];
-    const int is = u & 1;
-#define TFR_S16(v) (is ? ((v) >> 16) : (int)(short)((v) & 0xffff))
-    J[0] = dot16(r0, a0, 0) - 32 * TFR_S16(ss.x);
-    J[1] = dot16(r1, a1, 0) - 32 * TFR_S16(ss.y);
-    J[2] = dot16(r2, a2, 0) - 32 * TFR_S16(ss.z);
-    J[3] = dot16(r3, a3, 0) - 32 * TFR_S16(ss.w);
-#undef TFR_S16
-}
-
-__device__ __forceinline__ void q6k_unit_scales(const UnitW& w, int u, float sc[4]) {
-    const int is = u & 1;
+    const int J0 = dot16(r0, f.a0, f.aux.x), J1 = dot16(r1, f.a1, f.aux.y), J2 = dot16(r2, f.a2, f.aux.z),
+              J3 = dot16(r3, f.a3, f.aux.w);
     const unsigned lo = (unsigned)w.s.x >> (8 * is), hi = (unsigned)w.s.y >> (8 * is);
-    sc[0] = (float)(int)(signed char)(lo & 0xff);
-    sc[1] = (float)(int)(signed char)((lo >> 16) & 0xff);
-    sc[2] = (float)(int)(signed char)(hi & 0xff);
-    sc[3] = (float)(int)(signed char)((hi >> 16) & 0xff);
-}
-
-__device__ __forceinline__ float q6k_unit_dot(const UnitW& w, const Act& act, int u, int G) {
-    int J[4];
-    float sc[4];
-    q6k_unit_ints(w, act, u, G, J);
-    q6k_unit_scales(w, u, sc);
+    const float s0 = i2f_small((int)(signed char)(lo & 0xff)), s1 = i2f_small((int)(signed char)((lo >> 16) & 0xff));
+    const float s2 = i2f_small((int)(signed char)(hi & 0xff)), s3 = i2f_small((int)(signed char)((hi >> 16) & 0xff));
+    if (ints) {
+        ints[0] = J0;
+        ints[1] = J1;
+        ints[2] = J2;
+        ints[3] = J3;
+    }
     const float d = f16_to_f32((unsigned short)w.dbits);
-    const float4 d8 = reinterpret_cast<const float4*>(act.d8)[u >> 1];
-    return d * (sc[0] * d8.x * (float)J[0] + sc[1] * d8.y * (float)J[1] + sc[2] * d8.z * (float)J[2] +
-                sc[3] * d8.w * (float)J[3]);
+    return d * (s0 * f.d8.x * i2f_small(J0) + s1 * f.d8.y * i2f_small(J1) + s2 * f.d8.z * i2f_small(J2) +
+                s3 * f.d8.w * i2f_small(J3));
 }
 
-// Q6_K unit against the fp32 activation (the reference's route for a Q6_K attn_v,
-// kernels/gemv.cu:233-264: acc += d * scale * q * x with x unquantised).
-__device__ __forceinline__ float q6k_unit_dot_f32(const UnitW& w, const Act& act, int u) {
+// One run of 16 elements of a Q6_K row against the fp32 activation staged in shared memory
+// (the reference's route for a Q6_K attn_v, kernels/gemv.cu:233-264: acc += d * scale * q * x
+// with x unquantised).  u = 4b + 2n + is names the unit, j the run: elements
+// 256b + 128n + 32j + 16is + [0, 16).  Reads the SoA row layout directly.
+__device__ __forceinline__ float q6k_run_dot_f32(const uint8_t* row, int nb, int u, int j, const float* xf) {
     const int b = u >> 2, n = (u >> 1) & 1, is = u & 1;
-    const float* x = act.xf + 256 * b + 128 * n + 16 * is;
-    float sc[4];
-    q6k_unit_scales(w, u, sc);
-    const float d = f16_to_f32((unsigned short)w.dbits);
+    const int4 ql = __ldg(reinterpret_cast<const int4*>(row + b * 128 + 64 * n + 32 * (j & 1) + 16 * is));
+    const int4 qh = __ldg(reinterpret_cast<const int4*>(row + nb * 128 + b * 64 + 32 * n + 16 * is));
+    const float sc = (float)(int)*reinterpret_cast<const signed char*>(row + nb * 192 + b * 16 + 8 * n + is + 2 * j);
+    const float d = f16_to_f32(__ldg(reinterpret_cast<const unsigned short*>(row + nb * 208 + 2 * b)));
+    const float dsc = d * sc;
+    const float4* x4 = reinterpret_cast<const float4*>(xf + xs_idx(256 * b + 128 * n + 32 * j + 16 * is));
+    const int qlw[4] = {ql.x, ql.y, ql.z, ql.w};
+    const int qhw[4] = {qh.x, qh.y, qh.z, qh.w};
+    const int nsh = 4 * (j >> 1), hsh = 2 * j;
     float acc = 0.f;
-    const int qa[4] = {w.a.x, w.a.y, w.a.z, w.a.w};
-    const int qb[4] = {w.b.x, w.b.y, w.b.z, w.b.w};
-    const int qh[4] = {w.c.x, w.c.y, w.c.z, w.c.w};
 #pragma unroll
     for (int k = 0; k < 4; k++) {
+        const float4 x = x4[k];
+        const float xv[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
         for (int by = 0; by < 4; by++) {
-            const int a = (qa[k] >> (8 * by)) & 0xff, bb = (qb[k] >> (8 * by)) & 0xff, hh = (qh[k] >> (8 * by)) & 0xff;
-            const int e = 4 * k + by;
-            const int q0 = ((a & 0xF) | ((hh & 3) << 4)) - 32;
-            const int q1 = ((bb & 0xF) | (((hh >> 2) & 3) << 4)) - 32;
-            const int q2 = ((a >> 4) | (((hh >> 4) & 3) << 4)) - 32;
-            const int q3 = ((bb >> 4) | (((hh >> 6) & 3) << 4)) - 32;
-            acc += d * sc[0] * (float)q0 * x[e];
-            acc += d * sc[1] * (float)q1 * x[32 + e];
-            acc += d * sc[2] * (float)q2 * x[64 + e];
-            acc += d * sc[3] * (float)q3 * x[96 + e];
+            const int nib = (qlw[k] >> (8 * by + nsh)) & 0xF;
+            const int hb = (qhw[k] >> (8 * by + hsh)) & 3;
+            acc += dsc * (float)((nib | (hb << 4)) - 32) * xv[by];
         }
     }
     return acc;
 }
 
-__device__ __forceinline__ float unit_dot(const UnitW& w, int wt, const Act& act, int u, int G) {
-    if (wt == WT_Q4K) return q4k_unit_dot(w, act, u, G);
-    if (wt == WT_Q6K) return q6k_unit_dot(w, act, u, G);
-    return q6k_unit_dot_f32(w, act, u);
+// ------------------------------------------------------------------ row-pair maps
+
+// All kernels walk "row pairs": two rows whose results go to the epilogue together.
+// pair p of a plain matrix = rows (2p, 2p+1); of the gate/up map = (gate row p, up row p).
+struct PairRows {
+    const uint8_t* r0;
+    const uint8_t* r1;
+    int id;  // pair id handed to the epilogue
+};
+
+// Contiguous share of n items for CTA c of C, with n = C*quot + rem split on the host so that
+// the kernel needs no division: the first `rem` CTAs take quot+1 items.
+struct Share {
+    int quot, rem;
+    __device__ __forceinline__ int begin(int c) const { return c * quot + min(c, rem); }
+    __device__ __forceinline__ int count(int c) const { return quot + (c < rem ? 1 : 0); }
+};
+inline Share make_share(int n, int C) {
+    Share s;
+    s.quot = n / C;
+    s.rem = n % C;
+    return s;
 }
 
-// ------------------------------------------------------------------ row maps
-
-// vrow -> (row pointer, weight type).  "Virtual rows" let one kernel walk several matrices.
 struct MapSingle {
     Mat m;
-    int wt;
-    __device__ __forceinline__ const uint8_t* row(int v, int& t) const {
-        t = wt;
-        return m.data + (long long)v * m.row_stride;
+    Share sh;
+    __device__ __forceinline__ int n_local(int c) const { return sh.count(c); }
+    __device__ __forceinline__ PairRows pair(int c, int i) const {
+        const int p = sh.begin(c) + i;
+        PairRows r;
+        r.r0 = m.data + (long long)(2 * p) * m.row_stride;
+        r.r1 = (2 * p + 1 < m.N) ? r.r0 + m.row_stride : r.r0;  // odd N: the last pair repeats its row
+        r.id = p;
+        return r;
     }
     __device__ __forceinline__ int nb() const { return m.nb; }
 };
-// Two matrices interleaved row by row: vrow 2j -> a[j], 2j+1 -> b[j] (gate / up).
 struct MapPair {
     Mat a, b;
-    __device__ __forceinline__ const uint8_t* row(int v, int& t) const {
-        t = WT_Q4K;
-        const Mat& m = (v & 1) ? b : a;
-        return m.data + (long long)(v >> 1) * m.row_stride;
+    Share sh;
+    __device__ __forceinline__ int n_local(int c) const { return sh.count(c); }
+    __device__ __forceinline__ PairRows pair(int c, int i) const {
+        const int p = sh.begin(c) + i;
+        PairRows r;
+        r.r0 = a.data + (long long)p * a.row_stride;
+        r.r1 = b.data + (long long)p * b.row_stride;
+        r.id = p;
+        return r;
     }
     __device__ __forceinline__ int nb() const { return a.nb; }
 };
-// Up to four matrices stacked: vrows [0,n0) -> m[0], [n0, n0+n1) -> m[1], ...
-struct MapStack {
-    Mat m[4];
-    int wt[4];
-    int start[5];
-    int count;
-    __device__ __forceinline__ const uint8_t* row(int v, int& t) const {
-        int s = 0;
-#pragma unroll
-        for (int i = 1; i < 4; i++)
-            if (i < count && v >= start[i]) s = i;
-        t = wt[s];
-        return m[s].data + (long long)(v - start[s]) * m[s].row_stride;
+// Q and K stacked, each spread over all CTAs: a CTA's local list is its Q pairs, then its K
+// pairs.  Pair ids continue across the matrices (Q pairs first, then K, then V).
+struct MapQK {
+    Mat q, k;
+    Share shq, shk;
+    __device__ __forceinline__ int n_local(int c) const { return shq.count(c) + shk.count(c); }
+    __device__ __forceinline__ PairRows pair(int c, int i) const {
+        const int nq = shq.count(c);
+        const bool isk = i >= nq;
+        const Mat& m = isk ? k : q;
+        const int p = isk ? shk.begin(c) + (i - nq) : shq.begin(c) + i;
+        PairRows r;
+        r.r0 = m.data + (long long)(2 * p) * m.row_stride;
+        r.r1 = r.r0 + m.row_stride;
+        r.id = isk ? (q.N >> 1) + p : p;
+        return r;
     }
-    __device__ __forceinline__ int nb() const { return m[0].nb; }
+    __device__ __forceinline__ int nb() const { return q.nb; }
 };
 
-// ------------------------------------------------------------------ tile walker
-
-__host__ __device__ inline int gemv_partial_floats(int K, int row_align) {
-    int G = K / 64;
-    int need = row_align * G;
-    return need > GEMV_PT_MIN ? need : GEMV_PT_MIN;
-}
-
-// Walks row groups [grp0, grp1) (a group = Epi::ROW_ALIGN consecutive vrows reduced by one
-// warp and handed to the epilogue together).  pbuf: 2 * PT floats of shared memory.
-template <class Map, class Epi>
-__device__ void gemv_tiles(const Map& map, Epi& epi, const Act& act, int K, int grp0, int grp1, float* pbuf, int PT) {
-    constexpr int RA = Epi::ROW_ALIGN;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int G = K >> 6, nb = map.nb();
-    const unsigned magic = 0xffffffffu / (unsigned)G + 1u;  // exact f / G for f*G < 2^32
-    int rows_per_tile = GEMV_PT_MIN / G;
-    rows_per_tile -= rows_per_tile % RA;
-    if (rows_per_tile < RA) rows_per_tile = RA;
-    const int v0 = grp0 * RA, v1 = grp1 * RA;
-    int buf = 0;
-    for (int tv = v0; tv < v1; tv += rows_per_tile, buf ^= 1) {
-        const int rows = min(rows_per_tile, v1 - tv);
-        const int n = rows * G;
-        float* part = pbuf + buf * PT;
-        for (int base = 0; base < n; base += GEMV_THREADS * GEMV_UNROLL) {
-            UnitW w[GEMV_UNROLL];
-            int uu[GEMV_UNROLL], wt[GEMV_UNROLL];
-#pragma unroll
-            for (int k = 0; k < GEMV_UNROLL; k++) {
-                const int f = base + tid + k * GEMV_THREADS;
-                if (f < n) {
-                    const int r = (int)__umulhi((unsigned)f, magic);
-                    uu[k] = f - r * G;
-                    const uint8_t* rp = map.row(tv + r, wt[k]);
-                    load_unit(w[k], wt[k], rp, nb, uu[k]);
-                }
-            }
-#pragma unroll
-            for (int k = 0; k < GEMV_UNROLL; k++) {
-                const int f = base + tid + k * GEMV_THREADS;
-                if (f < n) part[f] = unit_dot(w[k], wt[k], act, uu[k], G);
-            }
-        }
-        __syncthreads();
-        for (int g = warp; g * RA < rows; g += GEMV_THREADS / 32) {
-            float s[RA];
-#pragma unroll
-            for (int a = 0; a < RA; a++) {
-                const float* pr = part + (g * RA + a) * G;
-                float acc = 0.f;
-                for (int i = lane; i < G; i += 32) acc += pr[i];
-                s[a] = warp_sum(acc);
-            }
-            epi.apply(tv + g * RA, s, lane);
-        }
-    }
-}
-
-// Contiguous share of `groups` row groups for CTA c of C.
-__device__ __forceinline__ void cta_share(int groups, int c, int C, int& g0, int& g1) {
-    g0 = (int)(((long long)groups * c) / C);
-    g1 = (int)(((long long)groups * (c + 1)) / C);
+// Sum of v0 over the warp in lane 0 and of v1 in lane 16, with five shuffles.
+__device__ __forceinline__ float warp_sum_pair(float v0, float v1, int lane) {
+    const bool up = (lane & 16) != 0;
+    float x = (up ? v1 : v0) + __shfl_xor_sync(TFR_FULL_MASK, up ? v0 : v1, 16);
+    x += __shfl_xor_sync(TFR_FULL_MASK, x, 8);
+    x += __shfl_xor_sync(TFR_FULL_MASK, x, 4);
+    x += __shfl_xor_sync(TFR_FULL_MASK, x, 2);
+    x += __shfl_xor_sync(TFR_FULL_MASK, x, 1);
+    return x;
 }
 
 }  // namespace tfr
