@@ -121,6 +121,10 @@ float tfr_last_device_ms(const tfr_engine* e);
  * request switches that tap on for later steps and returns zeros). */
 int tfr_debug_read(tfr_engine* e, tfr_kv* kv, const char* what, int layer, void* out, size_t nbytes);
 
+/* Test aid: when device_buffer != NULL, thread 0 of every CTA of the matrix-vector kernel stores the
+ * GPU nanosecond timer at six points into device_buffer[cta * 8 + point] (needs 8 * n_sm entries). */
+int tfr_debug_set_timeline(unsigned long long* device_buffer);
+
 /* ---- operator level (device pointers unless stated; stream = cudaStream_t or NULL) ---- */
 
 /* GpuMat, crates/core/src/cuda/types.rs:26-39: a weight matrix resident on the device in

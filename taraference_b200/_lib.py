@@ -62,6 +62,7 @@ def lib() -> C.CDLL:
         "tfr_launch_count": (i64, [vp]),
         "tfr_last_device_ms": (f32, [vp]),
         "tfr_debug_read": (i32, [vp, vp, C.c_char_p, i32, vp, sz]),
+        "tfr_debug_set_timeline": (i32, [vp]),
         "tfr_mat_create": (i32, [i32, i64, i64, vp, sz, i32, C.POINTER(vp)]),
         "tfr_mat_free": (None, [vp]),
         "tfr_mat_device_bytes": (i64, [vp]),

@@ -111,16 +111,31 @@ static size_t raw_bytes(int type, int64_t K, int64_t N) {
     return 0;
 }
 
+template <class F>
+static void configure_kernel(F f, bool dynamic) {
+    if (dynamic) cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMV_SMEM_MAX);
+    // one L1/shared split for every kernel of the token loop: a change of carve-out between two
+    // launches drains the SMs
+    cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
 static void configure_kernels_once() {
     static bool done = false;
     if (done) return;
     done = true;
-    const int big = 200 * 1024;
-    cudaFuncSetAttribute(k_gemv<MapQK, EpiQkv>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-    cudaFuncSetAttribute(k_gemv<MapSingle, EpiStore>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-    cudaFuncSetAttribute(k_gemv<MapPair, EpiSilu>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-    cudaFuncSetAttribute(k_gemv<MapSingle, EpiLogits>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-    cudaFuncSetAttribute(k_int_dots, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    configure_kernel(k_gemv<BlockQ4, EpiQkv>, true);
+    configure_kernel(k_gemv<BlockQ4, EpiStore>, true);
+    configure_kernel(k_gemv<BlockQ6, EpiStore>, true);
+    configure_kernel(k_gemv<BlockQ4, EpiSilu>, true);
+    configure_kernel(k_gemv<BlockQ4, EpiLogits>, true);
+    configure_kernel(k_gemv<BlockQ6, EpiLogits>, true);
+    configure_kernel(k_int_dots<BlockQ4>, true);
+    configure_kernel(k_int_dots<BlockQ6>, true);
+    configure_kernel(k_attn_decode<64>, false);
+    configure_kernel(k_attn_decode<128>, false);
+    configure_kernel(k_attn_decode<256>, false);
+    configure_kernel(k_state_begin, false);
+    configure_kernel(k_state_next_prompt, false);
 }
 
 static int sm_count_cached() {
@@ -149,8 +164,7 @@ static int mat_create_impl(tfr_engine* e, int type, int64_t K, int64_t N, const 
     m->m.K = (int)K;
     m->m.N = (int)N;
     m->m.nb = (int)(K / 256);
-    m->m.row_stride = mat_row_stride(type, (int)K);
-    m->bytes = (size_t)m->m.row_stride * (size_t)N;
+    m->bytes = (size_t)mat_device_bytes(type, (int)K, N);
     m->perm_hd = perm_hd;
     void* staging = nullptr;
     cudaError_t r = cudaMalloc(&m->dev, m->bytes);
@@ -158,13 +172,9 @@ static int mat_create_impl(tfr_engine* e, int type, int64_t K, int64_t N, const 
     if (r == cudaSuccess) r = cudaMemcpyAsync(staging, bytes, nbytes, cudaMemcpyDefault, stream);
     if (r == cudaSuccess) {
         const int grid = sm_count_cached() * 8;
-        if (type == TFR_Q4_K)
-            k_repack_q4k<<<grid, 256, 0, stream>>>((const uint8_t*)staging, (uint8_t*)m->dev, (int)N, m->m.nb, perm_hd);
-        else {
-            cudaMemsetAsync(m->dev, 0, m->bytes, stream);
-            k_repack_q6k<<<grid, 256, 0, stream>>>((const uint8_t*)staging, (uint8_t*)m->dev, (int)N, m->m.nb,
-                                                   m->m.row_stride, perm_hd);
-        }
+        const size_t last_tile = (size_t)tile_bytes(type);  // zero the tail tile's unused lanes
+        cudaMemsetAsync((uint8_t*)m->dev + m->bytes - last_tile, 0, last_tile, stream);
+        k_repack_tiled<<<grid, 256, 0, stream>>>((const uint8_t*)staging, (uint8_t*)m->dev, type, (int)N, m->m.nb, perm_hd);
         r = cudaGetLastError();
     }
     if (r == cudaSuccess) r = cudaStreamSynchronize(stream);
@@ -453,7 +463,12 @@ static cudaError_t launch_attention(cudaStream_t s, const AttnArgs& a, int hd, c
     return cudaGetLastError();
 }
 
-static int wt_of(const tfr_mat* m) { return m->m.type == TFR_Q4_K ? WT_Q4K : WT_Q6K; }
+template <class Epi>
+static cudaError_t launch_typed(cudaStream_t s, int grid, int type, const PrepArgs& pa, const RowJob& ja, const RowJob& jb,
+                                const F32Seg& fseg, const Epi& epi, int K, TokenState* st) {
+    if (type == TFR_Q4_K) return launch_gemv<BlockQ4, Epi>(s, grid, pa, ja, jb, fseg, epi, K, st);
+    return launch_gemv<BlockQ6, Epi>(s, grid, pa, ja, jb, fseg, epi, K, st);
+}
 
 // Enqueues the kernels of one decode step; returns the number of launches or a negative error.
 static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
@@ -470,22 +485,13 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
             pa.embed = e->token_embd->m;
             pa.normw = L.attn_norm;
             pa.eps = c.rms_eps;
-            pa.wt = WT_Q4K;
             pa.raw_out = e->x;
-            const bool v_f32 = L.wv->m.type == TFR_Q6_K;
-            MapQK map{};
-            map.q = L.wq->m;
-            map.k = L.wk->m;
-            map.shq = make_share(nq / 2, cap);
-            map.shk = make_share(nkv / 2, cap);
+            if (L.wv->m.type != TFR_Q6_K) return -2;  // a Q4_K attn_v would join the Q8 route; not wired yet
+            const RowJob jq = make_job(L.wq->m, 2, cap, 0), jk = make_job(L.wk->m, 2, cap, nq / 2);
             F32Seg fseg{};
-            if (v_f32) {
-                fseg.m = L.wv->m;
-                fseg.sh = make_share(nkv / 2, cap);
-                fseg.id_base = (nq + nkv) / 2;
-            } else {
-                return -2;  // a Q4_K attn_v would join the Q8 route; not wired yet
-            }
+            fseg.m = L.wv->m;
+            fseg.sh = make_share(nkv / 2, cap);
+            fseg.id_base = (nq + nkv) / 2;
             EpiQkv epi{};
             epi.q_out = e->q;
             epi.kc = kv->k + (size_t)li * kv->layer_stride;
@@ -496,7 +502,7 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
             epi.hd = hd;
             epi.kvdim = nkv;
             epi.theta = c.rope_theta;
-            if (launch_gemv(s, cap, pa, map, fseg, epi, K, e->st) != cudaSuccess) return -1;
+            if (launch_gemv<BlockQ4, EpiQkv>(s, cap, pa, jq, jk, fseg, epi, K, e->st) != cudaSuccess) return -1;
             n++;
         }
         {  // 2. attention
@@ -519,10 +525,9 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
         {  // 3. o-proj + residual
             PrepArgs pa{};
             pa.vec = e->attn;
-            pa.wt = wt_of(L.wo);
-            MapSingle map{L.wo->m, make_share((K + 1) / 2, cap)};
             EpiStore epi{e->x, nullptr, 2, K};
-            if (launch_gemv(s, cap, pa, map, F32Seg{}, epi, nq, e->st) != cudaSuccess) return -1;
+            if (launch_typed(s, cap, L.wo->m.type, pa, make_job(L.wo->m, 2, cap), RowJob{}, F32Seg{}, epi, nq, e->st) != cudaSuccess)
+                return -1;
             n++;
         }
         {  // 4. norm + quant + gate/up + silu*mul
@@ -530,19 +535,19 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
             pa.vec = e->x;
             pa.normw = L.ffn_norm;
             pa.eps = c.rms_eps;
-            pa.wt = WT_Q4K;
-            MapPair map{L.gate->m, L.up->m, make_share(FF, cap)};
             EpiSilu epi{e->h};
-            if (launch_gemv(s, cap, pa, map, F32Seg{}, epi, K, e->st) != cudaSuccess) return -1;
+            if (launch_gemv<BlockQ4, EpiSilu>(s, cap, pa, make_job(L.gate->m, 1, cap), make_job(L.up->m, 1, cap), F32Seg{}, epi,
+                                              K, e->st) != cudaSuccess)
+                return -1;
             n++;
         }
         {  // 5. down + residual
             PrepArgs pa{};
             pa.vec = e->h;
-            pa.wt = wt_of(L.down);
-            MapSingle map{L.down->m, make_share((K + 1) / 2, cap)};
             EpiStore epi{e->x, nullptr, 2, K};
-            if (launch_gemv(s, cap, pa, map, F32Seg{}, epi, FF, e->st) != cudaSuccess) return -1;
+            if (launch_typed(s, cap, L.down->m.type, pa, make_job(L.down->m, 2, cap), RowJob{}, F32Seg{}, epi, FF, e->st) !=
+                cudaSuccess)
+                return -1;
             n++;
         }
         if (e->layer_taps &&
@@ -554,13 +559,13 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
         pa.vec = e->x;
         pa.normw = e->output_norm;
         pa.eps = c.rms_eps;
-        pa.wt = wt_of(e->head);
-        MapSingle map{e->head->m, make_share((V + 1) / 2, cap)};
         EpiLogits epi{};
         epi.logits = e->logits;
         epi.out_tokens = e->out_tokens;
         epi.n_rows = V;
-        if (launch_gemv(s, cap, pa, map, F32Seg{}, epi, K, e->st) != cudaSuccess) return -1;
+        if (launch_typed(s, cap, e->head->m.type, pa, make_job(e->head->m, 2, cap), RowJob{}, F32Seg{}, epi, K, e->st) !=
+            cudaSuccess)
+            return -1;
         n++;
     } else {
         k_state_next_prompt<<<1, 1, 0, s>>>(e->st, e->prompt);
@@ -744,6 +749,10 @@ extern "C" int tfr_debug_read(tfr_engine* e, tfr_kv* kv, const char* what, int l
 
 // ------------------------------------------------------------------ operator level
 
+extern "C" int tfr_debug_set_timeline(unsigned long long* device_buffer) {
+    return cudaMemcpyToSymbol(g_prof, &device_buffer, sizeof(device_buffer)) == cudaSuccess ? TFR_OK : TFR_E_CUDA;
+}
+
 static int check(cudaError_t r) { return r == cudaSuccess ? TFR_OK : TFR_E_CUDA; }
 
 extern "C" int tfr_op_quantize_q8(const float* x, int n, int8_t* q8, float* d8, void* stream) {
@@ -763,17 +772,17 @@ extern "C" int tfr_op_gemv(const tfr_mat* w, const float* x, float* out, const f
     pa.vec = x;
     pa.normw = norm_w;
     pa.eps = eps;
-    pa.wt = wt_of(w);
-    const int C = sm_count_cached(), pairs = (w->m.N + 1) / 2;
-    MapSingle map{w->m, make_share(act_mode == 1 ? 0 : pairs, C)};
+    const int C = sm_count_cached();
+    RowJob ja = make_job(w->m, 2, C);
     F32Seg fseg{};
     if (act_mode == 1) {
+        ja.sh = make_share(0, C);  // every row goes through the fp32-activation route
         fseg.m = w->m;
-        fseg.sh = make_share(pairs, C);
+        fseg.sh = make_share((w->m.N + 1) / 2, C);
         fseg.id_base = 0;
     }
     EpiStore epi{out, bias, use_res, w->m.N};
-    return check(launch_gemv((cudaStream_t)stream, C, pa, map, fseg, epi, w->m.K, nullptr));
+    return check(launch_typed((cudaStream_t)stream, C, w->m.type, pa, ja, RowJob{}, fseg, epi, w->m.K, nullptr));
 }
 
 extern "C" int tfr_op_ffn_gate_up(const tfr_mat* gate, const tfr_mat* up, const float* x, const float* norm_w, float eps, float* h,
@@ -785,10 +794,10 @@ extern "C" int tfr_op_ffn_gate_up(const tfr_mat* gate, const tfr_mat* up, const 
     pa.vec = x;
     pa.normw = norm_w;
     pa.eps = eps;
-    pa.wt = WT_Q4K;
-    MapPair map{gate->m, up->m, make_share(gate->m.N, sm_count_cached())};
+    const int C = sm_count_cached();
     EpiSilu epi{h};
-    return check(launch_gemv((cudaStream_t)stream, sm_count_cached(), pa, map, F32Seg{}, epi, gate->m.K, nullptr));
+    return check(launch_gemv<BlockQ4, EpiSilu>((cudaStream_t)stream, C, pa, make_job(gate->m, 1, C), make_job(up->m, 1, C),
+                                               F32Seg{}, epi, gate->m.K, nullptr));
 }
 
 extern "C" int tfr_op_ffn_block(const tfr_mat* gate, const tfr_mat* up, const tfr_mat* down, const float* x, float* h_scratch,
@@ -823,7 +832,10 @@ extern "C" int tfr_op_int_dots(const tfr_mat* w, const int8_t* q8, const float* 
     if (w->m.type == TFR_Q4_K && !b) return TFR_E_INVALID;
     configure_kernels_once();
     const size_t smem = act_smem_bytes(w->m.K, false, false);
-    k_int_dots<<<sm_count_cached(), 256, smem, (cudaStream_t)stream>>>(w->m, (const signed char*)q8, d8, a, b);
+    if (w->m.type == TFR_Q4_K)
+        k_int_dots<BlockQ4><<<sm_count_cached(), 256, smem, (cudaStream_t)stream>>>(w->m, (const signed char*)q8, d8, a, b);
+    else
+        k_int_dots<BlockQ6><<<sm_count_cached(), 256, smem, (cudaStream_t)stream>>>(w->m, (const signed char*)q8, d8, a, b);
     return check(cudaGetLastError());
 }
 
@@ -892,13 +904,8 @@ extern "C" int tfr_op_qkv_rope_store(const tfr_mat* wq, const tfr_mat* wk, const
     pa.vec = x;
     pa.normw = norm_w;
     pa.eps = eps;
-    pa.wt = WT_Q4K;
     const int C = sm_count_cached();
-    MapQK map{};
-    map.q = wq->m;
-    map.k = wk->m;
-    map.shq = make_share(nq / 2, C);
-    map.shk = make_share(nkv / 2, C);
+    const RowJob jq = make_job(wq->m, 2, C, 0), jk = make_job(wk->m, 2, C, nq / 2);
     F32Seg fseg{};
     fseg.m = wv->m;
     fseg.sh = make_share(nkv / 2, C);
@@ -914,7 +921,7 @@ extern "C" int tfr_op_qkv_rope_store(const tfr_mat* wq, const tfr_mat* wk, const
     epi.kvdim = nkv;
     epi.theta = theta;
     epi.pos = pos;
-    return check(launch_gemv(s, C, pa, map, fseg, epi, wq->m.K, nullptr));
+    return check(launch_gemv<BlockQ4, EpiQkv>(s, C, pa, jq, jk, fseg, epi, wq->m.K, nullptr));
 }
 
 // ------------------------------------------------------------------ synthetic quantiser

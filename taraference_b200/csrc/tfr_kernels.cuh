@@ -7,10 +7,13 @@ namespace tfr {
 
 // ------------------------------------------------------------------ epilogues
 //
-// An epilogue receives the two finished dot products of a row pair from exactly one thread.
+// An epilogue receives two finished dot products from exactly one thread: rows (2p, 2p+1) of a
+// matrix (EPI_PAIRS) or row p of two matrices walked together (EPI_ZIP).
+enum { EPI_PAIRS = 0, EPI_ZIP = 1 };
 
 // y = W x (+y) (+bias): kernels/gemv.cu:367-373 residual rule (2 = accumulate in place).
 struct EpiStore {
+    static constexpr int MODE = EPI_PAIRS;
     float* out;
     const float* bias;
     int use_res;
@@ -30,6 +33,7 @@ struct EpiStore {
 
 // h = silu(gate.x) * (up.x), kernels/gemv.cu:2570-2574.  Pair p = (gate row p, up row p).
 struct EpiSilu {
+    static constexpr int MODE = EPI_ZIP;
     float* out;
     __device__ void begin(const TokenState*) {}
     __device__ __forceinline__ void apply(int p, float gate, float up) {
@@ -42,6 +46,7 @@ struct EpiSilu {
 // (kernels/ops.cu:471-486).  Q and K rows were re-ordered at upload so that the RoPE
 // partners (i, i + hd/2) of a head are the two rows of a pair; biases likewise.
 struct EpiQkv {
+    static constexpr int MODE = EPI_PAIRS;
     float* q_out;            // [n_head * hd] natural order
     unsigned short* kc;      // layer base [max_seq][kvdim]
     unsigned short* vc;
@@ -91,6 +96,7 @@ struct EpiQkv {
 // kernel can start without the host (the reference reads the argmax back every token,
 // crates/core/src/cuda/forward.rs:100-104).
 struct EpiLogits {
+    static constexpr int MODE = EPI_PAIRS;
     float* logits;
     int* out_tokens;   // ring of emitted tokens, indexed by TokenState::step
     int n_rows;
@@ -106,14 +112,19 @@ struct EpiLogits {
         if (2 * p + 1 < n_rows) one(2 * p + 1, v1);
     }
     __device__ void end(TokenState* st) {
-        __shared__ unsigned long long sbest[GEMV_THREADS / 32];
+        __shared__ unsigned long long sbest[GEMV_WARPS];
         __shared__ int last;
         const int tid = threadIdx.x;
+        // several lanes of a warp may have handled rows: fold their candidates first
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(TFR_FULL_MASK, best, o);
+            best = other > best ? other : best;
+        }
         if ((tid & 31) == 0) sbest[tid >> 5] = best;
         __syncthreads();
         if (tid == 0) {
             unsigned long long b = 0ull;
-            for (int i = 0; i < GEMV_THREADS / 32; i++) b = sbest[i] > b ? sbest[i] : b;
+            for (int i = 0; i < GEMV_WARPS; i++) b = sbest[i] > b ? sbest[i] : b;
             atomicMax(&st->best, b);
             __threadfence();
             const unsigned int old = atomicAdd(&st->head_done, 1u);
@@ -140,74 +151,187 @@ struct EpiLogits {
 
 // ------------------------------------------------------------------ the GEMV kernel
 
+// Optional timeline probe (test aid): when set, thread 0 of every CTA stores %globaltimer at six
+// points of k_gemv into g_prof[cta * 8 + point].
+__constant__ unsigned long long* g_prof = nullptr;
+__device__ __forceinline__ void prof_mark(int point) {
+    if (g_prof && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        g_prof[blockIdx.x * 8 + point] = t;
+    }
+}
+
 struct PrepArgs {
     const float* vec;     // source vector; nullptr -> embedding row of TokenState::token
     Mat embed;
     const float* normw;   // RMSNorm weight or nullptr
     float eps;
-    int wt;               // WT_Q4K / WT_Q6K: type of the rows that take the Q8 activation
     float* raw_out;       // embedding source only: CTA 0 stores the decoded row here (residual stream)
     int token;            // embedding source without TokenState
 };
 
-// Rows that take the fp32 activation instead (Q6_K attn_v); data == nullptr: none.
+// A matrix whose rows are spread over the CTAs in contiguous shares of `rows_per_item` rows.
+// data == nullptr: absent.
+struct RowJob {
+    Mat m;
+    Share sh;
+    int rows_per_item;  // 2: the share counts row pairs; 1: rows
+    int id_base;        // epilogue id of the matrix's first item
+};
+
+// Rows that take the fp32 activation instead (Q6_K attn_v); m.data == nullptr: none.
 struct F32Seg {
     Mat m;
     Share sh;     // over row pairs
     int id_base;  // pair id of the segment's first pair
 };
 
-constexpr int GEMV_PT = 2 * GEMV_THREADS;  // floats per partial-sum buffer
-
-// Shared-memory map of k_gemv: [ Act | partial sums x2 | 272 floats | 512 pair ids ].
-inline size_t gemv_smem_bytes(int K, bool has_norm) {
+// Shared-memory map of k_gemv:
+//   [ Act | partial sums (pbuf_floats) | 272 floats | full[slots] mbarriers | tile slots ].
+constexpr size_t GEMV_SMEM_MAX = 225 * 1024;  // opt-in limit is 227 KB including the kernels' small static arrays
+inline size_t gemv_smem_fixed(int K, bool has_norm, int pbuf_floats) {
     size_t act_bytes = (act_smem_bytes(K, true, has_norm) + 15) & ~(size_t)15;
-    return act_bytes + 2 * (size_t)GEMV_PT * sizeof(float) + 272 * sizeof(float) + 512 * sizeof(int);
+    return act_bytes + (size_t)pbuf_floats * sizeof(float) + 272 * sizeof(float);
+}
+inline int gemv_pbuf_floats(int rows_a, int rows_b, int nb) {
+    const int need = (rows_a + rows_b) * nb;
+    return need > 4096 ? ((need + 3) & ~3) : 4096;
 }
 
-// One CTA of GEMV_THREADS threads per SM walks its share of row pairs.  Thread
-// (r, u) = (tid / G, tid % G) owns unit column u of the r-th pair of every pass, so its byte
-// offsets inside a row never change.  The weight loads of the first pass are issued before
-// anything else: HBM streams while the activation is staged, normalised and quantised, and
-// inside the loop the next pass is requested before the current one is reduced.
-// K = 2048 (G = 32) makes a warp own a whole row pair: the reduction is five shuffles and the
-// CTA never synchronises in the loop.  Other K go through shared-memory partial sums.
-template <class Map, class Epi>
+// Row sums from the per-block partials and the epilogue.  LPR lanes add up one row.
+template <int MODE, class Epi>
+__device__ __forceinline__ void reduce_rows(const float* pa, const float* pb, int n_rows, int nb, int id0, Epi& epi) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (nb <= 16) {
+        const int LPR = nb <= 8 ? 8 : 16, RPW = 32 / LPR;
+        const int k = lane & (LPR - 1), rl = lane / LPR;
+        for (int base = warp * RPW; base < n_rows; base += GEMV_WARPS * RPW) {
+            const int r = base + rl;
+            const bool on = r < n_rows && k < nb;
+            float a = on ? pa[r * nb + k] : 0.f;
+            float b = (MODE == EPI_ZIP && on) ? pb[r * nb + k] : 0.f;
+            for (int o = LPR >> 1; o > 0; o >>= 1) {
+                a += __shfl_xor_sync(TFR_FULL_MASK, a, o);
+                if (MODE == EPI_ZIP) b += __shfl_xor_sync(TFR_FULL_MASK, b, o);
+            }
+            if (MODE == EPI_ZIP) {
+                if (k == 0 && r < n_rows) epi.apply(id0 + r, a, b);
+            } else {
+                const float other = __shfl_down_sync(TFR_FULL_MASK, a, LPR);  // the odd row of the pair
+                if (k == 0 && !(rl & 1) && r < n_rows) epi.apply(id0 + (r >> 1), a, other);
+            }
+        }
+    } else {
+        const int items = MODE == EPI_ZIP ? n_rows : (n_rows + 1) >> 1;
+        for (int it = warp; it < items; it += GEMV_WARPS) {
+            const float* ra = MODE == EPI_ZIP ? pa + it * nb : pa + (2 * it) * nb;
+            const float* rb = MODE == EPI_ZIP ? pb + it * nb : ra + nb;
+            const bool has_b = MODE == EPI_ZIP || 2 * it + 1 < n_rows;
+            float a = 0.f, b = 0.f;
+            for (int i = lane; i < nb; i += 32) {
+                a += ra[i];
+                if (has_b) b += rb[i];
+            }
+            a = warp_sum(a);
+            b = warp_sum(b);
+            if (lane == 0) epi.apply(id0 + it, a, b);
+        }
+    }
+}
+
+// One CTA of 1024 threads per SM.  The weight tiles of the CTA's rows are pulled into
+// shared memory by bulk copies (TMA, one 4.5 / 6.6 KB request per tile).  Every warp requests
+// its own tiles at kernel entry (one issuing thread cannot keep HBM busy: a thread issues
+// only a few copies per microsecond), so they stream from HBM while all warps stage,
+// normalise and quantise the activation.  A warp then waits on its tile's mbarrier, each
+// lane reads its own block from the tile, the lane's partial goes to shared memory and,
+// after a single barrier, rows are summed in a fixed order and handed to the epilogue.  When
+// the CTA has more tiles than slots (the vocabulary head), a warp owns one slot and refills
+// it itself after each tile.
+template <class BLK, class Epi>
 __global__ void __launch_bounds__(GEMV_THREADS, 1)
-k_gemv(PrepArgs pa, Map map, F32Seg fseg, Epi epi_in, int K, TokenState* st) {
-    extern __shared__ __align__(16) unsigned char smem[];
-    constexpr int NW = GEMV_THREADS / 32;
+k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pbuf_floats, int slots, TokenState* st) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    prof_mark(0);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, cta = blockIdx.x;
     const bool has_norm = pa.normw != nullptr;
     Epi epi = epi_in;
     Act act = act_carve(smem, K, true, has_norm);
     const size_t act_bytes = (act_smem_bytes(K, true, has_norm) + 15) & ~(size_t)15;
     float* pbuf = reinterpret_cast<float*>(smem + act_bytes);
-    float* red = pbuf + 2 * GEMV_PT;
-    int* ids = reinterpret_cast<int*>(red + 272);
+    float* red = pbuf + pbuf_floats;
+    unsigned long long* full = reinterpret_cast<unsigned long long*>(red + 272);
     float* xs = act.xf;
+    const int nb = K >> 8;
+    constexpr int TB = BLK::TILE_BYTES;
+    unsigned char* ring = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(full + slots) + 127) & ~(uintptr_t)127);
 
-    const int G = K >> 6;
-    const int R = GEMV_THREADS / G;  // row pairs per pass
-    const int r = tid / G, u = tid - r * G;
-    const bool active = r < R;
-    const UnitOff off = unit_offsets(u, map.nb());
-    const int wt = pa.wt;
-    const int n_loc = map.n_local(cta);
+    // flat block ranges of this CTA in A and B, and the tiles that cover them
+    const int rows_a0 = ja.sh.begin(cta) * ja.rows_per_item;
+    const int rows_a = max(0, min(ja.sh.count(cta) * ja.rows_per_item, ja.m.N - rows_a0));
+    const int rows_b0 = jb.m.data ? jb.sh.begin(cta) * jb.rows_per_item : 0;
+    const int rows_b = jb.m.data ? max(0, min(jb.sh.count(cta) * jb.rows_per_item, jb.m.N - rows_b0)) : 0;
+    const long long fa0 = (long long)rows_a0 * nb, fa1 = fa0 + (long long)rows_a * nb;
+    const long long fb0 = (long long)rows_b0 * nb, fb1 = fb0 + (long long)rows_b * nb;
+    const int ta0 = (int)(fa0 >> 5), tiles_a = rows_a > 0 ? (int)((fa1 + 31) >> 5) - ta0 : 0;
+    const int tb0 = (int)(fb0 >> 5), tiles_b = rows_b > 0 ? (int)((fb1 + 31) >> 5) - tb0 : 0;
+    const int n_jobs = tiles_a + tiles_b;
+    float* part_a = pbuf;
+    float* part_b = pbuf + rows_a * nb;
+    auto job_src = [&](int j) -> const uint8_t* {
+        return j < tiles_a ? ja.m.data + (long long)(ta0 + j) * TB : jb.m.data + (long long)(tb0 + j - tiles_a) * TB;
+    };
+    // Tile j of the CTA belongs to warp j % stride.  Without reuse every tile has its own slot; with
+    // reuse (more tiles than slots) warp w owns slot w and walks its tiles through it in order.
+    const bool reuse = n_jobs > slots;
+    const int stride = reuse ? slots : GEMV_WARPS;
+    auto issue = [&](int j) {
+        const int s = reuse ? warp : j;
+        mbar_expect_tx(full + s, TB);
+        bulk_load(ring + (size_t)s * TB, job_src(j), TB, full + s);
+    };
 
-    // first pass of weights: requested before anything else
-    UnitW w0, w1;
-    PairRows pr = map.pair(cta, (active && r < n_loc) ? r : 0);
-    if (n_loc > 0) {
-        load_unit(w0, wt, pr.r0, off);
-        load_unit(w1, wt, pr.r1, off);
-    }
+    // The activation is requested first so that its loads are ahead of the bulk tile copies in the
+    // memory system's queues; the copies are issued while those loads are in flight.
+    constexpr int STAGE_REGS = 4;  // float4 per thread held in registers: K <= 16384
+    float4 sx[STAGE_REGS], sw[STAGE_REGS];
     const int done = st ? st->done : 0;
     if (pa.vec) {
-        for (int i4 = tid; i4 < (K >> 2); i4 += GEMV_THREADS) {
-            const int at = xs_idx(4 * i4);
-            *reinterpret_cast<float4*>(xs + at) = reinterpret_cast<const float4*>(pa.vec)[i4];
-            if (has_norm) *reinterpret_cast<float4*>(act.wf + at) = reinterpret_cast<const float4*>(pa.normw)[i4];
+#pragma unroll
+        for (int k = 0; k < STAGE_REGS; k++) {
+            const int i4 = tid + k * GEMV_THREADS;
+            if (i4 < (K >> 2)) {
+                sx[k] = reinterpret_cast<const float4*>(pa.vec)[i4];
+                if (has_norm) sw[k] = reinterpret_cast<const float4*>(pa.normw)[i4];
+            }
+        }
+    }
+    if (lane == 0 && warp < stride) {
+        for (int j = warp; j < n_jobs; j += stride) {
+            mbar_init(full + (reuse ? warp : j), 1);
+            if (reuse) break;
+        }
+        mbar_fence_init();
+        for (int j = warp; j < n_jobs; j += stride) {
+            issue(j);
+            if (reuse) break;
+        }
+    }
+    __syncwarp();
+    prof_mark(1);
+    const bool want_xf = fseg.m.data != nullptr;  // only fp32-route rows read the staged vector afterwards
+    const bool from_regs = pa.vec != nullptr && K <= STAGE_REGS * GEMV_THREADS * 4;
+    if (pa.vec) {
+        if (has_norm || want_xf || !from_regs) {
+#pragma unroll
+            for (int k = 0; k < STAGE_REGS; k++) {
+                const int i4 = tid + k * GEMV_THREADS;
+                if (i4 < (K >> 2)) *reinterpret_cast<float4*>(xs + xs_idx(4 * i4)) = sx[k];
+            }
+            for (int i4 = tid + STAGE_REGS * GEMV_THREADS; i4 < (K >> 2); i4 += GEMV_THREADS)
+                *reinterpret_cast<float4*>(xs + xs_idx(4 * i4)) = reinterpret_cast<const float4*>(pa.vec)[i4];
         }
     } else {
         int tok = st ? st->token : pa.token;
@@ -219,23 +343,57 @@ k_gemv(PrepArgs pa, Map map, F32Seg fseg, Epi epi_in, int K, TokenState* st) {
         for (int i = tid; i < K; i += GEMV_THREADS) {
             const float v = src.get(i);
             xs[xs_idx(i)] = v;
-            if (has_norm) act.wf[xs_idx(i)] = pa.normw[i];
             if (cta == 0 && pa.raw_out && !done) pa.raw_out[i] = v;
         }
     }
-    if (done) return;
-    __syncthreads();
+    __syncthreads();  // also publishes the initialised mbarriers to the consumer warps
+    prof_mark(2);
+    if (done) {
+        // the copies already in flight must land before the CTA's shared memory is released
+        if (lane == 0 && warp < stride)
+            for (int j = warp; j < n_jobs; j += stride) {
+                mbar_wait(full + (reuse ? warp : j), 0);
+                if (reuse) break;
+            }
+        return;
+    }
     float scale = 1.f;
     if (has_norm) scale = rms_scale_staged(xs, K, pa.eps, red);
-    act_quantize_staged(act, has_norm, scale, K, wt == WT_Q4K ? SWZ_Q4 : SWZ_Q6);
+    // quantise: straight from the registers that fetched the vector when it fits, else from the staged copy
+    for (int k0 = 0; k0 < (K >> 2); k0 += GEMV_THREADS) {
+        const int i4 = k0 + tid, kk = k0 / GEMV_THREADS;
+        const bool on = i4 < (K >> 2);
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f), w = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (from_regs) {
+#pragma unroll
+            for (int k = 0; k < STAGE_REGS; k++)
+                if (k == kk) {
+                    x = sx[k];
+                    w = sw[k];
+                }
+            if (!on) x = make_float4(0.f, 0.f, 0.f, 0.f);
+        } else if (on) {
+            x = *reinterpret_cast<const float4*>(xs + xs_idx(4 * i4));
+            if (has_norm) w = reinterpret_cast<const float4*>(pa.normw)[i4];
+        }
+        if (has_norm) {
+            x.x = x.x * scale * w.x;
+            x.y = x.y * scale * w.y;
+            x.z = x.z * scale * w.z;
+            x.w = x.w * scale * w.w;
+            if (want_xf && on) *reinterpret_cast<float4*>(xs + xs_idx(4 * i4)) = x;
+        }
+        act_quantize4(act, x, i4, on, nb);
+    }
     epi.begin(st);
     __syncthreads();
+    prof_mark(3);
 
-    // rows on the fp32 activation route: one task per (row, unit, run of 16), all threads
+    // rows on the fp32 activation route: one task per (row, block, run of 16), all threads
     if (fseg.m.data) {
         const int np = fseg.sh.count(cta), pbase = fseg.sh.begin(cta);
-        const int per_row = 4 * G, tasks = 2 * np * per_row;
-        const int chunk = ((2 * GEMV_PT) / (2 * per_row)) * (2 * per_row);  // whole row pairs per chunk
+        const int per_row = 16 * nb, tasks = 2 * np * per_row;
+        const int chunk = (pbuf_floats / (2 * per_row)) * (2 * per_row);  // whole row pairs per chunk
         for (int t0 = 0; t0 < tasks; t0 += chunk) {
             const int tn = min(chunk, tasks - t0);
             for (int t = tid; t < tn; t += GEMV_THREADS) {
@@ -243,92 +401,94 @@ k_gemv(PrepArgs pa, Map map, F32Seg fseg, Epi epi_in, int K, TokenState* st) {
                 const int row_l = task / per_row, rem = task - row_l * per_row;
                 const int row_g = 2 * pbase + row_l;
                 float v = 0.f;
-                if (row_g < fseg.m.N)
-                    v = q6k_run_dot_f32(fseg.m.data + (long long)row_g * fseg.m.row_stride, fseg.m.nb, rem >> 2, rem & 3, xs);
+                if (row_g < fseg.m.N) v = q6k_run_dot_f32(fseg.m, (long long)row_g * nb + (rem >> 4), rem >> 4, rem & 15, xs);
                 pbuf[t] = v;
             }
             __syncthreads();
             const int pairs_here = tn / (2 * per_row), pair_first = t0 / (2 * per_row);
-            for (int rr = warp; rr < pairs_here; rr += NW) {
+            for (int rr = warp; rr < pairs_here; rr += GEMV_WARPS) {
                 const float* a = pbuf + (2 * rr) * per_row;
                 float s0 = 0.f, s1 = 0.f;
                 for (int i = lane; i < per_row; i += 32) {
                     s0 += a[i];
                     s1 += a[per_row + i];
                 }
-                const float x = warp_sum_pair(s0, s1, lane);
-                const float y = __shfl_sync(TFR_FULL_MASK, x, 16);
-                if (lane == 0) epi.apply(fseg.id_base + pbase + pair_first + rr, x, y);
+                s0 = warp_sum(s0);
+                s1 = warp_sum(s1);
+                if (lane == 0) epi.apply(fseg.id_base + pbase + pair_first + rr, s0, s1);
             }
             __syncthreads();
         }
     }
 
-    const int t4 = u & 3, is = u & 1;
-    int buf = 0;
-    for (int base = 0; base < n_loc; base += R) {
-        const bool valid = active && base + r < n_loc;
-        const int id = pr.id;
-        float v0, v1;
-        {
-            Frag f;
-            frag_load(f, wt, act, active ? u : 0, G);
-            if (wt == WT_Q4K) {
-                v0 = q4k_dot(w0, f, t4, nullptr);
-                v1 = q4k_dot(w1, f, t4, nullptr);
-            } else {
-                v0 = q6k_dot(w0, f, is, nullptr);
-                v1 = q6k_dot(w1, f, is, nullptr);
+    // phase A: per-block partials out of the tiles
+    bool ok = true;
+    if (warp < stride) {
+        int it = 0;
+        for (int j = warp; j < n_jobs; j += stride, it++) {
+            const int s = reuse ? warp : j;
+            const bool is_b = j >= tiles_a;
+            const long long f = (long long)(is_b ? tb0 + (j - tiles_a) : ta0 + j) * 32 + lane;
+            const bool mine = is_b ? (f >= fb0 && f < fb1) : (f >= fa0 && f < fa1);
+            ok = mbar_wait(full + s, reuse ? (it & 1) : 0) && ok;
+            if (mine) {
+                float* dst = is_b ? part_b + (f - fb0) : part_a + (f - fa0);
+                *dst = block_dot<true>(BLK{}, ring + (size_t)s * TB, lane, act, (int)(f % nb), nb, nullptr);
+            }
+            __syncwarp();
+            if (reuse && lane == 0 && j + stride < n_jobs) {
+                fence_proxy_async();
+                issue(j + stride);
             }
         }
-        const int nbase = base + R;
-        if (nbase < n_loc) {
-            pr = map.pair(cta, (active && nbase + r < n_loc) ? nbase + r : 0);
-            load_unit(w0, wt, pr.r0, off);
-            load_unit(w1, wt, pr.r1, off);
-        }
-        if (G == 32) {
-            // warp == r: the 32 lanes hold the 32 units of both rows
-            const float x = warp_sum_pair(v0, v1, lane);
-            const float y = __shfl_sync(TFR_FULL_MASK, x, 16);
-            if (lane == 0 && valid) epi.apply(id, x, y);
-        } else {
-            float* part = pbuf + buf * GEMV_PT;
-            if (active) {
-                part[(2 * r) * G + u] = v0;
-                part[(2 * r + 1) * G + u] = v1;
-                if (u == 0) ids[buf * 256 + r] = id;
-            }
-            __syncthreads();
-            const int np = min(R, n_loc - base);
-            for (int pp = warp; pp < np; pp += NW) {
-                const float* a = part + (2 * pp) * G;
-                float s0 = 0.f, s1 = 0.f;
-                for (int i = lane; i < G; i += 32) {
-                    s0 += a[i];
-                    s1 += a[G + i];
-                }
-                const float x = warp_sum_pair(s0, s1, lane);
-                const float y = __shfl_sync(TFR_FULL_MASK, x, 16);
-                if (lane == 0) epi.apply(ids[buf * 256 + pp], x, y);
-            }
-            buf ^= 1;
-        }
+    }
+    if (!ok && st) st->err = 2;  // a bulk copy never completed: results of this step are invalid
+    __syncthreads();
+    prof_mark(4);
+    // phase B: row sums in a fixed order + epilogue
+    if (Epi::MODE == EPI_ZIP) {
+        reduce_rows<EPI_ZIP>(part_a, part_b, rows_a, nb, ja.id_base + rows_a0, epi);
+    } else {
+        reduce_rows<EPI_PAIRS>(part_a, part_a, rows_a, nb, ja.id_base + (rows_a0 >> 1), epi);
+        if (rows_b > 0) reduce_rows<EPI_PAIRS>(part_b, part_b, rows_b, nb, jb.id_base + (rows_b0 >> 1), epi);
     }
     epi.end(st);
+    prof_mark(5);
 }
 
-template <class Map, class Epi>
-inline cudaError_t launch_gemv(cudaStream_t stream, int grid, const PrepArgs& pa, const Map& map, const F32Seg& fseg,
-                               const Epi& epi, int K, TokenState* st) {
-    const size_t smem = gemv_smem_bytes(K, pa.normw != nullptr);
-    k_gemv<Map, Epi><<<grid, GEMV_THREADS, smem, stream>>>(pa, map, fseg, epi, K, st);
+template <class BLK, class Epi>
+inline cudaError_t launch_gemv(cudaStream_t stream, int grid, const PrepArgs& pa, const RowJob& ja, const RowJob& jb,
+                               const F32Seg& fseg, const Epi& epi, int K, TokenState* st) {
+    const int nb = K / 256;
+    constexpr int TB = BLK::TILE_BYTES;
+    const int ra = (ja.sh.quot + 1) * ja.rows_per_item, rb = jb.m.data ? (jb.sh.quot + 1) * jb.rows_per_item : 0;
+    int pf = gemv_pbuf_floats(ra, rb, nb);
+    if (fseg.m.data && pf < 2 * 16 * nb) pf = 2 * 16 * nb;
+    const size_t fixed = gemv_smem_fixed(K, pa.normw != nullptr, pf);
+    // tiles a CTA can need: each matrix's share may straddle one extra tile at either end
+    const int need = (ra * nb + 31) / 32 + 1 + (rb ? (rb * nb + 31) / 32 + 1 : 0);
+    if (fixed + 256 + 1024 + TB > GEMV_SMEM_MAX) return cudaErrorInvalidValue;
+    int slots = (int)((GEMV_SMEM_MAX - fixed - 256 - 1024) / (TB + 8));
+    if (slots >= need) slots = need;
+    else if (slots > GEMV_WARPS) slots = GEMV_WARPS;  // reuse: one slot per warp
+    if (slots < 1) slots = 1;
+    const size_t smem = fixed + (size_t)slots * 8 + 256 + (size_t)slots * TB;
+    k_gemv<BLK, Epi><<<grid, GEMV_THREADS, smem, stream>>>(pa, ja, jb, fseg, epi, K, pf, slots, st);
     return cudaGetLastError();
+}
+
+inline RowJob make_job(const Mat& m, int rows_per_item, int C, int id_base = 0) {
+    RowJob j{};
+    j.m = m;
+    j.rows_per_item = rows_per_item;
+    j.sh = make_share((m.N + rows_per_item - 1) / rows_per_item, C);
+    j.id_base = id_base;
+    return j;
 }
 
 // ------------------------------------------------------------------ small kernels
 
-// Stand-alone quantiser with linear output (A1), same expression as act_quantize_group.
+// Stand-alone quantiser with linear output (A1), same expression as act_quantize_staged.
 __global__ void k_quantize_q8(const float* __restrict__ x, signed char* __restrict__ q8, float* __restrict__ d8, int n) {
     const int lane = threadIdx.x & 31;
     const int g = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -343,59 +503,52 @@ __global__ void k_quantize_q8(const float* __restrict__ x, signed char* __restri
 
 // Builds an Act from an already quantised activation (linear int8 + scales); test-only path
 // used to expose the integer sub-block dots.
-__device__ void act_from_q8(Act& act, const signed char* q8, const float* d8, int K, int swz) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, G = K >> 6;
-    signed char* q8b = reinterpret_cast<signed char*>(act.q8);
-    for (int g = warp; g < (K >> 5); g += blockDim.x >> 5) {
-        const int i = (g << 5) + lane;
-        const int q = q8[i];
-        q8b[swz_pos(i >> 4, G, swz) * 16 + (i & 15)] = (signed char)q;
-        int s = q;
-        s += __shfl_xor_sync(TFR_FULL_MASK, s, 8);
-        s += __shfl_xor_sync(TFR_FULL_MASK, s, 4);
-        s += __shfl_xor_sync(TFR_FULL_MASK, s, 2);
+__device__ void act_from_q8(const Act& act, const signed char* q8, const float* d8, int K) {
+    const int tid = threadIdx.x, j = tid & 7, nb = K >> 8;
+    for (int g0 = 0; g0 < (K >> 5); g0 += blockDim.x / 8) {
+        const int g = g0 + (tid >> 3);
+        const bool on = g < (K >> 5);
+        const int e = 32 * (on ? g : 0) + 4 * j;
+        const int q0 = q8[e], q1 = q8[e + 1], q2 = q8[e + 2], q3 = q8[e + 3];
+        int s = q0 + q1 + q2 + q3;
         s += __shfl_xor_sync(TFR_FULL_MASK, s, 1);
-        const int hi = __shfl_sync(TFR_FULL_MASK, s, 16);
-        if (lane == 0) {
-            act.d8[g] = d8[g];
-            act.ss[g] = (s & 0xffff) | (hi << 16);
+        s += __shfl_xor_sync(TFR_FULL_MASK, s, 2);
+        const int other = __shfl_xor_sync(TFR_FULL_MASK, s, 4);
+        if (on) {
+            *act_word_ptr(act, e, nb) = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | ((q3 & 0xff) << 24);
+            if (j == 0) act_store_group(act, g, d8[g], s, other);
         }
     }
     __syncthreads();
 }
 
-// Integer contract taps, computed by the very dot routines the GEMV kernel uses.
+// Integer contract taps, computed by the very block-dot routines the GEMV kernel uses.
 // Q4_K: I[row][K/32], S[row][K/32].  Q6_K: J[row][K/16].
+template <class BLK>
 __global__ void k_int_dots(Mat m, const signed char* q8, const float* d8, int* outA, int* outB) {
     extern __shared__ __align__(16) unsigned char smem[];
-    const int K = m.K, G = K >> 6;
+    const int K = m.K, nb = m.nb, lane = threadIdx.x & 31;
     Act act = act_carve(smem, K, false, false);
-    const int wt = m.type == TFR_Q4_K ? WT_Q4K : WT_Q6K;
-    act_from_q8(act, q8, d8, K, m.type == TFR_Q4_K ? SWZ_Q4 : SWZ_Q6);
-    const int total = m.N * G;
-    for (int fidx = blockIdx.x * blockDim.x + threadIdx.x; fidx < total; fidx += gridDim.x * blockDim.x) {
-        const int r = fidx / G, u = fidx % G;
-        UnitW w;
-        Frag f;
-        const UnitOff off = unit_offsets(u, m.nb);
-        load_unit(w, wt, m.data + (long long)r * m.row_stride, off);
-        frag_load(f, wt, act, u, G);
-        if (m.type == TFR_Q4_K) {
-            int ints[2];
-            q4k_dot(w, f, u & 3, ints);
-            const int2 ss = reinterpret_cast<const int2*>(act.ss)[u];
-            int* I = outA + (size_t)r * (K / 32) + 2 * u;
-            int* S = outB + (size_t)r * (K / 32) + 2 * u;
-            I[0] = ints[0];
-            I[1] = ints[1];
-            S[0] = (int)(short)(ss.x & 0xffff) + (ss.x >> 16);
-            S[1] = (int)(short)(ss.y & 0xffff) + (ss.y >> 16);
+    act_from_q8(act, q8, d8, K);
+    const long long total = (long long)m.N * nb;
+    const long long tiles = (total + 31) >> 5;
+    const int TB = tile_bytes(m.type);
+    for (long long t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < tiles; t += (long long)gridDim.x * (blockDim.x >> 5)) {
+        const long long f = t * 32 + lane;
+        if (f >= total) continue;
+        const int r = (int)(f / nb), b = (int)(f % nb);
+        int ints[16];
+        block_dot<false>(BLK{}, m.data + t * TB, lane, act, b, nb, ints);
+        if (BLK::TILE_BYTES == Q4_TILE_BYTES) {
+            for (int j = 0; j < 8; j++) {
+                outA[(size_t)r * (K / 32) + 8 * b + j] = ints[j];
+                // S from the stored product is not exact; recompute from the int8 activation
+                int sacc = 0;
+                for (int i = 0; i < 32; i++) sacc += q8[256 * b + 32 * j + i];
+                outB[(size_t)r * (K / 32) + 8 * b + j] = sacc;
+            }
         } else {
-            int J[4];
-            q6k_dot(w, f, u & 1, J);
-            // run j of unit (b, n, is) is scale group 16b + 8n + 2j + is
-            const int b = u >> 2, n = (u >> 1) & 1, is = u & 1;
-            for (int j = 0; j < 4; j++) outA[(size_t)r * (K / 16) + 16 * b + 8 * n + 2 * j + is] = J[j];
+            for (int c = 0; c < 16; c++) outA[(size_t)r * (K / 16) + 16 * b + c] = ints[c];
         }
     }
 }
@@ -408,32 +561,26 @@ __device__ __forceinline__ int perm_src_row(int v, int perm_hd) {
     return h * perm_hd + (w >> 1) + (w & 1) * (perm_hd >> 1);
 }
 
-__global__ void k_repack_q4k(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int N, int nb, int perm_hd) {
-    const long long row_bytes = (long long)nb * 144;
-    const long long total = (long long)N * row_bytes;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (long long)gridDim.x * blockDim.x) {
-        const int v = (int)(i / row_bytes);
-        const long long off = i - (long long)v * row_bytes;
-        dst[i] = src[(long long)perm_src_row(v, perm_hd) * row_bytes + off];
-    }
-}
-
-__global__ void k_repack_q6k(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int N, int nb,
-                             long long dst_stride, int perm_hd) {
-    const long long src_row = (long long)nb * 210;
-    const long long total = (long long)N * src_row;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (long long)gridDim.x * blockDim.x) {
-        const int v = (int)(i / src_row);
-        const int off = (int)(i - (long long)v * src_row);
-        const int b = off / 210, e = off % 210;
-        long long d;
-        if (e < 128) d = (long long)b * 128 + e;
-        else if (e < 192) d = (long long)nb * 128 + b * 64 + (e - 128);
-        else if (e < 208) d = (long long)nb * 192 + b * 16 + (e - 192);
-        else d = (long long)nb * 208 + b * 2 + (e - 208);
-        dst[(long long)v * dst_stride + d] = src[(long long)perm_src_row(v, perm_hd) * src_row + off];
+// GGUF block bytes -> warp-tiled layout (see tfr_gemv.cuh).  One thread per (flat block, 16-byte
+// piece); tail tiles are zero-filled by the caller.
+__global__ void k_repack_tiled(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int type, int N, int nb,
+                               int perm_hd) {
+    const int pieces = type == TFR_Q4_K ? Q4_PIECES : Q6_PIECES + 1;  // Q6_K: 13 pieces + the 2-byte d
+    const int blk = type == TFR_Q4_K ? 144 : 210, TB = tile_bytes(type);
+    const long long total = (long long)N * nb * pieces;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long f = i / pieces;
+        const int pc = (int)(i - f * pieces);
+        const int row = (int)(f / nb), b = (int)(f - (long long)row * nb);
+        const uint8_t* sb = src + ((long long)perm_src_row(row, perm_hd) * nb + b) * blk;
+        uint8_t* tile = dst + (f >> 5) * TB;
+        const int lane = (int)(f & 31);
+        if (type == TFR_Q6_K && pc == Q6_PIECES) {
+            tile[Q6_PIECES * 512 + lane * 2] = sb[208];
+            tile[Q6_PIECES * 512 + lane * 2 + 1] = sb[209];
+        } else {
+            for (int k = 0; k < 16; k++) tile[pc * 512 + lane * 16 + k] = sb[pc * 16 + k];
+        }
     }
 }
 
