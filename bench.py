@@ -90,6 +90,20 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def aggregate_over_ranks(dev_ms_total: float, wall_s_total: float, tokens_per_rank: int, world: int, dist=None,
+                         device="cpu"):
+    """Whole-job numbers from per-rank timings: every rank decodes `tokens_per_rank` tokens on its own
+    replica; the job takes as long as its slowest rank (MAX over ranks), and the value counts all tokens."""
+    import torch
+    if world > 1:
+        t = torch.tensor([dev_ms_total, wall_s_total], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms_total, wall_s_total = float(t[0]), float(t[1])
+    tokens_all = tokens_per_rank * world
+    return {"value": tokens_all / (dev_ms_total / 1000.0), "e2e": tokens_all / wall_s_total,
+            "dev_ms": dev_ms_total, "wall_s": wall_s_total, "tokens": tokens_all}
+
+
 def dist_env():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -245,6 +259,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-reference-gpu", action="store_true")
+    ap.add_argument("--roofline-only", action="store_true",
+                    help="time only the fused gate+up kernel over 254 MB of weights (the small case used for ncu)")
     args = ap.parse_args()
     rank, world, local = dist_env()
     if args.impl == "reference":
@@ -255,6 +271,11 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the decode library has no CPU fallback")
     from taraference_b200 import engine as E, synth as S, synth_gpu
+    if args.roofline_only:
+        peak, peak_kind = measured_peaks()
+        torch.cuda.set_device(local)
+        print(json.dumps({"roofline": gate_up_roofline(E, S, dict(S.QWEN25_3B), peak, peak_kind)}), flush=True)
+        return
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
@@ -298,14 +319,9 @@ def main():
     wall_all = time.perf_counter() - t_all
     clocks = sampler.stop() if rank == 0 else None
     launches = model.launch_count() - launches0
-    dev_total, wall_total = float(np.sum(dev_ms)), float(np.sum(walls))
-    if world > 1:
-        t = torch.tensor([dev_total, wall_total], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_total, wall_total = float(t[0]), float(t[1])
-    tokens_all = N_DECODE * args.steps * world
-    value = tokens_all / (dev_total / 1000.0)
-    e2e_value = tokens_all / wall_total
+    agg = aggregate_over_ranks(float(np.sum(dev_ms)), float(np.sum(walls)), N_DECODE * args.steps, world,
+                               dist if world > 1 else None, "cuda")
+    dev_total, wall_total, value, e2e_value = agg["dev_ms"], agg["wall_s"], agg["value"], agg["e2e"]
 
     # per-token host round-trip through forward_greedy (the reference's call pattern), rank 0 only
     per_token_api = None
