@@ -37,8 +37,8 @@ PROMPT_LEN, N_DECODE, CTX = 32, 256, 4096
 METRIC, UNIT = "batch1_decode_tokens_per_s", "tok/s"
 NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate+up launch, from the ncu capture
-# summarised in profiles/ffn_gate_up_qwen25_3b.md (None until such a capture exists)
-GATE_UP_DRAM_TRAFFIC_BYTES = None
+# summarised in profiles/ffn_gate_up_qwen25_3b.md
+GATE_UP_DRAM_TRAFFIC_BYTES = 25426432
 
 
 def measured_peaks() -> tuple[float, str]:
@@ -245,7 +245,7 @@ def gate_up_roofline(E, S, cfg, peak_gbs, peak_kind):
     for mg, mu in sets:
         mg.free(), mu.free()
     ach = alg / us * 1e-3
-    return {"bound": "hbm", "kernel": "k_gemv<MapPair,EpiSilu> (RMSNorm+Q8+gate/up+SiLU*mul, 11008x2048 Q4_K x2)",
+    return {"bound": "hbm", "kernel": "k_gemv<BlockQ4,EpiSilu> (RMSNorm+Q8+gate/up+SiLU*mul, 11008x2048 Q4_K x2)",
             "achieved": ach, "peak": peak_gbs, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": ach / peak_gbs,
             "traffic": GATE_UP_DRAM_TRAFFIC_BYTES, "algorithmic_bytes_per_launch": alg, "us_per_launch": us,
             "note": "back-to-back launches on one stream: includes the launch gap"}

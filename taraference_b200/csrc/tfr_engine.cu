@@ -69,7 +69,7 @@ struct tfr_engine {
     TokenState* st_host = nullptr;  // pinned
     int *out_tokens = nullptr, *out_host = nullptr, *prompt = nullptr;
     int *args_dev = nullptr, *args_host = nullptr;  // per-call scalars: pinned host -> device
-    int attn_S = 1, attn_min_keys = 256;
+    int attn_S = 1, attn_min_keys = 32;
     float* layer_taps = nullptr;  // [n_layer][n_embd] residual stream after each layer (test aid)
     // graphs
     bool use_graph = true;
@@ -869,7 +869,7 @@ extern "C" int tfr_op_attention(const float* q, const uint16_t* kc, const uint16
     a.out = out;
     a.n_head = n_head;
     a.n_kv = n_kv;
-    a.min_keys = 256;
+    a.min_keys = 32;
     a.scale = 1.0f / sqrtf((float)head_dim);
     a.pos = pos;
     return check(launch_attention((cudaStream_t)stream, a, head_dim, nullptr));
