@@ -526,7 +526,7 @@ __device__ void act_from_q8(const Act& act, const signed char* q8, const float* 
 // Q4_K: I[row][K/32], S[row][K/32].  Q6_K: J[row][K/16].
 template <class BLK>
 __global__ void k_int_dots(Mat m, const signed char* q8, const float* d8, int* outA, int* outB) {
-    extern __shared__ __align__(16) unsigned char smem[];
+    extern __shared__ __align__(128) unsigned char smem[];
     const int K = m.K, nb = m.nb, lane = threadIdx.x & 31;
     Act act = act_carve(smem, K, false, false);
     act_from_q8(act, q8, d8, K);
