@@ -157,6 +157,18 @@ int tfr_op_int_dots(const tfr_mat* w, const int8_t* q8, const float* d8, int32_t
  * at position pos over cache rows [0, pos].  kc / vc: [max_seq][n_kv*head_dim] f16 bits. */
 int tfr_op_attention(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv,
                      int head_dim, int pos, void* stream);
+/* Same computation as tfr_op_attention for callers that cannot allocate device memory when they
+ * call (a graph capture in progress elsewhere in the context, a fixed memory budget, a real-time
+ * loop).  It has no counterpart in the reference.  The split-KV scratch is a fixed 2 MiB array
+ * inside the library image (held by every GPU that loads the library, until exit); the call
+ * performs no cudaMalloc / cudaFree and uses no allocating library routine.  Shapes whose scratch
+ * n_head * (n_sm / n_kv) * (2 + head_dim) * 4 bytes exceeds 2 MiB - 256 B, or with more than 64 KV
+ * heads, are refused with TFR_E_UNSUPPORTED and a message on stderr.  The first call on a device
+ * looks up the array's device address (that device must be current); make that first call before
+ * any stream capture begins.  All calls share the one array: calls that overlap on the GPU
+ * (different streams, or threads) race on it — serialise them. */
+int tfr_op_attention_noalloc(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv,
+                             int head_dim, int pos, void* stream);
 /* Fused attention front end: RMSNorm + Q8 + Q/K/V projections + bias + RoPE + f16 KV store
  * (rms_norm_f32, gemv_q4_k_pair, gemv_q6_k, rope_neox_f32, copy_kv_f16; layer.rs:196-600).
  * wq / wk must have been created with rope_pair_head_dim = head_dim; biases natural order. */

@@ -73,6 +73,7 @@ def lib() -> C.CDLL:
         "tfr_ffn_block_host": (i32, [vp, vp, vp, vp, vp]),
         "tfr_op_int_dots": (i32, [vp, vp, vp, vp, vp, vp]),
         "tfr_op_attention": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
+        "tfr_op_attention_noalloc": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
         "tfr_op_qkv_rope_store": (i32, [vp] * 8 + [f32, f32, i32, i32, vp, vp, vp, vp]),
         "tfr_synth_quantize": (i32, [i32, vp, i64, i64, vp, vp]),
     }

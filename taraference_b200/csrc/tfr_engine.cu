@@ -875,6 +875,64 @@ extern "C" int tfr_op_attention(const float* q, const uint16_t* kc, const uint16
     return check(launch_attention((cudaStream_t)stream, a, head_dim, nullptr));
 }
 
+// ---- flash-decode without any allocation --------------------------------------------------
+//
+// Some callers of this library must not allocate device memory at the moment they need
+// attention: code running while a CUDA graph is being captured on another stream of the same
+// context, hosts that hand the GPU a fixed memory budget at start-up and forbid later growth,
+// and real-time loops where an allocator call (which may synchronise the whole device) is not
+// acceptable.  For them the split-KV scratch of the decode kernel — the per-split (m, l, O)
+// partials and the per-KV-head arrival counters — lives in a fixed array inside the library
+// image.  Every GPU that loads the library carries these TFR_NOALLOC_SCRATCH_BYTES until exit.
+constexpr size_t TFR_NOALLOC_COUNTER_BYTES = 256;            // 64 KV heads
+constexpr size_t TFR_NOALLOC_SCRATCH_BYTES = 2u << 20;       // counters + partials, 2 MiB in total
+static __device__ __align__(256) unsigned char g_attn_noalloc_scratch[TFR_NOALLOC_SCRATCH_BYTES];
+constexpr int TFR_NOALLOC_MAX_DEVICES = 64;
+static unsigned char* g_attn_noalloc_ptr[TFR_NOALLOC_MAX_DEVICES] = {};  // device address of the array, per device
+
+extern "C" int tfr_op_attention_noalloc(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head,
+                                        int n_kv, int head_dim, int pos, void* stream) {
+    if (!q || !kc || !vc || !out || n_kv <= 0 || n_head % n_kv || n_head / n_kv > ATTN_REP_MAX || pos < 0) return TFR_E_INVALID;
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256) return TFR_E_UNSUPPORTED;
+    int dev = -1, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= TFR_NOALLOC_MAX_DEVICES) return TFR_E_CUDA;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return TFR_E_CUDA;
+    AttnArgs a{};
+    a.S = sms / n_kv;
+    if (a.S < 1) a.S = 1;
+    const size_t need = (size_t)n_head * a.S * (2 + head_dim) * sizeof(float);
+    if ((size_t)n_kv * sizeof(unsigned int) > TFR_NOALLOC_COUNTER_BYTES || need > TFR_NOALLOC_SCRATCH_BYTES - TFR_NOALLOC_COUNTER_BYTES) {
+        fprintf(stderr,
+                "tfr_op_attention_noalloc: %d heads / %d KV heads / head_dim %d need %zu bytes of split scratch; the built-in "
+                "array holds %zu\n",
+                n_head, n_kv, head_dim, need, TFR_NOALLOC_SCRATCH_BYTES - TFR_NOALLOC_COUNTER_BYTES);
+        return TFR_E_UNSUPPORTED;
+    }
+    // The array's name is only a host-side handle here; the kernel needs its address on THIS device.
+    // Looked up once per device, with that device current (it is: cudaGetDevice above).
+    if (!g_attn_noalloc_ptr[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_attn_noalloc_scratch) != cudaSuccess || !p) return TFR_E_CUDA;
+        g_attn_noalloc_ptr[dev] = (unsigned char*)p;
+    }
+    unsigned char* base = g_attn_noalloc_ptr[dev];
+    cudaStream_t s = (cudaStream_t)stream;
+    // the array keeps whatever the previous call left: the arrival counters must start at zero
+    if (cudaMemsetAsync(base, 0, TFR_NOALLOC_COUNTER_BYTES, s) != cudaSuccess) return TFR_E_CUDA;
+    a.q = q;
+    a.kc = kc;
+    a.vc = vc;
+    a.counters = reinterpret_cast<unsigned int*>(base);
+    a.partial = reinterpret_cast<float*>(base + TFR_NOALLOC_COUNTER_BYTES);
+    a.out = out;
+    a.n_head = n_head;
+    a.n_kv = n_kv;
+    a.min_keys = 32;
+    a.scale = 1.0f / sqrtf((float)head_dim);
+    a.pos = pos;
+    return check(launch_attention(s, a, head_dim, nullptr));
+}
+
 extern "C" int tfr_op_qkv_rope_store(const tfr_mat* wq, const tfr_mat* wk, const tfr_mat* wv, const float* bq, const float* bk,
                                      const float* bv, const float* x, const float* norm_w, float eps, float theta, int head_dim,
                                      int pos, float* q_out, uint16_t* kc, uint16_t* vc, void* stream) {

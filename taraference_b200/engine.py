@@ -241,6 +241,13 @@ def op_attention(q, kc, vc, out, n_head: int, n_kv: int, head_dim: int, pos: int
         "attention")
 
 
+def op_attention_noalloc(q, kc, vc, out, n_head: int, n_kv: int, head_dim: int, pos: int, stream: int = 0) -> None:
+    """op_attention for callers that may not allocate: the split scratch is a fixed array inside the library
+    (2 MiB, shared by all calls; larger shapes raise).  Call it once per device before any stream capture."""
+    _ok(_lib.lib().tfr_op_attention_noalloc(_ptr(q), _ptr(kc), _ptr(vc), _ptr(out), n_head, n_kv, head_dim, pos,
+                                            stream), "attention_noalloc: shape exceeds the built-in scratch or CUDA error")
+
+
 def op_qkv_rope_store(wq: GpuMat, wk: GpuMat, wv: GpuMat, bq, bk, bv, x, norm_w, eps: float, theta: float,
                       head_dim: int, pos: int, q_out, kc, vc, stream: int = 0) -> None:
     _ok(_lib.lib().tfr_op_qkv_rope_store(wq._h, wk._h, wv._h, _ptr(bq), _ptr(bk), _ptr(bv), _ptr(x), _ptr(norm_w),
