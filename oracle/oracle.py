@@ -32,9 +32,15 @@ class Mat(C.Structure):
                 ("data", C.c_void_p)]
 
 
+LAYER_DENSE, LAYER_LINEAR, LAYER_FULL_GATED = 0, 1, 2
+
+
 class Layer(C.Structure):
     _fields_ = [(n, Mat) for n in ("wq", "wk", "wv", "wo", "gate", "up", "down")] + \
-               [(n, C.c_void_p) for n in ("bq", "bk", "bv", "attn_norm", "ffn_norm")]
+               [(n, C.c_void_p) for n in ("bq", "bk", "bv", "attn_norm", "ffn_norm")] + \
+               [("kind", C.c_int32), ("pad_", C.c_int32)] + \
+               [(n, Mat) for n in ("wqkv", "wgate", "wbeta", "walpha", "ssm_out")] + \
+               [(n, C.c_void_p) for n in ("conv1d", "ssm_a", "ssm_dt", "ssm_norm", "q_norm", "k_norm")]
 
 
 class Model(C.Structure):
@@ -42,7 +48,8 @@ class Model(C.Structure):
                                          "n_vocab", "max_seq")] + \
                [("rope_theta", C.c_float), ("eps", C.c_float),
                 ("token_embd", Mat), ("output", Mat), ("output_norm", C.c_void_p),
-                ("layers", C.POINTER(Layer))]
+                ("layers", C.POINTER(Layer))] + \
+               [(n, C.c_int32) for n in ("rope_dim", "ssm_n_k", "ssm_n_v", "ssm_state", "conv_kernel", "pad_")]
 
 
 class Taps(C.Structure):
@@ -72,10 +79,13 @@ def lib():
         _lib.tfo_gemv.argtypes = [C.POINTER(Mat), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]
         _lib.tfo_ffn_gate_up.argtypes = [C.POINTER(Mat), C.POINTER(Mat), C.c_void_p, C.c_void_p]
         _lib.tfo_decode_token.argtypes = [C.POINTER(Model), C.c_void_p, C.c_void_p, C.c_int, C.c_int,
-                                          C.c_void_p, C.POINTER(Taps), C.c_int]
+                                          C.c_void_p, C.POINTER(Taps), C.c_int, C.c_void_p, C.c_void_p]
         _lib.tfo_decode_greedy.argtypes = [C.POINTER(Model), C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
-                                           C.c_void_p, C.c_void_p, C.c_void_p]
-        _lib.tfo_layer_forward.argtypes = [C.POINTER(Model), C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]
+                                           C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        _lib.tfo_layer_forward.argtypes = [C.POINTER(Model), C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                           C.c_void_p, C.c_void_p]
+        _lib.tfo_linear_attn_block.argtypes = [C.POINTER(Model), C.POINTER(Layer)] + [C.c_void_p] * 4
+        _lib.tfo_gated_attn_block.argtypes = [C.POINTER(Model), C.POINTER(Layer)] + [C.c_void_p] * 4 + [C.c_int]
         _lib.tfo_head_forward.argtypes = [C.POINTER(Model), C.c_void_p, C.c_void_p, C.c_void_p]
         _lib.tfo_embed.argtypes = [C.POINTER(Model), C.c_int, C.c_void_p]
         _lib.tfo_rms_norm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_float]
@@ -88,13 +98,15 @@ def lib():
         _lib.tfo_copy_kv_f16.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int]
         _lib.tfo_argmax.argtypes = [C.c_void_p, C.c_int]
         _lib.tfo_set_threads.argtypes = [C.c_int]
-        _gdn_bind(_lib)
     return _lib
 
 
-def _gdn_bind(l) -> None:
-    if hasattr(l, "tfo_gdn_step"):
-        l.tfo_gdn_step.argtypes = [C.c_void_p] * 11 + [C.c_int] * 4 + [C.c_float]
+def layer_kind(cfg: dict, i: int) -> int:
+    """config.rs:174-199: in the hybrid architecture layer i is a (gated) full-attention layer iff
+    (i + 1) % full_attention_interval == 0, every other layer a Gated-DeltaNet mixer."""
+    if cfg.get("arch") not in ("qwen35", "qwen3_5"):
+        return LAYER_DENSE
+    return LAYER_FULL_GATED if (i + 1) % cfg.get("full_attention_interval", 4) == 0 else LAYER_LINEAR
 
 
 def _p(a: np.ndarray) -> int:
@@ -205,8 +217,8 @@ def attention(q, kc: np.ndarray, vc: np.ndarray, n_head: int, n_kv: int, hd: int
 
 
 class OracleModel:
-    """Dense decoder held as raw GGUF tensors (dict name -> (ggml_type, K, N, uint8 array) for
-    matrices, name -> float32 array for vectors), with the names of cuda/load.rs:280-417."""
+    """Dense or hybrid decoder held as raw GGUF tensors (dict name -> (ggml_type, K, N, uint8 array)
+    for matrices, name -> float32 array for vectors), with the names of cuda/load.rs:280-417."""
 
     def __init__(self, cfg: dict, tensors: dict, max_seq: int):
         self.cfg, self.tensors, self.max_seq = cfg, tensors, max_seq
@@ -225,13 +237,23 @@ class OracleModel:
             self._keep.append(a)
             return _p(a)
 
+        self.kinds = [layer_kind(cfg, i) for i in range(L)]
         for i in range(L):
             p = f"blk.{i}."
             ly = self._layers[i]
-            ly.wq, ly.wk, ly.wv, ly.wo = (m(p + n + ".weight") for n in ("attn_q", "attn_k", "attn_v", "attn_output"))
+            ly.kind = self.kinds[i]
+            if ly.kind == LAYER_LINEAR:
+                ly.wqkv, ly.wgate, ly.wbeta, ly.walpha, ly.ssm_out = (
+                    m(p + n + ".weight") for n in ("attn_qkv", "attn_gate", "ssm_beta", "ssm_alpha", "ssm_out"))
+                ly.conv1d, ly.ssm_a, ly.ssm_dt, ly.ssm_norm = (
+                    v(p + n) for n in ("ssm_conv1d.weight", "ssm_a", "ssm_dt.bias", "ssm_norm.weight"))
+            else:
+                ly.wq, ly.wk, ly.wv, ly.wo = (m(p + n + ".weight") for n in ("attn_q", "attn_k", "attn_v", "attn_output"))
+                ly.bq, ly.bk, ly.bv = v(p + "attn_q.bias"), v(p + "attn_k.bias"), v(p + "attn_v.bias")
+                ly.q_norm, ly.k_norm = v(p + "attn_q_norm.weight"), v(p + "attn_k_norm.weight")
             ly.gate, ly.up, ly.down = (m(p + n + ".weight") for n in ("ffn_gate", "ffn_up", "ffn_down"))
-            ly.bq, ly.bk, ly.bv = v(p + "attn_q.bias"), v(p + "attn_k.bias"), v(p + "attn_v.bias")
-            ly.attn_norm, ly.ffn_norm = v(p + "attn_norm.weight"), v(p + "ffn_norm.weight")
+            ly.attn_norm = v(p + "attn_norm.weight")
+            ly.ffn_norm = v(p + "ffn_norm.weight") or v(p + "post_attention_norm.weight")
         self.m = Model()
         for k in ("n_layer", "n_embd", "n_head", "n_kv", "head_dim", "n_ff", "n_vocab"):
             setattr(self.m, k, cfg[k])
@@ -242,9 +264,26 @@ class OracleModel:
             self.m.output = m("output.weight")
         self.m.output_norm = v("output_norm.weight")
         self.m.layers = self._layers
+        self.hybrid = any(k != LAYER_DENSE for k in self.kinds)
+        if self.hybrid:
+            self.m.rope_dim = cfg.get("rope_dim", 0)
+            self.m.ssm_n_k, self.m.ssm_n_v = cfg["ssm_n_k"], cfg["ssm_n_v"]
+            self.m.ssm_state, self.m.conv_kernel = cfg["ssm_state"], cfg["conv_kernel"]
         kvn = cfg["n_kv"] * cfg["head_dim"]
         self.kc = np.zeros((L, max_seq, kvn), np.uint16)
         self.vc = np.zeros((L, max_seq, kvn), np.uint16)
+        # recurrent state of the linear layers (kv.rs:12-15): S[n_v][d][d] and the conv ring [kernel-1][channels]
+        d = cfg.get("ssm_state", 0)
+        ch = (2 * cfg.get("ssm_n_k", 0) + cfg.get("ssm_n_v", 0)) * d
+        self.ssm = np.zeros((L, max(1, cfg.get("ssm_n_v", 0) * d * d)), np.float32)
+        self.conv = np.zeros((L, max(1, (cfg.get("conv_kernel", 1) - 1) * ch)), np.float32)
+
+    def zero_recurrent(self) -> None:
+        self.ssm[:] = 0
+        self.conv[:] = 0
+
+    def _state(self):
+        return (_p(self.ssm), _p(self.conv)) if self.hybrid else (None, None)
 
     def decode_token(self, pos: int, token: int, act_f32: bool = False, want_taps: bool = False):
         logits = np.zeros(self.cfg["n_vocab"], np.float32)
@@ -253,7 +292,7 @@ class OracleModel:
         xn = np.zeros(self.cfg["n_embd"], np.float32)
         taps.x_final, taps.xn_final = _p(xf), _p(xn)
         rc = lib().tfo_decode_token(C.byref(self.m), _p(self.kc), _p(self.vc), pos, token, _p(logits),
-                                    C.byref(taps), int(act_f32))
+                                    C.byref(taps), int(act_f32), *self._state())
         assert rc == 0, rc
         return (logits, xf, xn) if want_taps else logits
 
@@ -265,7 +304,8 @@ class OracleModel:
     def layer_forward(self, li: int, x: np.ndarray, pos: int) -> np.ndarray:
         """One layer applied to a copy of the residual stream x at position pos (writes cache row pos)."""
         x = _f32(x).copy()
-        rc = lib().tfo_layer_forward(C.byref(self.m), li, _p(x), _p(self.kc[li]), _p(self.vc[li]), pos, 0)
+        st = (_p(self.ssm[li]), _p(self.conv[li])) if self.hybrid else (None, None)
+        rc = lib().tfo_layer_forward(C.byref(self.m), li, _p(x), _p(self.kc[li]), _p(self.vc[li]), pos, 0, *st)
         assert rc == 0, rc
         return x
 
@@ -280,6 +320,6 @@ class OracleModel:
         margins = np.zeros(n, np.float32)
         last = np.zeros(self.cfg["n_vocab"], np.float32)
         rc = lib().tfo_decode_greedy(C.byref(self.m), _p(self.kc), _p(self.vc), pos0, first, n, _p(toks),
-                                     _p(margins), _p(last))
+                                     _p(margins), _p(last), *self._state())
         assert rc == 0, rc
         return toks, margins, last

@@ -25,12 +25,9 @@
 #include <omp.h>
 #endif
 
-#define TFO_Q4_K 12 /* ggml type ids, crates/gguf/src/types.rs:7-60 */
-#define TFO_Q6_K 14
-#define TFO_Q4_K_BYTES 144
-#define TFO_Q6_K_BYTES 210
+#include "tfr_oracle.h"
 
-static int g_threads = 1;
+int g_threads = 1;
 
 void tfo_set_threads(int n) {
     g_threads = n < 1 ? 1 : n;
@@ -294,15 +291,7 @@ float tfo_dot_q4k_f32(const uint8_t* row, int nb, const float* x) {
 
 /* ---------------------------------------------------------------- GEMV ---------- */
 
-typedef struct {
-    int32_t type; /* TFO_Q4_K or TFO_Q6_K */
-    int32_t K;    /* input features, contiguous (GGUF dims[0]) */
-    int32_t N;    /* output rows (GGUF dims[1]) */
-    int32_t pad_;
-    const uint8_t* data; /* raw GGUF bytes, N rows of K/256 blocks */
-} tfo_mat;
-
-static size_t row_bytes(const tfo_mat* m) { return (size_t)(m->K / 256) * blk_bytes(m->type); }
+size_t tfo_row_bytes(const tfo_mat* m) { return (size_t)(m->K / 256) * blk_bytes(m->type); }
 
 /* y = W x (+bias) (+y).  act_mode 0: x is quantised to Q8 first (gemv.cu:377-403,
  * 469-490, 515-536, 2081-2115); act_mode 1: fp32 activation (gemv.cu:405-438, only
@@ -318,7 +307,7 @@ int tfo_gemv(const tfo_mat* w, const float* x, float* out, const float* bias, in
         d8 = (float*)malloc(sizeof(float) * (size_t)(K / 32));
         tfo_quantize_q8(x, K, q8, d8);
     }
-    size_t rb = row_bytes(w);
+    size_t rb = tfo_row_bytes(w);
 #pragma omp parallel for schedule(static) if (g_threads > 1)
     for (int j = 0; j < N; j++) {
         const uint8_t* row = w->data + (size_t)j * rb;
@@ -344,7 +333,7 @@ int tfo_ffn_gate_up(const tfo_mat* gate, const tfo_mat* up, const float* x, floa
     int8_t* q8 = (int8_t*)malloc((size_t)K);
     float* d8 = (float*)malloc(sizeof(float) * (size_t)(K / 32));
     tfo_quantize_q8(x, K, q8, d8);
-    size_t rb = row_bytes(gate);
+    size_t rb = tfo_row_bytes(gate);
 #pragma omp parallel for schedule(static) if (g_threads > 1)
     for (int j = 0; j < N; j++) {
         float g = tfo_dot_q4k_q8(gate->data + (size_t)j * rb, nb, q8, d8);
@@ -435,28 +424,6 @@ int tfo_argmax(const float* x, int n) {
 
 /* ---------------------------------------------------------------- dense model --- */
 
-typedef struct {
-    tfo_mat wq, wk, wv, wo, gate, up, down;
-    const float *bq, *bk, *bv;   /* may be NULL */
-    const float *attn_norm, *ffn_norm;
-} tfo_layer;
-
-typedef struct {
-    int32_t n_layer, n_embd, n_head, n_kv, head_dim, n_ff, n_vocab, max_seq;
-    float rope_theta, eps;
-    tfo_mat token_embd;
-    tfo_mat output; /* data == NULL: tied to token_embd */
-    const float* output_norm;
-    const tfo_layer* layers;
-} tfo_model;
-
-/* Optional taps of intermediate vectors of the LAST layer processed and of the head,
- * for stage-by-stage parity tests.  Any pointer may be NULL. */
-typedef struct {
-    float* x_final;  /* [n_embd] residual stream after the last layer */
-    float* xn_final; /* [n_embd] after output_norm */
-} tfo_taps;
-
 /* One decoder layer at n_tok = 1, applied in place to the residual stream x: layer
  * schedule of layer.rs:142-709 (attention block) and layer.rs:1210-1456 (dense FFN) with
  * the BASELINE dispatch: Q4_K matrices take Q8 activations, a Q6_K attn_v takes fp32
@@ -464,12 +431,17 @@ typedef struct {
  * [max_seq][n_kv*hd] f16 bits; row `pos` is written.
  * act_f32 != 0 restates the reference's PREFILL arithmetic instead (gemm.cu: every
  * projection is dequantise-then-fp32; ops.cu silu_mul), as forward.rs:54-65 fills a cache. */
-int tfo_layer_forward(const tfo_model* M, int li, float* x, uint16_t* kc, uint16_t* vc, int pos, int act_f32) {
+int tfo_layer_forward(const tfo_model* M, int li, float* x, uint16_t* kc, uint16_t* vc, int pos, int act_f32, float* ssm,
+                      float* conv) {
     int K = M->n_embd, H = M->n_head, Hkv = M->n_kv, hd = M->head_dim, FF = M->n_ff;
     if (li < 0 || li >= M->n_layer || pos < 0 || pos >= M->max_seq) return -1;
     int qn = H * hd, kvn = Hkv * hd;
     const tfo_layer* L = &M->layers[li];
-    float* xb = (float*)malloc(sizeof(float) * (size_t)(K > qn ? K : qn));
+    int mix = M->ssm_n_v * M->ssm_state; /* width of the linear mixer's output */
+    int wide = K > qn ? K : qn;
+    if (mix > wide) wide = mix;
+    float* xb = (float*)malloc(sizeof(float) * (size_t)wide);
+    float* y = (float*)malloc(sizeof(float) * (size_t)wide);
     float* q = (float*)malloc(sizeof(float) * (size_t)qn);
     float* kb = (float*)malloc(sizeof(float) * (size_t)kvn);
     float* vb = (float*)malloc(sizeof(float) * (size_t)kvn);
@@ -477,15 +449,25 @@ int tfo_layer_forward(const tfo_model* M, int li, float* x, uint16_t* kc, uint16
     float* u = (float*)malloc(sizeof(float) * (size_t)FF);
     int rc = 0;
     tfo_rms_norm(x, L->attn_norm, xb, K, M->eps);
-    rc |= tfo_gemv(&L->wq, xb, q, L->bq, 0, act_f32);
-    rc |= tfo_gemv(&L->wk, xb, kb, L->bk, 0, act_f32);
-    rc |= tfo_gemv(&L->wv, xb, vb, L->bv, 0, (act_f32 || L->wv.type == TFO_Q6_K) ? 1 : 0);
-    tfo_rope_neox(q, H, hd, pos, M->rope_theta);
-    tfo_rope_neox(kb, Hkv, hd, pos, M->rope_theta);
-    tfo_copy_kv_f16(kb, kc, pos, kvn);
-    tfo_copy_kv_f16(vb, vc, pos, kvn);
-    tfo_attention(q, kc, vc, xb, H, Hkv, hd, pos, 1.0f / sqrtf((float)hd));
-    rc |= tfo_gemv(&L->wo, xb, x, NULL, 2, act_f32);
+    if (L->kind == TFO_LAYER_LINEAR) {
+        /* layer.rs:711-1208 at n_tok = 1: mixer output projected onto the residual stream */
+        if (!ssm || !conv) rc = -1;
+        else rc |= tfo_linear_attn_block(M, L, xb, y, ssm, conv);
+        if (!rc) rc |= tfo_gemv(&L->ssm_out, y, x, NULL, 2, 0);
+    } else if (L->kind == TFO_LAYER_FULL_GATED) {
+        rc |= tfo_gated_attn_block(M, L, xb, y, kc, vc, pos);
+        rc |= tfo_gemv(&L->wo, y, x, NULL, 2, 0);
+    } else {
+        rc |= tfo_gemv(&L->wq, xb, q, L->bq, 0, act_f32);
+        rc |= tfo_gemv(&L->wk, xb, kb, L->bk, 0, act_f32);
+        rc |= tfo_gemv(&L->wv, xb, vb, L->bv, 0, (act_f32 || L->wv.type == TFO_Q6_K) ? 1 : 0);
+        tfo_rope_neox(q, H, hd, pos, M->rope_theta);
+        tfo_rope_neox(kb, Hkv, hd, pos, M->rope_theta);
+        tfo_copy_kv_f16(kb, kc, pos, kvn);
+        tfo_copy_kv_f16(vb, vc, pos, kvn);
+        tfo_attention(q, kc, vc, xb, H, Hkv, hd, pos, 1.0f / sqrtf((float)hd));
+        rc |= tfo_gemv(&L->wo, xb, x, NULL, 2, act_f32);
+    }
     tfo_rms_norm(x, L->ffn_norm, xb, K, M->eps);
     if (!act_f32) {
         rc |= tfo_ffn_gate_up(&L->gate, &L->up, xb, h);
@@ -495,8 +477,16 @@ int tfo_layer_forward(const tfo_model* M, int li, float* x, uint16_t* kc, uint16
         for (int j = 0; j < FF; j++) h[j] = (h[j] / (1.f + expf(-h[j]))) * u[j];
     }
     rc |= tfo_gemv(&L->down, h, x, NULL, 2, act_f32);
-    free(xb); free(q); free(kb); free(vb); free(h); free(u);
+    free(xb); free(y); free(q); free(kb); free(vb); free(h); free(u);
     return rc;
+}
+
+/* Sizes of the per-layer recurrent state (kv.rs:12-15, config.rs:305-316): fp32 S[n_v][d][d] and the
+ * conv ring [kernel-1][channels]. */
+size_t tfo_ssm_floats(const tfo_model* M) { return (size_t)M->ssm_n_v * M->ssm_state * M->ssm_state; }
+size_t tfo_conv_floats(const tfo_model* M) {
+    size_t ch = (size_t)(2 * M->ssm_n_k + M->ssm_n_v) * M->ssm_state;
+    return M->conv_kernel > 1 ? (size_t)(M->conv_kernel - 1) * ch : 0;
 }
 
 /* Vocabulary head, layer.rs:2125-2259: logits = E . Q8(RMSNorm(x, output_norm)). */
@@ -514,21 +504,23 @@ int tfo_head_forward(const tfo_model* M, const float* x, float* logits, float* x
 /* Embedding row of a token, kernels/embed.cu:71-131. */
 int tfo_embed(const tfo_model* M, int token, float* x) {
     if (token < 0 || token >= M->token_embd.N) return -1;
-    return tfo_dequant_row(M->token_embd.type, M->token_embd.data + (size_t)token * row_bytes(&M->token_embd),
+    return tfo_dequant_row(M->token_embd.type, M->token_embd.data + (size_t)token * tfo_row_bytes(&M->token_embd),
                            M->n_embd, x);
 }
 
 /* One batch-1 decode step (forward.rs:360-407 at n_tok = 1): embed, every layer, head.
  * kcache/vcache: [n_layer][max_seq][n_kv*hd] f16 bits. */
 int tfo_decode_token(const tfo_model* M, uint16_t* kcache, uint16_t* vcache, int pos, int token, float* logits,
-                     const tfo_taps* taps, int act_f32) {
+                     const tfo_taps* taps, int act_f32, float* ssm_all, float* conv_all) {
     int K = M->n_embd;
     if (pos < 0 || pos >= M->max_seq) return -1;
     float* x = (float*)malloc(sizeof(float) * (size_t)K);
     size_t lstride = (size_t)M->max_seq * M->n_kv * M->head_dim;
     int rc = tfo_embed(M, token, x);
     for (int li = 0; li < M->n_layer && rc == 0; li++)
-        rc = tfo_layer_forward(M, li, x, kcache + (size_t)li * lstride, vcache + (size_t)li * lstride, pos, act_f32);
+        rc = tfo_layer_forward(M, li, x, kcache + (size_t)li * lstride, vcache + (size_t)li * lstride, pos, act_f32,
+                               ssm_all ? ssm_all + (size_t)li * tfo_ssm_floats(M) : NULL,
+                               conv_all ? conv_all + (size_t)li * tfo_conv_floats(M) : NULL);
     if (rc == 0) {
         if (taps && taps->x_final) memcpy(taps->x_final, x, sizeof(float) * (size_t)K);
         if (logits) rc = tfo_head_forward(M, x, logits, taps ? taps->xn_final : NULL);
@@ -541,12 +533,12 @@ int tfo_decode_token(const tfo_model* M, uint16_t* kcache, uint16_t* vcache, int
  * `first` at position pos0, then each argmax; writes n tokens and, if margins != NULL,
  * the top-1 minus top-2 logit gap of every step (for margin-gated token comparison). */
 int tfo_decode_greedy(const tfo_model* M, uint16_t* kcache, uint16_t* vcache, int pos0, int first, int n,
-                      int32_t* out_tokens, float* margins, float* last_logits) {
+                      int32_t* out_tokens, float* margins, float* last_logits, float* ssm_all, float* conv_all) {
     int V = M->output.data ? M->output.N : M->token_embd.N;
     float* logits = (float*)malloc(sizeof(float) * (size_t)V);
     int tok = first, rc = 0;
     for (int s = 0; s < n && rc == 0; s++) {
-        rc = tfo_decode_token(M, kcache, vcache, pos0 + s, tok, logits, NULL, 0);
+        rc = tfo_decode_token(M, kcache, vcache, pos0 + s, tok, logits, NULL, 0, ssm_all, conv_all);
         if (rc) break;
         tok = tfo_argmax(logits, V);
         out_tokens[s] = tok;

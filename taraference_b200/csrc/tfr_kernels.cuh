@@ -359,6 +359,7 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
     }
     float scale = 1.f;
     if (has_norm) scale = rms_scale_staged(xs, K, pa.eps, red);
+    prof_mark(6);
     // quantise: straight from the registers that fetched the vector when it fits, else from the staged copy
     for (int k0 = 0; k0 < (K >> 2); k0 += GEMV_THREADS) {
         const int i4 = k0 + tid, kk = k0 / GEMV_THREADS;
@@ -385,6 +386,7 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
         }
         act_quantize4(act, x, i4, on, nb);
     }
+    prof_mark(7);
     epi.begin(st);
     __syncthreads();
     prof_mark(3);
