@@ -176,6 +176,29 @@ int tfr_op_qkv_rope_store(const tfr_mat* wq, const tfr_mat* wk, const tfr_mat* w
                           const float* bv, const float* x, const float* norm_w, float eps, float theta, int head_dim,
                           int pos, float* q_out, uint16_t* kc, uint16_t* vc, void* stream);
 
+/* Gated-DeltaNet decode step of one linear-attention layer, after the four input projections:
+ * gdn_conv_qkvl2_one_f32 + gdn_delta_gated_one_d128_f32 (kernels/deltanet.cu:561-728; layer.rs:838-885)
+ * in one launch.  proj = [qkv (2*n_k+n_v)*128 | z n_v*128 | beta n_v | alpha n_v] raw projections;
+ * conv_w [channels][kernel] as the GGUF stores it; state [n_v][128][128] is updated in place.
+ * conv_ring differs from the reference's shifted window [kernel-1][channels]: it is a ring of
+ * `kernel` slots of [channels]; the call reads the kernel-1 slots before `slot` (modulo kernel,
+ * oldest first) and stores the current input into `slot`.  Callers advance slot by one per token.
+ * state_size must be 128 and 2 <= kernel <= 4. */
+int tfr_op_gdn_step(const float* proj, const float* conv_w, float* conv_ring, float* state, const float* ssm_a,
+                    const float* ssm_dt, const float* norm_w, float* out, int n_k, int n_v, int state_size, int kernel,
+                    int slot, float eps, void* stream);
+/* Front end of a gated full-attention layer after the raw projections: split_q_gate_interleaved_f32,
+ * qk_rms_norm_partial_rope_neox_f32 on Q and K, copy_kv_f16 of K and V (kernels/deltanet.cu:144-235,
+ * kernels/ops.cu:471-486; layer.rs:386-600) in one launch.  raw = [n_head x (Q_h | G_h) | K | V];
+ * n_rot = rotated leading dims of every head (rope.dimension_count, or head_dim). */
+int tfr_op_qk_norm_rope_store(const float* raw, const float* q_norm, const float* k_norm, float* q_out, float* gate_out,
+                              uint16_t* kc, uint16_t* vc, int n_head, int n_kv, int head_dim, int n_rot, int pos,
+                              float theta, float eps, void* stream);
+/* tfr_op_attention with the sigmoid output gate of the hybrid's full-attention layers folded in:
+ * out = attention(q) * sigmoid(gate) (mul_sigmoid_f32, kernels/deltanet.cu:176-186). */
+int tfr_op_attention_gated(const float* q, const uint16_t* kc, const uint16_t* vc, const float* gate, float* out,
+                           int n_head, int n_kv, int head_dim, int pos, void* stream);
+
 /* Synthetic-model aid (no counterpart in the reference, which has no quantiser): quantise
  * fp32 rows [N][K] on the device into GGUF Q4_K / Q6_K bytes. */
 int tfr_synth_quantize(int ggml_type, const float* w, int64_t n_rows_k, int64_t n_cols_n, void* out_bytes, void* stream);

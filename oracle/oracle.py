@@ -86,6 +86,8 @@ def lib():
                                            C.c_void_p, C.c_void_p]
         _lib.tfo_linear_attn_block.argtypes = [C.POINTER(Model), C.POINTER(Layer)] + [C.c_void_p] * 4
         _lib.tfo_gated_attn_block.argtypes = [C.POINTER(Model), C.POINTER(Layer)] + [C.c_void_p] * 4 + [C.c_int]
+        _lib.tfo_gdn_step.argtypes = [C.c_void_p] * 11 + [C.c_int] * 4 + [C.c_float]
+        _lib.tfo_qk_norm_partial_rope.argtypes = [C.c_void_p, C.c_void_p] + [C.c_int] * 4 + [C.c_float, C.c_float]
         _lib.tfo_head_forward.argtypes = [C.POINTER(Model), C.c_void_p, C.c_void_p, C.c_void_p]
         _lib.tfo_embed.argtypes = [C.POINTER(Model), C.c_int, C.c_void_p]
         _lib.tfo_rms_norm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_float]
@@ -214,6 +216,27 @@ def attention(q, kc: np.ndarray, vc: np.ndarray, n_head: int, n_kv: int, hd: int
     out = np.zeros(n_head * hd, np.float32)
     lib().tfo_attention(_p(q), _p(kc), _p(vc), _p(out), n_head, n_kv, hd, pos, float(1.0 / np.sqrt(np.float32(hd))))
     return out
+
+
+def gdn_step(qkv, z, beta, alpha, conv_w, conv_state, ssm, ssm_a, ssm_dt, norm_w, nk: int, nv: int, d: int,
+             kernel: int, eps: float) -> np.ndarray:
+    """Gated-DeltaNet decode step after the projections; conv_state [kernel-1][channels] and
+    ssm [nv][d][d] (float32 arrays) are updated in place."""
+    args = [_f32(a) for a in (qkv, z, beta, alpha, conv_w)]
+    assert conv_state.dtype == np.float32 and ssm.dtype == np.float32
+    vecs = [_f32(a) for a in (ssm_a, ssm_dt, norm_w)]
+    y = np.zeros(nv * d, np.float32)
+    rc = lib().tfo_gdn_step(*[_p(a) for a in args], _p(conv_state), _p(ssm), *[_p(a) for a in vecs], _p(y), nk, nv, d,
+                            kernel, eps)
+    assert rc == 0
+    return y
+
+
+def qk_norm_partial_rope(x, w, n_heads: int, hd: int, n_rot: int, pos: int, theta: float, eps: float) -> np.ndarray:
+    x = _f32(x).copy()
+    w = _f32(w) if w is not None else None
+    lib().tfo_qk_norm_partial_rope(_p(x), _p(w) if w is not None else None, n_heads, hd, n_rot, pos, theta, eps)
+    return x
 
 
 class OracleModel:

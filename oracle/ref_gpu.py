@@ -137,7 +137,12 @@ def gemv_q8(m: RefMat, x, out=None, bias=None, use_res=0, warps=16):
     smem = m.K + (m.K // 32) * 4
     if m.type == Q4_K:
         if m.K >= 4096:
-            raise NotImplementedError("split-K Q4_K route not wired in the harness")
+            # split-K route, matmul.rs:199-289: grid (N, 4) x 64, then the reduce with bias / residual
+            partial = torch.zeros(4 * m.N, dtype=torch.float32, device="cuda")
+            kernels().launch("gemv_q4_k_global_splitk", (m.N, 4), (64,), 0, m.data, q, d, partial, m.K, m.N, m.col_bytes, 4)
+            kernels().launch("gemv_splitk_reduce", ((m.N + 255) // 256,), (256,), 0, partial, out, m.N, 4,
+                             int(bias is not None), b, use_res, x)
+            return out
         kernels().launch("gemv_q4_k_global", ((m.N + warps - 1) // warps,), (warps * 32,), smem, m.data, q, d, out,
                          m.K, m.N, m.col_bytes, int(bias is not None), b, use_res, x)
     elif m.K >= 4096:
@@ -224,11 +229,54 @@ def embed(table: RefMat, token: int):
     return out
 
 
-# ------------------------------------------------------------------ whole dense model
+# ------------------------------------------------------------------ hybrid-layer kernels
+
+def gdn_conv_qkvl2(qkv, conv_w, conv_state, n_k, n_v, d, kernel, eps):
+    """layer.rs:845-862: grid n_k x 128 (deltanet.cu:561-622); conv_state [kernel-1][channels] is updated."""
+    q = torch.zeros(n_k * d, dtype=torch.float32, device="cuda")
+    k = torch.zeros(n_k * d, dtype=torch.float32, device="cuda")
+    v = torch.zeros(n_v * d, dtype=torch.float32, device="cuda")
+    kernels().launch("gdn_conv_qkvl2_one_f32", (n_k,), (128,), 0, qkv, conv_w, conv_state, q, k, v, n_k, n_v, d, kernel,
+                     float(eps))
+    return q, k, v
+
+
+def gdn_delta_gated_d128(q, k, v, alpha, beta, dt, a, state, norm_w, z, n_k, n_v, eps):
+    """layer.rs:863-885: grid n_v x 128 (deltanet.cu:628-728); state [n_v][128][128] is updated."""
+    out = torch.zeros(n_v * 128, dtype=torch.float32, device="cuda")
+    kernels().launch("gdn_delta_gated_one_d128_f32", (n_v,), (128,), 0, q, k, v, alpha, beta, dt, a, state, norm_w, z, out,
+                     n_k, n_v, float(eps))
+    return out
+
+
+def split_q_gate(qg, n_head, hd):
+    """layer.rs:386-410: grid (n_head, 1) x 128, interleaved mode (deltanet.cu:144-173)."""
+    q = torch.zeros(n_head * hd, dtype=torch.float32, device="cuda")
+    g = torch.zeros(n_head * hd, dtype=torch.float32, device="cuda")
+    kernels().launch("split_q_gate_interleaved_f32", (n_head, 1), (128,), 0, qg, q, g, n_head, hd, 1, 0)
+    return q, g
+
+
+def qk_norm_partial_rope(x, w, n_heads, hd, n_rot, pos, theta, eps):
+    """layer.rs:430-505: grid (heads, 1) x 128, in place (deltanet.cu:189-235)."""
+    kernels().launch("qk_rms_norm_partial_rope_neox_f32", (n_heads, 1), (128,), 0, x, w, n_heads, hd, n_rot, pos, 1,
+                     float(theta), float(eps))
+    return x
+
+
+def mul_sigmoid(x, gate):
+    """layer.rs:646-659 (deltanet.cu:176-186)."""
+    n = x.numel()
+    kernels().launch("mul_sigmoid_f32", ((n + 1023) // 1024,), (1024,), 0, x, gate, n)
+    return x
+
+
+# ------------------------------------------------------------------ whole model
 
 class RefModel:
-    """The reference's n_tok = 1 schedule (layer.rs:142-709, 1210-1456, 2125-2259) assembled
-    from its own kernels, for the BASELINE dense mix at K < 4096."""
+    """The reference's n_tok = 1 schedule (layer.rs:142-709, 711-1208, 1210-1456, 2125-2259)
+    assembled from its own kernels, for the Q4_K / Q6_K mix of the benchmark configurations,
+    dense or hybrid."""
 
     def __init__(self, cfg: dict, tensors: dict, max_seq: int, alt_ffn: bool = False):
         """alt_ffn: use the reference's other FFN kernel (gemv_q4_k_ffn_8way).  Both are the
@@ -248,13 +296,29 @@ class RefModel:
         self.head = m("output.weight") if "output.weight" in tensors else self.embd
         self.out_norm = v("output_norm.weight")
         self.layers = []
+        self.hybrid = cfg.get("arch") in ("qwen35", "qwen3_5")
+        iv = cfg.get("full_attention_interval", 4)
         for i in range(L):
             p = f"blk.{i}."
-            self.layers.append(dict(
-                wq=m(p + "attn_q.weight"), wk=m(p + "attn_k.weight"), wv=m(p + "attn_v.weight"),
-                wo=m(p + "attn_output.weight"), gate=m(p + "ffn_gate.weight"), up=m(p + "ffn_up.weight"),
-                down=m(p + "ffn_down.weight"), bq=v(p + "attn_q.bias"), bk=v(p + "attn_k.bias"),
-                bv=v(p + "attn_v.bias"), an=v(p + "attn_norm.weight"), fn=v(p + "ffn_norm.weight")))
+            ly = dict(gate=m(p + "ffn_gate.weight"), up=m(p + "ffn_up.weight"), down=m(p + "ffn_down.weight"),
+                      an=v(p + "attn_norm.weight"), fn=v(p + "ffn_norm.weight"), kind="dense")
+            if self.hybrid and (i + 1) % iv != 0:
+                ly.update(kind="linear", wqkv=m(p + "attn_qkv.weight"), wgate=m(p + "attn_gate.weight"),
+                          wbeta=m(p + "ssm_beta.weight"), walpha=m(p + "ssm_alpha.weight"), ssm_out=m(p + "ssm_out.weight"),
+                          conv=v(p + "ssm_conv1d.weight"), a=v(p + "ssm_a"), dt=v(p + "ssm_dt.bias"),
+                          norm=v(p + "ssm_norm.weight"))
+            else:
+                ly.update(wq=m(p + "attn_q.weight"), wk=m(p + "attn_k.weight"), wv=m(p + "attn_v.weight"),
+                          wo=m(p + "attn_output.weight"), bq=v(p + "attn_q.bias"), bk=v(p + "attn_k.bias"),
+                          bv=v(p + "attn_v.bias"))
+                if self.hybrid:
+                    ly.update(kind="gated", qn=v(p + "attn_q_norm.weight"), kn=v(p + "attn_k_norm.weight"))
+            self.layers.append(ly)
+        if self.hybrid:
+            d, nk, nv = cfg["ssm_state"], cfg["ssm_n_k"], cfg["ssm_n_v"]
+            ch = (2 * nk + nv) * d
+            self.ssm = [torch.zeros(nv * d * d, dtype=torch.float32, device="cuda") for _ in range(L)]
+            self.conv = [torch.zeros((cfg["conv_kernel"] - 1) * ch, dtype=torch.float32, device="cuda") for _ in range(L)]
         kvn = cfg["n_kv"] * cfg["head_dim"]
         self.kc = [torch.zeros(max_seq * kvn, dtype=torch.int16, device="cuda") for _ in range(L)]
         self.vc = [torch.zeros(max_seq * kvn, dtype=torch.int16, device="cuda") for _ in range(L)]
@@ -266,17 +330,34 @@ class RefModel:
         kvn = Hkv * hd
         L = self.layers[li]
         xb = rms_norm(x, L["an"], c["eps"])
-        q, k = gemv_q4_pair(L["wq"], L["wk"], xb, L["bq"], L["bk"])
-        if L["wv"].type == Q6_K:
-            v = gemv_q6_f32(L["wv"], xb, L["bv"])
+        if L["kind"] == "linear":
+            d, nk, nv = c["ssm_state"], c["ssm_n_k"], c["ssm_n_v"]
+            qkv, z = gemv_q8(L["wqkv"], xb), gemv_q8(L["wgate"], xb)
+            beta, alpha = gemv_q8(L["wbeta"], xb), gemv_q8(L["walpha"], xb)
+            gq, gk, gv = gdn_conv_qkvl2(qkv, L["conv"], self.conv[li], nk, nv, d, c["conv_kernel"], c["eps"])
+            att = gdn_delta_gated_d128(gq, gk, gv, alpha, beta, L["dt"], L["a"], self.ssm[li], L["norm"], z, nk, nv, c["eps"])
+            q = gq
+            gemv_q8(L["ssm_out"], att, out=x, use_res=2)
         else:
-            v = gemv_q8(L["wv"], xb, bias=L["bv"])
-        rope(q, H, hd, pos, c["rope_theta"])
-        rope(k, Hkv, hd, pos, c["rope_theta"])
-        copy_kv(k, self.kc[li], pos, kvn)
-        copy_kv(v, self.vc[li], pos, kvn)
-        att = attention(q, self.kc[li], self.vc[li], H, Hkv, hd, pos)
-        gemv_q8(L["wo"], att, out=x, use_res=2)
+            q, k = gemv_q4_pair(L["wq"], L["wk"], xb, L["bq"], L["bk"])
+            if L["wv"].type == Q6_K:
+                v = gemv_q6_f32(L["wv"], xb, L["bv"])
+            else:
+                v = gemv_q8(L["wv"], xb, bias=L["bv"])
+            if L["kind"] == "gated":
+                n_rot = c["rope_dim"] if 0 < c.get("rope_dim", 0) < hd else hd
+                q, g = split_q_gate(q, H, hd)
+                qk_norm_partial_rope(q, L["qn"], H, hd, n_rot, pos, c["rope_theta"], c["eps"])
+                qk_norm_partial_rope(k, L["kn"], Hkv, hd, n_rot, pos, c["rope_theta"], c["eps"])
+            else:
+                rope(q, H, hd, pos, c["rope_theta"])
+                rope(k, Hkv, hd, pos, c["rope_theta"])
+            copy_kv(k, self.kc[li], pos, kvn)
+            copy_kv(v, self.vc[li], pos, kvn)
+            att = attention(q, self.kc[li], self.vc[li], H, Hkv, hd, pos)
+            if L["kind"] == "gated":
+                mul_sigmoid(att, g)
+            gemv_q8(L["wo"], att, out=x, use_res=2)
         xb = rms_norm(x, L["fn"], c["eps"])
         h = (ffn_gate_up_8way if self.alt_ffn else ffn_gate_up)(L["gate"], L["up"], xb)
         gemv_q8(L["down"], h, out=x, use_res=2)

@@ -61,6 +61,10 @@ void tfo_copy_kv_f16(const float* src, uint16_t* cache, int pos, int stride);
 void tfo_attention(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv, int hd, int pos,
                    float scale);
 /* tfr_oracle_gdn.c */
+int tfo_gdn_step(const float* qkv, const float* z, const float* beta, const float* alpha, const float* conv_w,
+                 float* conv_state, float* ssm, const float* ssm_a, const float* ssm_dt, const float* norm_w, float* y, int nk,
+                 int nv, int d, int kernel, float eps);
+void tfo_qk_norm_partial_rope(float* x, const float* w, int n_heads, int hd, int n_rot, int pos, float theta, float eps);
 int tfo_linear_attn_block(const tfo_model* M, const tfo_layer* L, const float* xb, float* y, float* ssm, float* conv);
 int tfo_gated_attn_block(const tfo_model* M, const tfo_layer* L, const float* xb, float* out, uint16_t* kc, uint16_t* vc, int pos);
 #endif

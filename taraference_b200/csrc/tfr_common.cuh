@@ -128,7 +128,7 @@ struct TokenState {
     int prompt_left;               // prompt tokens still to be fed (prefill by decode steps)
     int prompt_idx;
     int max_seq;                   // KV capacity; reaching it sets done
-    int pad_;
+    int ring_off;                  // conv-history ring: slot of the current input = (pos + ring_off) % kernel
 };
 
 // Orderable 64-bit key: larger logit wins; on equal logits the lower index wins.

@@ -15,6 +15,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -36,10 +37,26 @@ struct tfr_mat {
     int perm_hd = 0;
 };
 
+// Layer kinds of crates/core/src/config.rs (LayerKind) with the hybrid's gated variant of full attention.
+enum { LAYER_DENSE = 0, LAYER_LINEAR = 1, LAYER_FULL_GATED = 2 };
+
 struct LayerW {
+    int kind = LAYER_DENSE;
     tfr_mat *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *gate = nullptr, *up = nullptr, *down = nullptr;
     float* bias_qkv = nullptr;  // vrow order, or nullptr
     float *attn_norm = nullptr, *ffn_norm = nullptr;
+    // linear (Gated-DeltaNet) layers: the four input projections stacked into one matrix
+    tfr_mat *gdn_proj = nullptr, *ssm_out = nullptr;
+    float *conv_w = nullptr, *ssm_a = nullptr, *ssm_dt = nullptr, *ssm_norm = nullptr;
+    // gated full-attention layers
+    float *q_norm = nullptr, *k_norm = nullptr;
+};
+
+// Raw GGUF bytes of a matrix kept on the host until tfr_finalize_load stacks it with its siblings.
+struct HostRaw {
+    int type = 0;
+    int64_t K = 0, N = 0;
+    std::vector<uint8_t> bytes;
 };
 
 struct VecT {
@@ -59,11 +76,13 @@ struct tfr_engine {
     bool has_cfg = false, finalized = false;
     std::map<std::string, tfr_mat*> mats;
     std::map<std::string, VecT> vecs;
+    std::map<std::string, HostRaw> held;
     std::vector<LayerW> layers;
     tfr_mat *token_embd = nullptr, *head = nullptr;
     float* output_norm = nullptr;
     // workspaces
     float *x = nullptr, *q = nullptr, *attn = nullptr, *h = nullptr, *logits = nullptr, *partial = nullptr;
+    float *proj = nullptr, *qgate = nullptr;  // hybrid: raw projections; sigmoid gate of the attention output
     unsigned int* counters = nullptr;
     TokenState* st = nullptr;
     TokenState* st_host = nullptr;  // pinned
@@ -86,7 +105,21 @@ struct tfr_kv {
     unsigned short *k = nullptr, *v = nullptr;
     int len = 0, max_seq = 0;
     size_t layer_stride = 0;  // elements
+    // hybrid models (kv.rs:12-15): per layer the fp32 state S[n_v][128][128] and the conv history,
+    // held as a ring of `kernel` slots of [channels] (see tfr_gdn.cuh)
+    float *ssm = nullptr, *conv = nullptr;
+    size_t ssm_stride = 0, conv_stride = 0;  // floats per layer
+    long long rec_steps = 0;                 // tokens the recurrent state has absorbed
 };
+
+static bool is_hybrid(const tfr_engine* e) { return e->cfg.hybrid != 0; }
+static int gdn_channels(const tfr_model_config& c) { return (2 * c.ssm_group_count + c.ssm_time_step_rank) * c.ssm_state_size; }
+static int gdn_val_dim(const tfr_model_config& c) { return c.ssm_time_step_rank * c.ssm_state_size; }
+static int layer_kind(const tfr_model_config& c, int i) {
+    if (!c.hybrid) return LAYER_DENSE;
+    const int iv = c.full_attention_interval > 0 ? c.full_attention_interval : 4;  // config.rs:186-199
+    return (i + 1) % iv == 0 ? LAYER_FULL_GATED : LAYER_LINEAR;
+}
 
 static int fail(tfr_engine* e, int code, const char* fmt, ...) {
     char buf[512];
@@ -134,6 +167,8 @@ static void configure_kernels_once() {
     configure_kernel(k_attn_decode<64>, false);
     configure_kernel(k_attn_decode<128>, false);
     configure_kernel(k_attn_decode<256>, false);
+    configure_kernel(k_gdn_step, false);
+    configure_kernel(k_qk_norm_rope_store, false);
     configure_kernel(k_state_begin, false);
     configure_kernel(k_state_next_prompt, false);
 }
@@ -236,7 +271,7 @@ extern "C" void tfr_destroy(tfr_engine* e) {
     for (auto& kv : e->vecs) cudaFree(kv.second.dev);
     for (auto& L : e->layers) cudaFree(L.bias_qkv);
     void* ws[] = {e->x, e->q, e->attn, e->h, e->logits, e->partial, e->counters, e->st, e->out_tokens, e->prompt,
-                  e->layer_taps};
+                  e->layer_taps, e->proj, e->qgate};
     for (void* p : ws) cudaFree(p);
     if (e->st_host) cudaFreeHost(e->st_host);
     if (e->out_host) cudaFreeHost(e->out_host);
@@ -269,7 +304,16 @@ extern "C" int tfr_set_config(tfr_engine* e, const tfr_model_config* c) {
         return fail(e, TFR_E_UNSUPPORTED, "head_dim %d (supported: 64, 128, 256)", c->head_dim);
     if (c->n_head / c->n_kv_head > ATTN_REP_MAX)
         return fail(e, TFR_E_UNSUPPORTED, "more than %d query heads per KV head", ATTN_REP_MAX);
-    if (c->hybrid) return fail(e, TFR_E_UNSUPPORTED, "hybrid (Gated-DeltaNet) models are not built yet");
+    if (c->hybrid) {
+        if (c->ssm_state_size != GDN_D)
+            return fail(e, TFR_E_UNSUPPORTED, "ssm.state_size %d (supported: %d)", c->ssm_state_size, GDN_D);
+        if (c->ssm_conv_kernel < 2 || c->ssm_conv_kernel > GDN_MAX_KERNEL)
+            return fail(e, TFR_E_UNSUPPORTED, "ssm.conv_kernel %d (supported: 2..%d)", c->ssm_conv_kernel, GDN_MAX_KERNEL);
+        if (c->ssm_group_count <= 0 || c->ssm_time_step_rank <= 0) return fail(e, TFR_E_INVALID, "bad ssm head counts");
+        if (c->ssm_inner_size && c->ssm_inner_size != c->ssm_time_step_rank * c->ssm_state_size)
+            return fail(e, TFR_E_UNSUPPORTED, "ssm.inner_size %d != time_step_rank * state_size", c->ssm_inner_size);
+        if (c->rope_dim < 0 || c->rope_dim > c->head_dim || c->rope_dim % 2) return fail(e, TFR_E_INVALID, "bad rope.dimension_count");
+    }
     if (c->tp_size > 1) return fail(e, TFR_E_UNSUPPORTED, "tensor parallelism is not built yet");
     e->cfg = *c;
     if (e->cfg.tp_size < 1) e->cfg.tp_size = 1;
@@ -302,7 +346,23 @@ extern "C" int tfr_upload_tensor(tfr_engine* e, const char* name, int type, int6
         return TFR_OK;
     }
     // F32/F16 matrices are rejected like load.rs:15-28
-    int perm = (ends_with(nm, "attn_q.weight") || ends_with(nm, "attn_k.weight")) ? e->cfg.head_dim : 0;
+    if (is_hybrid(e) && (ends_with(nm, "attn_qkv.weight") || ends_with(nm, "attn_gate.weight") ||
+                         ends_with(nm, "ssm_beta.weight") || ends_with(nm, "ssm_alpha.weight"))) {
+        // the four input projections of a linear layer become one matrix at finalize
+        if (type != TFR_Q4_K && type != TFR_Q6_K) return fail(e, TFR_E_UNSUPPORTED, "matrix type %d not supported", type);
+        if (n_rows <= 0 || n_cols <= 0 || n_rows % 256 || nbytes != raw_bytes(type, n_rows, n_cols))
+            return fail(e, TFR_E_INVALID, "tensor %s: bad shape or byte size", name);
+        if (e->held.count(nm)) return fail(e, TFR_E_INVALID, "tensor %s uploaded twice", name);
+        HostRaw& h = e->held[nm];
+        h.type = type;
+        h.K = n_rows;
+        h.N = n_cols;
+        h.bytes.resize(nbytes);
+        CU(e, cudaMemcpy(h.bytes.data(), bytes, nbytes, cudaMemcpyDefault));  // the source may be device memory
+        return TFR_OK;
+    }
+    // dense layers pair the RoPE partners of Q and K at upload; the hybrid's Q/K are normalised per head first
+    int perm = (!is_hybrid(e) && (ends_with(nm, "attn_q.weight") || ends_with(nm, "attn_k.weight"))) ? e->cfg.head_dim : 0;
     tfr_mat* m = nullptr;
     int rc = mat_create_impl(e, type, n_rows, n_cols, bytes, nbytes, perm, e->stream, &m);
     if (rc) return rc;
@@ -335,6 +395,41 @@ static float* need_vec(tfr_engine* e, const std::string& n, int len, bool option
     return it->second.dev;
 }
 
+// Stacks attn_qkv, attn_gate, ssm_beta and ssm_alpha of a linear layer (layer.rs:736-798 runs four
+// GEMVs on the same activation) into one row-concatenated matrix [qkv | z | beta | alpha].
+static int finalize_linear_layer(tfr_engine* e, int i, LayerW& L) {
+    const tfr_model_config& c = e->cfg;
+    const int K = c.n_embd, ch = gdn_channels(c), vd = gdn_val_dim(c), nv = c.ssm_time_step_rank;
+    const std::string p = "blk." + std::to_string(i) + ".";
+    const char* names[4] = {"attn_qkv.weight", "attn_gate.weight", "ssm_beta.weight", "ssm_alpha.weight"};
+    const int rows[4] = {ch, vd, nv, nv};
+    std::vector<uint8_t> all;
+    int type = 0;
+    for (int k = 0; k < 4; k++) {
+        auto it = e->held.find(p + names[k]);
+        if (it == e->held.end()) return fail(e, TFR_E_INVALID, "missing tensor %s%s", p.c_str(), names[k]);
+        const HostRaw& h = it->second;
+        if (h.K != K || h.N != rows[k])
+            return fail(e, TFR_E_INVALID, "tensor %s%s is %lldx%lld, expected %dx%d", p.c_str(), names[k], (long long)h.K,
+                        (long long)h.N, K, rows[k]);
+        if (k == 0) type = h.type;
+        if (h.type != type) return fail(e, TFR_E_UNSUPPORTED, "layer %d: the four linear-attention projections must share one type", i);
+        all.insert(all.end(), h.bytes.begin(), h.bytes.end());
+    }
+    const int total = ch + vd + 2 * nv;
+    tfr_mat* m = nullptr;
+    int rc = mat_create_impl(e, type, K, total, all.data(), all.size(), 0, e->stream, &m);
+    if (rc) return rc;
+    e->mats[p + "gdn_proj"] = m;
+    L.gdn_proj = m;
+    L.ssm_out = need_mat(e, p + "ssm_out.weight", vd, K, rc);
+    L.conv_w = need_vec(e, p + "ssm_conv1d.weight", c.ssm_conv_kernel * ch, false, rc);
+    L.ssm_a = need_vec(e, p + "ssm_a", nv, false, rc);
+    L.ssm_dt = need_vec(e, p + "ssm_dt.bias", nv, false, rc);
+    L.ssm_norm = need_vec(e, p + "ssm_norm.weight", c.ssm_state_size, false, rc);
+    return rc;
+}
+
 extern "C" int tfr_finalize_load(tfr_engine* e) {
     if (!e || !e->has_cfg) return TFR_E_INVALID;
     if (e->finalized) return TFR_OK;
@@ -351,10 +446,7 @@ extern "C" int tfr_finalize_load(tfr_engine* e) {
     for (int i = 0; i < c.n_layer; i++) {
         const std::string p = "blk." + std::to_string(i) + ".";
         LayerW& L = e->layers[i];
-        L.wq = need_mat(e, p + "attn_q.weight", K, nq, rc);
-        L.wk = need_mat(e, p + "attn_k.weight", K, nkv, rc);
-        L.wv = need_mat(e, p + "attn_v.weight", K, nkv, rc);
-        L.wo = need_mat(e, p + "attn_output.weight", nq, K, rc);
+        L.kind = layer_kind(c, i);
         L.gate = need_mat(e, p + "ffn_gate.weight", K, FF, rc);
         L.up = need_mat(e, p + "ffn_up.weight", K, FF, rc);
         L.down = need_mat(e, p + "ffn_down.weight", FF, K, rc);
@@ -362,31 +454,56 @@ extern "C" int tfr_finalize_load(tfr_engine* e) {
         L.ffn_norm = need_vec(e, p + "ffn_norm.weight", K, true, rc);
         if (!L.ffn_norm && !rc) L.ffn_norm = need_vec(e, p + "post_attention_norm.weight", K, false, rc);  // load.rs:280-417
         if (rc) return rc;
-        if (L.wq->m.type != TFR_Q4_K || L.wk->m.type != TFR_Q4_K)
-            return fail(e, TFR_E_UNSUPPORTED, "layer %d: attn_q / attn_k must be Q4_K", i);
         if (L.gate->m.type != TFR_Q4_K || L.up->m.type != TFR_Q4_K)
             return fail(e, TFR_E_UNSUPPORTED, "layer %d: ffn_gate / ffn_up must be Q4_K", i);
-        float* bq = need_vec(e, p + "attn_q.bias", nq, true, rc);
+        if (L.kind == LAYER_LINEAR) {
+            rc = finalize_linear_layer(e, i, L);
+            if (rc) return rc;
+            continue;
+        }
+        const int nq_rows = L.kind == LAYER_FULL_GATED ? 2 * nq : nq;  // fused Q|gate, deltanet.cu:144-173
+        L.wq = need_mat(e, p + "attn_q.weight", K, nq_rows, rc);
+        L.wk = need_mat(e, p + "attn_k.weight", K, nkv, rc);
+        L.wv = need_mat(e, p + "attn_v.weight", K, nkv, rc);
+        L.wo = need_mat(e, p + "attn_output.weight", nq, K, rc);
+        if (rc) return rc;
+        if (L.wq->m.type != TFR_Q4_K || L.wk->m.type != TFR_Q4_K)
+            return fail(e, TFR_E_UNSUPPORTED, "layer %d: attn_q / attn_k must be Q4_K", i);
+        if (L.wv->m.type != TFR_Q6_K) return fail(e, TFR_E_UNSUPPORTED, "layer %d: attn_v must be Q6_K", i);
+        float* bq = need_vec(e, p + "attn_q.bias", nq_rows, true, rc);
         float* bk = need_vec(e, p + "attn_k.bias", nkv, true, rc);
         float* bv = need_vec(e, p + "attn_v.bias", nkv, true, rc);
         if (rc) return rc;
+        if (L.kind == LAYER_FULL_GATED) {
+            L.q_norm = need_vec(e, p + "attn_q_norm.weight", hd, true, rc);
+            L.k_norm = need_vec(e, p + "attn_k_norm.weight", hd, true, rc);
+            if (rc) return rc;
+            if (!L.q_norm || !L.k_norm) return fail(e, TFR_E_UNSUPPORTED, "layer %d: attn_q_norm / attn_k_norm are required", i);
+        }
         if (bq || bk || bv) {
-            const int tot = nq + 2 * nkv;
+            const int tot = nq_rows + 2 * nkv, perm = L.kind == LAYER_DENSE ? hd : 0;
             CU(e, cudaMalloc(&L.bias_qkv, (size_t)tot * 4));
             CU(e, cudaMemsetAsync(L.bias_qkv, 0, (size_t)tot * 4, e->stream));
-            if (bq) k_permute_f32<<<(nq + 255) / 256, 256, 0, e->stream>>>(bq, L.bias_qkv, nq, hd);
-            if (bk) k_permute_f32<<<(nkv + 255) / 256, 256, 0, e->stream>>>(bk, L.bias_qkv + nq, nkv, hd);
-            if (bv) k_permute_f32<<<(nkv + 255) / 256, 256, 0, e->stream>>>(bv, L.bias_qkv + nq + nkv, nkv, 0);
+            if (bq) k_permute_f32<<<(nq_rows + 255) / 256, 256, 0, e->stream>>>(bq, L.bias_qkv, nq_rows, perm);
+            if (bk) k_permute_f32<<<(nkv + 255) / 256, 256, 0, e->stream>>>(bk, L.bias_qkv + nq_rows, nkv, perm);
+            if (bv) k_permute_f32<<<(nkv + 255) / 256, 256, 0, e->stream>>>(bv, L.bias_qkv + nq_rows + nkv, nkv, 0);
             CU(e, cudaGetLastError());
         }
     }
+    e->held.clear();
     // workspaces (load.rs:547-607: everything allocated once)
     const int sms = e->prop.multiProcessorCount;
     e->attn_S = sms / c.n_kv_head;
     if (e->attn_S < 1) e->attn_S = 1;
     CU(e, cudaMalloc(&e->x, (size_t)K * 4));
+    const int vd = c.hybrid ? gdn_val_dim(c) : 0;
     CU(e, cudaMalloc(&e->q, (size_t)nq * 4));
-    CU(e, cudaMalloc(&e->attn, (size_t)nq * 4));
+    CU(e, cudaMalloc(&e->attn, (size_t)(nq > vd ? nq : vd) * 4));  // attention output, or the mixer output of a linear layer
+    if (c.hybrid) {
+        const int lin = gdn_channels(c) + vd + 2 * c.ssm_time_step_rank, full = 2 * nq + 2 * nkv;
+        CU(e, cudaMalloc(&e->proj, (size_t)(lin > full ? lin : full) * 4));
+        CU(e, cudaMalloc(&e->qgate, (size_t)nq * 4));
+    }
     CU(e, cudaMalloc(&e->h, (size_t)FF * 4));
     CU(e, cudaMalloc(&e->logits, (size_t)V * 4));
     CU(e, cudaMalloc(&e->partial, (size_t)c.n_head * e->attn_S * (2 + hd) * 4));
@@ -424,6 +541,19 @@ extern "C" int tfr_alloc_kv(tfr_engine* e, int max_seq, tfr_kv** out) {
     }
     cudaMemsetAsync(kv->k, 0, bytes, e->stream);
     cudaMemsetAsync(kv->v, 0, bytes, e->stream);
+    if (is_hybrid(e)) {
+        const tfr_model_config& c = e->cfg;
+        kv->ssm_stride = (size_t)c.ssm_time_step_rank * GDN_D * GDN_D;
+        kv->conv_stride = (size_t)c.ssm_conv_kernel * gdn_channels(c);
+        const size_t sb = kv->ssm_stride * c.n_layer * 4, cb = kv->conv_stride * c.n_layer * 4;
+        if (cudaMalloc(&kv->ssm, sb) != cudaSuccess || cudaMalloc(&kv->conv, cb) != cudaSuccess) {
+            cudaGetLastError();
+            tfr_free_kv(kv);
+            return fail(e, TFR_E_CUDA, "alloc_kv: out of device memory for the recurrent state (%zu bytes)", sb + cb);
+        }
+        cudaMemsetAsync(kv->ssm, 0, sb, e->stream);
+        cudaMemsetAsync(kv->conv, 0, cb, e->stream);
+    }
     cudaStreamSynchronize(e->stream);
     *out = kv;
     return TFR_OK;
@@ -433,6 +563,8 @@ extern "C" void tfr_free_kv(tfr_kv* kv) {
     if (kv->e && kv->e->graph_kv == kv) drop_graphs(kv->e);
     cudaFree(kv->k);
     cudaFree(kv->v);
+    cudaFree(kv->ssm);
+    cudaFree(kv->conv);
     delete kv;
 }
 extern "C" int tfr_kv_len(const tfr_kv* kv) { return kv ? kv->len : TFR_E_INVALID; }
@@ -449,8 +581,14 @@ extern "C" int64_t tfr_kv_bytes_per_token(const tfr_kv* kv) {
     return (int64_t)c.n_layer * c.n_kv_head * c.head_dim * 2 * 2;  // kv.rs:36-41
 }
 extern "C" int tfr_zero_recurrent(tfr_engine* e, tfr_kv* kv) {
-    if (!e || !kv) return TFR_E_INVALID;
-    return TFR_OK;  // dense models carry no recurrent state (model.rs:165-194 is a no-op for them)
+    if (!e || !kv || kv->e != e) return TFR_E_INVALID;
+    if (!kv->ssm) return TFR_OK;  // dense models carry no recurrent state (model.rs:165-194 is a no-op for them)
+    cudaSetDevice(e->device);
+    CU(e, cudaMemsetAsync(kv->ssm, 0, kv->ssm_stride * e->cfg.n_layer * 4, e->stream));
+    CU(e, cudaMemsetAsync(kv->conv, 0, kv->conv_stride * e->cfg.n_layer * 4, e->stream));
+    CU(e, cudaStreamSynchronize(e->stream));
+    kv->rec_steps = 0;
+    return TFR_OK;
 }
 
 // ------------------------------------------------------------------ one token
@@ -479,14 +617,87 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
     int n = 0;
     for (int li = 0; li < c.n_layer; li++) {
         const LayerW& L = e->layers[li];
-        {  // 1. norm + quant + QKV + rope + KV store
-            PrepArgs pa{};
-            pa.vec = li == 0 ? nullptr : e->x;
-            pa.embed = e->token_embd->m;
-            pa.normw = L.attn_norm;
-            pa.eps = c.rms_eps;
-            pa.raw_out = e->x;
-            if (L.wv->m.type != TFR_Q6_K) return -2;  // a Q4_K attn_v would join the Q8 route; not wired yet
+        PrepArgs pn{};  // first kernel of the layer: embedding or residual stream, attn_norm, Q8
+        pn.vec = li == 0 ? nullptr : e->x;
+        pn.embed = e->token_embd->m;
+        pn.normw = L.attn_norm;
+        pn.eps = c.rms_eps;
+        pn.raw_out = e->x;
+        AttnArgs a{};
+        a.q = e->q;
+        a.kc = kv->k + (size_t)li * kv->layer_stride;
+        a.vc = kv->v + (size_t)li * kv->layer_stride;
+        a.partial = e->partial;
+        a.counters = e->counters;
+        a.out = e->attn;
+        a.gate = nullptr;
+        a.n_head = c.n_head;
+        a.n_kv = c.n_kv_head;
+        a.S = e->attn_S;
+        a.min_keys = e->attn_min_keys;
+        a.scale = 1.0f / sqrtf((float)hd);  // forward.rs:389
+        int mix_width = nq;                 // width of the vector the output projection consumes
+        const tfr_mat* wout = L.wo;
+        if (L.kind == LAYER_LINEAR) {
+            // 1. norm + quant + [qkv | z | beta | alpha] projections (layer.rs:736-798)
+            EpiStore ep{e->proj, nullptr, 0, L.gdn_proj->m.N};
+            if (launch_typed(s, cap, L.gdn_proj->m.type, pn, make_job(L.gdn_proj->m, 2, cap), RowJob{}, F32Seg{}, ep, K, e->st) !=
+                cudaSuccess)
+                return -1;
+            n++;
+            // 2. conv + SiLU + L2 + gated delta rule + gated RMSNorm (layer.rs:838-911)
+            GdnArgs g{};
+            g.proj = e->proj;
+            g.conv_w = L.conv_w;
+            g.conv_ring = kv->conv + (size_t)li * kv->conv_stride;
+            g.state = kv->ssm + (size_t)li * kv->ssm_stride;
+            g.ssm_a = L.ssm_a;
+            g.ssm_dt = L.ssm_dt;
+            g.norm_w = L.ssm_norm;
+            g.out = e->attn;
+            g.n_k = c.ssm_group_count;
+            g.n_v = c.ssm_time_step_rank;
+            g.kernel = c.ssm_conv_kernel;
+            g.eps = c.rms_eps;
+            k_gdn_step<<<g.n_v, GDN_THREADS, 0, s>>>(g, e->st);
+            if (cudaGetLastError() != cudaSuccess) return -1;
+            n++;
+            mix_width = gdn_val_dim(c);
+            wout = L.ssm_out;
+        } else if (L.kind == LAYER_FULL_GATED) {
+            // 1. norm + quant + raw [Q|gate, K, V] (+bias)
+            const RowJob jq = make_job(L.wq->m, 2, cap, 0), jk = make_job(L.wk->m, 2, cap, nq);
+            F32Seg fseg{};
+            fseg.m = L.wv->m;
+            fseg.sh = make_share(nkv / 2, cap);
+            fseg.id_base = (2 * nq + nkv) / 2;
+            EpiStore ep{e->proj, L.bias_qkv, 0, 2 * nq + 2 * nkv};
+            if (launch_gemv<BlockQ4, EpiStore>(s, cap, pn, jq, jk, fseg, ep, K, e->st) != cudaSuccess) return -1;
+            n++;
+            // 2. per-head Q/K RMSNorm + partial RoPE, Q|gate split, f16 KV store (layer.rs:386-560)
+            QkNormArgs qa{};
+            qa.raw = e->proj;
+            qa.q_norm = L.q_norm;
+            qa.k_norm = L.k_norm;
+            qa.q_out = e->q;
+            qa.gate_out = e->qgate;
+            qa.kc = kv->k + (size_t)li * kv->layer_stride;
+            qa.vc = kv->v + (size_t)li * kv->layer_stride;
+            qa.n_head = c.n_head;
+            qa.n_kv = c.n_kv_head;
+            qa.hd = hd;
+            qa.n_rot = (c.rope_dim > 0 && c.rope_dim < hd) ? c.rope_dim : hd;
+            qa.theta = c.rope_theta;
+            qa.eps = c.rms_eps;
+            k_qk_norm_rope_store<<<c.n_head + c.n_kv_head, 256, 0, s>>>(qa, e->st);
+            if (cudaGetLastError() != cudaSuccess) return -1;
+            n++;
+            // 3. attention with the sigmoid output gate (layer.rs:646-659)
+            a.gate = e->qgate;
+            if (launch_attention(s, a, hd, e->st) != cudaSuccess) return -1;
+            n++;
+        } else {
+            // 1. norm + quant + QKV + rope + KV store
             const RowJob jq = make_job(L.wq->m, 2, cap, 0), jk = make_job(L.wk->m, 2, cap, nq / 2);
             F32Seg fseg{};
             fseg.m = L.wv->m;
@@ -502,31 +713,18 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
             epi.hd = hd;
             epi.kvdim = nkv;
             epi.theta = c.rope_theta;
-            if (launch_gemv<BlockQ4, EpiQkv>(s, cap, pa, jq, jk, fseg, epi, K, e->st) != cudaSuccess) return -1;
+            if (launch_gemv<BlockQ4, EpiQkv>(s, cap, pn, jq, jk, fseg, epi, K, e->st) != cudaSuccess) return -1;
             n++;
-        }
-        {  // 2. attention
-            AttnArgs a{};
-            a.q = e->q;
-            a.kc = kv->k + (size_t)li * kv->layer_stride;
-            a.vc = kv->v + (size_t)li * kv->layer_stride;
-            a.partial = e->partial;
-            a.counters = e->counters;
-            a.out = e->attn;
-            a.gate = nullptr;
-            a.n_head = c.n_head;
-            a.n_kv = c.n_kv_head;
-            a.S = e->attn_S;
-            a.min_keys = e->attn_min_keys;
-            a.scale = 1.0f / sqrtf((float)hd);  // forward.rs:389
+            // 2. attention
             if (launch_attention(s, a, hd, e->st) != cudaSuccess) return -1;
             n++;
         }
-        {  // 3. o-proj + residual
+        {  // output projection of the mixer + residual
             PrepArgs pa{};
             pa.vec = e->attn;
             EpiStore epi{e->x, nullptr, 2, K};
-            if (launch_typed(s, cap, L.wo->m.type, pa, make_job(L.wo->m, 2, cap), RowJob{}, F32Seg{}, epi, nq, e->st) != cudaSuccess)
+            if (launch_typed(s, cap, wout->m.type, pa, make_job(wout->m, 2, cap), RowJob{}, F32Seg{}, epi, mix_width, e->st) !=
+                cudaSuccess)
                 return -1;
             n++;
         }
@@ -616,8 +814,13 @@ static int run_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
     return TFR_OK;
 }
 
-static int begin_state(tfr_engine* e, int token, int pos, int max_steps, int max_seq, const uint32_t* stops, int n_stop) {
+static int begin_state(tfr_engine* e, const tfr_kv* kv, int token, int pos, int max_steps, int max_seq, const uint32_t* stops,
+                       int n_stop) {
     int* a = e->args_host;
+    // the conv ring's write slot follows the position; the offset keeps it continuous when the
+    // caller moved the KV length between calls
+    const int ck = is_hybrid(e) ? e->cfg.ssm_conv_kernel : 1;
+    a[13] = (int)(((kv->rec_steps - pos) % ck + ck) % ck);
     a[0] = token;
     a[1] = pos;
     a[2] = max_steps;
@@ -654,7 +857,7 @@ extern "C" int tfr_forward_greedy(tfr_engine* e, tfr_kv* kv, const uint32_t* tok
         if (rc) return rc;
     }
     CU(e, cudaMemcpyAsync(e->prompt, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, e->stream));
-    int rc = begin_state(e, (int)tokens[0], kv->len, 1, kv->max_seq + 1, nullptr, 0);
+    int rc = begin_state(e, kv, (int)tokens[0], kv->len, 1, kv->max_seq + 1, nullptr, 0);
     if (rc) return rc;
     CU(e, cudaEventRecord(e->ev0, e->stream));
     for (int i = 0; i < n && !rc; i++) rc = run_token(e, kv, i == n - 1);
@@ -663,6 +866,7 @@ extern "C" int tfr_forward_greedy(tfr_engine* e, tfr_kv* kv, const uint32_t* tok
     rc = finish_state(e, 1);
     if (rc) return rc;
     kv->len += n;
+    kv->rec_steps += n;
     if (next_token) *next_token = (uint32_t)e->out_host[0];
     return TFR_OK;
 }
@@ -682,7 +886,7 @@ extern "C" int tfr_decode_burst(tfr_engine* e, tfr_kv* kv, uint32_t first_token,
         int rc = ensure_graphs(e, kv);
         if (rc) return rc;
     }
-    int rc = begin_state(e, (int)first_token, kv->len, n_run, kv->max_seq + 1, stop_ids, n_stop);
+    int rc = begin_state(e, kv, (int)first_token, kv->len, n_run, kv->max_seq + 1, stop_ids, n_stop);
     if (rc) return rc;
     CU(e, cudaEventRecord(e->ev0, e->stream));
     for (int i = 0; i < n_run && !rc; i++) rc = run_token(e, kv, true);
@@ -694,6 +898,7 @@ extern "C" int tfr_decode_burst(tfr_engine* e, tfr_kv* kv, uint32_t first_token,
     for (int i = 0; i < produced; i++) out[i] = (uint32_t)e->out_host[i];
     *n_out = produced;
     kv->len += produced;
+    kv->rec_steps += produced;
     return TFR_OK;
 }
 
@@ -723,7 +928,7 @@ extern "C" int tfr_debug_read(tfr_engine* e, tfr_kv* kv, const char* what, int l
     std::string w(what);
     if (w == "x") src = e->x, have = (size_t)c.n_embd * 4;
     else if (w == "q") src = e->q, have = (size_t)c.n_head * c.head_dim * 4;
-    else if (w == "attn") src = e->attn, have = (size_t)c.n_head * c.head_dim * 4;
+    else if (w == "attn") src = e->attn, have = (size_t)std::max(c.n_head * c.head_dim, c.hybrid ? gdn_val_dim(c) : 0) * 4;
     else if (w == "h") src = e->h, have = (size_t)c.n_ff * 4;
     else if (w == "logits") src = e->logits, have = (size_t)c.n_vocab * 4;
     else if (w == "layer_x") {
@@ -735,6 +940,26 @@ extern "C" int tfr_debug_read(tfr_engine* e, tfr_kv* kv, const char* what, int l
             drop_graphs(e);
         }
         src = e->layer_taps, have = (size_t)c.n_layer * c.n_embd * 4;
+    }
+    else if (w == "proj" && e->proj) src = e->proj, have = (size_t)(gdn_channels(c) + gdn_val_dim(c) + 2 * c.ssm_time_step_rank) * 4;
+    else if (w == "qgate" && e->qgate) src = e->qgate, have = (size_t)c.n_head * c.head_dim * 4;
+    else if (w == "ssm_state" && kv && kv->ssm && layer >= 0 && layer < c.n_layer)
+        src = kv->ssm + (size_t)layer * kv->ssm_stride, have = kv->ssm_stride * 4;
+    else if (w == "conv_state" && kv && kv->conv && layer >= 0 && layer < c.n_layer) {
+        // the reference's window [kernel-1][channels], oldest first (deltanet.cu:530-559), read out of the ring
+        const int ck = c.ssm_conv_kernel, km1 = ck - 1, ch = gdn_channels(c);
+        if (nbytes > (size_t)km1 * ch * 4) return fail(e, TFR_E_INVALID, "debug_read: conv_state holds %d floats", km1 * ch);
+        std::vector<float> ring((size_t)ck * ch);
+        cudaSetDevice(e->device);
+        CU(e, cudaStreamSynchronize(e->stream));
+        CU(e, cudaMemcpy(ring.data(), kv->conv + (size_t)layer * kv->conv_stride, ring.size() * 4, cudaMemcpyDeviceToHost));
+        std::vector<float> win((size_t)km1 * ch);
+        for (int k = 0; k < km1; k++) {
+            const int slot = (int)(((kv->rec_steps - km1 + k) % ck + ck) % ck);
+            memcpy(win.data() + (size_t)k * ch, ring.data() + (size_t)slot * ch, (size_t)ch * 4);
+        }
+        memcpy(out, win.data(), nbytes);
+        return TFR_OK;
     }
     else if ((w == "k" || w == "v") && kv && layer >= 0 && layer < c.n_layer) {
         src = (w == "k" ? kv->k : kv->v) + (size_t)layer * kv->layer_stride;
@@ -839,8 +1064,8 @@ extern "C" int tfr_op_int_dots(const tfr_mat* w, const int8_t* q8, const float* 
     return check(cudaGetLastError());
 }
 
-extern "C" int tfr_op_attention(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv,
-                                int head_dim, int pos, void* stream) {
+static int op_attention_impl(const float* q, const uint16_t* kc, const uint16_t* vc, const float* gate, float* out, int n_head,
+                             int n_kv, int head_dim, int pos, void* stream) {
     if (!q || !kc || !vc || !out || n_kv <= 0 || n_head % n_kv || n_head / n_kv > ATTN_REP_MAX || pos < 0) return TFR_E_INVALID;
     if (head_dim != 64 && head_dim != 128 && head_dim != 256) return TFR_E_UNSUPPORTED;
     if (n_kv > 64) return TFR_E_UNSUPPORTED;
@@ -869,10 +1094,71 @@ extern "C" int tfr_op_attention(const float* q, const uint16_t* kc, const uint16
     a.out = out;
     a.n_head = n_head;
     a.n_kv = n_kv;
+    a.gate = gate;
     a.min_keys = 32;
     a.scale = 1.0f / sqrtf((float)head_dim);
     a.pos = pos;
     return check(launch_attention((cudaStream_t)stream, a, head_dim, nullptr));
+}
+
+extern "C" int tfr_op_attention(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv,
+                                int head_dim, int pos, void* stream) {
+    return op_attention_impl(q, kc, vc, nullptr, out, n_head, n_kv, head_dim, pos, stream);
+}
+extern "C" int tfr_op_attention_gated(const float* q, const uint16_t* kc, const uint16_t* vc, const float* gate, float* out,
+                                      int n_head, int n_kv, int head_dim, int pos, void* stream) {
+    if (!gate) return TFR_E_INVALID;
+    return op_attention_impl(q, kc, vc, gate, out, n_head, n_kv, head_dim, pos, stream);
+}
+
+extern "C" int tfr_op_gdn_step(const float* proj, const float* conv_w, float* conv_ring, float* state, const float* ssm_a,
+                               const float* ssm_dt, const float* norm_w, float* out, int n_k, int n_v, int state_size,
+                               int kernel, int slot, float eps, void* stream) {
+    if (!proj || !conv_w || !conv_ring || !state || !ssm_a || !ssm_dt || !norm_w || !out || n_k <= 0 || n_v <= 0) return TFR_E_INVALID;
+    if (state_size != GDN_D || kernel < 2 || kernel > GDN_MAX_KERNEL) return TFR_E_UNSUPPORTED;
+    if (slot < 0 || slot >= kernel) return TFR_E_INVALID;
+    configure_kernels_once();
+    GdnArgs g{};
+    g.proj = proj;
+    g.conv_w = conv_w;
+    g.conv_ring = conv_ring;
+    g.state = state;
+    g.ssm_a = ssm_a;
+    g.ssm_dt = ssm_dt;
+    g.norm_w = norm_w;
+    g.out = out;
+    g.n_k = n_k;
+    g.n_v = n_v;
+    g.kernel = kernel;
+    g.eps = eps;
+    g.slot = slot;
+    k_gdn_step<<<n_v, GDN_THREADS, 0, (cudaStream_t)stream>>>(g, nullptr);
+    return check(cudaGetLastError());
+}
+
+extern "C" int tfr_op_qk_norm_rope_store(const float* raw, const float* q_norm, const float* k_norm, float* q_out, float* gate_out,
+                                         uint16_t* kc, uint16_t* vc, int n_head, int n_kv, int head_dim, int n_rot, int pos,
+                                         float theta, float eps, void* stream) {
+    if (!raw || !q_out || !gate_out || !kc || !vc || n_head <= 0 || n_kv <= 0 || pos < 0) return TFR_E_INVALID;
+    if (head_dim <= 0 || head_dim > 256 || n_rot < 0 || n_rot > head_dim || n_rot % 2) return TFR_E_UNSUPPORTED;
+    configure_kernels_once();
+    QkNormArgs a{};
+    a.raw = raw;
+    a.q_norm = q_norm;
+    a.k_norm = k_norm;
+    a.q_out = q_out;
+    a.gate_out = gate_out;
+    a.kc = kc;
+    a.vc = vc;
+    a.n_head = n_head;
+    a.n_kv = n_kv;
+    a.hd = head_dim;
+    a.n_rot = n_rot;
+    a.theta = theta;
+    a.eps = eps;
+    a.pos = pos;
+    k_qk_norm_rope_store<<<n_head + n_kv, 256, 0, (cudaStream_t)stream>>>(a, nullptr);
+    return check(cudaGetLastError());
 }
 
 // ---- flash-decode without any allocation --------------------------------------------------

@@ -1,6 +1,7 @@
 // __global__ kernels of the batch-1 decode path and their launch helpers.
 #pragma once
 #include "tfr_attn.cuh"
+#include "tfr_gdn.cuh"
 #include "tfr_gemv.cuh"
 
 namespace tfr {
@@ -151,7 +152,7 @@ struct EpiLogits {
 
 // ------------------------------------------------------------------ the GEMV kernel
 
-// Optional timeline probe (test aid): when set, thread 0 of every CTA stores %globaltimer at six
+// Optional timeline probe (test aid): when set, thread 0 of every CTA stores %globaltimer at eight
 // points of k_gemv into g_prof[cta * 8 + point].
 __constant__ unsigned long long* g_prof = nullptr;
 __device__ __forceinline__ void prof_mark(int point) {
@@ -592,7 +593,7 @@ __global__ void k_permute_f32(const float* __restrict__ src, float* __restrict__
 }
 
 // Decode-state control (single thread each).  args (device memory, copied from the host per call):
-// [0] token, [1] pos, [2] max_steps, [3] max_seq, [4] n_stop, [5..12] stop ids.
+// [0] token, [1] pos, [2] max_steps, [3] max_seq, [4] n_stop, [5..12] stop ids, [13] conv ring offset.
 __global__ void k_state_begin(TokenState* st, const int* __restrict__ args) {
     st->token = args[0];
     st->pos = args[1];
@@ -606,6 +607,7 @@ __global__ void k_state_begin(TokenState* st, const int* __restrict__ args) {
     st->head_done = 0u;
     st->prompt_idx = 0;
     st->err = 0;
+    st->ring_off = args[13];
 }
 
 // Prefill by decode steps: after a head-less pass, feed the next prompt token.

@@ -44,10 +44,15 @@ def model_config(cfg: dict, context_length: int = 4096) -> ModelConfig:
     c.head_dim, c.n_ff, c.n_vocab = cfg["head_dim"], cfg["n_ff"], cfg["n_vocab"]
     c.context_length = context_length
     c.rope_theta, c.rms_eps = cfg["rope_theta"], cfg["eps"]
-    c.hybrid = int(cfg.get("hybrid", 0))
-    for k in ("rope_dim", "ssm_conv_kernel", "ssm_state_size", "ssm_group_count", "ssm_time_step_rank",
-              "ssm_inner_size", "full_attention_interval"):
-        setattr(c, k, int(cfg.get(k, 0)))
+    # hybrid keys as ModelConfig::from_gguf reads them (config.rs:174-199): rope.dimension_count,
+    # ssm.conv_kernel / state_size / group_count (K heads) / time_step_rank (V heads) / inner_size
+    c.hybrid = int(cfg.get("arch") in ("qwen35", "qwen3_5"))
+    if c.hybrid:
+        c.rope_dim = int(cfg.get("rope_dim", 0))
+        c.ssm_conv_kernel, c.ssm_state_size = int(cfg["conv_kernel"]), int(cfg["ssm_state"])
+        c.ssm_group_count, c.ssm_time_step_rank = int(cfg["ssm_n_k"]), int(cfg["ssm_n_v"])
+        c.ssm_inner_size = c.ssm_time_step_rank * c.ssm_state_size
+        c.full_attention_interval = int(cfg.get("full_attention_interval", 4))
     c.tp_rank, c.tp_size = int(cfg.get("tp_rank", 0)), int(cfg.get("tp_size", 1))
     return c
 
@@ -246,6 +251,25 @@ def op_attention_noalloc(q, kc, vc, out, n_head: int, n_kv: int, head_dim: int, 
     (2 MiB, shared by all calls; larger shapes raise).  Call it once per device before any stream capture."""
     _ok(_lib.lib().tfr_op_attention_noalloc(_ptr(q), _ptr(kc), _ptr(vc), _ptr(out), n_head, n_kv, head_dim, pos,
                                             stream), "attention_noalloc: shape exceeds the built-in scratch or CUDA error")
+
+
+def op_attention_gated(q, kc, vc, gate, out, n_head: int, n_kv: int, head_dim: int, pos: int, stream: int = 0) -> None:
+    _ok(_lib.lib().tfr_op_attention_gated(_ptr(q), _ptr(kc), _ptr(vc), _ptr(gate), _ptr(out), n_head, n_kv, head_dim,
+                                          pos, stream), "attention_gated")
+
+
+def op_gdn_step(proj, conv_w, conv_ring, state, ssm_a, ssm_dt, norm_w, out, n_k: int, n_v: int, state_size: int,
+                kernel: int, slot: int, eps: float, stream: int = 0) -> None:
+    """Gated-DeltaNet decode step (conv + SiLU + L2 + delta rule + gated RMSNorm) after the projections."""
+    _ok(_lib.lib().tfr_op_gdn_step(_ptr(proj), _ptr(conv_w), _ptr(conv_ring), _ptr(state), _ptr(ssm_a), _ptr(ssm_dt),
+                                   _ptr(norm_w), _ptr(out), n_k, n_v, state_size, kernel, slot, eps, stream), "gdn_step")
+
+
+def op_qk_norm_rope_store(raw, q_norm, k_norm, q_out, gate_out, kc, vc, n_head: int, n_kv: int, head_dim: int,
+                          n_rot: int, pos: int, theta: float, eps: float, stream: int = 0) -> None:
+    _ok(_lib.lib().tfr_op_qk_norm_rope_store(_ptr(raw), _ptr(q_norm), _ptr(k_norm), _ptr(q_out), _ptr(gate_out),
+                                             _ptr(kc), _ptr(vc), n_head, n_kv, head_dim, n_rot, pos, theta, eps,
+                                             stream), "qk_norm_rope_store")
 
 
 def op_qkv_rope_store(wq: GpuMat, wk: GpuMat, wv: GpuMat, bq, bk, bv, x, norm_w, eps: float, theta: float,

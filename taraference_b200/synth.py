@@ -122,43 +122,97 @@ TINY_DENSE = dict(arch="qwen2", n_layer=2, n_embd=256, n_head=4, n_kv=2, head_di
                   n_vocab=320, rope_theta=1e6, eps=1e-6, tied=True, qkv_bias=True)
 
 
-def dense_tensor_plan(cfg: dict) -> list[tuple[str, int, int, int]]:
-    """(name, ggml_type, K, N) of every matrix of a dense decoder in the Q4_K_M mix used by the
-    benchmark configurations: Q6_K for token_embd / output, attn_v and ffn_down, Q4_K elsewhere."""
+QWEN35_4B = dict(arch="qwen35", n_layer=32, n_embd=2560, n_head=16, n_kv=4, head_dim=256, n_ff=9216,
+                 n_vocab=151936, rope_theta=1e7, eps=1e-6, tied=True, qkv_bias=False, rope_dim=64,
+                 ssm_n_k=16, ssm_n_v=32, ssm_state=128, conv_kernel=4, full_attention_interval=4)
+TINY_HYBRID = dict(arch="qwen35", n_layer=4, n_embd=256, n_head=2, n_kv=1, head_dim=128, n_ff=512,
+                   n_vocab=320, rope_theta=1e7, eps=1e-6, tied=True, qkv_bias=False, rope_dim=32,
+                   ssm_n_k=2, ssm_n_v=4, ssm_state=128, conv_kernel=4, full_attention_interval=4)
+
+
+def is_hybrid(cfg: dict) -> bool:
+    return cfg.get("arch") in ("qwen35", "qwen3_5")
+
+
+def is_linear_layer(cfg: dict, i: int) -> bool:
+    """Layer i of the hybrid architecture is a full-attention layer iff (i + 1) % interval == 0."""
+    return is_hybrid(cfg) and (i + 1) % cfg.get("full_attention_interval", 4) != 0
+
+
+def tensor_plan(cfg: dict) -> list[tuple[str, int, int, int]]:
+    """(name, ggml_type, K, N) of every matrix in the Q4_K_M mix used by the benchmark
+    configurations: Q6_K for token_embd / output, attn_v and ffn_down, Q4_K elsewhere.  Hybrid
+    models: linear layers carry attn_qkv / attn_gate / ssm_beta / ssm_alpha / ssm_out, full layers
+    a fused Q|gate attn_q of twice the width."""
     K, H, Hkv, hd, FF, V = (cfg[k] for k in ("n_embd", "n_head", "n_kv", "head_dim", "n_ff", "n_vocab"))
+    hyb = is_hybrid(cfg)
     plan = [("token_embd.weight", Q6_K, K, V)]
     if not cfg.get("tied", True):
         plan.append(("output.weight", Q6_K, K, V))
     for i in range(cfg["n_layer"]):
         p = f"blk.{i}."
-        plan += [(p + "attn_q.weight", Q4_K, K, H * hd), (p + "attn_k.weight", Q4_K, K, Hkv * hd),
-                 (p + "attn_v.weight", Q6_K, K, Hkv * hd), (p + "attn_output.weight", Q4_K, H * hd, K),
-                 (p + "ffn_gate.weight", Q4_K, K, FF), (p + "ffn_up.weight", Q4_K, K, FF),
+        if is_linear_layer(cfg, i):
+            d, nk, nv = cfg["ssm_state"], cfg["ssm_n_k"], cfg["ssm_n_v"]
+            plan += [(p + "attn_qkv.weight", Q4_K, K, (2 * nk + nv) * d), (p + "attn_gate.weight", Q4_K, K, nv * d),
+                     (p + "ssm_beta.weight", Q4_K, K, nv), (p + "ssm_alpha.weight", Q4_K, K, nv),
+                     (p + "ssm_out.weight", Q4_K, nv * d, K)]
+        else:
+            plan += [(p + "attn_q.weight", Q4_K, K, (2 if hyb else 1) * H * hd), (p + "attn_k.weight", Q4_K, K, Hkv * hd),
+                     (p + "attn_v.weight", Q6_K, K, Hkv * hd), (p + "attn_output.weight", Q4_K, H * hd, K)]
+        plan += [(p + "ffn_gate.weight", Q4_K, K, FF), (p + "ffn_up.weight", Q4_K, K, FF),
                  (p + "ffn_down.weight", Q6_K, FF, K)]
     return plan
 
 
-def dense_vector_plan(cfg: dict) -> list[tuple[str, int, str]]:
-    """(name, length, kind) of every fp32 vector; kind 'norm' -> ones, 'bias' -> N(0, 0.02)."""
+def vector_plan(cfg: dict) -> list[tuple[str, int, str]]:
+    """(name, length, kind) of every fp32 tensor; kind 'norm' -> ones, 'bias' -> N(0, sigma),
+    'conv' -> U(-0.5, 0.5), 'a' -> -U(0.5, 16) (the GGUF stores -exp(A_log)), 'dt' -> inverse
+    softplus of U(0.001, 0.1)."""
     K, H, Hkv, hd = (cfg[k] for k in ("n_embd", "n_head", "n_kv", "head_dim"))
     plan = [("output_norm.weight", K, "norm")]
     for i in range(cfg["n_layer"]):
         p = f"blk.{i}."
         plan += [(p + "attn_norm.weight", K, "norm"), (p + "ffn_norm.weight", K, "norm")]
+        if is_linear_layer(cfg, i):
+            d, nk, nv, ck = cfg["ssm_state"], cfg["ssm_n_k"], cfg["ssm_n_v"], cfg["conv_kernel"]
+            plan += [(p + "ssm_conv1d.weight", ck * (2 * nk + nv) * d, "conv"), (p + "ssm_a", nv, "a"),
+                     (p + "ssm_dt.bias", nv, "dt"), (p + "ssm_norm.weight", d, "norm")]
+            continue
+        if is_hybrid(cfg):
+            plan += [(p + "attn_q_norm.weight", hd, "norm"), (p + "attn_k_norm.weight", hd, "norm")]
         if cfg.get("qkv_bias", False):
             plan += [(p + "attn_q.bias", H * hd, "bias"), (p + "attn_k.bias", Hkv * hd, "bias"),
                      (p + "attn_v.bias", Hkv * hd, "bias")]
     return plan
 
 
-def make_dense_model(cfg: dict, seed: int = 0, sigma: float = 0.02) -> dict:
-    """Whole dense model on the host: name -> (type, K, N, uint8 bytes) or fp32 vector.
+dense_tensor_plan = tensor_plan
+dense_vector_plan = vector_plan
+
+
+def make_vector(kind: str, n: int, rng, sigma: float) -> np.ndarray:
+    if kind == "norm":
+        return np.ones(n, np.float32)
+    if kind == "conv":
+        return rng.uniform(-0.5, 0.5, n).astype(np.float32)
+    if kind == "a":
+        return (-rng.uniform(0.5, 16.0, n)).astype(np.float32)
+    if kind == "dt":
+        return np.log(np.expm1(rng.uniform(0.001, 0.1, n))).astype(np.float32)
+    return rng.normal(0, sigma, n).astype(np.float32)
+
+
+def make_model(cfg: dict, seed: int = 0, sigma: float = 0.02) -> dict:
+    """Whole model on the host: name -> (type, K, N, uint8 bytes) or fp32 vector.
     Only for sizes numpy handles in seconds; full-size models are generated on the GPU."""
     rng = np.random.default_rng(seed)
     tensors: dict = {}
-    for name, t, K, N in dense_tensor_plan(cfg):
+    for name, t, K, N in tensor_plan(cfg):
         w = rng.normal(0.0, sigma, size=(N, K)).astype(np.float32)
         tensors[name] = (t, K, N, np.ascontiguousarray(quantize(t, w).reshape(-1)))
-    for name, n, kind in dense_vector_plan(cfg):
-        tensors[name] = np.ones(n, np.float32) if kind == "norm" else rng.normal(0, sigma, n).astype(np.float32)
+    for name, n, kind in vector_plan(cfg):
+        tensors[name] = make_vector(kind, n, rng, sigma)
     return tensors
+
+
+make_dense_model = make_model

@@ -180,3 +180,89 @@ def test_tiny_model_deterministic_and_threaded(oracle):
     assert np.isfinite(la).all()
     # KV rows written for exactly the decoded positions
     assert (a.kc[:, :6] != 0).any() and (a.kc[:, 6:] == 0).all()
+
+
+def gdn_step_f64(qkv, z, beta, alpha, conv_w, win, S_, a, dt, norm_w, nk, nv, d, kernel, eps):
+    """Gated delta rule written as matrix algebra in float64 (kernels/deltanet.cu:530-728):
+    S' = g S + k (x) ((v - (g S)^T k) beta),  o = S'^T q / sqrt(d),  y = rmsnorm(o) * w * silu(z)."""
+    ch = (2 * nk + nv) * d
+    win = win.reshape(kernel - 1, ch).astype(np.float64)
+    w = conv_w.reshape(ch, kernel).astype(np.float64)
+    acc = (w[:, :kernel - 1].T * win).sum(0) + w[:, kernel - 1] * qkv
+    cv = acc / (1 + np.exp(-acc))
+    new_win = np.concatenate([win[1:], qkv[None].astype(np.float64)]) if kernel > 1 else win
+    Q, K, V = cv[:nk * d].reshape(nk, d), cv[nk * d:2 * nk * d].reshape(nk, d), cv[2 * nk * d:].reshape(nv, d)
+    Q = Q / np.sqrt((Q * Q).sum(1, keepdims=True) + eps)
+    K = K / np.sqrt((K * K).sum(1, keepdims=True) + eps)
+    S_ = S_.reshape(nv, d, d).astype(np.float64).copy()
+    y = np.zeros((nv, d))
+    for h in range(nv):
+        k, q = K[h % nk], Q[h % nk]
+        b = 1 / (1 + np.exp(-beta[h]))
+        zz = alpha[h] + dt[h]
+        g = np.exp((zz if zz > 20 else np.log1p(np.exp(zz))) * a[h])
+        Sg = g * S_[h]
+        delta = (V[h] - Sg.T @ k) * b
+        S_[h] = Sg + np.outer(k, delta)
+        o = S_[h].T @ q / np.sqrt(d)
+        zz_ = z[h * d:(h + 1) * d]
+        y[h] = o / np.sqrt((o * o).mean() + eps) * norm_w * (zz_ / (1 + np.exp(-zz_)))
+    return y.reshape(-1), S_.reshape(-1), new_win.reshape(-1)
+
+
+@pytest.mark.parametrize("nk,nv,d,kernel", [(2, 4, 128, 4), (1, 3, 32, 2), (3, 3, 16, 3)])
+def test_gdn_step_matches_float64_algebra(oracle, nk, nv, d, kernel):
+    rng = np.random.default_rng(nk * 10 + nv)
+    ch, vd, eps = (2 * nk + nv) * d, nv * d, 1e-6
+    conv_w = rng.uniform(-0.5, 0.5, ch * kernel).astype(np.float32)
+    a = (-rng.uniform(0.5, 16.0, nv)).astype(np.float32)
+    dt = np.log(np.expm1(rng.uniform(0.001, 0.1, nv))).astype(np.float32)
+    norm_w = rng.uniform(0.5, 1.5, d).astype(np.float32)
+    win, st = np.zeros((kernel - 1) * ch, np.float32), np.zeros(nv * d * d, np.float32)
+    win64, st64 = win.astype(np.float64), st.astype(np.float64)
+    for step in range(5):
+        qkv, z = rng.normal(0, 1, ch).astype(np.float32), rng.normal(0, 1, vd).astype(np.float32)
+        beta, alpha = rng.normal(0, 1.5, nv).astype(np.float32), rng.normal(0, 1.5, nv).astype(np.float32)
+        y = oracle.gdn_step(qkv, z, beta, alpha, conv_w, win, st, a, dt, norm_w, nk, nv, d, kernel, eps)
+        y64, st64, win64 = gdn_step_f64(qkv, z, beta, alpha, conv_w, win64, st64, a, dt, norm_w, nk, nv, d, kernel, eps)
+        assert np.allclose(y, y64, rtol=2e-4, atol=2e-5), step
+        assert np.allclose(st, st64, rtol=2e-4, atol=2e-6), step
+        assert np.array_equal(win.astype(np.float64), win64), "the conv window holds the raw inputs"
+    assert np.abs(st).max() > 0 and np.isfinite(st).all()
+
+
+def test_qk_norm_partial_rope_properties(oracle):
+    rng = np.random.default_rng(3)
+    H, hd, n_rot, theta, eps = 3, 64, 16, 1e7, 1e-6
+    x = rng.normal(0, 1, H * hd).astype(np.float32)
+    w = rng.uniform(0.5, 1.5, hd).astype(np.float32)
+    y0 = oracle.qk_norm_partial_rope(x, w, H, hd, n_rot, 0, theta, eps).reshape(H, hd)
+    xn = x.reshape(H, hd).astype(np.float64)
+    want = xn / np.sqrt((xn * xn).mean(1, keepdims=True) + eps) * w
+    assert np.allclose(y0, want, rtol=1e-5, atol=1e-6)          # position 0: rotation is the identity
+    y9 = oracle.qk_norm_partial_rope(x, w, H, hd, n_rot, 9, theta, eps).reshape(H, hd)
+    assert np.array_equal(y9[:, n_rot:], y0[:, n_rot:])         # dims beyond n_rot are not rotated
+    half = n_rot // 2
+    for i in range(half):                                       # rotation preserves each pair's norm
+        n0 = y0[:, i] ** 2 + y0[:, i + half] ** 2
+        n9 = y9[:, i] ** 2 + y9[:, i + half] ** 2
+        assert np.allclose(n0, n9, rtol=1e-4)
+    ang = 9 * theta ** (-2.0 * 1 / n_rot)
+    assert np.allclose(y9[:, 1], y0[:, 1] * np.cos(ang) - y0[:, 1 + half] * np.sin(ang), rtol=1e-4, atol=1e-5)
+
+
+def test_tiny_hybrid_model_layer_kinds_state_and_reset(oracle):
+    cfg = S.TINY_HYBRID
+    tens = S.make_model(cfg, 2)
+    om = oracle.OracleModel(cfg, tens, 32)
+    assert om.kinds == [oracle.LAYER_LINEAR] * 3 + [oracle.LAYER_FULL_GATED]
+    toks, margins, last = om.decode_greedy(0, 5, 6)
+    assert np.isfinite(last).all()
+    # linear layers leave no KV rows, the full-attention layer fills exactly the decoded positions
+    assert not om.kc[:3].any() and om.kc[3, :6].any() and not om.kc[3, 6:].any()
+    assert om.ssm[:3].any() and not om.ssm[3].any() and om.conv[:3].any()
+    om.zero_recurrent()
+    t2, _, l2 = om.decode_greedy(0, 5, 6)
+    assert np.array_equal(toks, t2) and np.array_equal(last, l2)
+    t3, _, l3 = om.decode_greedy(0, 5, 6)  # state carried over: a different sequence state
+    assert not np.array_equal(last, l3)
