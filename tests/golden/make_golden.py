@@ -9,6 +9,7 @@ pin the C restatement (oracle/) against these vectors; nothing here is read at r
 by the library.
 
     python tests/golden/make_golden.py [out.npz]
+    python tests/golden/make_golden.py --hybrid [out.npz]     # ref_kernels_hybrid_sm100.npz
 """
 import sys
 from pathlib import Path
@@ -96,7 +97,72 @@ def main(out_path):
     print("wrote", out_path, {k: v.shape for k, v in g.items()})
 
 
+def hybrid_inputs():
+    """Seeded inputs of the hybrid-layer kernels, shared with tests/test_golden_cpu.py."""
+    rng = np.random.default_rng(20250907)
+    nk, nv, d, kernel = 2, 4, 128, 4
+    ch, vd = (2 * nk + nv) * d, nv * d
+    h = dict(nk=nk, nv=nv, d=d, kernel=kernel, ch=ch, vd=vd)
+    h["conv_w"] = rng.uniform(-0.5, 0.5, ch * kernel).astype(np.float32)
+    h["a"] = (-rng.uniform(0.5, 16.0, nv)).astype(np.float32)
+    h["dt"] = np.log(np.expm1(rng.uniform(0.001, 0.1, nv))).astype(np.float32)
+    h["dt"][0] = 25.0  # softplus takes its linear branch (z > 20) for head 0
+    h["norm_w"] = rng.uniform(0.5, 1.5, d).astype(np.float32)
+    h["steps"] = [dict(qkv=rng.normal(0, 1, ch).astype(np.float32), z=rng.normal(0, 1, vd).astype(np.float32),
+                       beta=rng.normal(0, 1.5, nv).astype(np.float32), alpha=rng.normal(0, 1.5, nv).astype(np.float32))
+                  for _ in range(5)]
+    H, Hkv, hd = 4, 1, 256
+    h.update(H=H, Hkv=Hkv, hd=hd, n_rot=64, theta=1e7, eps=1e-6)
+    h["qg"] = rng.normal(0, 1, 2 * H * hd).astype(np.float32)
+    h["k"] = rng.normal(0, 1, Hkv * hd).astype(np.float32)
+    h["qw"] = rng.uniform(0.5, 1.5, hd).astype(np.float32)
+    h["kw"] = rng.uniform(0.5, 1.5, hd).astype(np.float32)
+    h["gate"] = rng.normal(0, 2, H * hd).astype(np.float32)
+    h["att"] = rng.normal(0, 1, H * hd).astype(np.float32)
+    return h
+
+
+def main_hybrid(out_path):
+    dev = R.dev
+    h = hybrid_inputs()
+    g = {}
+    nk, nv, d, kernel, ch = h["nk"], h["nv"], h["d"], h["kernel"], h["ch"]
+    win = torch.zeros((kernel - 1) * ch, dtype=torch.float32, device="cuda")
+    state = torch.zeros(nv * d * d, dtype=torch.float32, device="cuda")
+    cw, a, dt, nw = dev(h["conv_w"]), dev(h["a"]), dev(h["dt"]), dev(h["norm_w"])
+    for i, st in enumerate(h["steps"]):
+        q, k, v = R.gdn_conv_qkvl2(dev(st["qkv"]), cw, win, nk, nv, d, kernel, h["eps"])
+        y = R.gdn_delta_gated_d128(q, k, v, dev(st["alpha"]), dev(st["beta"]), dt, a, state, nw, dev(st["z"]), nk, nv, h["eps"])
+        g[f"gdn_q_{i}"], g[f"gdn_k_{i}"], g[f"gdn_v_{i}"] = q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy()
+        g[f"gdn_y_{i}"] = y.cpu().numpy()
+    g["gdn_state"], g["gdn_window"] = state.cpu().numpy(), win.cpu().numpy()
+    q, gate = R.split_q_gate(dev(h["qg"]), h["H"], h["hd"])
+    g["split_q"], g["split_gate"] = q.cpu().numpy(), gate.cpu().numpy()
+    for pos in (0, 5, 4000):
+        qq = R.qk_norm_partial_rope(q.clone(), dev(h["qw"]), h["H"], h["hd"], h["n_rot"], pos, h["theta"], h["eps"])
+        kk = R.qk_norm_partial_rope(dev(h["k"]).clone(), dev(h["kw"]), h["Hkv"], h["hd"], h["n_rot"], pos, h["theta"], h["eps"])
+        g[f"qnorm_rope_pos{pos}"], g[f"knorm_rope_pos{pos}"] = qq.cpu().numpy(), kk.cpu().numpy()
+    g["mul_sigmoid"] = R.mul_sigmoid(dev(h["att"]).clone(), dev(h["gate"])).cpu().numpy()
+    # tiny hybrid model: teacher-forced layer outputs and free-running logits of the reference kernels
+    cfg = S.TINY_HYBRID
+    tens = S.make_model(cfg, seed=12)
+    rm = R.RefModel(cfg, tens, 16)
+    for i, t in enumerate([3, 200, 45, 17]):
+        taps = {}
+        logits = rm.decode_token(i, t, taps)
+        g[f"tinyh_logits_{i}"] = logits.cpu().numpy()
+        for li in range(cfg["n_layer"]):
+            g[f"tinyh_x_{i}_{li}"] = taps[f"x{li}"].cpu().numpy()
+    g["tinyh_ssm0"] = rm.ssm[0].cpu().numpy()
+    torch.cuda.synchronize()
+    np.savez_compressed(out_path, **g)
+    print("wrote", out_path, {k: v.shape for k, v in g.items()})
+
+
 if __name__ == "__main__":
-    out = Path(sys.argv[1]) if len(sys.argv) > 1 else ROOT / "tests" / "golden" / "ref_kernels_sm100.npz"
+    args = [a for a in sys.argv[1:] if a != "--hybrid"]
+    hybrid = "--hybrid" in sys.argv[1:]
+    default = "ref_kernels_hybrid_sm100.npz" if hybrid else "ref_kernels_sm100.npz"
+    out = Path(args[0]) if args else ROOT / "tests" / "golden" / default
     out.parent.mkdir(parents=True, exist_ok=True)
-    main(out)
+    (main_hybrid if hybrid else main)(out)

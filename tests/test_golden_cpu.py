@@ -120,3 +120,69 @@ def test_tiny_model_layers_match_reference_build(oracle, G):
     worst = np.array(worst)
     # most stages agree to rounding; a stage in which one activation rounded differently is ~1e-3 off
     assert np.median(worst) < 2e-5 and worst.max() < 2e-2, worst
+
+
+# ------------------------------------------------------------------ hybrid-layer kernels
+
+@pytest.fixture(scope="module")
+def GH():
+    return np.load(HERE / "golden" / "ref_kernels_hybrid_sm100.npz")
+
+
+@pytest.fixture(scope="module")
+def IH():
+    src = (HERE / "golden" / "make_golden.py").read_text()
+    start = src.index("def hybrid_inputs():")
+    end = src.index("def main_hybrid(out_path):")
+    ns = dict(np=np)
+    exec(src[start:end], ns)
+    return ns["hybrid_inputs"]()
+
+
+def test_gdn_step_matches_reference_build(oracle, GH, IH):
+    """gdn_conv_qkvl2_one_f32 + gdn_delta_gated_one_d128_f32 over five tokens (fast-math vs IEEE)."""
+    h = IH
+    nk, nv, d, kernel, ch = h["nk"], h["nv"], h["d"], h["kernel"], h["ch"]
+    win = np.zeros((kernel - 1) * ch, np.float32)
+    state = np.zeros(nv * d * d, np.float32)
+    for i, st in enumerate(h["steps"]):
+        y = oracle.gdn_step(st["qkv"], st["z"], st["beta"], st["alpha"], h["conv_w"], win, state, h["a"], h["dt"],
+                            h["norm_w"], nk, nv, d, kernel, h["eps"])
+        assert rel(y, GH[f"gdn_y_{i}"]) < 2e-5, (i, rel(y, GH[f"gdn_y_{i}"]))
+    assert rel(state, GH["gdn_state"]) < 2e-5
+    assert np.array_equal(win, GH["gdn_window"])
+
+
+def test_gated_attention_front_end_matches_reference_build(oracle, GH, IH):
+    h = IH
+    H, Hkv, hd = h["H"], h["Hkv"], h["hd"]
+    qg = h["qg"].reshape(H, 2, hd)
+    assert np.array_equal(qg[:, 0].reshape(-1), GH["split_q"]) and np.array_equal(qg[:, 1].reshape(-1), GH["split_gate"])
+    for pos in (0, 5, 4000):
+        q = oracle.qk_norm_partial_rope(GH["split_q"], h["qw"], H, hd, h["n_rot"], pos, h["theta"], h["eps"])
+        k = oracle.qk_norm_partial_rope(h["k"], h["kw"], Hkv, hd, h["n_rot"], pos, h["theta"], h["eps"])
+        # fast powf / sinf / cosf in the reference build: angle error grows with the position
+        tol = 2e-6 if pos == 0 else 2e-4
+        assert rel(q, GH[f"qnorm_rope_pos{pos}"]) < tol, (pos, rel(q, GH[f"qnorm_rope_pos{pos}"]))
+        assert rel(k, GH[f"knorm_rope_pos{pos}"]) < tol
+    want = h["att"].astype(np.float64) / (1 + np.exp(-h["gate"].astype(np.float64)))
+    assert rel(want, GH["mul_sigmoid"]) < 2e-6
+
+
+def test_tiny_hybrid_layers_match_reference_build(oracle, GH):
+    from taraference_b200 import synth as S
+    cfg = S.TINY_HYBRID
+    tens = S.make_model(cfg, seed=12)
+    om = oracle.OracleModel(cfg, tens, 16)
+    worst = []
+    for i, t in enumerate([3, 200, 45, 17]):
+        x = om.embed(t)
+        for li in range(cfg["n_layer"]):
+            xin = x if li == 0 else GH[f"tinyh_x_{i}_{li - 1}"]   # teacher-forced with the reference's stream
+            x = om.layer_forward(li, xin, i)
+            worst.append(rel(x, GH[f"tinyh_x_{i}_{li}"]))
+        logits = om.head_forward(GH[f"tinyh_x_{i}_{cfg['n_layer'] - 1}"])
+        worst.append(rel(logits, GH[f"tinyh_logits_{i}"]))
+    worst = np.array(worst)
+    assert np.median(worst) < 2e-5 and worst.max() < 2e-2, worst
+    assert rel(om.ssm[0], GH["tinyh_ssm0"]) < 1e-2
