@@ -106,8 +106,31 @@ int tfr_forward_greedy(tfr_engine* e, tfr_kv* kv, const uint32_t* tokens, int n,
  * emitted tokens, *n_out their count; kv.len advances by *n_out. */
 int tfr_decode_burst(tfr_engine* e, tfr_kv* kv, uint32_t first_token, int max_n, const uint32_t* stop_ids, int n_stop,
                      uint32_t* out, int* n_out);
-/* CudaModel::current_logits, forward.rs:20-39: logits of the last decoded position. */
+/* CudaModel::current_logits, forward.rs:20-39: logits of the last decoded position.  With
+ * tp_size > 1 every rank holds the logits of its vocabulary rows only: the call fills
+ * out[first, end) of tfr_tp_vocab_range and leaves the rest of out untouched. */
 int tfr_current_logits(tfr_engine* e, float* out, int n);
+
+/* ---- tensor parallelism (new: the reference drives one GPU, device.rs:85-95) ----
+ * One engine per GPU, created with tfr_model_config.tp_size = N and its tp_rank.  Every rank is
+ * handed the SAME full tensors through tfr_upload_tensor and keeps its Megatron shard: rows of
+ * attn_q/k/v (+bias), ffn_gate/up and the vocabulary head; K blocks of attn_output and ffn_down.
+ * The row-parallel GEMVs all-reduce inside the kernel through an exchange buffer that each rank
+ * owns and all peers map.  After tfr_finalize_load and before the first forward call the host
+ * connects the ranks in one of two ways:
+ *   - one process per GPU: tfr_tp_ipc_handle on every rank, gather the 64-byte handles in rank
+ *     order over any channel, tfr_tp_attach_ipc on every rank;
+ *   - one process driving all GPUs: tfr_tp_local_pointer on every engine, tfr_tp_attach_pointers
+ *     with the N pointers in rank order (peer access is enabled by the call).
+ * All ranks must then issue the same forward / burst calls with the same arguments; a rank
+ * that does not show up makes the others return TFR_E_CUDA after a bounded wait (about 2 s). */
+int tfr_tp_exchange_bytes(const tfr_engine* e, size_t* bytes);
+int tfr_tp_ipc_handle(tfr_engine* e, void* handle_out_64_bytes);
+int tfr_tp_attach_ipc(tfr_engine* e, const void* handles_rank_order);
+int tfr_tp_local_pointer(tfr_engine* e, void** ptr);
+int tfr_tp_attach_pointers(tfr_engine* e, void* const* bases_rank_order);
+/* Vocabulary rows [first, end) whose logits this rank computes (all of them when tp_size == 1). */
+int tfr_tp_vocab_range(const tfr_engine* e, int* first, int* end);
 /* set_cuda_graph / graph_active / invalidate_decode_graph, model.rs:101-112,197 */
 int tfr_set_cuda_graph(tfr_engine* e, int enabled);
 int tfr_graph_active(const tfr_engine* e);

@@ -57,6 +57,12 @@ def lib() -> C.CDLL:
         "tfr_forward_greedy": (i32, [vp, vp, vp, i32, C.POINTER(C.c_uint32)]),
         "tfr_decode_burst": (i32, [vp, vp, C.c_uint32, i32, vp, i32, vp, C.POINTER(i32)]),
         "tfr_current_logits": (i32, [vp, vp, i32]),
+        "tfr_tp_exchange_bytes": (i32, [vp, C.POINTER(sz)]),
+        "tfr_tp_ipc_handle": (i32, [vp, vp]),
+        "tfr_tp_attach_ipc": (i32, [vp, vp]),
+        "tfr_tp_local_pointer": (i32, [vp, C.POINTER(vp)]),
+        "tfr_tp_attach_pointers": (i32, [vp, vp]),
+        "tfr_tp_vocab_range": (i32, [vp, C.POINTER(i32), C.POINTER(i32)]),
         "tfr_set_cuda_graph": (i32, [vp, i32]),
         "tfr_graph_active": (i32, [vp]),
         "tfr_launch_count": (i64, [vp]),

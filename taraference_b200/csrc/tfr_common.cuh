@@ -129,6 +129,8 @@ struct TokenState {
     int prompt_idx;
     int max_seq;                   // KV capacity; reaching it sets done
     int ring_off;                  // conv-history ring: slot of the current input = (pos + ring_off) % kernel
+    unsigned int ar_epoch;         // tensor parallelism: all-reduces completed before this token (never reset)
+    int pad_;
 };
 
 // Orderable 64-bit key: larger logit wins; on equal logits the lower index wins.

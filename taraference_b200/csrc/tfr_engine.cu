@@ -64,6 +64,17 @@ struct VecT {
     int64_t n = 0;
 };
 
+// This rank's share of the model (Megatron split).  With tp == 1 it covers everything.
+struct TpPlan {
+    int tp = 1, rank = 0;
+    int n_head = 0, n_kv = 0, nq = 0, nkv = 0;  // local heads and their widths
+    int q_lo = 0;                               // first element of the local heads in the full attention output
+    int wo_b0 = 0, wo_b1 = 0;                   // K blocks of attn_output that cover the local heads
+    int attn_off = 0, attn_width = 0;           // local heads sit at attn[attn_off ..) of a zero-padded vector
+    int ff_b0 = 0, ff_b1 = 0, ff = 0;           // block-aligned slice of the FFN width
+    int v0 = 0, v1 = 0;                         // vocabulary rows of the head
+};
+
 constexpr int TFR_MAX_BURST = 8192;
 constexpr int TFR_MAX_PROMPT = 65536;
 
@@ -73,6 +84,10 @@ struct tfr_engine {
     cudaDeviceProp prop{};
     std::string err;
     tfr_model_config cfg{};
+    TpPlan plan{};
+    TpComm comm{};
+    unsigned char* comm_local = nullptr;
+    bool comm_attached = false, comm_ipc = false;
     bool has_cfg = false, finalized = false;
     std::map<std::string, tfr_mat*> mats;
     std::map<std::string, VecT> vecs;
@@ -160,6 +175,8 @@ static void configure_kernels_once() {
     configure_kernel(k_gemv<BlockQ4, EpiStore>, true);
     configure_kernel(k_gemv<BlockQ6, EpiStore>, true);
     configure_kernel(k_gemv<BlockQ4, EpiSilu>, true);
+    configure_kernel(k_gemv<BlockQ4, EpiAllReduce>, true);
+    configure_kernel(k_gemv<BlockQ6, EpiAllReduce>, true);
     configure_kernel(k_gemv<BlockQ4, EpiLogits>, true);
     configure_kernel(k_gemv<BlockQ6, EpiLogits>, true);
     configure_kernel(k_int_dots<BlockQ4>, true);
@@ -267,6 +284,10 @@ extern "C" void tfr_destroy(tfr_engine* e) {
     cudaSetDevice(e->device);
     cudaStreamSynchronize(e->stream);
     drop_graphs(e);
+    if (e->comm_ipc)
+        for (int r = 0; r < e->plan.tp; r++)
+            if (r != e->plan.rank && e->comm.base[r]) cudaIpcCloseMemHandle(e->comm.base[r]);
+    cudaFree(e->comm_local);
     for (auto& kv : e->mats) tfr_mat_free(kv.second);
     for (auto& kv : e->vecs) cudaFree(kv.second.dev);
     for (auto& L : e->layers) cudaFree(L.bias_qkv);
@@ -314,9 +335,37 @@ extern "C" int tfr_set_config(tfr_engine* e, const tfr_model_config* c) {
             return fail(e, TFR_E_UNSUPPORTED, "ssm.inner_size %d != time_step_rank * state_size", c->ssm_inner_size);
         if (c->rope_dim < 0 || c->rope_dim > c->head_dim || c->rope_dim % 2) return fail(e, TFR_E_INVALID, "bad rope.dimension_count");
     }
-    if (c->tp_size > 1) return fail(e, TFR_E_UNSUPPORTED, "tensor parallelism is not built yet");
+    const int tp = c->tp_size < 1 ? 1 : c->tp_size;
+    if (tp > 1) {
+        if (tp > TP_MAX) return fail(e, TFR_E_UNSUPPORTED, "tp_size %d (at most %d)", tp, TP_MAX);
+        if (c->tp_rank < 0 || c->tp_rank >= tp) return fail(e, TFR_E_INVALID, "tp_rank %d outside [0, %d)", c->tp_rank, tp);
+        if (c->hybrid) return fail(e, TFR_E_UNSUPPORTED, "tensor parallelism covers the dense architecture only");
+        if (c->n_head % tp || c->n_kv_head % tp)
+            return fail(e, TFR_E_UNSUPPORTED, "tp_size %d does not divide %d query / %d KV heads", tp, c->n_head, c->n_kv_head);
+        if (c->n_ff / 256 < tp || c->n_vocab < 2 * tp) return fail(e, TFR_E_UNSUPPORTED, "model too narrow for tp_size %d", tp);
+        if (e->prop.multiProcessorCount > TP_MAX_CTAS) return fail(e, TFR_E_UNSUPPORTED, "more than %d SMs", TP_MAX_CTAS);
+    }
     e->cfg = *c;
-    if (e->cfg.tp_size < 1) e->cfg.tp_size = 1;
+    e->cfg.tp_size = tp;
+    if (tp == 1) e->cfg.tp_rank = 0;
+    TpPlan& P = e->plan;
+    P.tp = tp;
+    P.rank = e->cfg.tp_rank;
+    P.n_head = c->n_head / tp;
+    P.n_kv = c->n_kv_head / tp;
+    P.nq = P.n_head * c->head_dim;
+    P.nkv = P.n_kv * c->head_dim;
+    P.q_lo = P.rank * P.nq;
+    P.wo_b0 = P.q_lo / 256;
+    P.wo_b1 = (P.q_lo + P.nq + 255) / 256;
+    P.attn_off = P.q_lo - P.wo_b0 * 256;
+    P.attn_width = (P.wo_b1 - P.wo_b0) * 256;
+    const long long nbf = c->n_ff / 256;
+    P.ff_b0 = (int)(nbf * P.rank / tp);
+    P.ff_b1 = (int)(nbf * (P.rank + 1) / tp);
+    P.ff = (P.ff_b1 - P.ff_b0) * 256;
+    P.v0 = (int)((long long)c->n_vocab * P.rank / tp);
+    P.v1 = (int)((long long)c->n_vocab * (P.rank + 1) / tp);
     e->has_cfg = true;
     return TFR_OK;
 }
@@ -334,15 +383,63 @@ extern "C" int tfr_upload_tensor(tfr_engine* e, const char* name, int type, int6
     cudaSetDevice(e->device);
     std::string nm(name);
     if (e->mats.count(nm) || e->vecs.count(nm)) return fail(e, TFR_E_INVALID, "tensor %s uploaded twice", name);
+    const TpPlan& P = e->plan;
     if (type == TFR_TYPE_F32) {
         // vectors must be F32 (load.rs:135-143)
         int64_t n = n_rows * (n_cols > 0 ? n_cols : 1);
         if (nbytes != (size_t)n * 4) return fail(e, TFR_E_INVALID, "vector %s: %zu bytes for %lld floats", name, nbytes, (long long)n);
+        int64_t first = 0, keep = n;
+        if (P.tp > 1) {  // biases of column-parallel projections follow their rows
+            if (ends_with(nm, "attn_q.bias")) first = (int64_t)P.rank * P.nq, keep = P.nq;
+            else if (ends_with(nm, "attn_k.bias") || ends_with(nm, "attn_v.bias")) first = (int64_t)P.rank * P.nkv, keep = P.nkv;
+            if (first + keep > n) return fail(e, TFR_E_INVALID, "vector %s is shorter than its tensor-parallel slice", name);
+        }
         VecT v;
-        v.n = n;
-        CU(e, cudaMalloc(&v.dev, nbytes));
-        CU(e, cudaMemcpy(v.dev, bytes, nbytes, cudaMemcpyDefault));
+        v.n = keep;
+        CU(e, cudaMalloc(&v.dev, (size_t)keep * 4));
+        CU(e, cudaMemcpy(v.dev, (const float*)bytes + first, (size_t)keep * 4, cudaMemcpyDefault));
         e->vecs[nm] = v;
+        return TFR_OK;
+    }
+    if (P.tp > 1) {
+        if (type != TFR_Q4_K && type != TFR_Q6_K) return fail(e, TFR_E_UNSUPPORTED, "matrix type %d not supported", type);
+        if (n_rows <= 0 || n_cols <= 0 || n_rows % 256 || nbytes != raw_bytes(type, n_rows, n_cols))
+            return fail(e, TFR_E_INVALID, "tensor %s: bad shape or byte size", name);
+        const int blk = type == TFR_Q4_K ? 144 : 210;
+        const size_t row_bytes = (size_t)(n_rows / 256) * blk;
+        int64_t r0 = 0, r1 = n_cols;   // rows kept (column-parallel)
+        int64_t b0 = 0, b1 = n_rows / 256;  // K blocks kept (row-parallel)
+        if (ends_with(nm, "attn_q.weight")) r0 = (int64_t)P.rank * P.nq, r1 = r0 + P.nq;
+        else if (ends_with(nm, "attn_k.weight") || ends_with(nm, "attn_v.weight")) r0 = (int64_t)P.rank * P.nkv, r1 = r0 + P.nkv;
+        else if (ends_with(nm, "ffn_gate.weight") || ends_with(nm, "ffn_up.weight")) r0 = (int64_t)P.ff_b0 * 256, r1 = (int64_t)P.ff_b1 * 256;
+        else if (nm == "output.weight") r0 = P.v0, r1 = P.v1;
+        else if (ends_with(nm, "attn_output.weight")) b0 = P.wo_b0, b1 = P.wo_b1;
+        else if (ends_with(nm, "ffn_down.weight")) b0 = P.ff_b0, b1 = P.ff_b1;
+        if (r1 > n_cols || b1 > n_rows / 256) return fail(e, TFR_E_INVALID, "tensor %s is smaller than its tensor-parallel slice", name);
+        const int perm = (ends_with(nm, "attn_q.weight") || ends_with(nm, "attn_k.weight")) ? e->cfg.head_dim : 0;
+        tfr_mat* m = nullptr;
+        int rc;
+        if (b0 == 0 && b1 == n_rows / 256) {
+            rc = mat_create_impl(e, type, n_rows, r1 - r0, (const uint8_t*)bytes + (size_t)r0 * row_bytes, (size_t)(r1 - r0) * row_bytes,
+                                 perm, e->stream, &m);
+        } else {
+            // K-block slice of every row, gathered into a dense temporary on the device
+            const size_t width = (size_t)(b1 - b0) * blk;
+            void* tmp = nullptr;
+            CU(e, cudaMalloc(&tmp, width * (size_t)n_cols));
+            // on the engine's stream: a synchronous copy from pageable memory may return before its DMA has
+            // landed, and this (non-blocking) stream would not wait for it
+            cudaError_t r = cudaMemcpy2DAsync(tmp, width, (const uint8_t*)bytes + (size_t)b0 * blk, row_bytes, width, (size_t)n_cols,
+                                              cudaMemcpyDefault, e->stream);
+            if (r != cudaSuccess) {
+                cudaFree(tmp);
+                return fail(e, TFR_E_CUDA, "slicing %s: %s", name, cudaGetErrorString(r));
+            }
+            rc = mat_create_impl(e, type, (b1 - b0) * 256, n_cols, tmp, width * (size_t)n_cols, 0, e->stream, &m);
+            cudaFree(tmp);
+        }
+        if (rc) return rc;
+        e->mats[nm] = m;
         return TFR_OK;
     }
     // F32/F16 matrices are rejected like load.rs:15-28
@@ -435,11 +532,27 @@ extern "C" int tfr_finalize_load(tfr_engine* e) {
     if (e->finalized) return TFR_OK;
     cudaSetDevice(e->device);
     const tfr_model_config& c = e->cfg;
-    const int K = c.n_embd, hd = c.head_dim, nq = c.n_head * hd, nkv = c.n_kv_head * hd, FF = c.n_ff, V = c.n_vocab;
+    const TpPlan& P = e->plan;
+    // widths below are this rank's (everything when tp_size == 1)
+    const int K = c.n_embd, hd = c.head_dim, nq = P.nq, nkv = P.nkv, FF = P.ff, V = c.n_vocab, Vl = P.v1 - P.v0;
     int rc = TFR_OK;
     e->token_embd = need_mat(e, "token_embd.weight", K, V, rc);
     if (rc) return rc;
-    e->head = e->mats.count("output.weight") ? need_mat(e, "output.weight", K, V, rc) : e->token_embd;
+    if (e->mats.count("output.weight")) {
+        e->head = need_mat(e, "output.weight", K, Vl, rc);
+    } else if (P.tp == 1) {
+        e->head = e->token_embd;
+    } else {
+        // tied head: this rank's vocabulary rows are a run of whole tiles of the embedding matrix
+        const long long f0 = (long long)P.v0 * (K / 256);
+        if (f0 % 32) return fail(e, TFR_E_UNSUPPORTED, "tied vocabulary head: slice of rank %d does not start on a tile", P.rank);
+        tfr_mat* view = new tfr_mat();
+        view->m = e->token_embd->m;
+        view->m.N = Vl;
+        view->m.data = e->token_embd->m.data + (f0 / 32) * tile_bytes(view->m.type);
+        e->mats["output.weight(view)"] = view;
+        e->head = view;
+    }
     e->output_norm = need_vec(e, "output_norm.weight", K, false, rc);
     if (rc) return rc;
     e->layers.resize(c.n_layer);
@@ -465,7 +578,7 @@ extern "C" int tfr_finalize_load(tfr_engine* e) {
         L.wq = need_mat(e, p + "attn_q.weight", K, nq_rows, rc);
         L.wk = need_mat(e, p + "attn_k.weight", K, nkv, rc);
         L.wv = need_mat(e, p + "attn_v.weight", K, nkv, rc);
-        L.wo = need_mat(e, p + "attn_output.weight", nq, K, rc);
+        L.wo = need_mat(e, p + "attn_output.weight", P.attn_width, K, rc);
         if (rc) return rc;
         if (L.wq->m.type != TFR_Q4_K || L.wk->m.type != TFR_Q4_K)
             return fail(e, TFR_E_UNSUPPORTED, "layer %d: attn_q / attn_k must be Q4_K", i);
@@ -493,21 +606,31 @@ extern "C" int tfr_finalize_load(tfr_engine* e) {
     e->held.clear();
     // workspaces (load.rs:547-607: everything allocated once)
     const int sms = e->prop.multiProcessorCount;
-    e->attn_S = sms / c.n_kv_head;
+    e->attn_S = sms / P.n_kv;
     if (e->attn_S < 1) e->attn_S = 1;
     CU(e, cudaMalloc(&e->x, (size_t)K * 4));
     const int vd = c.hybrid ? gdn_val_dim(c) : 0;
     CU(e, cudaMalloc(&e->q, (size_t)nq * 4));
-    CU(e, cudaMalloc(&e->attn, (size_t)(nq > vd ? nq : vd) * 4));  // attention output, or the mixer output of a linear layer
+    const int aw = P.attn_width > vd ? P.attn_width : vd;
+    CU(e, cudaMalloc(&e->attn, (size_t)aw * 4));  // attention output (zero outside the local heads), or a linear layer's mixer output
+    CU(e, cudaMemsetAsync(e->attn, 0, (size_t)aw * 4, e->stream));
     if (c.hybrid) {
         const int lin = gdn_channels(c) + vd + 2 * c.ssm_time_step_rank, full = 2 * nq + 2 * nkv;
         CU(e, cudaMalloc(&e->proj, (size_t)(lin > full ? lin : full) * 4));
         CU(e, cudaMalloc(&e->qgate, (size_t)nq * 4));
     }
     CU(e, cudaMalloc(&e->h, (size_t)FF * 4));
-    CU(e, cudaMalloc(&e->logits, (size_t)V * 4));
-    CU(e, cudaMalloc(&e->partial, (size_t)c.n_head * e->attn_S * (2 + hd) * 4));
-    CU(e, cudaMalloc(&e->counters, (size_t)c.n_kv_head * 4));
+    CU(e, cudaMalloc(&e->logits, (size_t)Vl * 4));
+    CU(e, cudaMalloc(&e->partial, (size_t)P.n_head * e->attn_S * (2 + hd) * 4));
+    CU(e, cudaMalloc(&e->counters, (size_t)P.n_kv * 4));
+    if (P.tp > 1) {
+        e->comm.lay = tp_layout(K);
+        e->comm.tp = P.tp;
+        e->comm.rank = P.rank;
+        e->comm.ops_per_token = 2 * c.n_layer + 1;
+        CU(e, cudaMalloc(&e->comm_local, e->comm.lay.total));
+        CU(e, cudaMemsetAsync(e->comm_local, 0, e->comm.lay.total, e->stream));
+    }
     CU(e, cudaMalloc(&e->st, sizeof(TokenState)));
     CU(e, cudaMalloc(&e->out_tokens, (size_t)TFR_MAX_BURST * 4));
     CU(e, cudaMalloc(&e->prompt, (size_t)TFR_MAX_PROMPT * 4));
@@ -515,9 +638,9 @@ extern "C" int tfr_finalize_load(tfr_engine* e) {
     CU(e, cudaMallocHost(&e->out_host, (size_t)TFR_MAX_BURST * 4));
     CU(e, cudaMalloc(&e->args_dev, 16 * sizeof(int)));
     CU(e, cudaMallocHost(&e->args_host, 16 * sizeof(int)));
-    CU(e, cudaMemsetAsync(e->counters, 0, (size_t)c.n_kv_head * 4, e->stream));
+    CU(e, cudaMemsetAsync(e->counters, 0, (size_t)P.n_kv * 4, e->stream));
     CU(e, cudaMemsetAsync(e->st, 0, sizeof(TokenState), e->stream));
-    CU(e, cudaMemsetAsync(e->logits, 0, (size_t)V * 4, e->stream));
+    CU(e, cudaMemsetAsync(e->logits, 0, (size_t)Vl * 4, e->stream));
     CU(e, cudaStreamSynchronize(e->stream));
     e->finalized = true;
     return TFR_OK;
@@ -531,7 +654,7 @@ extern "C" int tfr_alloc_kv(tfr_engine* e, int max_seq, tfr_kv** out) {
     tfr_kv* kv = new tfr_kv();
     kv->e = e;
     kv->max_seq = max_seq;
-    kv->layer_stride = (size_t)max_seq * e->cfg.n_kv_head * e->cfg.head_dim;
+    kv->layer_stride = (size_t)max_seq * e->plan.nkv;
     const size_t bytes = kv->layer_stride * e->cfg.n_layer * 2;
     if (cudaMalloc(&kv->k, bytes) != cudaSuccess || cudaMalloc(&kv->v, bytes) != cudaSuccess) {
         cudaFree(kv->k);
@@ -578,7 +701,7 @@ extern "C" int tfr_kv_clear(tfr_kv* kv) { return tfr_kv_set_len(kv, 0); }
 extern "C" int64_t tfr_kv_bytes_per_token(const tfr_kv* kv) {
     if (!kv) return 0;
     const tfr_model_config& c = kv->e->cfg;
-    return (int64_t)c.n_layer * c.n_kv_head * c.head_dim * 2 * 2;  // kv.rs:36-41
+    return (int64_t)c.n_layer * kv->e->plan.nkv * 2 * 2;  // kv.rs:36-41 (this rank's KV heads)
 }
 extern "C" int tfr_zero_recurrent(tfr_engine* e, tfr_kv* kv) {
     if (!e || !kv || kv->e != e) return TFR_E_INVALID;
@@ -611,10 +734,28 @@ static cudaError_t launch_typed(cudaStream_t s, int grid, int type, const PrepAr
 // Enqueues the kernels of one decode step; returns the number of launches or a negative error.
 static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
     const tfr_model_config& c = e->cfg;
-    const int K = c.n_embd, hd = c.head_dim, nq = c.n_head * hd, nkv = c.n_kv_head * hd, FF = c.n_ff, V = c.n_vocab;
+    const TpPlan& P = e->plan;
+    const int K = c.n_embd, hd = c.head_dim, nq = P.nq, nkv = P.nkv, FF = P.ff, V = P.v1 - P.v0;
     const int cap = e->prop.multiProcessorCount;  // one 1024-thread CTA per SM
     cudaStream_t s = e->stream;
     int n = 0;
+    // y = W x + y for a row-parallel matrix: plain store on one GPU, in-kernel all-reduce otherwise
+    auto launch_residual = [&](const tfr_mat* w, const float* vec, int width, int op_index) -> cudaError_t {
+        PrepArgs pa{};
+        pa.vec = vec;
+        const RowJob job = make_job(w->m, 2, cap);
+        if (P.tp == 1) {
+            EpiStore epi{e->x, nullptr, 2, K};
+            return launch_typed(s, cap, w->m.type, pa, job, RowJob{}, F32Seg{}, epi, width, e->st);
+        }
+        EpiAllReduce epi{};
+        epi.x = e->x;
+        epi.n_rows = K;
+        epi.sh = job.sh;
+        epi.c = e->comm;
+        epi.op_index = op_index;
+        return launch_typed(s, cap, w->m.type, pa, job, RowJob{}, F32Seg{}, epi, width, e->st);
+    };
     for (int li = 0; li < c.n_layer; li++) {
         const LayerW& L = e->layers[li];
         PrepArgs pn{};  // first kernel of the layer: embedding or residual stream, attn_norm, Q8
@@ -629,14 +770,14 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
         a.vc = kv->v + (size_t)li * kv->layer_stride;
         a.partial = e->partial;
         a.counters = e->counters;
-        a.out = e->attn;
+        a.out = e->attn + P.attn_off;
         a.gate = nullptr;
-        a.n_head = c.n_head;
-        a.n_kv = c.n_kv_head;
+        a.n_head = P.n_head;
+        a.n_kv = P.n_kv;
         a.S = e->attn_S;
         a.min_keys = e->attn_min_keys;
         a.scale = 1.0f / sqrtf((float)hd);  // forward.rs:389
-        int mix_width = nq;                 // width of the vector the output projection consumes
+        int mix_width = P.attn_width;       // width of the vector the output projection consumes
         const tfr_mat* wout = L.wo;
         if (L.kind == LAYER_LINEAR) {
             // 1. norm + quant + [qkv | z | beta | alpha] projections (layer.rs:736-798)
@@ -683,13 +824,13 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
             qa.gate_out = e->qgate;
             qa.kc = kv->k + (size_t)li * kv->layer_stride;
             qa.vc = kv->v + (size_t)li * kv->layer_stride;
-            qa.n_head = c.n_head;
-            qa.n_kv = c.n_kv_head;
+            qa.n_head = P.n_head;
+            qa.n_kv = P.n_kv;
             qa.hd = hd;
             qa.n_rot = (c.rope_dim > 0 && c.rope_dim < hd) ? c.rope_dim : hd;
             qa.theta = c.rope_theta;
             qa.eps = c.rms_eps;
-            k_qk_norm_rope_store<<<c.n_head + c.n_kv_head, 256, 0, s>>>(qa, e->st);
+            k_qk_norm_rope_store<<<P.n_head + P.n_kv, 256, 0, s>>>(qa, e->st);
             if (cudaGetLastError() != cudaSuccess) return -1;
             n++;
             // 3. attention with the sigmoid output gate (layer.rs:646-659)
@@ -719,15 +860,9 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
             if (launch_attention(s, a, hd, e->st) != cudaSuccess) return -1;
             n++;
         }
-        {  // output projection of the mixer + residual
-            PrepArgs pa{};
-            pa.vec = e->attn;
-            EpiStore epi{e->x, nullptr, 2, K};
-            if (launch_typed(s, cap, wout->m.type, pa, make_job(wout->m, 2, cap), RowJob{}, F32Seg{}, epi, mix_width, e->st) !=
-                cudaSuccess)
-                return -1;
-            n++;
-        }
+        // output projection of the mixer + residual
+        if (launch_residual(wout, e->attn, mix_width, 2 * li) != cudaSuccess) return -1;
+        n++;
         {  // 4. norm + quant + gate/up + silu*mul
             PrepArgs pa{};
             pa.vec = e->x;
@@ -739,15 +874,9 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
                 return -1;
             n++;
         }
-        {  // 5. down + residual
-            PrepArgs pa{};
-            pa.vec = e->h;
-            EpiStore epi{e->x, nullptr, 2, K};
-            if (launch_typed(s, cap, L.down->m.type, pa, make_job(L.down->m, 2, cap), RowJob{}, F32Seg{}, epi, FF, e->st) !=
-                cudaSuccess)
-                return -1;
-            n++;
-        }
+        // 5. down + residual
+        if (launch_residual(L.down, e->h, FF, 2 * li + 1) != cudaSuccess) return -1;
+        n++;
         if (e->layer_taps &&
             cudaMemcpyAsync(e->layer_taps + (size_t)li * K, e->x, (size_t)K * 4, cudaMemcpyDeviceToDevice, s) != cudaSuccess)
             return -1;
@@ -761,12 +890,15 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
         epi.logits = e->logits;
         epi.out_tokens = e->out_tokens;
         epi.n_rows = V;
+        epi.row_offset = P.v0;
+        epi.use_tp = P.tp > 1;
+        epi.c = e->comm;
         if (launch_typed(s, cap, e->head->m.type, pa, make_job(e->head->m, 2, cap), RowJob{}, F32Seg{}, epi, K, e->st) !=
             cudaSuccess)
             return -1;
         n++;
     } else {
-        k_state_next_prompt<<<1, 1, 0, s>>>(e->st, e->prompt);
+        k_state_next_prompt<<<1, 1, 0, s>>>(e->st, e->prompt, P.tp > 1 ? e->comm.ops_per_token : 0);
         if (cudaGetLastError() != cudaSuccess) return -1;
         n++;
     }
@@ -840,6 +972,8 @@ static int finish_state(tfr_engine* e, int n_tokens_out) {
         CU(e, cudaMemcpyAsync(e->out_host, e->out_tokens, (size_t)n_tokens_out * 4, cudaMemcpyDeviceToHost, e->stream));
     CU(e, cudaStreamSynchronize(e->stream));
     cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1);
+    if (e->st_host->err == 3) return fail(e, TFR_E_CUDA, "tensor parallelism: a peer rank did not deliver within the wait limit");
+    if (e->st_host->err == 2) return fail(e, TFR_E_CUDA, "a weight tile copy did not complete");
     if (e->st_host->err) return fail(e, TFR_E_INVALID, "device reported an invalid token id");
     return TFR_OK;
 }
@@ -847,6 +981,7 @@ static int finish_state(tfr_engine* e, int n_tokens_out) {
 extern "C" int tfr_forward_greedy(tfr_engine* e, tfr_kv* kv, const uint32_t* tokens, int n, uint32_t* next_token) {
     if (!e || !kv || kv->e != e || !e->finalized) return e ? fail(e, TFR_E_INVALID, "forward_greedy: bad handle") : TFR_E_INVALID;
     if (n <= 0 || !tokens) return fail(e, TFR_E_EMPTY, "empty tokens");
+    if (e->plan.tp > 1 && !e->comm_attached) return fail(e, TFR_E_INVALID, "tensor-parallel ranks are not connected (tfr_tp_attach_*)");
     if (kv->len + n > kv->max_seq) return fail(e, TFR_E_FULL, "context full");
     if (n > TFR_MAX_PROMPT) return fail(e, TFR_E_INVALID, "more than %d tokens in one call", TFR_MAX_PROMPT);
     for (int i = 0; i < n; i++)
@@ -876,6 +1011,7 @@ extern "C" int tfr_decode_burst(tfr_engine* e, tfr_kv* kv, uint32_t first_token,
     if (!e || !kv || kv->e != e || !e->finalized || !out || !n_out)
         return e ? fail(e, TFR_E_INVALID, "decode_burst: bad argument") : TFR_E_INVALID;
     if (max_n <= 0) return fail(e, TFR_E_EMPTY, "empty tokens");
+    if (e->plan.tp > 1 && !e->comm_attached) return fail(e, TFR_E_INVALID, "tensor-parallel ranks are not connected (tfr_tp_attach_*)");
     if (n_stop < 0 || n_stop > 8) return fail(e, TFR_E_INVALID, "at most 8 stop ids");
     if (kv->len + 1 > kv->max_seq) return fail(e, TFR_E_FULL, "context full");
     if (first_token >= (uint32_t)e->token_embd->m.N) return fail(e, TFR_E_INVALID, "token id %u out of range", first_token);
@@ -905,9 +1041,80 @@ extern "C" int tfr_decode_burst(tfr_engine* e, tfr_kv* kv, uint32_t first_token,
 extern "C" int tfr_current_logits(tfr_engine* e, float* out, int n) {
     if (!e || !out || !e->finalized || n <= 0 || n > e->cfg.n_vocab) return e ? fail(e, TFR_E_INVALID, "current_logits: bad argument") : TFR_E_INVALID;
     cudaSetDevice(e->device);
-    CU(e, cudaMemcpyAsync(out, e->logits, (size_t)n * 4, cudaMemcpyDeviceToHost, e->stream));
+    const int first = e->plan.v0, end = e->plan.v1 < n ? e->plan.v1 : n;
+    if (end > first) CU(e, cudaMemcpyAsync(out + first, e->logits, (size_t)(end - first) * 4, cudaMemcpyDeviceToHost, e->stream));
     CU(e, cudaStreamSynchronize(e->stream));
     return TFR_OK;
+}
+
+// ------------------------------------------------------------------ tensor-parallel wiring
+
+extern "C" int tfr_tp_exchange_bytes(const tfr_engine* e, size_t* bytes) {
+    if (!e || !bytes || !e->finalized) return TFR_E_INVALID;
+    *bytes = e->plan.tp > 1 ? e->comm.lay.total : 0;
+    return TFR_OK;
+}
+extern "C" int tfr_tp_vocab_range(const tfr_engine* e, int* first, int* end) {
+    if (!e || !e->has_cfg) return TFR_E_INVALID;
+    if (first) *first = e->plan.v0;
+    if (end) *end = e->plan.v1;
+    return TFR_OK;
+}
+extern "C" int tfr_tp_ipc_handle(tfr_engine* e, void* handle_out) {
+    if (!e || !handle_out || !e->finalized || e->plan.tp < 2) return e ? fail(e, TFR_E_INVALID, "tp_ipc_handle: not a tensor-parallel engine") : TFR_E_INVALID;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size is part of the ABI");
+    cudaSetDevice(e->device);
+    cudaIpcMemHandle_t h;
+    CU(e, cudaIpcGetMemHandle(&h, e->comm_local));
+    memcpy(handle_out, &h, sizeof h);
+    return TFR_OK;
+}
+static int tp_finish_attach(tfr_engine* e) {
+    e->comm.base[e->plan.rank] = e->comm_local;
+    e->comm_attached = true;
+    drop_graphs(e);
+    return TFR_OK;
+}
+extern "C" int tfr_tp_attach_ipc(tfr_engine* e, const void* handles) {
+    if (!e || !handles || !e->finalized || e->plan.tp < 2) return e ? fail(e, TFR_E_INVALID, "tp_attach_ipc: not a tensor-parallel engine") : TFR_E_INVALID;
+    if (e->comm_attached) return fail(e, TFR_E_INVALID, "ranks already connected");
+    cudaSetDevice(e->device);
+    for (int r = 0; r < e->plan.tp; r++) {
+        if (r == e->plan.rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const uint8_t*)handles + (size_t)r * sizeof h, sizeof h);
+        void* ptr = nullptr;
+        CU(e, cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        e->comm.base[r] = (unsigned char*)ptr;
+    }
+    e->comm_ipc = true;
+    return tp_finish_attach(e);
+}
+extern "C" int tfr_tp_local_pointer(tfr_engine* e, void** ptr) {
+    if (!e || !ptr || !e->finalized || e->plan.tp < 2) return TFR_E_INVALID;
+    *ptr = e->comm_local;
+    return TFR_OK;
+}
+extern "C" int tfr_tp_attach_pointers(tfr_engine* e, void* const* bases) {
+    if (!e || !bases || !e->finalized || e->plan.tp < 2) return e ? fail(e, TFR_E_INVALID, "tp_attach_pointers: not a tensor-parallel engine") : TFR_E_INVALID;
+    if (e->comm_attached) return fail(e, TFR_E_INVALID, "ranks already connected");
+    cudaSetDevice(e->device);
+    for (int r = 0; r < e->plan.tp; r++) {
+        if (r == e->plan.rank) continue;
+        cudaPointerAttributes at{};
+        CU(e, cudaPointerGetAttributes(&at, bases[r]));
+        if (at.type != cudaMemoryTypeDevice) return fail(e, TFR_E_INVALID, "rank %d: not a device pointer", r);
+        if (at.device != e->device) {
+            int can = 0;
+            CU(e, cudaDeviceCanAccessPeer(&can, e->device, at.device));
+            if (!can) return fail(e, TFR_E_UNSUPPORTED, "device %d cannot access device %d", e->device, at.device);
+            cudaError_t r2 = cudaDeviceEnablePeerAccess(at.device, 0);
+            if (r2 != cudaSuccess && r2 != cudaErrorPeerAccessAlreadyEnabled) return fail(e, TFR_E_CUDA, "peer access: %s", cudaGetErrorString(r2));
+            cudaGetLastError();
+        }
+        e->comm.base[r] = (unsigned char*)bases[r];
+    }
+    return tp_finish_attach(e);
 }
 
 extern "C" int tfr_set_cuda_graph(tfr_engine* e, int enabled) {

@@ -388,4 +388,8 @@ inline Share make_share(int n, int C) {
     return s;
 }
 
+// An epilogue receives two finished dot products from exactly one thread: rows (2p, 2p+1) of a
+// matrix (EPI_PAIRS) or row p of two matrices walked together (EPI_ZIP).
+enum { EPI_PAIRS = 0, EPI_ZIP = 1 };
+
 }  // namespace tfr

@@ -3,14 +3,13 @@
 #include "tfr_attn.cuh"
 #include "tfr_gdn.cuh"
 #include "tfr_gemv.cuh"
+#include "tfr_tp.cuh"
 
 namespace tfr {
 
 // ------------------------------------------------------------------ epilogues
 //
-// An epilogue receives two finished dot products from exactly one thread: rows (2p, 2p+1) of a
-// matrix (EPI_PAIRS) or row p of two matrices walked together (EPI_ZIP).
-enum { EPI_PAIRS = 0, EPI_ZIP = 1 };
+// (EPI_PAIRS / EPI_ZIP are declared in tfr_gemv.cuh.)
 
 // y = W x (+y) (+bias): kernels/gemv.cu:367-373 residual rule (2 = accumulate in place).
 struct EpiStore {
@@ -101,11 +100,14 @@ struct EpiLogits {
     float* logits;
     int* out_tokens;   // ring of emitted tokens, indexed by TokenState::step
     int n_rows;
+    int row_offset;    // vocabulary id of local row 0 (vocabulary-parallel head)
+    int use_tp;
+    TpComm c;
     unsigned long long best;
     __device__ void begin(const TokenState*) { best = 0ull; }
     __device__ __forceinline__ void one(int row, float v) {
         logits[row] = v;
-        const unsigned long long k = argmax_key(v, row);
+        const unsigned long long k = argmax_key(v, row + row_offset);
         best = k > best ? k : best;
     }
     __device__ __forceinline__ void apply(int p, float v0, float v1) {
@@ -134,7 +136,15 @@ struct EpiLogits {
         __syncthreads();
         if (last && tid == 0) {
             __threadfence();
-            const unsigned long long b = atomicMax(&st->best, 0ull);
+            unsigned long long b = atomicMax(&st->best, 0ull);
+            if (use_tp) {
+                // every rank's local winner -> the global one, identical on all ranks
+                if (!tp_allreduce_best(c, st->ar_epoch + (unsigned)c.ops_per_token, b)) {
+                    st->err = 3;
+                    st->done = 1;
+                }
+                st->ar_epoch += (unsigned)c.ops_per_token;
+            }
             const int tok = argmax_key_index(b);
             const int step = st->step;
             out_tokens[step] = tok;
@@ -611,8 +621,9 @@ __global__ void k_state_begin(TokenState* st, const int* __restrict__ args) {
 }
 
 // Prefill by decode steps: after a head-less pass, feed the next prompt token.
-__global__ void k_state_next_prompt(TokenState* st, const int* prompt) {
+__global__ void k_state_next_prompt(TokenState* st, const int* prompt, int ar_ops) {
     if (st->done) return;
+    st->ar_epoch += (unsigned)ar_ops;  // tensor parallelism: keep the epoch numbering per token fixed
     st->prompt_idx += 1;
     st->pos += 1;
     st->token = prompt[st->prompt_idx];

@@ -170,9 +170,36 @@ class CudaModel:
         return out[: n.value].copy()
 
     def current_logits(self) -> np.ndarray:
+        """Logits of the last decoded position.  A tensor-parallel rank gets its own vocabulary
+        rows and zeros elsewhere (taraference_b200.tp.gather_logits merges the ranks)."""
         out = np.zeros(self.cfg["n_vocab"], np.float32)
         self._check(_lib.lib().tfr_current_logits(self._h, out.ctypes.data, out.size))
         return out
+
+    # -- tensor parallelism (one engine per GPU; see include/tarafer_b200.h) ---------------------------
+    def tp_vocab_range(self) -> tuple[int, int]:
+        a, b = C.c_int(), C.c_int()
+        self._check(_lib.lib().tfr_tp_vocab_range(self._h, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
+    def tp_ipc_handle(self) -> bytes:
+        buf = C.create_string_buffer(64)
+        self._check(_lib.lib().tfr_tp_ipc_handle(self._h, buf))
+        return buf.raw
+
+    def tp_attach_ipc(self, handles: list[bytes]) -> None:
+        blob = b"".join(handles)
+        assert len(blob) == 64 * len(handles)
+        self._check(_lib.lib().tfr_tp_attach_ipc(self._h, C.c_char_p(blob)))
+
+    def tp_local_pointer(self) -> int:
+        p = C.c_void_p()
+        self._check(_lib.lib().tfr_tp_local_pointer(self._h, C.byref(p)))
+        return p.value
+
+    def tp_attach_pointers(self, bases: list[int]) -> None:
+        arr = (C.c_void_p * len(bases))(*bases)
+        self._check(_lib.lib().tfr_tp_attach_pointers(self._h, arr))
 
     def launch_count(self) -> int:
         return int(_lib.lib().tfr_launch_count(self._h))
