@@ -9,13 +9,19 @@ resident in HBM (CUDA events around the kernels); `e2e` is the same count of tok
 the wall-clock time of the C-ABI call that takes its scalars from host memory and returns
 the tokens to host memory.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
 
 N > 1 runs N independent replicas (one process per GPU under torchrun): the decode loop
 of this model has no unit to shard without a per-layer exchange, which costs more than a
 layer's HBM time at this size.  `--impl reference` times the CPU restatement of the
 reference algorithm (the reference has no CPU path of its own for these kernels) on all
 host cores, on a bounded sample of the same workload.
+
+`--workload` selects one of the other BASELINE configurations instead (same JSON line, other
+`config.workload`): `3b-long` (16384-token prompt, ctx 32768, 512 decoded tokens), `hybrid-4b`
+(Gated-DeltaNet hybrid, 64-token prompt), `32b-tp` (Qwen2.5-32B shape, 128-token prompt; under
+torchrun the N ranks form ONE tensor-parallel engine: strong scaling, the value is not
+multiplied by N).
 """
 from __future__ import annotations
 
@@ -34,6 +40,21 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 PROMPT_LEN, N_DECODE, CTX = 32, 256, 4096
+# name -> (config attribute of taraference_b200.synth, prompt tokens, decoded tokens per step, ctx, description)
+WORKLOADS = {
+    "3b": ("QWEN25_3B", 32, 256, 4096,
+           "qwen2.5-3b-shape Q4_K_M, batch-1 greedy decode, 32-token prompt, 256 decoded tokens per step, ctx 4096 "
+           "(BASELINE configuration 2)"),
+    "3b-long": ("QWEN25_3B", 16384, 512, 32768,
+                "qwen2.5-3b-shape Q4_K_M, long-context flash-decode: 16384-token prompt in the fp16 KV cache, 512 decoded "
+                "tokens per step at positions 16384..16895, ctx 32768 (BASELINE configuration 3)"),
+    "hybrid-4b": ("QWEN35_4B", 64, 256, 4096,
+                  "qwen3.5-4b-style hybrid Q4_K_M (3 Gated-DeltaNet layers : 1 gated full-attention layer), 64-token prompt, "
+                  "256 decoded tokens per step (BASELINE configuration 4)"),
+    "32b-tp": ("QWEN25_32B", 128, 256, 4096,
+               "qwen2.5-32b-shape Q4_K_M, tensor-parallel over the ranks of the job, 128-token prompt, 256 decoded tokens "
+               "per step (BASELINE configuration 5)"),
+}
 METRIC, UNIT = "batch1_decode_tokens_per_s", "tok/s"
 NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate+up launch, from the ncu capture
@@ -259,6 +280,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-reference-gpu", action="store_true")
+    ap.add_argument("--workload", default="3b", choices=sorted(WORKLOADS))
     ap.add_argument("--roofline-only", action="store_true",
                     help="time only the fused gate+up kernel over 254 MB of weights (the small case used for ncu)")
     args = ap.parse_args()
@@ -281,9 +303,16 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     torch.cuda.set_device(local)
     warmup = max(args.warmup, 3)
-    cfg = dict(S.QWEN25_3B)
-    want_host = rank == 0 and world == 1 and not (args.skip_cpu_baseline and args.skip_reference_gpu)
-    model, host = synth_gpu.build_dense_model(cfg, seed=0, device=local, context_length=CTX, keep_host=want_host)
+    cfg_name, PROMPT_LEN, N_DECODE, CTX, workload_text = WORKLOADS[args.workload]
+    cfg = dict(getattr(S, cfg_name))
+    tp = world if args.workload == "32b-tp" else 1   # the ranks form one engine instead of N replicas
+    main_workload = args.workload == "3b"
+    want_host = main_workload and rank == 0 and world == 1 and not (args.skip_cpu_baseline and args.skip_reference_gpu)
+    build_cfg = dict(cfg, tp_rank=rank, tp_size=tp) if tp > 1 else cfg
+    model, host = synth_gpu.build_model(build_cfg, seed=0, device=local, context_length=CTX, keep_host=want_host)
+    if tp > 1:
+        from taraference_b200 import tp as TP
+        TP.connect(model, dist)
     kv = model.alloc_kv(CTX)
     rng = np.random.default_rng(0)
     prompt = rng.integers(0, cfg["n_vocab"], PROMPT_LEN)
@@ -295,6 +324,8 @@ def main():
         torch.cuda.synchronize()
 
     def one_step():
+        # every step restarts at the end of the prompt; a hybrid model's recurrent state simply carries on
+        # (its cost does not depend on the content)
         kv.len = PROMPT_LEN
         t0 = time.perf_counter()
         toks = model.decode_burst(first, N_DECODE, kv)
@@ -321,11 +352,13 @@ def main():
     launches = model.launch_count() - launches0
     agg = aggregate_over_ranks(float(np.sum(dev_ms)), float(np.sum(walls)), N_DECODE * args.steps, world,
                                dist if world > 1 else None, "cuda")
+    if tp > 1:  # one engine: every rank emitted the same tokens
+        agg["value"], agg["e2e"], agg["tokens"] = agg["value"] / world, agg["e2e"] / world, agg["tokens"] // world
     dev_total, wall_total, value, e2e_value = agg["dev_ms"], agg["wall_s"], agg["value"], agg["e2e"]
 
     # per-token host round-trip through forward_greedy (the reference's call pattern), rank 0 only
     per_token_api = None
-    if rank == 0:
+    if tp > 1 or rank == 0:  # a tensor-parallel engine needs every rank in every call
         kv.len = PROMPT_LEN
         t, t0 = first, time.perf_counter()
         for _ in range(64):
@@ -336,10 +369,10 @@ def main():
         peak, peak_kind = measured_peaks()
         wbytes = synth_gpu.weight_bytes(cfg)
         kvb = synth_gpu.kv_bytes_per_position(cfg)
-        bytes_per_token = wbytes + kvb * (PROMPT_LEN + N_DECODE / 2)
+        bytes_per_token = wbytes + kvb * (PROMPT_LEN + N_DECODE / 2) + synth_gpu.recurrent_state_bytes(cfg)
         us_tok = dev_total * 1000 / (N_DECODE * args.steps)
         token_gbs = bytes_per_token / us_tok * 1e-3
-        roof = gate_up_roofline(E, S, cfg, peak, peak_kind) if world == 1 else None
+        roof = gate_up_roofline(E, S, dict(S.QWEN25_3B), peak, peak_kind) if world == 1 and main_workload else None
         cpu = None
         if want_host and not args.skip_cpu_baseline:
             from oracle import oracle as O
@@ -352,13 +385,13 @@ def main():
             ref_gpu_info = reference_kernels_on_gpu(cfg, host, PROMPT_LEN)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
-            "ms_per_step": dev_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "int8", "data": "synthetic",
-            "config": {"workload": "qwen2.5-3b-shape Q4_K_M, batch-1 greedy decode, 32-token prompt, 256 decoded tokens "
-                                   "per step, ctx 4096 (BASELINE configuration 2)",
+            "ms_per_step": dev_total / args.steps, "higher_is_better": True, "scaling": "strong" if tp > 1 else "weak",
+            "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": workload_text,
                        "weights": "N(0,0.02) quantised on device; Q6_K token_embd/attn_v/ffn_down, Q4_K elsewhere",
-                       "l2": "each token streams 2.03 GB of weights, far beyond the 126 MB L2",
-                       "parallelism": "replicas" if world > 1 else "single GPU",
+                       "l2": f"each token streams {wbytes / 1e9:.2f} GB of weights, far beyond the 126 MB L2",
+                       "parallelism": f"tp{tp} (in-kernel all-reduce over NVLink peer memory)" if tp > 1 else
+                                      ("replicas" if world > 1 else "single GPU"),
                        "timing": "CUDA events on the engine's stream around each 256-token burst; max over ranks"},
             "us_per_token": us_tok,
             "token_roofline": {"bytes_per_token": bytes_per_token, "achieved_gbs": token_gbs,

@@ -4,9 +4,13 @@
 // launches one CTA per (query head, split) with 8 fixed splits, so every query head
 // re-reads the K/V rows of its KV head.  Here one CTA serves ALL query heads that share a
 // KV head (GQA group), so each K/V row is read from HBM once per token; the number of
-// splits is sized to the SM count and shrinks for short contexts, and the CTA that
-// finishes last for a KV head merges the (m, l, O) partials itself (no second launch).
-// Arithmetic is fp32 on f16 data as in the reference; exp is the build's ex2-based expf.
+// splits is sized to the SM count and shrinks for short contexts.  The splits of a KV head are
+// launched as thread-block clusters of eight: up to eight splits merge their (m, l, O) partials
+// through distributed shared memory behind one cluster barrier, each CTA of the cluster
+// finishing an eighth of the output dims (no global round trip, no second launch).  Longer
+// contexts use more splits; there the CTA that finishes last for a KV head merges the partials
+// from global memory.  Arithmetic is fp32 on f16 data as in the reference; exp is the build's
+// ex2-based expf.
 #pragma once
 #include "tfr_common.cuh"
 
@@ -15,18 +19,32 @@ namespace tfr {
 constexpr int ATTN_THREADS = 256;
 constexpr int ATTN_TILE = 64;     // keys per tile
 constexpr int ATTN_REP_MAX = 8;   // query heads per KV head handled by one CTA
+constexpr int ATTN_CLUSTER = 8;   // CTAs per cluster (the portable maximum); AttnArgs::S is a multiple of it
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Reads a float at the same shared-memory offset in CTA `rank` of this cluster.
+__device__ __forceinline__ float ld_dsmem_f32(const float* local, unsigned rank) {
+    unsigned remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
 
 struct AttnArgs {
     const float* q;             // [n_head * hd], RoPE applied
     const unsigned short* kc;   // layer base, [max_seq][n_kv * hd] f16 bits
     const unsigned short* vc;
-    float* partial;             // [n_head][S][2 + hd]
+    float* partial;             // [n_head][S][2 + hd] (contexts of more than 8 splits)
     unsigned int* counters;     // [n_kv], zero between launches
     float* out;                 // [n_head * hd]
     const float* gate;          // optional [n_head * hd]: out *= sigmoid(gate) (deltanet.cu:176-186)
     int n_head, n_kv, S, min_keys;
     float scale;
     int pos;                    // used when st == nullptr
+    int prof_id;                // timeline probe: which launch of the token this is (test aid)
 };
 
 // After the five butterfly steps lane L holds the sum over all lanes of v[L].
@@ -46,20 +64,28 @@ __device__ __forceinline__ float warp_transpose_reduce32(float (&v)[32], int lan
 
 template <int HD>
 __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const TokenState* st) {
+    prof_mark(0, a.prof_id);
+    griddep_wait();  // q and the new K/V row come from the previous kernel
+    griddep_launch_dependents();
+    prof_mark(1, a.prof_id);
     if (st && st->done) return;
     constexpr int DL = HD / 32;   // dims per lane in the score phase
     constexpr int DPT = HD / 64;  // dims per thread in the value phase
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = blockIdx.x / a.S, s = blockIdx.x % a.S;
+    const int g = blockIdx.y, s = blockIdx.x;  // grid (S, n_kv), clusters of ATTN_CLUSTER along x
     const int rep = a.n_head / a.n_kv;
     const int kvdim = a.n_kv * HD;
     const int T = (st ? st->pos : a.pos) + 1;
     int S_eff = (T + a.min_keys - 1) / a.min_keys;
     S_eff = S_eff < 1 ? 1 : (S_eff > a.S ? a.S : S_eff);
-    if (s >= S_eff) return;
+    // up to ATTN_CLUSTER splits: the first cluster of the KV head merges on chip; its idle members
+    // still attend the cluster barriers.  More splits: every CTA for itself, merge through memory.
+    const bool on_chip = S_eff > 1 && S_eff <= ATTN_CLUSTER;
+    if (on_chip ? s >= ATTN_CLUSTER : s >= S_eff) return;
+    const bool active = s < S_eff;
     const int chunk = (T + S_eff - 1) / S_eff;
-    const int t0 = s * chunk;
-    const int t1 = min(T, t0 + chunk);
+    const int t0 = min(T, s * chunk);
+    const int t1 = active ? min(T, t0 + chunk) : t0;
 
     __shared__ float sc[ATTN_REP_MAX][ATTN_TILE];
     __shared__ float m_s[ATTN_REP_MAX], l_s[ATTN_REP_MAX], alpha_s[ATTN_REP_MAX];
@@ -84,7 +110,22 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
     __syncthreads();
 
     const int kg = tid >> 6, dp = tid & 63;
+    constexpr int VK = ATTN_TILE / 4;  // keys per thread and tile in the value phase
     for (int tt = t0; tt < t1; tt += ATTN_TILE) {
+        // the tile's V rows do not depend on the scores: request them now, use them after the softmax
+        const int tn = min(ATTN_TILE, t1 - tt);
+        uint2 vraw[VK];
+#pragma unroll
+        for (int i = 0; i < VK; i++) {
+            const int k = kg + 4 * i;
+            vraw[i] = make_uint2(0u, 0u);
+            if (k < tn) {
+                const unsigned short* vr = a.vc + (size_t)(tt + k) * kvdim + g * HD + dp * DPT;
+                if constexpr (DPT == 4) vraw[i] = *reinterpret_cast<const uint2*>(vr);
+                else if constexpr (DPT == 2) vraw[i].x = *reinterpret_cast<const unsigned int*>(vr);
+                else vraw[i].x = *vr;
+            }
+        }
         // ---- scores: each warp takes two batches of four keys
 #pragma unroll
         for (int bt = 0; bt < 2; bt++) {
@@ -158,36 +199,31 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
 #pragma unroll
             for (int d = 0; d < DPT; d++) o[h][d] *= al;
         }
-        const int tn = min(ATTN_TILE, t1 - tt);
-        for (int k = kg; k < tn; k += 4) {
-            const unsigned short* vr = a.vc + (size_t)(tt + k) * kvdim + g * HD + dp * DPT;
-            float vf[DPT];
-            if constexpr (DPT == 2) {
-                const unsigned int raw = *reinterpret_cast<const unsigned int*>(vr);
-                vf[0] = f16_to_f32((unsigned short)(raw & 0xffff));
-                vf[1] = f16_to_f32((unsigned short)(raw >> 16));
-            } else if constexpr (DPT == 4) {
-                const uint2 raw = *reinterpret_cast<const uint2*>(vr);
-                vf[0] = f16_to_f32((unsigned short)(raw.x & 0xffff));
-                vf[1] = f16_to_f32((unsigned short)(raw.x >> 16));
-                vf[2] = f16_to_f32((unsigned short)(raw.y & 0xffff));
-                vf[3] = f16_to_f32((unsigned short)(raw.y >> 16));
-            } else {
 #pragma unroll
-                for (int d = 0; d < DPT; d++) vf[d] = f16_to_f32(vr[d]);
-            }
+        for (int i = 0; i < VK; i++) {
+            const int k = kg + 4 * i;
+            if (k < tn) {
+                float vf[DPT];
+                vf[0] = f16_to_f32((unsigned short)(vraw[i].x & 0xffff));
+                if constexpr (DPT >= 2) vf[1] = f16_to_f32((unsigned short)(vraw[i].x >> 16));
+                if constexpr (DPT == 4) {
+                    vf[2] = f16_to_f32((unsigned short)(vraw[i].y & 0xffff));
+                    vf[3] = f16_to_f32((unsigned short)(vraw[i].y >> 16));
+                }
 #pragma unroll
-            for (int h = 0; h < ATTN_REP_MAX; h++) {
-                if (h < rep) {
-                    const float p = sc[h][k];
+                for (int h = 0; h < ATTN_REP_MAX; h++) {
+                    if (h < rep) {
+                        const float p = sc[h][k];
 #pragma unroll
-                    for (int d = 0; d < DPT; d++) o[h][d] += p * vf[d];
+                        for (int d = 0; d < DPT; d++) o[h][d] += p * vf[d];
+                    }
                 }
             }
         }
         __syncthreads();
     }
 
+    prof_mark(2, a.prof_id);
     // ---- combine the four key groups and write this split's (m, l, O)
 #pragma unroll
     for (int h = 0; h < ATTN_REP_MAX; h++)
@@ -195,6 +231,34 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
         for (int d = 0; d < DPT; d++) ored[kg][h][dp * DPT + d] = o[h][d];
     __syncthreads();
     const int po = 2 + HD;
+    if (on_chip) {
+        // ored[0] <- this split's O (sum of its four key groups); idle members contribute l = 0
+        for (int idx = tid; idx < rep * HD; idx += ATTN_THREADS) {
+            const int h = idx / HD, d = idx % HD;
+            ored[0][h][d] = ored[0][h][d] + ored[1][h][d] + ored[2][h][d] + ored[3][h][d];
+        }
+        cluster_sync_all();
+        prof_mark(3, a.prof_id);
+        // member s finishes the dims idx with idx % ATTN_CLUSTER == s
+        for (int idx = s + ATTN_CLUSTER * tid; idx < rep * HD; idx += ATTN_CLUSTER * ATTN_THREADS) {
+            const int h = idx / HD, d = idx % HD;
+            const int hg = g * rep + h;
+            float m = -1e30f;
+            for (int r = 0; r < S_eff; r++) m = fmaxf(m, ld_dsmem_f32(&m_s[h], r));
+            float l = 0.f, acc = 0.f;
+            for (int r = 0; r < S_eff; r++) {
+                const float al = expf(ld_dsmem_f32(&m_s[h], r) - m);
+                l += al * ld_dsmem_f32(&l_s[h], r);
+                acc += al * ld_dsmem_f32(&ored[0][h][d], r);
+            }
+            float res = acc / fmaxf(l, 1e-20f);
+            if (a.gate) res *= 1.f / (1.f + expf(-a.gate[hg * HD + d]));
+            a.out[hg * HD + d] = res;
+        }
+        cluster_sync_all();  // nobody leaves while its shared memory may still be read
+        prof_mark(5, a.prof_id);
+        return;
+    }
     if (S_eff == 1) {
         // single split: normalise and store directly (the merge of one partial is the identity)
         for (int idx = tid; idx < rep * HD; idx += ATTN_THREADS) {
@@ -205,6 +269,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
             if (a.gate) r *= 1.f / (1.f + expf(-a.gate[hg * HD + d]));
             a.out[hg * HD + d] = r;
         }
+        prof_mark(5, a.prof_id);
         return;
     }
     for (int idx = tid; idx < rep * HD; idx += ATTN_THREADS) {
@@ -226,6 +291,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
         if (is_last_s) a.counters[g] = 0u;
     }
     __syncthreads();
+    prof_mark(3, a.prof_id);
     if (!is_last_s) return;
     __threadfence();
     for (int idx = tid; idx < rep * HD; idx += ATTN_THREADS) {
@@ -245,6 +311,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
         if (a.gate) r *= 1.f / (1.f + expf(-a.gate[hg * HD + d]));
         a.out[hg * HD + d] = r;
     }
+    prof_mark(5, a.prof_id);
 }
 
 }  // namespace tfr

@@ -110,6 +110,28 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, unsigned i
                  : "memory");
 }
 
+// Programmatic dependent launch (sm_90+): the first lets the next kernel in the stream start its
+// prologue, the second blocks until the previous kernel has completed and its writes are visible.
+// Both are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Optional timeline probe (test aid): when set, thread 0 of every CTA stores %globaltimer at eight
+// points of a kernel into g_prof[(launch id * 160 + cta) * 8 + point].
+__constant__ unsigned long long* g_prof = nullptr;
+__device__ __forceinline__ void prof_mark(int point, int kernel_id = 0) {
+    if (g_prof && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        g_prof[((size_t)kernel_id * 160 + blockIdx.y * gridDim.x + blockIdx.x) * 8 + point] = t;
+    }
+}
+
+// Asks the memory system to bring a range into L2 (no destination, no completion to wait for).
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, unsigned int bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
 // Device-resident decode state shared by every kernel of the token loop.  The host never
 // reads it while a burst is in flight; kernels read pos/token from here so one captured
 // graph serves every position (the reference's `_d` kernel variants do the same with

@@ -190,6 +190,12 @@ static void configure_kernels_once() {
     configure_kernel(k_state_next_prompt, false);
 }
 
+// Splits per KV head: a multiple of the cluster size, about one CTA per SM over all KV heads.
+static int attn_splits(int sms, int n_kv) {
+    const int s = sms / n_kv / ATTN_CLUSTER * ATTN_CLUSTER;
+    return s < ATTN_CLUSTER ? ATTN_CLUSTER : s;
+}
+
 static int sm_count_cached() {
     static int n = 0;
     if (!n) {
@@ -343,7 +349,6 @@ extern "C" int tfr_set_config(tfr_engine* e, const tfr_model_config* c) {
         if (c->n_head % tp || c->n_kv_head % tp)
             return fail(e, TFR_E_UNSUPPORTED, "tp_size %d does not divide %d query / %d KV heads", tp, c->n_head, c->n_kv_head);
         if (c->n_ff / 256 < tp || c->n_vocab < 2 * tp) return fail(e, TFR_E_UNSUPPORTED, "model too narrow for tp_size %d", tp);
-        if (e->prop.multiProcessorCount > TP_MAX_CTAS) return fail(e, TFR_E_UNSUPPORTED, "more than %d SMs", TP_MAX_CTAS);
     }
     e->cfg = *c;
     e->cfg.tp_size = tp;
@@ -606,8 +611,7 @@ extern "C" int tfr_finalize_load(tfr_engine* e) {
     e->held.clear();
     // workspaces (load.rs:547-607: everything allocated once)
     const int sms = e->prop.multiProcessorCount;
-    e->attn_S = sms / P.n_kv;
-    if (e->attn_S < 1) e->attn_S = 1;
+    e->attn_S = attn_splits(sms, P.n_kv);
     CU(e, cudaMalloc(&e->x, (size_t)K * 4));
     const int vd = c.hybrid ? gdn_val_dim(c) : 0;
     CU(e, cudaMalloc(&e->q, (size_t)nq * 4));
@@ -717,11 +721,22 @@ extern "C" int tfr_zero_recurrent(tfr_engine* e, tfr_kv* kv) {
 // ------------------------------------------------------------------ one token
 
 static cudaError_t launch_attention(cudaStream_t s, const AttnArgs& a, int hd, const TokenState* st) {
-    const int grid = a.n_kv * a.S;
-    if (hd == 64) k_attn_decode<64><<<grid, ATTN_THREADS, 0, s>>>(a, st);
-    else if (hd == 128) k_attn_decode<128><<<grid, ATTN_THREADS, 0, s>>>(a, st);
-    else k_attn_decode<256><<<grid, ATTN_THREADS, 0, s>>>(a, st);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(a.S, a.n_kv);
+    cfg.blockDim = dim3(ATTN_THREADS);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ATTN_CLUSTER;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = gemv_pdl_enabled() ? 2 : 1;
+    if (hd == 64) return cudaLaunchKernelEx(&cfg, k_attn_decode<64>, a, st);
+    if (hd == 128) return cudaLaunchKernelEx(&cfg, k_attn_decode<128>, a, st);
+    return cudaLaunchKernelEx(&cfg, k_attn_decode<256>, a, st);
 }
 
 template <class Epi>
@@ -743,6 +758,7 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
     auto launch_residual = [&](const tfr_mat* w, const float* vec, int width, int op_index) -> cudaError_t {
         PrepArgs pa{};
         pa.vec = vec;
+        pa.prof_id = n;
         const RowJob job = make_job(w->m, 2, cap);
         if (P.tp == 1) {
             EpiStore epi{e->x, nullptr, 2, K};
@@ -764,6 +780,7 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
         pn.normw = L.attn_norm;
         pn.eps = c.rms_eps;
         pn.raw_out = e->x;
+        pn.prof_id = n;
         AttnArgs a{};
         a.q = e->q;
         a.kc = kv->k + (size_t)li * kv->layer_stride;
@@ -777,6 +794,7 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
         a.S = e->attn_S;
         a.min_keys = e->attn_min_keys;
         a.scale = 1.0f / sqrtf((float)hd);  // forward.rs:389
+        a.prof_id = 0;
         int mix_width = P.attn_width;       // width of the vector the output projection consumes
         const tfr_mat* wout = L.wo;
         if (L.kind == LAYER_LINEAR) {
@@ -800,8 +818,7 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
             g.n_v = c.ssm_time_step_rank;
             g.kernel = c.ssm_conv_kernel;
             g.eps = c.rms_eps;
-            k_gdn_step<<<g.n_v, GDN_THREADS, 0, s>>>(g, e->st);
-            if (cudaGetLastError() != cudaSuccess) return -1;
+            if (launch_pdl(k_gdn_step, dim3(g.n_v), dim3(GDN_THREADS), 0, s, g, (const TokenState*)e->st) != cudaSuccess) return -1;
             n++;
             mix_width = gdn_val_dim(c);
             wout = L.ssm_out;
@@ -830,11 +847,12 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
             qa.n_rot = (c.rope_dim > 0 && c.rope_dim < hd) ? c.rope_dim : hd;
             qa.theta = c.rope_theta;
             qa.eps = c.rms_eps;
-            k_qk_norm_rope_store<<<P.n_head + P.n_kv, 256, 0, s>>>(qa, e->st);
-            if (cudaGetLastError() != cudaSuccess) return -1;
+            if (launch_pdl(k_qk_norm_rope_store, dim3(P.n_head + P.n_kv), dim3(256), 0, s, qa, (const TokenState*)e->st) != cudaSuccess)
+                return -1;
             n++;
             // 3. attention with the sigmoid output gate (layer.rs:646-659)
             a.gate = e->qgate;
+            a.prof_id = n;
             if (launch_attention(s, a, hd, e->st) != cudaSuccess) return -1;
             n++;
         } else {
@@ -857,6 +875,7 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
             if (launch_gemv<BlockQ4, EpiQkv>(s, cap, pn, jq, jk, fseg, epi, K, e->st) != cudaSuccess) return -1;
             n++;
             // 2. attention
+            a.prof_id = n;
             if (launch_attention(s, a, hd, e->st) != cudaSuccess) return -1;
             n++;
         }
@@ -868,6 +887,7 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
             pa.vec = e->x;
             pa.normw = L.ffn_norm;
             pa.eps = c.rms_eps;
+            pa.prof_id = n;
             EpiSilu epi{e->h};
             if (launch_gemv<BlockQ4, EpiSilu>(s, cap, pa, make_job(L.gate->m, 1, cap), make_job(L.up->m, 1, cap), F32Seg{}, epi,
                                               K, e->st) != cudaSuccess)
@@ -886,6 +906,7 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
         pa.vec = e->x;
         pa.normw = e->output_norm;
         pa.eps = c.rms_eps;
+        pa.prof_id = n;
         EpiLogits epi{};
         epi.logits = e->logits;
         epi.out_tokens = e->out_tokens;
@@ -898,8 +919,9 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
             return -1;
         n++;
     } else {
-        k_state_next_prompt<<<1, 1, 0, s>>>(e->st, e->prompt, P.tp > 1 ? e->comm.ops_per_token : 0);
-        if (cudaGetLastError() != cudaSuccess) return -1;
+        if (launch_pdl(k_state_next_prompt, dim3(1), dim3(1), 0, s, e->st, (const int*)e->prompt,
+                       P.tp > 1 ? e->comm.ops_per_token : 0) != cudaSuccess)
+            return -1;
         n++;
     }
     return n;
@@ -1281,8 +1303,7 @@ static int op_attention_impl(const float* q, const uint16_t* kc, const uint16_t*
     static unsigned int* counters = nullptr;
     static size_t cap = 0;
     AttnArgs a{};
-    a.S = sm_count_cached() / n_kv;
-    if (a.S < 1) a.S = 1;
+    a.S = attn_splits(sm_count_cached(), n_kv);
     const size_t need = (size_t)n_head * a.S * (2 + head_dim) * 4;
     if (need > cap || !counters) {
         cudaFree(partial);
@@ -1391,8 +1412,7 @@ extern "C" int tfr_op_attention_noalloc(const float* q, const uint16_t* kc, cons
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= TFR_NOALLOC_MAX_DEVICES) return TFR_E_CUDA;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return TFR_E_CUDA;
     AttnArgs a{};
-    a.S = sms / n_kv;
-    if (a.S < 1) a.S = 1;
+    a.S = attn_splits(sms, n_kv);
     const size_t need = (size_t)n_head * a.S * (2 + head_dim) * sizeof(float);
     if ((size_t)n_kv * sizeof(unsigned int) > TFR_NOALLOC_COUNTER_BYTES || need > TFR_NOALLOC_SCRATCH_BYTES - TFR_NOALLOC_COUNTER_BYTES) {
         fprintf(stderr,

@@ -52,6 +52,8 @@ __device__ __forceinline__ float gdn_conv_channel(const GdnArgs& a, int c, int c
 }
 
 __global__ void __launch_bounds__(GDN_THREADS, 1) k_gdn_step(GdnArgs a, const TokenState* st) {
+    griddep_wait();  // the projections come from the previous kernel
+    griddep_launch_dependents();
     if (st && st->done) return;
     constexpr int D = GDN_D, R = D / GDN_PARTS;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -151,6 +153,8 @@ struct QkNormArgs {
 };
 
 __global__ void __launch_bounds__(256) k_qk_norm_rope_store(QkNormArgs a, const TokenState* st) {
+    griddep_wait();
+    griddep_launch_dependents();
     if (st && st->done) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int head = blockIdx.x, hd = a.hd;

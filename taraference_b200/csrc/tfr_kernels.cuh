@@ -162,17 +162,6 @@ struct EpiLogits {
 
 // ------------------------------------------------------------------ the GEMV kernel
 
-// Optional timeline probe (test aid): when set, thread 0 of every CTA stores %globaltimer at eight
-// points of k_gemv into g_prof[cta * 8 + point].
-__constant__ unsigned long long* g_prof = nullptr;
-__device__ __forceinline__ void prof_mark(int point) {
-    if (g_prof && threadIdx.x == 0) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        g_prof[blockIdx.x * 8 + point] = t;
-    }
-}
-
 struct PrepArgs {
     const float* vec;     // source vector; nullptr -> embedding row of TokenState::token
     Mat embed;
@@ -180,6 +169,7 @@ struct PrepArgs {
     float eps;
     float* raw_out;       // embedding source only: CTA 0 stores the decoded row here (residual stream)
     int token;            // embedding source without TokenState
+    int prof_id;          // timeline probe: which launch of the token this is (test aid)
 };
 
 // A matrix whose rows are spread over the CTAs in contiguous shares of `rows_per_item` rows.
@@ -200,14 +190,20 @@ struct F32Seg {
 
 // Shared-memory map of k_gemv:
 //   [ Act | partial sums (pbuf_floats) | 272 floats | full[slots] mbarriers | tile slots ].
-constexpr size_t GEMV_SMEM_MAX = 225 * 1024;  // opt-in limit is 227 KB including the kernels' small static arrays
-inline size_t gemv_smem_fixed(int K, bool has_norm, int pbuf_floats) {
-    size_t act_bytes = (act_smem_bytes(K, true, has_norm) + 15) & ~(size_t)15;
+// A CTA takes at most half an SM (threads, registers, shared memory), so that the CTAs of the
+// NEXT kernel of the token loop can become resident while this one still runs: launched with
+// programmatic stream serialisation, they request their first weight tiles and then sleep in
+// griddepcontrol.wait until this kernel's results are complete.  HBM keeps streaming across the
+// kernel boundary although every kernel depends on its predecessor's output.
+constexpr size_t GEMV_SMEM_MAX = 112 * 1024;
+constexpr int GEMV_L2_AHEAD = 4;  // tiles per warp requested into L2 beyond the one in its ring slot
+inline size_t gemv_smem_fixed(int K, bool with_xf, bool has_norm, int pbuf_floats) {
+    size_t act_bytes = (act_smem_bytes(K, with_xf, has_norm) + 15) & ~(size_t)15;
     return act_bytes + (size_t)pbuf_floats * sizeof(float) + 272 * sizeof(float);
 }
 inline int gemv_pbuf_floats(int rows_a, int rows_b, int nb) {
     const int need = (rows_a + rows_b) * nb;
-    return need > 4096 ? ((need + 3) & ~3) : 4096;
+    return need > 1024 ? ((need + 3) & ~3) : 1024;
 }
 
 // Row sums from the per-block partials and the epilogue.  LPR lanes add up one row.
@@ -251,7 +247,7 @@ __device__ __forceinline__ void reduce_rows(const float* pa, const float* pb, in
     }
 }
 
-// One CTA of 1024 threads per SM.  The weight tiles of the CTA's rows are pulled into
+// One CTA of 512 threads per SM (two kernels of the loop can share an SM).  The weight tiles of the CTA's rows are pulled into
 // shared memory by bulk copies (TMA, one 4.5 / 6.6 KB request per tile).  Every warp requests
 // its own tiles at kernel entry (one issuing thread cannot keep HBM busy: a thread issues
 // only a few copies per microsecond), so they stream from HBM while all warps stage,
@@ -261,15 +257,18 @@ __device__ __forceinline__ void reduce_rows(const float* pa, const float* pb, in
 // the CTA has more tiles than slots (the vocabulary head), a warp owns one slot and refills
 // it itself after each tile.
 template <class BLK, class Epi>
-__global__ void __launch_bounds__(GEMV_THREADS, 1)
+__global__ void __launch_bounds__(GEMV_THREADS, 2)
 k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pbuf_floats, int slots, TokenState* st) {
     extern __shared__ __align__(128) unsigned char smem[];
-    prof_mark(0);
+    prof_mark(0, pa.prof_id);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, cta = blockIdx.x;
     const bool has_norm = pa.normw != nullptr;
+    // the fp32 copy of the vector is staged only where something reads it back: the norm's reduction,
+    // the fp32-route rows, the embedding source
+    const bool with_xf = has_norm || fseg.m.data != nullptr || pa.vec == nullptr;
     Epi epi = epi_in;
-    Act act = act_carve(smem, K, true, has_norm);
-    const size_t act_bytes = (act_smem_bytes(K, true, has_norm) + 15) & ~(size_t)15;
+    Act act = act_carve(smem, K, with_xf, has_norm);
+    const size_t act_bytes = (act_smem_bytes(K, with_xf, has_norm) + 15) & ~(size_t)15;
     float* pbuf = reinterpret_cast<float*>(smem + act_bytes);
     float* red = pbuf + pbuf_floats;
     unsigned long long* full = reinterpret_cast<unsigned long long*>(red + 272);
@@ -304,21 +303,7 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
         bulk_load(ring + (size_t)s * TB, job_src(j), TB, full + s);
     };
 
-    // The activation is requested first so that its loads are ahead of the bulk tile copies in the
-    // memory system's queues; the copies are issued while those loads are in flight.
-    constexpr int STAGE_REGS = 4;  // float4 per thread held in registers: K <= 16384
-    float4 sx[STAGE_REGS], sw[STAGE_REGS];
-    const int done = st ? st->done : 0;
-    if (pa.vec) {
-#pragma unroll
-        for (int k = 0; k < STAGE_REGS; k++) {
-            const int i4 = tid + k * GEMV_THREADS;
-            if (i4 < (K >> 2)) {
-                sx[k] = reinterpret_cast<const float4*>(pa.vec)[i4];
-                if (has_norm) sw[k] = reinterpret_cast<const float4*>(pa.normw)[i4];
-            }
-        }
-    }
+    // Weights do not depend on the previous kernel: every warp requests its first tiles at once.
     if (lane == 0 && warp < stride) {
         for (int j = warp; j < n_jobs; j += stride) {
             mbar_init(full + (reuse ? warp : j), 1);
@@ -329,36 +314,90 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
             issue(j);
             if (reuse) break;
         }
+        // The ring holds one tile per warp: too few bytes in flight to keep HBM busy.  The warp's
+        // next tiles are therefore pulled into L2 ahead of time; its refills then hit L2.
+        if (reuse)
+            for (int k = 1; k <= GEMV_L2_AHEAD && warp + k * stride < n_jobs; k++) bulk_prefetch_l2(job_src(warp + k * stride), TB);
+    }
+    if (fseg.m.data && tid == GEMV_THREADS - 1) {
+        // the fp32-route rows are read with plain loads later: have their tiles in L2 by then
+        const long long f0 = 2ll * fseg.sh.begin(cta) * nb, f1 = f0 + 2ll * fseg.sh.count(cta) * nb;
+        if (f1 > f0) {
+            const long long t0 = f0 >> 5, t1 = (f1 + 31) >> 5;
+            bulk_prefetch_l2(fseg.m.data + t0 * Q6_TILE_BYTES, (unsigned)((t1 - t0) * Q6_TILE_BYTES));
+        }
     }
     __syncwarp();
-    prof_mark(1);
-    const bool want_xf = fseg.m.data != nullptr;  // only fp32-route rows read the staged vector afterwards
-    const bool from_regs = pa.vec != nullptr && K <= STAGE_REGS * GEMV_THREADS * 4;
-    if (pa.vec) {
-        if (has_norm || want_xf || !from_regs) {
+    prof_mark(1, pa.prof_id);
+    // Everything below reads what earlier kernels wrote (the vector, the decode state).
+    griddep_wait();
+    // Only now may the next kernel start its prologue: its bulk weight requests then queue behind this
+    // kernel's own latency-critical loads instead of in front of them, and never run two kernels ahead.
+    griddep_launch_dependents();
+    const int done = st ? st->done : 0;
+    constexpr int STAGE_REGS = 6;  // float4 per thread and pass: one pass up to K = 12288
+    const int n4 = K >> 2;
+    float scale = 1.f;
+    if (pa.vec && !with_xf) {
+        // plain vector: quantise pass by pass straight from the registers that fetched it
+        if (!done) {
+            for (int base = 0; base < n4; base += STAGE_REGS * GEMV_THREADS) {
+                float4 sx[STAGE_REGS];
 #pragma unroll
-            for (int k = 0; k < STAGE_REGS; k++) {
-                const int i4 = tid + k * GEMV_THREADS;
-                if (i4 < (K >> 2)) *reinterpret_cast<float4*>(xs + xs_idx(4 * i4)) = sx[k];
+                for (int k = 0; k < STAGE_REGS; k++) {
+                    const int i4 = base + k * GEMV_THREADS + tid;
+                    sx[k] = i4 < n4 ? reinterpret_cast<const float4*>(pa.vec)[i4] : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int k = 0; k < STAGE_REGS; k++) {
+                    const int i4 = base + k * GEMV_THREADS + tid;
+                    if (base + k * GEMV_THREADS < n4) act_quantize4(act, sx[k], i4, i4 < n4, nb);
+                }
             }
-            for (int i4 = tid + STAGE_REGS * GEMV_THREADS; i4 < (K >> 2); i4 += GEMV_THREADS)
-                *reinterpret_cast<float4*>(xs + xs_idx(4 * i4)) = reinterpret_cast<const float4*>(pa.vec)[i4];
         }
+        prof_mark(2, pa.prof_id);
+        prof_mark(6, pa.prof_id);
     } else {
-        int tok = st ? st->token : pa.token;
-        if (tok < 0 || tok >= pa.embed.N) {
-            if (st && tid == 0) st->err = 1;
-            tok = 0;
+        if (pa.vec) {
+            for (int i4 = tid; i4 < n4; i4 += GEMV_THREADS)
+                *reinterpret_cast<float4*>(xs + xs_idx(4 * i4)) = reinterpret_cast<const float4*>(pa.vec)[i4];
+        } else {
+            int tok = st ? st->token : pa.token;
+            if (tok < 0 || tok >= pa.embed.N) {
+                if (st && tid == 0) st->err = 1;
+                tok = 0;
+            }
+            const SrcEmbed src{pa.embed, tok};
+            for (int i = tid; i < K; i += GEMV_THREADS) {
+                const float v = src.get(i);
+                xs[xs_idx(i)] = v;
+                if (cta == 0 && pa.raw_out && !done) pa.raw_out[i] = v;
+            }
         }
-        const SrcEmbed src{pa.embed, tok};
-        for (int i = tid; i < K; i += GEMV_THREADS) {
-            const float v = src.get(i);
-            xs[xs_idx(i)] = v;
-            if (cta == 0 && pa.raw_out && !done) pa.raw_out[i] = v;
+        __syncthreads();
+        prof_mark(2, pa.prof_id);
+        if (!done) {
+            if (has_norm) scale = rms_scale_staged(xs, K, pa.eps, red);
+            prof_mark(6, pa.prof_id);
+            for (int k0 = 0; k0 < n4; k0 += GEMV_THREADS) {
+                const int i4 = k0 + tid;
+                const bool on = i4 < n4;
+                float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (on) {
+                    x = *reinterpret_cast<const float4*>(xs + xs_idx(4 * i4));
+                    if (has_norm) {
+                        const float4 w = reinterpret_cast<const float4*>(pa.normw)[i4];
+                        x.x = x.x * scale * w.x;
+                        x.y = x.y * scale * w.y;
+                        x.z = x.z * scale * w.z;
+                        x.w = x.w * scale * w.w;
+                        if (fseg.m.data) *reinterpret_cast<float4*>(xs + xs_idx(4 * i4)) = x;
+                    }
+                }
+                act_quantize4(act, x, i4, on, nb);
+            }
         }
     }
-    __syncthreads();  // also publishes the initialised mbarriers to the consumer warps
-    prof_mark(2);
     if (done) {
         // the copies already in flight must land before the CTA's shared memory is released
         if (lane == 0 && warp < stride)
@@ -368,39 +407,10 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
             }
         return;
     }
-    float scale = 1.f;
-    if (has_norm) scale = rms_scale_staged(xs, K, pa.eps, red);
-    prof_mark(6);
-    // quantise: straight from the registers that fetched the vector when it fits, else from the staged copy
-    for (int k0 = 0; k0 < (K >> 2); k0 += GEMV_THREADS) {
-        const int i4 = k0 + tid, kk = k0 / GEMV_THREADS;
-        const bool on = i4 < (K >> 2);
-        float4 x = make_float4(0.f, 0.f, 0.f, 0.f), w = make_float4(1.f, 1.f, 1.f, 1.f);
-        if (from_regs) {
-#pragma unroll
-            for (int k = 0; k < STAGE_REGS; k++)
-                if (k == kk) {
-                    x = sx[k];
-                    w = sw[k];
-                }
-            if (!on) x = make_float4(0.f, 0.f, 0.f, 0.f);
-        } else if (on) {
-            x = *reinterpret_cast<const float4*>(xs + xs_idx(4 * i4));
-            if (has_norm) w = reinterpret_cast<const float4*>(pa.normw)[i4];
-        }
-        if (has_norm) {
-            x.x = x.x * scale * w.x;
-            x.y = x.y * scale * w.y;
-            x.z = x.z * scale * w.z;
-            x.w = x.w * scale * w.w;
-            if (want_xf && on) *reinterpret_cast<float4*>(xs + xs_idx(4 * i4)) = x;
-        }
-        act_quantize4(act, x, i4, on, nb);
-    }
-    prof_mark(7);
+    prof_mark(7, pa.prof_id);
     epi.begin(st);
     __syncthreads();
-    prof_mark(3);
+    prof_mark(3, pa.prof_id);
 
     // rows on the fp32 activation route: one task per (row, block, run of 16), all threads
     if (fseg.m.data) {
@@ -452,12 +462,13 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
             if (reuse && lane == 0 && j + stride < n_jobs) {
                 fence_proxy_async();
                 issue(j + stride);
+                if (j + (GEMV_L2_AHEAD + 1) * stride < n_jobs) bulk_prefetch_l2(job_src(j + (GEMV_L2_AHEAD + 1) * stride), TB);
             }
         }
     }
     if (!ok && st) st->err = 2;  // a bulk copy never completed: results of this step are invalid
     __syncthreads();
-    prof_mark(4);
+    prof_mark(4, pa.prof_id);
     // phase B: row sums in a fixed order + epilogue
     if (Epi::MODE == EPI_ZIP) {
         reduce_rows<EPI_ZIP>(part_a, part_b, rows_a, nb, ja.id_base + rows_a0, epi);
@@ -466,7 +477,28 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
         if (rows_b > 0) reduce_rows<EPI_PAIRS>(part_b, part_b, rows_b, nb, jb.id_base + (rows_b0 >> 1), epi);
     }
     epi.end(st);
-    prof_mark(5);
+    prof_mark(5, pa.prof_id);
+}
+
+// Set once per process: launch with programmatic stream serialisation (overlap with the previous kernel).
+inline bool& gemv_pdl_enabled() {
+    static bool on = true;
+    return on;
+}
+
+template <class... Args>
+inline cudaError_t launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = gemv_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
 template <class BLK, class Epi>
@@ -477,7 +509,9 @@ inline cudaError_t launch_gemv(cudaStream_t stream, int grid, const PrepArgs& pa
     const int ra = (ja.sh.quot + 1) * ja.rows_per_item, rb = jb.m.data ? (jb.sh.quot + 1) * jb.rows_per_item : 0;
     int pf = gemv_pbuf_floats(ra, rb, nb);
     if (fseg.m.data && pf < 2 * 16 * nb) pf = 2 * 16 * nb;
-    const size_t fixed = gemv_smem_fixed(K, pa.normw != nullptr, pf);
+    const bool has_norm = pa.normw != nullptr;
+    const bool with_xf = has_norm || fseg.m.data != nullptr || pa.vec == nullptr;  // as in the kernel
+    const size_t fixed = gemv_smem_fixed(K, with_xf, has_norm, pf);
     // tiles a CTA can need: each matrix's share may straddle one extra tile at either end
     const int need = (ra * nb + 31) / 32 + 1 + (rb ? (rb * nb + 31) / 32 + 1 : 0);
     if (fixed + 256 + 1024 + TB > GEMV_SMEM_MAX) return cudaErrorInvalidValue;
@@ -486,8 +520,7 @@ inline cudaError_t launch_gemv(cudaStream_t stream, int grid, const PrepArgs& pa
     else if (slots > GEMV_WARPS) slots = GEMV_WARPS;  // reuse: one slot per warp
     if (slots < 1) slots = 1;
     const size_t smem = fixed + (size_t)slots * 8 + 256 + (size_t)slots * TB;
-    k_gemv<BLK, Epi><<<grid, GEMV_THREADS, smem, stream>>>(pa, ja, jb, fseg, epi, K, pf, slots, st);
-    return cudaGetLastError();
+    return launch_pdl(k_gemv<BLK, Epi>, dim3(grid), dim3(GEMV_THREADS), smem, stream, pa, ja, jb, fseg, epi, K, pf, slots, st);
 }
 
 inline RowJob make_job(const Mat& m, int rows_per_item, int C, int id_base = 0) {
@@ -622,6 +655,7 @@ __global__ void k_state_begin(TokenState* st, const int* __restrict__ args) {
 
 // Prefill by decode steps: after a head-less pass, feed the next prompt token.
 __global__ void k_state_next_prompt(TokenState* st, const int* prompt, int ar_ops) {
+    griddep_wait();
     if (st->done) return;
     st->ar_epoch += (unsigned)ar_ops;  // tensor parallelism: keep the epoch numbering per token fixed
     st->prompt_idx += 1;
