@@ -126,10 +126,15 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
                 else vraw[i].x = *vr;
             }
         }
-        // ---- scores: each warp takes two batches of four keys
+        // ---- scores: batches of four keys; batch bt of warp w covers keys 32*bt + 4*w .., so a short
+        // tile spreads over all warps and its empty second batch is skipped
 #pragma unroll
         for (int bt = 0; bt < 2; bt++) {
-            const int kbase = (warp * 2 + bt) * 4;
+            const int kbase = (bt * 8 + warp) * 4;
+            if (kbase >= tn) {
+                if (kbase + (lane >> 3) < ATTN_TILE && (lane & 7) < ATTN_REP_MAX) sc[lane & 7][kbase + (lane >> 3)] = -1e30f;
+                continue;
+            }
             float v[32];
 #pragma unroll
             for (int kk = 0; kk < 4; kk++) {
@@ -202,6 +207,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
 #pragma unroll
         for (int i = 0; i < VK; i++) {
             const int k = kg + 4 * i;
+            if (4 * i >= tn) break;  // uniform: nothing left in this tile for any key group
             if (k < tn) {
                 float vf[DPT];
                 vf[0] = f16_to_f32((unsigned short)(vraw[i].x & 0xffff));

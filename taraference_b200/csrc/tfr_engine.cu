@@ -103,7 +103,7 @@ struct tfr_engine {
     TokenState* st_host = nullptr;  // pinned
     int *out_tokens = nullptr, *out_host = nullptr, *prompt = nullptr;
     int *args_dev = nullptr, *args_host = nullptr;  // per-call scalars: pinned host -> device
-    int attn_S = 1, attn_min_keys = 32;
+    int attn_S = 1, attn_min_keys = 64;
     float* layer_taps = nullptr;  // [n_layer][n_embd] residual stream after each layer (test aid)
     // graphs
     bool use_graph = true;
@@ -862,6 +862,9 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
             fseg.m = L.wv->m;
             fseg.sh = make_share(nkv / 2, cap);
             fseg.id_base = (nq + nkv) / 2;
+            pn.l2_rows_a = (const unsigned char*)(kv->k + (size_t)li * kv->layer_stride);
+            pn.l2_rows_b = (const unsigned char*)(kv->v + (size_t)li * kv->layer_stride);
+            pn.l2_row_bytes = nkv * 2;
             EpiQkv epi{};
             epi.q_out = e->q;
             epi.kc = kv->k + (size_t)li * kv->layer_stride;
@@ -1323,7 +1326,7 @@ static int op_attention_impl(const float* q, const uint16_t* kc, const uint16_t*
     a.n_head = n_head;
     a.n_kv = n_kv;
     a.gate = gate;
-    a.min_keys = 32;
+    a.min_keys = 64;
     a.scale = 1.0f / sqrtf((float)head_dim);
     a.pos = pos;
     return check(launch_attention((cudaStream_t)stream, a, head_dim, nullptr));
@@ -1440,7 +1443,7 @@ extern "C" int tfr_op_attention_noalloc(const float* q, const uint16_t* kc, cons
     a.out = out;
     a.n_head = n_head;
     a.n_kv = n_kv;
-    a.min_keys = 32;
+    a.min_keys = 64;
     a.scale = 1.0f / sqrtf((float)head_dim);
     a.pos = pos;
     return check(launch_attention(s, a, head_dim, nullptr));

@@ -30,7 +30,7 @@
 
 namespace tfr {
 
-constexpr int GEMV_THREADS = 512;  // half an SM's threads: see the note on co-residency in tfr_kernels.cuh
+constexpr int GEMV_THREADS = 1024;  // one CTA per SM
 constexpr int GEMV_WARPS = GEMV_THREADS / 32;
 constexpr int Q4_PIECES = 9, Q6_PIECES = 13;
 constexpr int Q4_TILE_BYTES = 32 * 144, Q6_TILE_BYTES = 32 * 210;

@@ -170,6 +170,11 @@ struct PrepArgs {
     float* raw_out;       // embedding source only: CTA 0 stores the decoded row here (residual stream)
     int token;            // embedding source without TokenState
     int prof_id;          // timeline probe: which launch of the token this is (test aid)
+    // rows [0, pos] of these two arrays (row_bytes each) are pulled into L2 for the kernel that follows
+    // (the layer's K and V cache before flash-decode); nullptr: none
+    const unsigned char* l2_rows_a;
+    const unsigned char* l2_rows_b;
+    int l2_row_bytes;
 };
 
 // A matrix whose rows are spread over the CTAs in contiguous shares of `rows_per_item` rows.
@@ -190,12 +195,13 @@ struct F32Seg {
 
 // Shared-memory map of k_gemv:
 //   [ Act | partial sums (pbuf_floats) | 272 floats | full[slots] mbarriers | tile slots ].
-// A CTA takes at most half an SM (threads, registers, shared memory), so that the CTAs of the
-// NEXT kernel of the token loop can become resident while this one still runs: launched with
-// programmatic stream serialisation, they request their first weight tiles and then sleep in
-// griddepcontrol.wait until this kernel's results are complete.  HBM keeps streaming across the
-// kernel boundary although every kernel depends on its predecessor's output.
-constexpr size_t GEMV_SMEM_MAX = 112 * 1024;
+// One CTA owns an SM (1024 threads, nearly all shared memory): 32 warps and up to ~46 tile slots
+// keep the dot phase at HBM speed.  (Half-SM CTAs, which would let the next kernel's CTA sit
+// beside this one and prefetch, were measured slower: fewer warps and slots cost more than the
+// overlap gained.)  Kernels are chained with programmatic stream serialisation: a CTA requests
+// its weight tiles, then sleeps in griddepcontrol.wait until the previous kernel's results are
+// complete, so launch latency and the first tiles' fetch hide behind the predecessor's tail.
+constexpr size_t GEMV_SMEM_MAX = 225 * 1024;  // opt-in limit is 227 KB including the kernels' small static arrays
 constexpr int GEMV_L2_AHEAD = 4;  // tiles per warp requested into L2 beyond the one in its ring slot
 inline size_t gemv_smem_fixed(int K, bool with_xf, bool has_norm, int pbuf_floats) {
     size_t act_bytes = (act_smem_bytes(K, with_xf, has_norm) + 15) & ~(size_t)15;
@@ -247,7 +253,7 @@ __device__ __forceinline__ void reduce_rows(const float* pa, const float* pb, in
     }
 }
 
-// One CTA of 512 threads per SM (two kernels of the loop can share an SM).  The weight tiles of the CTA's rows are pulled into
+// One CTA of 1024 threads per SM.  The weight tiles of the CTA's rows are pulled into
 // shared memory by bulk copies (TMA, one 4.5 / 6.6 KB request per tile).  Every warp requests
 // its own tiles at kernel entry (one issuing thread cannot keep HBM busy: a thread issues
 // only a few copies per microsecond), so they stream from HBM while all warps stage,
@@ -257,7 +263,7 @@ __device__ __forceinline__ void reduce_rows(const float* pa, const float* pb, in
 // the CTA has more tiles than slots (the vocabulary head), a warp owns one slot and refills
 // it itself after each tile.
 template <class BLK, class Epi>
-__global__ void __launch_bounds__(GEMV_THREADS, 2)
+__global__ void __launch_bounds__(GEMV_THREADS, 1)
 k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pbuf_floats, int slots, TokenState* st) {
     extern __shared__ __align__(128) unsigned char smem[];
     prof_mark(0, pa.prof_id);
@@ -314,10 +320,6 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
             issue(j);
             if (reuse) break;
         }
-        // The ring holds one tile per warp: too few bytes in flight to keep HBM busy.  The warp's
-        // next tiles are therefore pulled into L2 ahead of time; its refills then hit L2.
-        if (reuse)
-            for (int k = 1; k <= GEMV_L2_AHEAD && warp + k * stride < n_jobs; k++) bulk_prefetch_l2(job_src(warp + k * stride), TB);
     }
     if (fseg.m.data && tid == GEMV_THREADS - 1) {
         // the fp32-route rows are read with plain loads later: have their tiles in L2 by then
@@ -325,6 +327,30 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
         if (f1 > f0) {
             const long long t0 = f0 >> 5, t1 = (f1 + 31) >> 5;
             bulk_prefetch_l2(fseg.m.data + t0 * Q6_TILE_BYTES, (unsigned)((t1 - t0) * Q6_TILE_BYTES));
+        }
+    }
+    // RMSNorm weights are constants: fetch them before the wait (K <= 4 * threads on this path)
+    constexpr int NORM_REGS = 2;
+    float4 wreg[NORM_REGS];
+    if (has_norm) {
+#pragma unroll
+        for (int k = 0; k < NORM_REGS; k++) {
+            const int i4 = k * GEMV_THREADS + tid;
+            wreg[k] = i4 < (K >> 2) ? reinterpret_cast<const float4*>(pa.normw)[i4] : make_float4(1.f, 1.f, 1.f, 1.f);
+        }
+    }
+    if (pa.l2_rows_a && st && tid == GEMV_THREADS - 32) {
+        // A hint only: the position may still be the previous token's if the kernel before this one is the
+        // vocabulary head; a row more or less in L2 changes nothing but timing.
+        const int rows = st->pos + 1, per = (rows + (int)gridDim.x - 1) / (int)gridDim.x;
+        const int r0 = cta * per, r1 = min(rows, r0 + per);
+        if (r1 > r0) {
+            const size_t off = (size_t)r0 * pa.l2_row_bytes;
+            const unsigned bytes = (unsigned)((r1 - r0) * pa.l2_row_bytes) & ~15u;
+            if (bytes) {
+                bulk_prefetch_l2(pa.l2_rows_a + off, bytes);
+                bulk_prefetch_l2(pa.l2_rows_b + off, bytes);
+            }
         }
     }
     __syncwarp();
@@ -386,7 +412,9 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
                 if (on) {
                     x = *reinterpret_cast<const float4*>(xs + xs_idx(4 * i4));
                     if (has_norm) {
-                        const float4 w = reinterpret_cast<const float4*>(pa.normw)[i4];
+                        float4 w = wreg[0];
+                        if (k0 == GEMV_THREADS) w = wreg[1];
+                        if (k0 >= NORM_REGS * GEMV_THREADS) w = reinterpret_cast<const float4*>(pa.normw)[i4];
                         x.x = x.x * scale * w.x;
                         x.y = x.y * scale * w.y;
                         x.z = x.z * scale * w.z;
@@ -407,6 +435,11 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
             }
         return;
     }
+    // With a ring (one tile per warp) too few bytes are in flight to keep HBM busy: the warp's next
+    // tiles are pulled into L2 ahead of time and its refills then hit L2.  Requested only now, so that
+    // the bulk traffic queues behind the activation loads above, not in front of them.
+    if (reuse && lane == 0 && warp < stride)
+        for (int k = 1; k <= GEMV_L2_AHEAD && warp + k * stride < n_jobs; k++) bulk_prefetch_l2(job_src(warp + k * stride), TB);
     prof_mark(7, pa.prof_id);
     epi.begin(st);
     __syncthreads();
