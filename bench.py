@@ -272,6 +272,47 @@ def gate_up_roofline(E, S, cfg, peak_gbs, peak_kind):
             "note": "back-to-back launches on one stream: includes the launch gap"}
 
 
+def tensor_parallel_32b(rank, world, local, dist, steps: int = 2, warmup: int = 3):
+    """BASELINE configuration 5 as a side measurement of the default run: the Qwen2.5-32B shape with the
+    job's ranks as ONE tensor-parallel engine (a single GPU at N = 1).  All ranks call this."""
+    import torch
+    from taraference_b200 import synth as S, synth_gpu
+    cfg_name, prompt_len, n_decode, ctx, text = WORKLOADS["32b-tp"]
+    cfg = dict(getattr(S, cfg_name))
+    t_build = time.perf_counter()
+    build_cfg = dict(cfg, tp_rank=rank, tp_size=world) if world > 1 else cfg
+    model, _ = synth_gpu.build_model(build_cfg, seed=0, device=local, context_length=ctx)
+    if world > 1:
+        from taraference_b200 import tp as TP
+        TP.connect(model, dist)
+    kv = model.alloc_kv(ctx)
+    t_build = time.perf_counter() - t_build
+    prompt = np.random.default_rng(0).integers(0, cfg["n_vocab"], prompt_len)
+    first = model.forward_greedy(prompt, kv)
+    dev = []
+    for i in range(warmup + steps):
+        kv.len = prompt_len
+        if world > 1:
+            dist.barrier()
+        toks = model.decode_burst(first, n_decode, kv)
+        assert len(toks) == n_decode
+        if i >= warmup:
+            dev.append(model.last_device_ms())
+    total = float(np.sum(dev))
+    if world > 1:
+        t = torch.tensor([total], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total = float(t[0])
+    kv.free()
+    model.destroy()
+    us = total * 1000 / (n_decode * steps)
+    wbytes = synth_gpu.weight_bytes(cfg) + synth_gpu.kv_bytes_per_position(cfg) * (prompt_len + n_decode / 2)
+    return {"workload": text, "parallelism": f"tp{world}" if world > 1 else "single GPU", "scaling": "strong",
+            "tokens_per_s": 1e6 / us, "us_per_token": us, "steps": steps, "warmup": warmup,
+            "aggregate_weight_kv_gbs": wbytes / us * 1e-3, "build_s": t_build,
+            "timing": "CUDA events around each 256-token burst, max over ranks"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -281,6 +322,8 @@ def main():
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-reference-gpu", action="store_true")
     ap.add_argument("--workload", default="3b", choices=sorted(WORKLOADS))
+    ap.add_argument("--skip-32b", action="store_true",
+                    help="default workload only: leave out the 32B-shape tensor-parallel side measurement")
     ap.add_argument("--roofline-only", action="store_true",
                     help="time only the fused gate+up kernel over 254 MB of weights (the small case used for ncu)")
     args = ap.parse_args()
@@ -365,6 +408,12 @@ def main():
             t = model.forward_greedy([t], kv)
         per_token_api = 64 / (time.perf_counter() - t0)
 
+    tp32 = None
+    if main_workload and not args.skip_32b:
+        kv.free()
+        model.destroy()
+        kv = model = None
+        tp32 = tensor_parallel_32b(rank, world, local, dist if world > 1 else None)
     if rank == 0:
         peak, peak_kind = measured_peaks()
         wbytes = synth_gpu.weight_bytes(cfg)
@@ -372,7 +421,7 @@ def main():
         bytes_per_token = wbytes + kvb * (PROMPT_LEN + N_DECODE / 2) + synth_gpu.recurrent_state_bytes(cfg)
         us_tok = dev_total * 1000 / (N_DECODE * args.steps)
         token_gbs = bytes_per_token / us_tok * 1e-3
-        roof = gate_up_roofline(E, S, dict(S.QWEN25_3B), peak, peak_kind) if world == 1 and main_workload else None
+        roof = gate_up_roofline(E, S, dict(S.QWEN25_3B), peak, peak_kind) if main_workload else None
         cpu = None
         if want_host and not args.skip_cpu_baseline:
             from oracle import oracle as O
@@ -402,12 +451,14 @@ def main():
                     "call": "tfr_decode_burst: scalars from pinned host memory, tokens back to host memory",
                     "per_token_forward_greedy_tok_s": per_token_api},
             "gpu_launches": int(launches), "clocks": clocks, "reference_kernels_same_gpu": ref_gpu_info,
-            "wall_s_timed_region": wall_all,
+            "wall_s_timed_region": wall_all, "tensor_parallel_32b": tp32,
         }
         print(json.dumps(line), flush=True)
-    kv.free()
-    model.destroy()
+    if model is not None:
+        kv.free()
+        model.destroy()
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
