@@ -1301,6 +1301,7 @@ static int op_attention_impl(const float* q, const uint16_t* kc, const uint16_t*
     if (!q || !kc || !vc || !out || n_kv <= 0 || n_head % n_kv || n_head / n_kv > ATTN_REP_MAX || pos < 0) return TFR_E_INVALID;
     if (head_dim != 64 && head_dim != 128 && head_dim != 256) return TFR_E_UNSUPPORTED;
     if (n_kv > 64) return TFR_E_UNSUPPORTED;
+    configure_kernels_once();
     // scratch for the stand-alone call: partials + counters, grown on demand and kept
     static float* partial = nullptr;
     static unsigned int* counters = nullptr;

@@ -187,7 +187,11 @@ def test_ffn_block_config1_shape(E, oracle, R):
 
 
 @pytest.mark.parametrize("H,Hkv,hd,T", [(4, 2, 64, 1), (4, 2, 64, 70), (16, 2, 128, 33), (16, 2, 128, 700),
-                                        (40, 8, 128, 300), (16, 4, 256, 130), (5, 1, 128, 257)])
+                                        (40, 8, 128, 300), (16, 4, 256, 130), (5, 1, 128, 257),
+                                        # one split, a full cluster, cluster + second level, tiles of 512 keys
+                                        (16, 2, 128, 64), (16, 2, 128, 65), (16, 2, 128, 512), (16, 2, 128, 513),
+                                        (16, 2, 128, 4608), (16, 2, 128, 16896), (40, 8, 128, 9000), (16, 4, 256, 2500),
+                                        (6, 2, 64, 5000)])
 def test_flash_decode_vs_oracle_and_reference(E, oracle, H, Hkv, hd, T):
     rng = np.random.default_rng(H * 1000 + T)
     q = rng.normal(0, 1, H * hd).astype(np.float32)
