@@ -289,27 +289,41 @@ def tensor_parallel_32b(rank, world, local, dist, steps: int = 2, warmup: int = 
     t_build = time.perf_counter() - t_build
     prompt = np.random.default_rng(0).integers(0, cfg["n_vocab"], prompt_len)
     first = model.forward_greedy(prompt, kv)
-    dev = []
-    for i in range(warmup + steps):
-        kv.len = prompt_len
+
+    def timed_us_per_token():
+        dev = []
+        for i in range(warmup + steps):
+            kv.len = prompt_len
+            if world > 1:
+                dist.barrier()
+            toks = model.decode_burst(first, n_decode, kv)
+            assert len(toks) == n_decode
+            if i >= warmup:
+                dev.append(model.last_device_ms())
+        total = float(np.sum(dev))
         if world > 1:
-            dist.barrier()
-        toks = model.decode_burst(first, n_decode, kv)
-        assert len(toks) == n_decode
-        if i >= warmup:
-            dev.append(model.last_device_ms())
-    total = float(np.sum(dev))
+            t = torch.tensor([total], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            total = float(t[0])
+        return total * 1000 / (n_decode * steps)
+
+    us = timed_us_per_token()
+    nccl = None
     if world > 1:
-        t = torch.tensor([total], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total = float(t[0])
+        # comparison baseline: the same engine with ncclAllReduce between kernels instead of the in-kernel exchange
+        try:
+            TP.use_nccl(model, dist)
+            us_nccl = timed_us_per_token()
+            nccl = {"tokens_per_s": 1e6 / us_nccl, "us_per_token": us_nccl,
+                    "what": "row-parallel partial sums and the argmax through ncclAllReduce nodes in the same CUDA graph"}
+        except Exception as exc:  # the baseline is informative only
+            nccl = {"error": repr(exc)[:200]}
     kv.free()
     model.destroy()
-    us = total * 1000 / (n_decode * steps)
     wbytes = synth_gpu.weight_bytes(cfg) + synth_gpu.kv_bytes_per_position(cfg) * (prompt_len + n_decode / 2)
     return {"workload": text, "parallelism": f"tp{world}" if world > 1 else "single GPU", "scaling": "strong",
             "tokens_per_s": 1e6 / us, "us_per_token": us, "steps": steps, "warmup": warmup,
-            "aggregate_weight_kv_gbs": wbytes / us * 1e-3, "build_s": t_build,
+            "aggregate_weight_kv_gbs": wbytes / us * 1e-3, "build_s": t_build, "nccl_allreduce_baseline": nccl,
             "timing": "CUDA events around each 256-token burst, max over ranks"}
 
 

@@ -129,6 +129,13 @@ int tfr_tp_ipc_handle(tfr_engine* e, void* handle_out_64_bytes);
 int tfr_tp_attach_ipc(tfr_engine* e, const void* handles_rank_order);
 int tfr_tp_local_pointer(tfr_engine* e, void** ptr);
 int tfr_tp_attach_pointers(tfr_engine* e, void* const* bases_rank_order);
+/* Comparison baseline only: route the row-parallel partial sums and the argmax through ncclAllReduce
+ * between kernels (three graph nodes per all-reduce) instead of the in-kernel exchange.  libnccl.so.2
+ * is loaded at run time; TFR_E_UNSUPPORTED if it is absent.  Rank 0 obtains an id with
+ * tfr_tp_nccl_unique_id and hands it to all ranks; every rank then calls tfr_tp_use_nccl(e, id)
+ * (collective: ncclCommInitRank).  tfr_tp_use_nccl(e, NULL) returns to the in-kernel exchange. */
+int tfr_tp_nccl_unique_id(void* id_out_128_bytes);
+int tfr_tp_use_nccl(tfr_engine* e, const void* id_128_bytes);
 /* Vocabulary rows [first, end) whose logits this rank computes (all of them when tp_size == 1). */
 int tfr_tp_vocab_range(const tfr_engine* e, int* first, int* end);
 /* set_cuda_graph / graph_active / invalidate_decode_graph, model.rs:101-112,197 */

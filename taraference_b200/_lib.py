@@ -63,6 +63,8 @@ def lib() -> C.CDLL:
         "tfr_tp_local_pointer": (i32, [vp, C.POINTER(vp)]),
         "tfr_tp_attach_pointers": (i32, [vp, vp]),
         "tfr_tp_vocab_range": (i32, [vp, C.POINTER(i32), C.POINTER(i32)]),
+        "tfr_tp_nccl_unique_id": (i32, [vp]),
+        "tfr_tp_use_nccl": (i32, [vp, vp]),
         "tfr_set_cuda_graph": (i32, [vp, i32]),
         "tfr_graph_active": (i32, [vp]),
         "tfr_launch_count": (i64, [vp]),

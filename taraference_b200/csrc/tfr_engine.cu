@@ -16,6 +16,8 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <dlfcn.h>
+
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -64,6 +66,39 @@ struct VecT {
     int64_t n = 0;
 };
 
+// NCCL, loaded at run time and only for the comparison mode of the tensor-parallel engine (the product
+// path all-reduces inside its own kernels).  Minimal declarations of the stable NCCL 2.x C API.
+struct NcclId {  // ncclUniqueId: 128 opaque bytes, passed by value
+    char b[128];
+};
+struct NcclApi {
+    void* lib = nullptr;
+    int (*GetUniqueId)(void*) = nullptr;
+    int (*CommInitRank)(void**, int, NcclId, int) = nullptr;
+    int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*CommDestroy)(void*) = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+};
+constexpr int NCCL_UINT64 = 5, NCCL_FLOAT32 = 7, NCCL_SUM = 0, NCCL_MAX = 2;
+static NcclApi* nccl_api() {
+    static NcclApi api;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (h) {
+            api.lib = h;
+            api.GetUniqueId = (decltype(api.GetUniqueId))dlsym(h, "ncclGetUniqueId");
+            api.CommInitRank = (decltype(api.CommInitRank))dlsym(h, "ncclCommInitRank");
+            api.AllReduce = (decltype(api.AllReduce))dlsym(h, "ncclAllReduce");
+            api.CommDestroy = (decltype(api.CommDestroy))dlsym(h, "ncclCommDestroy");
+            api.GetErrorString = (decltype(api.GetErrorString))dlsym(h, "ncclGetErrorString");
+            if (!api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.CommDestroy) api.lib = nullptr;
+        }
+    }
+    return api.lib ? &api : nullptr;
+}
+
 // This rank's share of the model (Megatron split).  With tp == 1 it covers everything.
 struct TpPlan {
     int tp = 1, rank = 0;
@@ -88,6 +123,11 @@ struct tfr_engine {
     TpComm comm{};
     unsigned char* comm_local = nullptr;
     bool comm_attached = false, comm_ipc = false;
+    // comparison mode: partial sums through ncclAllReduce between kernels instead of the in-kernel exchange
+    void* nccl_comm = nullptr;
+    bool use_nccl = false;
+    float* ypart = nullptr;
+    unsigned long long* best_buf = nullptr;
     bool has_cfg = false, finalized = false;
     std::map<std::string, tfr_mat*> mats;
     std::map<std::string, VecT> vecs;
@@ -186,6 +226,8 @@ static void configure_kernels_once() {
     configure_kernel(k_attn_decode<256>, false);
     configure_kernel(k_gdn_step, false);
     configure_kernel(k_qk_norm_rope_store, false);
+    configure_kernel(k_state_advance, false);
+    configure_kernel(k_add_residual, false);
     configure_kernel(k_state_begin, false);
     configure_kernel(k_state_next_prompt, false);
 }
@@ -290,6 +332,9 @@ extern "C" void tfr_destroy(tfr_engine* e) {
     cudaSetDevice(e->device);
     cudaStreamSynchronize(e->stream);
     drop_graphs(e);
+    if (e->nccl_comm && nccl_api()) nccl_api()->CommDestroy(e->nccl_comm);
+    cudaFree(e->ypart);
+    cudaFree(e->best_buf);
     if (e->comm_ipc)
         for (int r = 0; r < e->plan.tp; r++)
             if (r != e->plan.rank && e->comm.base[r]) cudaIpcCloseMemHandle(e->comm.base[r]);
@@ -764,6 +809,16 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
             EpiStore epi{e->x, nullptr, 2, K};
             return launch_typed(s, cap, w->m.type, pa, job, RowJob{}, F32Seg{}, epi, width, e->st);
         }
+        if (e->use_nccl) {
+            // comparison baseline: partial y -> ncclAllReduce -> x += y, three nodes instead of one
+            EpiStore epi{e->ypart, nullptr, 0, K};
+            cudaError_t r = launch_typed(s, cap, w->m.type, pa, job, RowJob{}, F32Seg{}, epi, width, e->st);
+            if (r != cudaSuccess) return r;
+            if (nccl_api()->AllReduce(e->ypart, e->ypart, (size_t)K, NCCL_FLOAT32, NCCL_SUM, e->nccl_comm, s) != 0) return cudaErrorUnknown;
+            n += 2;
+            return launch_pdl(k_add_residual, dim3((K + 255) / 256), dim3(256), 0, s, e->x, (const float*)e->ypart, K,
+                              (const TokenState*)e->st);
+        }
         EpiAllReduce epi{};
         epi.x = e->x;
         epi.n_rows = K;
@@ -915,12 +970,20 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
         epi.out_tokens = e->out_tokens;
         epi.n_rows = V;
         epi.row_offset = P.v0;
-        epi.use_tp = P.tp > 1;
+        epi.use_tp = P.tp > 1 && !e->use_nccl;
         epi.c = e->comm;
+        epi.defer_best = P.tp > 1 && e->use_nccl ? e->best_buf : nullptr;
         if (launch_typed(s, cap, e->head->m.type, pa, make_job(e->head->m, 2, cap), RowJob{}, F32Seg{}, epi, K, e->st) !=
             cudaSuccess)
             return -1;
         n++;
+        if (epi.defer_best) {
+            if (nccl_api()->AllReduce(e->best_buf, e->best_buf, 1, NCCL_UINT64, NCCL_MAX, e->nccl_comm, s) != 0) return -1;
+            if (launch_pdl(k_state_advance, dim3(1), dim3(1), 0, s, e->st, (const unsigned long long*)e->best_buf, e->out_tokens) !=
+                cudaSuccess)
+                return -1;
+            n += 2;
+        }
     } else {
         if (launch_pdl(k_state_next_prompt, dim3(1), dim3(1), 0, s, e->st, (const int*)e->prompt,
                        P.tp > 1 ? e->comm.ops_per_token : 0) != cudaSuccess)
@@ -1140,6 +1203,35 @@ extern "C" int tfr_tp_attach_pointers(tfr_engine* e, void* const* bases) {
         e->comm.base[r] = (unsigned char*)bases[r];
     }
     return tp_finish_attach(e);
+}
+
+extern "C" int tfr_tp_nccl_unique_id(void* id_out_128_bytes) {
+    NcclApi* api = nccl_api();
+    if (!api || !id_out_128_bytes) return TFR_E_UNSUPPORTED;
+    return api->GetUniqueId(id_out_128_bytes) == 0 ? TFR_OK : TFR_E_CUDA;
+}
+extern "C" int tfr_tp_use_nccl(tfr_engine* e, const void* id_128_bytes) {
+    if (!e || !e->finalized || e->plan.tp < 2) return e ? fail(e, TFR_E_INVALID, "tp_use_nccl: not a tensor-parallel engine") : TFR_E_INVALID;
+    cudaSetDevice(e->device);
+    if (!id_128_bytes) {  // back to the in-kernel exchange
+        e->use_nccl = false;
+        drop_graphs(e);
+        return TFR_OK;
+    }
+    NcclApi* api = nccl_api();
+    if (!api) return fail(e, TFR_E_UNSUPPORTED, "libnccl.so.2 could not be loaded");
+    if (!e->nccl_comm) {
+        NcclId id;
+        memcpy(id.b, id_128_bytes, sizeof id.b);
+        const int rc = api->CommInitRank(&e->nccl_comm, e->plan.tp, id, e->plan.rank);
+        if (rc != 0) return fail(e, TFR_E_CUDA, "ncclCommInitRank: %s", api->GetErrorString ? api->GetErrorString(rc) : "error");
+        CU(e, cudaMalloc(&e->ypart, (size_t)e->cfg.n_embd * 4));
+        CU(e, cudaMalloc(&e->best_buf, 8));
+    }
+    e->use_nccl = true;
+    e->comm_attached = true;  // nothing else to wire in this mode
+    drop_graphs(e);
+    return TFR_OK;
 }
 
 extern "C" int tfr_set_cuda_graph(tfr_engine* e, int enabled) {

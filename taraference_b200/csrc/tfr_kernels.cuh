@@ -103,6 +103,8 @@ struct EpiLogits {
     int row_offset;    // vocabulary id of local row 0 (vocabulary-parallel head)
     int use_tp;
     TpComm c;
+    unsigned long long* defer_best;  // non-null: publish the local winner here and leave the state alone
+                                     // (a library all-reduce and k_state_advance finish the step)
     unsigned long long best;
     __device__ void begin(const TokenState*) { best = 0ull; }
     __device__ __forceinline__ void one(int row, float v) {
@@ -137,6 +139,12 @@ struct EpiLogits {
         if (last && tid == 0) {
             __threadfence();
             unsigned long long b = atomicMax(&st->best, 0ull);
+            if (defer_best) {
+                *defer_best = b;
+                st->best = 0ull;
+                st->head_done = 0u;
+                return;
+            }
             if (use_tp) {
                 // every rank's local winner -> the global one, identical on all ranks
                 if (!tp_allreduce_best(c, st->ar_epoch + (unsigned)c.ops_per_token, b)) {
@@ -684,6 +692,30 @@ __global__ void k_state_begin(TokenState* st, const int* __restrict__ args) {
     st->prompt_idx = 0;
     st->err = 0;
     st->ring_off = args[13];
+}
+
+// Second half of the vocabulary head when the (max, argmax) exchange is done by a library all-reduce:
+// publishes the token and advances the decode state (the tail of EpiLogits::end).
+__global__ void k_state_advance(TokenState* st, const unsigned long long* best, int* out_tokens) {
+    griddep_wait();
+    if (st->done) return;
+    const int tok = argmax_key_index(*best);
+    const int step = st->step;
+    out_tokens[step] = tok;
+    st->token = tok;
+    st->pos += 1;
+    st->step = step + 1;
+    int stop = (step + 1 >= st->max_steps) || (st->pos >= st->max_seq);
+    for (int i = 0; i < st->n_stop; i++) stop |= (st->stop_ids[i] == tok);
+    if (stop) st->done = 1;
+}
+
+// x += y (the residual add after a library all-reduce of the row-parallel partial sums)
+__global__ void k_add_residual(float* __restrict__ x, const float* __restrict__ y, int n, const TokenState* st) {
+    griddep_wait();
+    if (st && st->done) return;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += y[i];
 }
 
 // Prefill by decode steps: after a head-less pass, feed the next prompt token.

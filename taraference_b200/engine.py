@@ -192,6 +192,10 @@ class CudaModel:
         assert len(blob) == 64 * len(handles)
         self._check(_lib.lib().tfr_tp_attach_ipc(self._h, C.c_char_p(blob)))
 
+    def tp_use_nccl(self, unique_id: bytes | None) -> None:
+        """Comparison baseline: all-reduce through NCCL between kernels (collective call); None switches back."""
+        self._check(_lib.lib().tfr_tp_use_nccl(self._h, C.c_char_p(unique_id) if unique_id else None))
+
     def tp_local_pointer(self) -> int:
         p = C.c_void_p()
         self._check(_lib.lib().tfr_tp_local_pointer(self._h, C.byref(p)))
@@ -278,6 +282,12 @@ def op_attention_noalloc(q, kc, vc, out, n_head: int, n_kv: int, head_dim: int, 
     (2 MiB, shared by all calls; larger shapes raise).  Call it once per device before any stream capture."""
     _ok(_lib.lib().tfr_op_attention_noalloc(_ptr(q), _ptr(kc), _ptr(vc), _ptr(out), n_head, n_kv, head_dim, pos,
                                             stream), "attention_noalloc: shape exceeds the built-in scratch or CUDA error")
+
+
+def nccl_unique_id() -> bytes:
+    buf = C.create_string_buffer(128)
+    _ok(_lib.lib().tfr_tp_nccl_unique_id(buf), "nccl_unique_id: libnccl.so.2 not available")
+    return buf.raw
 
 
 def op_attention_gated(q, kc, vc, gate, out, n_head: int, n_kv: int, head_dim: int, pos: int, stream: int = 0) -> None:

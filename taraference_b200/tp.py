@@ -45,6 +45,19 @@ def connect(model, dist) -> None:
     dist.barrier()
 
 
+def use_nccl(model, dist, on: bool = True) -> None:
+    """Comparison baseline for measurements: the same engine with ncclAllReduce between kernels instead
+    of the in-kernel exchange.  All ranks call this."""
+    from . import engine as E
+    if not on:
+        model.tp_use_nccl(None)
+        return
+    box = [E.nccl_unique_id() if dist.get_rank() == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    model.tp_use_nccl(box[0])
+    dist.barrier()
+
+
 def gather_logits(model, dist) -> np.ndarray:
     """Full logits on every rank from the ranks' vocabulary slices (host side, not a hot path)."""
     parts = [None] * dist.get_world_size()

@@ -52,6 +52,20 @@ def _worker(rank, world, port, out, graph):
     res = dict(first=first, nxt=nxt, toks=toks, x=x, lx0=lx0, logits=logits, kv_len=kv.len,
                kv_bytes=kv.bytes_per_token(), vocab=m.tp_vocab_range())
     dist.barrier()
+    # the comparison mode (ncclAllReduce between kernels) must give the same tokens: with two ranks the sum
+    # a + b has one order only
+    try:
+        TP.use_nccl(m, dist)
+        kv.clear()
+        n2 = m.forward_greedy(PROMPT, kv)
+        res["nccl"] = dict(nxt=n2, toks=m.decode_burst(n2, 20, kv), x=m.debug_read("x", K))
+        TP.use_nccl(m, dist, on=False)
+        kv.clear()
+        n3 = m.forward_greedy(PROMPT, kv)
+        res["back"] = dict(nxt=n3, toks=m.decode_burst(n3, 20, kv))
+    except E.TfrError as exc:
+        res["nccl"] = dict(error=str(exc))
+    dist.barrier()
     if rank == 0:
         # the same model on one GPU, and the CPU oracle
         m1 = E.CudaModel.load_with(TP_CFG, tens, device=0)
@@ -102,6 +116,13 @@ def test_two_ranks_match_single_gpu_and_oracle(cuda_lib, graph):
     assert _rel(r0["logits"], s["logits"]) < 5e-2 and _rel(r0["logits"], o["logits"]) < 5e-2
     assert r0["first"] == s["first"]
     assert margin_gated_equal(r0["toks"], o["toks"], o["margins"]), (r0["toks"], o["toks"], o["margins"])
+    if "error" in r0["nccl"]:
+        assert "libnccl" in r0["nccl"]["error"], r0["nccl"]   # only a missing library excuses the baseline
+    else:
+        for r in (r0, r1):
+            assert r["nccl"]["nxt"] == r["nxt"] and np.array_equal(r["nccl"]["toks"], r["toks"])
+            assert np.array_equal(r["nccl"]["x"], r["x"])
+            assert r["back"]["nxt"] == r["nxt"] and np.array_equal(r["back"]["toks"], r["toks"])
 
 
 def test_missing_peer_ends_in_an_error_not_a_hang(cuda_lib):
