@@ -84,6 +84,34 @@ int tfr_upload_tensor(tfr_engine* e, const char* name, int ggml_type, int64_t n_
 /* End of load_with: checks every tensor the configuration needs is present, allocates workspaces. */
 int tfr_finalize_load(tfr_engine* e);
 
+/* ---- GGUF files: crates/gguf/src/reader.rs:29-215 (GgufFile), value.rs, types.rs; host code only ----
+ * tfr_gguf_open maps the file read-only and parses header, metadata and tensor table with the
+ * reference reader's rules (magic, version 2 or 3, count and n_dims limits, known tensor types,
+ * data section at the header's end rounded up to general.alignment (default 32), every tensor's
+ * bytes inside the file).  On failure *out is NULL and err receives the reason.  Pointers returned
+ * by the accessors live until tfr_gguf_close. */
+typedef struct tfr_gguf tfr_gguf;
+int tfr_gguf_open(const char* path, tfr_gguf** out, char* err, size_t err_cap);
+void tfr_gguf_close(tfr_gguf* g);
+int tfr_gguf_version(const tfr_gguf* g);
+uint64_t tfr_gguf_data_offset(const tfr_gguf* g);
+int64_t tfr_gguf_tensor_count(const tfr_gguf* g);
+int64_t tfr_gguf_find_tensor(const tfr_gguf* g, const char* name); /* index or -1 (GgufFile::tensor) */
+int tfr_gguf_tensor_info(const tfr_gguf* g, int64_t i, const char** name, int* ggml_type, int* n_dims, int64_t dims[4],
+                         uint64_t* offset, uint64_t* nbytes);
+const void* tfr_gguf_tensor_data(const tfr_gguf* g, int64_t i); /* GgufFile::tensor_data: the mapped bytes */
+/* Metadata with the reference's lenient coercions (Value::as_u64 / as_f32 / as_str, value.rs:55-100);
+ * a missing key or another kind of value returns TFR_E_INVALID.  Arrays are parsed but only counted. */
+int tfr_gguf_meta_u64(const tfr_gguf* g, const char* key, uint64_t* out);
+int tfr_gguf_meta_f32(const tfr_gguf* g, const char* key, float* out);
+int tfr_gguf_meta_str(const tfr_gguf* g, const char* key, const char** out);
+int64_t tfr_gguf_meta_array_len(const tfr_gguf* g, const char* key);
+/* ModelConfig::from_gguf, crates/core/src/config.rs:107-264: `<arch>.*` keys, defaults and the qwen35 extras. */
+int tfr_gguf_model_config(const tfr_gguf* g, tfr_model_config* out, char* err, size_t err_cap);
+/* CudaModel::load_with(gguf), load.rs:166-417: tfr_set_config from the metadata, tfr_upload_tensor for every
+ * tensor of the decode path straight from the mapping, tfr_finalize_load.  The file may be closed afterwards. */
+int tfr_load_gguf(tfr_engine* e, const tfr_gguf* g, int tp_rank, int tp_size);
+
 /* ---- KV cache: CudaKv, crates/core/src/cuda/kv.rs:6-42; alloc_kv model.rs:114-162 ---- */
 int tfr_alloc_kv(tfr_engine* e, int max_seq, tfr_kv** out);
 void tfr_free_kv(tfr_kv* kv);

@@ -46,6 +46,21 @@ def lib() -> C.CDLL:
         "tfr_set_config": (i32, [vp, C.POINTER(ModelConfig)]),
         "tfr_upload_tensor": (i32, [vp, C.c_char_p, i32, i64, i64, vp, sz]),
         "tfr_finalize_load": (i32, [vp]),
+        "tfr_gguf_open": (i32, [C.c_char_p, C.POINTER(vp), C.c_char_p, sz]),
+        "tfr_gguf_close": (None, [vp]),
+        "tfr_gguf_version": (i32, [vp]),
+        "tfr_gguf_data_offset": (C.c_uint64, [vp]),
+        "tfr_gguf_tensor_count": (i64, [vp]),
+        "tfr_gguf_find_tensor": (i64, [vp, C.c_char_p]),
+        "tfr_gguf_tensor_info": (i32, [vp, i64, C.POINTER(C.c_char_p), C.POINTER(i32), C.POINTER(i32), C.POINTER(i64 * 4),
+                                       C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+        "tfr_gguf_tensor_data": (vp, [vp, i64]),
+        "tfr_gguf_meta_u64": (i32, [vp, C.c_char_p, C.POINTER(C.c_uint64)]),
+        "tfr_gguf_meta_f32": (i32, [vp, C.c_char_p, C.POINTER(f32)]),
+        "tfr_gguf_meta_str": (i32, [vp, C.c_char_p, C.POINTER(C.c_char_p)]),
+        "tfr_gguf_meta_array_len": (i64, [vp, C.c_char_p]),
+        "tfr_gguf_model_config": (i32, [vp, C.POINTER(ModelConfig), C.c_char_p, sz]),
+        "tfr_load_gguf": (i32, [vp, vp, i32, i32]),
         "tfr_alloc_kv": (i32, [vp, i32, C.POINTER(vp)]),
         "tfr_free_kv": (None, [vp]),
         "tfr_kv_len": (i32, [vp]),

@@ -57,6 +57,76 @@ def model_config(cfg: dict, context_length: int = 4096) -> ModelConfig:
     return c
 
 
+class GgufFile:
+    """crates/gguf GgufFile over the C ABI: header, metadata and tensor table of a mapped GGUF file.
+    Host code only (works without a GPU)."""
+
+    def __init__(self, path):
+        h = C.c_void_p()
+        err = C.create_string_buffer(512)
+        rc = _lib.lib().tfr_gguf_open(str(path).encode(), C.byref(h), err, 512)
+        if rc:
+            raise TfrError(rc, err.value.decode())
+        self._h = h.value
+        self.path = str(path)
+
+    @property
+    def version(self) -> int:
+        return _lib.lib().tfr_gguf_version(self._h)
+
+    @property
+    def data_offset(self) -> int:
+        return int(_lib.lib().tfr_gguf_data_offset(self._h))
+
+    def tensors(self) -> list[dict]:
+        out = []
+        for i in range(_lib.lib().tfr_gguf_tensor_count(self._h)):
+            name, ty, nd = C.c_char_p(), C.c_int(), C.c_int()
+            dims = (C.c_int64 * 4)()
+            off, nb = C.c_uint64(), C.c_uint64()
+            _lib.lib().tfr_gguf_tensor_info(self._h, i, C.byref(name), C.byref(ty), C.byref(nd), C.byref(dims), C.byref(off),
+                                            C.byref(nb))
+            out.append(dict(name=name.value.decode(), ggml_type=ty.value, dims=list(dims)[: nd.value], offset=off.value,
+                            nbytes=nb.value))
+        return out
+
+    def tensor_bytes(self, name: str) -> np.ndarray:
+        i = _lib.lib().tfr_gguf_find_tensor(self._h, name.encode())
+        if i < 0:
+            raise KeyError(name)
+        nb = self.tensors()[i]["nbytes"]
+        p = _lib.lib().tfr_gguf_tensor_data(self._h, i)
+        return np.ctypeslib.as_array((C.c_uint8 * nb).from_address(p)).copy()
+
+    def meta_u64(self, key: str):
+        v = C.c_uint64()
+        return int(v.value) if _lib.lib().tfr_gguf_meta_u64(self._h, key.encode(), C.byref(v)) == 0 else None
+
+    def meta_f32(self, key: str):
+        v = C.c_float()
+        return float(v.value) if _lib.lib().tfr_gguf_meta_f32(self._h, key.encode(), C.byref(v)) == 0 else None
+
+    def meta_str(self, key: str):
+        v = C.c_char_p()
+        return v.value.decode() if _lib.lib().tfr_gguf_meta_str(self._h, key.encode(), C.byref(v)) == 0 else None
+
+    def meta_array_len(self, key: str) -> int:
+        return int(_lib.lib().tfr_gguf_meta_array_len(self._h, key.encode()))
+
+    def model_config(self) -> ModelConfig:
+        c = ModelConfig()
+        err = C.create_string_buffer(512)
+        rc = _lib.lib().tfr_gguf_model_config(self._h, C.byref(c), err, 512)
+        if rc:
+            raise TfrError(rc, err.value.decode())
+        return c
+
+    def close(self) -> None:
+        if self._h:
+            _lib.lib().tfr_gguf_close(self._h)
+            self._h = 0
+
+
 class CudaKv:
     """kv.rs:6-42: append-only f16 K/V arena; `len` is assignable by the caller (session.rs:345)."""
 
@@ -138,6 +208,21 @@ class CudaModel:
                 m.upload_tensor(name, TYPE_F32, _nbytes(a) // 4, 1, a)
         m.finalize_load()
         return m
+
+    @classmethod
+    def load_gguf(cls, path, device: int = 0, tp_rank: int = 0, tp_size: int = 1) -> "CudaModel":
+        """CudaModel::load_with(gguf): configuration and tensors straight from a GGUF file."""
+        g = GgufFile(path)
+        try:
+            m = cls(device)
+            c = g.model_config()
+            m.cfg = dict(n_layer=c.n_layer, n_embd=c.n_embd, n_head=c.n_head, n_kv=c.n_kv_head, head_dim=c.head_dim,
+                         n_ff=c.n_ff, n_vocab=c.n_vocab, rope_theta=c.rope_theta, eps=c.rms_eps,
+                         arch=g.meta_str("general.architecture"))
+            m._check(_lib.lib().tfr_load_gguf(m._h, g._h, tp_rank, tp_size))
+            return m
+        finally:
+            g.close()
 
     # -- runtime ----------------------------------------------------------------------------
     def alloc_kv(self, max_seq: int) -> CudaKv:

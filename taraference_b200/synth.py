@@ -216,3 +216,48 @@ def make_model(cfg: dict, seed: int = 0, sigma: float = 0.02) -> dict:
 
 
 make_dense_model = make_model
+
+
+def write_gguf(path, cfg: dict, tensors: dict, version_alignment: int | None = None) -> None:
+    """Writes a model (layout of make_model) as a GGUF file with the tensor names of load.rs:280-417 and the
+    metadata keys ModelConfig::from_gguf reads (config.rs:118-235), using gguf-py's writer."""
+    import gguf
+    arch = cfg["arch"]
+    w = gguf.GGUFWriter(str(path), arch)
+    if version_alignment:
+        w.add_custom_alignment(version_alignment)
+    w.add_name("synthetic " + arch)
+    w.add_uint32(f"{arch}.embedding_length", cfg["n_embd"])
+    w.add_uint32(f"{arch}.block_count", cfg["n_layer"])
+    w.add_uint32(f"{arch}.attention.head_count", cfg["n_head"])
+    w.add_uint32(f"{arch}.attention.head_count_kv", cfg["n_kv"])
+    w.add_uint32(f"{arch}.attention.key_length", cfg["head_dim"])
+    w.add_uint32(f"{arch}.attention.value_length", cfg["head_dim"])
+    w.add_uint32(f"{arch}.feed_forward_length", cfg["n_ff"])
+    w.add_uint32(f"{arch}.context_length", 4096)
+    w.add_uint32(f"{arch}.vocab_size", cfg["n_vocab"])
+    w.add_float32(f"{arch}.rope.freq_base", float(cfg["rope_theta"]))
+    w.add_float32(f"{arch}.attention.layer_norm_rms_epsilon", float(cfg["eps"]))
+    if is_hybrid(cfg):
+        w.add_uint32(f"{arch}.rope.dimension_count", cfg["rope_dim"])
+        w.add_uint32(f"{arch}.ssm.conv_kernel", cfg["conv_kernel"])
+        w.add_uint32(f"{arch}.ssm.state_size", cfg["ssm_state"])
+        w.add_uint32(f"{arch}.ssm.group_count", cfg["ssm_n_k"])
+        w.add_uint32(f"{arch}.ssm.time_step_rank", cfg["ssm_n_v"])
+        w.add_uint32(f"{arch}.ssm.inner_size", cfg["ssm_n_v"] * cfg["ssm_state"])
+        w.add_uint32(f"{arch}.full_attention_interval", cfg.get("full_attention_interval", 4))
+    w.add_array("tokenizer.ggml.tokens", [f"<{i}>" for i in range(8)])  # an array the reader must step over
+    qt = {Q4_K: gguf.GGMLQuantizationType.Q4_K, Q6_K: gguf.GGMLQuantizationType.Q6_K}
+    for name, t in tensors.items():
+        if isinstance(t, tuple):
+            wt, K, N, data = t
+            w.add_tensor(name, np.ascontiguousarray(data).reshape(N, (K // 256) * BLOCK_BYTES[wt]), raw_dtype=qt[wt])
+        else:
+            a = np.ascontiguousarray(t, dtype=np.float32)
+            if name.endswith("ssm_conv1d.weight"):  # GGUF dims [kernel, channels]: numpy shape is the reverse
+                a = a.reshape(-1, cfg["conv_kernel"])
+            w.add_tensor(name, a)
+    w.write_header_to_file()
+    w.write_kv_data_to_file()
+    w.write_tensors_to_file()
+    w.close()
