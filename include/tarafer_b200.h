@@ -127,6 +127,11 @@ int tfr_zero_recurrent(tfr_engine* e, tfr_kv* kv); /* CudaModel::zero_recurrent,
  * greedy next token, advances kv.len by n.  n == 0 -> TFR_E_EMPTY, overflow -> TFR_E_FULL.
  * Prompts (n > 1) are fed through the decode kernels one position at a time. */
 int tfr_forward_greedy(tfr_engine* e, tfr_kv* kv, const uint32_t* tokens, int n, uint32_t* next_token);
+/* CudaModel::forward_greedy_all, forward.rs:268-290 (the verification primitive of speculative decoding,
+ * session.rs:321-367): feeds tokens[0..n) at positions kv.len .. and returns in out[i] the greedy prediction
+ * AFTER tokens[i]; kv.len advances by n.  The caller accepts a prefix and moves kv.len back with
+ * tfr_kv_set_len (models with recurrent state cannot be moved back: their state has absorbed all n tokens). */
+int tfr_forward_greedy_all(tfr_engine* e, tfr_kv* kv, const uint32_t* tokens, int n, uint32_t* out);
 /* The on-device loop that replaces the per-token host round-trip of session.rs:288-368 /
  * forward.rs:73-105: starting from first_token at position kv.len, runs up to max_n decode
  * steps, each feeding the previous step's argmax, without returning to the host.  Stops

@@ -70,6 +70,7 @@ def lib() -> C.CDLL:
         "tfr_kv_bytes_per_token": (i64, [vp]),
         "tfr_zero_recurrent": (i32, [vp, vp]),
         "tfr_forward_greedy": (i32, [vp, vp, vp, i32, C.POINTER(C.c_uint32)]),
+        "tfr_forward_greedy_all": (i32, [vp, vp, vp, i32, vp]),
         "tfr_decode_burst": (i32, [vp, vp, C.c_uint32, i32, vp, i32, vp, C.POINTER(i32)]),
         "tfr_current_logits": (i32, [vp, vp, i32]),
         "tfr_tp_exchange_bytes": (i32, [vp, C.POINTER(sz)]),

@@ -152,7 +152,7 @@ struct TokenState {
     int max_seq;                   // KV capacity; reaching it sets done
     int ring_off;                  // conv-history ring: slot of the current input = (pos + ring_off) % kernel
     unsigned int ar_epoch;         // tensor parallelism: all-reduces completed before this token (never reset)
-    int pad_;
+    int force_prompt;              // 1: every step is fed the next prompt token, not its own argmax (verification)
 };
 
 // Orderable 64-bit key: larger logit wins; on equal logits the lower index wins.

@@ -685,7 +685,7 @@ extern "C" int tfr_finalize_load(tfr_engine* e) {
     CU(e, cudaMalloc(&e->prompt, (size_t)TFR_MAX_PROMPT * 4));
     CU(e, cudaMallocHost(&e->st_host, sizeof(TokenState)));
     CU(e, cudaMallocHost(&e->out_host, (size_t)TFR_MAX_BURST * 4));
-    CU(e, cudaMalloc(&e->args_dev, 16 * sizeof(int)));
+    CU(e, cudaMalloc(&e->args_dev, 16 * sizeof(int)));  // k_state_begin reads [0..14]
     CU(e, cudaMallocHost(&e->args_host, 16 * sizeof(int)));
     CU(e, cudaMemsetAsync(e->counters, 0, (size_t)P.n_kv * 4, e->stream));
     CU(e, cudaMemsetAsync(e->st, 0, sizeof(TokenState), e->stream));
@@ -968,6 +968,7 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
         EpiLogits epi{};
         epi.logits = e->logits;
         epi.out_tokens = e->out_tokens;
+        epi.prompt = e->prompt;
         epi.n_rows = V;
         epi.row_offset = P.v0;
         epi.use_tp = P.tp > 1 && !e->use_nccl;
@@ -979,7 +980,8 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
         n++;
         if (epi.defer_best) {
             if (nccl_api()->AllReduce(e->best_buf, e->best_buf, 1, NCCL_UINT64, NCCL_MAX, e->nccl_comm, s) != 0) return -1;
-            if (launch_pdl(k_state_advance, dim3(1), dim3(1), 0, s, e->st, (const unsigned long long*)e->best_buf, e->out_tokens) !=
+            if (launch_pdl(k_state_advance, dim3(1), dim3(1), 0, s, e->st, (const unsigned long long*)e->best_buf, e->out_tokens,
+                           (const int*)e->prompt) !=
                 cudaSuccess)
                 return -1;
             n += 2;
@@ -1035,12 +1037,13 @@ static int run_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
 }
 
 static int begin_state(tfr_engine* e, const tfr_kv* kv, int token, int pos, int max_steps, int max_seq, const uint32_t* stops,
-                       int n_stop) {
+                       int n_stop, int force_prompt = 0) {
     int* a = e->args_host;
     // the conv ring's write slot follows the position; the offset keeps it continuous when the
     // caller moved the KV length between calls
     const int ck = is_hybrid(e) ? e->cfg.ssm_conv_kernel : 1;
     a[13] = (int)(((kv->rec_steps - pos) % ck + ck) % ck);
+    a[14] = force_prompt;
     a[0] = token;
     a[1] = pos;
     a[2] = max_steps;
@@ -1091,6 +1094,36 @@ extern "C" int tfr_forward_greedy(tfr_engine* e, tfr_kv* kv, const uint32_t* tok
     kv->len += n;
     kv->rec_steps += n;
     if (next_token) *next_token = (uint32_t)e->out_host[0];
+    return TFR_OK;
+}
+
+// CudaModel::forward_greedy_all, forward.rs:268-290: the caller's tokens are fed one per step (not the model's
+// own predictions) and the greedy prediction after EVERY position comes back.
+extern "C" int tfr_forward_greedy_all(tfr_engine* e, tfr_kv* kv, const uint32_t* tokens, int n, uint32_t* out) {
+    if (!e || !kv || kv->e != e || !e->finalized || !out) return e ? fail(e, TFR_E_INVALID, "forward_greedy_all: bad argument") : TFR_E_INVALID;
+    if (n <= 0 || !tokens) return fail(e, TFR_E_EMPTY, "empty tokens");
+    if (e->plan.tp > 1 && !e->comm_attached) return fail(e, TFR_E_INVALID, "tensor-parallel ranks are not connected (tfr_tp_attach_*)");
+    if (kv->len + n > kv->max_seq) return fail(e, TFR_E_FULL, "context full");
+    if (n > TFR_MAX_BURST) return fail(e, TFR_E_INVALID, "more than %d tokens in one call", TFR_MAX_BURST);
+    for (int i = 0; i < n; i++)
+        if (tokens[i] >= (uint32_t)e->token_embd->m.N) return fail(e, TFR_E_INVALID, "token id %u out of range", tokens[i]);
+    cudaSetDevice(e->device);
+    if (e->use_graph) {
+        int rc = ensure_graphs(e, kv);
+        if (rc) return rc;
+    }
+    CU(e, cudaMemcpyAsync(e->prompt, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, e->stream));
+    int rc = begin_state(e, kv, (int)tokens[0], kv->len, n, kv->max_seq + 1, nullptr, 0, 1);
+    if (rc) return rc;
+    CU(e, cudaEventRecord(e->ev0, e->stream));
+    for (int i = 0; i < n && !rc; i++) rc = run_token(e, kv, true);
+    if (rc) return rc;
+    CU(e, cudaEventRecord(e->ev1, e->stream));
+    rc = finish_state(e, n);
+    if (rc) return rc;
+    for (int i = 0; i < n; i++) out[i] = (uint32_t)e->out_host[i];
+    kv->len += n;
+    kv->rec_steps += n;
     return TFR_OK;
 }
 

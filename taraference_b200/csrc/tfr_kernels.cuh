@@ -95,10 +95,29 @@ struct EpiQkv {
 // the token and advances the device-resident decode state, so the next token's first
 // kernel can start without the host (the reference reads the argmax back every token,
 // crates/core/src/cuda/forward.rs:100-104).
+// End of a decode step: record the greedy token and choose the next input — the token itself, or, in a
+// verification pass (forward.rs:268-290), the next token the caller supplied.
+__device__ __forceinline__ void advance_state(TokenState* st, int tok, int* out_tokens, const int* prompt) {
+    const int step = st->step;
+    out_tokens[step] = tok;
+    int next = tok;
+    if (st->force_prompt) {
+        st->prompt_idx += 1;
+        if (step + 1 < st->max_steps) next = prompt[st->prompt_idx];
+    }
+    st->token = next;
+    st->pos += 1;
+    st->step = step + 1;
+    int stop = (step + 1 >= st->max_steps) || (st->pos >= st->max_seq);
+    for (int i = 0; i < st->n_stop; i++) stop |= (st->stop_ids[i] == tok);
+    if (stop) st->done = 1;
+}
+
 struct EpiLogits {
     static constexpr int MODE = EPI_PAIRS;
     float* logits;
     int* out_tokens;   // ring of emitted tokens, indexed by TokenState::step
+    const int* prompt; // forced inputs of a verification pass (TokenState::force_prompt)
     int n_rows;
     int row_offset;    // vocabulary id of local row 0 (vocabulary-parallel head)
     int use_tp;
@@ -153,15 +172,7 @@ struct EpiLogits {
                 }
                 st->ar_epoch += (unsigned)c.ops_per_token;
             }
-            const int tok = argmax_key_index(b);
-            const int step = st->step;
-            out_tokens[step] = tok;
-            st->token = tok;
-            st->pos += 1;
-            st->step = step + 1;
-            int stop = (step + 1 >= st->max_steps) || (st->pos >= st->max_seq);
-            for (int i = 0; i < st->n_stop; i++) stop |= (st->stop_ids[i] == tok);
-            if (stop) st->done = 1;
+            advance_state(st, argmax_key_index(b), out_tokens, prompt);
             st->best = 0ull;
             st->head_done = 0u;
         }
@@ -677,7 +688,8 @@ __global__ void k_permute_f32(const float* __restrict__ src, float* __restrict__
 }
 
 // Decode-state control (single thread each).  args (device memory, copied from the host per call):
-// [0] token, [1] pos, [2] max_steps, [3] max_seq, [4] n_stop, [5..12] stop ids, [13] conv ring offset.
+// [0] token, [1] pos, [2] max_steps, [3] max_seq, [4] n_stop, [5..12] stop ids, [13] conv ring offset,
+// [14] forced-input (verification) flag.
 __global__ void k_state_begin(TokenState* st, const int* __restrict__ args) {
     st->token = args[0];
     st->pos = args[1];
@@ -692,22 +704,15 @@ __global__ void k_state_begin(TokenState* st, const int* __restrict__ args) {
     st->prompt_idx = 0;
     st->err = 0;
     st->ring_off = args[13];
+    st->force_prompt = args[14];
 }
 
 // Second half of the vocabulary head when the (max, argmax) exchange is done by a library all-reduce:
 // publishes the token and advances the decode state (the tail of EpiLogits::end).
-__global__ void k_state_advance(TokenState* st, const unsigned long long* best, int* out_tokens) {
+__global__ void k_state_advance(TokenState* st, const unsigned long long* best, int* out_tokens, const int* prompt) {
     griddep_wait();
     if (st->done) return;
-    const int tok = argmax_key_index(*best);
-    const int step = st->step;
-    out_tokens[step] = tok;
-    st->token = tok;
-    st->pos += 1;
-    st->step = step + 1;
-    int stop = (step + 1 >= st->max_steps) || (st->pos >= st->max_seq);
-    for (int i = 0; i < st->n_stop; i++) stop |= (st->stop_ids[i] == tok);
-    if (stop) st->done = 1;
+    advance_state(st, argmax_key_index(*best), out_tokens, prompt);
 }
 
 // x += y (the residual add after a library all-reduce of the row-parallel partial sums)

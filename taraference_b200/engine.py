@@ -245,6 +245,13 @@ class CudaModel:
         self._check(_lib.lib().tfr_forward_greedy(self._h, kv._h, t.ctypes.data, t.size, C.byref(out)))
         return int(out.value)
 
+    def forward_greedy_all(self, tokens, kv: CudaKv) -> np.ndarray:
+        """Greedy prediction after every one of the given tokens (speculative-decoding verification)."""
+        t = np.ascontiguousarray(tokens, dtype=np.uint32)
+        out = np.zeros(max(t.size, 1), np.uint32)
+        self._check(_lib.lib().tfr_forward_greedy_all(self._h, kv._h, t.ctypes.data, t.size, out.ctypes.data))
+        return out[: t.size].copy()
+
     def decode_burst(self, first_token: int, max_n: int, kv: CudaKv, stop_ids=()) -> np.ndarray:
         stops = np.ascontiguousarray(stop_ids, dtype=np.uint32)
         out = np.zeros(max(max_n, 1), np.uint32)

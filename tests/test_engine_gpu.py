@@ -265,3 +265,32 @@ def test_full_size_3b_shapes_teacher_forced(E, oracle):
     assert margin_gated_equal(toks, otoks, omarg), (toks, otoks, omarg)
     kv.free()
     m.destroy()
+
+
+@pytest.mark.parametrize("cfg", [S.TINY_DENSE, SMALL_128, S.TINY_HYBRID], ids=["tiny", "small128", "hybrid"])
+def test_forward_greedy_all_equals_token_by_token(E, cfg):
+    """The verification primitive: predictions after every supplied token, then a roll-back of the length."""
+    tens = S.make_model(cfg, seed=12)
+    toks = [7, 3, 99, 250, 12, 5, 41, 8, 19]
+    m = E.CudaModel.load_with(cfg, tens)
+    kv = m.alloc_kv(64)
+    m.forward_greedy([1, 2], kv)
+    want = [m.forward_greedy([t], kv) for t in toks]
+    want_logits = m.current_logits()
+    kv2 = m.alloc_kv(64)
+    m.forward_greedy([1, 2], kv2)
+    got = m.forward_greedy_all(toks, kv2)
+    assert list(got) == want and kv2.len == 2 + len(toks)
+    assert np.array_equal(m.current_logits(), want_logits)
+    if not S.is_hybrid(cfg):
+        # accept the first four, move the length back, continue from there: same as never having run the rest
+        kv2.len = 2 + 4
+        again = m.forward_greedy_all(toks[4:], kv2)
+        assert list(again) == want[4:]
+    with pytest.raises(E.TfrError, match="empty tokens"):
+        m.forward_greedy_all([], kv2)
+    with pytest.raises(E.TfrError, match="context full"):
+        m.forward_greedy_all(list(range(60)), kv2)
+    kv.free()
+    kv2.free()
+    m.destroy()
