@@ -215,7 +215,8 @@ int tfr_op_ffn_block(const tfr_mat* gate, const tfr_mat* up, const tfr_mat* down
 /* Same with HOST buffers: copies x in, runs the two kernels, copies y out, synchronises. */
 int tfr_ffn_block_host(const tfr_mat* gate, const tfr_mat* up, const tfr_mat* down, const float* x_host, float* y_host);
 /* Integer contract taps (test aid, no reference kernel exposes these): for Q4_K, a = I[N][K/32]
- * and b = S[N][K/32] of kernels/gemv.cu:71-130; for Q6_K, a = J[N][K/16] of gemv.cu:302-337. */
+ * and b = S[N][K/32] of kernels/gemv.cu:71-130; for Q6_K, a = J[N][K/16] of gemv.cu:302-337; for Q8_0,
+ * a = the per-32-block sums [N][K/32] of gemv.cu:1558-1582. */
 int tfr_op_int_dots(const tfr_mat* w, const int8_t* q8, const float* d8, int32_t* a, int32_t* b, void* stream);
 /* attn_flash_partial + attn_flash_reduce, kernels/attn/flash.cu:16-255, for one query token
  * at position pos over cache rows [0, pos].  kc / vc: [max_seq][n_kv*head_dim] f16 bits. */
@@ -262,6 +263,12 @@ int tfr_op_qk_norm_rope_store(const float* raw, const float* q_norm, const float
  * out = attention(q) * sigmoid(gate) (mul_sigmoid_f32, kernels/deltanet.cu:176-186). */
 int tfr_op_attention_gated(const float* q, const uint16_t* kc, const uint16_t* vc, const float* gate, float* out,
                            int n_head, int n_kv, int head_dim, int pos, void* stream);
+
+/* transcode_q5_k_to_q8_0 / transcode_q5_1_to_q8_0, load.rs:33-133 (host code): src_type 13 (Q5_K, 176-byte
+ * blocks) or 7 (Q5_1, 24-byte blocks) -> Q8_0 bytes (34 per 32 weights) in out.  tfr_upload_tensor and
+ * tfr_mat_create apply it themselves to tensors of those types; Q8_0 (type 8) matrices run on their own
+ * dot routine (kernels/gemv.cu:1558-1749). */
+int tfr_transcode_to_q8_0(int src_type, const void* raw, size_t nbytes, void* out);
 
 /* Synthetic-model aid (no counterpart in the reference, which has no quantiser): quantise
  * fp32 rows [N][K] on the device into GGUF Q4_K / Q6_K bytes. */

@@ -15,8 +15,8 @@ import numpy as np
 HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "liboracle.so"
 
-Q4_K, Q6_K = 12, 14
-BLOCK_BYTES = {Q4_K: 144, Q6_K: 210}
+Q4_K, Q6_K, Q8_0 = 12, 14, 8
+BLOCK_BYTES = {Q4_K: 144, Q6_K: 210, Q8_0: 8 * 34}  # bytes per 256 weights
 
 
 def build(force: bool = False) -> None:
@@ -100,6 +100,9 @@ def lib():
         _lib.tfo_copy_kv_f16.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int]
         _lib.tfo_argmax.argtypes = [C.c_void_p, C.c_int]
         _lib.tfo_set_threads.argtypes = [C.c_int]
+        _lib.tfo_q8_0_blockdots.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+        _lib.tfo_transcode_q5_k_to_q8_0.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
+        _lib.tfo_transcode_q5_1_to_q8_0.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
     return _lib
 
 
@@ -196,6 +199,22 @@ def q6k_groupdots(block: np.ndarray, q8: np.ndarray) -> np.ndarray:
     J = np.zeros(16, np.int32)
     lib().tfo_q6k_groupdots(_p(block), _p(q8), _p(J))
     return J
+
+
+def q8_0_blockdots(row: np.ndarray, K: int, q8: np.ndarray) -> np.ndarray:
+    sums = np.zeros(K // 32, np.int32)
+    lib().tfo_q8_0_blockdots(_p(row), K, _p(q8), _p(sums))
+    return sums
+
+
+def transcode_to_q8_0(src_type: int, raw: np.ndarray) -> np.ndarray:
+    """Q5_K (13) or Q5_1 (7) bytes -> Q8_0 bytes, the reference loader's one-off conversion (load.rs:33-133)."""
+    raw = np.ascontiguousarray(raw, dtype=np.uint8).reshape(-1)
+    blk, per = (176, 8) if src_type == 13 else (24, 1)
+    out = np.zeros(raw.size // blk * per * 34, np.uint8)
+    f = lib().tfo_transcode_q5_k_to_q8_0 if src_type == 13 else lib().tfo_transcode_q5_1_to_q8_0
+    assert f(_p(raw), raw.size, _p(out)) == 0
+    return out
 
 
 def rms_norm(x, w, eps: float) -> np.ndarray:

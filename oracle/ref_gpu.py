@@ -20,7 +20,7 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 CUBIN = HERE / "_ref" / "ref_kernels.cubin"
-Q4_K, Q6_K = 12, 14
+Q4_K, Q6_K, Q8_0 = 12, 14, 8
 
 
 def available() -> bool:
@@ -103,7 +103,7 @@ class RefMat:
     def __init__(self, wtype: int, K: int, N: int, raw: np.ndarray):
         self.type, self.K, self.N = wtype, K, N
         nb = K // 256
-        self.col_bytes = nb * (144 if wtype == Q4_K else 210)
+        self.col_bytes = nb * (144 if wtype == Q4_K else 272 if wtype == Q8_0 else 210)
         self.data = dev(raw)
         self.compact = dev(compact_q6(raw, K, N)) if wtype == Q6_K else None
         self.compact_col_bytes = nb * 212
@@ -135,6 +135,12 @@ def gemv_q8(m: RefMat, x, out=None, bias=None, use_res=0, warps=16):
     q, d = quantize_q8(x)
     b = bias if bias is not None else x
     smem = m.K + (m.K // 32) * 4
+    if m.type == Q8_0:
+        # gemv_q8_0_global, matmul.rs:160-164 + 286-300 (K < 4096: no split)
+        assert m.K < 4096, "split-K Q8_0 route not wired in the harness"
+        kernels().launch("gemv_q8_0_global", ((m.N + warps - 1) // warps,), (warps * 32,), smem, m.data, q, d, out, m.K, m.N,
+                         m.col_bytes, int(bias is not None), b, use_res, x)
+        return out
     if m.type == Q4_K:
         if m.K >= 4096:
             # split-K route, matmul.rs:199-289: grid (N, 4) x 64, then the reduce with bias / residual
@@ -156,9 +162,18 @@ def gemv_q8(m: RefMat, x, out=None, bias=None, use_res=0, warps=16):
 
 def gemv_q6_f32(m: RefMat, x, bias=None):
     """gemv_baseline for Q6_K, matmul.rs:346-412 (lc_q5_gemv): fp32 activations."""
-    assert m.type == Q6_K and m.K < 4096
+    assert m.type == Q6_K
     out = torch.zeros(m.N, dtype=torch.float32, device="cuda")
     b = bias if bias is not None else x
+    if m.K >= 4096:
+        # gemv_splitk, matmul.rs:414-505: four K splits (gemv_n_split), grid (ceil(N/32), 4) x 1024, then the reduce
+        nb = m.K // 256
+        rows_per_split = max(256, -(-nb // 4) * 256)
+        partial = torch.zeros(4 * m.N, dtype=torch.float32, device="cuda")
+        kernels().launch("gemv_q6_k_splitk", ((m.N + 31) // 32, 4), (1024,), rows_per_split * 4, m.data, x, partial, m.K, m.N,
+                         m.col_bytes, 4)
+        kernels().launch("gemv_splitk_reduce", ((m.N + 255) // 256,), (256,), 0, partial, out, m.N, 4, int(bias is not None), b, 0, x)
+        return out
     kernels().launch("gemv_q6_k", ((m.N + 7) // 8,), (256,), m.K * 4, m.data, x, out, m.K, m.N, m.col_bytes,
                      int(bias is not None), b, 0, x)
     return out

@@ -161,7 +161,10 @@ void tfo_dequant_q6_k(const uint8_t* b, float* out) {
         out[e] = d * (float)sc[q6_scale_index(e)] * (float)q6_value(b, e);
 }
 
-static int blk_bytes(int type) { return type == TFO_Q4_K ? TFO_Q4_K_BYTES : (type == TFO_Q6_K ? TFO_Q6_K_BYTES : 0); }
+/* bytes per 256 elements */
+static int blk_bytes(int type) {
+    return type == TFO_Q4_K ? TFO_Q4_K_BYTES : type == TFO_Q6_K ? TFO_Q6_K_BYTES : type == TFO_Q8_0 ? 8 * TFO_Q8_0_BYTES : 0;
+}
 
 /* One weight row (K elements, GGUF bytes) to floats.  kernels/embed.cu:71-131 is this
  * applied to the row of a token id. */
@@ -291,6 +294,144 @@ float tfo_dot_q4k_f32(const uint8_t* row, int nb, const float* x) {
 
 /* ---------------------------------------------------------------- GEMV ---------- */
 
+/* Q8_0 x Q8, kernels/gemv.cu:1558-1582: per 32-block sum = dot(int8 weights, int8 activation);
+ * acc += d_w * d_x * (float)sum. */
+void tfo_q8_0_blockdots(const uint8_t* row, int K, const int8_t* q8, int32_t* sums) {
+    for (int bi = 0; bi < K / 32; bi++) {
+        const int8_t* qs = (const int8_t*)(row + (size_t)bi * TFO_Q8_0_BYTES + 2);
+        int32_t s = 0;
+        for (int t = 0; t < 32; t++) s += (int32_t)qs[t] * (int32_t)q8[32 * bi + t];
+        sums[bi] = s;
+    }
+}
+float tfo_dot_q8_0_q8(const uint8_t* row, int K, const int8_t* q8, const float* d8) {
+    float acc = 0.f;
+    for (int bi = 0; bi < K / 32; bi++) {
+        const uint8_t* base = row + (size_t)bi * TFO_Q8_0_BYTES;
+        const float dw = tfo_half_to_float((uint16_t)(base[0] | (base[1] << 8)));
+        const int8_t* qs = (const int8_t*)(base + 2);
+        int32_t s = 0;
+        for (int t = 0; t < 32; t++) s += (int32_t)qs[t] * (int32_t)q8[32 * bi + t];
+        acc += dw * d8[bi] * (float)s;
+    }
+    return acc;
+}
+
+/* IEEE f32 -> f16, round to nearest even (crates/core/src/quant.rs:26-62). */
+static uint16_t f32_to_f16_rne(float value) {
+    uint32_t bits;
+    memcpy(&bits, &value, 4);
+    uint16_t sign = (uint16_t)((bits >> 16) & 0x8000);
+    int exponent = (int)((bits >> 23) & 0xff);
+    uint32_t fraction = bits & 0x007fffffu;
+    if (exponent == 255) return (uint16_t)(sign | (fraction == 0 ? 0x7c00 : 0x7e00));
+    int half_exp = exponent - 127 + 15;
+    if (half_exp >= 31) return (uint16_t)(sign | 0x7c00);
+    if (half_exp <= 0) {
+        if (half_exp < -10) return sign;
+        uint32_t mantissa = fraction | 0x00800000u;
+        uint32_t shift = (uint32_t)(14 - half_exp);
+        uint32_t rounded = mantissa >> shift;
+        uint32_t remainder = mantissa & ((1u << shift) - 1u);
+        uint32_t halfway = 1u << (shift - 1);
+        if (remainder > halfway || (remainder == halfway && (rounded & 1u))) rounded += 1;
+        return (uint16_t)(sign | rounded);
+    }
+    uint32_t rounded = fraction + 0x00000fffu + ((fraction >> 13) & 1u);
+    uint16_t out_exp = (uint16_t)half_exp;
+    if (rounded & 0x00800000u) {
+        rounded = 0;
+        out_exp += 1;
+        if (out_exp >= 31) return (uint16_t)(sign | 0x7c00);
+    }
+    return (uint16_t)(sign | (out_exp << 10) | (rounded >> 13));
+}
+
+/* 32 fp32 values -> one Q8_0 block (load.rs:88-101): d = amax / 127, q = clamp(round-half-away(v / d)). */
+static void q8_0_from_f32(const float* v, uint8_t* out) {
+    float amax = 0.f;
+    for (int i = 0; i < 32; i++) {
+        float a = fabsf(v[i]);
+        if (a > amax) amax = a;
+    }
+    volatile float d = amax == 0.f ? 0.f : amax / 127.0f;
+    uint16_t h = f32_to_f16_rne(d);
+    out[0] = (uint8_t)(h & 0xff);
+    out[1] = (uint8_t)(h >> 8);
+    for (int i = 0; i < 32; i++) {
+        int q = 0;
+        if (d != 0.f) {
+            float r = roundf(v[i] / d);
+            r = r < -127.f ? -127.f : (r > 127.f ? 127.f : r);
+            q = (int)r;
+        }
+        out[2 + i] = (uint8_t)(int8_t)q;
+    }
+}
+
+/* load.rs:33-104: Q5_K block (176 B: d, dmin, 12 scale bytes, 32 qh, 128 qs) -> 8 Q8_0 blocks. */
+int tfo_transcode_q5_k_to_q8_0(const uint8_t* raw, size_t nbytes, uint8_t* out) {
+    if (nbytes % 176) return -1;
+    for (size_t b = 0; b < nbytes / 176; b++) {
+        const uint8_t* blk = raw + b * 176;
+        const float d = tfo_half_to_float((uint16_t)(blk[0] | (blk[1] << 8)));
+        const float dmin = tfo_half_to_float((uint16_t)(blk[2] | (blk[3] << 8)));
+        const uint8_t *sc = blk + 4, *qh = blk + 16, *qs = blk + 48;
+        float vals[256];
+        uint8_t hl = 1, hh = 2;
+        for (int g = 0; g < 4; g++) {
+            uint8_t s0, m0, s1, m1;
+            int j = 2 * g;
+            for (int w = 0; w < 2; w++, j++) {
+                uint8_t s, m;
+                if (j < 4) {
+                    s = sc[j] & 0x3f;
+                    m = sc[j + 4] & 0x3f;
+                } else {
+                    s = (uint8_t)((sc[j + 4] & 0x0f) | ((sc[j - 4] >> 6) << 4));
+                    m = (uint8_t)((sc[j + 4] >> 4) | ((sc[j] >> 6) << 4));
+                }
+                if (w == 0) s0 = s, m0 = m;
+                else s1 = s, m1 = m;
+            }
+            volatile float scale0 = d * (float)s0, scale1 = d * (float)s1;
+            volatile float off0 = dmin * (float)m0, off1 = dmin * (float)m1;
+            for (int l = 0; l < 32; l++) {
+                int low = (qs[32 * g + l] & 0x0f) + ((qh[l] & hl) ? 16 : 0);
+                int high = (qs[32 * g + l] >> 4) + ((qh[l] & hh) ? 16 : 0);
+                volatile float p0 = scale0 * (float)low, p1 = scale1 * (float)high; /* no fused multiply-add */
+                vals[64 * g + l] = p0 - off0;
+                vals[64 * g + 32 + l] = p1 - off1;
+            }
+            hl = (uint8_t)(hl << 2);
+            hh = (uint8_t)(hh << 2);
+        }
+        for (int k = 0; k < 8; k++) q8_0_from_f32(vals + 32 * k, out + (b * 8 + k) * 34);
+    }
+    return 0;
+}
+
+/* load.rs:106-133: Q5_1 block (24 B: d, min, 4 qh, 16 qs) -> one Q8_0 block. */
+int tfo_transcode_q5_1_to_q8_0(const uint8_t* raw, size_t nbytes, uint8_t* out) {
+    if (nbytes % 24) return -1;
+    for (size_t b = 0; b < nbytes / 24; b++) {
+        const uint8_t* blk = raw + b * 24;
+        const float d = tfo_half_to_float((uint16_t)(blk[0] | (blk[1] << 8)));
+        const float mn = tfo_half_to_float((uint16_t)(blk[2] | (blk[3] << 8)));
+        const uint32_t qh = (uint32_t)blk[4] | ((uint32_t)blk[5] << 8) | ((uint32_t)blk[6] << 16) | ((uint32_t)blk[7] << 24);
+        const uint8_t* qs = blk + 8;
+        float vals[32];
+        for (int j = 0; j < 16; j++) {
+            uint8_t h0 = (uint8_t)(((qh >> j) << 4) & 0x10), h1 = (uint8_t)((qh >> (j + 12)) & 0x10);
+            volatile float p0 = (float)((qs[j] & 0x0f) | h0) * d, p1 = (float)((qs[j] >> 4) | h1) * d;
+            vals[j] = p0 + mn;
+            vals[j + 16] = p1 + mn;
+        }
+        q8_0_from_f32(vals, out + b * 34);
+    }
+    return 0;
+}
+
 size_t tfo_row_bytes(const tfo_mat* m) { return (size_t)(m->K / 256) * blk_bytes(m->type); }
 
 /* y = W x (+bias) (+y).  act_mode 0: x is quantised to Q8 first (gemv.cu:377-403,
@@ -300,6 +441,7 @@ size_t tfo_row_bytes(const tfo_mat* m) { return (size_t)(m->K / 256) * blk_bytes
 int tfo_gemv(const tfo_mat* w, const float* x, float* out, const float* bias, int use_res, int act_mode) {
     int K = w->K, N = w->N, nb = K / 256;
     if (K % 256 || !blk_bytes(w->type)) return -1;
+    if (w->type == TFO_Q8_0) act_mode = 0; /* Q8_0 weights always take the Q8 activation (gemv.cu:1585-1749) */
     int8_t* q8 = NULL;
     float* d8 = NULL;
     if (act_mode == 0) {
@@ -312,7 +454,9 @@ int tfo_gemv(const tfo_mat* w, const float* x, float* out, const float* bias, in
     for (int j = 0; j < N; j++) {
         const uint8_t* row = w->data + (size_t)j * rb;
         float acc;
-        if (act_mode == 0)
+        if (w->type == TFO_Q8_0)
+            acc = tfo_dot_q8_0_q8(row, K, q8, d8);
+        else if (act_mode == 0)
             acc = w->type == TFO_Q4_K ? tfo_dot_q4k_q8(row, nb, q8, d8) : tfo_dot_q6k_q8(row, nb, q8, d8);
         else
             acc = w->type == TFO_Q4_K ? tfo_dot_q4k_f32(row, nb, x) : tfo_dot_q6k_f32(row, nb, x);

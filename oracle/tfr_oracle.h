@@ -6,8 +6,12 @@
 
 #define TFO_Q4_K 12 /* ggml type ids, crates/gguf/src/types.rs:7-60 */
 #define TFO_Q6_K 14
+#define TFO_Q8_0 8
+#define TFO_Q5_K 13
+#define TFO_Q5_1 7
 #define TFO_Q4_K_BYTES 144
 #define TFO_Q6_K_BYTES 210
+#define TFO_Q8_0_BYTES 34 /* per 32 elements */
 
 typedef struct {
     int32_t type; /* TFO_Q4_K or TFO_Q6_K */
@@ -60,6 +64,10 @@ void tfo_rms_norm(const float* x, const float* w, float* out, int n, float eps);
 void tfo_copy_kv_f16(const float* src, uint16_t* cache, int pos, int stride);
 void tfo_attention(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv, int hd, int pos,
                    float scale);
+float tfo_dot_q8_0_q8(const uint8_t* row, int K, const int8_t* q8, const float* d8);
+void tfo_q8_0_blockdots(const uint8_t* row, int K, const int8_t* q8, int32_t* sums);
+int tfo_transcode_q5_k_to_q8_0(const uint8_t* raw, size_t nbytes, uint8_t* out);
+int tfo_transcode_q5_1_to_q8_0(const uint8_t* raw, size_t nbytes, uint8_t* out);
 /* tfr_oracle_gdn.c */
 int tfo_gdn_step(const float* qkv, const float* z, const float* beta, const float* alpha, const float* conv_w,
                  float* conv_state, float* ssm, const float* ssm_a, const float* ssm_dt, const float* norm_w, float* y, int nk,

@@ -102,6 +102,7 @@ def lib() -> C.CDLL:
         "tfr_op_gdn_step": (i32, [vp] * 8 + [i32, i32, i32, i32, i32, f32, vp]),
         "tfr_op_qk_norm_rope_store": (i32, [vp] * 7 + [i32, i32, i32, i32, i32, f32, f32, vp]),
         "tfr_op_attention_gated": (i32, [vp] * 5 + [i32, i32, i32, i32, vp]),
+        "tfr_transcode_to_q8_0": (i32, [i32, vp, sz, vp]),
         "tfr_synth_quantize": (i32, [i32, vp, i64, i64, vp, vp]),
     }
     for name, (res, args) in sig.items():

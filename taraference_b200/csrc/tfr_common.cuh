@@ -12,6 +12,9 @@
 
 #define TFR_Q4_K 12
 #define TFR_Q6_K 14
+#define TFR_Q8_0 8
+#define TFR_Q5_K 13
+#define TFR_Q5_1 7
 #define TFR_FULL_MASK 0xffffffffu
 
 namespace tfr {

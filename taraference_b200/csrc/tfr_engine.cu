@@ -49,6 +49,7 @@ struct LayerW {
     float *attn_norm = nullptr, *ffn_norm = nullptr;
     // linear (Gated-DeltaNet) layers: the four input projections stacked into one matrix
     tfr_mat *gdn_proj = nullptr, *ssm_out = nullptr;
+    tfr_mat* proj4[4] = {nullptr, nullptr, nullptr, nullptr};  // the four projections kept apart when their types differ
     float *conv_w = nullptr, *ssm_a = nullptr, *ssm_dt = nullptr, *ssm_norm = nullptr;
     // gated full-attention layers
     float *q_norm = nullptr, *k_norm = nullptr;
@@ -196,6 +197,9 @@ static size_t raw_bytes(int type, int64_t K, int64_t N) {
     int64_t nb = K / 256;
     if (type == TFR_Q4_K) return (size_t)(N * nb * 144);
     if (type == TFR_Q6_K) return (size_t)(N * nb * 210);
+    if (type == TFR_Q8_0) return (size_t)(N * nb * Q8_SUPER_BYTES);
+    if (type == TFR_Q5_K) return (size_t)(N * nb * 176);
+    if (type == TFR_Q5_1) return (size_t)(N * nb * 8 * 24);
     return 0;
 }
 
@@ -215,6 +219,10 @@ static void configure_kernels_once() {
     configure_kernel(k_gemv<BlockQ4, EpiStore>, true);
     configure_kernel(k_gemv<BlockQ6, EpiStore>, true);
     configure_kernel(k_gemv<BlockQ4, EpiSilu>, true);
+    configure_kernel(k_gemv<BlockQ8, EpiStore>, true);
+    configure_kernel(k_gemv<BlockQ8, EpiLogits>, true);
+    configure_kernel(k_gemv<BlockQ8, EpiAllReduce>, true);
+    configure_kernel(k_int_dots<BlockQ8>, true);
     configure_kernel(k_gemv<BlockQ4, EpiAllReduce>, true);
     configure_kernel(k_gemv<BlockQ6, EpiAllReduce>, true);
     configure_kernel(k_gemv<BlockQ4, EpiLogits>, true);
@@ -249,11 +257,130 @@ static int sm_count_cached() {
     return n;
 }
 
+// ------------------------------------------------------------------ Q5 -> Q8_0 conversion (host)
+
+// IEEE f32 -> f16, round to nearest even (crates/core/src/quant.rs:26-62), and back.
+static uint16_t host_f32_to_f16(float value) {
+    uint32_t bits;
+    memcpy(&bits, &value, 4);
+    const uint16_t sign = (uint16_t)((bits >> 16) & 0x8000);
+    const int exponent = (int)((bits >> 23) & 0xff);
+    const uint32_t fraction = bits & 0x007fffffu;
+    if (exponent == 255) return (uint16_t)(sign | (fraction == 0 ? 0x7c00 : 0x7e00));
+    const int half_exp = exponent - 127 + 15;
+    if (half_exp >= 31) return (uint16_t)(sign | 0x7c00);
+    if (half_exp <= 0) {
+        if (half_exp < -10) return sign;
+        const uint32_t mantissa = fraction | 0x00800000u, shift = (uint32_t)(14 - half_exp);
+        uint32_t rounded = mantissa >> shift;
+        const uint32_t remainder = mantissa & ((1u << shift) - 1u), halfway = 1u << (shift - 1);
+        if (remainder > halfway || (remainder == halfway && (rounded & 1u))) rounded += 1;
+        return (uint16_t)(sign | rounded);
+    }
+    uint32_t rounded = fraction + 0x00000fffu + ((fraction >> 13) & 1u);
+    uint16_t out_exp = (uint16_t)half_exp;
+    if (rounded & 0x00800000u) {
+        rounded = 0;
+        out_exp += 1;
+        if (out_exp >= 31) return (uint16_t)(sign | 0x7c00);
+    }
+    return (uint16_t)(sign | (out_exp << 10) | (rounded >> 13));
+}
+static float host_f16_to_f32(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+// 32 fp32 values -> one Q8_0 block, load.rs:88-101: d = amax / 127, q = clamp(round half away from zero (v / d)).
+static void host_q8_0_block(const float* v, uint8_t* out) {
+    float amax = 0.f;
+    for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(v[i]));
+    volatile float d = amax == 0.f ? 0.f : amax / 127.0f;
+    const uint16_t h = host_f32_to_f16(d);
+    out[0] = (uint8_t)(h & 0xff);
+    out[1] = (uint8_t)(h >> 8);
+    for (int i = 0; i < 32; i++) {
+        int q = 0;
+        if (d != 0.f) {
+            volatile float r = v[i] / d;
+            float rr = roundf(r);
+            rr = rr < -127.f ? -127.f : (rr > 127.f ? 127.f : rr);
+            q = (int)rr;
+        }
+        out[2 + i] = (uint8_t)(int8_t)q;
+    }
+}
+
+// transcode_q5_k_to_q8_0 / transcode_q5_1_to_q8_0, load.rs:33-133.  The products and differences are kept as
+// separate fp32 operations (volatile), as the reference's host code computes them.
+extern "C" int tfr_transcode_to_q8_0(int src_type, const void* raw_v, size_t nbytes, void* out_v) {
+    const uint8_t* raw = (const uint8_t*)raw_v;
+    uint8_t* out = (uint8_t*)out_v;
+    if (!raw || !out) return TFR_E_INVALID;
+    if (src_type == TFR_Q5_K) {
+        if (nbytes % 176) return TFR_E_INVALID;
+        for (size_t b = 0; b < nbytes / 176; b++) {
+            const uint8_t* blk = raw + b * 176;
+            const float d = host_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8))), dmin = host_f16_to_f32((uint16_t)(blk[2] | (blk[3] << 8)));
+            const uint8_t *sc = blk + 4, *qh = blk + 16, *qs = blk + 48;
+            float vals[256];
+            for (int g = 0; g < 4; g++) {
+                uint8_t s[2], m[2];
+                for (int w = 0; w < 2; w++) {
+                    const int j = 2 * g + w;
+                    if (j < 4) {
+                        s[w] = sc[j] & 0x3f;
+                        m[w] = sc[j + 4] & 0x3f;
+                    } else {
+                        s[w] = (uint8_t)((sc[j + 4] & 0x0f) | ((sc[j - 4] >> 6) << 4));
+                        m[w] = (uint8_t)((sc[j + 4] >> 4) | ((sc[j] >> 6) << 4));
+                    }
+                }
+                volatile float scale0 = d * (float)s[0], scale1 = d * (float)s[1], off0 = dmin * (float)m[0], off1 = dmin * (float)m[1];
+                const uint8_t hl = (uint8_t)(1u << (2 * g)), hh = (uint8_t)(2u << (2 * g));
+                for (int l = 0; l < 32; l++) {
+                    const int low = (qs[32 * g + l] & 0x0f) + ((qh[l] & hl) ? 16 : 0), high = (qs[32 * g + l] >> 4) + ((qh[l] & hh) ? 16 : 0);
+                    volatile float p0 = scale0 * (float)low, p1 = scale1 * (float)high;
+                    vals[64 * g + l] = p0 - off0;
+                    vals[64 * g + 32 + l] = p1 - off1;
+                }
+            }
+            for (int k = 0; k < 8; k++) host_q8_0_block(vals + 32 * k, out + (b * 8 + k) * 34);
+        }
+        return TFR_OK;
+    }
+    if (src_type == TFR_Q5_1) {
+        if (nbytes % 24) return TFR_E_INVALID;
+        for (size_t b = 0; b < nbytes / 24; b++) {
+            const uint8_t* blk = raw + b * 24;
+            const float d = host_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8))), mn = host_f16_to_f32((uint16_t)(blk[2] | (blk[3] << 8)));
+            const uint32_t qh = (uint32_t)blk[4] | ((uint32_t)blk[5] << 8) | ((uint32_t)blk[6] << 16) | ((uint32_t)blk[7] << 24);
+            const uint8_t* qs = blk + 8;
+            float vals[32];
+            for (int j = 0; j < 16; j++) {
+                const uint8_t h0 = (uint8_t)(((qh >> j) << 4) & 0x10), h1 = (uint8_t)((qh >> (j + 12)) & 0x10);
+                volatile float p0 = (float)((qs[j] & 0x0f) | h0) * d, p1 = (float)((qs[j] >> 4) | h1) * d;
+                vals[j] = p0 + mn;
+                vals[j + 16] = p1 + mn;
+            }
+            host_q8_0_block(vals, out + b * 34);
+        }
+        return TFR_OK;
+    }
+    return TFR_E_UNSUPPORTED;
+}
+
 // ------------------------------------------------------------------ matrices
 
 static int mat_create_impl(tfr_engine* e, int type, int64_t K, int64_t N, const void* bytes, size_t nbytes, int perm_hd,
                            cudaStream_t stream, tfr_mat** out) {
-    if (type != TFR_Q4_K && type != TFR_Q6_K) return fail(e, TFR_E_UNSUPPORTED, "matrix type %d not supported", type);
+    if (type == TFR_Q5_K || type == TFR_Q5_1) {
+        // load.rs:191-233: Q5_K / Q5_1 tensors are converted to Q8_0 once, on the host, and run on the Q8_0 kernels
+        if (K <= 0 || N <= 0 || K % 256 || nbytes != raw_bytes(type, K, N))
+            return fail(e, TFR_E_INVALID, "matrix byte size %zu != expected %zu", nbytes, raw_bytes(type, K, N));
+        std::vector<uint8_t> src(nbytes), q8(raw_bytes(TFR_Q8_0, K, N));
+        if (cudaMemcpy(src.data(), bytes, nbytes, cudaMemcpyDefault) != cudaSuccess) return fail(e, TFR_E_CUDA, "reading the tensor");
+        if (tfr_transcode_to_q8_0(type, src.data(), nbytes, q8.data()) != TFR_OK) return fail(e, TFR_E_INVALID, "transcode failed");
+        return mat_create_impl(e, TFR_Q8_0, K, N, q8.data(), q8.size(), perm_hd, stream, out);
+    }
+    if (type != TFR_Q4_K && type != TFR_Q6_K && type != TFR_Q8_0) return fail(e, TFR_E_UNSUPPORTED, "matrix type %d not supported", type);
     if (K <= 0 || N <= 0 || K % 256) return fail(e, TFR_E_INVALID, "matrix K=%lld must be a positive multiple of 256", (long long)K);
     if (nbytes != raw_bytes(type, K, N))
         return fail(e, TFR_E_INVALID, "matrix byte size %zu != expected %zu", nbytes, raw_bytes(type, K, N));
@@ -452,10 +579,10 @@ extern "C" int tfr_upload_tensor(tfr_engine* e, const char* name, int type, int6
         return TFR_OK;
     }
     if (P.tp > 1) {
-        if (type != TFR_Q4_K && type != TFR_Q6_K) return fail(e, TFR_E_UNSUPPORTED, "matrix type %d not supported", type);
+        if (type != TFR_Q4_K && type != TFR_Q6_K && type != TFR_Q8_0) return fail(e, TFR_E_UNSUPPORTED, "matrix type %d not supported", type);
         if (n_rows <= 0 || n_cols <= 0 || n_rows % 256 || nbytes != raw_bytes(type, n_rows, n_cols))
             return fail(e, TFR_E_INVALID, "tensor %s: bad shape or byte size", name);
-        const int blk = type == TFR_Q4_K ? 144 : 210;
+        const int blk = block_bytes_256(type);
         const size_t row_bytes = (size_t)(n_rows / 256) * blk;
         int64_t r0 = 0, r1 = n_cols;   // rows kept (column-parallel)
         int64_t b0 = 0, b1 = n_rows / 256;  // K blocks kept (row-parallel)
@@ -493,10 +620,23 @@ extern "C" int tfr_upload_tensor(tfr_engine* e, const char* name, int type, int6
         return TFR_OK;
     }
     // F32/F16 matrices are rejected like load.rs:15-28
+    std::vector<uint8_t> converted;
+    if (type == TFR_Q5_K || type == TFR_Q5_1) {
+        // load.rs:191-233: Q5_K / Q5_1 tensors are converted to Q8_0 once, on the host, and run on the Q8_0 kernels
+        if (n_rows <= 0 || n_cols <= 0 || n_rows % 256 || nbytes != raw_bytes(type, n_rows, n_cols))
+            return fail(e, TFR_E_INVALID, "tensor %s: bad shape or byte size", name);
+        std::vector<uint8_t> src(nbytes);
+        CU(e, cudaMemcpy(src.data(), bytes, nbytes, cudaMemcpyDefault));
+        converted.resize(raw_bytes(TFR_Q8_0, n_rows, n_cols));
+        if (tfr_transcode_to_q8_0(type, src.data(), nbytes, converted.data()) != TFR_OK) return fail(e, TFR_E_INVALID, "tensor %s: transcode failed", name);
+        bytes = converted.data();
+        nbytes = converted.size();
+        type = TFR_Q8_0;
+    }
     if (is_hybrid(e) && (ends_with(nm, "attn_qkv.weight") || ends_with(nm, "attn_gate.weight") ||
                          ends_with(nm, "ssm_beta.weight") || ends_with(nm, "ssm_alpha.weight"))) {
         // the four input projections of a linear layer become one matrix at finalize
-        if (type != TFR_Q4_K && type != TFR_Q6_K) return fail(e, TFR_E_UNSUPPORTED, "matrix type %d not supported", type);
+        if (type != TFR_Q4_K && type != TFR_Q6_K && type != TFR_Q8_0) return fail(e, TFR_E_UNSUPPORTED, "matrix type %d not supported", type);
         if (n_rows <= 0 || n_cols <= 0 || n_rows % 256 || nbytes != raw_bytes(type, n_rows, n_cols))
             return fail(e, TFR_E_INVALID, "tensor %s: bad shape or byte size", name);
         if (e->held.count(nm)) return fail(e, TFR_E_INVALID, "tensor %s uploaded twice", name);
@@ -560,15 +700,25 @@ static int finalize_linear_layer(tfr_engine* e, int i, LayerW& L) {
             return fail(e, TFR_E_INVALID, "tensor %s%s is %lldx%lld, expected %dx%d", p.c_str(), names[k], (long long)h.K,
                         (long long)h.N, K, rows[k]);
         if (k == 0) type = h.type;
-        if (h.type != type) return fail(e, TFR_E_UNSUPPORTED, "layer %d: the four linear-attention projections must share one type", i);
+        if (h.type != type) type = -1;  // mixed types: one launch per matrix instead of the stacked one
         all.insert(all.end(), h.bytes.begin(), h.bytes.end());
     }
     const int total = ch + vd + 2 * nv;
-    tfr_mat* m = nullptr;
-    int rc = mat_create_impl(e, type, K, total, all.data(), all.size(), 0, e->stream, &m);
-    if (rc) return rc;
-    e->mats[p + "gdn_proj"] = m;
-    L.gdn_proj = m;
+    int rc = TFR_OK;
+    if (type >= 0) {
+        tfr_mat* m = nullptr;
+        rc = mat_create_impl(e, type, K, total, all.data(), all.size(), 0, e->stream, &m);
+        if (rc) return rc;
+        e->mats[p + "gdn_proj"] = m;
+        L.gdn_proj = m;
+    } else {
+        for (int k = 0; k < 4; k++) {
+            const HostRaw& h = e->held[p + names[k]];
+            rc = mat_create_impl(e, h.type, K, rows[k], h.bytes.data(), h.bytes.size(), 0, e->stream, &L.proj4[k]);
+            if (rc) return rc;
+            e->mats[p + names[k]] = L.proj4[k];
+        }
+    }
     L.ssm_out = need_mat(e, p + "ssm_out.weight", vd, K, rc);
     L.conv_w = need_vec(e, p + "ssm_conv1d.weight", c.ssm_conv_kernel * ch, false, rc);
     L.ssm_a = need_vec(e, p + "ssm_a", nv, false, rc);
@@ -605,6 +755,7 @@ extern "C" int tfr_finalize_load(tfr_engine* e) {
     }
     e->output_norm = need_vec(e, "output_norm.weight", K, false, rc);
     if (rc) return rc;
+    if (e->token_embd->m.type == TFR_Q8_0) return fail(e, TFR_E_UNSUPPORTED, "token_embd must be Q4_K or Q6_K (no Q8_0 embedding lookup)");
     e->layers.resize(c.n_layer);
     for (int i = 0; i < c.n_layer; i++) {
         const std::string p = "blk." + std::to_string(i) + ".";
@@ -788,6 +939,7 @@ template <class Epi>
 static cudaError_t launch_typed(cudaStream_t s, int grid, int type, const PrepArgs& pa, const RowJob& ja, const RowJob& jb,
                                 const F32Seg& fseg, const Epi& epi, int K, TokenState* st) {
     if (type == TFR_Q4_K) return launch_gemv<BlockQ4, Epi>(s, grid, pa, ja, jb, fseg, epi, K, st);
+    if (type == TFR_Q8_0) return launch_gemv<BlockQ8, Epi>(s, grid, pa, ja, jb, fseg, epi, K, st);
     return launch_gemv<BlockQ6, Epi>(s, grid, pa, ja, jb, fseg, epi, K, st);
 }
 
@@ -854,11 +1006,31 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
         const tfr_mat* wout = L.wo;
         if (L.kind == LAYER_LINEAR) {
             // 1. norm + quant + [qkv | z | beta | alpha] projections (layer.rs:736-798)
-            EpiStore ep{e->proj, nullptr, 0, L.gdn_proj->m.N};
-            if (launch_typed(s, cap, L.gdn_proj->m.type, pn, make_job(L.gdn_proj->m, 2, cap), RowJob{}, F32Seg{}, ep, K, e->st) !=
-                cudaSuccess)
-                return -1;
-            n++;
+            if (L.gdn_proj) {
+                EpiStore ep{e->proj, nullptr, 0, L.gdn_proj->m.N};
+                if (launch_typed(s, cap, L.gdn_proj->m.type, pn, make_job(L.gdn_proj->m, 2, cap), RowJob{}, F32Seg{}, ep, K, e->st) !=
+                    cudaSuccess)
+                    return -1;
+                n++;
+            } else {
+                // mixed weight types (e.g. a Q5_K attn_qkv beside a Q4_K attn_gate): one launch per matrix, as the
+                // reference does (layer.rs:754-797); only the first may be the embedding / residual-writing one
+                int off = 0;
+                for (int k4 = 0; k4 < 4; k4++) {
+                    const tfr_mat* w = L.proj4[k4];
+                    PrepArgs pk = pn;
+                    if (k4 > 0) {
+                        pk.vec = e->x;
+                        pk.raw_out = nullptr;
+                    }
+                    pk.prof_id = n;
+                    EpiStore ep{e->proj + off, nullptr, 0, w->m.N};
+                    if (launch_typed(s, cap, w->m.type, pk, make_job(w->m, 2, cap), RowJob{}, F32Seg{}, ep, K, e->st) != cudaSuccess)
+                        return -1;
+                    off += w->m.N;
+                    n++;
+                }
+            }
             // 2. conv + SiLU + L2 + gated delta rule + gated RMSNorm (layer.rs:838-911)
             GdnArgs g{};
             g.proj = e->proj;
@@ -1416,6 +1588,8 @@ extern "C" int tfr_op_int_dots(const tfr_mat* w, const int8_t* q8, const float* 
     const size_t smem = act_smem_bytes(w->m.K, false, false);
     if (w->m.type == TFR_Q4_K)
         k_int_dots<BlockQ4><<<sm_count_cached(), 256, smem, (cudaStream_t)stream>>>(w->m, (const signed char*)q8, d8, a, b);
+    else if (w->m.type == TFR_Q8_0)
+        k_int_dots<BlockQ8><<<sm_count_cached(), 256, smem, (cudaStream_t)stream>>>(w->m, (const signed char*)q8, d8, a, b);
     else
         k_int_dots<BlockQ6><<<sm_count_cached(), 256, smem, (cudaStream_t)stream>>>(w->m, (const signed char*)q8, d8, a, b);
     return check(cudaGetLastError());

@@ -32,18 +32,23 @@ namespace tfr {
 
 constexpr int GEMV_THREADS = 1024;  // one CTA per SM
 constexpr int GEMV_WARPS = GEMV_THREADS / 32;
-constexpr int Q4_PIECES = 9, Q6_PIECES = 13;
+constexpr int Q4_PIECES = 9, Q6_PIECES = 13, Q8_PIECES = 17;
 constexpr int Q4_TILE_BYTES = 32 * 144, Q6_TILE_BYTES = 32 * 210;
+// Q8_0 (34 B per 32 weights): eight consecutive blocks = 272 contiguous bytes are handled as one 256-weight block
+constexpr int Q8_SUPER_BYTES = 8 * 34, Q8_TILE_BYTES = 32 * Q8_SUPER_BYTES;
 
 enum { WT_Q4K = 0, WT_Q6K = 1 };
 
 struct Mat {
     const uint8_t* data;  // tiled
-    int type;             // TFR_Q4_K / TFR_Q6_K
+    int type;             // TFR_Q4_K / TFR_Q6_K / TFR_Q8_0
     int K, N, nb;         // nb = K / 256
 };
 
-__host__ __device__ inline int tile_bytes(int type) { return type == TFR_Q4_K ? Q4_TILE_BYTES : Q6_TILE_BYTES; }
+__host__ __device__ inline int tile_bytes(int type) {
+    return type == TFR_Q4_K ? Q4_TILE_BYTES : type == TFR_Q8_0 ? Q8_TILE_BYTES : Q6_TILE_BYTES;
+}
+__host__ __device__ inline int block_bytes_256(int type) { return type == TFR_Q4_K ? 144 : type == TFR_Q8_0 ? Q8_SUPER_BYTES : 210; }
 __host__ __device__ inline long long mat_tiles(int K, long long N) { return (N * (K / 256) + 31) / 32; }
 __host__ __device__ inline long long mat_device_bytes(int type, int K, long long N) {
     return mat_tiles(K, N) * tile_bytes(type);
@@ -238,6 +243,9 @@ struct BlockQ4 {
 struct BlockQ6 {
     static constexpr int TILE_BYTES = Q6_TILE_BYTES;
 };
+struct BlockQ8 {
+    static constexpr int TILE_BYTES = Q8_TILE_BYTES;
+};
 
 // 16-byte piece `i` of this lane's block inside a tile.  SMEM: the tile is the shared-memory copy.
 template <bool SMEM>
@@ -341,6 +349,51 @@ __device__ __forceinline__ float block_dot(BlockQ6, const uint8_t* tile, int lan
         }
     }
     return f16_to_f32((unsigned short)dbits) * acc;
+}
+
+// Eight Q8_0 blocks (kernels/gemv.cu:1558-1582 over a 256-weight stretch): per 32-block
+// sum = dot(int8 weights, int8 activation), acc += d_w * d_x * sum.  The 272 bytes are [d0 q0[32] d1 q1[32] ...]:
+// the quants of even blocks start 2 bytes into a word and are realigned with a funnel shift, those of
+// odd blocks are word-aligned.  ints (optional): the eight integer sums.
+template <bool SMEM>
+__device__ __forceinline__ float block_dot(BlockQ8, const uint8_t* tile, int lane, const Act& act, int b, int nb, int* ints) {
+    const float4 d8a = reinterpret_cast<const float4*>(act.d8)[2 * b], d8b = reinterpret_cast<const float4*>(act.d8)[2 * b + 1];
+    const float d8[8] = {d8a.x, d8a.y, d8a.z, d8a.w, d8b.x, d8b.y, d8b.z, d8b.w};
+    const int4* aq = act.q8 + b;
+    float acc = 0.f;
+    // words 17m .. 17m+16 hold blocks 2m (d in the low half of word 0) and 2m+1 (d in the high half of word 8)
+    auto word = [&](int w) -> unsigned int {
+        const uint8_t* p = tile + (w >> 2) * 512 + lane * 16 + (w & 3) * 4;
+        if (SMEM) {
+            unsigned int v;
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)));
+            return v;
+        }
+        return *reinterpret_cast<const unsigned int*>(p);
+    };
+#pragma unroll
+    for (int m = 0; m < 4; m++) {
+        unsigned int w[17];
+#pragma unroll
+        for (int i = 0; i < 17; i++) w[i] = word(17 * m + i);
+        const int4 a0 = aq[(4 * m) * nb], a1 = aq[(4 * m + 1) * nb], a2 = aq[(4 * m + 2) * nb], a3 = aq[(4 * m + 3) * nb];
+        const int ae[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        const int ao[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
+        int se = 0, so = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            se = __dp4a((int)__funnelshift_r(w[i], w[i + 1], 16), ae[i], se);
+            so = __dp4a((int)w[9 + i], ao[i], so);
+        }
+        if (ints) {
+            ints[2 * m] = se;
+            ints[2 * m + 1] = so;
+        }
+        const float de = f16_to_f32((unsigned short)(w[0] & 0xffff)), dq = f16_to_f32((unsigned short)(w[8] >> 16));
+        acc += de * d8[2 * m] * (float)se;
+        acc += dq * d8[2 * m + 1] * (float)so;
+    }
+    return acc;
 }
 
 // One run of 16 elements (scale group c = 8n + 2j + is) of Q6_K block f against the fp32

@@ -645,6 +645,8 @@ __global__ void k_int_dots(Mat m, const signed char* q8, const float* d8, int* o
                 for (int i = 0; i < 32; i++) sacc += q8[256 * b + 32 * j + i];
                 outB[(size_t)r * (K / 32) + 8 * b + j] = sacc;
             }
+        } else if (BLK::TILE_BYTES == Q8_TILE_BYTES) {
+            for (int j = 0; j < 8; j++) outA[(size_t)r * (K / 32) + 8 * b + j] = ints[j];
         } else {
             for (int c = 0; c < 16; c++) outA[(size_t)r * (K / 16) + 16 * b + c] = ints[c];
         }
@@ -663,8 +665,8 @@ __device__ __forceinline__ int perm_src_row(int v, int perm_hd) {
 // piece); tail tiles are zero-filled by the caller.
 __global__ void k_repack_tiled(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int type, int N, int nb,
                                int perm_hd) {
-    const int pieces = type == TFR_Q4_K ? Q4_PIECES : Q6_PIECES + 1;  // Q6_K: 13 pieces + the 2-byte d
-    const int blk = type == TFR_Q4_K ? 144 : 210, TB = tile_bytes(type);
+    const int pieces = type == TFR_Q4_K ? Q4_PIECES : type == TFR_Q8_0 ? Q8_PIECES : Q6_PIECES + 1;  // Q6_K: 13 pieces + the 2-byte d
+    const int blk = block_bytes_256(type), TB = tile_bytes(type);
     const long long total = (long long)N * nb * pieces;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const long long f = i / pieces;

@@ -376,6 +376,15 @@ def op_attention_noalloc(q, kc, vc, out, n_head: int, n_kv: int, head_dim: int, 
                                             stream), "attention_noalloc: shape exceeds the built-in scratch or CUDA error")
 
 
+def transcode_to_q8_0(src_type: int, raw: np.ndarray) -> np.ndarray:
+    """The loader's one-off Q5_K (13) / Q5_1 (7) -> Q8_0 conversion (host code, load.rs:33-133)."""
+    raw = np.ascontiguousarray(raw, dtype=np.uint8).reshape(-1)
+    blk, per = (176, 8) if src_type == 13 else (24, 1)
+    out = np.zeros(raw.size // blk * per * 34, np.uint8)
+    _ok(_lib.lib().tfr_transcode_to_q8_0(src_type, raw.ctypes.data, raw.size, out.ctypes.data), "transcode_to_q8_0")
+    return out
+
+
 def nccl_unique_id() -> bytes:
     buf = C.create_string_buffer(128)
     _ok(_lib.lib().tfr_tp_nccl_unique_id(buf), "nccl_unique_id: libnccl.so.2 not available")

@@ -13,7 +13,8 @@ from __future__ import annotations
 import numpy as np
 
 Q4_K, Q6_K, F32 = 12, 14, 0
-BLOCK_BYTES = {Q4_K: 144, Q6_K: 210}
+Q8_0, Q5_K, Q5_1 = 8, 13, 7
+BLOCK_BYTES = {Q4_K: 144, Q6_K: 210, Q8_0: 8 * 34}  # bytes per 256 weights
 
 
 # ------------------------------------------------------------------ random blocks
@@ -28,6 +29,39 @@ def random_q4_k(rng: np.random.Generator, n_blocks: int, d_sigma: float = 0.003)
     mn = rng.integers(0, 64, size=(n_blocks, 8), dtype=np.uint8)
     out[:, 4:16] = pack_scales_k4(sc, mn)
     out[:, 16:144] = rng.integers(0, 256, size=(n_blocks, 128), dtype=np.uint8)
+    return out
+
+
+def random_q5_k(rng: np.random.Generator, n_blocks: int, d_sigma: float = 0.003) -> np.ndarray:
+    """n_blocks Q5_K blocks (176 B: fp16 d, dmin, 12 scale bytes, 32 qh bytes, 128 qs bytes), uniform contents."""
+    out = np.empty((n_blocks, 176), np.uint8)
+    out[:, 4:] = rng.integers(0, 256, size=(n_blocks, 172), dtype=np.uint8)
+    dd = np.abs(rng.normal(0, d_sigma, size=(n_blocks, 2))).astype(np.float16)
+    out[:, 0:4] = dd.view(np.uint8).reshape(n_blocks, 4)
+    return out
+
+
+def random_q5_1(rng: np.random.Generator, n_blocks: int) -> np.ndarray:
+    """n_blocks Q5_1 blocks (24 B: fp16 d, fp16 min, 4 qh bytes, 16 qs bytes)."""
+    out = np.empty((n_blocks, 24), np.uint8)
+    out[:, 4:] = rng.integers(0, 256, size=(n_blocks, 20), dtype=np.uint8)
+    dm = np.stack([np.abs(rng.normal(0, 0.01, n_blocks)), rng.normal(0, 0.05, n_blocks)], 1).astype(np.float16)
+    out[:, 0:4] = dm.view(np.uint8).reshape(n_blocks, 4)
+    return out
+
+
+def quantize_q8_0(w: np.ndarray) -> np.ndarray:
+    """fp32 rows [N][K] -> Q8_0 bytes [N][K/32][34]: d = amax / 127 (fp16), q = round-half-away(x / d)."""
+    N, K = w.shape
+    g = w.reshape(N, K // 32, 32).astype(np.float32)
+    amax = np.abs(g).max(-1)
+    d = np.where(amax == 0, 0, amax / np.float32(127.0)).astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        r = np.where(d[..., None] == 0, 0, g / d[..., None])
+    q = np.clip(np.sign(r) * np.floor(np.abs(r) + 0.5), -127, 127).astype(np.int8)
+    out = np.empty((N, K // 32, 34), np.uint8)
+    out[..., 0:2] = d.astype(np.float16).view(np.uint8).reshape(N, K // 32, 2)
+    out[..., 2:] = q.view(np.uint8)
     return out
 
 

@@ -54,3 +54,15 @@ def test_random_blocks_have_requested_distribution():
     b6 = S.random_q6_k(rng, 4000)
     sc = b6[:, 192:208].view(np.int8)
     assert sc.min() == -32 and sc.max() == 31
+
+
+def test_host_transcode_matches_the_oracle_byte_for_byte(cuda_lib, oracle):
+    """tfr_transcode_to_q8_0 is host code: the library's Q5_K / Q5_1 -> Q8_0 conversion against the CPU oracle's."""
+    import numpy as np
+    from taraference_b200 import engine as E, synth as S
+    rng = np.random.default_rng(4)
+    for src, blocks in ((S.Q5_K, S.random_q5_k(rng, 200)), (S.Q5_1, S.random_q5_1(rng, 333))):
+        assert np.array_equal(E.transcode_to_q8_0(src, blocks), oracle.transcode_to_q8_0(src, blocks))
+    # all-zero blocks: scale 0, quants 0
+    z = np.zeros((3, 176), np.uint8)
+    assert not E.transcode_to_q8_0(S.Q5_K, z).any()

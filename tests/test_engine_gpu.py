@@ -294,3 +294,25 @@ def test_forward_greedy_all_equals_token_by_token(E, cfg):
     kv.free()
     kv2.free()
     m.destroy()
+
+
+def test_full_size_32b_shapes_teacher_forced(E):
+    """Two layers at the Qwen2.5-32B shape (K = 5120: the reference's split-K Q4_K route; down K = 27648;
+    40 / 8 heads) with the untied 152 064-row head, against the reference's kernels layer by layer."""
+    from oracle import ref_gpu
+    from taraference_b200 import synth_gpu
+    if not ref_gpu.available():
+        pytest.skip("reference cubin not present")
+    cfg = dict(S.QWEN25_32B, n_layer=2)
+    m, host = synth_gpu.build_model(cfg, seed=0, keep_host=True)
+    kv = m.alloc_kv(16)
+    rm = ref_gpu.RefModel(cfg, host, 16)
+    to_t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32).copy()).cuda()
+    le, he = teacher_forced_errors(
+        m, kv, lambda t: ref_gpu.embed(rm.embd, t).cpu().numpy(),
+        lambda li, x, pos: rm.layer_forward(li, to_t(x), pos).cpu().numpy(),
+        lambda x: rm.head_forward(to_t(x)).cpu().numpy(), cfg, [11, 152000, 4242])
+    assert np.median(le) < TF_TYPICAL and le.max() < TF_WORST, le
+    assert he.max() < TF_WORST and np.median(he) < TF_TYPICAL, he
+    kv.free()
+    m.destroy()

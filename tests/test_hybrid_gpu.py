@@ -244,3 +244,61 @@ def test_hybrid_config_errors(E):
     del tens["blk.0.ssm_beta.weight"]
     with pytest.raises(E.TfrError, match="ssm_beta"):
         E.CudaModel.load_with(S.TINY_HYBRID, tens)
+
+
+def test_full_size_hybrid_4b_shapes_teacher_forced(E, oracle):
+    """Four layers (three Gated-DeltaNet + one gated full attention) at the full hybrid 4B shape — 8192-channel
+    conv, 32 V heads, head_dim 256, 151 936-row tied head — against the reference's kernels and the CPU oracle,
+    layer by layer with identical inputs."""
+    from oracle import ref_gpu
+    from taraference_b200 import synth_gpu
+    cfg = dict(S.QWEN35_4B, n_layer=4)
+    m, host = synth_gpu.build_model(cfg, seed=0, keep_host=True)
+    kv = m.alloc_kv(32)
+    toks_in = [100, 2000, 30000, 151000, 7]
+    to_t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32).copy()).cuda()
+    if ref_gpu.available():
+        rm = ref_gpu.RefModel(cfg, host, 32)
+        le, he = teacher_forced_errors(
+            m, kv, lambda t: ref_gpu.embed(rm.embd, t).cpu().numpy(),
+            lambda li, x, pos: rm.layer_forward(li, to_t(x), pos).cpu().numpy(),
+            lambda x: rm.head_forward(to_t(x)).cpu().numpy(), cfg, toks_in)
+        assert np.median(le) < TF_TYPICAL and (le < 1e-5).mean() >= 0.5 and le.max() < TF_WORST, le
+        assert he.max() < TF_WORST and np.median(he) < TF_TYPICAL, he
+        gs = m.debug_read("ssm_state", cfg["ssm_n_v"] * 128 * 128, kv=kv, layer=1)
+        assert _rel(gs, rm.ssm[1].cpu().numpy()) < 1e-2
+        kv.clear()
+        m.zero_recurrent(kv)
+    oracle.set_threads(oracle.max_threads())
+    om = oracle.OracleModel(cfg, host, 32)
+    le, he = teacher_forced_errors(m, kv, om.embed, om.layer_forward, om.head_forward, cfg, toks_in[:3])
+    oracle.set_threads(1)
+    assert np.median(le) < 5e-5 and le.max() < TF_WORST and he.max() < TF_WORST, (le, he)
+    kv.free()
+    m.destroy()
+
+
+def test_hybrid_with_q5_k_and_q8_0_tensors(E, oracle):
+    """The tensor mix of real hybrid files: attn_qkv and ssm_out as Q5_K (converted to Q8_0 at upload, the other
+    three projections stay Q4_K, so the four are launched one by one), attn_output as Q8_0."""
+    cfg = S.TINY_HYBRID
+    tens = S.make_model(cfg, seed=5)
+    rng = np.random.default_rng(1)
+    oracle_tens = dict(tens)
+    for name in list(tens):
+        if name.endswith("attn_qkv.weight") or name.endswith("ssm_out.weight"):
+            t, K, N, _ = tens[name]
+            q5 = S.random_q5_k(rng, N * (K // 256), d_sigma=0.0015).reshape(-1)
+            tens[name] = (S.Q5_K, K, N, q5)
+            oracle_tens[name] = (S.Q8_0, K, N, oracle.transcode_to_q8_0(S.Q5_K, q5))
+        elif name.endswith("attn_output.weight"):
+            t, K, N, _ = tens[name]
+            q8 = S.quantize_q8_0(rng.normal(0, 0.02, (N, K)).astype(np.float32)).reshape(-1)
+            tens[name] = oracle_tens[name] = (S.Q8_0, K, N, q8)
+    om = oracle.OracleModel(cfg, oracle_tens, 32)
+    m = E.CudaModel.load_with(cfg, tens)
+    kv = m.alloc_kv(32)
+    le, he = teacher_forced_errors(m, kv, om.embed, om.layer_forward, om.head_forward, cfg, [5, 17, 3, 250])
+    assert np.median(le) < 2e-5 and le.max() < TF_WORST and he.max() < TF_WORST, (le, he)
+    kv.free()
+    m.destroy()

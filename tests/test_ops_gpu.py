@@ -268,3 +268,38 @@ def test_device_quantizer_emits_valid_blocks(E, oracle):
         E.synth_quantize(t, w, out)
         back = oracle.dequant_rows(t, out.cpu().numpy(), 1024, 64)
         assert np.abs(back - w.cpu().numpy()).max() <= tol * float(w.abs().max())
+
+
+@pytest.mark.parametrize("K,N", [(256, 40), (2048, 96), (2560, 33)])
+def test_q8_0_gemv_vs_oracle_and_reference(E, oracle, K, N):
+    """Q8_0 weights (what Q5_K / Q5_1 tensors become at load): integer block sums bit-exact, floats vs the
+    oracle and vs the reference's gemv_q8_0_global."""
+    from oracle import ref_gpu
+    rng = np.random.default_rng(K + N)
+    raw = S.quantize_q8_0(rng.normal(0, 0.05, (N, K)).astype(np.float32)).reshape(-1)
+    x = rng.normal(0, 1, K).astype(np.float32)
+    bias = rng.normal(0, 1, N).astype(np.float32)
+    m = E.GpuMat(S.Q8_0, K, N, raw)
+    out = torch.zeros(N, device="cuda")
+    E.op_gemv(m, dev(x), out, bias=dev(bias))
+    want = oracle.gemv(oracle.mat(oracle.Q8_0, raw, K, N), x, bias=bias)
+    assert _rel(out.cpu().numpy(), want) < 2e-5
+    q8, d8 = oracle.quantize_q8(x)
+    sums = torch.zeros(N * (K // 32), dtype=torch.int32, device="cuda")
+    E.op_int_dots(m, dev(q8), dev(d8), sums)
+    rows = raw.reshape(N, -1)
+    for r in (0, N // 2, N - 1):
+        assert np.array_equal(sums.cpu().numpy().reshape(N, K // 32)[r], oracle.q8_0_blockdots(rows[r], K, q8))
+    if ref_gpu.available():
+        ref = ref_gpu.gemv_q8(ref_gpu.RefMat(S.Q8_0, K, N, raw), dev(x), bias=dev(bias))
+        assert _rel(out.cpu().numpy(), ref.cpu().numpy()) < 5e-6
+    # a Q5_K tensor handed to the library becomes the same Q8_0 matrix
+    q5 = S.random_q5_k(rng, N * (K // 256)).reshape(-1)
+    m5 = E.GpuMat(S.Q5_K, K, N, q5)
+    out5, out8 = torch.zeros(N, device="cuda"), torch.zeros(N, device="cuda")
+    E.op_gemv(m5, dev(x), out5)
+    m8 = E.GpuMat(S.Q8_0, K, N, oracle.transcode_to_q8_0(S.Q5_K, q5))
+    E.op_gemv(m8, dev(x), out8)
+    assert torch.equal(out5, out8)
+    for mm in (m, m5, m8):
+        mm.free()

@@ -266,3 +266,36 @@ def test_tiny_hybrid_model_layer_kinds_state_and_reset(oracle):
     assert np.array_equal(toks, t2) and np.array_equal(last, l2)
     t3, _, l3 = om.decode_greedy(0, 5, 6)  # state carried over: a different sequence state
     assert not np.array_equal(last, l3)
+
+
+def test_q8_0_dot_and_transcodes_against_independent_restatements(oracle):
+    """Q8_0 x Q8 dots against numpy; the loader's Q5_K / Q5_1 -> Q8_0 conversion against gguf-py's
+    block decode followed by a numpy Q8_0 quantiser."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import GGMLQuantizationType as T, quants
+    rng = np.random.default_rng(9)
+    K, N = 512, 5
+    w = rng.normal(0, 0.05, (N, K)).astype(np.float32)
+    raw = S.quantize_q8_0(w)
+    assert np.array_equal(quants.dequantize(raw.reshape(-1), T.Q8_0).reshape(N, K),
+                          raw[..., 0:2].copy().view(np.float16).astype(np.float32).repeat(32, -1).reshape(N, K)
+                          * raw[..., 2:].view(np.int8).reshape(N, K))
+    x = rng.normal(0, 1, K).astype(np.float32)
+    q8, d8 = oracle.quantize_q8(x)
+    m = oracle.mat(oracle.Q8_0, raw.reshape(-1), K, N)
+    y = oracle.gemv(m, x)
+    qw = raw[..., 2:].view(np.int8).astype(np.int64).reshape(N, K // 32, 32)
+    sums = (qw * q8.astype(np.int64).reshape(K // 32, 32)).sum(-1)
+    assert np.array_equal(oracle.q8_0_blockdots(raw[3].reshape(-1), K, q8), sums[3].astype(np.int32))
+    dw = raw[..., 0:2].copy().view(np.float16).astype(np.float64).reshape(N, K // 32)
+    assert np.allclose(y, (dw * d8 * sums).sum(-1), rtol=1e-5, atol=1e-7)
+    # transcodes
+    for src, blocks, gt in ((S.Q5_K, S.random_q5_k(rng, 37), T.Q5_K), (S.Q5_1, S.random_q5_1(rng, 64), T.Q5_1)):
+        vals = quants.dequantize(blocks.reshape(-1), gt).reshape(-1, 32).astype(np.float32)
+        want = S.quantize_q8_0(vals.reshape(1, -1)).reshape(-1, 34)
+        got = oracle.transcode_to_q8_0(src, blocks).reshape(-1, 34)
+        assert np.array_equal(got[:, :2], want[:, :2])                      # fp16 scales
+        dq = got[:, 2:].view(np.int8).astype(np.int32) - want[:, 2:].view(np.int8).astype(np.int32)
+        # gguf-py decodes with numpy broadcasting (same products, possibly another rounding of the last bit of a
+        # value that sits on a rounding border): allow isolated +-1
+        assert np.abs(dq).max() <= 1 and (dq != 0).mean() < 2e-3, (np.abs(dq).max(), (dq != 0).mean())
