@@ -143,6 +143,15 @@ int tfr_decode_burst(tfr_engine* e, tfr_kv* kv, uint32_t first_token, int max_n,
  * tp_size > 1 every rank holds the logits of its vocabulary rows only: the call fills
  * out[first, end) of tfr_tp_vocab_range and leaves the rest of out untouched. */
 int tfr_current_logits(tfr_engine* e, float* out, int n);
+/* The reference's vocabulary shortlist, load.rs:285-352 (an approximation it reports on stderr): the head runs
+ * over ids [0, limit) and, when special_id lies in [limit, n_vocab), over that one extra row (the end-of-sequence
+ * token), whose logit is stored at index `limit` and whose argmax index is mapped back to special_id
+ * (forward.rs:107-118).  Call between tfr_set_config and tfr_finalize_load; limit must be even, >= 1024 and
+ * < n_vocab; limit = 0 removes the shortlist.  tfr_load_gguf applies the reference's rule by itself
+ * (TARAFER_VOCAB_LIMIT, else 49 152 for a hybrid with more than 100 000 tokens unless TARAFER_FULL_VOCAB is set).
+ * tfr_current_logits then fills n_active entries; tfr_active_vocab reports n_active and the extra row's id (-1: none). */
+int tfr_set_vocab_shortlist(tfr_engine* e, int limit, int special_id);
+int tfr_active_vocab(const tfr_engine* e, int* n_active, int* special_id);
 
 /* ---- tensor parallelism (new: the reference drives one GPU, device.rs:85-95) ----
  * One engine per GPU, created with tfr_model_config.tp_size = N and its tp_rank.  Every rank is

@@ -73,6 +73,8 @@ def lib() -> C.CDLL:
         "tfr_forward_greedy_all": (i32, [vp, vp, vp, i32, vp]),
         "tfr_decode_burst": (i32, [vp, vp, C.c_uint32, i32, vp, i32, vp, C.POINTER(i32)]),
         "tfr_current_logits": (i32, [vp, vp, i32]),
+        "tfr_set_vocab_shortlist": (i32, [vp, i32, i32]),
+        "tfr_active_vocab": (i32, [vp, vp, vp]),
         "tfr_tp_exchange_bytes": (i32, [vp, C.POINTER(sz)]),
         "tfr_tp_ipc_handle": (i32, [vp, vp]),
         "tfr_tp_attach_ipc": (i32, [vp, vp]),

@@ -12,6 +12,8 @@
 // from global memory.  Arithmetic is fp32 on f16 data as in the reference; exp is the build's
 // ex2-based expf.
 #pragma once
+#include <type_traits>
+
 #include "tfr_common.cuh"
 
 namespace tfr {
@@ -108,6 +110,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
 #pragma unroll
         for (int d = 0; d < DPT; d++) o[h][d] = 0.f;
     __syncthreads();
+    prof_mark(4, a.prof_id);
 
     const int kg = tid >> 6, dp = tid & 63;
     constexpr int VK = ATTN_TILE / 4;  // keys per thread and tile in the value phase
@@ -127,7 +130,24 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
             }
         }
         // ---- scores: batches of four keys; batch bt of warp w covers keys 32*bt + 4*w .., so a short
-        // tile spreads over all warps and its empty second batch is skipped
+        // tile spreads over all warps and its empty second batch is skipped.  The K rows of both batches
+        // are requested before the first is used: one memory round trip instead of two.
+        using KRaw = typename std::conditional<DL == 8, uint4, typename std::conditional<DL == 4, uint2, unsigned int>::type>::type;
+        KRaw kraw[2][4];
+#pragma unroll
+        for (int bt = 0; bt < 2; bt++) {
+            const int kbase = (bt * 8 + warp) * 4;
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++) {
+                const int t = tt + kbase + kk;
+                kraw[bt][kk] = KRaw{};
+                if (kbase < tn && t < t1) {
+                    const unsigned short* kr = a.kc + (size_t)t * kvdim + g * HD + lane * DL;
+                    if constexpr (DL == 1) kraw[bt][kk] = *kr;
+                    else kraw[bt][kk] = *reinterpret_cast<const KRaw*>(kr);
+                }
+            }
+        }
 #pragma unroll
         for (int bt = 0; bt < 2; bt++) {
             const int kbase = (bt * 8 + warp) * 4;
@@ -138,31 +158,26 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
             float v[32];
 #pragma unroll
             for (int kk = 0; kk < 4; kk++) {
-                const int t = tt + kbase + kk;
                 float kf[DL];
-                if (t < t1) {
-                    const unsigned short* kr = a.kc + (size_t)t * kvdim + g * HD + lane * DL;
-                    if constexpr (DL == 4) {
-                        const uint2 raw = *reinterpret_cast<const uint2*>(kr);
-                        kf[0] = f16_to_f32((unsigned short)(raw.x & 0xffff));
-                        kf[1] = f16_to_f32((unsigned short)(raw.x >> 16));
-                        kf[2] = f16_to_f32((unsigned short)(raw.y & 0xffff));
-                        kf[3] = f16_to_f32((unsigned short)(raw.y >> 16));
-                    } else if constexpr (DL == 8) {
-                        const uint4 raw = *reinterpret_cast<const uint4*>(kr);
-                        const unsigned int rw[4] = {raw.x, raw.y, raw.z, raw.w};
+                if constexpr (DL == 4) {
+                    const uint2 raw = kraw[bt][kk];
+                    kf[0] = f16_to_f32((unsigned short)(raw.x & 0xffff));
+                    kf[1] = f16_to_f32((unsigned short)(raw.x >> 16));
+                    kf[2] = f16_to_f32((unsigned short)(raw.y & 0xffff));
+                    kf[3] = f16_to_f32((unsigned short)(raw.y >> 16));
+                } else if constexpr (DL == 8) {
+                    const uint4 raw = kraw[bt][kk];
+                    const unsigned int rw[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-                        for (int d = 0; d < 4; d++) {
-                            kf[2 * d] = f16_to_f32((unsigned short)(rw[d] & 0xffff));
-                            kf[2 * d + 1] = f16_to_f32((unsigned short)(rw[d] >> 16));
-                        }
-                    } else {
-#pragma unroll
-                        for (int d = 0; d < DL; d++) kf[d] = f16_to_f32(kr[d]);
+                    for (int d = 0; d < 4; d++) {
+                        kf[2 * d] = f16_to_f32((unsigned short)(rw[d] & 0xffff));
+                        kf[2 * d + 1] = f16_to_f32((unsigned short)(rw[d] >> 16));
                     }
+                } else if constexpr (DL == 2) {
+                    kf[0] = f16_to_f32((unsigned short)(kraw[bt][kk] & 0xffff));
+                    kf[1] = f16_to_f32((unsigned short)(kraw[bt][kk] >> 16));
                 } else {
-#pragma unroll
-                    for (int d = 0; d < DL; d++) kf[d] = 0.f;
+                    kf[0] = f16_to_f32((unsigned short)kraw[bt][kk]);
                 }
 #pragma unroll
                 for (int h = 0; h < ATTN_REP_MAX; h++) {
@@ -178,6 +193,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
             sc[h][kbase + kk] = (t < t1 && h < rep) ? tot * a.scale : -1e30f;
         }
         __syncthreads();
+        prof_mark(6, a.prof_id);
         // ---- online softmax bookkeeping: warp h owns head h
         if (warp < rep) {
             const float s0 = sc[warp][lane], s1 = sc[warp][lane + 32];
@@ -197,6 +213,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
             }
         }
         __syncthreads();
+        prof_mark(7, a.prof_id);
         // ---- values: thread (kg, dp) accumulates keys kg, kg+4, ... for dims dp*DPT..
 #pragma unroll
         for (int h = 0; h < ATTN_REP_MAX; h++) {
@@ -245,17 +262,31 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
         }
         cluster_sync_all();
         prof_mark(3, a.prof_id);
-        // member s finishes the dims idx with idx % ATTN_CLUSTER == s
+        // member s finishes the dims idx with idx % ATTN_CLUSTER == s.  All members' values are requested
+        // before any is used (remote shared-memory loads cost a few hundred nanoseconds each when they
+        // wait for one another); idle members hold m = -1e30, l = 0, O = 0 and drop out of the sums.
         for (int idx = s + ATTN_CLUSTER * tid; idx < rep * HD; idx += ATTN_CLUSTER * ATTN_THREADS) {
             const int h = idx / HD, d = idx % HD;
             const int hg = g * rep + h;
+            float mr[ATTN_CLUSTER], lr[ATTN_CLUSTER], orr[ATTN_CLUSTER];
+#pragma unroll
+            for (int r = 0; r < ATTN_CLUSTER; r++) {
+                mr[r] = ld_dsmem_f32(&m_s[h], r);
+                lr[r] = ld_dsmem_f32(&l_s[h], r);
+                orr[r] = ld_dsmem_f32(&ored[0][h][d], r);
+            }
             float m = -1e30f;
-            for (int r = 0; r < S_eff; r++) m = fmaxf(m, ld_dsmem_f32(&m_s[h], r));
+#pragma unroll
+            for (int r = 0; r < ATTN_CLUSTER; r++)
+                if (r < S_eff) m = fmaxf(m, mr[r]);
             float l = 0.f, acc = 0.f;
-            for (int r = 0; r < S_eff; r++) {
-                const float al = expf(ld_dsmem_f32(&m_s[h], r) - m);
-                l += al * ld_dsmem_f32(&l_s[h], r);
-                acc += al * ld_dsmem_f32(&ored[0][h][d], r);
+#pragma unroll
+            for (int r = 0; r < ATTN_CLUSTER; r++) {
+                if (r < S_eff) {
+                    const float al = expf(mr[r] - m);
+                    l += al * lr[r];
+                    acc += al * orr[r];
+                }
             }
             float res = acc / fmaxf(l, 1e-20f);
             if (a.gate) res *= 1.f / (1.f + expf(-a.gate[hg * HD + d]));

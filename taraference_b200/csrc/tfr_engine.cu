@@ -134,7 +134,8 @@ struct tfr_engine {
     std::map<std::string, VecT> vecs;
     std::map<std::string, HostRaw> held;
     std::vector<LayerW> layers;
-    tfr_mat *token_embd = nullptr, *head = nullptr;
+    tfr_mat *token_embd = nullptr, *head = nullptr, *head_special = nullptr;
+    int vocab_limit = 0, special_id = -1;  // shortlisted head (load.rs:285-352); 0: the whole vocabulary
     float* output_norm = nullptr;
     // workspaces
     float *x = nullptr, *q = nullptr, *attn = nullptr, *h = nullptr, *logits = nullptr, *partial = nullptr;
@@ -753,6 +754,32 @@ extern "C" int tfr_finalize_load(tfr_engine* e) {
         e->mats["output.weight(view)"] = view;
         e->head = view;
     }
+    if (e->vocab_limit) {
+        // the head runs over rows [0, limit) plus, optionally, one more row (the end-of-sequence token)
+        if (P.tp > 1) return fail(e, TFR_E_UNSUPPORTED, "vocabulary shortlist with tensor parallelism");
+        if (e->vocab_limit >= V) return fail(e, TFR_E_INVALID, "vocabulary shortlist %d is not below n_vocab %d", e->vocab_limit, V);
+        if (e->special_id >= V) return fail(e, TFR_E_INVALID, "shortlist: extra row %d outside the vocabulary", e->special_id);
+        const tfr_mat* full = e->head;
+        tfr_mat* view = new tfr_mat();
+        view->m = full->m;
+        view->m.N = e->vocab_limit;
+        e->mats["output(shortlist)"] = view;
+        e->head = view;
+        if (e->special_id >= 0) {
+            tfr_mat* one = new tfr_mat();
+            one->m = full->m;
+            one->m.N = 1;
+            one->bytes = (size_t)tile_bytes(full->m.type);
+            CU(e, cudaMalloc(&one->dev, one->bytes));
+            CU(e, cudaMemsetAsync(one->dev, 0, one->bytes, e->stream));
+            const int work = full->m.nb * 18;
+            k_extract_row<<<(work + 127) / 128, 128, 0, e->stream>>>(full->m.data, (uint8_t*)one->dev, full->m.type, e->special_id, full->m.nb);
+            CU(e, cudaGetLastError());
+            one->m.data = (const uint8_t*)one->dev;
+            e->mats["output(shortlist extra row)"] = one;
+            e->head_special = one;
+        }
+    }
     e->output_norm = need_vec(e, "output_norm.weight", K, false, rc);
     if (rc) return rc;
     if (e->token_embd->m.type == TFR_Q8_0) return fail(e, TFR_E_UNSUPPORTED, "token_embd must be Q4_K or Q6_K (no Q8_0 embedding lookup)");
@@ -1141,12 +1168,15 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
         epi.logits = e->logits;
         epi.out_tokens = e->out_tokens;
         epi.prompt = e->prompt;
-        epi.n_rows = V;
+        epi.n_rows = e->vocab_limit ? e->vocab_limit + (e->head_special ? 1 : 0) : V;
+        epi.special_row = e->vocab_limit;
+        epi.special_id = e->head_special ? e->special_id : -1;
         epi.row_offset = P.v0;
         epi.use_tp = P.tp > 1 && !e->use_nccl;
         epi.c = e->comm;
         epi.defer_best = P.tp > 1 && e->use_nccl ? e->best_buf : nullptr;
-        if (launch_typed(s, cap, e->head->m.type, pa, make_job(e->head->m, 2, cap), RowJob{}, F32Seg{}, epi, K, e->st) !=
+        const RowJob extra = e->head_special ? make_job(e->head_special->m, 2, cap, e->vocab_limit / 2) : RowJob{};
+        if (launch_typed(s, cap, e->head->m.type, pa, make_job(e->head->m, 2, cap), extra, F32Seg{}, epi, K, e->st) !=
             cudaSuccess)
             return -1;
         n++;
@@ -1334,9 +1364,34 @@ extern "C" int tfr_decode_burst(tfr_engine* e, tfr_kv* kv, uint32_t first_token,
 extern "C" int tfr_current_logits(tfr_engine* e, float* out, int n) {
     if (!e || !out || !e->finalized || n <= 0 || n > e->cfg.n_vocab) return e ? fail(e, TFR_E_INVALID, "current_logits: bad argument") : TFR_E_INVALID;
     cudaSetDevice(e->device);
-    const int first = e->plan.v0, end = e->plan.v1 < n ? e->plan.v1 : n;
+    const int active = e->vocab_limit ? e->vocab_limit + (e->head_special ? 1 : 0) : e->plan.v1;
+    const int first = e->plan.v0, end = active < n ? active : n;
     if (end > first) CU(e, cudaMemcpyAsync(out + first, e->logits, (size_t)(end - first) * 4, cudaMemcpyDeviceToHost, e->stream));
     CU(e, cudaStreamSynchronize(e->stream));
+    return TFR_OK;
+}
+
+extern "C" int tfr_set_vocab_shortlist(tfr_engine* e, int limit, int special_id) {
+    if (!e || !e->has_cfg) return TFR_E_INVALID;
+    if (e->finalized) return fail(e, TFR_E_INVALID, "set_vocab_shortlist: the model is already finalized");
+    if (limit == 0) {
+        e->vocab_limit = 0;
+        e->special_id = -1;
+        return TFR_OK;
+    }
+    // load.rs:301: limits below 1024 or not below n_vocab are ignored there; here they are an error
+    if (limit < 1024 || limit >= e->cfg.n_vocab || (limit & 1))
+        return fail(e, TFR_E_INVALID, "set_vocab_shortlist: limit %d must be even, >= 1024 and < n_vocab %d", limit, e->cfg.n_vocab);
+    // load.rs:308: the extra row exists only for an id outside the shortlist
+    e->vocab_limit = limit;
+    e->special_id = (special_id >= limit && special_id < e->cfg.n_vocab) ? special_id : -1;
+    return TFR_OK;
+}
+extern "C" int tfr_active_vocab(const tfr_engine* e, int* n_active, int* special_id) {
+    if (!e || !e->has_cfg) return TFR_E_INVALID;
+    const bool extra = e->vocab_limit && e->special_id >= 0;
+    if (n_active) *n_active = e->vocab_limit ? e->vocab_limit + (extra ? 1 : 0) : e->cfg.n_vocab;
+    if (special_id) *special_id = extra ? e->special_id : -1;
     return TFR_OK;
 }
 

@@ -14,6 +14,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <string>
@@ -415,6 +416,26 @@ extern "C" int tfr_load_gguf(tfr_engine* e, const tfr_gguf* g, int tp_rank, int 
     c.tp_size = tp_size < 1 ? 1 : tp_size;
     rc = tfr_set_config(e, &c);
     if (rc) return rc;
+    {
+        // load.rs:285-352: TARAFER_VOCAB_LIMIT, else 49 152 for a hybrid with more than 100 000 tokens unless
+        // TARAFER_FULL_VOCAB is set; limits below 1024 or not below n_vocab are ignored; the end-of-sequence
+        // token keeps a row of its own when it lies outside the shortlist.  Not combined with tensor parallelism.
+        long long limit = 0;
+        if (const char* v = getenv("TARAFER_VOCAB_LIMIT")) {
+            char* end = nullptr;
+            const long long n = strtoll(v, &end, 10);
+            if (end != v && *end == 0 && n > 0) limit = n;
+        }
+        if (!limit && !getenv("TARAFER_VOCAB_LIMIT") && c.hybrid && c.n_vocab > 100000 && !getenv("TARAFER_FULL_VOCAB")) limit = 49152;
+        if (limit >= 1024 && limit < c.n_vocab && c.tp_size == 1) {
+            uint64_t eos = 0;
+            const bool has_eos = tfr_gguf_meta_u64(g, "tokenizer.ggml.eos_token_id", &eos) == TFR_OK;
+            limit &= ~1ll;
+            rc = tfr_set_vocab_shortlist(e, (int)limit, has_eos && eos < (uint64_t)c.n_vocab ? (int)eos : -1);
+            if (rc) return rc;
+            fprintf(stderr, "approximation | active_vocab=%lld/%d (low-id shortlist)\n", limit, c.n_vocab);
+        }
+    }
     for (size_t i = 0; i < g->tensors.size(); i++) {
         const Tensor& t = g->tensors[i];
         if (!wanted(t.name)) continue;

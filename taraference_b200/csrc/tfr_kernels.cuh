@@ -124,6 +124,7 @@ struct EpiLogits {
     TpComm c;
     unsigned long long* defer_best;  // non-null: publish the local winner here and leave the state alone
                                      // (a library all-reduce and k_state_advance finish the step)
+    int special_row, special_id;     // shortlisted head: local row special_row stands for vocabulary id special_id (-1: none)
     unsigned long long best;
     __device__ void begin(const TokenState*) { best = 0ull; }
     __device__ __forceinline__ void one(int row, float v) {
@@ -172,7 +173,9 @@ struct EpiLogits {
                 }
                 st->ar_epoch += (unsigned)c.ops_per_token;
             }
-            advance_state(st, argmax_key_index(b), out_tokens, prompt);
+            int tok = argmax_key_index(b);
+            if (special_id >= 0 && tok == special_row) tok = special_id;  // forward.rs:107-118 (map_output_id)
+            advance_state(st, tok, out_tokens, prompt);
             st->best = 0ull;
             st->head_done = 0u;
         }
@@ -376,6 +379,7 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
     prof_mark(1, pa.prof_id);
     // Everything below reads what earlier kernels wrote (the vector, the decode state).
     griddep_wait();
+    prof_mark(3, pa.prof_id);
     // Only now may the next kernel start its prologue: its bulk weight requests then queue behind this
     // kernel's own latency-critical loads instead of in front of them, and never run two kernels ahead.
     griddep_launch_dependents();
@@ -462,7 +466,6 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
     prof_mark(7, pa.prof_id);
     epi.begin(st);
     __syncthreads();
-    prof_mark(3, pa.prof_id);
 
     // rows on the fp32 activation route: one task per (row, block, run of 16), all threads
     if (fseg.m.data) {
@@ -681,6 +684,25 @@ __global__ void k_repack_tiled(const uint8_t* __restrict__ src, uint8_t* __restr
         } else {
             for (int k = 0; k < 16; k++) tile[pc * 512 + lane * 16 + k] = sb[pc * 16 + k];
         }
+    }
+}
+
+// One row of a tiled matrix as a one-row tiled matrix (a single tile, lanes 0 .. nb-1): the extra
+// vocabulary row of a shortlisted head (load.rs:308-342).  One thread per (block, piece).
+__global__ void k_extract_row(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int type, int row, int nb) {
+    const int pieces = type == TFR_Q4_K ? Q4_PIECES : type == TFR_Q8_0 ? Q8_PIECES : Q6_PIECES + 1;
+    const int TB = tile_bytes(type);
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nb * pieces) return;
+    const int b = i / pieces, pc = i - b * pieces;
+    const long long f = (long long)row * nb + b;
+    const uint8_t* st = src + (f >> 5) * TB;
+    const int sl = (int)(f & 31);
+    if (type == TFR_Q6_K && pc == Q6_PIECES) {
+        dst[Q6_PIECES * 512 + b * 2] = st[Q6_PIECES * 512 + sl * 2];
+        dst[Q6_PIECES * 512 + b * 2 + 1] = st[Q6_PIECES * 512 + sl * 2 + 1];
+    } else {
+        for (int k = 0; k < 16; k++) dst[pc * 512 + b * 16 + k] = st[pc * 512 + sl * 16 + k];
     }
 }
 

@@ -194,11 +194,14 @@ class CudaModel:
         self._check(_lib.lib().tfr_finalize_load(self._h))
 
     @classmethod
-    def load_with(cls, cfg: dict, tensors: dict, device: int = 0, context_length: int = 4096) -> "CudaModel":
+    def load_with(cls, cfg: dict, tensors: dict, device: int = 0, context_length: int = 4096,
+                  vocab_shortlist: tuple[int, int] | None = None) -> "CudaModel":
         """CudaModel::load_with for tensors already in memory: name -> (type, K, N, bytes) for
-        matrices, name -> fp32 array for vectors."""
+        matrices, name -> fp32 array for vectors.  vocab_shortlist = (limit, extra id or -1)."""
         m = cls(device)
         m.set_config(cfg, context_length)
+        if vocab_shortlist:
+            m.set_vocab_shortlist(*vocab_shortlist)
         for name, t in tensors.items():
             if isinstance(t, tuple):
                 wt, K, N, data = t
@@ -263,10 +266,22 @@ class CudaModel:
 
     def current_logits(self) -> np.ndarray:
         """Logits of the last decoded position.  A tensor-parallel rank gets its own vocabulary
-        rows and zeros elsewhere (taraference_b200.tp.gather_logits merges the ranks)."""
+        rows and zeros elsewhere (taraference_b200.tp.gather_logits merges the ranks).  With a
+        vocabulary shortlist only the active entries come back (see active_vocab)."""
+        n_active, _ = self.active_vocab()
         out = np.zeros(self.cfg["n_vocab"], np.float32)
         self._check(_lib.lib().tfr_current_logits(self._h, out.ctypes.data, out.size))
-        return out
+        return out[:n_active] if n_active < out.size else out
+
+    def set_vocab_shortlist(self, limit: int, special_id: int = -1) -> None:
+        """load.rs:285-352: head over ids [0, limit) plus one extra row (special_id outside the shortlist)."""
+        self._check(_lib.lib().tfr_set_vocab_shortlist(self._h, int(limit), int(special_id)))
+
+    def active_vocab(self) -> tuple[int, int]:
+        """(number of logits the head produces, id behind the last one or -1)."""
+        n, sid = C.c_int(0), C.c_int(-1)
+        self._check(_lib.lib().tfr_active_vocab(self._h, C.byref(n), C.byref(sid)))
+        return n.value, sid.value
 
     # -- tensor parallelism (one engine per GPU; see include/tarafer_b200.h) ---------------------------
     def tp_vocab_range(self) -> tuple[int, int]:

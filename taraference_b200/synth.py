@@ -263,6 +263,8 @@ def write_gguf(path, cfg: dict, tensors: dict, version_alignment: int | None = N
     w.add_name("synthetic " + arch)
     w.add_uint32(f"{arch}.embedding_length", cfg["n_embd"])
     w.add_uint32(f"{arch}.block_count", cfg["n_layer"])
+    if "eos_token_id" in cfg:
+        w.add_uint32("tokenizer.ggml.eos_token_id", cfg["eos_token_id"])
     w.add_uint32(f"{arch}.attention.head_count", cfg["n_head"])
     w.add_uint32(f"{arch}.attention.head_count_kv", cfg["n_kv"])
     w.add_uint32(f"{arch}.attention.key_length", cfg["head_dim"])

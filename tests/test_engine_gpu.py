@@ -316,3 +316,56 @@ def test_full_size_32b_shapes_teacher_forced(E):
     assert he.max() < TF_WORST and np.median(he) < TF_TYPICAL, he
     kv.free()
     m.destroy()
+
+
+def test_vocab_shortlist_head_and_extra_row(E, oracle):
+    """The reference's shortlisted head (load.rs:285-352): logits of ids [0, limit) and of one extra row are
+    the full head's values at those ids, the argmax runs over that subset only and the extra row's index is
+    mapped back to its id (forward.rs:107-118)."""
+    cfg = dict(S.TINY_DENSE, n_vocab=2304)
+    tens = S.make_dense_model(cfg, seed=11)
+    full = E.CudaModel.load_with(cfg, tens)
+    kvf = full.alloc_kv(32)
+    prompt = [7, 1900, 42, 1033]
+    full.forward_greedy(prompt, kvf)
+    ref_logits = full.current_logits()
+    assert ref_logits.shape == (2304,)
+    limit = 1024
+    outside = limit + int(np.argmax(ref_logits[limit:]))         # best id outside the shortlist
+    boost = np.array(ref_logits)
+    for special, expect_special in ((outside, ref_logits[outside] > ref_logits[:limit].max()), (limit + 5, False), (-1, False), (3, False)):
+        m = E.CudaModel.load_with(cfg, tens, vocab_shortlist=(limit, special))
+        n_active, sid = m.active_vocab()
+        has_extra = special >= limit
+        assert (n_active, sid) == (limit + (1 if has_extra else 0), special if has_extra else -1)
+        kv = m.alloc_kv(32)
+        tok = m.forward_greedy(prompt, kv)
+        lg = m.current_logits()
+        assert lg.shape == (n_active,)
+        assert np.array_equal(lg[:limit], ref_logits[:limit])
+        if has_extra:
+            assert lg[limit] == ref_logits[special]
+        want = int(np.argmax(lg))
+        want = special if (has_extra and want == limit) else want
+        assert tok == want
+        if special == outside:
+            assert (tok == special) == bool(expect_special)
+        # the burst loop feeds mapped ids back: compare with token-by-token calls
+        burst = m.decode_burst(tok, 6, kv)
+        kv2 = m.alloc_kv(32)
+        t2 = m.forward_greedy(prompt, kv2)
+        seq = []
+        for _ in range(6):
+            t2 = m.forward_greedy([t2], kv2)
+            seq.append(t2)
+        assert list(burst) == seq
+        assert all(t < limit or t == special for t in burst)
+        kv.free(); kv2.free(); m.destroy()
+    # argument checks
+    m = E.CudaModel()
+    m.set_config(cfg)
+    for bad in ((512, -1), (2304, -1), (1025, -1)):
+        with pytest.raises(E.TfrError):
+            m.set_vocab_shortlist(*bad)
+    m.destroy()
+    kvf.free(); full.destroy()

@@ -35,3 +35,31 @@ def test_load_gguf_errors_name_the_tensor(cuda_lib, tmp_path):
     S.write_gguf(path, cfg, tens)
     with pytest.raises(E.TfrError, match="blk.1.ffn_down.weight"):
         E.CudaModel.load_gguf(path)
+
+
+def test_load_gguf_applies_the_vocabulary_shortlist_rule(cuda_lib, tmp_path, monkeypatch):
+    """load.rs:285-352: TARAFER_VOCAB_LIMIT shortens the head; the end-of-sequence id outside it keeps a row."""
+    from taraference_b200 import engine as E
+    cfg = dict(S.TINY_DENSE, n_vocab=2304, eos_token_id=2000)
+    tens = S.make_model(cfg, seed=8)
+    path = tmp_path / "model.gguf"
+    S.write_gguf(path, cfg, tens)
+    monkeypatch.delenv("TARAFER_VOCAB_LIMIT", raising=False)
+    m = E.CudaModel.load_gguf(path)
+    assert m.active_vocab() == (2304, -1)            # dense model, no variable: whole vocabulary
+    kv = m.alloc_kv(16)
+    m.forward_greedy([1, 2, 3], kv)
+    full = m.current_logits()
+    kv.free(); m.destroy()
+    monkeypatch.setenv("TARAFER_VOCAB_LIMIT", "1024")
+    m = E.CudaModel.load_gguf(path)
+    assert m.active_vocab() == (1025, 2000)
+    kv = m.alloc_kv(16)
+    m.forward_greedy([1, 2, 3], kv)
+    lg = m.current_logits()
+    assert np.array_equal(lg[:1024], full[:1024]) and lg[1024] == full[2000]
+    kv.free(); m.destroy()
+    monkeypatch.setenv("TARAFER_VOCAB_LIMIT", "512")   # below 1024: ignored, as in the reference
+    m = E.CudaModel.load_gguf(path)
+    assert m.active_vocab() == (2304, -1)
+    m.destroy()
