@@ -193,7 +193,7 @@ float tfr_last_device_ms(const tfr_engine* e);
  * request switches that tap on for later steps and returns zeros). */
 int tfr_debug_read(tfr_engine* e, tfr_kv* kv, const char* what, int layer, void* out, size_t nbytes);
 
-/* Test aid: when device_buffer != NULL, thread 0 of every CTA of the matrix-vector kernel stores the
+/* Test aid: when device_buffer != NULL, thread 0 of every CTA of the matrix-vector and attention kernels stores the
  * GPU nanosecond timer at up to eight points into device_buffer[(launch * 160 + cta) * 8 + point], launch =
  * index of the kernel within the decode step (0 for the stand-alone operators). */
 int tfr_debug_set_timeline(unsigned long long* device_buffer);

@@ -26,13 +26,11 @@ constexpr int ATTN_CLUSTER = 8;   // CTAs per cluster (the portable maximum); At
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Reads a float at the same shared-memory offset in CTA `rank` of this cluster.
-__device__ __forceinline__ float ld_dsmem_f32(const float* local, unsigned rank) {
+// Writes a float to the same shared-memory offset in CTA `rank` of this cluster.
+__device__ __forceinline__ void st_dsmem_f32(float* local, unsigned rank, float v) {
     unsigned remote;
-    float v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 
 struct AttnArgs {
@@ -67,32 +65,78 @@ __device__ __forceinline__ float warp_transpose_reduce32(float (&v)[32], int lan
 template <int HD>
 __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const TokenState* st) {
     prof_mark(0, a.prof_id);
-    griddep_wait();  // q and the new K/V row come from the previous kernel
-    griddep_launch_dependents();
-    prof_mark(1, a.prof_id);
-    if (st && st->done) return;
     constexpr int DL = HD / 32;   // dims per lane in the score phase
     constexpr int DPT = HD / 64;  // dims per thread in the value phase
+    constexpr int VK = ATTN_TILE / 4;  // keys per thread and tile in the value phase
+    using KRaw = typename std::conditional<DL == 8, uint4, typename std::conditional<DL == 4, uint2, unsigned int>::type>::type;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = blockIdx.y, s = blockIdx.x;  // grid (S, n_kv), clusters of ATTN_CLUSTER along x
     const int rep = a.n_head / a.n_kv;
     const int kvdim = a.n_kv * HD;
+    const int kg = tid >> 6, dp = tid & 63;
+    // The decode state was last written by the previous token's final kernel, and every kernel of the chain
+    // completes only after its predecessor: position and stop flag are final here, before the wait.
+    const int done = st ? st->done : 0;
     const int T = (st ? st->pos : a.pos) + 1;
     int S_eff = (T + a.min_keys - 1) / a.min_keys;
     S_eff = S_eff < 1 ? 1 : (S_eff > a.S ? a.S : S_eff);
     // up to ATTN_CLUSTER splits: the first cluster of the KV head merges on chip; its idle members
     // still attend the cluster barriers.  More splits: every CTA for itself, merge through memory.
     const bool on_chip = S_eff > 1 && S_eff <= ATTN_CLUSTER;
-    if (on_chip ? s >= ATTN_CLUSTER : s >= S_eff) return;
+    const bool leave = done || (on_chip ? s >= ATTN_CLUSTER : s >= S_eff);
     const bool active = s < S_eff;
     const int chunk = (T + S_eff - 1) / S_eff;
     const int t0 = min(T, s * chunk);
-    const int t1 = active ? min(T, t0 + chunk) : t0;
+    const int t1 = (active && !leave) ? min(T, t0 + chunk) : t0;
 
-    __shared__ float sc[ATTN_REP_MAX][ATTN_TILE];
+    // K and V rows of one tile in registers: the value rows are used after the softmax, the key rows of both
+    // score batches (batch bt of warp w covers keys 32*bt + 4*w ..) are requested before the first is used.
+    // fresh = false: every row of the tile below `limit`; fresh = true: only row T-1, which the previous
+    // kernel has just written (the others keep what an earlier call loaded).
+    uint2 vraw[VK];
+    KRaw kraw[2][4];
+    auto load_tile = [&](int tt, int limit, bool fresh) {
+#pragma unroll
+        for (int i = 0; i < VK; i++) {
+            const int t = tt + kg + 4 * i;
+            if (!fresh) vraw[i] = make_uint2(0u, 0u);
+            if (fresh ? (t == T - 1 && t < t1) : t < limit) {
+                const unsigned short* vr = a.vc + (size_t)t * kvdim + g * HD + dp * DPT;
+                if constexpr (DPT == 4) vraw[i] = *reinterpret_cast<const uint2*>(vr);
+                else if constexpr (DPT == 2) vraw[i].x = *reinterpret_cast<const unsigned int*>(vr);
+                else vraw[i].x = *vr;
+            }
+        }
+#pragma unroll
+        for (int bt = 0; bt < 2; bt++) {
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++) {
+                const int t = tt + (bt * 8 + warp) * 4 + kk;
+                if (!fresh) kraw[bt][kk] = KRaw{};
+                if (fresh ? (t == T - 1 && t < t1) : t < limit) {
+                    const unsigned short* kr = a.kc + (size_t)t * kvdim + g * HD + lane * DL;
+                    if constexpr (DL == 1) kraw[bt][kk] = *kr;
+                    else kraw[bt][kk] = *reinterpret_cast<const KRaw*>(kr);
+                }
+            }
+        }
+    };
+    // Rows of earlier positions do not depend on the previous kernel: the first tile's are requested before
+    // the grid-dependency wait, so their latency hides behind the kernel boundary.
+    load_tile(t0, min(t1, T - 1), false);
+    griddep_wait();  // q and the new K/V row come from the previous kernel
+    griddep_launch_dependents();
+    prof_mark(1, a.prof_id);
+    if (leave) return;
+    load_tile(t0, 0, true);
+
+    __shared__ __align__(16) float sc[ATTN_TILE][ATTN_REP_MAX];  // [key][head]: the value phase reads a key's eight weights as two float4
     __shared__ float m_s[ATTN_REP_MAX], l_s[ATTN_REP_MAX], alpha_s[ATTN_REP_MAX];
     __shared__ float ored[4][ATTN_REP_MAX][HD];
     __shared__ int is_last_s;
+    // on-chip merge: slice s of every member's O, and every member's (m, l), land here
+    __shared__ float gath[ATTN_CLUSTER][HD];
+    __shared__ float gm[ATTN_CLUSTER][ATTN_REP_MAX], gl[ATTN_CLUSTER][ATTN_REP_MAX];
 
     // q fragment of every head of the group: dims lane*DL .. lane*DL+DL-1
     float qr[ATTN_REP_MAX][DL];
@@ -112,47 +156,14 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
     __syncthreads();
     prof_mark(4, a.prof_id);
 
-    const int kg = tid >> 6, dp = tid & 63;
-    constexpr int VK = ATTN_TILE / 4;  // keys per thread and tile in the value phase
     for (int tt = t0; tt < t1; tt += ATTN_TILE) {
-        // the tile's V rows do not depend on the scores: request them now, use them after the softmax
         const int tn = min(ATTN_TILE, t1 - tt);
-        uint2 vraw[VK];
-#pragma unroll
-        for (int i = 0; i < VK; i++) {
-            const int k = kg + 4 * i;
-            vraw[i] = make_uint2(0u, 0u);
-            if (k < tn) {
-                const unsigned short* vr = a.vc + (size_t)(tt + k) * kvdim + g * HD + dp * DPT;
-                if constexpr (DPT == 4) vraw[i] = *reinterpret_cast<const uint2*>(vr);
-                else if constexpr (DPT == 2) vraw[i].x = *reinterpret_cast<const unsigned int*>(vr);
-                else vraw[i].x = *vr;
-            }
-        }
-        // ---- scores: batches of four keys; batch bt of warp w covers keys 32*bt + 4*w .., so a short
-        // tile spreads over all warps and its empty second batch is skipped.  The K rows of both batches
-        // are requested before the first is used: one memory round trip instead of two.
-        using KRaw = typename std::conditional<DL == 8, uint4, typename std::conditional<DL == 4, uint2, unsigned int>::type>::type;
-        KRaw kraw[2][4];
-#pragma unroll
-        for (int bt = 0; bt < 2; bt++) {
-            const int kbase = (bt * 8 + warp) * 4;
-#pragma unroll
-            for (int kk = 0; kk < 4; kk++) {
-                const int t = tt + kbase + kk;
-                kraw[bt][kk] = KRaw{};
-                if (kbase < tn && t < t1) {
-                    const unsigned short* kr = a.kc + (size_t)t * kvdim + g * HD + lane * DL;
-                    if constexpr (DL == 1) kraw[bt][kk] = *kr;
-                    else kraw[bt][kk] = *reinterpret_cast<const KRaw*>(kr);
-                }
-            }
-        }
+        // ---- scores
 #pragma unroll
         for (int bt = 0; bt < 2; bt++) {
             const int kbase = (bt * 8 + warp) * 4;
             if (kbase >= tn) {
-                if (kbase + (lane >> 3) < ATTN_TILE && (lane & 7) < ATTN_REP_MAX) sc[lane & 7][kbase + (lane >> 3)] = -1e30f;
+                if (kbase + (lane >> 3) < ATTN_TILE && (lane & 7) < ATTN_REP_MAX) sc[kbase + (lane >> 3)][lane & 7] = -1e30f;
                 continue;
             }
             float v[32];
@@ -190,21 +201,21 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
             const float tot = warp_transpose_reduce32(v, lane);
             const int kk = lane >> 3, h = lane & 7;
             const int t = tt + kbase + kk;
-            sc[h][kbase + kk] = (t < t1 && h < rep) ? tot * a.scale : -1e30f;
+            sc[kbase + kk][h] = (t < t1 && h < rep) ? tot * a.scale : -1e30f;
         }
         __syncthreads();
         prof_mark(6, a.prof_id);
         // ---- online softmax bookkeeping: warp h owns head h
         if (warp < rep) {
-            const float s0 = sc[warp][lane], s1 = sc[warp][lane + 32];
+            const float s0 = sc[lane][warp], s1 = sc[lane + 32][warp];
             const float tile_m = warp_max(fmaxf(s0, s1));
             const float m_old = m_s[warp];
             const float m_new = fmaxf(m_old, tile_m);
             const float p0 = (tt + lane < t1) ? expf(s0 - m_new) : 0.f;
             const float p1 = (tt + lane + 32 < t1) ? expf(s1 - m_new) : 0.f;
             const float tile_l = warp_sum(p0 + p1);
-            sc[warp][lane] = p0;
-            sc[warp][lane + 32] = p1;
+            sc[lane][warp] = p0;
+            sc[lane + 32][warp] = p1;
             if (lane == 0) {
                 const float alpha = expf(m_old - m_new);
                 alpha_s[warp] = alpha;
@@ -221,28 +232,39 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
 #pragma unroll
             for (int d = 0; d < DPT; d++) o[h][d] *= al;
         }
+        // Keys past the end of the tile carry weight 0 and value 0, so groups of four keys run without
+        // per-key branches; a group that lies wholly past the end is skipped (uniform over the CTA).
 #pragma unroll
-        for (int i = 0; i < VK; i++) {
-            const int k = kg + 4 * i;
-            if (4 * i >= tn) break;  // uniform: nothing left in this tile for any key group
-            if (k < tn) {
+        for (int i0 = 0; i0 < VK; i0 += 4) {
+            if (4 * i0 >= tn) break;
+            float4 pa[4], pb[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int k = kg + 4 * (i0 + j);
+                pa[j] = *reinterpret_cast<const float4*>(&sc[k][0]);
+                pb[j] = *reinterpret_cast<const float4*>(&sc[k][4]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
                 float vf[DPT];
-                vf[0] = f16_to_f32((unsigned short)(vraw[i].x & 0xffff));
-                if constexpr (DPT >= 2) vf[1] = f16_to_f32((unsigned short)(vraw[i].x >> 16));
+                vf[0] = f16_to_f32((unsigned short)(vraw[i0 + j].x & 0xffff));
+                if constexpr (DPT >= 2) vf[1] = f16_to_f32((unsigned short)(vraw[i0 + j].x >> 16));
                 if constexpr (DPT == 4) {
-                    vf[2] = f16_to_f32((unsigned short)(vraw[i].y & 0xffff));
-                    vf[3] = f16_to_f32((unsigned short)(vraw[i].y >> 16));
+                    vf[2] = f16_to_f32((unsigned short)(vraw[i0 + j].y & 0xffff));
+                    vf[3] = f16_to_f32((unsigned short)(vraw[i0 + j].y >> 16));
                 }
+                const float p[ATTN_REP_MAX] = {pa[j].x, pa[j].y, pa[j].z, pa[j].w, pb[j].x, pb[j].y, pb[j].z, pb[j].w};
 #pragma unroll
                 for (int h = 0; h < ATTN_REP_MAX; h++) {
                     if (h < rep) {
-                        const float p = sc[h][k];
 #pragma unroll
-                        for (int d = 0; d < DPT; d++) o[h][d] += p * vf[d];
+                        for (int d = 0; d < DPT; d++) o[h][d] += p[h] * vf[d];
                     }
                 }
             }
         }
+        // the next tile's rows are requested now and used in the next iteration
+        if (tt + ATTN_TILE < t1) load_tile(tt + ATTN_TILE, t1, false);
         __syncthreads();
     }
 
@@ -255,44 +277,40 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
     __syncthreads();
     const int po = 2 + HD;
     if (on_chip) {
-        // ored[0] <- this split's O (sum of its four key groups); idle members contribute l = 0
-        for (int idx = tid; idx < rep * HD; idx += ATTN_THREADS) {
+        // Every member sends slice j of its O (the sum of its four key groups) and its (m, l) into member
+        // j's shared memory: remote stores stream out without waiting, where remote loads (the obvious
+        // formulation) cost a round trip each.  After one cluster barrier every member merges its own slice
+        // from local memory; nothing remote is touched afterwards, so members leave independently.  Idle
+        // members (s >= S_eff) send zeros that the merge skips, and still finish their slice.
+        const int total = rep * HD, per = total / ATTN_CLUSTER;  // per <= HD
+        for (int idx = tid; idx < total; idx += ATTN_THREADS) {
             const int h = idx / HD, d = idx % HD;
-            ored[0][h][d] = ored[0][h][d] + ored[1][h][d] + ored[2][h][d] + ored[3][h][d];
+            const float v = ored[0][h][d] + ored[1][h][d] + ored[2][h][d] + ored[3][h][d];
+            st_dsmem_f32(&gath[s][idx % per], (unsigned)(idx / per), v);
+        }
+        if (tid < ATTN_CLUSTER * ATTN_REP_MAX) {
+            const int r = tid / ATTN_REP_MAX, h = tid % ATTN_REP_MAX;
+            st_dsmem_f32(&gm[s][h], (unsigned)r, m_s[h]);
+            st_dsmem_f32(&gl[s][h], (unsigned)r, l_s[h]);
         }
         cluster_sync_all();
         prof_mark(3, a.prof_id);
-        // member s finishes the dims idx with idx % ATTN_CLUSTER == s.  All members' values are requested
-        // before any is used (remote shared-memory loads cost a few hundred nanoseconds each when they
-        // wait for one another); idle members hold m = -1e30, l = 0, O = 0 and drop out of the sums.
-        for (int idx = s + ATTN_CLUSTER * tid; idx < rep * HD; idx += ATTN_CLUSTER * ATTN_THREADS) {
+        for (int i = tid; i < per; i += ATTN_THREADS) {
+            const int idx = s * per + i;
             const int h = idx / HD, d = idx % HD;
             const int hg = g * rep + h;
-            float mr[ATTN_CLUSTER], lr[ATTN_CLUSTER], orr[ATTN_CLUSTER];
-#pragma unroll
-            for (int r = 0; r < ATTN_CLUSTER; r++) {
-                mr[r] = ld_dsmem_f32(&m_s[h], r);
-                lr[r] = ld_dsmem_f32(&l_s[h], r);
-                orr[r] = ld_dsmem_f32(&ored[0][h][d], r);
-            }
             float m = -1e30f;
-#pragma unroll
-            for (int r = 0; r < ATTN_CLUSTER; r++)
-                if (r < S_eff) m = fmaxf(m, mr[r]);
+            for (int r = 0; r < S_eff; r++) m = fmaxf(m, gm[r][h]);
             float l = 0.f, acc = 0.f;
-#pragma unroll
-            for (int r = 0; r < ATTN_CLUSTER; r++) {
-                if (r < S_eff) {
-                    const float al = expf(mr[r] - m);
-                    l += al * lr[r];
-                    acc += al * orr[r];
-                }
+            for (int r = 0; r < S_eff; r++) {
+                const float al = expf(gm[r][h] - m);
+                l += al * gl[r][h];
+                acc += al * gath[r][i];
             }
             float res = acc / fmaxf(l, 1e-20f);
             if (a.gate) res *= 1.f / (1.f + expf(-a.gate[hg * HD + d]));
             a.out[hg * HD + d] = res;
         }
-        cluster_sync_all();  // nobody leaves while its shared memory may still be read
         prof_mark(5, a.prof_id);
         return;
     }
