@@ -18,9 +18,19 @@ struct EpiStore {
     const float* bias;
     int use_res;
     int n_rows;
+    const float* res_smem = nullptr;  // the CTA's residual values, fetched right after the dependency wait
+    int res_row0 = 0;
     __device__ void begin(const TokenState*) {}
+    // The in-place residual is read long before the epilogue needs it: by then the successor's weight
+    // requests already fill the memory system and a plain load would queue behind them.
+    __device__ __forceinline__ bool wants_residual() const { return use_res == 2; }
+    __device__ __forceinline__ float residual(int row) const { return row < n_rows ? out[row] : 0.f; }
+    __device__ __forceinline__ void set_residual(const float* buf, int row0) {
+        res_smem = buf;
+        res_row0 = row0;
+    }
     __device__ __forceinline__ void one(int row, float acc) {
-        if (use_res == 2) acc += out[row];
+        if (use_res == 2) acc += res_smem ? res_smem[row - res_row0] : out[row];
         if (bias) acc += bias[row];
         out[row] = acc;
     }
@@ -35,6 +45,9 @@ struct EpiStore {
 struct EpiSilu {
     static constexpr int MODE = EPI_ZIP;
     float* out;
+    __device__ __forceinline__ bool wants_residual() const { return false; }
+    __device__ __forceinline__ float residual(int) const { return 0.f; }
+    __device__ __forceinline__ void set_residual(const float*, int) {}
     __device__ void begin(const TokenState*) {}
     __device__ __forceinline__ void apply(int p, float gate, float up) {
         out[p] = (gate / (1.f + __expf(-gate))) * up;
@@ -57,6 +70,9 @@ struct EpiQkv {
     __device__ void begin(const TokenState* st) {
         if (st) pos = st->pos;
     }
+    __device__ __forceinline__ bool wants_residual() const { return false; }
+    __device__ __forceinline__ float residual(int) const { return 0.f; }
+    __device__ __forceinline__ void set_residual(const float*, int) {}
     __device__ __forceinline__ void apply(int p, float x0, float x1) {
         const int v = 2 * p;
         if (bias) {
@@ -127,6 +143,9 @@ struct EpiLogits {
     int special_row, special_id;     // shortlisted head: local row special_row stands for vocabulary id special_id (-1: none)
     unsigned long long best;
     __device__ void begin(const TokenState*) { best = 0ull; }
+    __device__ __forceinline__ bool wants_residual() const { return false; }
+    __device__ __forceinline__ float residual(int) const { return 0.f; }
+    __device__ __forceinline__ void set_residual(const float*, int) {}
     __device__ __forceinline__ void one(int row, float v) {
         logits[row] = v;
         const unsigned long long k = argmax_key(v, row + row_offset);
@@ -331,7 +350,10 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
         bulk_load(ring + (size_t)s * TB, job_src(j), TB, full + s);
     };
 
-    // Weights do not depend on the previous kernel: every warp requests its first tiles at once.
+    // Weights do not depend on the previous kernel: every warp requests its first tiles at once.  (Requesting
+    // the tiles of a large CTA only after its vector has arrived was measured: the vector then lands within
+    // 0.5 us instead of 2-3, but a bulk request costs its issuing thread a third of a microsecond, and paying
+    // that after the wait instead of before it loses more than the faster vector gains.)
     if (lane == 0 && warp < stride) {
         for (int j = warp; j < n_jobs; j += stride) {
             mbar_init(full + (reuse ? warp : j), 1);
@@ -384,6 +406,11 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
     // kernel's own latency-critical loads instead of in front of them, and never run two kernels ahead.
     griddep_launch_dependents();
     const int done = st ? st->done : 0;
+    // residual values of this CTA's rows (pair-ordered epilogues only), one per thread
+    const int res_row0 = 2 * (ja.id_base + (rows_a0 >> 1));
+    const bool res_pre = Epi::MODE == EPI_PAIRS && epi.wants_residual() && rows_a <= 256 && rows_b == 0 && !fseg.m.data;
+    float resv = 0.f;
+    if (res_pre && tid < rows_a) resv = epi.residual(res_row0 + tid);
     constexpr int STAGE_REGS = 6;  // float4 per thread and pass: one pass up to K = 12288
     const int n4 = K >> 2;
     float scale = 1.f;
@@ -465,6 +492,10 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
         for (int k = 1; k <= GEMV_L2_AHEAD && warp + k * stride < n_jobs; k++) bulk_prefetch_l2(job_src(warp + k * stride), TB);
     prof_mark(7, pa.prof_id);
     epi.begin(st);
+    if (res_pre) {
+        if (tid < rows_a) red[tid] = resv;  // red is free once the norm's reduction is over
+        epi.set_residual(red, res_row0);
+    }
     __syncthreads();
 
     // rows on the fp32 activation route: one task per (row, block, run of 16), all threads

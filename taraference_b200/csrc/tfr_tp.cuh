@@ -88,6 +88,9 @@ struct EpiAllReduce {
     int op_index;      // which all-reduce of the token this is
     unsigned epoch;
     __device__ void begin(const TokenState* st) { epoch = st->ar_epoch + (unsigned)op_index + 1u; }
+    __device__ __forceinline__ bool wants_residual() const { return false; }
+    __device__ __forceinline__ float residual(int) const { return 0.f; }
+    __device__ __forceinline__ void set_residual(const float*, int) {}
     __device__ __forceinline__ uint4* slot(int dst_rank, int src_rank) const {
         return reinterpret_cast<uint4*>(c.base[dst_rank] + c.lay.data_off) +
                ((size_t)(epoch & 1u) * TP_MAX + src_rank) * (c.lay.k_max >> 1);
