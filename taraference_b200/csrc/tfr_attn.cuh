@@ -5,10 +5,11 @@
 // re-reads the K/V rows of its KV head.  Here one CTA serves ALL query heads that share a
 // KV head (GQA group), so each K/V row is read from HBM once per token; the number of
 // splits is sized to the SM count and shrinks for short contexts.  The splits of a KV head are
-// launched as thread-block clusters of eight: up to eight splits merge their (m, l, O) partials
-// through distributed shared memory behind one cluster barrier, each CTA of the cluster
+// launched as thread-block clusters of eight: the eight splits of a cluster merge their (m, l, O)
+// partials through distributed shared memory behind one cluster barrier, each CTA of the cluster
 // finishing an eighth of the output dims (no global round trip, no second launch).  Longer
-// contexts use more splits; there the CTA that finishes last for a KV head merges the partials
+// contexts use several clusters per KV head; their merged partials meet in global memory, where for
+// every eighth of the dims the CTA that arrives last merges the clusters' partials
 // from global memory.  Arithmetic is fp32 on f16 data as in the reference; exp is the build's
 // ex2-based expf.
 #pragma once
@@ -37,8 +38,8 @@ struct AttnArgs {
     const float* q;             // [n_head * hd], RoPE applied
     const unsigned short* kc;   // layer base, [max_seq][n_kv * hd] f16 bits
     const unsigned short* vc;
-    float* partial;             // [n_head][S][2 + hd] (contexts of more than 8 splits)
-    unsigned int* counters;     // [n_kv], zero between launches
+    float* partial;             // [n_head][S][2 + hd]: per-cluster partials (contexts of more than 8 splits)
+    unsigned int* counters;     // [n_kv][8] (KV head, output slice), zero between launches
     float* out;                 // [n_head * hd]
     const float* gate;          // optional [n_head * hd]: out *= sigmoid(gate) (deltanet.cu:176-186)
     int n_head, n_kv, S, min_keys;
@@ -82,8 +83,8 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
     S_eff = S_eff < 1 ? 1 : (S_eff > a.S ? a.S : S_eff);
     // up to ATTN_CLUSTER splits: the first cluster of the KV head merges on chip; its idle members
     // still attend the cluster barriers.  More splits: every CTA for itself, merge through memory.
-    const bool on_chip = S_eff > 1 && S_eff <= ATTN_CLUSTER;
-    const bool leave = done || (on_chip ? s >= ATTN_CLUSTER : s >= S_eff);
+    const int n_cl = (S_eff + ATTN_CLUSTER - 1) / ATTN_CLUSTER;  // clusters that have work
+    const bool leave = done || (S_eff == 1 ? s >= 1 : s >= n_cl * ATTN_CLUSTER);
     const bool active = s < S_eff;
     const int chunk = (T + S_eff - 1) / S_eff;
     const int t0 = min(T, s * chunk);
@@ -95,7 +96,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
     // kernel has just written (the others keep what an earlier call loaded).
     uint2 vraw[VK];
     KRaw kraw[2][4];
-    auto load_tile = [&](int tt, int limit, bool fresh) {
+    auto load_v = [&](int tt, int limit, bool fresh) {
 #pragma unroll
         for (int i = 0; i < VK; i++) {
             const int t = tt + kg + 4 * i;
@@ -107,6 +108,8 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
                 else vraw[i].x = *vr;
             }
         }
+    };
+    auto load_k = [&](int tt, int limit, bool fresh) {
 #pragma unroll
         for (int bt = 0; bt < 2; bt++) {
 #pragma unroll
@@ -123,12 +126,14 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
     };
     // Rows of earlier positions do not depend on the previous kernel: the first tile's are requested before
     // the grid-dependency wait, so their latency hides behind the kernel boundary.
-    load_tile(t0, min(t1, T - 1), false);
+    load_k(t0, min(t1, T - 1), false);
+    load_v(t0, min(t1, T - 1), false);
     griddep_wait();  // q and the new K/V row come from the previous kernel
     griddep_launch_dependents();
     prof_mark(1, a.prof_id);
     if (leave) return;
-    load_tile(t0, 0, true);
+    load_k(t0, 0, true);
+    load_v(t0, 0, true);
 
     __shared__ __align__(16) float sc[ATTN_TILE][ATTN_REP_MAX];  // [key][head]: the value phase reads a key's eight weights as two float4
     __shared__ float m_s[ATTN_REP_MAX], l_s[ATTN_REP_MAX], alpha_s[ATTN_REP_MAX];
@@ -203,6 +208,8 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
             const int t = tt + kbase + kk;
             sc[kbase + kk][h] = (t < t1 && h < rep) ? tot * a.scale : -1e30f;
         }
+        // the key registers are free: the next tile's key rows travel during the softmax and the value phase
+        if (tt + ATTN_TILE < t1) load_k(tt + ATTN_TILE, t1, false);
         __syncthreads();
         prof_mark(6, a.prof_id);
         // ---- online softmax bookkeeping: warp h owns head h
@@ -263,8 +270,8 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
                 }
             }
         }
-        // the next tile's rows are requested now and used in the next iteration
-        if (tt + ATTN_TILE < t1) load_tile(tt + ATTN_TILE, t1, false);
+        // the next tile's value rows are requested now and used after the next tile's softmax
+        if (tt + ATTN_TILE < t1) load_v(tt + ATTN_TILE, t1, false);
         __syncthreads();
     }
 
@@ -276,44 +283,6 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
         for (int d = 0; d < DPT; d++) ored[kg][h][dp * DPT + d] = o[h][d];
     __syncthreads();
     const int po = 2 + HD;
-    if (on_chip) {
-        // Every member sends slice j of its O (the sum of its four key groups) and its (m, l) into member
-        // j's shared memory: remote stores stream out without waiting, where remote loads (the obvious
-        // formulation) cost a round trip each.  After one cluster barrier every member merges its own slice
-        // from local memory; nothing remote is touched afterwards, so members leave independently.  Idle
-        // members (s >= S_eff) send zeros that the merge skips, and still finish their slice.
-        const int total = rep * HD, per = total / ATTN_CLUSTER;  // per <= HD
-        for (int idx = tid; idx < total; idx += ATTN_THREADS) {
-            const int h = idx / HD, d = idx % HD;
-            const float v = ored[0][h][d] + ored[1][h][d] + ored[2][h][d] + ored[3][h][d];
-            st_dsmem_f32(&gath[s][idx % per], (unsigned)(idx / per), v);
-        }
-        if (tid < ATTN_CLUSTER * ATTN_REP_MAX) {
-            const int r = tid / ATTN_REP_MAX, h = tid % ATTN_REP_MAX;
-            st_dsmem_f32(&gm[s][h], (unsigned)r, m_s[h]);
-            st_dsmem_f32(&gl[s][h], (unsigned)r, l_s[h]);
-        }
-        cluster_sync_all();
-        prof_mark(3, a.prof_id);
-        for (int i = tid; i < per; i += ATTN_THREADS) {
-            const int idx = s * per + i;
-            const int h = idx / HD, d = idx % HD;
-            const int hg = g * rep + h;
-            float m = -1e30f;
-            for (int r = 0; r < S_eff; r++) m = fmaxf(m, gm[r][h]);
-            float l = 0.f, acc = 0.f;
-            for (int r = 0; r < S_eff; r++) {
-                const float al = expf(gm[r][h] - m);
-                l += al * gl[r][h];
-                acc += al * gath[r][i];
-            }
-            float res = acc / fmaxf(l, 1e-20f);
-            if (a.gate) res *= 1.f / (1.f + expf(-a.gate[hg * HD + d]));
-            a.out[hg * HD + d] = res;
-        }
-        prof_mark(5, a.prof_id);
-        return;
-    }
     if (S_eff == 1) {
         // single split: normalise and store directly (the merge of one partial is the identity)
         for (int idx = tid; idx < rep * HD; idx += ATTN_THREADS) {
@@ -327,37 +296,94 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
         prof_mark(5, a.prof_id);
         return;
     }
-    for (int idx = tid; idx < rep * HD; idx += ATTN_THREADS) {
+    // ---- level 1, inside the cluster.  Every member sends slice j of its O (the sum of its four key
+    // groups) and its (m, l) into member j's shared memory: remote stores stream out without waiting,
+    // where remote loads cost a round trip each.  After one cluster barrier member j merges slice j of the
+    // cluster's eight splits from local memory; nothing remote is touched afterwards, so members leave
+    // independently.  Members past the last split send zeros that the merge skips, and still own a slice.
+    const int cl = s / ATTN_CLUSTER, rk = s % ATTN_CLUSTER;
+    const int total = rep * HD, per = total / ATTN_CLUSTER;  // per <= HD
+    for (int idx = tid; idx < total; idx += ATTN_THREADS) {
         const int h = idx / HD, d = idx % HD;
-        const float tot = ored[0][h][d] + ored[1][h][d] + ored[2][h][d] + ored[3][h][d];
-        float* base = a.partial + ((size_t)(g * rep + h) * a.S + s) * po;
-        base[2 + d] = tot;
-        if (d == 0) {
-            base[0] = m_s[h];
-            base[1] = l_s[h];
+        const float v = ored[0][h][d] + ored[1][h][d] + ored[2][h][d] + ored[3][h][d];
+        st_dsmem_f32(&gath[rk][idx % per], (unsigned)(idx / per), v);
+    }
+    if (tid < ATTN_CLUSTER * ATTN_REP_MAX) {
+        const int r = tid / ATTN_REP_MAX, h = tid % ATTN_REP_MAX;
+        st_dsmem_f32(&gm[rk][h], (unsigned)r, m_s[h]);
+        st_dsmem_f32(&gl[rk][h], (unsigned)r, l_s[h]);
+    }
+    cluster_sync_all();
+    prof_mark(3, a.prof_id);
+    const int in_cl = min(ATTN_CLUSTER, S_eff - cl * ATTN_CLUSTER);  // splits of this cluster that had keys
+    if (n_cl == 1) {
+        for (int i = tid; i < per; i += ATTN_THREADS) {
+            const int idx = rk * per + i;
+            const int h = idx / HD, d = idx % HD;
+            const int hg = g * rep + h;
+            float m = -1e30f;
+            for (int r = 0; r < in_cl; r++) m = fmaxf(m, gm[r][h]);
+            float l = 0.f, acc = 0.f;
+            for (int r = 0; r < in_cl; r++) {
+                const float al = expf(gm[r][h] - m);
+                l += al * gl[r][h];
+                acc += al * gath[r][i];
+            }
+            float res = acc / fmaxf(l, 1e-20f);
+            if (a.gate) res *= 1.f / (1.f + expf(-a.gate[hg * HD + d]));
+            a.out[hg * HD + d] = res;
+        }
+        prof_mark(5, a.prof_id);
+        return;
+    }
+    // ---- level 2, across clusters (long contexts).  Member j of every cluster writes its cluster's merged
+    // slice j — (m, l) of the heads it touches and the unnormalised O — to global memory; the member j that
+    // arrives last (one counter per KV head and slice) merges the n_cl cluster partials of that slice.  The
+    // eight slices of a KV head finish independently on eight SMs.
+    {
+        float* pbase = a.partial;
+        for (int i = tid; i < per; i += ATTN_THREADS) {
+            const int idx = rk * per + i;
+            const int h = idx / HD, d = idx % HD;
+            float m = -1e30f;
+            for (int r = 0; r < in_cl; r++) m = fmaxf(m, gm[r][h]);
+            float l = 0.f, acc = 0.f;
+            for (int r = 0; r < in_cl; r++) {
+                const float al = expf(gm[r][h] - m);
+                l += al * gl[r][h];
+                acc += al * gath[r][i];
+            }
+            float* base = pbase + ((size_t)(g * rep + h) * a.S + cl) * po;
+            base[2 + d] = acc;
+            if (d == 0 || i == 0) {  // the first element of every head inside the slice
+                base[0] = m;
+                base[1] = l;
+            }
         }
     }
-    // ---- last CTA of this KV head merges (flash.cu:222-255)
     __threadfence();
     __syncthreads();
     if (tid == 0) {
-        const unsigned int old = atomicAdd(&a.counters[g], 1u);
-        is_last_s = (old == (unsigned int)(S_eff - 1));
-        if (is_last_s) a.counters[g] = 0u;
+        unsigned int* ctr = a.counters + g * ATTN_CLUSTER + rk;
+        const unsigned int old = atomicAdd(ctr, 1u);
+        is_last_s = (old == (unsigned int)(n_cl - 1));
+        if (is_last_s) *ctr = 0u;
     }
     __syncthreads();
-    prof_mark(3, a.prof_id);
     if (!is_last_s) return;
     __threadfence();
-    for (int idx = tid; idx < rep * HD; idx += ATTN_THREADS) {
+    for (int i = tid; i < per; i += ATTN_THREADS) {
+        const int idx = rk * per + i;
         const int h = idx / HD, d = idx % HD;
         const int hg = g * rep + h;
         const float* hb = a.partial + (size_t)hg * a.S * po;
         float m = -1e30f;
-        for (int ss = 0; ss < S_eff; ss++) m = fmaxf(m, __ldcg(hb + (size_t)ss * po));
+#pragma unroll 4
+        for (int c = 0; c < n_cl; c++) m = fmaxf(m, __ldcg(hb + (size_t)c * po));
         float l = 0.f, acc = 0.f;
-        for (int ss = 0; ss < S_eff; ss++) {
-            const float* b = hb + (size_t)ss * po;
+#pragma unroll 4
+        for (int c = 0; c < n_cl; c++) {
+            const float* b = hb + (size_t)c * po;
             const float al = expf(__ldcg(b) - m);
             l += al * __ldcg(b + 1);
             acc += al * __ldcg(b + 2 + d);

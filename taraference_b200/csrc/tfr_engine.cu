@@ -241,9 +241,40 @@ static void configure_kernels_once() {
     configure_kernel(k_state_next_prompt, false);
 }
 
-// Splits per KV head: a multiple of the cluster size, about one CTA per SM over all KV heads.
-static int attn_splits(int sms, int n_kv) {
-    const int s = sms / n_kv / ATTN_CLUSTER * ATTN_CLUSTER;
+// Clusters of eight attention CTAs the device can hold at once for a head size (a cluster needs eight SMs
+// of one GPC with room for a CTA each); 0 when the query fails.  Cached per head size.
+static int attn_max_clusters(int hd) {
+    static int cache[3] = {-1, -1, -1};
+    const int slot = hd == 64 ? 0 : hd == 128 ? 1 : 2;
+    if (cache[slot] >= 0) return cache[slot];
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(ATTN_CLUSTER * 64, 1);
+    cfg.blockDim = dim3(ATTN_THREADS);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ATTN_CLUSTER;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    cudaError_t r = hd == 64    ? cudaOccupancyMaxActiveClusters(&n, k_attn_decode<64>, &cfg)
+                    : hd == 128 ? cudaOccupancyMaxActiveClusters(&n, k_attn_decode<128>, &cfg)
+                                : cudaOccupancyMaxActiveClusters(&n, k_attn_decode<256>, &cfg);
+    if (r != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+    }
+    cache[slot] = n;
+    return n;
+}
+
+// Splits per KV head: a multiple of the cluster size, about one CTA per SM over all KV heads, and no more
+// clusters than run at the same time (a second wave would double the kernel's duration).
+static int attn_splits(int sms, int n_kv, int hd) {
+    int s = sms / n_kv / ATTN_CLUSTER * ATTN_CLUSTER;
+    const int fit = attn_max_clusters(hd) / n_kv * ATTN_CLUSTER;
+    if (fit >= ATTN_CLUSTER && fit < s) s = fit;
     return s < ATTN_CLUSTER ? ATTN_CLUSTER : s;
 }
 
@@ -834,7 +865,7 @@ extern "C" int tfr_finalize_load(tfr_engine* e) {
     e->held.clear();
     // workspaces (load.rs:547-607: everything allocated once)
     const int sms = e->prop.multiProcessorCount;
-    e->attn_S = attn_splits(sms, P.n_kv);
+    e->attn_S = attn_splits(sms, P.n_kv, hd);
     CU(e, cudaMalloc(&e->x, (size_t)K * 4));
     const int vd = c.hybrid ? gdn_val_dim(c) : 0;
     CU(e, cudaMalloc(&e->q, (size_t)nq * 4));
@@ -849,7 +880,7 @@ extern "C" int tfr_finalize_load(tfr_engine* e) {
     CU(e, cudaMalloc(&e->h, (size_t)FF * 4));
     CU(e, cudaMalloc(&e->logits, (size_t)Vl * 4));
     CU(e, cudaMalloc(&e->partial, (size_t)P.n_head * e->attn_S * (2 + hd) * 4));
-    CU(e, cudaMalloc(&e->counters, (size_t)P.n_kv * 4));
+    CU(e, cudaMalloc(&e->counters, (size_t)P.n_kv * ATTN_CLUSTER * 4));  // one per KV head and output slice
     if (P.tp > 1) {
         e->comm.lay = tp_layout(K);
         e->comm.tp = P.tp;
@@ -865,7 +896,7 @@ extern "C" int tfr_finalize_load(tfr_engine* e) {
     CU(e, cudaMallocHost(&e->out_host, (size_t)TFR_MAX_BURST * 4));
     CU(e, cudaMalloc(&e->args_dev, 16 * sizeof(int)));  // k_state_begin reads [0..14]
     CU(e, cudaMallocHost(&e->args_host, 16 * sizeof(int)));
-    CU(e, cudaMemsetAsync(e->counters, 0, (size_t)P.n_kv * 4, e->stream));
+    CU(e, cudaMemsetAsync(e->counters, 0, (size_t)P.n_kv * ATTN_CLUSTER * 4, e->stream));
     CU(e, cudaMemsetAsync(e->st, 0, sizeof(TokenState), e->stream));
     CU(e, cudaMemsetAsync(e->logits, 0, (size_t)Vl * 4, e->stream));
     CU(e, cudaStreamSynchronize(e->stream));
@@ -1661,13 +1692,13 @@ static int op_attention_impl(const float* q, const uint16_t* kc, const uint16_t*
     static unsigned int* counters = nullptr;
     static size_t cap = 0;
     AttnArgs a{};
-    a.S = attn_splits(sm_count_cached(), n_kv);
+    a.S = attn_splits(sm_count_cached(), n_kv, head_dim);
     const size_t need = (size_t)n_head * a.S * (2 + head_dim) * 4;
     if (need > cap || !counters) {
         cudaFree(partial);
         if (!counters) {
-            if (cudaMalloc(&counters, 64 * 4) != cudaSuccess) return TFR_E_CUDA;
-            cudaMemset(counters, 0, 64 * 4);
+            if (cudaMalloc(&counters, 64 * ATTN_CLUSTER * 4) != cudaSuccess) return TFR_E_CUDA;
+            cudaMemset(counters, 0, 64 * ATTN_CLUSTER * 4);
         }
         if (cudaMalloc(&partial, need) != cudaSuccess) return TFR_E_CUDA;
         cap = need;
@@ -1756,7 +1787,7 @@ extern "C" int tfr_op_qk_norm_rope_store(const float* raw, const float* q_norm, 
 // acceptable.  For them the split-KV scratch of the decode kernel — the per-split (m, l, O)
 // partials and the per-KV-head arrival counters — lives in a fixed array inside the library
 // image.  Every GPU that loads the library carries these TFR_NOALLOC_SCRATCH_BYTES until exit.
-constexpr size_t TFR_NOALLOC_COUNTER_BYTES = 256;            // 64 KV heads
+constexpr size_t TFR_NOALLOC_COUNTER_BYTES = 2048;           // 64 KV heads x 8 output slices
 constexpr size_t TFR_NOALLOC_SCRATCH_BYTES = 2u << 20;       // counters + partials, 2 MiB in total
 static __device__ __align__(256) unsigned char g_attn_noalloc_scratch[TFR_NOALLOC_SCRATCH_BYTES];
 constexpr int TFR_NOALLOC_MAX_DEVICES = 64;
@@ -1770,9 +1801,9 @@ extern "C" int tfr_op_attention_noalloc(const float* q, const uint16_t* kc, cons
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= TFR_NOALLOC_MAX_DEVICES) return TFR_E_CUDA;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return TFR_E_CUDA;
     AttnArgs a{};
-    a.S = attn_splits(sms, n_kv);
+    a.S = attn_splits(sms, n_kv, head_dim);
     const size_t need = (size_t)n_head * a.S * (2 + head_dim) * sizeof(float);
-    if ((size_t)n_kv * sizeof(unsigned int) > TFR_NOALLOC_COUNTER_BYTES || need > TFR_NOALLOC_SCRATCH_BYTES - TFR_NOALLOC_COUNTER_BYTES) {
+    if ((size_t)n_kv * ATTN_CLUSTER * sizeof(unsigned int) > TFR_NOALLOC_COUNTER_BYTES || need > TFR_NOALLOC_SCRATCH_BYTES - TFR_NOALLOC_COUNTER_BYTES) {
         fprintf(stderr,
                 "tfr_op_attention_noalloc: %d heads / %d KV heads / head_dim %d need %zu bytes of split scratch; the built-in "
                 "array holds %zu\n",
