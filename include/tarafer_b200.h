@@ -101,12 +101,22 @@ int tfr_gguf_tensor_info(const tfr_gguf* g, int64_t i, const char** name, int* g
                          uint64_t* offset, uint64_t* nbytes);
 const void* tfr_gguf_tensor_data(const tfr_gguf* g, int64_t i); /* GgufFile::tensor_data: the mapped bytes */
 /* Metadata with the reference's lenient coercions (Value::as_u64 / as_f32 / as_str, value.rs:55-100);
- * a missing key or another kind of value returns TFR_E_INVALID.  Arrays are parsed but only counted. */
+ * a missing key or another kind of value returns TFR_E_INVALID.  Strings above 64 MiB and arrays above 10 M
+ * items are refused (value.rs:163-183, 246-262), as is invalid UTF-8. */
 int tfr_gguf_meta_u64(const tfr_gguf* g, const char* key, uint64_t* out);
 int tfr_gguf_meta_f32(const tfr_gguf* g, const char* key, float* out);
 int tfr_gguf_meta_str(const tfr_gguf* g, const char* key, const char** out);
 int64_t tfr_gguf_meta_array_len(const tfr_gguf* g, const char* key);
-/* ModelConfig::from_gguf, crates/core/src/config.rs:107-264: `<arch>.*` keys, defaults and the qwen35 extras. */
+/* Items of a metadata array (Value::Array, value.rs:246-262): what Tokenizer::from_gguf reads
+ * (crates/core/src/tokenizer/mod.rs:27-106) - tokenizer.ggml.tokens / .merges (strings, not NUL-terminated: *len
+ * bytes), .scores (floats), .token_type (integers).  TFR_E_INVALID for a missing key, another item kind or an
+ * index past the end. */
+int tfr_gguf_meta_array_str(const tfr_gguf* g, const char* key, int64_t i, const char** out, uint64_t* len);
+int tfr_gguf_meta_array_f32(const tfr_gguf* g, const char* key, int64_t i, float* out);
+int tfr_gguf_meta_array_i64(const tfr_gguf* g, const char* key, int64_t i, int64_t* out);
+/* ModelConfig::from_gguf, crates/core/src/config.rs:107-264: `<arch>.*` keys, defaults and the qwen35 extras.
+ * Architectures whose schedule this library does not build (smollm3's no-RoPE layers, mixture-of-experts
+ * models) return TFR_E_UNSUPPORTED instead of being decoded as a plain dense model. */
 int tfr_gguf_model_config(const tfr_gguf* g, tfr_model_config* out, char* err, size_t err_cap);
 /* CudaModel::load_with(gguf), load.rs:166-417: tfr_set_config from the metadata, tfr_upload_tensor for every
  * tensor of the decode path straight from the mapping, tfr_finalize_load.  The file may be closed afterwards. */
@@ -183,6 +193,16 @@ int tfr_tp_vocab_range(const tfr_engine* e, int* first, int* end);
 /* set_cuda_graph / graph_active / invalidate_decode_graph, model.rs:101-112,197 */
 int tfr_set_cuda_graph(tfr_engine* e, int enabled);
 int tfr_graph_active(const tfr_engine* e);
+/* DecodeBackend / REGISTRY, crates/core/src/cuda/decode.rs:87-240 (the reference picks its decode backend by name,
+ * `--decode flash|fastv2`).  Two schedules compute the same token loop here:
+ *   1 = chained kernels: five launches per layer, one CUDA graph per token replayed back to back;
+ *   2 = persistent loop: one cooperative kernel per call that runs every decode step of the call, streams the
+ *       weights through shared memory without stopping at phase boundaries and hands activations over through
+ *       grid-wide barriers (dense models on one GPU; Q4_K / Q6_K matrices; no vocabulary shortlist).
+ * path 0 (default) takes the persistent loop when the model qualifies and the chained kernels otherwise;
+ * path 2 fails with TFR_E_UNSUPPORTED when it does not.  tfr_decode_path reports which one the next call takes. */
+int tfr_set_decode_path(tfr_engine* e, int path);
+int tfr_decode_path(const tfr_engine* e);
 /* Kernel launches issued by this engine so far (graph replays count their kernel nodes). */
 int64_t tfr_launch_count(const tfr_engine* e);
 /* Device time of the last tfr_decode_burst / tfr_forward_greedy in milliseconds (CUDA events
@@ -197,6 +217,10 @@ int tfr_debug_read(tfr_engine* e, tfr_kv* kv, const char* what, int layer, void*
  * GPU nanosecond timer at up to eight points into device_buffer[(launch * 160 + cta) * 8 + point], launch =
  * index of the kernel within the decode step (0 for the stand-alone operators). */
 int tfr_debug_set_timeline(unsigned long long* device_buffer);
+/* Test aid for the persistent loop: during decode step `step` of the next calls, thread 0 of every CTA stores the
+ * GPU nanosecond timer at successive points of the step into device_buffer[point * n_sm + cta] (point < points).
+ * device_buffer == NULL switches it off. */
+int tfr_debug_set_loop_timeline(tfr_engine* e, unsigned long long* device_buffer, int step, int points);
 
 /* ---- operator level (device pointers unless stated; stream = cudaStream_t or NULL) ---- */
 
@@ -228,7 +252,9 @@ int tfr_ffn_block_host(const tfr_mat* gate, const tfr_mat* up, const tfr_mat* do
  * a = the per-32-block sums [N][K/32] of gemv.cu:1558-1582. */
 int tfr_op_int_dots(const tfr_mat* w, const int8_t* q8, const float* d8, int32_t* a, int32_t* b, void* stream);
 /* attn_flash_partial + attn_flash_reduce, kernels/attn/flash.cu:16-255, for one query token
- * at position pos over cache rows [0, pos].  kc / vc: [max_seq][n_kv*head_dim] f16 bits. */
+ * at position pos over cache rows [0, pos].  kc / vc: [max_seq][n_kv*head_dim] f16 bits.  The split-KV scratch
+ * of this stand-alone call is one buffer per device, grown on demand: calls that overlap on the same GPU
+ * (different streams, or threads) race on it - serialise them. */
 int tfr_op_attention(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv,
                      int head_dim, int pos, void* stream);
 /* Same computation as tfr_op_attention for callers that cannot allocate device memory when they
@@ -236,7 +262,8 @@ int tfr_op_attention(const float* q, const uint16_t* kc, const uint16_t* vc, flo
  * loop).  It has no counterpart in the reference.  The split-KV scratch is a fixed 2 MiB array
  * inside the library image (held by every GPU that loads the library, until exit); the call
  * performs no cudaMalloc / cudaFree and uses no allocating library routine.  Shapes whose scratch
- * n_head * (n_sm / n_kv) * (2 + head_dim) * 4 bytes exceeds 2 MiB - 256 B, or with more than 64 KV
+ * n_head * S * (2 + head_dim) * 4 bytes exceeds 2 MiB - 2048 B, where S is the number of key splits the
+ * attention kernel uses on this GPU (a multiple of 8, at least 8, about n_sm / n_kv), or with more than 64 KV
  * heads, are refused with TFR_E_UNSUPPORTED and a message on stderr.  The first call on a device
  * looks up the array's device address (that device must be current); make that first call before
  * any stream capture begins.  All calls share the one array: calls that overlap on the GPU

@@ -59,6 +59,9 @@ def lib() -> C.CDLL:
         "tfr_gguf_meta_f32": (i32, [vp, C.c_char_p, C.POINTER(f32)]),
         "tfr_gguf_meta_str": (i32, [vp, C.c_char_p, C.POINTER(C.c_char_p)]),
         "tfr_gguf_meta_array_len": (i64, [vp, C.c_char_p]),
+        "tfr_gguf_meta_array_str": (i32, [vp, C.c_char_p, i64, C.POINTER(C.c_char_p), C.POINTER(C.c_uint64)]),
+        "tfr_gguf_meta_array_f32": (i32, [vp, C.c_char_p, i64, C.POINTER(f32)]),
+        "tfr_gguf_meta_array_i64": (i32, [vp, C.c_char_p, i64, C.POINTER(i64)]),
         "tfr_gguf_model_config": (i32, [vp, C.POINTER(ModelConfig), C.c_char_p, sz]),
         "tfr_load_gguf": (i32, [vp, vp, i32, i32]),
         "tfr_alloc_kv": (i32, [vp, i32, C.POINTER(vp)]),
@@ -85,6 +88,9 @@ def lib() -> C.CDLL:
         "tfr_tp_use_nccl": (i32, [vp, vp]),
         "tfr_set_cuda_graph": (i32, [vp, i32]),
         "tfr_graph_active": (i32, [vp]),
+        "tfr_set_decode_path": (i32, [vp, i32]),
+        "tfr_decode_path": (i32, [vp]),
+        "tfr_debug_set_loop_timeline": (i32, [vp, vp, i32, i32]),
         "tfr_launch_count": (i64, [vp]),
         "tfr_last_device_ms": (f32, [vp]),
         "tfr_debug_read": (i32, [vp, vp, C.c_char_p, i32, vp, sz]),

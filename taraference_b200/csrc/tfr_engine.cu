@@ -27,6 +27,7 @@
 
 #include "../../include/tarafer_b200.h"
 #include "tfr_kernels.cuh"
+#include "tfr_loop.cuh"
 
 using namespace tfr;
 
@@ -123,7 +124,8 @@ struct tfr_engine {
     TpPlan plan{};
     TpComm comm{};
     unsigned char* comm_local = nullptr;
-    bool comm_attached = false, comm_ipc = false;
+    bool peers_wired = false, comm_ipc = false;  // peers_wired: every rank's exchange buffer is mapped (tfr_tp_attach_*)
+    bool nccl_ready = false;                     // the comparison mode's communicator exists
     // comparison mode: partial sums through ncclAllReduce between kernels instead of the in-kernel exchange
     void* nccl_comm = nullptr;
     bool use_nccl = false;
@@ -155,6 +157,21 @@ struct tfr_engine {
     int64_t launches = 0;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_ms = 0.f;
+    // persistent decode loop (tfr_loop.cuh): one cooperative kernel per call instead of a graph per token
+    bool loop_ok = false;
+    int decode_path = 0;  // 0: the loop when the model qualifies, 1: chained kernels, 2: the loop or an error
+    std::string loop_why;
+    LoopArgs loop{};
+    LoopLayer* loop_layers = nullptr;
+    unsigned int* loop_bar = nullptr;
+    unsigned long long* loop_best = nullptr;
+    float* loop_partial = nullptr;
+    size_t loop_smem = 0;
+    int loop_grid = 0;
+    int* loop_blob = nullptr;
+    uint4* loop_head_tasks = nullptr;
+    unsigned long long* loop_prof = nullptr;
+    int loop_prof_step = -1, loop_prof_points = 0;
 };
 
 struct tfr_kv {
@@ -162,6 +179,10 @@ struct tfr_kv {
     unsigned short *k = nullptr, *v = nullptr;
     int len = 0, max_seq = 0;
     size_t layer_stride = 0;  // elements
+    // K/V exist for the softmax-attention layers only (kv.rs:8-12 keeps empty buffers for linear layers):
+    // kv_slot[layer] is the layer's index into the compact arrays, -1 for a Gated-DeltaNet layer
+    std::vector<int> kv_slot;
+    int n_kv_layers = 0;
     // hybrid models (kv.rs:12-15): per layer the fp32 state S[n_v][128][128] and the conv history,
     // held as a ring of `kernel` slots of [channels] (see tfr_gdn.cuh)
     float *ssm = nullptr, *conv = nullptr;
@@ -170,6 +191,10 @@ struct tfr_kv {
 };
 
 static bool is_hybrid(const tfr_engine* e) { return e->cfg.hybrid != 0; }
+static unsigned short* kv_k(const tfr_kv* kv, int li) { return kv->k + (size_t)(kv->kv_slot[li] < 0 ? 0 : kv->kv_slot[li]) * kv->layer_stride; }
+static unsigned short* kv_v(const tfr_kv* kv, int li) { return kv->v + (size_t)(kv->kv_slot[li] < 0 ? 0 : kv->kv_slot[li]) * kv->layer_stride; }
+// A forward call may run: the exchange the engine is set to use has everything it needs.
+static bool tp_ready(const tfr_engine* e) { return e->use_nccl ? e->nccl_ready : e->peers_wired; }
 static int gdn_channels(const tfr_model_config& c) { return (2 * c.ssm_group_count + c.ssm_time_step_rank) * c.ssm_state_size; }
 static int gdn_val_dim(const tfr_model_config& c) { return c.ssm_time_step_rank * c.ssm_state_size; }
 static int layer_kind(const tfr_model_config& c, int i) {
@@ -212,10 +237,20 @@ static void configure_kernel(F f, bool dynamic) {
     cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
 
+// CUDA function attributes, occupancy answers and the stand-alone operators' scratch are per-device state: one
+// process may drive several GPUs (tfr_tp_attach_pointers), so everything below is kept per device ordinal.
+constexpr int TFR_MAX_DEVICES = 64;
+static int current_device_slot() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return dev >= 0 && dev < TFR_MAX_DEVICES ? dev : 0;
+}
+
 static void configure_kernels_once() {
-    static bool done = false;
-    if (done) return;
-    done = true;
+    static bool done[TFR_MAX_DEVICES] = {};
+    const int dev = current_device_slot();
+    if (done[dev]) return;
+    done[dev] = true;
     configure_kernel(k_gemv<BlockQ4, EpiQkv>, true);
     configure_kernel(k_gemv<BlockQ4, EpiStore>, true);
     configure_kernel(k_gemv<BlockQ6, EpiStore>, true);
@@ -244,7 +279,13 @@ static void configure_kernels_once() {
 // Clusters of eight attention CTAs the device can hold at once for a head size (a cluster needs eight SMs
 // of one GPC with room for a CTA each); 0 when the query fails.  Cached per head size.
 static int attn_max_clusters(int hd) {
-    static int cache[3] = {-1, -1, -1};
+    static int cache_all[TFR_MAX_DEVICES][3];
+    static bool cache_init = false;
+    if (!cache_init) {
+        for (auto& d : cache_all) d[0] = d[1] = d[2] = -1;
+        cache_init = true;
+    }
+    int* cache = cache_all[current_device_slot()];
     const int slot = hd == 64 ? 0 : hd == 128 ? 1 : 2;
     if (cache[slot] >= 0) return cache[slot];
     cudaLaunchConfig_t cfg{};
@@ -279,10 +320,10 @@ static int attn_splits(int sms, int n_kv, int hd) {
 }
 
 static int sm_count_cached() {
-    static int n = 0;
+    static int count[TFR_MAX_DEVICES] = {};
+    const int dev = current_device_slot();
+    int& n = count[dev];
     if (!n) {
-        int dev = 0;
-        cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
         if (n <= 0) n = 148;
     }
@@ -502,7 +543,7 @@ extern "C" void tfr_destroy(tfr_engine* e) {
     for (auto& kv : e->vecs) cudaFree(kv.second.dev);
     for (auto& L : e->layers) cudaFree(L.bias_qkv);
     void* ws[] = {e->x, e->q, e->attn, e->h, e->logits, e->partial, e->counters, e->st, e->out_tokens, e->prompt,
-                  e->layer_taps, e->proj, e->qgate};
+                  e->layer_taps, e->proj, e->qgate, e->loop_layers, e->loop_bar, e->loop_best, e->loop_partial, e->loop_blob, e->loop_head_tasks};
     for (void* p : ws) cudaFree(p);
     if (e->st_host) cudaFreeHost(e->st_host);
     if (e->out_host) cudaFreeHost(e->out_host);
@@ -759,6 +800,185 @@ static int finalize_linear_layer(tfr_engine* e, int i, LayerW& L) {
     return rc;
 }
 
+// ------------------------------------------------------------------ persistent decode loop: plan
+
+template <class F>
+static cudaError_t loop_configure(F f, size_t smem) {
+    cudaError_t r = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (r == cudaSuccess) r = cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    return r;
+}
+static const void* loop_kernel(int hd) {
+    if (hd == 64) return (const void*)k_decode_loop<64>;
+    if (hd == 128) return (const void*)k_decode_loop<128>;
+    return (const void*)k_decode_loop<256>;
+}
+static size_t loop_attn_smem(int hd) {
+    return hd == 64 ? sizeof(AttnSmem<64>) : hd == 128 ? sizeof(AttnSmem<128>) : sizeof(AttnSmem<256>);
+}
+
+// Builds the persistent loop's plan after the weights are in place.  Models outside its scope keep the
+// chained-kernel path; loop_why says which condition failed.
+static int loop_setup(tfr_engine* e) {
+    const tfr_model_config& c = e->cfg;
+    const TpPlan& P = e->plan;
+    e->loop_ok = false;
+    auto no = [&](const char* why) {
+        e->loop_why = why;
+        return TFR_OK;
+    };
+    if (c.hybrid) return no("hybrid (Gated-DeltaNet) layers");
+    if (P.tp > 1) return no("tensor parallelism");
+    if (e->vocab_limit) return no("vocabulary shortlist");
+    int coop = 0;
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, e->device);
+    if (!coop) return no("no cooperative launch on this device");
+    const int G = e->prop.multiProcessorCount, K = c.n_embd, hd = c.head_dim;
+    if (c.n_head / c.n_kv_head > LOOP_REP_MAX || G < P.n_kv) return no("head grouping");
+    auto q46 = [](const tfr_mat* m) { return m->m.type == TFR_Q4_K || m->m.type == TFR_Q6_K; };
+    if (!q46(e->head) || !q46(e->token_embd)) return no("head / embedding type");
+    for (const LayerW& L : e->layers)
+        if (!q46(L.wo) || !q46(L.down)) return no("attn_output / ffn_down type");
+    int lpb[5] = {0, 0, 0, 0, 0};
+    if (const char* env = getenv("TFR_LOOP_LPB")) sscanf(env, "%d,%d,%d,%d,%d", &lpb[0], &lpb[1], &lpb[2], &lpb[3], &lpb[4]);
+    LoopArgs& a = e->loop;
+    a = LoopArgs{};
+    int pbuf = 4096;
+    if (const char* env = getenv("TFR_LOOP_PBUF")) pbuf = std::max(1024, atoi(env));
+    // sections: 0 Q/K/V, 1 o-proj Q4_K, 2 o-proj Q6_K, 3 gate/up, 4 down Q4_K, 5 down Q6_K, 6 head
+    LoopPhase ph[SCHED_SECTIONS] = {};
+    bool used[SCHED_SECTIONS] = {true, false, false, true, false, false, true};
+    for (const LayerW& L : e->layers) {
+        used[1 + (L.wo->m.type == TFR_Q6_K)] = true;
+        used[4 + (L.down->m.type == TFR_Q6_K)] = true;
+    }
+    ph[0].job[0] = loop_job(TFR_Q4_K, P.nq, 2, 0, 0, G);
+    ph[0].job[1] = loop_job(TFR_Q4_K, P.nkv, 2, P.nq / 2, 0, G);
+    ph[0].job[2] = loop_job(TFR_Q6_K, P.nkv, 2, (P.nq + P.nkv) / 2, 1, G);
+    for (int t = 0; t < 2; t++) {
+        const int type = t ? TFR_Q6_K : TFR_Q4_K;
+        ph[1 + t].job[0] = loop_job(type, K, 2, 0, 0, G);
+        ph[4 + t].job[0] = loop_job(type, K, 2, 0, 0, G);
+    }
+    ph[3].job[0] = loop_job(TFR_Q4_K, P.ff, 1, 0, 0, G);
+    ph[3].job[1] = loop_job(TFR_Q4_K, P.ff, 1, 0, 0, G);
+    ph[3].zip = 1;
+    const int V = e->head->m.N;
+    ph[6].job[0] = loop_job(e->head->m.type, V, 2, 0, 0, G);
+    const int sec_k[SCHED_SECTIONS] = {K, P.attn_width, P.attn_width, K, P.ff, P.ff, K};
+    const int sec_lpb[SCHED_SECTIONS] = {lpb[0], lpb[1], lpb[1], lpb[2], lpb[3], lpb[3], lpb[4]};
+    bool fits = true;
+    for (int sct = 0; sct < SCHED_SECTIONS; sct++) {
+        fits = fits && loop_finish_phase(ph[sct], sec_k[sct], pbuf, sec_lpb[sct]);
+        a.sec_nb[sct] = sec_k[sct] / 256;
+        a.sec_zip[sct] = ph[sct].zip;
+    }
+    LoopPlanHost plan;
+    if (!fits || !loop_build_plan(ph, used, G, pbuf, plan)) return no("a phase's partial sums exceed the shared-memory buffer");
+    a.blob_stride = plan.blob_stride, a.blob_chunks = plan.chunks_off, a.blob_tasks = plan.tasks_off, a.blob_sched = plan.sched_off;
+    a.head_stride = plan.head_stride;
+    // shared-memory map: [barriers, control, reduction scratch | plan | layer table | activation | staged fp32 vector |
+    // partial sums | weight ring]; the attention scratch aliases activation .. partial sums
+    const int k_act = std::max(std::max(K, P.ff), P.attn_width);
+    const size_t act_b = (act_smem_bytes(k_act, false, false) + 15) & ~(size_t)15;
+    const size_t xf_b = (xs_floats(K) * 4 + 15) & ~(size_t)15;
+    size_t work = act_b + xf_b + (size_t)pbuf * 4;
+    const size_t attn_need = std::max(loop_attn_smem(hd), (size_t)(2 * ((G / P.n_kv + 3) & ~3) + LOOP_CT) * 4);
+    if (work < attn_need) work = attn_need;
+    a.off_blob = 1536;
+    a.off_layers = (int)((a.off_blob + (size_t)plan.blob_stride * 4 + 15) & ~(size_t)15);
+    a.off_act = (int)((a.off_layers + (size_t)c.n_layer * sizeof(LoopLayer) + 127) & ~(size_t)127);
+    a.off_xf = a.off_act + (int)act_b;
+    a.off_pbuf = a.off_xf + (int)xf_b;
+    a.off_ring = (int)((a.off_act + work + 127) & ~(size_t)127);
+    a.pbuf_floats = pbuf;
+    const size_t cap = e->prop.sharedMemPerBlockOptin;
+    if (cap <= (size_t)a.off_ring + 3 * LOOP_SLOT) return no("not enough shared memory for the weight ring");
+    int nslot = (int)((cap - a.off_ring) / LOOP_SLOT);
+    if (nslot > LOOP_MAX_SLOTS) nslot = LOOP_MAX_SLOTS;
+    if (const char* env = getenv("TFR_LOOP_SLOTS")) nslot = std::max(3, std::min(nslot, atoi(env)));
+    a.nslot = nslot;
+    e->loop_smem = (size_t)a.off_ring + (size_t)nslot * LOOP_SLOT;
+    e->loop_grid = G;
+    cudaError_t r = hd == 64    ? loop_configure(k_decode_loop<64>, e->loop_smem)
+                    : hd == 128 ? loop_configure(k_decode_loop<128>, e->loop_smem)
+                                : loop_configure(k_decode_loop<256>, e->loop_smem);
+    int per_sm = 0;
+    if (r == cudaSuccess) r = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, loop_kernel(hd), LOOP_THREADS, e->loop_smem);
+    if (r != cudaSuccess || per_sm < 1) {
+        cudaGetLastError();
+        return no("the loop kernel does not fit an SM");
+    }
+    // per-layer pointers
+    std::vector<LoopLayer> tab(c.n_layer);
+    for (int i = 0; i < c.n_layer; i++) {
+        const LayerW& L = e->layers[i];
+        LoopLayer& t = tab[i];
+        t.wq = L.wq->m.data, t.wk = L.wk->m.data, t.wv = L.wv->m.data, t.wo = L.wo->m.data;
+        t.gate = L.gate->m.data, t.up = L.up->m.data, t.down = L.down->m.data;
+        t.bias_qkv = L.bias_qkv, t.attn_norm = L.attn_norm, t.ffn_norm = L.ffn_norm;
+        t.o_q6 = L.wo->m.type == TFR_Q6_K, t.down_q6 = L.down->m.type == TFR_Q6_K;
+    }
+    CU(e, cudaMalloc(&e->loop_blob, plan.blob.size() * sizeof(int)));
+    CU(e, cudaMalloc(&e->loop_head_tasks, plan.head_tasks.size() * sizeof(uint4)));
+    CU(e, cudaMemcpyAsync(e->loop_blob, plan.blob.data(), plan.blob.size() * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    CU(e, cudaMemcpyAsync(e->loop_head_tasks, plan.head_tasks.data(), plan.head_tasks.size() * sizeof(uint4), cudaMemcpyHostToDevice, e->stream));
+    a.blob = e->loop_blob;
+    a.head_tasks = e->loop_head_tasks;
+    CU(e, cudaMalloc(&e->loop_layers, tab.size() * sizeof(LoopLayer)));
+    CU(e, cudaMemcpyAsync(e->loop_layers, tab.data(), tab.size() * sizeof(LoopLayer), cudaMemcpyHostToDevice, e->stream));
+    CU(e, cudaStreamSynchronize(e->stream));  // tab goes out of scope
+    a.attn_smax = std::max(1, G / P.n_kv);
+    a.attn_min_keys = 64;
+    a.attn_inline_max = 8;
+    if (const char* env = getenv("TFR_LOOP_ATTN_KEYS")) a.attn_min_keys = std::max(8, atoi(env));
+    if (const char* env = getenv("TFR_LOOP_ATTN_INLINE")) a.attn_inline_max = std::max(1, atoi(env));
+    CU(e, cudaMalloc(&e->loop_partial, (size_t)P.n_head * a.attn_smax * (4 + hd) * 4));
+    CU(e, cudaMalloc(&e->loop_bar, 8 * LOOP_BAR_STRIDE * 4));
+    CU(e, cudaMalloc(&e->loop_best, 4 * 8));
+    a.layers = e->loop_layers;
+    a.n_layer = c.n_layer;
+    a.K = K, a.FF = P.ff, a.nq = P.nq, a.nkv = P.nkv, a.hd = hd, a.n_head = P.n_head, a.n_kv = P.n_kv, a.V = V;
+    a.eps = c.rms_eps, a.theta = c.rope_theta, a.attn_scale = 1.0f / sqrtf((float)hd);  // forward.rs:389
+    a.embed = e->token_embd->m;
+    a.head = e->head->m.data;
+    a.out_norm = e->output_norm;
+    a.x = e->x, a.q = e->q, a.attn = e->attn, a.h = e->h, a.logits = e->logits;
+    a.partial = e->loop_partial;
+    a.bar = e->loop_bar;
+    a.best = e->loop_best;
+    a.st = e->st;
+    a.out_tokens = e->out_tokens;
+    a.prompt = e->prompt;
+    e->loop_ok = true;
+    e->loop_why.clear();
+    return TFR_OK;
+}
+
+// path 0 (auto) takes the persistent loop only when the build says it is the faster schedule
+constexpr bool TFR_LOOP_IS_DEFAULT = false;
+static bool use_loop(const tfr_engine* e) { return e->loop_ok && (e->decode_path == 2 || (e->decode_path == 0 && TFR_LOOP_IS_DEFAULT)); }
+
+// One launch of the persistent loop: n_headless prompt-feeding steps, then the steps TokenState asks for.
+static int run_loop(tfr_engine* e, const tfr_kv* kv, int n_headless) {
+    LoopArgs a = e->loop;
+    a.kc = kv->k;
+    a.vc = kv->v;
+    a.kv_layer_stride = kv->layer_stride;
+    a.layer_taps = e->layer_taps;
+    a.n_headless = n_headless;
+    a.prof = e->loop_prof;
+    a.prof_step = e->loop_prof_step;
+    a.prof_points = e->loop_prof_points;
+    k_loop_reset<<<1, 256, 0, e->stream>>>(e->loop_bar, e->loop_best);
+    CU(e, cudaGetLastError());
+    void* params[] = {&a};
+    CU(e, cudaLaunchCooperativeKernel(loop_kernel(e->cfg.head_dim), dim3(e->loop_grid), dim3(LOOP_THREADS), params, e->loop_smem,
+                                      e->stream));
+    e->launches += 2;
+    return TFR_OK;
+}
+
 extern "C" int tfr_finalize_load(tfr_engine* e) {
     if (!e || !e->has_cfg) return TFR_E_INVALID;
     if (e->finalized) return TFR_OK;
@@ -900,6 +1120,9 @@ extern "C" int tfr_finalize_load(tfr_engine* e) {
     CU(e, cudaMemsetAsync(e->st, 0, sizeof(TokenState), e->stream));
     CU(e, cudaMemsetAsync(e->logits, 0, (size_t)Vl * 4, e->stream));
     CU(e, cudaStreamSynchronize(e->stream));
+    rc = loop_setup(e);
+    if (rc) return rc;
+    if (e->decode_path == 2 && !e->loop_ok) return fail(e, TFR_E_UNSUPPORTED, "persistent decode loop unavailable: %s", e->loop_why.c_str());
     e->finalized = true;
     return TFR_OK;
 }
@@ -913,7 +1136,10 @@ extern "C" int tfr_alloc_kv(tfr_engine* e, int max_seq, tfr_kv** out) {
     kv->e = e;
     kv->max_seq = max_seq;
     kv->layer_stride = (size_t)max_seq * e->plan.nkv;
-    const size_t bytes = kv->layer_stride * e->cfg.n_layer * 2;
+    kv->kv_slot.assign(e->cfg.n_layer, -1);
+    for (int i = 0; i < e->cfg.n_layer; i++)
+        if (layer_kind(e->cfg, i) != LAYER_LINEAR) kv->kv_slot[i] = kv->n_kv_layers++;
+    const size_t bytes = kv->layer_stride * (size_t)(kv->n_kv_layers > 0 ? kv->n_kv_layers : 1) * 2;
     if (cudaMalloc(&kv->k, bytes) != cudaSuccess || cudaMalloc(&kv->v, bytes) != cudaSuccess) {
         cudaFree(kv->k);
         delete kv;
@@ -959,7 +1185,8 @@ extern "C" int tfr_kv_clear(tfr_kv* kv) { return tfr_kv_set_len(kv, 0); }
 extern "C" int64_t tfr_kv_bytes_per_token(const tfr_kv* kv) {
     if (!kv) return 0;
     const tfr_model_config& c = kv->e->cfg;
-    return (int64_t)c.n_layer * kv->e->plan.nkv * 2 * 2;  // kv.rs:36-41 (this rank's KV heads)
+    (void)c;
+    return (int64_t)kv->n_kv_layers * kv->e->plan.nkv * 2 * 2;  // kv.rs:36-41: full-attention layers only (this rank's KV heads)
 }
 extern "C" int tfr_zero_recurrent(tfr_engine* e, tfr_kv* kv) {
     if (!e || !kv || kv->e != e) return TFR_E_INVALID;
@@ -1048,8 +1275,8 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
         pn.prof_id = n;
         AttnArgs a{};
         a.q = e->q;
-        a.kc = kv->k + (size_t)li * kv->layer_stride;
-        a.vc = kv->v + (size_t)li * kv->layer_stride;
+        a.kc = kv_k(kv, li);
+        a.vc = kv_v(kv, li);
         a.partial = e->partial;
         a.counters = e->counters;
         a.out = e->attn + P.attn_off;
@@ -1124,8 +1351,8 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
             qa.k_norm = L.k_norm;
             qa.q_out = e->q;
             qa.gate_out = e->qgate;
-            qa.kc = kv->k + (size_t)li * kv->layer_stride;
-            qa.vc = kv->v + (size_t)li * kv->layer_stride;
+            qa.kc = kv_k(kv, li);
+            qa.vc = kv_v(kv, li);
             qa.n_head = P.n_head;
             qa.n_kv = P.n_kv;
             qa.hd = hd;
@@ -1147,13 +1374,13 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
             fseg.m = L.wv->m;
             fseg.sh = make_share(nkv / 2, cap);
             fseg.id_base = (nq + nkv) / 2;
-            pn.l2_rows_a = (const unsigned char*)(kv->k + (size_t)li * kv->layer_stride);
-            pn.l2_rows_b = (const unsigned char*)(kv->v + (size_t)li * kv->layer_stride);
+            pn.l2_rows_a = (const unsigned char*)(kv_k(kv, li));
+            pn.l2_rows_b = (const unsigned char*)(kv_v(kv, li));
             pn.l2_row_bytes = nkv * 2;
             EpiQkv epi{};
             epi.q_out = e->q;
-            epi.kc = kv->k + (size_t)li * kv->layer_stride;
-            epi.vc = kv->v + (size_t)li * kv->layer_stride;
+            epi.kc = kv_k(kv, li);
+            epi.vc = kv_v(kv, li);
             epi.bias = L.bias_qkv;
             epi.nq = nq;
             epi.nk = nkv;
@@ -1297,6 +1524,7 @@ static int finish_state(tfr_engine* e, int n_tokens_out) {
     CU(e, cudaStreamSynchronize(e->stream));
     cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1);
     if (e->st_host->err == 3) return fail(e, TFR_E_CUDA, "tensor parallelism: a peer rank did not deliver within the wait limit");
+    if (e->st_host->err == 4) return fail(e, TFR_E_CUDA, "persistent decode loop: a grid-wide barrier did not complete within the wait limit");
     if (e->st_host->err == 2) return fail(e, TFR_E_CUDA, "a weight tile copy did not complete");
     if (e->st_host->err) return fail(e, TFR_E_INVALID, "device reported an invalid token id");
     return TFR_OK;
@@ -1305,13 +1533,14 @@ static int finish_state(tfr_engine* e, int n_tokens_out) {
 extern "C" int tfr_forward_greedy(tfr_engine* e, tfr_kv* kv, const uint32_t* tokens, int n, uint32_t* next_token) {
     if (!e || !kv || kv->e != e || !e->finalized) return e ? fail(e, TFR_E_INVALID, "forward_greedy: bad handle") : TFR_E_INVALID;
     if (n <= 0 || !tokens) return fail(e, TFR_E_EMPTY, "empty tokens");
-    if (e->plan.tp > 1 && !e->comm_attached) return fail(e, TFR_E_INVALID, "tensor-parallel ranks are not connected (tfr_tp_attach_*)");
+    if (e->plan.tp > 1 && !tp_ready(e)) return fail(e, TFR_E_INVALID, "tensor-parallel ranks are not connected (tfr_tp_attach_*)");
     if (kv->len + n > kv->max_seq) return fail(e, TFR_E_FULL, "context full");
     if (n > TFR_MAX_PROMPT) return fail(e, TFR_E_INVALID, "more than %d tokens in one call", TFR_MAX_PROMPT);
     for (int i = 0; i < n; i++)
         if (tokens[i] >= (uint32_t)e->token_embd->m.N) return fail(e, TFR_E_INVALID, "token id %u out of range", tokens[i]);
     cudaSetDevice(e->device);
-    if (e->use_graph) {
+    const bool loop = use_loop(e);
+    if (e->use_graph && !loop) {
         int rc = ensure_graphs(e, kv);
         if (rc) return rc;
     }
@@ -1319,7 +1548,9 @@ extern "C" int tfr_forward_greedy(tfr_engine* e, tfr_kv* kv, const uint32_t* tok
     int rc = begin_state(e, kv, (int)tokens[0], kv->len, 1, kv->max_seq + 1, nullptr, 0);
     if (rc) return rc;
     CU(e, cudaEventRecord(e->ev0, e->stream));
-    for (int i = 0; i < n && !rc; i++) rc = run_token(e, kv, i == n - 1);
+    if (loop) rc = run_loop(e, kv, n - 1);
+    else
+        for (int i = 0; i < n && !rc; i++) rc = run_token(e, kv, i == n - 1);
     if (rc) return rc;
     CU(e, cudaEventRecord(e->ev1, e->stream));
     rc = finish_state(e, 1);
@@ -1335,13 +1566,14 @@ extern "C" int tfr_forward_greedy(tfr_engine* e, tfr_kv* kv, const uint32_t* tok
 extern "C" int tfr_forward_greedy_all(tfr_engine* e, tfr_kv* kv, const uint32_t* tokens, int n, uint32_t* out) {
     if (!e || !kv || kv->e != e || !e->finalized || !out) return e ? fail(e, TFR_E_INVALID, "forward_greedy_all: bad argument") : TFR_E_INVALID;
     if (n <= 0 || !tokens) return fail(e, TFR_E_EMPTY, "empty tokens");
-    if (e->plan.tp > 1 && !e->comm_attached) return fail(e, TFR_E_INVALID, "tensor-parallel ranks are not connected (tfr_tp_attach_*)");
+    if (e->plan.tp > 1 && !tp_ready(e)) return fail(e, TFR_E_INVALID, "tensor-parallel ranks are not connected (tfr_tp_attach_*)");
     if (kv->len + n > kv->max_seq) return fail(e, TFR_E_FULL, "context full");
     if (n > TFR_MAX_BURST) return fail(e, TFR_E_INVALID, "more than %d tokens in one call", TFR_MAX_BURST);
     for (int i = 0; i < n; i++)
         if (tokens[i] >= (uint32_t)e->token_embd->m.N) return fail(e, TFR_E_INVALID, "token id %u out of range", tokens[i]);
     cudaSetDevice(e->device);
-    if (e->use_graph) {
+    const bool loop = use_loop(e);
+    if (e->use_graph && !loop) {
         int rc = ensure_graphs(e, kv);
         if (rc) return rc;
     }
@@ -1349,7 +1581,9 @@ extern "C" int tfr_forward_greedy_all(tfr_engine* e, tfr_kv* kv, const uint32_t*
     int rc = begin_state(e, kv, (int)tokens[0], kv->len, n, kv->max_seq + 1, nullptr, 0, 1);
     if (rc) return rc;
     CU(e, cudaEventRecord(e->ev0, e->stream));
-    for (int i = 0; i < n && !rc; i++) rc = run_token(e, kv, true);
+    if (loop) rc = run_loop(e, kv, 0);
+    else
+        for (int i = 0; i < n && !rc; i++) rc = run_token(e, kv, true);
     if (rc) return rc;
     CU(e, cudaEventRecord(e->ev1, e->stream));
     rc = finish_state(e, n);
@@ -1365,21 +1599,24 @@ extern "C" int tfr_decode_burst(tfr_engine* e, tfr_kv* kv, uint32_t first_token,
     if (!e || !kv || kv->e != e || !e->finalized || !out || !n_out)
         return e ? fail(e, TFR_E_INVALID, "decode_burst: bad argument") : TFR_E_INVALID;
     if (max_n <= 0) return fail(e, TFR_E_EMPTY, "empty tokens");
-    if (e->plan.tp > 1 && !e->comm_attached) return fail(e, TFR_E_INVALID, "tensor-parallel ranks are not connected (tfr_tp_attach_*)");
+    if (e->plan.tp > 1 && !tp_ready(e)) return fail(e, TFR_E_INVALID, "tensor-parallel ranks are not connected (tfr_tp_attach_*)");
     if (n_stop < 0 || n_stop > 8) return fail(e, TFR_E_INVALID, "at most 8 stop ids");
     if (kv->len + 1 > kv->max_seq) return fail(e, TFR_E_FULL, "context full");
     if (first_token >= (uint32_t)e->token_embd->m.N) return fail(e, TFR_E_INVALID, "token id %u out of range", first_token);
     cudaSetDevice(e->device);
     int n_run = max_n < TFR_MAX_BURST ? max_n : TFR_MAX_BURST;
     if (n_run > kv->max_seq - kv->len) n_run = kv->max_seq - kv->len;
-    if (e->use_graph) {
+    const bool loop = use_loop(e);
+    if (e->use_graph && !loop) {
         int rc = ensure_graphs(e, kv);
         if (rc) return rc;
     }
     int rc = begin_state(e, kv, (int)first_token, kv->len, n_run, kv->max_seq + 1, stop_ids, n_stop);
     if (rc) return rc;
     CU(e, cudaEventRecord(e->ev0, e->stream));
-    for (int i = 0; i < n_run && !rc; i++) rc = run_token(e, kv, true);
+    if (loop) rc = run_loop(e, kv, 0);
+    else
+        for (int i = 0; i < n_run && !rc; i++) rc = run_token(e, kv, true);
     if (rc) return rc;
     CU(e, cudaEventRecord(e->ev1, e->stream));
     rc = finish_state(e, n_run);
@@ -1450,13 +1687,13 @@ extern "C" int tfr_tp_ipc_handle(tfr_engine* e, void* handle_out) {
 }
 static int tp_finish_attach(tfr_engine* e) {
     e->comm.base[e->plan.rank] = e->comm_local;
-    e->comm_attached = true;
+    e->peers_wired = true;
     drop_graphs(e);
     return TFR_OK;
 }
 extern "C" int tfr_tp_attach_ipc(tfr_engine* e, const void* handles) {
     if (!e || !handles || !e->finalized || e->plan.tp < 2) return e ? fail(e, TFR_E_INVALID, "tp_attach_ipc: not a tensor-parallel engine") : TFR_E_INVALID;
-    if (e->comm_attached) return fail(e, TFR_E_INVALID, "ranks already connected");
+    if (e->peers_wired) return fail(e, TFR_E_INVALID, "ranks already connected");
     cudaSetDevice(e->device);
     for (int r = 0; r < e->plan.tp; r++) {
         if (r == e->plan.rank) continue;
@@ -1476,7 +1713,7 @@ extern "C" int tfr_tp_local_pointer(tfr_engine* e, void** ptr) {
 }
 extern "C" int tfr_tp_attach_pointers(tfr_engine* e, void* const* bases) {
     if (!e || !bases || !e->finalized || e->plan.tp < 2) return e ? fail(e, TFR_E_INVALID, "tp_attach_pointers: not a tensor-parallel engine") : TFR_E_INVALID;
-    if (e->comm_attached) return fail(e, TFR_E_INVALID, "ranks already connected");
+    if (e->peers_wired) return fail(e, TFR_E_INVALID, "ranks already connected");
     cudaSetDevice(e->device);
     for (int r = 0; r < e->plan.tp; r++) {
         if (r == e->plan.rank) continue;
@@ -1504,7 +1741,8 @@ extern "C" int tfr_tp_nccl_unique_id(void* id_out_128_bytes) {
 extern "C" int tfr_tp_use_nccl(tfr_engine* e, const void* id_128_bytes) {
     if (!e || !e->finalized || e->plan.tp < 2) return e ? fail(e, TFR_E_INVALID, "tp_use_nccl: not a tensor-parallel engine") : TFR_E_INVALID;
     cudaSetDevice(e->device);
-    if (!id_128_bytes) {  // back to the in-kernel exchange
+    if (!id_128_bytes) {  // back to the in-kernel exchange, which needs the peers' buffers
+        if (!e->peers_wired) return fail(e, TFR_E_INVALID, "tp_use_nccl(NULL): the ranks' exchange buffers were never connected (tfr_tp_attach_*)");
         e->use_nccl = false;
         drop_graphs(e);
         return TFR_OK;
@@ -1520,7 +1758,7 @@ extern "C" int tfr_tp_use_nccl(tfr_engine* e, const void* id_128_bytes) {
         CU(e, cudaMalloc(&e->best_buf, 8));
     }
     e->use_nccl = true;
-    e->comm_attached = true;  // nothing else to wire in this mode
+    e->nccl_ready = true;
     drop_graphs(e);
     return TFR_OK;
 }
@@ -1534,6 +1772,25 @@ extern "C" int tfr_set_cuda_graph(tfr_engine* e, int enabled) {
 extern "C" int tfr_graph_active(const tfr_engine* e) { return e && e->use_graph && e->g_decode ? 1 : 0; }
 extern "C" int64_t tfr_launch_count(const tfr_engine* e) { return e ? e->launches : 0; }
 extern "C" float tfr_last_device_ms(const tfr_engine* e) { return e ? e->last_ms : 0.f; }
+
+extern "C" int tfr_set_decode_path(tfr_engine* e, int path) {
+    if (!e || path < 0 || path > 2) return TFR_E_INVALID;
+    if (path == 2 && e->finalized && !e->loop_ok)
+        return fail(e, TFR_E_UNSUPPORTED, "persistent decode loop unavailable: %s", e->loop_why.c_str());
+    e->decode_path = path;
+    return TFR_OK;
+}
+extern "C" int tfr_decode_path(const tfr_engine* e) {
+    if (!e) return TFR_E_INVALID;
+    return use_loop(e) ? 2 : 1;
+}
+extern "C" int tfr_debug_set_loop_timeline(tfr_engine* e, unsigned long long* device_buffer, int step, int points) {
+    if (!e) return TFR_E_INVALID;
+    e->loop_prof = device_buffer;
+    e->loop_prof_step = step;
+    e->loop_prof_points = device_buffer ? points : 0;
+    return TFR_OK;
+}
 
 extern "C" int tfr_debug_read(tfr_engine* e, tfr_kv* kv, const char* what, int layer, void* out, size_t nbytes) {
     if (!e || !what || !out || !e->finalized) return TFR_E_INVALID;
@@ -1577,7 +1834,8 @@ extern "C" int tfr_debug_read(tfr_engine* e, tfr_kv* kv, const char* what, int l
         return TFR_OK;
     }
     else if ((w == "k" || w == "v") && kv && layer >= 0 && layer < c.n_layer) {
-        src = (w == "k" ? kv->k : kv->v) + (size_t)layer * kv->layer_stride;
+        if (kv->kv_slot[layer] < 0) return fail(e, TFR_E_INVALID, "debug_read: layer %d is a linear-attention layer and has no K/V cache", layer);
+        src = w == "k" ? kv_k(kv, layer) : kv_v(kv, layer);
         have = kv->layer_stride * 2;
     } else return fail(e, TFR_E_INVALID, "debug_read: unknown tap %s", what);
     if (nbytes > have) return fail(e, TFR_E_INVALID, "debug_read: %zu bytes requested, %zu available", nbytes, have);
@@ -1651,8 +1909,15 @@ extern "C" int tfr_op_ffn_block(const tfr_mat* gate, const tfr_mat* up, const tf
 extern "C" int tfr_ffn_block_host(const tfr_mat* gate, const tfr_mat* up, const tfr_mat* down, const float* x_host, float* y_host) {
     if (!gate || !up || !down || !x_host || !y_host) return TFR_E_INVALID;
     const int K = gate->m.K, FF = gate->m.N, N = down->m.N;
-    static float *dx = nullptr, *dh = nullptr, *dy = nullptr;
-    static int cap_k = 0, cap_f = 0, cap_n = 0;
+    // device buffers of this convenience call, grown on demand, one set per device
+    struct HostBlockBufs {
+        float *dx = nullptr, *dh = nullptr, *dy = nullptr;
+        int cap_k = 0, cap_f = 0, cap_n = 0;
+    };
+    static HostBlockBufs bufs[TFR_MAX_DEVICES];
+    HostBlockBufs& hb = bufs[current_device_slot()];
+    float *&dx = hb.dx, *&dh = hb.dh, *&dy = hb.dy;
+    int &cap_k = hb.cap_k, &cap_f = hb.cap_f, &cap_n = hb.cap_n;
     if (K > cap_k || FF > cap_f || N > cap_n) {
         cudaFree(dx), cudaFree(dh), cudaFree(dy);
         if (cudaMalloc(&dx, (size_t)K * 4) != cudaSuccess || cudaMalloc(&dh, (size_t)FF * 4) != cudaSuccess ||
@@ -1687,10 +1952,18 @@ static int op_attention_impl(const float* q, const uint16_t* kc, const uint16_t*
     if (head_dim != 64 && head_dim != 128 && head_dim != 256) return TFR_E_UNSUPPORTED;
     if (n_kv > 64) return TFR_E_UNSUPPORTED;
     configure_kernels_once();
-    // scratch for the stand-alone call: partials + counters, grown on demand and kept
-    static float* partial = nullptr;
-    static unsigned int* counters = nullptr;
-    static size_t cap = 0;
+    // scratch for the stand-alone call: partials + counters, grown on demand and kept, one set per device.
+    // All calls on a device share it: calls that overlap on the GPU (different streams or threads) race on it.
+    struct AttnScratch {
+        float* partial = nullptr;
+        unsigned int* counters = nullptr;
+        size_t cap = 0;
+    };
+    static AttnScratch scratch[TFR_MAX_DEVICES];
+    AttnScratch& sc = scratch[current_device_slot()];
+    float*& partial = sc.partial;
+    unsigned int*& counters = sc.counters;
+    size_t& cap = sc.cap;
     AttnArgs a{};
     a.S = attn_splits(sm_count_cached(), n_kv, head_dim);
     const size_t need = (size_t)n_head * a.S * (2 + head_dim) * 4;
@@ -1800,6 +2073,7 @@ extern "C" int tfr_op_attention_noalloc(const float* q, const uint16_t* kc, cons
     int dev = -1, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= TFR_NOALLOC_MAX_DEVICES) return TFR_E_CUDA;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return TFR_E_CUDA;
+    configure_kernels_once();  // function attributes only (shared-memory carve-out): nothing is allocated
     AttnArgs a{};
     a.S = attn_splits(sms, n_kv, head_dim);
     const size_t need = (size_t)n_head * a.S * (2 + head_dim) * sizeof(float);

@@ -431,8 +431,8 @@ __device__ __forceinline__ float q6k_run_dot_f32(const Mat& m, long long f, int 
 // the kernel needs no division: the first `rem` CTAs take quot+1 items.
 struct Share {
     int quot, rem;
-    __device__ __forceinline__ int begin(int c) const { return c * quot + min(c, rem); }
-    __device__ __forceinline__ int count(int c) const { return quot + (c < rem ? 1 : 0); }
+    __host__ __device__ __forceinline__ int begin(int c) const { return c * quot + (c < rem ? c : rem); }
+    __host__ __device__ __forceinline__ int count(int c) const { return quot + (c < rem ? 1 : 0); }
 };
 inline Share make_share(int n, int C) {
     Share s;

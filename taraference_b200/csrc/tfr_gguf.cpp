@@ -53,8 +53,13 @@ struct Value {
     int64_t i = 0;    // signed payload
     double f = 0.0;   // float payload
     std::string s;    // string payload
-    uint64_t count = 0;  // arrays: element count (elements themselves are skipped)
+    uint64_t count = 0;  // arrays: element count
     int item_kind = -1;
+    // array payloads the tokenizer needs (tokenizer/mod.rs:27-106): strings (tokens, merges), floats (scores),
+    // integers (token types).  Other item kinds are parsed to stay in step and dropped.
+    std::vector<std::string> items_s;
+    std::vector<double> items_f;
+    std::vector<int64_t> items_i;
 };
 
 struct Tensor {
@@ -83,9 +88,17 @@ struct Cursor {
         at += sizeof(T);
         return v;
     }
+    const char* malformed = nullptr;  // set with ok = false: a limit of value.rs was exceeded
+    uint64_t bad_len = 0;
     std::string str(const char* ctx) {
-        const uint64_t len = get<uint64_t>(ctx);
+        const uint64_t len = get<uint64_t>("string length");
         if (!ok) return {};
+        if (len > 64ull * 1024 * 1024) {  // value.rs:163-183
+            ok = false;
+            malformed = "string length %llu is unreasonably large";
+            bad_len = len;
+            return {};
+        }
         if (len > n - at) {
             ok = false;
             eof_ctx = ctx;
@@ -93,7 +106,36 @@ struct Cursor {
         }
         std::string s(reinterpret_cast<const char*>(p + at), (size_t)len);
         at += (size_t)len;
+        if (!valid_utf8(s)) {  // String::from_utf8 in read_string
+            ok = false;
+            malformed = "invalid UTF-8 in a string (offset %llu)";
+            bad_len = at - len;
+        }
         return s;
+    }
+    static bool valid_utf8(const std::string& s) {
+        const unsigned char* b = reinterpret_cast<const unsigned char*>(s.data());
+        const size_t m = s.size();
+        for (size_t i = 0; i < m;) {
+            const unsigned c = b[i];
+            int extra;
+            unsigned cp;
+            if (c < 0x80) { i++; continue; }
+            else if ((c & 0xe0) == 0xc0) extra = 1, cp = c & 0x1f;
+            else if ((c & 0xf0) == 0xe0) extra = 2, cp = c & 0x0f;
+            else if ((c & 0xf8) == 0xf0) extra = 3, cp = c & 0x07;
+            else return false;
+            if (i + (size_t)extra >= m) return false;  // truncated sequence
+            for (int k = 1; k <= extra; k++) {
+                if ((b[i + k] & 0xc0) != 0x80) return false;
+                cp = (cp << 6) | (b[i + k] & 0x3f);
+            }
+            if ((extra == 1 && cp < 0x80) || (extra == 2 && cp < 0x800) || (extra == 3 && cp < 0x10000) || cp > 0x10ffff ||
+                (cp >= 0xd800 && cp <= 0xdfff))
+                return false;
+            i += extra + 1;
+        }
+        return true;
     }
 };
 
@@ -143,11 +185,23 @@ bool read_value(Cursor& c, int kind, Value& v, int depth) {
             const uint64_t count = c.get<uint64_t>("array length");
             if (!c.ok) return false;
             if (item > V_F64 || depth > 4) return false;
+            if (count > 10000000ull) {  // value.rs:246-262
+                c.ok = false;
+                c.malformed = "array length %llu is unreasonably large";
+                c.bad_len = count;
+                return false;
+            }
             v.item_kind = (int)item;
             v.count = count;
-            for (uint64_t k = 0; k < count && c.ok; k++) {  // vocabularies etc.: parsed to stay in step, not kept
-                Value skip;
-                if (!read_value(c, (int)item, skip, depth + 1)) return false;
+            for (uint64_t k = 0; k < count && c.ok; k++) {
+                Value it;
+                if (!read_value(c, (int)item, it, depth + 1)) return false;
+                if (depth == 0) {
+                    if (item == V_STRING) v.items_s.push_back(std::move(it.s));
+                    else if (item == V_F32 || item == V_F64) v.items_f.push_back(it.f);
+                    else if (item == V_I8 || item == V_I16 || item == V_I32 || item == V_I64) v.items_i.push_back(it.i);
+                    else if (item != V_ARRAY) v.items_i.push_back((int64_t)it.u);
+                }
             }
             break;
         }
@@ -203,8 +257,16 @@ extern "C" int tfr_gguf_open(const char* path, tfr_gguf** out, char* err, size_t
         tfr_gguf_close(g);
         return rc;
     };
+    auto eof = [&]() {
+        if (c.malformed) {
+            char fmt[96];
+            snprintf(fmt, sizeof fmt, "malformed file: %s", c.malformed);
+            return bad(fmt, (unsigned long long)c.bad_len);
+        }
+        return bad("unexpected end of file in %s", c.eof_ctx);
+    };
     const uint32_t magic = c.get<uint32_t>("magic");
-    if (!c.ok) return bad("unexpected end of file in %s", c.eof_ctx);
+    if (!c.ok) return eof();
     if (magic != 0x46554747u) return bad("bad magic 0x%08x (not a GGUF file)", magic);
     g->version = c.get<uint32_t>("version");
     if (!c.ok) return bad("unexpected end of file in %s", c.eof_ctx);
@@ -216,11 +278,10 @@ extern "C" int tfr_gguf_open(const char* path, tfr_gguf** out, char* err, size_t
     for (uint64_t k = 0; k < n_kv; k++) {
         const std::string key = c.str("metadata key");
         const uint32_t ty = c.get<uint32_t>("metadata value type");
-        if (!c.ok) return bad("unexpected end of file in %s", c.eof_ctx);
+        if (!c.ok) return eof();
         if (ty > V_F64) return bad("unknown metadata value type %u", ty);
         Value v;
-        if (!read_value(c, (int)ty, v, 0))
-            return c.ok ? bad("malformed metadata value for key %s", key.c_str()) : bad("unexpected end of file in %s", c.eof_ctx);
+        if (!read_value(c, (int)ty, v, 0)) return c.ok ? bad("malformed metadata value for key %s", key.c_str()) : eof();
         g->meta[key] = std::move(v);
     }
     g->tensors.reserve((size_t)n_tensors);
@@ -228,7 +289,7 @@ extern "C" int tfr_gguf_open(const char* path, tfr_gguf** out, char* err, size_t
         Tensor t;
         t.name = c.str("tensor name");
         const uint32_t nd = c.get<uint32_t>("tensor n_dims");
-        if (!c.ok) return bad("unexpected end of file in %s", c.eof_ctx);
+        if (!c.ok) return eof();
         if (nd > 4) return bad("tensor %s: n_dims=%u > 4", t.name.c_str(), nd);
         t.n_dims = (int)nd;
         uint64_t elems = 1;
@@ -239,10 +300,12 @@ extern "C" int tfr_gguf_open(const char* path, tfr_gguf** out, char* err, size_t
         }
         t.type = c.get<uint32_t>("tensor type");
         t.offset = c.get<uint64_t>("tensor offset");
-        if (!c.ok) return bad("unexpected end of file in %s", c.eof_ctx);
+        if (!c.ok) return eof();
         const TypeInfo* ti = type_info(t.type);
         if (!ti) return bad("unknown tensor type %u (tensor %s)", t.type, t.name.c_str());
-        t.nbytes = elems == UINT64_MAX ? UINT64_MAX : elems / ti->block * ti->bytes;  // types.rs: nbytes()
+        const uint64_t blocks = elems / (uint64_t)ti->block;
+        t.nbytes = (elems == UINT64_MAX || blocks > UINT64_MAX / (uint64_t)ti->bytes) ? UINT64_MAX
+                                                                                      : blocks * (uint64_t)ti->bytes;  // types.rs: nbytes()
         g->index[t.name] = g->tensors.size();
         g->tensors.push_back(std::move(t));
     }
@@ -314,6 +377,25 @@ extern "C" int64_t tfr_gguf_meta_array_len(const tfr_gguf* g, const char* key) {
     const Value* v = g && key ? find(g, key) : nullptr;
     return v && v->kind == V_ARRAY ? (int64_t)v->count : -1;
 }
+extern "C" int tfr_gguf_meta_array_str(const tfr_gguf* g, const char* key, int64_t i, const char** out, uint64_t* len) {
+    const Value* v = g && key ? find(g, key) : nullptr;
+    if (!v || v->kind != V_ARRAY || v->item_kind != V_STRING || i < 0 || (uint64_t)i >= v->items_s.size()) return TFR_E_INVALID;
+    if (out) *out = v->items_s[(size_t)i].data();
+    if (len) *len = v->items_s[(size_t)i].size();
+    return TFR_OK;
+}
+extern "C" int tfr_gguf_meta_array_f32(const tfr_gguf* g, const char* key, int64_t i, float* out) {
+    const Value* v = g && key ? find(g, key) : nullptr;
+    if (!v || v->kind != V_ARRAY || i < 0 || (uint64_t)i >= v->items_f.size()) return TFR_E_INVALID;
+    if (out) *out = (float)v->items_f[(size_t)i];
+    return TFR_OK;
+}
+extern "C" int tfr_gguf_meta_array_i64(const tfr_gguf* g, const char* key, int64_t i, int64_t* out) {
+    const Value* v = g && key ? find(g, key) : nullptr;
+    if (!v || v->kind != V_ARRAY || i < 0 || (uint64_t)i >= v->items_i.size()) return TFR_E_INVALID;
+    if (out) *out = v->items_i[(size_t)i];
+    return TFR_OK;
+}
 
 // ModelConfig::from_gguf, crates/core/src/config.rs:107-264.
 extern "C" int tfr_gguf_model_config(const tfr_gguf* g, tfr_model_config* c, char* err, size_t err_cap) {
@@ -322,6 +404,18 @@ extern "C" int tfr_gguf_model_config(const tfr_gguf* g, tfr_model_config* c, cha
     const Value* av = find(g, "general.architecture");
     if (!av || av->kind != V_STRING) return set_err(err, err_cap, TFR_E_INVALID, "missing general.architecture");
     const std::string arch = av->s;
+    // Families whose layer schedule differs from the ones built here are refused instead of decoded wrongly:
+    // smollm3 skips RoPE on every fourth layer (config.rs:150, layer.rs:417-418); mixture-of-experts models
+    // (config.rs is_moe, backend.rs:19-27) run on kernels outside this library.
+    if (arch == "smollm3") return set_err(err, err_cap, TFR_E_UNSUPPORTED, "architecture smollm3 is not supported (no-RoPE layers)");
+    if (arch == "tara_moe_141" || arch.find("moe") != std::string::npos)
+        return set_err(err, err_cap, TFR_E_UNSUPPORTED, "architecture %s is not supported (mixture of experts)", arch.c_str());
+    {
+        uint64_t experts = 0;
+        if (as_u64(find(g, (arch + ".expert_count").c_str()), experts) && experts > 0)
+            return set_err(err, err_cap, TFR_E_UNSUPPORTED, "architecture %s with %llu experts is not supported (mixture of experts)",
+                           arch.c_str(), (unsigned long long)experts);
+    }
     const std::string key_arch = (arch == "llama" || arch == "llama2" || arch == "llama3") ? "llama" : arch;
     auto k = [&](const char* s) { return key_arch + "." + s; };
     auto get = [&](const char* s, uint64_t& v) { return as_u64(find(g, k(s).c_str()), v); };

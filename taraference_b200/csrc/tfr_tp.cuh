@@ -16,9 +16,11 @@
 // all ranks: the replicated residual stream stays bit-identical) and applies the residual.  No
 // grid-wide barrier and no second launch; a CTA only ever waits for its namesakes on the peers.
 //
-// Buffers alternate with the parity of a monotonically increasing epoch, and a mark is only valid
-// for its own epoch.  Rank A can only reach all-reduce k+2 (same parity as k) after every peer has
-// delivered k+1, i.e. after the peers' kernel k has completed in stream order, so a slot is never
+// The data buffers alternate with the parity of the all-reduce's index inside the token (a token has an
+// even number of them, 2 per layer, so consecutive all-reduces always use different buffers, across token
+// boundaries too, with or without a vocabulary head in between); a mark is only valid for its own
+// monotonically increasing epoch.  Rank A can only reach all-reduce k+2 (the buffer of k) after every peer
+// has delivered k+1, i.e. after the peers' kernel k has completed in stream order, so a slot is never
 // overwritten while it is being read.  Every wait is bounded: on expiry the kernel records an
 // error, ends the burst and returns.
 #pragma once
@@ -93,7 +95,7 @@ struct EpiAllReduce {
     __device__ __forceinline__ void set_residual(const float*, int) {}
     __device__ __forceinline__ uint4* slot(int dst_rank, int src_rank) const {
         return reinterpret_cast<uint4*>(c.base[dst_rank] + c.lay.data_off) +
-               ((size_t)(epoch & 1u) * TP_MAX + src_rank) * (c.lay.k_max >> 1);
+               ((size_t)(op_index & 1) * TP_MAX + src_rank) * (c.lay.k_max >> 1);
     }
     __device__ __forceinline__ void apply(int p, float v0, float v1) {
         for (int r = 0; r < c.tp; r++) st_sys_v4(slot(r, c.rank) + p, __float_as_uint(v0), epoch, __float_as_uint(v1), epoch);

@@ -113,6 +113,26 @@ class GgufFile:
     def meta_array_len(self, key: str) -> int:
         return int(_lib.lib().tfr_gguf_meta_array_len(self._h, key.encode()))
 
+    def meta_array(self, key: str) -> list | None:
+        """Items of a metadata array: bytes objects for string arrays (tokenizer.ggml.tokens / .merges), floats
+        (.scores) or integers (.token_type); None when the key is missing or holds another item kind."""
+        n = self.meta_array_len(key)
+        if n < 0:
+            return None
+        l, k = _lib.lib(), key.encode()
+        out: list = []
+        sp, sl, fv, iv = C.c_char_p(), C.c_uint64(), C.c_float(), C.c_int64()
+        for i in range(n):
+            if l.tfr_gguf_meta_array_str(self._h, k, i, C.byref(sp), C.byref(sl)) == 0:
+                out.append(C.string_at(sp, sl.value))
+            elif l.tfr_gguf_meta_array_f32(self._h, k, i, C.byref(fv)) == 0:
+                out.append(float(fv.value))
+            elif l.tfr_gguf_meta_array_i64(self._h, k, i, C.byref(iv)) == 0:
+                out.append(int(iv.value))
+            else:
+                return None
+        return out
+
     def model_config(self) -> ModelConfig:
         c = ModelConfig()
         err = C.create_string_buffer(512)
@@ -241,6 +261,22 @@ class CudaModel:
 
     def graph_active(self) -> bool:
         return bool(_lib.lib().tfr_graph_active(self._h))
+
+    PATH_AUTO, PATH_CHAINED, PATH_LOOP = 0, 1, 2
+
+    def set_decode_path(self, path: int) -> None:
+        """decode.rs:87-240 (backend choice): 0 = persistent loop when the model qualifies, 1 = chained kernels
+        (one CUDA graph per token), 2 = persistent loop or an error."""
+        self._check(_lib.lib().tfr_set_decode_path(self._h, int(path)))
+
+    def decode_path(self) -> int:
+        """The schedule the next forward call takes: 1 chained kernels, 2 persistent loop."""
+        return int(_lib.lib().tfr_decode_path(self._h))
+
+    def set_loop_timeline(self, device_buffer, step: int, points: int) -> None:
+        """Test aid: per-CTA nanosecond timestamps of decode step `step` of the persistent loop into a device
+        buffer of points * sm_count uint64 (None switches it off)."""
+        self._check(_lib.lib().tfr_debug_set_loop_timeline(self._h, _ptr(device_buffer), int(step), int(points)))
 
     def forward_greedy(self, tokens, kv: CudaKv) -> int:
         t = np.ascontiguousarray(tokens, dtype=np.uint32)

@@ -157,6 +157,7 @@ def test_burst_equals_token_by_token_and_graph_equals_eager(E):
     cfg = SMALL
     tens = S.make_dense_model(cfg, seed=5)
     m = E.CudaModel.load_with(cfg, tens)
+    m.set_decode_path(m.PATH_CHAINED)  # graphs belong to the chained-kernel schedule
     kv = m.alloc_kv(128)
     first = m.forward_greedy([11, 12, 13], kv)
     burst = m.decode_burst(first, 24, kv)
@@ -325,6 +326,7 @@ def test_vocab_shortlist_head_and_extra_row(E, oracle):
     cfg = dict(S.TINY_DENSE, n_vocab=2304)
     tens = S.make_dense_model(cfg, seed=11)
     full = E.CudaModel.load_with(cfg, tens)
+    full.set_decode_path(full.PATH_CHAINED)  # a shortlisted head runs on the chained kernels: same schedule, same bits
     kvf = full.alloc_kv(32)
     prompt = [7, 1900, 42, 1033]
     full.forward_greedy(prompt, kvf)

@@ -135,6 +135,9 @@ def test_missing_peer_ends_in_an_error_not_a_hang(cuda_lib):
     kv = m.alloc_kv(16)
     with pytest.raises(E.TfrError, match="not connected"):
         m.forward_greedy([1], kv)
+    # leaving the NCCL comparison mode needs the peers' buffers: refused while they were never connected
+    with pytest.raises(E.TfrError, match="never connected"):
+        m.tp_use_nccl(None)
     fake_peer = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
     m.tp_attach_pointers([m.tp_local_pointer(), fake_peer.data_ptr()])
     t0 = time.time()

@@ -37,17 +37,19 @@ def test_noalloc_attention_matches_regular_entry_point_twice(cuda_lib):
 
 
 def test_noalloc_attention_refuses_oversized_shapes(cuda_lib):
+    """The built-in array is 2 MiB: 512 query heads of 256 need 512 x 8 splits x 258 floats = 4.2 MB of partials and
+    are refused; so are more than 64 KV heads (the arrival counters take the first 2048 bytes)."""
     assert torch.cuda.is_available(), "GPU tests need a CUDA device"
     from taraference_b200 import engine as E
     rng = np.random.default_rng(8)
-    # 64 query heads on one KV head group of 8 each would be fine; 8 x 8 heads of 256 on 1 KV group exceed 2 MiB
-    H, Hkv, hd, T = 8, 1, 256, 16
-    q, kc, vc = _case(rng, H, Hkv, hd, T)
-    out = torch.zeros(H * hd, device="cuda")
-    sms = torch.cuda.get_device_properties(0).multi_processor_count
-    need = H * (sms // Hkv) * (2 + hd) * 4
-    if need > (2 << 20) - 256:
+    for H, Hkv, hd in [(512, 64, 256), (65, 65, 64)]:
+        q, kc, vc = _case(rng, H, Hkv, hd, 4)
+        out = torch.zeros(H * hd, device="cuda")
         with pytest.raises(E.TfrError):
-            E.op_attention_noalloc(q, kc, vc, out, H, Hkv, hd, T - 1)
-    else:
-        E.op_attention_noalloc(q, kc, vc, out, H, Hkv, hd, T - 1)
+            E.op_attention_noalloc(q, kc, vc, out, H, Hkv, hd, 3)
+    # a shape that fits still works after the refusals
+    q, kc, vc = _case(rng, 8, 1, 256, 16)
+    out = torch.full((8 * 256,), float("nan"), device="cuda")
+    E.op_attention_noalloc(q, kc, vc, out, 8, 1, 256, 15)
+    torch.cuda.synchronize()
+    assert bool(torch.isfinite(out).all())
