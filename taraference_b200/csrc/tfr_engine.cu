@@ -165,7 +165,8 @@ struct tfr_engine {
     LoopLayer* loop_layers = nullptr;
     unsigned int* loop_bar = nullptr;
     unsigned long long* loop_best = nullptr;
-    float* loop_partial = nullptr;
+    float* loop_vec = nullptr;  // the vectors the loop's phases hand to one another, one allocation
+    size_t loop_vec_n = 0;
     size_t loop_smem = 0;
     int loop_grid = 0;
     int* loop_blob = nullptr;
@@ -543,7 +544,7 @@ extern "C" void tfr_destroy(tfr_engine* e) {
     for (auto& kv : e->vecs) cudaFree(kv.second.dev);
     for (auto& L : e->layers) cudaFree(L.bias_qkv);
     void* ws[] = {e->x, e->q, e->attn, e->h, e->logits, e->partial, e->counters, e->st, e->out_tokens, e->prompt,
-                  e->layer_taps, e->proj, e->qgate, e->loop_layers, e->loop_bar, e->loop_best, e->loop_partial, e->loop_blob, e->loop_head_tasks};
+                  e->layer_taps, e->proj, e->qgate, e->loop_layers, e->loop_bar, e->loop_best, e->loop_vec, e->loop_blob, e->loop_head_tasks};
     for (void* p : ws) cudaFree(p);
     if (e->st_host) cudaFreeHost(e->st_host);
     if (e->out_host) cudaFreeHost(e->out_host);
@@ -839,7 +840,7 @@ static int loop_setup(tfr_engine* e) {
     if (!q46(e->head) || !q46(e->token_embd)) return no("head / embedding type");
     for (const LayerW& L : e->layers)
         if (!q46(L.wo) || !q46(L.down)) return no("attn_output / ffn_down type");
-    int lpb[5] = {0, 0, 0, 0, 0};
+    int lpb[5] = {0, 0, 0, 0, 0};  // forced lanes per block of Q/K/V, o-proj, gate/up, down, head (0: pick)
     if (const char* env = getenv("TFR_LOOP_LPB")) sscanf(env, "%d,%d,%d,%d,%d", &lpb[0], &lpb[1], &lpb[2], &lpb[3], &lpb[4]);
     LoopArgs& a = e->loop;
     a = LoopArgs{};
@@ -885,9 +886,11 @@ static int loop_setup(tfr_engine* e) {
     size_t work = act_b + xf_b + (size_t)pbuf * 4;
     const size_t attn_need = std::max(loop_attn_smem(hd), (size_t)(2 * ((G / P.n_kv + 3) & ~3) + LOOP_CT) * 4);
     if (work < attn_need) work = attn_need;
-    a.off_blob = 1536;
+    a.off_blob = LOOP_CTX_OFFSET + 256;  // barriers, control words, reduction scratch, then the context struct
     a.off_layers = (int)((a.off_blob + (size_t)plan.blob_stride * 4 + 15) & ~(size_t)15);
-    a.off_act = (int)((a.off_layers + (size_t)c.n_layer * sizeof(LoopLayer) + 127) & ~(size_t)127);
+    a.sh_x = make_share((K + 1) / 2, G);
+    a.off_own = (int)((a.off_layers + (size_t)c.n_layer * sizeof(LoopLayer) + 15) & ~(size_t)15);
+    a.off_act = (int)((a.off_own + (size_t)4 * 2 * (a.sh_x.quot + 1) + 127) & ~(size_t)127);
     a.off_xf = a.off_act + (int)act_b;
     a.off_pbuf = a.off_xf + (int)xf_b;
     a.off_ring = (int)((a.off_act + work + 127) & ~(size_t)127);
@@ -933,18 +936,32 @@ static int loop_setup(tfr_engine* e) {
     a.attn_inline_max = 8;
     if (const char* env = getenv("TFR_LOOP_ATTN_KEYS")) a.attn_min_keys = std::max(8, atoi(env));
     if (const char* env = getenv("TFR_LOOP_ATTN_INLINE")) a.attn_inline_max = std::max(1, atoi(env));
-    CU(e, cudaMalloc(&e->loop_partial, (size_t)P.n_head * a.attn_smax * (4 + hd) * 4));
-    CU(e, cudaMalloc(&e->loop_bar, 8 * LOOP_BAR_STRIDE * 4));
+    if (a.attn_inline_max > LOOP_INLINE_MAX) a.attn_inline_max = LOOP_INLINE_MAX;
+    {
+        // vectors handed between phases: q, attention output, SiLU*mul output, split partials
+        const size_t n_q = (size_t)P.nq, n_h = (size_t)P.ff;
+        const size_t n_p = (size_t)P.n_head * a.attn_smax * (4 + hd);
+        auto up = [](size_t n) { return (n + 31) & ~(size_t)31; };
+        e->loop_vec_n = 2 * up(n_q) + up(n_h) + up(n_p);
+        CU(e, cudaMalloc(&e->loop_vec, e->loop_vec_n * 4));
+        float* p = e->loop_vec;
+        a.q = p, p += up(n_q);
+        a.att = p, p += up(n_q);
+        a.h = p, p += up(n_h);
+        a.pc = p;
+    }
+    CU(e, cudaMalloc(&e->loop_bar, 8 * LOOP_BAR_STRIDE * 4));  // grid-barrier counters
     CU(e, cudaMalloc(&e->loop_best, 4 * 8));
     a.layers = e->loop_layers;
     a.n_layer = c.n_layer;
     a.K = K, a.FF = P.ff, a.nq = P.nq, a.nkv = P.nkv, a.hd = hd, a.n_head = P.n_head, a.n_kv = P.n_kv, a.V = V;
+    a.rep = P.n_head / P.n_kv;
+    a.hd_shift = hd == 64 ? 6 : (hd == 128 ? 7 : 8);
     a.eps = c.rms_eps, a.theta = c.rope_theta, a.attn_scale = 1.0f / sqrtf((float)hd);  // forward.rs:389
     a.embed = e->token_embd->m;
     a.head = e->head->m.data;
     a.out_norm = e->output_norm;
-    a.x = e->x, a.q = e->q, a.attn = e->attn, a.h = e->h, a.logits = e->logits;
-    a.partial = e->loop_partial;
+    a.x = e->x, a.logits = e->logits;
     a.bar = e->loop_bar;
     a.best = e->loop_best;
     a.st = e->st;

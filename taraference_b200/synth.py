@@ -249,6 +249,21 @@ def make_model(cfg: dict, seed: int = 0, sigma: float = 0.02) -> dict:
     return tensors
 
 
+def random_model(cfg: dict, seed: int = 0, sigma: float = 0.02) -> dict:
+    """Whole model on the host in the layout of make_model, but every matrix is made of random K-quant blocks
+    (random_q4_k / random_q6_k) instead of quantised Gaussian weights: full-size models in seconds.  The time a
+    CPU pass over the model takes does not depend on the values, so this is what the CPU baseline runs on."""
+    rng = np.random.default_rng(seed)
+    tensors: dict = {}
+    for name, t, K, N in tensor_plan(cfg):
+        n_blocks = N * (K // 256)
+        blocks = random_q4_k(rng, n_blocks) if t == Q4_K else random_q6_k(rng, n_blocks)
+        tensors[name] = (t, K, N, np.ascontiguousarray(blocks.reshape(-1)))
+    for name, n, kind in vector_plan(cfg):
+        tensors[name] = make_vector(kind, n, rng, sigma)
+    return tensors
+
+
 make_dense_model = make_model
 
 
