@@ -203,6 +203,14 @@ int tfr_graph_active(const tfr_engine* e);
  * path 2 fails with TFR_E_UNSUPPORTED when it does not.  tfr_decode_path reports which one the next call takes. */
 int tfr_set_decode_path(tfr_engine* e, int path);
 int tfr_decode_path(const tfr_engine* e);
+
+/* Prompts and verification batches go through the engine in chunks of up to `tokens` tokens, each chunk reading
+ * the weights once (CudaModel::forward_chunk, crates/core/src/cuda/forward.rs:54-65, 360-407; MAX_BATCH,
+ * MAX_VERIFY_TOKENS, crates/core/src/cuda/types.rs:7-9).  tokens = 0 feeds every token of a prompt as a decode step;
+ * values above the engine's chunk capacity are clamped.  tfr_prefill_chunk returns the size in effect, 0 for models
+ * the chunk kernels do not cover (hybrid layers, tensor parallelism), which keep the step-by-step route. */
+int tfr_set_prefill_chunk(tfr_engine* e, int tokens);
+int tfr_prefill_chunk(const tfr_engine* e);
 /* Kernel launches issued by this engine so far (graph replays count their kernel nodes). */
 int64_t tfr_launch_count(const tfr_engine* e);
 /* Device time of the last tfr_decode_burst / tfr_forward_greedy in milliseconds (CUDA events

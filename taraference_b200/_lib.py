@@ -90,6 +90,8 @@ def lib() -> C.CDLL:
         "tfr_graph_active": (i32, [vp]),
         "tfr_set_decode_path": (i32, [vp, i32]),
         "tfr_decode_path": (i32, [vp]),
+        "tfr_set_prefill_chunk": (i32, [vp, i32]),
+        "tfr_prefill_chunk": (i32, [vp]),
         "tfr_debug_set_loop_timeline": (i32, [vp, vp, i32, i32]),
         "tfr_launch_count": (i64, [vp]),
         "tfr_last_device_ms": (f32, [vp]),

@@ -27,6 +27,7 @@
 
 #include "../../include/tarafer_b200.h"
 #include "tfr_kernels.cuh"
+#include "tfr_chunk.cuh"
 #include "tfr_loop.cuh"
 
 using namespace tfr;
@@ -173,6 +174,13 @@ struct tfr_engine {
     uint4* loop_head_tasks = nullptr;
     unsigned long long* loop_prof = nullptr;
     int loop_prof_step = -1, loop_prof_points = 0;
+    // multi-token chunks (tfr_chunk.cuh): prompts and verification batches
+    int chunk_tokens = CHUNK_MAX_TOKENS;  // 0: every token of a prompt is a decode step
+    bool chunk_ok = false;
+    std::string chunk_why;
+    float *cx = nullptr, *cq = nullptr, *cattn = nullptr, *ch = nullptr, *cxn = nullptr, *clogits = nullptr;
+    unsigned char* cact = nullptr;
+    size_t cact_stride = 0;
 };
 
 struct tfr_kv {
@@ -266,6 +274,13 @@ static void configure_kernels_once() {
     configure_kernel(k_gemv<BlockQ6, EpiLogits>, true);
     configure_kernel(k_int_dots<BlockQ4>, true);
     configure_kernel(k_int_dots<BlockQ6>, true);
+    configure_kernel(k_gemm_q8<BlockQ4>, true);
+    configure_kernel(k_gemm_q8<BlockQ6>, true);
+    configure_kernel(k_gemm_q8<BlockQ8>, true);
+    configure_kernel(k_attn_chunk<64>, true);
+    configure_kernel(k_attn_chunk<128>, true);
+    configure_kernel(k_attn_chunk<256>, true);
+    configure_kernel(k_prep_rows, false);
     configure_kernel(k_attn_decode<64>, false);
     configure_kernel(k_attn_decode<128>, false);
     configure_kernel(k_attn_decode<256>, false);
@@ -544,7 +559,7 @@ extern "C" void tfr_destroy(tfr_engine* e) {
     for (auto& kv : e->vecs) cudaFree(kv.second.dev);
     for (auto& L : e->layers) cudaFree(L.bias_qkv);
     void* ws[] = {e->x, e->q, e->attn, e->h, e->logits, e->partial, e->counters, e->st, e->out_tokens, e->prompt,
-                  e->layer_taps, e->proj, e->qgate, e->loop_layers, e->loop_bar, e->loop_best, e->loop_vec, e->loop_blob, e->loop_head_tasks};
+                  e->layer_taps, e->proj, e->qgate, e->loop_layers, e->loop_bar, e->loop_best, e->loop_vec, e->cx, e->cq, e->cattn, e->ch, e->cxn, e->clogits, e->cact, e->loop_blob, e->loop_head_tasks};
     for (void* p : ws) cudaFree(p);
     if (e->st_host) cudaFreeHost(e->st_host);
     if (e->out_host) cudaFreeHost(e->out_host);
@@ -996,6 +1011,8 @@ static int run_loop(tfr_engine* e, const tfr_kv* kv, int n_headless) {
     return TFR_OK;
 }
 
+static void chunk_setup(tfr_engine* e);
+
 extern "C" int tfr_finalize_load(tfr_engine* e) {
     if (!e || !e->has_cfg) return TFR_E_INVALID;
     if (e->finalized) return TFR_OK;
@@ -1139,6 +1156,7 @@ extern "C" int tfr_finalize_load(tfr_engine* e) {
     CU(e, cudaStreamSynchronize(e->stream));
     rc = loop_setup(e);
     if (rc) return rc;
+    chunk_setup(e);
     if (e->decode_path == 2 && !e->loop_ok) return fail(e, TFR_E_UNSUPPORTED, "persistent decode loop unavailable: %s", e->loop_why.c_str());
     e->finalized = true;
     return TFR_OK;
@@ -1513,6 +1531,149 @@ static int run_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
     return TFR_OK;
 }
 
+
+// ------------------------------------------------------------------ multi-token chunks
+
+// Models the chunk kernels cover; everything else keeps feeding prompts by decode steps.
+static void chunk_setup(tfr_engine* e) {
+    const tfr_model_config& c = e->cfg;
+    e->chunk_ok = false;
+    auto no = [&](const char* why) { e->chunk_why = why; };
+    if (c.hybrid) return no("hybrid (Gated-DeltaNet) layers");
+    if (e->plan.tp > 1) return no("tensor parallelism");
+    auto q468 = [](const tfr_mat* m) { return m->m.type == TFR_Q4_K || m->m.type == TFR_Q6_K || m->m.type == TFR_Q8_0; };
+    if (!q468(e->head)) return no("head type");
+    for (const LayerW& L : e->layers) {
+        if (L.kind != LAYER_DENSE) return no("layer kind");
+        if (L.wq->m.type != TFR_Q4_K || L.wk->m.type != TFR_Q4_K || L.gate->m.type != TFR_Q4_K || L.up->m.type != TFR_Q4_K)
+            return no("attn_q / attn_k / ffn_gate / ffn_up type");
+        if (!q468(L.wo) || !q468(L.down)) return no("attn_output / ffn_down type");
+    }
+    e->chunk_ok = true;
+    e->chunk_why.clear();
+}
+
+static int chunk_buffers(tfr_engine* e) {
+    if (e->cx) return TFR_OK;
+    const TpPlan& P = e->plan;
+    const int K = e->cfg.n_embd, M = CHUNK_MAX_TOKENS;
+    const int kmax = std::max(std::max(K, P.ff), P.attn_width);
+    e->cact_stride = (act_smem_bytes(kmax, false, false) + 255) & ~(size_t)255;
+    CU(e, cudaMalloc(&e->cx, (size_t)M * K * 4));
+    CU(e, cudaMalloc(&e->cxn, (size_t)M * K * 4));
+    CU(e, cudaMalloc(&e->cq, (size_t)M * P.nq * 4));
+    CU(e, cudaMalloc(&e->cattn, (size_t)M * P.attn_width * 4));
+    CU(e, cudaMalloc(&e->ch, (size_t)M * P.ff * 4));
+    CU(e, cudaMalloc(&e->cact, (size_t)M * e->cact_stride));
+    CU(e, cudaMalloc(&e->clogits, (size_t)CHUNK_VERIFY_MAX * e->head->m.N * 4));
+    return TFR_OK;
+}
+
+static cudaError_t launch_gemm_typed(cudaStream_t s, int grid, int type, const unsigned char* act, size_t stride, const float* xn, int M,
+                                     const RowJob& ja, const RowJob& jb, const F32Seg& fseg, const ChunkEpi& epi, int K) {
+    if (type == TFR_Q4_K) return launch_gemm<BlockQ4>(s, grid, act, stride, xn, M, ja, jb, fseg, epi, K);
+    if (type == TFR_Q8_0) return launch_gemm<BlockQ8>(s, grid, act, stride, xn, M, ja, jb, fseg, epi, K);
+    return launch_gemm<BlockQ6>(s, grid, act, stride, xn, M, ja, jb, fseg, epi, K);
+}
+
+// M tokens (device ids at tok) at positions pos0 .. pos0 + M - 1 through all layers: their K / V rows land in the
+// cache and e->cx holds their residual streams.  all_rows: also the greedy token after every position, to
+// e->out_tokens[0 .. M).  forward.rs:360-407 (forward_chunk), 292-358 (logits_for_rows).
+static int forward_chunk(tfr_engine* e, const tfr_kv* kv, const int* tok, int M, int pos0, bool all_rows) {
+    const tfr_model_config& c = e->cfg;
+    const TpPlan& P = e->plan;
+    const int K = c.n_embd, hd = c.head_dim, nq = P.nq, nkv = P.nkv, FF = P.ff, V = e->head->m.N;
+    const int cap = e->prop.multiProcessorCount;
+    cudaStream_t s = e->stream;
+    int n = 0;
+    auto prep = [&](const float* x, int ldx, int width, const float* normw, float* xn) -> cudaError_t {
+        PrepRowsArgs a{x, ldx, width, normw, c.rms_eps, e->cact, e->cact_stride, xn};
+        const size_t smem = normw ? (xs_floats(width) + 272) * sizeof(float) : 0;
+        n++;
+        return launch_pdl(k_prep_rows, dim3(M), dim3(GEMV_THREADS), smem, s, a);
+    };
+    auto store_epi = [&](float* out, int ldo, int rows, int use_res) {
+        ChunkEpi ep{};
+        ep.kind = CEPI_STORE;
+        ep.out = out, ep.ldo = ldo, ep.n_rows = rows, ep.use_res = use_res;
+        return ep;
+    };
+    k_embed_rows<<<M, 256, 0, s>>>(e->token_embd->m, tok, K, e->cx, e->st);
+    if (cudaGetLastError() != cudaSuccess) return -1;
+    n++;
+    for (int li = 0; li < c.n_layer; li++) {
+        const LayerW& L = e->layers[li];
+        // 1. RMSNorm + Q8, Q/K/V (+bias) + RoPE + f16 KV rows
+        if (prep(e->cx, K, K, L.attn_norm, e->cxn) != cudaSuccess) return -1;
+        {
+            const RowJob jq = make_job(L.wq->m, 2, cap, 0), jk = make_job(L.wk->m, 2, cap, nq / 2);
+            F32Seg fseg{};
+            fseg.m = L.wv->m;
+            fseg.sh = make_share(nkv / 2, cap);
+            fseg.id_base = (nq + nkv) / 2;
+            ChunkEpi ep{};
+            ep.kind = CEPI_QKV;
+            ep.out = e->cq, ep.ldo = nq, ep.bias = L.bias_qkv;
+            ep.kc = kv_k(kv, li), ep.vc = kv_v(kv, li);
+            ep.nq = nq, ep.nk = nkv, ep.hd = hd, ep.kvdim = nkv, ep.pos0 = pos0, ep.theta = c.rope_theta;
+            if (launch_gemm<BlockQ4>(s, cap, e->cact, e->cact_stride, e->cxn, M, jq, jk, fseg, ep, K) != cudaSuccess) return -1;
+            n++;
+        }
+        // 2. causal attention over the cache (rows of this chunk included)
+        {
+            AttnChunkArgs a{};
+            a.q = e->cq, a.kc = kv_k(kv, li), a.vc = kv_v(kv, li), a.out = e->cattn;
+            a.M = M, a.n_head = P.n_head, a.n_kv = P.n_kv, a.pos0 = pos0, a.kvdim = nkv, a.ldq = nq;
+            a.scale = 1.0f / sqrtf((float)hd);  // forward.rs:389
+            const int rep = P.n_head / P.n_kv;
+            a.QT = std::max(1, ATTC_ROWS_MAX / rep);
+            const dim3 grid(P.n_kv, (M + a.QT - 1) / a.QT);
+            const size_t smem = attn_chunk_smem(hd);
+            cudaError_t r = hd == 64    ? launch_pdl(k_attn_chunk<64>, grid, dim3(ATTC_THREADS), smem, s, a)
+                            : hd == 128 ? launch_pdl(k_attn_chunk<128>, grid, dim3(ATTC_THREADS), smem, s, a)
+                                        : launch_pdl(k_attn_chunk<256>, grid, dim3(ATTC_THREADS), smem, s, a);
+            if (r != cudaSuccess) return -1;
+            n++;
+        }
+        // 3. Q8 + o-proj + residual
+        if (prep(e->cattn, P.attn_width, P.attn_width, nullptr, nullptr) != cudaSuccess) return -1;
+        if (launch_gemm_typed(s, cap, L.wo->m.type, e->cact, e->cact_stride, nullptr, M, make_job(L.wo->m, 2, cap), RowJob{}, F32Seg{},
+                              store_epi(e->cx, K, K, 2), P.attn_width) != cudaSuccess)
+            return -1;
+        n++;
+        // 4. RMSNorm + Q8 + gate/up + SiLU*mul
+        if (prep(e->cx, K, K, L.ffn_norm, nullptr) != cudaSuccess) return -1;
+        {
+            ChunkEpi ep{};
+            ep.kind = CEPI_SILU;
+            ep.out = e->ch, ep.ldo = FF;
+            if (launch_gemm<BlockQ4>(s, cap, e->cact, e->cact_stride, nullptr, M, make_job(L.gate->m, 1, cap), make_job(L.up->m, 1, cap),
+                                     F32Seg{}, ep, K) != cudaSuccess)
+                return -1;
+            n++;
+        }
+        // 5. Q8 + down + residual
+        if (prep(e->ch, FF, FF, nullptr, nullptr) != cudaSuccess) return -1;
+        if (launch_gemm_typed(s, cap, L.down->m.type, e->cact, e->cact_stride, nullptr, M, make_job(L.down->m, 2, cap), RowJob{}, F32Seg{},
+                              store_epi(e->cx, K, K, 2), FF) != cudaSuccess)
+            return -1;
+        n++;
+    }
+    if (all_rows) {
+        if (prep(e->cx, K, K, e->output_norm, nullptr) != cudaSuccess) return -1;
+        if (launch_gemm_typed(s, cap, e->head->m.type, e->cact, e->cact_stride, nullptr, M, make_job(e->head->m, 2, cap), RowJob{},
+                              F32Seg{}, store_epi(e->clogits, V, V, 0), K) != cudaSuccess)
+            return -1;
+        k_argmax_rows<<<M, 1024, 0, s>>>(e->clogits, V, e->out_tokens);
+        if (cudaGetLastError() != cudaSuccess) return -1;
+        // tfr_current_logits reports the last position's row
+        if (cudaMemcpyAsync(e->logits, e->clogits + (size_t)(M - 1) * V, (size_t)V * 4, cudaMemcpyDeviceToDevice, s) != cudaSuccess) return -1;
+        n += 2;
+    }
+    e->launches += n;
+    return TFR_OK;
+}
+
 static int begin_state(tfr_engine* e, const tfr_kv* kv, int token, int pos, int max_steps, int max_seq, const uint32_t* stops,
                        int n_stop, int force_prompt = 0) {
     int* a = e->args_host;
@@ -1562,12 +1723,26 @@ extern "C" int tfr_forward_greedy(tfr_engine* e, tfr_kv* kv, const uint32_t* tok
         if (rc) return rc;
     }
     CU(e, cudaMemcpyAsync(e->prompt, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, e->stream));
-    int rc = begin_state(e, kv, (int)tokens[0], kv->len, 1, kv->max_seq + 1, nullptr, 0);
+    // all but the last token go through the chunk kernels (weights read once per chunk); the last is a decode step
+    const bool chunked = !loop && e->chunk_ok && e->chunk_tokens > 0 && n > 1;
+    int rc = TFR_OK;
+    if (chunked) rc = chunk_buffers(e);
+    if (rc) return rc;
+    rc = begin_state(e, kv, (int)tokens[chunked ? n - 1 : 0], kv->len + (chunked ? n - 1 : 0), 1, kv->max_seq + 1, nullptr, 0);
     if (rc) return rc;
     CU(e, cudaEventRecord(e->ev0, e->stream));
-    if (loop) rc = run_loop(e, kv, n - 1);
-    else
+    if (loop) {
+        rc = run_loop(e, kv, n - 1);
+    } else if (chunked) {
+        for (int i = 0; i < n - 1 && !rc; i += e->chunk_tokens) {
+            const int M = std::min(e->chunk_tokens, n - 1 - i);
+            if (forward_chunk(e, kv, e->prompt + i, M, kv->len + i, false) != TFR_OK)
+                rc = fail(e, TFR_E_CUDA, "chunk kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        }
+        if (!rc) rc = run_token(e, kv, true);
+    } else {
         for (int i = 0; i < n && !rc; i++) rc = run_token(e, kv, i == n - 1);
+    }
     if (rc) return rc;
     CU(e, cudaEventRecord(e->ev1, e->stream));
     rc = finish_state(e, 1);
@@ -1595,7 +1770,30 @@ extern "C" int tfr_forward_greedy_all(tfr_engine* e, tfr_kv* kv, const uint32_t*
         if (rc) return rc;
     }
     CU(e, cudaMemcpyAsync(e->prompt, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, e->stream));
-    int rc = begin_state(e, kv, (int)tokens[0], kv->len, n, kv->max_seq + 1, nullptr, 0, 1);
+    const bool chunked = !loop && e->chunk_ok && e->chunk_tokens > 0 && n > 1 && !e->vocab_limit;
+    int rc = TFR_OK;
+    if (chunked) {
+        // one weight pass per chunk of up to CHUNK_VERIFY_MAX tokens (the reference: MAX_VERIFY_TOKENS = 9 per pass)
+        rc = chunk_buffers(e);
+        if (rc) return rc;
+        rc = begin_state(e, kv, (int)tokens[0], kv->len, n, kv->max_seq + 1, nullptr, 0, 1);  // resets the error word
+        if (rc) return rc;
+        CU(e, cudaEventRecord(e->ev0, e->stream));
+        for (int i = 0; i < n; i += CHUNK_VERIFY_MAX) {
+            const int M = std::min(CHUNK_VERIFY_MAX, n - i);
+            if (forward_chunk(e, kv, e->prompt + i, M, kv->len + i, true) != TFR_OK)
+                return fail(e, TFR_E_CUDA, "chunk kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+            CU(e, cudaMemcpyAsync(e->out_host + i, e->out_tokens, (size_t)M * 4, cudaMemcpyDeviceToHost, e->stream));
+        }
+        CU(e, cudaEventRecord(e->ev1, e->stream));
+        rc = finish_state(e, 0);
+        if (rc) return rc;
+        for (int i = 0; i < n; i++) out[i] = (uint32_t)e->out_host[i];
+        kv->len += n;
+        kv->rec_steps += n;
+        return TFR_OK;
+    }
+    rc = begin_state(e, kv, (int)tokens[0], kv->len, n, kv->max_seq + 1, nullptr, 0, 1);
     if (rc) return rc;
     CU(e, cudaEventRecord(e->ev0, e->stream));
     if (loop) rc = run_loop(e, kv, 0);
@@ -1797,6 +1995,15 @@ extern "C" int tfr_set_decode_path(tfr_engine* e, int path) {
     e->decode_path = path;
     return TFR_OK;
 }
+extern "C" int tfr_set_prefill_chunk(tfr_engine* e, int tokens) {
+    if (!e || tokens < 0) return TFR_E_INVALID;
+    e->chunk_tokens = tokens > CHUNK_MAX_TOKENS ? CHUNK_MAX_TOKENS : tokens;
+    return TFR_OK;
+}
+// Tokens per chunk in effect: 0 when prompts are fed by decode steps (switched off, or a model the chunk kernels do
+// not cover).
+extern "C" int tfr_prefill_chunk(const tfr_engine* e) { return e && e->finalized && e->chunk_ok ? e->chunk_tokens : 0; }
+
 extern "C" int tfr_decode_path(const tfr_engine* e) {
     if (!e) return TFR_E_INVALID;
     return use_loop(e) ? 2 : 1;

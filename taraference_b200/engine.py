@@ -273,6 +273,15 @@ class CudaModel:
         """The schedule the next forward call takes: 1 chained kernels, 2 persistent loop."""
         return int(_lib.lib().tfr_decode_path(self._h))
 
+    def set_prefill_chunk(self, tokens: int) -> None:
+        """forward.rs:54-65 (MAX_BATCH chunking): prompts and verification batches run in chunks of up to `tokens`
+        tokens, each reading the weights once; 0 feeds every prompt token as a decode step."""
+        self._check(_lib.lib().tfr_set_prefill_chunk(self._h, int(tokens)))
+
+    def prefill_chunk(self) -> int:
+        """Chunk size in effect; 0 when the model keeps the step-by-step route."""
+        return int(_lib.lib().tfr_prefill_chunk(self._h))
+
     def set_loop_timeline(self, device_buffer, step: int, points: int) -> None:
         """Test aid: per-CTA nanosecond timestamps of decode step `step` of the persistent loop into a device
         buffer of points * sm_count uint64 (None switches it off)."""

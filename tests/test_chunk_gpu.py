@@ -1,0 +1,183 @@
+"""Prompts and verification batches in chunks (one weight pass per chunk) against the step-by-step route, the CPU
+oracle and the reference's kernels, through the C ABI (needs a B200)."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from taraference_b200 import synth as S  # noqa: E402
+from tests.test_engine_gpu import SMALL, SMALL_128, TF_WORST, _rel, margin_gated_equal  # noqa: E402
+
+# K = 768 gives rows of three blocks, FF = 1280 five: rows that never fill a warp's 32 blocks
+ODD = dict(arch="qwen2", n_layer=2, n_embd=768, n_head=6, n_kv=2, head_dim=128, n_ff=1280, n_vocab=3001,
+           rope_theta=1e6, eps=1e-6, tied=True, qkv_bias=True)
+CFGS = [S.TINY_DENSE, SMALL, SMALL_128, ODD]
+IDS = ["tiny", "small64", "small128", "odd"]
+
+
+@pytest.fixture(scope="module")
+def E(cuda_lib):
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from taraference_b200 import engine
+    return engine
+
+
+def _margin(logits):
+    top = np.sort(logits)[-2:]
+    return float(top[1] - top[0])
+
+
+def _cache_rows(m, kv, cfg, layer, n_pos):
+    kvdim = cfg["n_kv"] * cfg["head_dim"]
+    k = m.debug_read("k", n_pos * kvdim, np.uint16, kv=kv, layer=layer)
+    v = m.debug_read("v", n_pos * kvdim, np.uint16, kv=kv, layer=layer)
+    return k, v
+
+
+@pytest.mark.parametrize("cfg", CFGS, ids=IDS)
+@pytest.mark.parametrize("chunk", [5, 16, 64])
+def test_chunked_prompt_equals_step_by_step(E, cfg, chunk):
+    """A prompt fed in chunks leaves the cache and the next-token logits of the same prompt fed token by token.
+    The projections are the same arithmetic, so layer 0 (no attention upstream) is bit-identical; deeper layers
+    differ by the summation order inside attention (fp32 rounding level, now and then an int8 flip)."""
+    tens = S.make_dense_model(cfg, seed=21)
+    rng = np.random.default_rng(7)
+    n = 45
+    prompt = [int(t) for t in rng.integers(0, cfg["n_vocab"], n)]
+    m = E.CudaModel.load_with(cfg, tens)
+    kv_a, kv_b = m.alloc_kv(96), m.alloc_kv(96)
+    m.set_prefill_chunk(0)
+    assert m.prefill_chunk() == 0
+    launches0 = m.launch_count()
+    tok_a = m.forward_greedy(prompt, kv_a)
+    launches_step = m.launch_count() - launches0
+    logits_a = m.current_logits()
+    m.set_prefill_chunk(chunk)
+    assert m.prefill_chunk() == chunk
+    launches0 = m.launch_count()
+    tok_b = m.forward_greedy(prompt, kv_b)
+    launches_chunk = m.launch_count() - launches0
+    logits_b = m.current_logits()
+    assert kv_a.len == kv_b.len == n
+    if chunk >= 16:
+        assert launches_chunk < launches_step / 2, (launches_chunk, launches_step)
+    k0a, v0a = _cache_rows(m, kv_a, cfg, 0, n)
+    k0b, v0b = _cache_rows(m, kv_b, cfg, 0, n)
+    assert np.array_equal(k0a, k0b) and np.array_equal(v0a, v0b)
+    last = cfg["n_layer"] - 1
+    kla, vla = _cache_rows(m, kv_a, cfg, last, n)
+    klb, vlb = _cache_rows(m, kv_b, cfg, last, n)
+    f16 = lambda a: a.view(np.float16).astype(np.float32)
+    assert _rel(f16(klb), f16(kla)) < TF_WORST and _rel(f16(vlb), f16(vla)) < TF_WORST
+    assert (kla != klb).mean() < 0.2 and (vla != vlb).mean() < 0.2  # most f16 values do not move at all
+    assert _rel(logits_b, logits_a) < TF_WORST
+    assert tok_a == tok_b or _margin(logits_a) <= 1e-2
+    kv_a.free()
+    kv_b.free()
+    m.destroy()
+
+
+@pytest.mark.parametrize("cfg", CFGS, ids=IDS)
+def test_chunked_prompt_vs_cpu_oracle(E, oracle, cfg):
+    tens = S.make_dense_model(cfg, seed=22)
+    rng = np.random.default_rng(8)
+    n = 37
+    prompt = [int(t) for t in rng.integers(0, cfg["n_vocab"], n)]
+    om = oracle.OracleModel(cfg, tens, 64)
+    ref_logits = None
+    for i, t in enumerate(prompt):
+        ref_logits = om.decode_token(i, t)
+    m = E.CudaModel.load_with(cfg, tens)
+    m.set_prefill_chunk(16)
+    kv = m.alloc_kv(64)
+    tok = m.forward_greedy(prompt, kv)
+    got = m.current_logits()
+    assert _rel(got, ref_logits) < 5e-2
+    assert tok == int(np.argmax(ref_logits)) or _margin(ref_logits) <= 1e-2
+    kv.free()
+    m.destroy()
+
+
+@pytest.mark.parametrize("cfg", [S.TINY_DENSE, SMALL_128], ids=["tiny", "small128"])
+def test_chunked_prompt_vs_reference_kernels(E, cfg):
+    """Against the reference's own kernels fed token by token (its decode route): the chunk kernels use that route's
+    arithmetic, not the fp32-activation GEMM of the reference's prefill (kernels/gemm.cu:6-190)."""
+    from oracle import ref_gpu
+    if not ref_gpu.available():
+        pytest.skip("reference cubin not present")
+    tens = S.make_dense_model(cfg, seed=23)
+    rng = np.random.default_rng(9)
+    n = 29
+    prompt = [int(t) for t in rng.integers(0, cfg["n_vocab"], n)]
+    rm = ref_gpu.RefModel(cfg, tens, 64)
+    ref_logits = None
+    for i, t in enumerate(prompt):
+        ref_logits = rm.decode_token(i, t).cpu().numpy()
+    m = E.CudaModel.load_with(cfg, tens)
+    m.set_prefill_chunk(16)
+    kv = m.alloc_kv(64)
+    tok = m.forward_greedy(prompt, kv)
+    got = m.current_logits()
+    assert _rel(got, ref_logits) < 5e-2
+    assert tok == int(np.argmax(ref_logits)) or _margin(ref_logits) <= 1e-2
+    kv.free()
+    m.destroy()
+
+
+@pytest.mark.parametrize("cfg", CFGS, ids=IDS)
+def test_verification_batch_in_one_pass(E, cfg):
+    """forward_greedy_all: the greedy token after every supplied position from ONE pass over the weights
+    (forward.rs:268-358), equal to the step-by-step answers wherever the step-by-step margin is large."""
+    tens = S.make_dense_model(cfg, seed=24)
+    toks = [7, 3, 99, 250, 12, 5, 41, 8, 19]
+    m = E.CudaModel.load_with(cfg, tens)
+    kv = m.alloc_kv(64)
+    m.set_prefill_chunk(0)
+    m.forward_greedy([1, 2], kv)
+    launches0 = m.launch_count()
+    want, margins = [], []
+    for t in toks:
+        want.append(m.forward_greedy([t], kv))
+        margins.append(_margin(m.current_logits()))
+    launches_step = m.launch_count() - launches0
+    want_logits = m.current_logits()
+    kv2 = m.alloc_kv(64)
+    m.forward_greedy([1, 2], kv2)
+    m.set_prefill_chunk(16)
+    launches0 = m.launch_count()
+    got = m.forward_greedy_all(toks, kv2)
+    launches_chunk = m.launch_count() - launches0
+    assert kv2.len == 2 + len(toks)
+    assert margin_gated_equal(list(got), want, margins)
+    assert _rel(m.current_logits(), want_logits) < TF_WORST
+    assert launches_chunk < launches_step / 3, (launches_chunk, launches_step)
+    # accept the first four, move the length back, continue from there
+    kv2.len = 2 + 4
+    again = m.forward_greedy_all(toks[4:], kv2)
+    assert margin_gated_equal(list(again), want[4:], margins[4:])
+    # more tokens than one pass holds
+    kv3 = m.alloc_kv(64)
+    long_toks = [int(t) for t in np.random.default_rng(3).integers(0, cfg["n_vocab"], 40)]
+    m.set_prefill_chunk(0)
+    want_long = m.forward_greedy_all(long_toks, kv3)
+    kv3.len = 0
+    m.set_prefill_chunk(16)
+    got_long = m.forward_greedy_all(long_toks, kv3)
+    agree = np.mean([a == b for a, b in zip(got_long, want_long)])
+    assert agree >= 0.8, agree
+    with pytest.raises(E.TfrError, match="context full"):
+        m.forward_greedy_all(list(range(60)), kv2)
+    for k in (kv, kv2, kv3):
+        k.free()
+    m.destroy()
+
+
+def test_hybrid_and_shortlisted_models_keep_the_step_route(E):
+    cfg = S.TINY_HYBRID
+    m = E.CudaModel.load_with(cfg, S.make_model(cfg, seed=2))
+    assert m.prefill_chunk() == 0
+    kv = m.alloc_kv(32)
+    assert isinstance(m.forward_greedy([1, 2, 3, 4], kv), int)
+    kv.free()
+    m.destroy()

@@ -274,6 +274,7 @@ def test_forward_greedy_all_equals_token_by_token(E, cfg):
     tens = S.make_model(cfg, seed=12)
     toks = [7, 3, 99, 250, 12, 5, 41, 8, 19]
     m = E.CudaModel.load_with(cfg, tens)
+    m.set_prefill_chunk(0)  # the step-by-step route: bit-identical to single steps (the chunked one: test_chunk_gpu.py)
     kv = m.alloc_kv(64)
     m.forward_greedy([1, 2], kv)
     want = [m.forward_greedy([t], kv) for t in toks]
