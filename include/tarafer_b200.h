@@ -218,13 +218,19 @@ int64_t tfr_launch_count(const tfr_engine* e);
 float tfr_last_device_ms(const tfr_engine* e);
 /* Test tap: copy a named workspace of the last step to the host ("x", "q", "attn", "h", "logits",
  * "k"/"v" = cache of `layer`, "layer_x" = residual stream after every layer; the first "layer_x"
- * request switches that tap on for later steps and returns zeros). */
+ * request switches that tap on for later steps and returns zeros).  "layer_attn", "layer_mid", "layer_h" (dense
+ * single-GPU models, chained kernels): per layer the attention output, the residual stream after the output
+ * projection and SiLU*mul, i.e. the vectors a layer rounds to int8 besides its input; switched on the same way. */
 int tfr_debug_read(tfr_engine* e, tfr_kv* kv, const char* what, int layer, void* out, size_t nbytes);
 
 /* Test aid: when device_buffer != NULL, thread 0 of every CTA of the matrix-vector and attention kernels stores the
  * GPU nanosecond timer at up to eight points into device_buffer[(launch * 160 + cta) * 8 + point], launch =
  * index of the kernel within the decode step (0 for the stand-alone operators). */
 int tfr_debug_set_timeline(unsigned long long* device_buffer);
+
+/* Test aid: dst[i] = the f16 bits the KV store writes for src[i] (crates/core/src/cuda/kernels/common.cu:9-38), over n
+ * device floats; lets a test walk all 2^32 inputs against the reference's copy_kv_f16. */
+int tfr_debug_f32_to_f16(const float* src, uint16_t* dst, int64_t n, void* stream);
 /* Test aid for the persistent loop: during decode step `step` of the next calls, thread 0 of every CTA stores the
  * GPU nanosecond timer at successive points of the step into device_buffer[point * n_sm + cta] (point < points).
  * device_buffer == NULL switches it off. */
@@ -259,6 +265,10 @@ int tfr_ffn_block_host(const tfr_mat* gate, const tfr_mat* up, const tfr_mat* do
  * and b = S[N][K/32] of kernels/gemv.cu:71-130; for Q6_K, a = J[N][K/16] of gemv.cu:302-337; for Q8_0,
  * a = the per-32-block sums [N][K/32] of gemv.cu:1558-1582. */
 int tfr_op_int_dots(const tfr_mat* w, const int8_t* q8, const float* d8, int32_t* a, int32_t* b, void* stream);
+/* The same taps with the activation given as fp32 x[K]: it is quantised by the quantiser the matrix-vector kernels run
+ * (kernels/gemv.cu:16-65 semantics), q8_out (optional, K bytes) receives the int8 values the block dots then read, and
+ * b (Q4_K) the 32-group sums exactly as the dots' activation record holds them. */
+int tfr_op_int_dots_x(const tfr_mat* w, const float* x, int32_t* a, int32_t* b, int8_t* q8_out, void* stream);
 /* attn_flash_partial + attn_flash_reduce, kernels/attn/flash.cu:16-255, for one query token
  * at position pos over cache rows [0, pos].  kc / vc: [max_seq][n_kv*head_dim] f16 bits.  The split-KV scratch
  * of this stand-alone call is one buffer per device, grown on demand: calls that overlap on the same GPU

@@ -91,6 +91,10 @@ def lib():
         _lib.tfo_head_forward.argtypes = [C.POINTER(Model), C.c_void_p, C.c_void_p, C.c_void_p]
         _lib.tfo_embed.argtypes = [C.POINTER(Model), C.c_int, C.c_void_p]
         _lib.tfo_rms_norm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_float]
+        _lib.tfo_float_to_half_bits_range.restype = None
+        _lib.tfo_float_to_half_bits_range.argtypes = [C.c_uint32, C.c_uint64, C.c_void_p]
+        _lib.tfo_set_layer_taps.restype = None
+        _lib.tfo_set_layer_taps.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         _lib.tfo_rope_neox.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float]
         _lib.tfo_attention.argtypes = [C.c_void_p] * 4 + [C.c_int] * 4 + [C.c_float]
         _lib.tfo_quantize_q8.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
@@ -141,6 +145,13 @@ def float_to_half_bits(x) -> np.ndarray:
     f = lib().tfo_float_to_half_bits
     for i, v in enumerate(x):
         out[i] = f(float(v))
+    return out
+
+
+def float_to_half_bits_range(first: int, count: int) -> np.ndarray:
+    """f16 bits of the `count` consecutive fp32 bit patterns starting at `first` (all host threads)."""
+    out = np.empty(count, np.uint16)
+    lib().tfo_float_to_half_bits_range(C.c_uint32(first), C.c_uint64(count), _p(out))
     return out
 
 
@@ -350,6 +361,20 @@ class OracleModel:
         rc = lib().tfo_layer_forward(C.byref(self.m), li, _p(x), _p(self.kc[li]), _p(self.vc[li]), pos, 0, *st)
         assert rc == 0, rc
         return x
+
+    def layer_forward_taps(self, li: int, x: np.ndarray, pos: int):
+        """layer_forward of a dense layer plus the three vectors it quantises on the way: attention output, residual
+        stream after o-proj, SiLU*mul."""
+        c = self.cfg
+        attn = np.zeros(c["n_head"] * c["head_dim"], np.float32)
+        mid = np.zeros(c["n_embd"], np.float32)
+        h = np.zeros(c["n_ff"], np.float32)
+        lib().tfo_set_layer_taps(_p(attn), _p(mid), _p(h))
+        try:
+            out = self.layer_forward(li, x, pos)
+        finally:
+            lib().tfo_set_layer_taps(None, None, None)
+        return out, attn, mid, h
 
     def head_forward(self, x: np.ndarray) -> np.ndarray:
         x = _f32(x)

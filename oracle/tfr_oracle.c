@@ -101,6 +101,18 @@ uint16_t tfo_float_to_half_bits(float f) {
     return (uint16_t)(sign | half);
 }
 
+/* The same conversion over a run of consecutive fp32 bit patterns [first, first + count): the exhaustive check of the
+ * rounding against the reference's copy_kv_f16 walks all 2^32 patterns through this. */
+void tfo_float_to_half_bits_range(uint32_t first, uint64_t count, uint16_t* out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < (int64_t)count; i++) {
+        uint32_t bits = first + (uint32_t)i;
+        float f;
+        memcpy(&f, &bits, 4);
+        out[i] = tfo_float_to_half_bits(f);
+    }
+}
+
 static inline uint16_t rd16(const uint8_t* p) { return (uint16_t)(p[0] | (p[1] << 8)); }
 
 /* ---------------------------------------------------------------- blocks -------- */
@@ -575,6 +587,16 @@ int tfo_argmax(const float* x, int n) {
  * [max_seq][n_kv*hd] f16 bits; row `pos` is written.
  * act_f32 != 0 restates the reference's PREFILL arithmetic instead (gemm.cu: every
  * projection is dequantise-then-fp32; ops.cu silu_mul), as forward.rs:54-65 fills a cache. */
+/* Optional taps of a dense layer (test aid, single-threaded callers): the vectors that are quantised to int8 inside the
+ * layer besides its input — the attention output (o-proj's activation, n_head*hd), the residual stream after o-proj
+ * (ffn_norm's input, n_embd) and SiLU*mul (down's activation, n_ff).  NULL switches a tap off. */
+static float *g_tap_attn = NULL, *g_tap_mid = NULL, *g_tap_h = NULL;
+void tfo_set_layer_taps(float* attn, float* mid, float* h) {
+    g_tap_attn = attn;
+    g_tap_mid = mid;
+    g_tap_h = h;
+}
+
 int tfo_layer_forward(const tfo_model* M, int li, float* x, uint16_t* kc, uint16_t* vc, int pos, int act_f32, float* ssm,
                       float* conv) {
     int K = M->n_embd, H = M->n_head, Hkv = M->n_kv, hd = M->head_dim, FF = M->n_ff;
@@ -610,8 +632,10 @@ int tfo_layer_forward(const tfo_model* M, int li, float* x, uint16_t* kc, uint16
         tfo_copy_kv_f16(kb, kc, pos, kvn);
         tfo_copy_kv_f16(vb, vc, pos, kvn);
         tfo_attention(q, kc, vc, xb, H, Hkv, hd, pos, 1.0f / sqrtf((float)hd));
+        if (g_tap_attn) memcpy(g_tap_attn, xb, sizeof(float) * (size_t)qn);
         rc |= tfo_gemv(&L->wo, xb, x, NULL, 2, act_f32);
     }
+    if (g_tap_mid) memcpy(g_tap_mid, x, sizeof(float) * (size_t)K);
     tfo_rms_norm(x, L->ffn_norm, xb, K, M->eps);
     if (!act_f32) {
         rc |= tfo_ffn_gate_up(&L->gate, &L->up, xb, h);
@@ -620,6 +644,7 @@ int tfo_layer_forward(const tfo_model* M, int li, float* x, uint16_t* kc, uint16
         rc |= tfo_gemv(&L->up, xb, u, NULL, 0, 1);
         for (int j = 0; j < FF; j++) h[j] = (h[j] / (1.f + expf(-h[j]))) * u[j];
     }
+    if (g_tap_h) memcpy(g_tap_h, h, sizeof(float) * (size_t)FF);
     rc |= tfo_gemv(&L->down, h, x, NULL, 2, act_f32);
     free(xb); free(y); free(q); free(kb); free(vb); free(h); free(u);
     return rc;

@@ -61,6 +61,8 @@ uint16_t tfo_float_to_half_bits(float f);
 int tfo_gemv(const tfo_mat* w, const float* x, float* out, const float* bias, int use_res, int act_mode);
 int tfo_ffn_gate_up(const tfo_mat* gate, const tfo_mat* up, const float* x, float* out);
 void tfo_rms_norm(const float* x, const float* w, float* out, int n, float eps);
+void tfo_float_to_half_bits_range(uint32_t first, uint64_t count, uint16_t* out);
+void tfo_set_layer_taps(float* attn, float* mid, float* h);
 void tfo_copy_kv_f16(const float* src, uint16_t* cache, int pos, int stride);
 void tfo_attention(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv, int hd, int pos,
                    float scale);

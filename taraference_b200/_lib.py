@@ -97,6 +97,7 @@ def lib() -> C.CDLL:
         "tfr_last_device_ms": (f32, [vp]),
         "tfr_debug_read": (i32, [vp, vp, C.c_char_p, i32, vp, sz]),
         "tfr_debug_set_timeline": (i32, [vp]),
+        "tfr_debug_f32_to_f16": (i32, [vp, vp, i64, vp]),
         "tfr_mat_create": (i32, [i32, i64, i64, vp, sz, i32, C.POINTER(vp)]),
         "tfr_mat_free": (None, [vp]),
         "tfr_mat_device_bytes": (i64, [vp]),
@@ -106,6 +107,7 @@ def lib() -> C.CDLL:
         "tfr_op_ffn_block": (i32, [vp, vp, vp, vp, vp, vp, i32, vp]),
         "tfr_ffn_block_host": (i32, [vp, vp, vp, vp, vp]),
         "tfr_op_int_dots": (i32, [vp, vp, vp, vp, vp, vp]),
+        "tfr_op_int_dots_x": (i32, [vp, vp, vp, vp, vp, vp]),
         "tfr_op_attention": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
         "tfr_op_attention_noalloc": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
         "tfr_op_qkv_rope_store": (i32, [vp] * 8 + [f32, f32, i32, i32, vp, vp, vp, vp]),

@@ -201,11 +201,12 @@ __device__ __forceinline__ void reduce_rows_group(const float* pa, const float* 
 // ------------------------------------------------------------------ the chunk GEMM
 
 // Shared memory: [ Act x Mt | staged fp32 vector (fp32-route rows only) | partial sums x Mt | mbarriers | tile slots ].
-// Warp w owns the tiles w, w + 32, ... of the CTA and `nsw` ring slots; it refills a slot as soon as it has used
+// Warp w < wa owns the tiles w, w + wa, ... of the CTA and `nsw` ring slots; it refills a slot as soon as it has used
 // the tile in it, so the stream runs `nsw` tiles ahead of the dots.  With more tokens than Mt the CTA walks its
 // tiles once per group of Mt tokens (the second pass finds them in L2).
 struct GemmGeom {
     int M, Mt, K, pbuf_floats, nsw;
+    int wa;              // warps that run block dots (each owns nsw ring slots); a power of two <= 32
     size_t act_stride;   // bytes between tokens in the global activation buffer
     int act_b16;         // bytes of one token's Act in shared memory (a multiple of 16)
 };
@@ -215,13 +216,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1)
 k_gemm_q8(const unsigned char* act_g, const float* xn, RowJob ja, RowJob jb, F32Seg fseg, ChunkEpi epi, GemmGeom g) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, cta = blockIdx.x;
-    const int K = g.K, nb = K >> 8, Mt = g.Mt, nsw = g.nsw;
+    const int K = g.K, nb = K >> 8, Mt = g.Mt, nsw = g.nsw, wa = g.wa;
     constexpr int TB = BLK::TILE_BYTES;
     unsigned char* act_s = smem;
     float* xs = reinterpret_cast<float*>(act_s + (size_t)Mt * g.act_b16);
     float* pbuf = xs + (fseg.m.data ? xs_floats(K) : 0);
     unsigned long long* full = reinterpret_cast<unsigned long long*>(pbuf + (size_t)Mt * g.pbuf_floats);
-    unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(full + GEMV_WARPS * nsw) + 127) & ~(uintptr_t)127);
+    unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(full + wa * nsw) + 127) & ~(uintptr_t)127);
 
     const int rows_a0 = ja.sh.begin(cta) * ja.rows_per_item;
     const int rows_a = max(0, min(ja.sh.count(cta) * ja.rows_per_item, ja.m.N - rows_a0));
@@ -232,18 +233,18 @@ k_gemm_q8(const unsigned char* act_g, const float* xn, RowJob ja, RowJob jb, F32
     const int ta0 = (int)(fa0 >> 5), tiles_a = rows_a > 0 ? (int)((fa1 + 31) >> 5) - ta0 : 0;
     const int tb0 = (int)(fb0 >> 5), tiles_b = rows_b > 0 ? (int)((fb1 + 31) >> 5) - tb0 : 0;
     const int n_jobs = tiles_a + tiles_b;
-    const int ntw = warp < n_jobs ? (n_jobs - warp + GEMV_WARPS - 1) / GEMV_WARPS : 0;  // tiles of this warp
+    const int ntw = (warp < wa && warp < n_jobs) ? (n_jobs - warp + wa - 1) / wa : 0;  // tiles of this warp
     const int n_groups = (g.M + Mt - 1) / Mt;
     const int uses = ntw * n_groups;  // tile uses of this warp over the whole launch
-    unsigned long long* wfull = full + warp * nsw;
-    unsigned char* wring = ring + (size_t)warp * nsw * TB;
-    auto issue = [&](int k) {  // use k of this warp: tile warp + 32 * (k mod ntw) into slot k mod nsw
-        const int j = warp + GEMV_WARPS * (k % ntw), s = k % nsw;
+    unsigned long long* wfull = full + (warp < wa ? warp : 0) * nsw;
+    unsigned char* wring = ring + (size_t)(warp < wa ? warp : 0) * nsw * TB;
+    auto issue = [&](int k) {  // use k of this warp: tile warp + wa * (k mod ntw) into slot k mod nsw
+        const int j = warp + wa * (k % ntw), s = k % nsw;
         const uint8_t* src = j < tiles_a ? ja.m.data + (long long)(ta0 + j) * TB : jb.m.data + (long long)(tb0 + j - tiles_a) * TB;
         mbar_expect_tx(wfull + s, TB);
         bulk_load(wring + (size_t)s * TB, src, TB, wfull + s);
     };
-    if (lane == 0) {
+    if (lane == 0 && warp < wa) {
         for (int s = 0; s < nsw; s++) mbar_init(wfull + s, 1);
         mbar_fence_init();
         for (int k = 0; k < nsw && k < uses; k++) issue(k);  // weights do not depend on the previous kernel
@@ -306,7 +307,7 @@ k_gemm_q8(const unsigned char* act_g, const float* xn, RowJob ja, RowJob jb, F32
         }
         // phase A: per-block partials of every token out of the tiles
         for (int i = 0; i < ntw; i++) {
-            const int k = grp_i * ntw + i, j = warp + GEMV_WARPS * i, s = k % nsw;
+            const int k = grp_i * ntw + i, j = warp + wa * i, s = k % nsw;
             const bool is_b = j >= tiles_a;
             const long long f = (long long)(is_b ? tb0 + (j - tiles_a) : ta0 + j) * 32 + lane;
             const bool mine = is_b ? (f >= fb0 && f < fb1) : (f >= fa0 && f < fa1);
@@ -359,19 +360,21 @@ inline GemmLaunch gemm_plan(int tile_bytes, int M, int K, const RowJob& ja, cons
     const size_t act_b16 = (act_smem_bytes(K, false, false) + 15) & ~(size_t)15;
     const size_t xf = with_f32 ? xs_floats(K) * 4 : 0;
     L.fits = false;
-    for (int Mt = std::min(M, 16); Mt >= 1; Mt--) {
-        const size_t fixed = (size_t)Mt * act_b16 + xf + (size_t)Mt * pf * 4 + 256;
-        const size_t need1 = fixed + (size_t)GEMV_WARPS * (8 + tile_bytes);
-        if (need1 > GEMV_SMEM_MAX) continue;
-        int nsw = (int)((GEMV_SMEM_MAX - fixed) / ((size_t)GEMV_WARPS * (8 + tile_bytes)));
-        if (nsw > 4) nsw = 4;
-        // prefer a deeper ring over the last few tokens per pass
-        if (nsw < 2 && Mt > 4) continue;
-        L.g = GemmGeom{M, Mt, K, pf, nsw, 0, (int)act_b16};
-        L.smem = fixed + (size_t)GEMV_WARPS * nsw * (8 + tile_bytes);
-        L.fits = true;
-        break;
-    }
+    // The dot work of a launch does not depend on Mt, the per-pass overhead shrinks with it: take the widest set of
+    // dot warps that still leaves room for a few tokens per pass, then as many tokens as fit.
+    const int want = std::min(M, 4);
+    for (int pass = 0; pass < 2 && !L.fits; pass++)
+        for (int wa = GEMV_WARPS; wa >= 8 && !L.fits; wa >>= 1)
+            for (int Mt = std::min(M, 16); Mt >= (pass == 0 ? want : 1); Mt--) {
+                const size_t fixed = (size_t)Mt * act_b16 + xf + (size_t)Mt * pf * 4 + 256;
+                if (fixed + (size_t)wa * (8 + tile_bytes) > GEMV_SMEM_MAX) continue;
+                int nsw = (int)((GEMV_SMEM_MAX - fixed) / ((size_t)wa * (8 + tile_bytes)));
+                if (nsw > 4) nsw = 4;
+                L.g = GemmGeom{M, Mt, K, pf, nsw, wa, 0, (int)act_b16};
+                L.smem = fixed + (size_t)wa * nsw * (8 + tile_bytes);
+                L.fits = true;
+                break;
+            }
     return L;
 }
 

@@ -150,6 +150,8 @@ struct tfr_engine {
     int *args_dev = nullptr, *args_host = nullptr;  // per-call scalars: pinned host -> device
     int attn_S = 1, attn_min_keys = 64;
     float* layer_taps = nullptr;  // [n_layer][n_embd] residual stream after each layer (test aid)
+    // [n_layer][...] the other vectors a dense layer quantises: attention output, residual after o-proj, SiLU*mul (test aid)
+    float *tap_attn = nullptr, *tap_mid = nullptr, *tap_h = nullptr;
     // graphs
     bool use_graph = true;
     cudaGraphExec_t g_decode = nullptr, g_body = nullptr;
@@ -559,7 +561,7 @@ extern "C" void tfr_destroy(tfr_engine* e) {
     for (auto& kv : e->vecs) cudaFree(kv.second.dev);
     for (auto& L : e->layers) cudaFree(L.bias_qkv);
     void* ws[] = {e->x, e->q, e->attn, e->h, e->logits, e->partial, e->counters, e->st, e->out_tokens, e->prompt,
-                  e->layer_taps, e->proj, e->qgate, e->loop_layers, e->loop_bar, e->loop_best, e->loop_vec, e->cx, e->cq, e->cattn, e->ch, e->cxn, e->clogits, e->cact, e->loop_blob, e->loop_head_tasks};
+                  e->layer_taps, e->tap_attn, e->tap_mid, e->tap_h, e->proj, e->qgate, e->loop_layers, e->loop_bar, e->loop_best, e->loop_vec, e->cx, e->cq, e->cattn, e->ch, e->cxn, e->clogits, e->cact, e->loop_blob, e->loop_head_tasks};
     for (void* p : ws) cudaFree(p);
     if (e->st_host) cudaFreeHost(e->st_host);
     if (e->out_host) cudaFreeHost(e->out_host);
@@ -1429,9 +1431,14 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
             if (launch_attention(s, a, hd, e->st) != cudaSuccess) return -1;
             n++;
         }
+        auto tap = [&](float* dst, const float* src, int width) {
+            return !dst || cudaMemcpyAsync(dst + (size_t)li * width, src, (size_t)width * 4, cudaMemcpyDeviceToDevice, s) == cudaSuccess;
+        };
+        if (!tap(e->tap_attn, e->attn, P.attn_width)) return -1;
         // output projection of the mixer + residual
         if (launch_residual(wout, e->attn, mix_width, 2 * li) != cudaSuccess) return -1;
         n++;
+        if (!tap(e->tap_mid, e->x, K)) return -1;
         {  // 4. norm + quant + gate/up + silu*mul
             PrepArgs pa{};
             pa.vec = e->x;
@@ -1444,6 +1451,7 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
                 return -1;
             n++;
         }
+        if (!tap(e->tap_h, e->h, FF)) return -1;
         // 5. down + residual
         if (launch_residual(L.down, e->h, FF, 2 * li + 1) != cudaSuccess) return -1;
         n++;
@@ -2037,6 +2045,23 @@ extern "C" int tfr_debug_read(tfr_engine* e, tfr_kv* kv, const char* what, int l
         }
         src = e->layer_taps, have = (size_t)c.n_layer * c.n_embd * 4;
     }
+    else if (w == "layer_attn" || w == "layer_mid" || w == "layer_h") {
+        // per-layer taps of the last step (dense models, chained kernels); the first request switches them on
+        if (c.hybrid || e->plan.tp > 1) return fail(e, TFR_E_UNSUPPORTED, "debug_read: %s is for dense single-GPU models", what);
+        if (!e->tap_attn) {
+            cudaSetDevice(e->device);
+            CU(e, cudaMalloc(&e->tap_attn, (size_t)c.n_layer * e->plan.attn_width * 4));
+            CU(e, cudaMalloc(&e->tap_mid, (size_t)c.n_layer * c.n_embd * 4));
+            CU(e, cudaMalloc(&e->tap_h, (size_t)c.n_layer * e->plan.ff * 4));
+            CU(e, cudaMemset(e->tap_attn, 0, (size_t)c.n_layer * e->plan.attn_width * 4));
+            CU(e, cudaMemset(e->tap_mid, 0, (size_t)c.n_layer * c.n_embd * 4));
+            CU(e, cudaMemset(e->tap_h, 0, (size_t)c.n_layer * e->plan.ff * 4));
+            drop_graphs(e);
+        }
+        if (w == "layer_attn") src = e->tap_attn, have = (size_t)c.n_layer * e->plan.attn_width * 4;
+        else if (w == "layer_mid") src = e->tap_mid, have = (size_t)c.n_layer * c.n_embd * 4;
+        else src = e->tap_h, have = (size_t)c.n_layer * e->plan.ff * 4;
+    }
     else if (w == "proj" && e->proj) src = e->proj, have = (size_t)(gdn_channels(c) + gdn_val_dim(c) + 2 * c.ssm_time_step_rank) * 4;
     else if (w == "qgate" && e->qgate) src = e->qgate, have = (size_t)c.n_head * c.head_dim * 4;
     else if (w == "ssm_state" && kv && kv->ssm && layer >= 0 && layer < c.n_layer)
@@ -2070,6 +2095,18 @@ extern "C" int tfr_debug_read(tfr_engine* e, tfr_kv* kv, const char* what, int l
 }
 
 // ------------------------------------------------------------------ operator level
+
+// Test aid: the KV-store rounding (f32_to_f16_bits_ref) applied to n device floats.
+__global__ void k_debug_f32_to_f16(const float* src, unsigned short* dst, long long n) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        dst[i] = f32_to_f16_bits_ref(src[i]);
+}
+extern "C" int tfr_debug_f32_to_f16(const float* src, uint16_t* dst, int64_t n, void* stream) {
+    if (!src || !dst || n < 0) return TFR_E_INVALID;
+    if (n == 0) return TFR_OK;
+    k_debug_f32_to_f16<<<148 * 8, 256, 0, (cudaStream_t)stream>>>(src, dst, (long long)n);
+    return cudaGetLastError() == cudaSuccess ? TFR_OK : TFR_E_CUDA;
+}
 
 extern "C" int tfr_debug_set_timeline(unsigned long long* device_buffer) {
     return cudaMemcpyToSymbol(g_prof, &device_buffer, sizeof(device_buffer)) == cudaSuccess ? TFR_OK : TFR_E_CUDA;
@@ -2156,18 +2193,26 @@ extern "C" int tfr_ffn_block_host(const tfr_mat* gate, const tfr_mat* up, const 
     return check(cudaStreamSynchronize(nullptr));
 }
 
-extern "C" int tfr_op_int_dots(const tfr_mat* w, const int8_t* q8, const float* d8, int32_t* a, int32_t* b, void* stream) {
-    if (!w || !q8 || !d8 || !a || w->perm_hd) return TFR_E_INVALID;
+static int int_dots_impl(const tfr_mat* w, const float* x, const int8_t* q8, const float* d8, int32_t* a, int32_t* b, int8_t* q8_out,
+                         void* stream) {
+    if (!w || !a || w->perm_hd) return TFR_E_INVALID;
     if (w->m.type == TFR_Q4_K && !b) return TFR_E_INVALID;
     configure_kernels_once();
     const size_t smem = act_smem_bytes(w->m.K, false, false);
-    if (w->m.type == TFR_Q4_K)
-        k_int_dots<BlockQ4><<<sm_count_cached(), 256, smem, (cudaStream_t)stream>>>(w->m, (const signed char*)q8, d8, a, b);
-    else if (w->m.type == TFR_Q8_0)
-        k_int_dots<BlockQ8><<<sm_count_cached(), 256, smem, (cudaStream_t)stream>>>(w->m, (const signed char*)q8, d8, a, b);
-    else
-        k_int_dots<BlockQ6><<<sm_count_cached(), 256, smem, (cudaStream_t)stream>>>(w->m, (const signed char*)q8, d8, a, b);
+    const int grid = sm_count_cached();
+    cudaStream_t s = (cudaStream_t)stream;
+    if (w->m.type == TFR_Q4_K) k_int_dots<BlockQ4><<<grid, 256, smem, s>>>(w->m, x, (const signed char*)q8, d8, a, b, (signed char*)q8_out);
+    else if (w->m.type == TFR_Q8_0) k_int_dots<BlockQ8><<<grid, 256, smem, s>>>(w->m, x, (const signed char*)q8, d8, a, b, (signed char*)q8_out);
+    else k_int_dots<BlockQ6><<<grid, 256, smem, s>>>(w->m, x, (const signed char*)q8, d8, a, b, (signed char*)q8_out);
     return check(cudaGetLastError());
+}
+extern "C" int tfr_op_int_dots(const tfr_mat* w, const int8_t* q8, const float* d8, int32_t* a, int32_t* b, void* stream) {
+    if (!q8 || !d8) return TFR_E_INVALID;
+    return int_dots_impl(w, nullptr, q8, d8, a, b, nullptr, stream);
+}
+extern "C" int tfr_op_int_dots_x(const tfr_mat* w, const float* x, int32_t* a, int32_t* b, int8_t* q8_out, void* stream) {
+    if (!x) return TFR_E_INVALID;
+    return int_dots_impl(w, x, nullptr, nullptr, a, b, q8_out, stream);
 }
 
 static int op_attention_impl(const float* q, const uint16_t* kc, const uint16_t* vc, const float* gate, float* out, int n_head,

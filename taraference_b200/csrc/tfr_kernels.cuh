@@ -654,14 +654,30 @@ __device__ void act_from_q8(const Act& act, const signed char* q8, const float* 
     __syncthreads();
 }
 
-// Integer contract taps, computed by the very block-dot routines the GEMV kernel uses.
-// Q4_K: I[row][K/32], S[row][K/32].  Q6_K: J[row][K/16].
+// Integer contract taps, computed by the very routines the GEMV kernel uses.
+// Q4_K: I[row][K/32], S[row][K/32].  Q6_K: J[row][K/16].  Q8_0: sums[row][K/32].
+// x != nullptr: the activation is quantised here by act_quantize4 (what k_gemv runs on a plain vector) instead of being
+// taken from (q8, d8); q8_out (optional) then receives the int8 values the block dots read.  S is read back from the
+// Act the dots use (s16n holds -32 * the sum of every 16-chunk, an exact integer), not recomputed from the int8.
 template <class BLK>
-__global__ void k_int_dots(Mat m, const signed char* q8, const float* d8, int* outA, int* outB) {
+__global__ void k_int_dots(Mat m, const float* x, const signed char* q8, const float* d8, int* outA, int* outB, signed char* q8_out) {
     extern __shared__ __align__(128) unsigned char smem[];
-    const int K = m.K, nb = m.nb, lane = threadIdx.x & 31;
+    const int K = m.K, nb = m.nb, lane = threadIdx.x & 31, tid = threadIdx.x;
     Act act = act_carve(smem, K, false, false);
-    act_from_q8(act, q8, d8, K);
+    if (x) {
+        const int n4 = K >> 2;
+        for (int k0 = 0; k0 < n4; k0 += blockDim.x) {
+            const int i4 = k0 + tid;
+            const bool on = i4 < n4;
+            const float4 v = on ? reinterpret_cast<const float4*>(x)[i4] : make_float4(0.f, 0.f, 0.f, 0.f);
+            act_quantize4(act, v, i4, on, nb);
+        }
+        __syncthreads();
+        if (q8_out && blockIdx.x == 0)
+            for (int e = 4 * tid; e < K; e += 4 * blockDim.x) *reinterpret_cast<int*>(q8_out + e) = *act_word_ptr(act, e, nb);
+    } else {
+        act_from_q8(act, q8, d8, K);
+    }
     const long long total = (long long)m.N * nb;
     const long long tiles = (total + 31) >> 5;
     const int TB = tile_bytes(m.type);
@@ -674,10 +690,8 @@ __global__ void k_int_dots(Mat m, const signed char* q8, const float* d8, int* o
         if (BLK::TILE_BYTES == Q4_TILE_BYTES) {
             for (int j = 0; j < 8; j++) {
                 outA[(size_t)r * (K / 32) + 8 * b + j] = ints[j];
-                // S from the stored product is not exact; recompute from the int8 activation
-                int sacc = 0;
-                for (int i = 0; i < 32; i++) sacc += q8[256 * b + 32 * j + i];
-                outB[(size_t)r * (K / 32) + 8 * b + j] = sacc;
+                const int g = 8 * b + j;
+                outB[(size_t)r * (K / 32) + g] = -(act.s16n[2 * g] + act.s16n[2 * g + 1]) / 32;
             }
         } else if (BLK::TILE_BYTES == Q8_TILE_BYTES) {
             for (int j = 0; j < 8; j++) outA[(size_t)r * (K / 32) + 8 * b + j] = ints[j];

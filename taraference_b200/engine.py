@@ -424,6 +424,17 @@ def op_int_dots(w: GpuMat, q8, d8, a, b=None, stream: int = 0) -> None:
     _ok(_lib.lib().tfr_op_int_dots(w._h, _ptr(q8), _ptr(d8), _ptr(a), _ptr(b), stream), "int_dots")
 
 
+def op_int_dots_x(w: GpuMat, x, a, b=None, q8_out=None, stream: int = 0) -> None:
+    """Integer taps with the activation quantised by the product's own in-kernel quantiser; q8_out receives the int8
+    values the block dots read, b (Q4_K) the group sums as the dots' activation record holds them."""
+    _ok(_lib.lib().tfr_op_int_dots_x(w._h, _ptr(x), _ptr(a), _ptr(b), _ptr(q8_out), stream), "int_dots_x")
+
+
+def debug_f32_to_f16(src, dst, n: int, stream: int = 0) -> None:
+    """Test aid: the KV store's f32 -> f16 rounding over n device floats."""
+    _ok(_lib.lib().tfr_debug_f32_to_f16(_ptr(src), _ptr(dst), int(n), stream), "debug_f32_to_f16")
+
+
 def op_attention(q, kc, vc, out, n_head: int, n_kv: int, head_dim: int, pos: int, stream: int = 0) -> None:
     _ok(_lib.lib().tfr_op_attention(_ptr(q), _ptr(kc), _ptr(vc), _ptr(out), n_head, n_kv, head_dim, pos, stream),
         "attention")

@@ -47,6 +47,25 @@ TF_TYPICAL = 2e-6   # fp32 reassociation level
 TF_WORST = 1e-2     # a layer in which one activation rounding flipped
 
 
+def free_running_bound(cfg, tens, prompt, max_seq=64):
+    """Bound for free-running logits against a checker: 4 x how far the REFERENCE moves on this very input when only
+    its own summation order changes (its mcol and 8-way FFN kernels, kernels/gemv.cu:2546-2575 and 2081-2115), and
+    never below one int8 flip per layer (a flip moves a layer's output by up to TF_WORST, see
+    test_layer_errors_are_attributed_to_int8_flips; free running, the flips of successive layers add up).  Returns
+    (bound, reference self-deviation); without the reference cubin the self-deviation is unknown (None)."""
+    from oracle import ref_gpu
+    floor = min(cfg["n_layer"], 5) * TF_WORST
+    if not ref_gpu.available():
+        return floor, None
+    rm = ref_gpu.RefModel(cfg, tens, max_seq)
+    rm_alt = ref_gpu.RefModel(cfg, tens, max_seq, alt_ffn=True)
+    for i, t in enumerate(prompt):
+        rl = rm.decode_token(i, int(t)).cpu().numpy()
+        rl_alt = rm_alt.decode_token(i, int(t)).cpu().numpy()
+    dev = _rel(rl_alt, rl)
+    return max(4 * dev, floor), dev
+
+
 def teacher_forced_errors(m, kv, checker_embed, checker_layer, checker_head, cfg, tokens, pos0=0):
     """Runs the engine token by token; for every layer compares its output with the checker's
     layer applied to the engine's own input of that layer.  Returns (layer errors, head errors)."""
@@ -103,6 +122,50 @@ def test_teacher_forced_layers_vs_cpu_oracle(E, oracle, cfg):
 
 
 @pytest.mark.parametrize("cfg", [S.TINY_DENSE, SMALL, SMALL_128], ids=["tiny", "small64", "small128"])
+def test_layer_errors_are_attributed_to_int8_flips(E, oracle, cfg):
+    """Teacher-forced layers again, now with the reason for every deviation: besides its input a dense layer rounds
+    three vectors to int8 (attention output, ffn_norm(residual after o-proj), SiLU*mul).  A layer whose output differs
+    from the checker's by more than 1e-5 must show at least one differing int8 among them, and a layer with identical
+    int8 everywhere must agree to 1e-5.  Prints the flip rate."""
+    cfg = dict(cfg, n_layer=4)
+    tens = S.make_dense_model(cfg, seed=31)
+    om = oracle.OracleModel(cfg, tens, 64)
+    m = E.CudaModel.load_with(cfg, tens)
+    kv = m.alloc_kv(64)
+    K, L, FF, nq = cfg["n_embd"], cfg["n_layer"], cfg["n_ff"], cfg["n_head"] * cfg["head_dim"]
+    for name, width in (("layer_x", K), ("layer_attn", nq), ("layer_mid", K), ("layer_h", FF)):
+        m.debug_read(name, L * width)  # switch the taps on
+    q = lambda v: oracle.quantize_q8(v)[0].astype(np.int32)
+    rows = []
+    tokens = [int(t) for t in np.random.default_rng(5).integers(0, cfg["n_vocab"], 24)]
+    for i, tok in enumerate(tokens):
+        m.forward_greedy([tok], kv)
+        lx = m.debug_read("layer_x", L * K).reshape(L, K)
+        la = m.debug_read("layer_attn", L * nq).reshape(L, nq)
+        lm = m.debug_read("layer_mid", L * K).reshape(L, K)
+        lh = m.debug_read("layer_h", L * FF).reshape(L, FF)
+        xin = om.embed(tok)
+        for li in range(L):
+            if li > 0:
+                xin = lx[li - 1]
+            want, attn_o, mid_o, h_o = om.layer_forward_taps(li, xin, i)
+            w_ffn = tens[f"blk.{li}.ffn_norm.weight"]
+            flips = int((q(la[li]) != q(attn_o)).sum())
+            flips += int((q(oracle.rms_norm(lm[li], w_ffn, cfg["eps"])) != q(oracle.rms_norm(mid_o, w_ffn, cfg["eps"]))).sum())
+            flips += int((q(lh[li]) != q(h_o)).sum())
+            rows.append((_rel(lx[li], want), flips))
+    err = np.array([r[0] for r in rows])
+    flips = np.array([r[1] for r in rows])
+    print(f"layers {len(rows)}: with a flipped int8 {int((flips > 0).sum())}, worst error with / without a flip "
+          f"{err[flips > 0].max() if (flips > 0).any() else 0:.2e} / {err[flips == 0].max() if (flips == 0).any() else 0:.2e}")
+    assert np.all(flips[err > 1e-5] >= 1), rows
+    assert np.all(err[flips == 0] < 1e-5), rows
+    assert err.max() < TF_WORST
+    kv.free()
+    m.destroy()
+
+
+@pytest.mark.parametrize("cfg", [S.TINY_DENSE, SMALL, SMALL_128], ids=["tiny", "small64", "small128"])
 def test_free_running_logits_and_tokens_vs_cpu_oracle(E, oracle, cfg):
     tens = S.make_dense_model(cfg, seed=3)
     om = oracle.OracleModel(cfg, tens, 64)
@@ -114,7 +177,9 @@ def test_free_running_logits_and_tokens_vs_cpu_oracle(E, oracle, cfg):
     for i, t in enumerate(prompt):
         ologits = om.decode_token(i, t)
     glogits = m.current_logits()
-    assert _rel(glogits, ologits) < 5e-2, _rel(glogits, ologits)
+    bound, self_dev = free_running_bound(cfg, tens, prompt)
+    print(f"engine vs CPU oracle {_rel(glogits, ologits):.2e}; reference vs itself {self_dev}; bound {bound:.2e}")
+    assert _rel(glogits, ologits) < bound, (_rel(glogits, ologits), bound, self_dev)
     assert nxt == int(np.argmax(ologits)) or np.sort(ologits)[-1] - np.sort(ologits)[-2] < 1e-2
     toks = m.decode_burst(nxt, 20, kv)
     otoks, omarg, _ = om.decode_greedy(5, nxt, 20)
@@ -145,7 +210,7 @@ def test_free_running_vs_reference_self_consistency(E, cfg):
     self_dev = _rel(rl_alt, rl)
     ours = _rel(gl, rl)
     print(f"reference vs itself {self_dev:.2e}, engine vs reference {ours:.2e}")
-    assert ours < max(1e-3, 4 * self_dev, 5e-2 if self_dev > 0 else 1e-3), (ours, self_dev)
+    assert ours < max(4 * self_dev, min(cfg["n_layer"], 5) * TF_WORST), (ours, self_dev)
     rtoks, rmarg, _ = rm.decode_greedy(7, nxt, 12)
     toks = m.decode_burst(nxt, 12, kv)
     assert margin_gated_equal(toks, rtoks, rmarg), (toks, rtoks, rmarg)
@@ -259,11 +324,56 @@ def test_full_size_3b_shapes_teacher_forced(E, oracle):
     nxt = m.forward_greedy(toks_in, kv)
     for i, t in enumerate(toks_in):
         ologits = om2.decode_token(i, t)
-    assert _rel(m.current_logits(), ologits) < 5e-2
+    bound, self_dev = free_running_bound(cfg, host, toks_in)
+    print(f"engine vs CPU oracle {_rel(m.current_logits(), ologits):.2e}; reference vs itself {self_dev}; bound {bound:.2e}")
+    assert _rel(m.current_logits(), ologits) < bound, (bound, self_dev)
     toks = m.decode_burst(nxt, 6, kv)
     otoks, omarg, _ = om2.decode_greedy(4, nxt, 6)
     oracle.set_threads(1)
     assert margin_gated_equal(toks, otoks, omarg), (toks, otoks, omarg)
+    kv.free()
+    m.destroy()
+
+
+def test_full_depth_3b_free_running_vs_reference_kernels(E):
+    """All 36 layers of the 3B shape: a 32-token prompt, then 64 positions, against the reference's own kernels (its
+    launch sequence from the cubin built beside the checker).  Over 36 layers the int8 flips of successive layers add
+    up, for the reference too: its two FFN kernels (mcol / 8-way), fed the same tokens, drift apart.  The engine, fed
+    those tokens, must stay as close to the reference as the reference stays to itself: logits within 4 x that
+    self-deviation, and the greedy token equal wherever the reference's top-2 margin exceeds 4 x its own uncertainty."""
+    from oracle import ref_gpu
+    if not ref_gpu.available():
+        pytest.skip("reference cubin not present")
+    from taraference_b200 import synth_gpu
+    cfg = dict(S.QWEN25_3B)
+    m, host = synth_gpu.build_dense_model(cfg, seed=0, keep_host=True, context_length=160)
+    rm, rm_alt = ref_gpu.RefModel(cfg, host, 160), ref_gpu.RefModel(cfg, host, 160, alt_ffn=True)
+    prompt = [int(t) for t in np.random.default_rng(0).integers(0, cfg["n_vocab"], 32)]
+    for i, t in enumerate(prompt):
+        rl = rm.decode_token(i, t).cpu().numpy()
+        rm_alt.decode_token(i, t)
+    first = int(np.argmax(rl))
+    rtoks, rmarg, rl_last = rm.decode_greedy(32, first, 64)      # the reference, free running
+    fed = [first] + [int(t) for t in rtoks[:-1]]                  # the tokens it consumed at positions 32 .. 95
+    alt_pred = []
+    for s_, t in enumerate(fed):
+        la = rm_alt.decode_token(32 + s_, t)
+        alt_pred.append(int(torch.argmax(la).item()))
+    la_last = la.cpu().numpy()
+    kv = m.alloc_kv(160)
+    m.set_prefill_chunk(0)                                        # decode steps throughout: the route the burst takes
+    m.forward_greedy(prompt, kv)
+    ours_pred = [int(t) for t in m.forward_greedy_all(fed, kv)]
+    ours_last = m.current_logits()
+    dev_ref, dev_ours = _rel(la_last, rl_last), _rel(ours_last, rl_last)
+    gate = 4 * dev_ref * float(np.abs(rl_last).max())
+    agree_alt = int(np.sum(np.array(alt_pred) == rtoks)), int(np.sum(np.array(ours_pred) == rtoks))
+    print(f"36 layers, 64 positions: logits vs reference {dev_ours:.2e} (reference vs itself {dev_ref:.2e}); greedy token equal "
+          f"at {agree_alt[1]}/64 positions (reference vs itself {agree_alt[0]}/64); margin gate {gate:.3f}")
+    assert dev_ref > 0 and dev_ours < 4 * dev_ref, (dev_ours, dev_ref)
+    bad = [i for i in range(64) if ours_pred[i] != rtoks[i] and rmarg[i] > gate]
+    assert not bad, (bad, [float(rmarg[i]) for i in bad], gate)
+    assert agree_alt[1] >= agree_alt[0] - 6, agree_alt
     kv.free()
     m.destroy()
 

@@ -197,7 +197,10 @@ def test_free_running_hybrid_tokens_and_state_reset(E, oracle, cfg):
     for i, t in enumerate(prompt):
         ologits = om.decode_token(i, t)
     glogits = m.current_logits()
-    assert _rel(glogits, ologits) < 5e-2, _rel(glogits, ologits)
+    from tests.test_engine_gpu import free_running_bound
+    bound, self_dev = free_running_bound(cfg, tens, prompt)
+    print(f"engine vs CPU oracle {_rel(glogits, ologits):.2e}; reference vs itself {self_dev}; bound {bound:.2e}")
+    assert _rel(glogits, ologits) < bound, (_rel(glogits, ologits), bound, self_dev)
     toks = m.decode_burst(nxt, 20, kv)
     otoks, omarg, _ = om.decode_greedy(5, nxt, 20)
     assert len(toks) == 20 and kv.len == 25

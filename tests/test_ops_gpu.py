@@ -104,6 +104,60 @@ def test_integer_sub_block_dots_bit_exact(E, oracle, wtype, K, N):
     m.free()
 
 
+@pytest.mark.parametrize("K,N", [(256, 3), (2048, 37), (11008, 5)])
+def test_group_sums_and_int8_tapped_from_the_product_quantiser(E, oracle, K, N):
+    """The fp32 vector goes through the quantiser the matrix-vector kernels run; the int8 values and the 32-group sums
+    S_j are read back from the activation record the block dots use, and I_j from those dots: all bit-exact against the
+    CPU restatement (the rare +-1 of the approximate division is the quantiser's own, kernels/gemv.cu:16-65)."""
+    rng = np.random.default_rng(K * 7 + N)
+    nb = K // 256
+    blocks = S.random_q4_k(rng, N * nb)
+    x = rng.normal(0, 1, K).astype(np.float32)
+    x[64:96] = 0.0  # a zero group
+    m = E.GpuMat(S.Q4_K, K, N, blocks.reshape(-1))
+    a = torch.zeros((N, K // 32), dtype=torch.int32, device="cuda")
+    b = torch.zeros((N, K // 32), dtype=torch.int32, device="cuda")
+    q8_dev = torch.zeros(K, dtype=torch.int8, device="cuda")
+    E.op_int_dots_x(m, dev(x), a, b, q8_dev)
+    q8 = q8_dev.cpu().numpy()
+    oq, _ = oracle.quantize_q8(x)
+    diff = q8.astype(np.int32) - oq.astype(np.int32)
+    assert np.abs(diff).max() <= 1 and (diff != 0).mean() < 2e-3
+    a, b = a.cpu().numpy(), b.cpu().numpy()
+    sums = q8.astype(np.int32).reshape(K // 32, 32).sum(1)
+    for r in range(N):
+        assert np.array_equal(b[r], sums)  # what the dots hold == the sums of the int8 they read
+        for bi in range(nb):
+            I, Sm = oracle.q4k_subdots(blocks[r * nb + bi], q8[256 * bi: 256 * bi + 256])
+            assert np.array_equal(a[r, 8 * bi: 8 * bi + 8], I)
+            assert np.array_equal(b[r, 8 * bi: 8 * bi + 8], Sm)
+    m.free()
+
+
+def test_kv_store_rounding_all_inputs_vs_reference_and_oracle(E, oracle):
+    """Every one of the 2^32 fp32 bit patterns: the library's KV-store rounding == the reference's copy_kv_f16
+    (kernels/ops.cu:471-486, kernels/common.cu:9-38, run from the reference cubin) == the CPU restatement."""
+    from oracle import ref_gpu
+    have_ref = ref_gpu.available()
+    n = 1 << 26
+    base = torch.arange(n, dtype=torch.int64, device="cuda")
+    ours = torch.empty(n, dtype=torch.int16, device="cuda")
+    theirs = torch.empty(n, dtype=torch.int16, device="cuda")
+    for chunk in range(64):
+        first = chunk << 26
+        bits = (base + first)
+        bits = torch.where(bits >= (1 << 31), bits - (1 << 32), bits).to(torch.int32)
+        x = bits.view(torch.float32)
+        E.debug_f32_to_f16(x, ours, n)
+        if have_ref:
+            ref_gpu.copy_kv(x, theirs, 0, n)
+            assert torch.equal(ours, theirs), f"chunk {chunk}"
+        host = ours.cpu().numpy().view(np.uint16)
+        assert np.array_equal(host, oracle.float_to_half_bits_range(first, n)), f"chunk {chunk}"
+    if not have_ref:
+        pytest.skip("reference cubin not present: checked against the CPU restatement only")
+
+
 def _rel(a, b):
     return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
 
