@@ -23,6 +23,14 @@ constexpr int ATTN_THREADS = 256;
 constexpr int ATTN_TILE = 64;     // keys per tile
 constexpr int ATTN_REP_MAX = 8;   // query heads per KV head handled by one CTA
 constexpr int ATTN_CLUSTER = 8;   // CTAs per cluster (the portable maximum); AttnArgs::S is a multiple of it
+constexpr int ATTN_LONG_MIN = 128;  // a split with more keys than this walks them through shared-memory stages
+// Dynamic shared memory of k_attn_decode: a few stages of one K tile (rows padded by 8 halfs: 16-byte reads of 32
+// different rows hit 32 different banks) and one V tile each, then q of the group's heads in fp32.  One tile in
+// flight per SM is far too little to cover the memory latency (measured: 4 us per 32 KB tile with two stages), so a
+// split keeps as many tiles in flight as shared memory holds.
+__host__ __device__ constexpr int attn_stages(int hd) { return hd == 256 ? 2 : 5; }
+inline size_t attn_stage_bytes(int hd) { return (size_t)ATTN_TILE * (hd + 8) * 2 + (size_t)ATTN_TILE * hd * 2; }
+inline size_t attn_dyn_smem(int hd) { return attn_stages(hd) * attn_stage_bytes(hd) + (size_t)ATTN_REP_MAX * hd * 4; }
 
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -126,14 +134,20 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
     };
     // Rows of earlier positions do not depend on the previous kernel: the first tile's are requested before
     // the grid-dependency wait, so their latency hides behind the kernel boundary.
-    load_k(t0, min(t1, T - 1), false);
-    load_v(t0, min(t1, T - 1), false);
+    // A split with many keys stages its tiles in shared memory instead (below): no register preload then.
+    const bool long_path = t1 - t0 > ATTN_LONG_MIN;
+    if (!long_path) {
+        load_k(t0, min(t1, T - 1), false);
+        load_v(t0, min(t1, T - 1), false);
+    }
     griddep_wait();  // q and the new K/V row come from the previous kernel
     griddep_launch_dependents();
     prof_mark(1, a.prof_id);
     if (leave) return;
-    load_k(t0, 0, true);
-    load_v(t0, 0, true);
+    if (!long_path) {
+        load_k(t0, 0, true);
+        load_v(t0, 0, true);
+    }
 
     __shared__ __align__(16) float sc[ATTN_TILE][ATTN_REP_MAX];  // [key][head]: the value phase reads a key's eight weights as two float4
     __shared__ float m_s[ATTN_REP_MAX], l_s[ATTN_REP_MAX], alpha_s[ATTN_REP_MAX];
@@ -161,7 +175,174 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
     __syncthreads();
     prof_mark(4, a.prof_id);
 
-    for (int tt = t0; tt < t1; tt += ATTN_TILE) {
+    if (long_path) {
+        // ---- long splits: K and V tiles travel global -> shared memory as asynchronous 16-byte copies, NST stages
+        // deep, so the loads of the next tiles run under the arithmetic of tile i and no register holds cache data.
+        extern __shared__ __align__(16) unsigned char attn_dyn[];
+        constexpr int KROW = HD + 8, CPR = HD / 8;  // halfs per staged K row; 16-byte chunks per cache row
+        constexpr int NST = attn_stages(HD);
+        const size_t stage_b = (size_t)ATTN_TILE * KROW * 2 + (size_t)ATTN_TILE * HD * 2;
+        float* q_s = reinterpret_cast<float*>(attn_dyn + NST * stage_b);
+        auto k_stage = [&](int st_) { return reinterpret_cast<unsigned short*>(attn_dyn + (size_t)st_ * stage_b); };
+        auto v_stage = [&](int st_) { return reinterpret_cast<unsigned short*>(attn_dyn + (size_t)st_ * stage_b + (size_t)ATTN_TILE * KROW * 2); };
+        auto issue_tile = [&](int tt, int st_) {
+            unsigned short* ks = k_stage(st_);
+            unsigned short* vs = v_stage(st_);
+            if (tt < t1)
+                for (int i = tid; i < ATTN_TILE * CPR; i += ATTN_THREADS) {
+                    const int row = i / CPR, c8 = i - row * CPR;
+                    const bool in = tt + row < t1;
+                    const size_t off = (size_t)(in ? tt + row : t1 - 1) * kvdim + (size_t)g * HD + c8 * 8;
+                    cp_async16(ks + row * KROW + c8 * 8, a.kc + off, in ? 16 : 0);
+                    cp_async16(vs + row * HD + c8 * 8, a.vc + off, in ? 16 : 0);
+                }
+            cp_async_commit();  // a group per tile slot, empty past the end: the wait below counts groups
+        };
+#pragma unroll
+        for (int p = 0; p < NST - 1; p++) issue_tile(t0 + p * ATTN_TILE, p);
+        for (int i = tid; i < rep * HD; i += ATTN_THREADS) q_s[i] = a.q[g * rep * HD + i];
+        // Both phases are register-blocked so that shared-memory reads stay well below the FMA count (a 16-byte read
+        // costs the load pipe four cycles per warp even when all lanes read the same address).
+        // Scores: a thread takes KPT keys x all heads x one slice of DSL dims: per 8 dims it reads q once for the
+        // eight heads (16 reads) and each key once (KPT reads) for KPT * 64 FMAs; the DS slices of a key group are
+        // DS adjacent lanes, their partial sums meet in a halving butterfly that leaves lane ds with values 2 ds, 2 ds + 1.
+        // Values: warp w takes keys w, w + 8, ... of the tile, lane l the dims l * DV ..: per key 2 reads of the eight
+        // weights and one of V for 8 * DV FMAs.
+        constexpr int DS = HD >= 128 ? 16 : 8;          // dim slices (lanes) per key group
+        constexpr int DSL = HD / DS;                    // dims per slice: 8 or 16
+        constexpr int KPT = DS / 4;                     // keys per thread: 8 warps x (32 / DS) groups x KPT = 64
+        constexpr int NV = KPT * ATTN_REP_MAX;          // partial sums per thread
+        constexpr int DV = HD / 32;                     // value dims per lane
+        const int ds = lane & (DS - 1), kgrp = warp * (32 / DS) + lane / DS;
+        const int key0 = kgrp * KPT;
+        float o2[ATTN_REP_MAX][DV];
+#pragma unroll
+        for (int h = 0; h < ATTN_REP_MAX; h++)
+#pragma unroll
+            for (int d = 0; d < DV; d++) o2[h][d] = 0.f;
+        int it = 0;
+        for (int tt = t0; tt < t1; tt += ATTN_TILE, it++) {
+            const int tn = min(ATTN_TILE, t1 - tt), cur = it % NST;
+            issue_tile(tt + (NST - 1) * ATTN_TILE, (it + NST - 1) % NST);  // the stage tile it - 1 has just left
+            cp_async_wait_group<NST - 1>();
+            __syncthreads();
+            if (it == 0) prof_mark(6, a.prof_id);
+            {
+                float v[NV];
+#pragma unroll
+                for (int i = 0; i < NV; i++) v[i] = 0.f;
+                const unsigned short* kbase = k_stage(cur) + key0 * KROW + ds * DSL;
+#pragma unroll
+                for (int c = 0; c < DSL; c += 8) {
+                    float kf[KPT][8];
+#pragma unroll
+                    for (int kk = 0; kk < KPT; kk++) {
+                        const int4 kw = *reinterpret_cast<const int4*>(kbase + kk * KROW + c);
+                        const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kw.x)), k1 = __half22float2(*reinterpret_cast<const __half2*>(&kw.y));
+                        const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kw.z)), k3 = __half22float2(*reinterpret_cast<const __half2*>(&kw.w));
+                        kf[kk][0] = k0.x, kf[kk][1] = k0.y, kf[kk][2] = k1.x, kf[kk][3] = k1.y;
+                        kf[kk][4] = k2.x, kf[kk][5] = k2.y, kf[kk][6] = k3.x, kf[kk][7] = k3.y;
+                    }
+#pragma unroll
+                    for (int h = 0; h < ATTN_REP_MAX; h++) {
+                        if (h < rep) {
+                            const float* qp = q_s + h * HD + ds * DSL + c;
+                            const float4 a0 = *reinterpret_cast<const float4*>(qp), a1 = *reinterpret_cast<const float4*>(qp + 4);
+#pragma unroll
+                            for (int kk = 0; kk < KPT; kk++)
+                                v[kk * ATTN_REP_MAX + h] += a0.x * kf[kk][0] + a0.y * kf[kk][1] + a0.z * kf[kk][2] + a0.w * kf[kk][3] +
+                                                            a1.x * kf[kk][4] + a1.y * kf[kk][5] + a1.z * kf[kk][6] + a1.w * kf[kk][7];
+                        }
+                    }
+                }
+                // halving butterfly over the DS lanes of the key group
+#pragma unroll
+                for (int off = DS / 2, n = NV; off >= 1; off >>= 1, n >>= 1) {
+                    const bool up = (lane & off) != 0;
+#pragma unroll
+                    for (int i = 0; i < n / 2; i++) {
+                        const float send = up ? v[i] : v[i + n / 2];
+                        const float keep = up ? v[i + n / 2] : v[i];
+                        v[i] = keep + __shfl_xor_sync(TFR_FULL_MASK, send, off);
+                    }
+                }
+                // this lane now holds values 2 ds and 2 ds + 1 of the group's KPT x 8: key 2 ds / 8, heads 2 ds % 8, + 1
+                const int kl = (2 * ds) >> 3, h0 = (2 * ds) & 7, k = key0 + kl;
+                sc[k][h0] = (k < tn && h0 < rep) ? v[0] * a.scale : -1e30f;
+                sc[k][h0 + 1] = (k < tn && h0 + 1 < rep) ? v[1] * a.scale : -1e30f;
+            }
+            __syncthreads();
+            if (warp < rep) {  // online softmax bookkeeping: warp h owns head h
+                const float s0 = sc[lane][warp], s1 = sc[lane + 32][warp];
+                const float tile_m = warp_max(fmaxf(s0, s1));
+                const float m_old = m_s[warp];
+                const float m_new = fmaxf(m_old, tile_m);
+                const float p0 = (lane < tn) ? expf(s0 - m_new) : 0.f;
+                const float p1 = (lane + 32 < tn) ? expf(s1 - m_new) : 0.f;
+                const float tile_l = warp_sum(p0 + p1);
+                sc[lane][warp] = p0;
+                sc[lane + 32][warp] = p1;
+                if (lane == 0) {
+                    const float alpha = expf(m_old - m_new);
+                    alpha_s[warp] = alpha;
+                    l_s[warp] = l_s[warp] * alpha + tile_l;
+                    m_s[warp] = m_new;
+                }
+            }
+            __syncthreads();
+#pragma unroll
+            for (int h = 0; h < ATTN_REP_MAX; h++) {
+                const float al = h < rep ? alpha_s[h] : 1.f;
+#pragma unroll
+                for (int d = 0; d < DV; d++) o2[h][d] *= al;
+            }
+            const unsigned short* vs = v_stage(cur);
+#pragma unroll 2
+            for (int k = warp; k < tn; k += 8) {
+                const float4 pa = *reinterpret_cast<const float4*>(&sc[k][0]), pb = *reinterpret_cast<const float4*>(&sc[k][4]);
+                const float p[ATTN_REP_MAX] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
+                float vf[DV];
+                const unsigned short* vr = vs + k * HD + lane * DV;
+                if constexpr (DV == 8) {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(vr);
+                    const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x)), v1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+                    const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&raw.z)), v3 = __half22float2(*reinterpret_cast<const __half2*>(&raw.w));
+                    vf[0] = v0.x, vf[1] = v0.y, vf[2] = v1.x, vf[3] = v1.y, vf[4] = v2.x, vf[5] = v2.y, vf[6] = v3.x, vf[7] = v3.y;
+                } else if constexpr (DV == 4) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(vr);
+                    const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x)), v1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+                    vf[0] = v0.x, vf[1] = v0.y, vf[2] = v1.x, vf[3] = v1.y;
+                } else {
+                    const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(vr));
+                    vf[0] = v0.x, vf[1] = v0.y;
+                }
+#pragma unroll
+                for (int h = 0; h < ATTN_REP_MAX; h++) {
+                    if (h < rep) {
+#pragma unroll
+                        for (int d = 0; d < DV; d++) o2[h][d] += p[h] * vf[d];
+                    }
+                }
+            }
+            __syncthreads();  // the next iteration overwrites sc and refills the stage just used
+            if (it == 0) prof_mark(7, a.prof_id);
+        }
+        // the eight key groups (warps) fold into the four slots the epilogue sums
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            if ((warp >> 2) == half) {
+#pragma unroll
+                for (int h = 0; h < ATTN_REP_MAX; h++)
+#pragma unroll
+                    for (int d = 0; d < DV; d++) {
+                        float* dst = &ored[warp & 3][h][lane * DV + d];
+                        *dst = half ? *dst + o2[h][d] : o2[h][d];
+                    }
+            }
+            __syncthreads();
+        }
+    }
+    for (int tt = t0; tt < t1 && !long_path; tt += ATTN_TILE) {
         const int tn = min(ATTN_TILE, t1 - tt);
         // ---- scores
 #pragma unroll
@@ -277,10 +458,12 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
 
     prof_mark(2, a.prof_id);
     // ---- combine the four key groups and write this split's (m, l, O)
+    if (!long_path) {
 #pragma unroll
-    for (int h = 0; h < ATTN_REP_MAX; h++)
+        for (int h = 0; h < ATTN_REP_MAX; h++)
 #pragma unroll
-        for (int d = 0; d < DPT; d++) ored[kg][h][dp * DPT + d] = o[h][d];
+            for (int d = 0; d < DPT; d++) ored[kg][h][dp * DPT + d] = o[h][d];
+    }
     __syncthreads();
     const int po = 2 + HD;
     if (S_eff == 1) {

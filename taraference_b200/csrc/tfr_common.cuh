@@ -113,6 +113,16 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, unsigned i
                  : "memory");
 }
 
+// 16-byte asynchronous copy global -> shared (LDGSTS); n_src = 0 fills the destination with zeros.
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int n_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(n_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// Blocks until at most N of this thread's committed copy groups are still in flight.
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 // Programmatic dependent launch (sm_90+): the first lets the next kernel in the stream start its
 // prologue, the second blocks until the previous kernel has completed and its writes are visible.
 // Both are no-ops for a kernel launched without the attribute.

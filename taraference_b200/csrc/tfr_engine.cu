@@ -283,9 +283,13 @@ static void configure_kernels_once() {
     configure_kernel(k_attn_chunk<128>, true);
     configure_kernel(k_attn_chunk<256>, true);
     configure_kernel(k_prep_rows, false);
+    // the attention kernel also has static shared memory: ask for exactly the dynamic part it uses
     configure_kernel(k_attn_decode<64>, false);
     configure_kernel(k_attn_decode<128>, false);
     configure_kernel(k_attn_decode<256>, false);
+    cudaFuncSetAttribute(k_attn_decode<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_dyn_smem(64));
+    cudaFuncSetAttribute(k_attn_decode<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_dyn_smem(128));
+    cudaFuncSetAttribute(k_attn_decode<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_dyn_smem(256));
     configure_kernel(k_gdn_step, false);
     configure_kernel(k_qk_norm_rope_store, false);
     configure_kernel(k_state_advance, false);
@@ -303,12 +307,14 @@ static int attn_max_clusters(int hd) {
         for (auto& d : cache_all) d[0] = d[1] = d[2] = -1;
         cache_init = true;
     }
+    configure_kernels_once();  // the query below asks for the kernel's opt-in dynamic shared memory
     int* cache = cache_all[current_device_slot()];
     const int slot = hd == 64 ? 0 : hd == 128 ? 1 : 2;
     if (cache[slot] >= 0) return cache[slot];
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(ATTN_CLUSTER * 64, 1);
     cfg.blockDim = dim3(ATTN_THREADS);
+    cfg.dynamicSmemBytes = attn_dyn_smem(hd);
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = ATTN_CLUSTER;
@@ -1242,6 +1248,7 @@ static cudaError_t launch_attention(cudaStream_t s, const AttnArgs& a, int hd, c
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(a.S, a.n_kv);
     cfg.blockDim = dim3(ATTN_THREADS);
+    cfg.dynamicSmemBytes = attn_dyn_smem(hd);
     cfg.stream = s;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;

@@ -181,12 +181,6 @@ __device__ __forceinline__ void red_add_u32(unsigned* p, unsigned v) {
     asm volatile("red.relaxed.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ float4 ldcg4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
-// 16-byte asynchronous copy global -> shared; n_src = 0 fills the destination with zeros.
-__device__ __forceinline__ void cp_async16(void* dst, const void* src, int n_src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(n_src) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-
 __device__ __forceinline__ void loop_fail(LoopCtx& c, const LoopArgs& a, int code) {
     a.st->err = code;
     c.ctl[CTL_ABORT] = 1;
