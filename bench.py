@@ -274,7 +274,51 @@ def gate_up_roofline(E, S, cfg, peak_gbs, peak_kind):
             "note": "back-to-back launches on one stream: includes the launch gap"}
 
 
-def tensor_parallel_32b(rank, world, local, dist, steps: int = 2, warmup: int = 3):
+def attention_roofline(E, cfg, n_keys, peak_gbs, peak_kind):
+    """Stand-alone split-KV attention at n_keys keys: CUDA events over 120 launches that rotate through 12 K/V buffer
+    pairs (more than L2 holds), and the reference's attn_flash_partial + attn_flash_reduce on the same cache."""
+    import torch
+    H, Hkv, hd = cfg["n_head"], cfg["n_kv"], cfg["head_dim"]
+    rng = np.random.default_rng(0)
+    base_k = rng.normal(0, 1, (n_keys + 8, Hkv * hd)).astype(np.float16).view(np.int16)
+    base_v = rng.normal(0, 1, (n_keys + 8, Hkv * hd)).astype(np.float16).view(np.int16)
+    nbuf = 12
+    kcs = [torch.from_numpy(base_k).cuda().clone() for _ in range(nbuf)]
+    vcs = [torch.from_numpy(base_v).cuda().clone() for _ in range(nbuf)]
+    q = torch.randn(H * hd, device="cuda")
+    out = torch.zeros(H * hd, device="cuda")
+
+    def timed(fn, reps=120):
+        for i in range(nbuf):
+            fn(i)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for r in range(reps):
+            fn(r % nbuf)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) * 1000 / reps
+
+    us = timed(lambda i: E.op_attention(q, kcs[i], vcs[i], out, H, Hkv, hd, n_keys - 1))
+    ref_us = None
+    try:
+        from oracle import ref_gpu
+        if ref_gpu.available():
+            ref_us = timed(lambda i: ref_gpu.attention(q, kcs[i], vcs[i], H, Hkv, hd, n_keys - 1), reps=36)
+    except Exception:  # the comparison is informative only
+        ref_us = None
+    alg = 2 * n_keys * Hkv * hd * 2 + 2 * H * hd * 4  # K and V rows once, q in, out
+    ach = alg / us * 1e-3
+    return {"bound": "hbm", "kernel": f"k_attn_decode<{hd}> (split-KV flash-decode, {n_keys} keys, {H} query / {Hkv} KV heads)",
+            "achieved": ach, "peak": peak_gbs, "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": ach / peak_gbs,
+            "traffic": None, "algorithmic_bytes_per_launch": alg, "us_per_launch": us,
+            "reference_attn_flash_us_per_launch": ref_us,
+            "note": "back-to-back launches on one stream over 12 rotating K/V buffers (208 MB); includes the launch gap; the "
+                    "reference figure is its attn_flash_partial + attn_flash_reduce launched through the driver API"}
+
+
+def tensor_parallel_32b(rank, world, local, dist, steps: int = 8, warmup: int = 3):
     """BASELINE configuration 5 as a side measurement of the default run: the Qwen2.5-32B shape with the
     job's ranks as ONE tensor-parallel engine (a single GPU at N = 1).  All ranks call this."""
     import torch
@@ -291,6 +335,7 @@ def tensor_parallel_32b(rank, world, local, dist, steps: int = 2, warmup: int = 
     t_build = time.perf_counter() - t_build
     prompt = np.random.default_rng(0).integers(0, cfg["n_vocab"], prompt_len)
     first = model.forward_greedy(prompt, kv)
+    last_tokens = []
 
     def timed_us_per_token():
         dev = []
@@ -300,6 +345,7 @@ def tensor_parallel_32b(rank, world, local, dist, steps: int = 2, warmup: int = 
                 dist.barrier()
             toks = model.decode_burst(first, n_decode, kv)
             assert len(toks) == n_decode
+            last_tokens[:] = [int(t) for t in toks]
             if i >= warmup:
                 dev.append(model.last_device_ms())
         total = float(np.sum(dev))
@@ -309,7 +355,19 @@ def tensor_parallel_32b(rank, world, local, dist, steps: int = 2, warmup: int = 
             total = float(t[0])
         return total * 1000 / (n_decode * steps)
 
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     us = timed_us_per_token()
+    clocks = sampler.stop() if rank == 0 else None
+    tp_tokens = list(last_tokens)
+    # every rank must have emitted the same tokens
+    ranks_agree = True
+    if world > 1:
+        mine = torch.tensor([first] + tp_tokens, dtype=torch.int64, device="cuda")
+        everyone = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(everyone, mine)
+        ranks_agree = all(bool(torch.equal(everyone[0], t)) for t in everyone)
     nccl = None
     if world > 1:
         # comparison baseline: the same engine with ncclAllReduce between kernels instead of the in-kernel exchange
@@ -322,9 +380,34 @@ def tensor_parallel_32b(rank, world, local, dist, steps: int = 2, warmup: int = 
             nccl = {"error": repr(exc)[:200]}
     kv.free()
     model.destroy()
+    # the same bytes on ONE GPU (rank 0), fed the tensor-parallel engine's own tokens: its greedy choice must be the
+    # token the tensor-parallel engine emitted wherever its top-2 margin is not small
+    check = {"ranks_agree": ranks_agree, "compared_with_one_gpu": 0, "mismatches_beyond_margin": 0}
+    if world > 1:
+        n_cmp = 48
+        bad = 0
+        if rank == 0:
+            single, _ = synth_gpu.build_model(cfg, seed=0, device=local, context_length=ctx)
+            kv1 = single.alloc_kv(ctx)
+            single.forward_greedy(prompt, kv1)
+            fed = [int(first)] + tp_tokens[:n_cmp - 1]
+            for i, t in enumerate(fed):
+                nxt = single.forward_greedy([t], kv1)
+                if nxt != tp_tokens[i]:
+                    top = np.sort(single.current_logits())[-2:]
+                    if float(top[1] - top[0]) > 1e-2 * max(1.0, float(np.abs(top[1]))):
+                        bad += 1
+            kv1.free()
+            single.destroy()
+        flag = torch.tensor([bad], dtype=torch.int64, device="cuda")
+        dist.broadcast(flag, src=0)
+        check["compared_with_one_gpu"] = n_cmp
+        check["mismatches_beyond_margin"] = int(flag[0])
+    tokens_match = bool(check["ranks_agree"] and check["mismatches_beyond_margin"] == 0)
     wbytes = synth_gpu.weight_bytes(cfg) + synth_gpu.kv_bytes_per_position(cfg) * (prompt_len + n_decode / 2)
     return {"workload": text, "parallelism": f"tp{world}" if world > 1 else "single GPU", "scaling": "strong",
             "tokens_per_s": 1e6 / us, "us_per_token": us, "steps": steps, "warmup": warmup,
+            "tokens_match": tokens_match, "tokens_check": check, "clocks": clocks,
             "aggregate_weight_kv_gbs": wbytes / us * 1e-3, "build_s": t_build, "nccl_allreduce_baseline": nccl,
             "timing": "CUDA events around each 256-token burst, max over ranks"}
 
@@ -376,6 +459,10 @@ def main():
     rng = np.random.default_rng(0)
     prompt = rng.integers(0, cfg["n_vocab"], PROMPT_LEN)
     first = model.forward_greedy(prompt, kv)  # prefill once; every step restarts from this cache state
+    prefill = {"tokens": int(PROMPT_LEN), "device_ms": model.last_device_ms(),
+               "tokens_per_s": PROMPT_LEN / max(model.last_device_ms(), 1e-9) * 1e3, "chunk_tokens": model.prefill_chunk(),
+               "what": "tfr_forward_greedy over the whole prompt: chunks of chunk_tokens through the batched kernels "
+                       "(0: one decode step per token), the last token as a decode step with the head"}
 
     def barrier():
         if world > 1:
@@ -424,12 +511,27 @@ def main():
             t = model.forward_greedy([t], kv)
         per_token_api = 64 / (time.perf_counter() - t0)
 
+    verify = None
+    if main_workload and rank == 0 and tp == 1:
+        # one-pass verification batch (forward_greedy_all, 9 tokens as the reference's MAX_VERIFY_TOKENS)
+        vt = [int(t) for t in rng.integers(0, cfg["n_vocab"], 9)]
+        kv.len = PROMPT_LEN
+        model.forward_greedy_all(vt, kv)
+        kv.len = PROMPT_LEN
+        model.forward_greedy_all(vt, kv)
+        v_us = model.last_device_ms() * 1000
+        step_us = float(np.sum(dev_ms)) * 1000 / (N_DECODE * args.steps)
+        verify = {"tokens": 9, "device_us": v_us, "decode_steps_equivalent": v_us / step_us, "chunk_tokens": model.prefill_chunk()}
+    attn_roof = None
+    if args.workload == "3b-long" and rank == 0:
+        peak_a, kind_a = measured_peaks()
+        attn_roof = attention_roofline(E, cfg, PROMPT_LEN + N_DECODE, peak_a, kind_a)
     tp32 = None
     if main_workload and not args.skip_32b:
         kv.free()
         model.destroy()
         kv = model = None
-        tp32 = tensor_parallel_32b(rank, world, local, dist if world > 1 else None)
+        tp32 = tensor_parallel_32b(rank, world, local, dist if world > 1 else None, steps=max(args.steps, 1))
     if rank == 0:
         peak, peak_kind = measured_peaks()
         wbytes = synth_gpu.weight_bytes(cfg)
@@ -437,7 +539,7 @@ def main():
         bytes_per_token = wbytes + kvb * (PROMPT_LEN + N_DECODE / 2) + synth_gpu.recurrent_state_bytes(cfg)
         us_tok = dev_total * 1000 / (N_DECODE * args.steps)
         token_gbs = bytes_per_token / us_tok * 1e-3
-        roof = gate_up_roofline(E, S, dict(S.QWEN25_3B), peak, peak_kind) if main_workload else None
+        roof = gate_up_roofline(E, S, dict(S.QWEN25_3B), peak, peak_kind) if main_workload else attn_roof
         cpu = None
         if want_host and not args.skip_cpu_baseline:
             from oracle import oracle as O
@@ -467,7 +569,7 @@ def main():
                     "call": "tfr_decode_burst: scalars from pinned host memory, tokens back to host memory",
                     "per_token_forward_greedy_tok_s": per_token_api},
             "gpu_launches": int(launches), "clocks": clocks, "reference_kernels_same_gpu": ref_gpu_info,
-            "wall_s_timed_region": wall_all, "tensor_parallel_32b": tp32,
+            "wall_s_timed_region": wall_all, "prefill": prefill, "verify_batch": verify, "tensor_parallel_32b": tp32,
         }
         print(json.dumps(line), flush=True)
     if model is not None:

@@ -22,6 +22,7 @@ namespace tfr {
 
 constexpr int CHUNK_MAX_TOKENS = 64;   // tokens per chunk forward
 constexpr int CHUNK_VERIFY_MAX = 16;   // tokens per chunk when every row's greedy token is wanted (logits [M][V])
+constexpr int CHUNK_ATTN_SPLITS_MAX = 32;  // most key splits of the chunk attention
 
 // ------------------------------------------------------------------ embedding rows
 
@@ -389,35 +390,59 @@ inline cudaError_t launch_gemm(cudaStream_t stream, int grid, const unsigned cha
 
 // ------------------------------------------------------------------ causal attention of a chunk
 
-// CTA = (KV head g, tile of QT query tokens); its rows are the QT x rep (query token, query head of the group) pairs.
-// Keys are walked in tiles of 32 staged in shared memory; a warp owns rows, a lane owns one key of the tile for the
-// scores and HD / 32 output dims for the values (fp32 math on the f16 cache, as kernels/attn/fast_v2.cu:12-192;
-// row (m, h) sees keys 0 .. pos0 + m).
-constexpr int ATTC_THREADS = 256, ATTC_WARPS = ATTC_THREADS / 32, ATTC_TK = 32;
+// CTA = (KV head g, tile of QT query tokens, split s of the keys); its rows are the QT x rep (query token, query head
+// of the group) pairs.  Keys are walked in tiles of 32 that travel global -> shared memory as asynchronous 16-byte
+// copies, ATTC_STAGES tiles deep; a warp owns rows, a lane owns one key of the tile for the scores and HD / 32 output
+// dims for the values (fp32 math on the f16 cache, as kernels/attn/fast_v2.cu:12-192; row (m, h) sees keys
+// 0 .. pos0 + m).  With S > 1 splits (long contexts: a chunk has few query tiles, the keys supply the parallelism)
+// every CTA leaves (m, l, O) partials that k_attn_chunk_merge combines (kernels/attn/flash.cu:236-254 algebra).
+constexpr int ATTC_THREADS = 256, ATTC_WARPS = ATTC_THREADS / 32, ATTC_TK = 32, ATTC_STAGES = 4;
 constexpr int ATTC_ROWS_MAX = 32;  // rows per CTA: 4 per warp
-inline size_t attn_chunk_smem(int hd) { return sizeof(float) * ATTC_ROWS_MAX * hd + 2 * ATTC_TK * (hd + 8) + 2 * ATTC_TK * hd; }
+inline size_t attn_chunk_smem(int hd) {
+    return sizeof(float) * ATTC_ROWS_MAX * hd + (size_t)ATTC_STAGES * (2 * ATTC_TK * (hd + 8) + 2 * ATTC_TK * hd);
+}
 
 struct AttnChunkArgs {
     const float* q;   // [M][n_head * hd]
     const unsigned short *kc, *vc;  // layer base [max_seq][kvdim]
     float* out;       // [M][n_head * hd]
-    int M, QT, n_head, n_kv, pos0, kvdim, ldq;
+    float* partial;   // [M * n_head][S][2 + hd] when S > 1
+    int M, QT, S, n_head, n_kv, pos0, kvdim, ldq;
     float scale;
 };
 
 template <int HD>
 __global__ void __launch_bounds__(ATTC_THREADS) k_attn_chunk(AttnChunkArgs a) {
-    constexpr int KROW = HD + 8, DPL = HD / 32, RPW = ATTC_ROWS_MAX / ATTC_WARPS;
-    extern __shared__ __align__(16) unsigned char attc_smem[];
+    constexpr int KROW = HD + 8, DPL = HD / 32, RPW = ATTC_ROWS_MAX / ATTC_WARPS, CPR = HD / 8;
+    extern __shared__ __align__(128) unsigned char attc_smem[];
     float (*q_s)[HD] = reinterpret_cast<float (*)[HD]>(attc_smem);
-    unsigned short (*k_s)[KROW] = reinterpret_cast<unsigned short (*)[KROW]>(attc_smem + sizeof(float) * ATTC_ROWS_MAX * HD);
-    unsigned short (*v_s)[HD] = reinterpret_cast<unsigned short (*)[HD]>(attc_smem + sizeof(float) * ATTC_ROWS_MAX * HD + 2 * ATTC_TK * KROW);
+    constexpr size_t STAGE_B = 2 * ATTC_TK * KROW + 2 * ATTC_TK * HD;
+    unsigned char* stages = attc_smem + sizeof(float) * ATTC_ROWS_MAX * HD;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = blockIdx.x, rep = a.n_head / a.n_kv;
+    const int g = blockIdx.x, rep = a.n_head / a.n_kv, sp = blockIdx.z;
     const int m_first = blockIdx.y * a.QT, qt = min(a.QT, a.M - m_first);
     const int n_rows = qt * rep;
+    const int T = a.pos0 + m_first + qt;  // keys the tile's last token sees
+    // this split's run of whole key tiles
+    const int n_tiles = (T + ATTC_TK - 1) / ATTC_TK, per = (n_tiles + a.S - 1) / a.S;
+    const int k0 = min(T, sp * per * ATTC_TK), k1 = min(T, (sp + 1) * per * ATTC_TK);
+    auto issue_tile = [&](int tt, int st_) {
+        unsigned short* ks = reinterpret_cast<unsigned short*>(stages + (size_t)st_ * STAGE_B);
+        unsigned short* vs = ks + ATTC_TK * KROW;
+        if (tt < k1)
+            for (int i = tid; i < ATTC_TK * CPR; i += ATTC_THREADS) {
+                const int row = i / CPR, c8 = i - row * CPR;
+                const bool in = tt + row < k1;
+                const size_t off = (size_t)(in ? tt + row : k1 - 1) * a.kvdim + (size_t)g * HD + c8 * 8;
+                cp_async16(ks + row * KROW + c8 * 8, a.kc + off, in ? 16 : 0);
+                cp_async16(vs + row * HD + c8 * 8, a.vc + off, in ? 16 : 0);
+            }
+        cp_async_commit();
+    };
     griddep_wait();
     griddep_launch_dependents();
+#pragma unroll
+    for (int p = 0; p < ATTC_STAGES - 1; p++) issue_tile(k0 + p * ATTC_TK, p);
     for (int i = tid; i < n_rows * (HD / 4); i += ATTC_THREADS) {
         const int r = i / (HD / 4), c4 = i - r * (HD / 4);
         const int m = m_first + r / rep, h = g * rep + r % rep;
@@ -431,21 +456,13 @@ __global__ void __launch_bounds__(ATTC_THREADS) k_attn_chunk(AttnChunkArgs a) {
 #pragma unroll
         for (int d = 0; d < DPL; d++) o[rr][d] = 0.f;
     }
-    const int T = a.pos0 + m_first + qt;  // keys the tile's last token sees
-    for (int tt = 0; tt < T; tt += ATTC_TK) {
+    int it = 0;
+    for (int tt = k0; tt < k1; tt += ATTC_TK, it++) {
+        issue_tile(tt + (ATTC_STAGES - 1) * ATTC_TK, (it + ATTC_STAGES - 1) % ATTC_STAGES);
+        cp_async_wait_group<ATTC_STAGES - 1>();
         __syncthreads();
-        for (int i = tid; i < ATTC_TK * (HD / 8); i += ATTC_THREADS) {
-            const int row = i / (HD / 8), c8 = i - row * (HD / 8);
-            int4 kk = make_int4(0, 0, 0, 0), vv = kk;
-            if (tt + row < T) {
-                const size_t off = (size_t)(tt + row) * a.kvdim + (size_t)g * HD + c8 * 8;
-                kk = __ldcg(reinterpret_cast<const int4*>(a.kc + off));
-                vv = __ldcg(reinterpret_cast<const int4*>(a.vc + off));
-            }
-            *reinterpret_cast<int4*>(&k_s[row][c8 * 8]) = kk;
-            *reinterpret_cast<int4*>(&v_s[row][c8 * 8]) = vv;
-        }
-        __syncthreads();
+        const unsigned short* k_s = reinterpret_cast<const unsigned short*>(stages + (size_t)(it % ATTC_STAGES) * STAGE_B);
+        const unsigned short* v_s = k_s + ATTC_TK * KROW;
 #pragma unroll
         for (int rr = 0; rr < RPW; rr++) {
             const int r = warp * RPW + rr;
@@ -453,18 +470,19 @@ __global__ void __launch_bounds__(ATTC_THREADS) k_attn_chunk(AttnChunkArgs a) {
             const int last_key = a.pos0 + m_first + r / rep;  // causal limit of this row
             if (tt > last_key) continue;
             float acc = 0.f;
+            const unsigned short* kr = k_s + lane * KROW;
 #pragma unroll 4
             for (int d = 0; d < HD; d += 8) {
-                const int4 kr = *reinterpret_cast<const int4*>(&k_s[lane][d]);
+                const int4 kw = *reinterpret_cast<const int4*>(kr + d);
                 const float4 qa = *reinterpret_cast<const float4*>(&q_s[r][d]), qb = *reinterpret_cast<const float4*>(&q_s[r][d + 4]);
-                const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kr.x)), k1 = __half22float2(*reinterpret_cast<const __half2*>(&kr.y));
-                const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kr.z)), k3 = __half22float2(*reinterpret_cast<const __half2*>(&kr.w));
-                acc += qa.x * k0.x + qa.y * k0.y;
-                acc += qa.z * k1.x + qa.w * k1.y;
-                acc += qb.x * k2.x + qb.y * k2.y;
-                acc += qb.z * k3.x + qb.w * k3.y;
+                const float2 k0f = __half22float2(*reinterpret_cast<const __half2*>(&kw.x)), k1f = __half22float2(*reinterpret_cast<const __half2*>(&kw.y));
+                const float2 k2f = __half22float2(*reinterpret_cast<const __half2*>(&kw.z)), k3f = __half22float2(*reinterpret_cast<const __half2*>(&kw.w));
+                acc += qa.x * k0f.x + qa.y * k0f.y;
+                acc += qa.z * k1f.x + qa.w * k1f.y;
+                acc += qb.x * k2f.x + qb.y * k2f.y;
+                acc += qb.z * k3f.x + qb.w * k3f.y;
             }
-            const bool seen = tt + lane <= last_key;
+            const bool seen = tt + lane <= last_key && tt + lane < k1;
             const float sc = seen ? acc * a.scale : -1e30f;
             const float m_new = fmaxf(mx[rr], warp_max(sc));
             const float p = seen ? expf(sc - m_new) : 0.f;
@@ -473,11 +491,11 @@ __global__ void __launch_bounds__(ATTC_THREADS) k_attn_chunk(AttnChunkArgs a) {
             mx[rr] = m_new;
 #pragma unroll
             for (int d = 0; d < DPL; d++) o[rr][d] *= alpha;
-            const int n_keys = min(ATTC_TK, last_key - tt + 1);
+            const int n_keys = min(min(ATTC_TK, k1 - tt), last_key - tt + 1);
             for (int key = 0; key < n_keys; key++) {
                 const float pk = __shfl_sync(TFR_FULL_MASK, p, key);
                 if (DPL == 4) {
-                    const uint2 vv = *reinterpret_cast<const uint2*>(&v_s[key][lane * 4]);
+                    const uint2 vv = *reinterpret_cast<const uint2*>(v_s + key * HD + lane * 4);
                     const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&vv.x)), v1 = __half22float2(*reinterpret_cast<const __half2*>(&vv.y));
                     o[rr][0] += pk * v0.x;
                     o[rr][1] += pk * v0.y;
@@ -486,24 +504,56 @@ __global__ void __launch_bounds__(ATTC_THREADS) k_attn_chunk(AttnChunkArgs a) {
                 } else {
 #pragma unroll
                     for (int d = 0; d < DPL; d += 2) {
-                        const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&v_s[key][lane * DPL + d]));
+                        const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(v_s + key * HD + lane * DPL + d));
                         o[rr][d] += pk * v0.x;
                         o[rr][d + 1] += pk * v0.y;
                     }
                 }
             }
         }
+        __syncthreads();  // the stage is refilled at the top of the next iteration
     }
+    cp_async_wait_all();
 #pragma unroll
     for (int rr = 0; rr < RPW; rr++) {
         const int r = warp * RPW + rr;
         if (r >= n_rows) break;
         const int m = m_first + r / rep, h = g * rep + r % rep;
-        const float inv = 1.f / fmaxf(ls[rr], 1e-20f);
-        float* dst = a.out + (size_t)m * a.ldq + (size_t)h * HD + lane * DPL;
+        if (a.S == 1) {
+            const float inv = 1.f / fmaxf(ls[rr], 1e-20f);
+            float* dst = a.out + (size_t)m * a.ldq + (size_t)h * HD + lane * DPL;
 #pragma unroll
-        for (int d = 0; d < DPL; d++) dst[d] = o[rr][d] * inv;
+            for (int d = 0; d < DPL; d++) dst[d] = o[rr][d] * inv;
+        } else {
+            float* dst = a.partial + (((size_t)m * a.n_head + h) * a.S + sp) * (2 + HD);
+            if (lane == 0) {
+                dst[0] = mx[rr];
+                dst[1] = ls[rr];
+            }
+#pragma unroll
+            for (int d = 0; d < DPL; d++) dst[2 + lane * DPL + d] = o[rr][d];
+        }
     }
+}
+
+// out[row][d] = sum_s exp(m_s - m) O_s[d] / max(sum_s exp(m_s - m) l_s, 1e-20) over the S partials of a row
+// (kernels/attn/flash.cu:236-254).  One CTA of hd threads per (token, head) row.
+__global__ void k_attn_chunk_merge(const float* partial, float* out, int S, int hd, int n_head, int ldq) {
+    const int row = blockIdx.x, d = threadIdx.x;
+    griddep_wait();
+    griddep_launch_dependents();
+    const float* pb = partial + (size_t)row * S * (2 + hd);
+    float m = -1e30f;
+    for (int s = 0; s < S; s++) m = fmaxf(m, pb[(size_t)s * (2 + hd)]);
+    float l = 0.f, acc = 0.f;
+    for (int s = 0; s < S; s++) {
+        const float* p = pb + (size_t)s * (2 + hd);
+        const float al = expf(p[0] - m);
+        l += al * p[1];
+        acc += al * p[2 + d];
+    }
+    const int tok = row / n_head, h = row - tok * n_head;
+    out[(size_t)tok * ldq + (size_t)h * hd + d] = acc / fmaxf(l, 1e-20f);
 }
 
 // ------------------------------------------------------------------ greedy token of every row

@@ -180,7 +180,7 @@ struct tfr_engine {
     int chunk_tokens = CHUNK_MAX_TOKENS;  // 0: every token of a prompt is a decode step
     bool chunk_ok = false;
     std::string chunk_why;
-    float *cx = nullptr, *cq = nullptr, *cattn = nullptr, *ch = nullptr, *cxn = nullptr, *clogits = nullptr;
+    float *cx = nullptr, *cq = nullptr, *cattn = nullptr, *ch = nullptr, *cxn = nullptr, *clogits = nullptr, *cpart = nullptr;
     unsigned char* cact = nullptr;
     size_t cact_stride = 0;
 };
@@ -283,6 +283,7 @@ static void configure_kernels_once() {
     configure_kernel(k_attn_chunk<128>, true);
     configure_kernel(k_attn_chunk<256>, true);
     configure_kernel(k_prep_rows, false);
+    configure_kernel(k_attn_chunk_merge, false);
     // the attention kernel also has static shared memory: ask for exactly the dynamic part it uses
     configure_kernel(k_attn_decode<64>, false);
     configure_kernel(k_attn_decode<128>, false);
@@ -567,7 +568,7 @@ extern "C" void tfr_destroy(tfr_engine* e) {
     for (auto& kv : e->vecs) cudaFree(kv.second.dev);
     for (auto& L : e->layers) cudaFree(L.bias_qkv);
     void* ws[] = {e->x, e->q, e->attn, e->h, e->logits, e->partial, e->counters, e->st, e->out_tokens, e->prompt,
-                  e->layer_taps, e->tap_attn, e->tap_mid, e->tap_h, e->proj, e->qgate, e->loop_layers, e->loop_bar, e->loop_best, e->loop_vec, e->cx, e->cq, e->cattn, e->ch, e->cxn, e->clogits, e->cact, e->loop_blob, e->loop_head_tasks};
+                  e->layer_taps, e->tap_attn, e->tap_mid, e->tap_h, e->proj, e->qgate, e->loop_layers, e->loop_bar, e->loop_best, e->loop_vec, e->cx, e->cq, e->cattn, e->ch, e->cxn, e->clogits, e->cpart, e->cact, e->loop_blob, e->loop_head_tasks};
     for (void* p : ws) cudaFree(p);
     if (e->st_host) cudaFreeHost(e->st_host);
     if (e->out_host) cudaFreeHost(e->out_host);
@@ -1581,6 +1582,7 @@ static int chunk_buffers(tfr_engine* e) {
     CU(e, cudaMalloc(&e->ch, (size_t)M * P.ff * 4));
     CU(e, cudaMalloc(&e->cact, (size_t)M * e->cact_stride));
     CU(e, cudaMalloc(&e->clogits, (size_t)CHUNK_VERIFY_MAX * e->head->m.N * 4));
+    CU(e, cudaMalloc(&e->cpart, (size_t)M * P.n_head * CHUNK_ATTN_SPLITS_MAX * (2 + e->cfg.head_dim) * 4));
     return TFR_OK;
 }
 
@@ -1642,13 +1644,24 @@ static int forward_chunk(tfr_engine* e, const tfr_kv* kv, const int* tok, int M,
             a.scale = 1.0f / sqrtf((float)hd);  // forward.rs:389
             const int rep = P.n_head / P.n_kv;
             a.QT = std::max(1, ATTC_ROWS_MAX / rep);
-            const dim3 grid(P.n_kv, (M + a.QT - 1) / a.QT);
+            const int q_tiles = (M + a.QT - 1) / a.QT;
+            // key splits: enough CTAs for every SM, never less than eight key tiles (256 keys) per split
+            const int tiles_max = (pos0 + M + ATTC_TK - 1) / ATTC_TK;
+            a.S = std::max(1, std::min(std::min(CHUNK_ATTN_SPLITS_MAX, tiles_max / 8), (2 * cap + P.n_kv * q_tiles - 1) / (P.n_kv * q_tiles)));
+            a.partial = e->cpart;
+            const dim3 grid(P.n_kv, q_tiles, a.S);
             const size_t smem = attn_chunk_smem(hd);
             cudaError_t r = hd == 64    ? launch_pdl(k_attn_chunk<64>, grid, dim3(ATTC_THREADS), smem, s, a)
                             : hd == 128 ? launch_pdl(k_attn_chunk<128>, grid, dim3(ATTC_THREADS), smem, s, a)
                                         : launch_pdl(k_attn_chunk<256>, grid, dim3(ATTC_THREADS), smem, s, a);
             if (r != cudaSuccess) return -1;
             n++;
+            if (a.S > 1) {
+                if (launch_pdl(k_attn_chunk_merge, dim3(M * P.n_head), dim3(hd), 0, s, (const float*)e->cpart, e->cattn, a.S, hd, P.n_head,
+                               nq) != cudaSuccess)
+                    return -1;
+                n++;
+            }
         }
         // 3. Q8 + o-proj + residual
         if (prep(e->cattn, P.attn_width, P.attn_width, nullptr, nullptr) != cudaSuccess) return -1;
