@@ -381,11 +381,15 @@ def tensor_parallel_32b(rank, world, local, dist, steps: int = 8, warmup: int = 
     kv.free()
     model.destroy()
     # the same bytes on ONE GPU (rank 0), fed the tensor-parallel engine's own tokens: its greedy choice must be the
-    # token the tensor-parallel engine emitted wherever its top-2 margin is not small
-    check = {"ranks_agree": ranks_agree, "compared_with_one_gpu": 0, "mismatches_beyond_margin": 0}
+    # token the tensor-parallel engine emitted wherever its top-2 margin is not small.  "Small" is set by what two
+    # correct implementations show at this depth: after 36 layers the reference's own two FFN kernels move the logits
+    # by 4.7e-2 of the largest logit (tests/test_engine_gpu.py, full-depth test), so a margin below 0.2 of the largest
+    # logit decides nothing at 64 layers.
+    check = {"ranks_agree": ranks_agree, "compared_with_one_gpu": 0, "equal": 0, "mismatches_within_margin": 0,
+             "mismatches_beyond_margin": 0, "margin_gate": "0.2 x largest logit of the position"}
     if world > 1:
         n_cmp = 48
-        bad = 0
+        counts = [0, 0, 0]
         if rank == 0:
             single, _ = synth_gpu.build_model(cfg, seed=0, device=local, context_length=ctx)
             kv1 = single.alloc_kv(ctx)
@@ -393,16 +397,18 @@ def tensor_parallel_32b(rank, world, local, dist, steps: int = 8, warmup: int = 
             fed = [int(first)] + tp_tokens[:n_cmp - 1]
             for i, t in enumerate(fed):
                 nxt = single.forward_greedy([t], kv1)
-                if nxt != tp_tokens[i]:
-                    top = np.sort(single.current_logits())[-2:]
-                    if float(top[1] - top[0]) > 1e-2 * max(1.0, float(np.abs(top[1]))):
-                        bad += 1
+                if nxt == tp_tokens[i]:
+                    counts[0] += 1
+                    continue
+                lg = single.current_logits()
+                top = np.sort(lg)[-2:]
+                counts[1 if float(top[1] - top[0]) <= 0.2 * float(np.abs(lg).max()) else 2] += 1
             kv1.free()
             single.destroy()
-        flag = torch.tensor([bad], dtype=torch.int64, device="cuda")
+        flag = torch.tensor(counts, dtype=torch.int64, device="cuda")
         dist.broadcast(flag, src=0)
         check["compared_with_one_gpu"] = n_cmp
-        check["mismatches_beyond_margin"] = int(flag[0])
+        check["equal"], check["mismatches_within_margin"], check["mismatches_beyond_margin"] = (int(v) for v in flag)
     tokens_match = bool(check["ranks_agree"] and check["mismatches_beyond_margin"] == 0)
     wbytes = synth_gpu.weight_bytes(cfg) + synth_gpu.kv_bytes_per_position(cfg) * (prompt_len + n_decode / 2)
     return {"workload": text, "parallelism": f"tp{world}" if world > 1 else "single GPU", "scaling": "strong",

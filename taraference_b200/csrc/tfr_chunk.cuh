@@ -214,7 +214,7 @@ struct GemmGeom {
 
 template <class BLK>
 __global__ void __launch_bounds__(GEMV_THREADS, 1)
-k_gemm_q8(const unsigned char* act_g, const float* xn, RowJob ja, RowJob jb, F32Seg fseg, ChunkEpi epi, GemmGeom g) {
+k_gemm_q8(const unsigned char* act_g, const float* xn, RowJob ja, RowJob jb, F32Seg fseg, ChunkEpi epi, GemmGeom g, TokenState* st) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, cta = blockIdx.x;
     const int K = g.K, nb = K >> 8, Mt = g.Mt, nsw = g.nsw, wa = g.wa;
@@ -256,7 +256,9 @@ k_gemm_q8(const unsigned char* act_g, const float* xn, RowJob ja, RowJob jb, F32
 
     const int G = Mt >= 8 ? 8 : (Mt >= 4 ? 4 : (Mt >= 2 ? 2 : 1));  // token groups of the row-sum phase
     const int gw = GEMV_WARPS / G, grp = warp / gw, wig = warp % gw;
-    bool ok = true;
+    bool ok = true, dead = false;  // dead: this warp saw a copy time out and takes no further tiles
+    int late_slot = -1;
+    unsigned late_parity = 0;
     for (int grp_i = 0; grp_i < n_groups; grp_i++) {
         const int m0 = grp_i * Mt, mt = min(Mt, g.M - m0);
         // the Q8 activations of tokens m0 .. m0 + mt - 1
@@ -307,21 +309,32 @@ k_gemm_q8(const unsigned char* act_g, const float* xn, RowJob ja, RowJob jb, F32
             }
         }
         // phase A: per-block partials of every token out of the tiles
-        for (int i = 0; i < ntw; i++) {
+        for (int i = 0; i < ntw && !dead; i++) {
             const int k = grp_i * ntw + i, j = warp + wa * i, s = k % nsw;
             const bool is_b = j >= tiles_a;
             const long long f = (long long)(is_b ? tb0 + (j - tiles_a) : ta0 + j) * 32 + lane;
             const bool mine = is_b ? (f >= fb0 && f < fb1) : (f >= fa0 && f < fa1);
-            ok = mbar_wait(wfull + s, (unsigned)((k / nsw) & 1)) && ok;
+            // a copy that did not land within the wait limit: its tile is not read, the error word marks the call invalid
+            // and the warp stops issuing; it waits for that copy once more before the CTA leaves
+            const bool landed = mbar_wait(wfull + s, (unsigned)((k / nsw) & 1));
+            if (!landed) {
+                ok = false;
+                late_slot = s;
+                late_parity = (unsigned)((k / nsw) & 1);
+            }
             if (mine) {
                 const int off = is_b ? rows_a * nb + (int)(f - fb0) : (int)(f - fa0);
                 const int b = (int)(f % nb);
                 for (int m = 0; m < mt; m++) {
                     const Act act = act_carve(act_s + (size_t)m * g.act_b16, K, false, false);
-                    pbuf[(size_t)m * g.pbuf_floats + off] = block_dot<true>(BLK{}, wring + (size_t)s * TB, lane, act, b, nb, nullptr);
+                    pbuf[(size_t)m * g.pbuf_floats + off] = landed ? block_dot<true>(BLK{}, wring + (size_t)s * TB, lane, act, b, nb, nullptr) : 0.f;
                 }
             }
             __syncwarp();
+            if (!landed) {
+                dead = true;
+                break;
+            }
             if (lane == 0 && k + nsw < uses) {
                 fence_proxy_async();
                 issue(k + nsw);
@@ -342,7 +355,8 @@ k_gemm_q8(const unsigned char* act_g, const float* xn, RowJob ja, RowJob jb, F32
         }
         __syncthreads();
     }
-    (void)ok;  // a copy that never completed leaves wrong rows; the caller's parity checks would show it
+    if (!ok && st) st->err = 2;
+    if (late_slot >= 0) mbar_wait(wfull + late_slot, late_parity);  // bounded: a second limit, then the CTA leaves regardless
 }
 
 struct GemmLaunch {
@@ -381,11 +395,11 @@ inline GemmLaunch gemm_plan(int tile_bytes, int M, int K, const RowJob& ja, cons
 
 template <class BLK>
 inline cudaError_t launch_gemm(cudaStream_t stream, int grid, const unsigned char* act_g, size_t act_stride, const float* xn, int M,
-                               const RowJob& ja, const RowJob& jb, const F32Seg& fseg, const ChunkEpi& epi, int K) {
+                               const RowJob& ja, const RowJob& jb, const F32Seg& fseg, const ChunkEpi& epi, int K, TokenState* st) {
     GemmLaunch L = gemm_plan(BLK::TILE_BYTES, M, K, ja, jb, fseg.m.data != nullptr);
     if (!L.fits) return cudaErrorInvalidValue;
     L.g.act_stride = act_stride;
-    return launch_pdl(k_gemm_q8<BLK>, dim3(grid), dim3(GEMV_THREADS), L.smem, stream, act_g, xn, ja, jb, fseg, epi, L.g);
+    return launch_pdl(k_gemm_q8<BLK>, dim3(grid), dim3(GEMV_THREADS), L.smem, stream, act_g, xn, ja, jb, fseg, epi, L.g, st);
 }
 
 // ------------------------------------------------------------------ causal attention of a chunk

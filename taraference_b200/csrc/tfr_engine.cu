@@ -1587,10 +1587,10 @@ static int chunk_buffers(tfr_engine* e) {
 }
 
 static cudaError_t launch_gemm_typed(cudaStream_t s, int grid, int type, const unsigned char* act, size_t stride, const float* xn, int M,
-                                     const RowJob& ja, const RowJob& jb, const F32Seg& fseg, const ChunkEpi& epi, int K) {
-    if (type == TFR_Q4_K) return launch_gemm<BlockQ4>(s, grid, act, stride, xn, M, ja, jb, fseg, epi, K);
-    if (type == TFR_Q8_0) return launch_gemm<BlockQ8>(s, grid, act, stride, xn, M, ja, jb, fseg, epi, K);
-    return launch_gemm<BlockQ6>(s, grid, act, stride, xn, M, ja, jb, fseg, epi, K);
+                                     const RowJob& ja, const RowJob& jb, const F32Seg& fseg, const ChunkEpi& epi, int K, TokenState* st) {
+    if (type == TFR_Q4_K) return launch_gemm<BlockQ4>(s, grid, act, stride, xn, M, ja, jb, fseg, epi, K, st);
+    if (type == TFR_Q8_0) return launch_gemm<BlockQ8>(s, grid, act, stride, xn, M, ja, jb, fseg, epi, K, st);
+    return launch_gemm<BlockQ6>(s, grid, act, stride, xn, M, ja, jb, fseg, epi, K, st);
 }
 
 // M tokens (device ids at tok) at positions pos0 .. pos0 + M - 1 through all layers: their K / V rows land in the
@@ -1633,7 +1633,7 @@ static int forward_chunk(tfr_engine* e, const tfr_kv* kv, const int* tok, int M,
             ep.out = e->cq, ep.ldo = nq, ep.bias = L.bias_qkv;
             ep.kc = kv_k(kv, li), ep.vc = kv_v(kv, li);
             ep.nq = nq, ep.nk = nkv, ep.hd = hd, ep.kvdim = nkv, ep.pos0 = pos0, ep.theta = c.rope_theta;
-            if (launch_gemm<BlockQ4>(s, cap, e->cact, e->cact_stride, e->cxn, M, jq, jk, fseg, ep, K) != cudaSuccess) return -1;
+            if (launch_gemm<BlockQ4>(s, cap, e->cact, e->cact_stride, e->cxn, M, jq, jk, fseg, ep, K, e->st) != cudaSuccess) return -1;
             n++;
         }
         // 2. causal attention over the cache (rows of this chunk included)
@@ -1666,7 +1666,7 @@ static int forward_chunk(tfr_engine* e, const tfr_kv* kv, const int* tok, int M,
         // 3. Q8 + o-proj + residual
         if (prep(e->cattn, P.attn_width, P.attn_width, nullptr, nullptr) != cudaSuccess) return -1;
         if (launch_gemm_typed(s, cap, L.wo->m.type, e->cact, e->cact_stride, nullptr, M, make_job(L.wo->m, 2, cap), RowJob{}, F32Seg{},
-                              store_epi(e->cx, K, K, 2), P.attn_width) != cudaSuccess)
+                              store_epi(e->cx, K, K, 2), P.attn_width, e->st) != cudaSuccess)
             return -1;
         n++;
         // 4. RMSNorm + Q8 + gate/up + SiLU*mul
@@ -1676,21 +1676,21 @@ static int forward_chunk(tfr_engine* e, const tfr_kv* kv, const int* tok, int M,
             ep.kind = CEPI_SILU;
             ep.out = e->ch, ep.ldo = FF;
             if (launch_gemm<BlockQ4>(s, cap, e->cact, e->cact_stride, nullptr, M, make_job(L.gate->m, 1, cap), make_job(L.up->m, 1, cap),
-                                     F32Seg{}, ep, K) != cudaSuccess)
+                                     F32Seg{}, ep, K, e->st) != cudaSuccess)
                 return -1;
             n++;
         }
         // 5. Q8 + down + residual
         if (prep(e->ch, FF, FF, nullptr, nullptr) != cudaSuccess) return -1;
         if (launch_gemm_typed(s, cap, L.down->m.type, e->cact, e->cact_stride, nullptr, M, make_job(L.down->m, 2, cap), RowJob{}, F32Seg{},
-                              store_epi(e->cx, K, K, 2), FF) != cudaSuccess)
+                              store_epi(e->cx, K, K, 2), FF, e->st) != cudaSuccess)
             return -1;
         n++;
     }
     if (all_rows) {
         if (prep(e->cx, K, K, e->output_norm, nullptr) != cudaSuccess) return -1;
         if (launch_gemm_typed(s, cap, e->head->m.type, e->cact, e->cact_stride, nullptr, M, make_job(e->head->m, 2, cap), RowJob{},
-                              F32Seg{}, store_epi(e->clogits, V, V, 0), K) != cudaSuccess)
+                              F32Seg{}, store_epi(e->clogits, V, V, 0), K, e->st) != cudaSuccess)
             return -1;
         k_argmax_rows<<<M, 1024, 0, s>>>(e->clogits, V, e->out_tokens);
         if (cudaGetLastError() != cudaSuccess) return -1;

@@ -532,6 +532,8 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
 
     // phase A: per-block partials out of the tiles
     bool ok = true;
+    int late_slot = -1;
+    unsigned late_parity = 0;
     if (warp < stride) {
         int it = 0;
         for (int j = warp; j < n_jobs; j += stride, it++) {
@@ -539,12 +541,26 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
             const bool is_b = j >= tiles_a;
             const long long f = (long long)(is_b ? tb0 + (j - tiles_a) : ta0 + j) * 32 + lane;
             const bool mine = is_b ? (f >= fb0 && f < fb1) : (f >= fa0 && f < fa1);
-            ok = mbar_wait(full + s, reuse ? (it & 1) : 0) && ok;
+            // A copy that did not land within the wait limit: the tile is NOT read (its partials become zero and the
+            // error word marks the step invalid), the slot is not refilled, and the warp waits for that copy once
+            // more before the CTA may leave (below), so shared memory is never released under a copy in flight.
+            const bool landed = mbar_wait(full + s, reuse ? (it & 1) : 0);
+            if (!landed) {
+                ok = false;
+                late_slot = s;
+                late_parity = reuse ? (it & 1) : 0;
+            }
             if (mine) {
                 float* dst = is_b ? part_b + (f - fb0) : part_a + (f - fa0);
-                *dst = block_dot<true>(BLK{}, ring + (size_t)s * TB, lane, act, (int)(f % nb), nb, nullptr);
+                *dst = landed ? block_dot<true>(BLK{}, ring + (size_t)s * TB, lane, act, (int)(f % nb), nb, nullptr) : 0.f;
             }
             __syncwarp();
+            if (!landed) {
+                // without slot reuse the warp's later tiles were requested at kernel entry: let them land (bounded)
+                if (!reuse)
+                    for (int j2 = j + stride; j2 < n_jobs; j2 += stride) mbar_wait(full + j2, 0);
+                break;
+            }
             if (reuse && lane == 0 && j + stride < n_jobs) {
                 fence_proxy_async();
                 issue(j + stride);
@@ -563,6 +579,7 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
         if (rows_b > 0) reduce_rows<EPI_PAIRS>(part_b, part_b, rows_b, nb, jb.id_base + (rows_b0 >> 1), epi);
     }
     epi.end(st);
+    if (late_slot >= 0) mbar_wait(full + late_slot, late_parity);  // bounded: a second limit, then the CTA leaves regardless
     prof_mark(5, pa.prof_id);
 }
 

@@ -160,3 +160,66 @@ def test_tp_config_errors(cuda_lib):
     with pytest.raises(E.TfrError, match="dense"):
         m.set_config(dict(S.TINY_HYBRID, tp_rank=0, tp_size=2))
     m.destroy()
+
+
+def test_one_process_drives_two_gpus_through_attached_pointers(cuda_lib):
+    """Two engines on two GPUs in ONE process, wired with tfr_tp_local_pointer / tfr_tp_attach_pointers (no IPC
+    handles, no process group).  Every forward call needs both ranks at the same time, so each engine is driven
+    by its own host thread.  The ranks must emit identical tokens, equal to the single-GPU engine's wherever that
+    engine's margin is large."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import threading
+    from taraference_b200 import engine as E
+    from test_engine_gpu import margin_gated_equal
+    tens = S.make_model(TP_CFG, seed=4)
+    models = [E.CudaModel.load_with(dict(TP_CFG, tp_rank=r, tp_size=2), tens, device=r) for r in range(2)]
+    with pytest.raises(E.TfrError, match="not connected"):
+        kv_bad = models[0].alloc_kv(8)
+        try:
+            models[0].forward_greedy([1], kv_bad)
+        finally:
+            kv_bad.free()
+    bases = [m.tp_local_pointer() for m in models]
+    for m in models:
+        m.tp_attach_pointers(bases)
+    kvs = [m.alloc_kv(64) for m in models]
+    results = [None, None]
+
+    def run(r):
+        try:
+            torch.cuda.set_device(r)
+            nxt = models[r].forward_greedy(PROMPT, kvs[r])
+            toks = models[r].decode_burst(nxt, 20, kvs[r])
+            results[r] = (nxt, [int(t) for t in toks], models[r].debug_read("x", TP_CFG["n_embd"]))
+        except Exception as exc:  # surfaced by the assertions below
+            results[r] = exc
+
+    threads = [threading.Thread(target=run, args=(r,)) for r in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=120)
+    assert not any(t.is_alive() for t in threads), "a rank did not return"
+    for r in results:
+        assert not isinstance(r, Exception), r
+    assert results[0][0] == results[1][0] and results[0][1] == results[1][1]
+    assert np.array_equal(results[0][2], results[1][2])  # the replicated residual stream, bit for bit
+    torch.cuda.set_device(0)
+    single = E.CudaModel.load_with(TP_CFG, tens, device=0)
+    kv1 = single.alloc_kv(64)
+    n1 = single.forward_greedy(PROMPT, kv1)
+    margins, want, t = [], [], n1
+    for _ in range(20):
+        t = single.forward_greedy([t], kv1)
+        top = np.sort(single.current_logits())[-2:]
+        want.append(t)
+        margins.append(float(top[1] - top[0]))
+    if results[0][0] == n1:
+        assert margin_gated_equal(results[0][1], want, margins), (results[0][1], want, margins)
+    kv1.free()
+    single.destroy()
+    for kv in kvs:
+        kv.free()
+    for m in models:
+        m.destroy()
