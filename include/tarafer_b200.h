@@ -20,6 +20,11 @@
 #include <stddef.h>
 #include <stdint.h>
 
+/* Two builds come from the same sources.  libtarafer_b200.so is the product: the decode path, the loader, the stand-alone
+ * operators and the read-only taps (tfr_debug_read).  libtarafer_b200_aids.so (-DTFR_TEST_AIDS) adds what only tests,
+ * the timeline tool and the benchmark's model builder need: in-kernel timeline probes, the integer-contract taps, the
+ * KV-store rounding as an operator and the synthetic K-quant quantiser.  Declarations of the second kind sit inside
+ * #ifdef TFR_TEST_AIDS below. */
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -226,15 +231,21 @@ int tfr_debug_read(tfr_engine* e, tfr_kv* kv, const char* what, int layer, void*
 /* Test aid: when device_buffer != NULL, thread 0 of every CTA of the matrix-vector and attention kernels stores the
  * GPU nanosecond timer at up to eight points into device_buffer[(launch * 160 + cta) * 8 + point], launch =
  * index of the kernel within the decode step (0 for the stand-alone operators). */
+#ifdef TFR_TEST_AIDS
 int tfr_debug_set_timeline(unsigned long long* device_buffer);
+#endif
 
 /* Test aid: dst[i] = the f16 bits the KV store writes for src[i] (crates/core/src/cuda/kernels/common.cu:9-38), over n
  * device floats; lets a test walk all 2^32 inputs against the reference's copy_kv_f16. */
+#ifdef TFR_TEST_AIDS
 int tfr_debug_f32_to_f16(const float* src, uint16_t* dst, int64_t n, void* stream);
+#endif
 /* Test aid for the persistent loop: during decode step `step` of the next calls, thread 0 of every CTA stores the
  * GPU nanosecond timer at successive points of the step into device_buffer[point * n_sm + cta] (point < points).
  * device_buffer == NULL switches it off. */
+#ifdef TFR_TEST_AIDS
 int tfr_debug_set_loop_timeline(tfr_engine* e, unsigned long long* device_buffer, int step, int points);
+#endif
 
 /* ---- operator level (device pointers unless stated; stream = cudaStream_t or NULL) ---- */
 
@@ -264,11 +275,15 @@ int tfr_ffn_block_host(const tfr_mat* gate, const tfr_mat* up, const tfr_mat* do
 /* Integer contract taps (test aid, no reference kernel exposes these): for Q4_K, a = I[N][K/32]
  * and b = S[N][K/32] of kernels/gemv.cu:71-130; for Q6_K, a = J[N][K/16] of gemv.cu:302-337; for Q8_0,
  * a = the per-32-block sums [N][K/32] of gemv.cu:1558-1582. */
+#ifdef TFR_TEST_AIDS
 int tfr_op_int_dots(const tfr_mat* w, const int8_t* q8, const float* d8, int32_t* a, int32_t* b, void* stream);
+#endif
 /* The same taps with the activation given as fp32 x[K]: it is quantised by the quantiser the matrix-vector kernels run
  * (kernels/gemv.cu:16-65 semantics), q8_out (optional, K bytes) receives the int8 values the block dots then read, and
  * b (Q4_K) the 32-group sums exactly as the dots' activation record holds them. */
+#ifdef TFR_TEST_AIDS
 int tfr_op_int_dots_x(const tfr_mat* w, const float* x, int32_t* a, int32_t* b, int8_t* q8_out, void* stream);
+#endif
 /* attn_flash_partial + attn_flash_reduce, kernels/attn/flash.cu:16-255, for one query token
  * at position pos over cache rows [0, pos].  kc / vc: [max_seq][n_kv*head_dim] f16 bits.  The split-KV scratch
  * of this stand-alone call is one buffer per device, grown on demand: calls that overlap on the same GPU
@@ -326,7 +341,9 @@ int tfr_transcode_to_q8_0(int src_type, const void* raw, size_t nbytes, void* ou
 
 /* Synthetic-model aid (no counterpart in the reference, which has no quantiser): quantise
  * fp32 rows [N][K] on the device into GGUF Q4_K / Q6_K bytes. */
+#ifdef TFR_TEST_AIDS
 int tfr_synth_quantize(int ggml_type, const float* w, int64_t n_rows_k, int64_t n_cols_n, void* out_bytes, void* stream);
+#endif
 
 #ifdef __cplusplus
 }

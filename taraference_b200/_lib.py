@@ -6,7 +6,7 @@ import ctypes as C
 import re
 from pathlib import Path
 
-from .build import LIB, PKG
+from .build import AIDS_LIB, LIB, PKG
 
 HEADER = PKG.parent / "include" / "tarafer_b200.h"
 
@@ -20,23 +20,64 @@ class ModelConfig(C.Structure):
                                          "tp_rank", "tp_size")]
 
 
-def declared_symbols() -> list[str]:
-    """Every function name the public header declares."""
+def _header_split() -> tuple[list[str], list[str]]:
     text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
-    return sorted(set(re.findall(r"\b(tfr_[a-z0-9_]+)\s*\(", text)))
+    aids_blocks = re.findall(r"#ifdef TFR_TEST_AIDS(.*?)#endif", text, flags=re.S)
+    aids = sorted(set(re.findall(r"\b(tfr_[a-z0-9_]+)\s*\(", "\n".join(aids_blocks))))
+    everything = sorted(set(re.findall(r"\b(tfr_[a-z0-9_]+)\s*\(", text)))
+    return [n for n in everything if n not in aids], aids
+
+
+def declared_symbols() -> list[str]:
+    """Every function name the public header declares for the product library."""
+    return _header_split()[0]
+
+
+def declared_aid_symbols() -> list[str]:
+    """The function names declared inside #ifdef TFR_TEST_AIDS: exported by the instrumented build only."""
+    return _header_split()[1]
 
 
 _lib = None
+AID_NAMES = ("tfr_debug_set_timeline", "tfr_debug_set_loop_timeline", "tfr_debug_f32_to_f16", "tfr_op_int_dots",
+             "tfr_op_int_dots_x", "tfr_synth_quantize")
+_aids = None
+_use_aids = False
+
+
+def use_aids_build() -> None:
+    """Makes lib() return the instrumented build for this process (the timeline tool: probes live inside the kernels, so
+    the engine itself must come from that build).  Call before the first lib()."""
+    global _use_aids
+    if _lib is not None and not _use_aids:
+        raise RuntimeError("use_aids_build() must be called before the library is first loaded")
+    _use_aids = True
 
 
 def lib() -> C.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not LIB.exists():
-        raise RuntimeError(f"{LIB} is not built; run `python -m taraference_b200.build` (needs nvcc). "
+    l = _load(AIDS_LIB if _use_aids else LIB, with_aids=_use_aids)
+    _lib = l
+    return l
+
+
+def aids() -> C.CDLL:
+    """The instrumented build, loaded beside the product library for the entry points only it has (integer taps,
+    KV-store rounding operator, synthetic quantiser).  Handles of stand-alone matrices (tfr_mat) are plain data and may
+    cross between the two; engines may not."""
+    global _aids
+    if _aids is None:
+        _aids = lib() if _use_aids else _load(AIDS_LIB, with_aids=True)
+    return _aids
+
+
+def _load(path: Path, with_aids: bool) -> C.CDLL:
+    if not path.exists():
+        raise RuntimeError(f"{path} is not built; run `python -m taraference_b200.build` (needs nvcc). "
                            "There is no CPU fallback.")
-    l = C.CDLL(str(LIB))
+    l = C.CDLL(str(path))
     vp, i32, i64, f32, sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
     sig = {
         "tfr_create": (i32, [i32, C.POINTER(vp)]),
@@ -118,7 +159,8 @@ def lib() -> C.CDLL:
         "tfr_synth_quantize": (i32, [i32, vp, i64, i64, vp, vp]),
     }
     for name, (res, args) in sig.items():
+        if name in AID_NAMES and not with_aids:
+            continue
         fn = getattr(l, name)
         fn.restype, fn.argtypes = res, args
-    _lib = l
     return l

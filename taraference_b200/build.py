@@ -1,4 +1,4 @@
-"""Ahead-of-time build of libtarafer_b200.so for sm_100a (no JIT at run time).
+"""Ahead-of-time build of libtarafer_b200.so and its instrumented twin for sm_100a (no JIT at run time).
 
 The reference compiles its kernels with NVRTC when a model is loaded
 (crates/core/src/cuda/device.rs:96-122); this library ships compiled sm_100a code instead.
@@ -15,7 +15,8 @@ from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
-LIB = PKG / "libtarafer_b200.so"
+LIB = PKG / "libtarafer_b200.so"            # the product: decode path, loader, operators, read-only taps
+AIDS_LIB = PKG / "libtarafer_b200_aids.so"  # the same sources with -DTFR_TEST_AIDS: timeline probes, integer taps, quantiser
 SOURCES = [CSRC / "tfr_engine.cu", CSRC / "tfr_gguf.cpp"]
 HEADERS = sorted(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "tarafer_b200.h"]
 
@@ -24,26 +25,32 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a",
 
 
 def is_stale() -> bool:
-    if not LIB.exists():
-        return True
-    t = LIB.stat().st_mtime
-    return any(p.stat().st_mtime > t for p in SOURCES + HEADERS)
+    for lib in (LIB, AIDS_LIB):
+        if not lib.exists():
+            return True
+        t = lib.stat().st_mtime
+        if any(p.stat().st_mtime > t for p in SOURCES + HEADERS):
+            return True
+    return False
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the library in-tree if sources are newer than the binary."""
+    """Compile both libraries in-tree (side by side) if sources are newer than the binaries."""
     if not force and not is_stale():
         return LIB
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-    cmd = [nvcc, *NVCC_FLAGS, "-o", str(LIB), *map(str, SOURCES)]
-    if verbose:
-        cmd.insert(1, "-Xptxas=-v")
-    env = dict(os.environ)
-    r = subprocess.run(cmd, capture_output=True, text=True, env=env)
-    if r.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + r.stdout + r.stderr)
-    if verbose:
-        print(r.stderr)
+    procs = []
+    for lib, extra in ((LIB, []), (AIDS_LIB, ["-DTFR_TEST_AIDS"])):
+        cmd = [nvcc, *NVCC_FLAGS, *extra, "-o", str(lib), *map(str, SOURCES)]
+        if verbose:
+            cmd.insert(1, "-Xptxas=-v")
+        procs.append((lib, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=dict(os.environ))))
+    for lib, pr in procs:
+        out, err = pr.communicate()
+        if pr.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {lib.name}:\n" + out + err)
+        if verbose:
+            print(err)
     return LIB
 
 

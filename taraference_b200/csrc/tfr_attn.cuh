@@ -53,6 +53,7 @@ struct AttnArgs {
     int n_head, n_kv, S, min_keys;
     float scale;
     int pos;                    // used when st == nullptr
+    int staged;                 // 1: the launch carries the dynamic shared memory of the long-split route (attn_dyn_smem)
     int prof_id;                // timeline probe: which launch of the token this is (test aid)
 };
 
@@ -135,7 +136,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
     // Rows of earlier positions do not depend on the previous kernel: the first tile's are requested before
     // the grid-dependency wait, so their latency hides behind the kernel boundary.
     // A split with many keys stages its tiles in shared memory instead (below): no register preload then.
-    const bool long_path = t1 - t0 > ATTN_LONG_MIN;
+    const bool long_path = a.staged && t1 - t0 > ATTN_LONG_MIN;
     if (!long_path) {
         load_k(t0, min(t1, T - 1), false);
         load_v(t0, min(t1, T - 1), false);

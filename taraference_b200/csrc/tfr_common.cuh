@@ -129,8 +129,10 @@ __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.w
 __device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-// Optional timeline probe (test aid): when set, thread 0 of every CTA stores %globaltimer at eight
-// points of a kernel into g_prof[(launch id * 160 + cta) * 8 + point].
+// Optional timeline probe (test aid, only in builds with -DTFR_TEST_AIDS; the product library compiles it to nothing):
+// when set, thread 0 of every CTA stores %globaltimer at eight points of a kernel into
+// g_prof[(launch id * 160 + cta) * 8 + point].
+#ifdef TFR_TEST_AIDS
 __constant__ unsigned long long* g_prof = nullptr;
 __device__ __forceinline__ void prof_mark(int point, int kernel_id = 0) {
     if (g_prof && threadIdx.x == 0) {
@@ -139,6 +141,9 @@ __device__ __forceinline__ void prof_mark(int point, int kernel_id = 0) {
         g_prof[((size_t)kernel_id * 160 + blockIdx.y * gridDim.x + blockIdx.x) * 8 + point] = t;
     }
 }
+#else
+__device__ __forceinline__ void prof_mark(int, int = 0) {}
+#endif
 
 // Asks the memory system to bring a range into L2 (no destination, no completion to wait for).
 __device__ __forceinline__ void bulk_prefetch_l2(const void* src, unsigned int bytes) {

@@ -269,13 +269,15 @@ static void configure_kernels_once() {
     configure_kernel(k_gemv<BlockQ8, EpiStore>, true);
     configure_kernel(k_gemv<BlockQ8, EpiLogits>, true);
     configure_kernel(k_gemv<BlockQ8, EpiAllReduce>, true);
-    configure_kernel(k_int_dots<BlockQ8>, true);
     configure_kernel(k_gemv<BlockQ4, EpiAllReduce>, true);
     configure_kernel(k_gemv<BlockQ6, EpiAllReduce>, true);
     configure_kernel(k_gemv<BlockQ4, EpiLogits>, true);
     configure_kernel(k_gemv<BlockQ6, EpiLogits>, true);
+#ifdef TFR_TEST_AIDS
+    configure_kernel(k_int_dots<BlockQ8>, true);
     configure_kernel(k_int_dots<BlockQ4>, true);
     configure_kernel(k_int_dots<BlockQ6>, true);
+#endif
     configure_kernel(k_gemm_q8<BlockQ4>, true);
     configure_kernel(k_gemm_q8<BlockQ6>, true);
     configure_kernel(k_gemm_q8<BlockQ8>, true);
@@ -1249,7 +1251,7 @@ static cudaError_t launch_attention(cudaStream_t s, const AttnArgs& a, int hd, c
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(a.S, a.n_kv);
     cfg.blockDim = dim3(ATTN_THREADS);
-    cfg.dynamicSmemBytes = attn_dyn_smem(hd);
+    cfg.dynamicSmemBytes = a.staged ? attn_dyn_smem(hd) : 0;
     cfg.stream = s;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1329,6 +1331,8 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
         a.n_head = P.n_head;
         a.n_kv = P.n_kv;
         a.S = e->attn_S;
+        // short caches never reach the long-split route: launch without its shared memory (a lighter launch)
+        a.staged = kv->max_seq > e->attn_S * ATTN_LONG_MIN;
         a.min_keys = e->attn_min_keys;
         a.scale = 1.0f / sqrtf((float)hd);  // forward.rs:389
         a.prof_id = 0;
@@ -2036,6 +2040,7 @@ extern "C" int tfr_decode_path(const tfr_engine* e) {
     if (!e) return TFR_E_INVALID;
     return use_loop(e) ? 2 : 1;
 }
+#ifdef TFR_TEST_AIDS
 extern "C" int tfr_debug_set_loop_timeline(tfr_engine* e, unsigned long long* device_buffer, int step, int points) {
     if (!e) return TFR_E_INVALID;
     e->loop_prof = device_buffer;
@@ -2043,6 +2048,8 @@ extern "C" int tfr_debug_set_loop_timeline(tfr_engine* e, unsigned long long* de
     e->loop_prof_points = device_buffer ? points : 0;
     return TFR_OK;
 }
+
+#endif  // TFR_TEST_AIDS
 
 extern "C" int tfr_debug_read(tfr_engine* e, tfr_kv* kv, const char* what, int layer, void* out, size_t nbytes) {
     if (!e || !what || !out || !e->finalized) return TFR_E_INVALID;
@@ -2116,6 +2123,7 @@ extern "C" int tfr_debug_read(tfr_engine* e, tfr_kv* kv, const char* what, int l
 
 // ------------------------------------------------------------------ operator level
 
+#ifdef TFR_TEST_AIDS
 // Test aid: the KV-store rounding (f32_to_f16_bits_ref) applied to n device floats.
 __global__ void k_debug_f32_to_f16(const float* src, unsigned short* dst, long long n) {
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
@@ -2131,6 +2139,8 @@ extern "C" int tfr_debug_f32_to_f16(const float* src, uint16_t* dst, int64_t n, 
 extern "C" int tfr_debug_set_timeline(unsigned long long* device_buffer) {
     return cudaMemcpyToSymbol(g_prof, &device_buffer, sizeof(device_buffer)) == cudaSuccess ? TFR_OK : TFR_E_CUDA;
 }
+
+#endif  // TFR_TEST_AIDS
 
 static int check(cudaError_t r) { return r == cudaSuccess ? TFR_OK : TFR_E_CUDA; }
 
@@ -2213,6 +2223,7 @@ extern "C" int tfr_ffn_block_host(const tfr_mat* gate, const tfr_mat* up, const 
     return check(cudaStreamSynchronize(nullptr));
 }
 
+#ifdef TFR_TEST_AIDS
 static int int_dots_impl(const tfr_mat* w, const float* x, const int8_t* q8, const float* d8, int32_t* a, int32_t* b, int8_t* q8_out,
                          void* stream) {
     if (!w || !a || w->perm_hd) return TFR_E_INVALID;
@@ -2234,6 +2245,8 @@ extern "C" int tfr_op_int_dots_x(const tfr_mat* w, const float* x, int32_t* a, i
     if (!x) return TFR_E_INVALID;
     return int_dots_impl(w, x, nullptr, nullptr, a, b, q8_out, stream);
 }
+
+#endif  // TFR_TEST_AIDS
 
 static int op_attention_impl(const float* q, const uint16_t* kc, const uint16_t* vc, const float* gate, float* out, int n_head,
                              int n_kv, int head_dim, int pos, void* stream) {
@@ -2277,6 +2290,7 @@ static int op_attention_impl(const float* q, const uint16_t* kc, const uint16_t*
     a.min_keys = 64;
     a.scale = 1.0f / sqrtf((float)head_dim);
     a.pos = pos;
+    a.staged = pos + 1 > a.S * ATTN_LONG_MIN;
     return check(launch_attention((cudaStream_t)stream, a, head_dim, nullptr));
 }
 
@@ -2395,6 +2409,7 @@ extern "C" int tfr_op_attention_noalloc(const float* q, const uint16_t* kc, cons
     a.min_keys = 64;
     a.scale = 1.0f / sqrtf((float)head_dim);
     a.pos = pos;
+    a.staged = pos + 1 > a.S * ATTN_LONG_MIN;
     return check(launch_attention(s, a, head_dim, nullptr));
 }
 
@@ -2447,7 +2462,8 @@ extern "C" int tfr_op_qkv_rope_store(const tfr_mat* wq, const tfr_mat* wk, const
     return check(launch_gemv<BlockQ4, EpiQkv>(s, C, pa, jq, jk, fseg, epi, wq->m.K, nullptr));
 }
 
-// ------------------------------------------------------------------ synthetic quantiser
+#ifdef TFR_TEST_AIDS
+// ------------------------------------------------------------------ synthetic quantiser (test and benchmark aid)
 
 // One thread per 256-element super-block.  Asymmetric min/max per 32-element sub-block.
 __global__ void k_synth_q4k(const float* __restrict__ w, uint8_t* __restrict__ out, long long n_blocks) {
@@ -2532,3 +2548,4 @@ extern "C" int tfr_synth_quantize(int type, const float* w, int64_t K, int64_t N
     else return TFR_E_UNSUPPORTED;
     return check(cudaGetLastError());
 }
+#endif  // TFR_TEST_AIDS

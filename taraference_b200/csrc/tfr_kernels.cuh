@@ -650,6 +650,7 @@ __global__ void k_quantize_q8(const float* __restrict__ x, signed char* __restri
     if (lane == 0) d8[g] = d;
 }
 
+#ifdef TFR_TEST_AIDS
 // Builds an Act from an already quantised activation (linear int8 + scales); test-only path
 // used to expose the integer sub-block dots.
 __device__ void act_from_q8(const Act& act, const signed char* q8, const float* d8, int K) {
@@ -717,6 +718,8 @@ __global__ void k_int_dots(Mat m, const float* x, const signed char* q8, const f
         }
     }
 }
+
+#endif  // TFR_TEST_AIDS
 
 // Row-permuting repack.  perm_hd > 0: within each head of perm_hd rows, destination row
 // 2i + s takes source row i + s * perm_hd / 2 (RoPE partners become adjacent).

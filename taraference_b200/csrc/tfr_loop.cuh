@@ -187,7 +187,9 @@ __device__ __forceinline__ void loop_fail(LoopCtx& c, const LoopArgs& a, int cod
     c.ctl[CTL_STOP] = 1;
 }
 
-// Timeline probe: thread 0 stores the nanosecond timer at successive points of one decode step.
+// Timeline probe (builds with -DTFR_TEST_AIDS only): thread 0 stores the nanosecond timer at successive points of one
+// decode step.
+#ifdef TFR_TEST_AIDS
 __device__ __noinline__ void loop_mark(LoopCtx& c, const LoopArgs& a) {
     if (ltid() == 0 && c.mark_on) {
         if (c.mark_id < a.prof_points) {
@@ -198,6 +200,9 @@ __device__ __noinline__ void loop_mark(LoopCtx& c, const LoopArgs& a) {
         c.mark_id++;
     }
 }
+#else
+__device__ __forceinline__ void loop_mark(LoopCtx&, const LoopArgs&) {}
+#endif
 
 __host__ __device__ __forceinline__ void cursor_advance(int& slot, int& lap, int n, int nslot) {
     slot += n;

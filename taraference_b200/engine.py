@@ -284,7 +284,8 @@ class CudaModel:
 
     def set_loop_timeline(self, device_buffer, step: int, points: int) -> None:
         """Test aid: per-CTA nanosecond timestamps of decode step `step` of the persistent loop into a device
-        buffer of points * sm_count uint64 (None switches it off)."""
+        buffer of points * sm_count uint64 (None switches it off).  Only the instrumented build has the probes:
+        call _lib.use_aids_build() before anything loads the library."""
         self._check(_lib.lib().tfr_debug_set_loop_timeline(self._h, _ptr(device_buffer), int(step), int(points)))
 
     def forward_greedy(self, tokens, kv: CudaKv) -> int:
@@ -421,18 +422,18 @@ def ffn_block_host(gate: GpuMat, up: GpuMat, down: GpuMat, x: np.ndarray, y: np.
 
 
 def op_int_dots(w: GpuMat, q8, d8, a, b=None, stream: int = 0) -> None:
-    _ok(_lib.lib().tfr_op_int_dots(w._h, _ptr(q8), _ptr(d8), _ptr(a), _ptr(b), stream), "int_dots")
+    _ok(_lib.aids().tfr_op_int_dots(w._h, _ptr(q8), _ptr(d8), _ptr(a), _ptr(b), stream), "int_dots")
 
 
 def op_int_dots_x(w: GpuMat, x, a, b=None, q8_out=None, stream: int = 0) -> None:
     """Integer taps with the activation quantised by the product's own in-kernel quantiser; q8_out receives the int8
     values the block dots read, b (Q4_K) the group sums as the dots' activation record holds them."""
-    _ok(_lib.lib().tfr_op_int_dots_x(w._h, _ptr(x), _ptr(a), _ptr(b), _ptr(q8_out), stream), "int_dots_x")
+    _ok(_lib.aids().tfr_op_int_dots_x(w._h, _ptr(x), _ptr(a), _ptr(b), _ptr(q8_out), stream), "int_dots_x")
 
 
 def debug_f32_to_f16(src, dst, n: int, stream: int = 0) -> None:
     """Test aid: the KV store's f32 -> f16 rounding over n device floats."""
-    _ok(_lib.lib().tfr_debug_f32_to_f16(_ptr(src), _ptr(dst), int(n), stream), "debug_f32_to_f16")
+    _ok(_lib.aids().tfr_debug_f32_to_f16(_ptr(src), _ptr(dst), int(n), stream), "debug_f32_to_f16")
 
 
 def op_attention(q, kc, vc, out, n_head: int, n_kv: int, head_dim: int, pos: int, stream: int = 0) -> None:
@@ -491,4 +492,4 @@ def op_qkv_rope_store(wq: GpuMat, wk: GpuMat, wv: GpuMat, bq, bk, bv, x, norm_w,
 def synth_quantize(ggml_type: int, w, out, stream: int = 0) -> None:
     """Quantise fp32 device rows w[N][K] into GGUF bytes on the device."""
     N, K = w.shape
-    _ok(_lib.lib().tfr_synth_quantize(ggml_type, _ptr(w), K, N, _ptr(out), stream), "synth_quantize")
+    _ok(_lib.aids().tfr_synth_quantize(ggml_type, _ptr(w), K, N, _ptr(out), stream), "synth_quantize")

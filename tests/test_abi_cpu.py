@@ -14,6 +14,16 @@ def test_library_exports_every_declared_symbol(cuda_lib):
     assert not missing, missing
 
 
+def test_test_aids_live_in_the_instrumented_build_only(cuda_lib):
+    """Timeline probes, integer taps, the rounding operator and the synthetic quantiser are compiled under
+    -DTFR_TEST_AIDS: the product library must not export them, the instrumented one must export everything."""
+    aid_names = _lib.declared_aid_symbols()
+    assert set(aid_names) == set(_lib.AID_NAMES)
+    assert not [n for n in aid_names if hasattr(cuda_lib, n)]
+    aids = _lib.aids()
+    assert not [n for n in aid_names + _lib.declared_symbols() if not hasattr(aids, n)]
+
+
 def test_create_without_gpu_fails_cleanly(cuda_lib):
     import torch
     if torch.cuda.is_available():
