@@ -498,8 +498,14 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
     }
     __syncthreads();
 
-    // rows on the fp32 activation route: one task per (row, block, run of 16), all threads
-    if (fseg.m.data) {
+    // rows on the fp32 activation route: one task per (row, block, run of 16).  When their partials fit behind the
+    // block partials of the tiles (the usual case: a CTA holds one or two V row pairs), the tasks run side by side
+    // with the tile dots — taken from the last thread downwards, so the few warps that own tiles keep to their tiles —
+    // and share the tile dots' barrier; otherwise they run first, chunk by chunk, with barriers of their own.
+    const int f32_tasks = fseg.m.data ? 2 * fseg.sh.count(cta) * 16 * nb : 0;
+    const int f32_off = ((rows_a + rows_b) * nb + 3) & ~3;
+    const bool f32_fused = f32_tasks > 0 && f32_off + f32_tasks <= pbuf_floats;
+    if (fseg.m.data && !f32_fused) {
         const int np = fseg.sh.count(cta), pbase = fseg.sh.begin(cta);
         const int per_row = 16 * nb, tasks = 2 * np * per_row;
         const int chunk = (pbuf_floats / (2 * per_row)) * (2 * per_row);  // whole row pairs per chunk
@@ -568,9 +574,34 @@ k_gemv(PrepArgs pa, RowJob ja, RowJob jb, F32Seg fseg, Epi epi_in, int K, int pb
             }
         }
     }
+    if (f32_fused) {
+        const int pbase = fseg.sh.begin(cta), per_row = 16 * nb;
+        for (int t = GEMV_THREADS - 1 - tid; t < f32_tasks; t += GEMV_THREADS) {
+            const int row_l = t / per_row, rem = t - row_l * per_row;
+            const int row_g = 2 * pbase + row_l;
+            float v = 0.f;
+            if (row_g < fseg.m.N) v = q6k_run_dot_f32(fseg.m, (long long)row_g * nb + (rem >> 4), rem >> 4, rem & 15, xs);
+            pbuf[f32_off + t] = v;
+        }
+    }
     if (!ok && st) st->err = 2;  // a bulk copy never completed: results of this step are invalid
     __syncthreads();
     prof_mark(4, pa.prof_id);
+    if (f32_fused) {
+        // the same sums as the stand-alone route: lanes stride over a row's runs, then the warp tree
+        const int pbase = fseg.sh.begin(cta), per_row = 16 * nb, pairs = f32_tasks / (2 * per_row);
+        for (int rr = GEMV_WARPS - 1 - warp; rr < pairs; rr += GEMV_WARPS) {
+            const float* a = pbuf + f32_off + (2 * rr) * per_row;
+            float s0 = 0.f, s1 = 0.f;
+            for (int i = lane; i < per_row; i += 32) {
+                s0 += a[i];
+                s1 += a[per_row + i];
+            }
+            s0 = warp_sum(s0);
+            s1 = warp_sum(s1);
+            if (lane == 0) epi.apply(fseg.id_base + pbase + rr, s0, s1);
+        }
+    }
     // phase B: row sums in a fixed order + epilogue
     if (Epi::MODE == EPI_ZIP) {
         reduce_rows<EPI_ZIP>(part_a, part_b, rows_a, nb, ja.id_base + rows_a0, epi);
