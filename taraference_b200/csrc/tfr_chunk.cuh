@@ -201,7 +201,7 @@ __device__ __forceinline__ void reduce_rows_group(const float* pa, const float* 
 
 // ------------------------------------------------------------------ the chunk GEMM
 
-// Shared memory: [ Act x Mt | staged fp32 vector (fp32-route rows only) | partial sums x Mt | mbarriers | tile slots ].
+// Shared memory: [ Act x Mt | partial sums x Mt | mbarriers | tile slots ].
 // Warp w < wa owns the tiles w, w + wa, ... of the CTA and `nsw` ring slots; it refills a slot as soon as it has used
 // the tile in it, so the stream runs `nsw` tiles ahead of the dots.  With more tokens than Mt the CTA walks its
 // tiles once per group of Mt tokens (the second pass finds them in L2).
@@ -220,8 +220,7 @@ k_gemm_q8(const unsigned char* act_g, const float* xn, RowJob ja, RowJob jb, F32
     const int K = g.K, nb = K >> 8, Mt = g.Mt, nsw = g.nsw, wa = g.wa;
     constexpr int TB = BLK::TILE_BYTES;
     unsigned char* act_s = smem;
-    float* xs = reinterpret_cast<float*>(act_s + (size_t)Mt * g.act_b16);
-    float* pbuf = xs + (fseg.m.data ? xs_floats(K) : 0);
+    float* pbuf = reinterpret_cast<float*>(act_s + (size_t)Mt * g.act_b16);
     unsigned long long* full = reinterpret_cast<unsigned long long*>(pbuf + (size_t)Mt * g.pbuf_floats);
     unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(full + wa * nsw) + 127) & ~(uintptr_t)127);
 
@@ -271,41 +270,37 @@ k_gemm_q8(const unsigned char* act_g, const float* xn, RowJob ja, RowJob jb, F32
             }
         }
         __syncthreads();
-        // rows on the fp32 activation route (kernels/gemv.cu:233-264), token by token through one staged vector
+        // rows on the fp32 activation route (kernels/gemv.cu:233-264): a task = (row, block, run of 16) reads its
+        // weights once and walks the tokens of the group, each token's normalised vector straight from global memory
         if (fseg.m.data) {
             const int np = fseg.sh.count(cta), pbase = fseg.sh.begin(cta);
-            const int per_row = 16 * nb, tasks = 2 * np * per_row;
-            const int chunk = (g.pbuf_floats * Mt / (2 * per_row)) * (2 * per_row);  // whole row pairs per pass
-            for (int m = 0; m < mt; m++) {
-                const ChunkEpiTok et{&epi, m0 + m};
-                for (int i4 = tid; i4 < (K >> 2); i4 += GEMV_THREADS)
-                    *reinterpret_cast<float4*>(xs + xs_idx(4 * i4)) = reinterpret_cast<const float4*>(xn + (size_t)(m0 + m) * K)[i4];
-                __syncthreads();
-                for (int t0 = 0; t0 < tasks; t0 += chunk) {
-                    const int tn = min(chunk, tasks - t0);
-                    for (int t = tid; t < tn; t += GEMV_THREADS) {
-                        const int task = t0 + t;
-                        const int row_l = task / per_row, rem = task - row_l * per_row;
-                        const int row_g = 2 * pbase + row_l;
+            const int per_row = 16 * nb, ppp = max(1, g.pbuf_floats / (2 * per_row));  // row pairs per pass
+            for (int p0 = 0; p0 < np; p0 += ppp) {
+                const int pn = min(ppp, np - p0), tn = pn * 2 * per_row;
+                for (int t = tid; t < tn; t += GEMV_THREADS) {
+                    const int row_l = t / per_row, rem = t - row_l * per_row;
+                    const int row_g = 2 * (pbase + p0) + row_l;
+                    for (int m = 0; m < mt; m++) {
                         float v = 0.f;
-                        if (row_g < fseg.m.N) v = q6k_run_dot_f32(fseg.m, (long long)row_g * nb + (rem >> 4), rem >> 4, rem & 15, xs);
-                        pbuf[t] = v;
+                        if (row_g < fseg.m.N)
+                            v = q6k_run_dot_f32_g(fseg.m, (long long)row_g * nb + (rem >> 4), rem >> 4, rem & 15, xn + (size_t)(m0 + m) * K);
+                        pbuf[(size_t)m * g.pbuf_floats + t] = v;
                     }
-                    __syncthreads();
-                    const int pairs_here = tn / (2 * per_row), pair_first = t0 / (2 * per_row);
-                    for (int rr = warp; rr < pairs_here; rr += GEMV_WARPS) {
-                        const float* a = pbuf + (2 * rr) * per_row;
-                        float s0 = 0.f, s1 = 0.f;
-                        for (int i = lane; i < per_row; i += 32) {
-                            s0 += a[i];
-                            s1 += a[per_row + i];
-                        }
-                        s0 = warp_sum(s0);
-                        s1 = warp_sum(s1);
-                        if (lane == 0) et.apply(fseg.id_base + pbase + pair_first + rr, s0, s1);
-                    }
-                    __syncthreads();
                 }
+                __syncthreads();
+                for (int item = warp; item < pn * mt; item += GEMV_WARPS) {
+                    const int m = item / pn, rr = item - m * pn;
+                    const float* a = pbuf + (size_t)m * g.pbuf_floats + (2 * rr) * per_row;
+                    float s0 = 0.f, s1 = 0.f;
+                    for (int i = lane; i < per_row; i += 32) {
+                        s0 += a[i];
+                        s1 += a[per_row + i];
+                    }
+                    s0 = warp_sum(s0);
+                    s1 = warp_sum(s1);
+                    if (lane == 0) ChunkEpiTok{&epi, m0 + m}.apply(fseg.id_base + pbase + p0 + rr, s0, s1);
+                }
+                __syncthreads();
             }
         }
         // phase A: per-block partials of every token out of the tiles
@@ -373,7 +368,7 @@ inline GemmLaunch gemm_plan(int tile_bytes, int M, int K, const RowJob& ja, cons
     int pf = ((ra + rb) * nb + 3) & ~3;
     if (with_f32 && pf < 2 * 16 * nb) pf = 2 * 16 * nb;
     const size_t act_b16 = (act_smem_bytes(K, false, false) + 15) & ~(size_t)15;
-    const size_t xf = with_f32 ? xs_floats(K) * 4 : 0;
+    const size_t xf = 0;  // fp32-route rows read the normalised vectors from global memory
     L.fits = false;
     // The dot work of a launch does not depend on Mt, the per-pass overhead shrinks with it: take the widest set of
     // dot warps that still leaves room for a few tokens per pass, then as many tokens as fit.

@@ -425,6 +425,34 @@ __device__ __forceinline__ float q6k_run_dot_f32(const Mat& m, long long f, int 
     return acc;
 }
 
+// The same run against a plain fp32 vector in global memory (x = the row's start): the chunk kernels keep no staged
+// copy per token.  Same operations in the same order as q6k_run_dot_f32.
+__device__ __forceinline__ float q6k_run_dot_f32_g(const Mat& m, long long f, int b, int c, const float* x) {
+    const int n = c >> 3, j = (c >> 1) & 3, is = c & 1;
+    const int4 ql = __ldg(reinterpret_cast<const int4*>(block_byte(m, f, 64 * n + 32 * (j & 1) + 16 * is)));
+    const int4 qh = __ldg(reinterpret_cast<const int4*>(block_byte(m, f, 128 + 32 * n + 16 * is)));
+    const float sc = (float)(int)*reinterpret_cast<const signed char*>(block_byte(m, f, 192 + 8 * n + is + 2 * j));
+    const float d = f16_to_f32(__ldg(reinterpret_cast<const unsigned short*>(block_byte(m, f, 208))));
+    const float dsc = d * sc;
+    const float4* x4 = reinterpret_cast<const float4*>(x + 256 * b + 16 * c);
+    const int qlw[4] = {ql.x, ql.y, ql.z, ql.w};
+    const int qhw[4] = {qh.x, qh.y, qh.z, qh.w};
+    const int nsh = 4 * (j >> 1), hsh = 2 * j;
+    float acc = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const float4 xq = x4[k];
+        const float xv[4] = {xq.x, xq.y, xq.z, xq.w};
+#pragma unroll
+        for (int by = 0; by < 4; by++) {
+            const int nib = (qlw[k] >> (8 * by + nsh)) & 0xF;
+            const int hb = (qhw[k] >> (8 * by + hsh)) & 3;
+            acc += dsc * (float)((nib | (hb << 4)) - 32) * xv[by];
+        }
+    }
+    return acc;
+}
+
 // ------------------------------------------------------------------ shares
 
 // Contiguous share of n items for CTA c of C, with n = C*quot + rem split on the host so that
