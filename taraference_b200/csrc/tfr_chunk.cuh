@@ -320,6 +320,8 @@ k_gemm_q8(const unsigned char* act_g, const float* xn, RowJob ja, RowJob jb, F32
             if (mine) {
                 const int off = is_b ? rows_a * nb + (int)(f - fb0) : (int)(f - fa0);
                 const int b = (int)(f % nb);
+                // (Sharing the nibble masks / 6-bit assembly of a block across four tokens was measured: at the 64
+                // registers a 1024-thread CTA allows it spills and runs 13 % slower than one block_dot per token.)
                 for (int m = 0; m < mt; m++) {
                     const Act act = act_carve(act_s + (size_t)m * g.act_b16, K, false, false);
                     pbuf[(size_t)m * g.pbuf_floats + off] = landed ? block_dot<true>(BLK{}, wring + (size_t)s * TB, lane, act, b, nb, nullptr) : 0.f;
@@ -567,13 +569,18 @@ __global__ void k_attn_chunk_merge(const float* partial, float* out, int S, int 
 
 // ------------------------------------------------------------------ greedy token of every row
 
-// kernels/ops.cu:601-629 (argmax_rows_f32); ties resolve to the lowest index.
-__global__ void k_argmax_rows(const float* logits, int V, int* out) {
+// kernels/ops.cu:601-629 (argmax_rows_f32); ties resolve to the lowest index.  A row of the vocabulary's size is too
+// long for one CTA: ARGMAX_SLICES CTAs per row fold their slice into a packed key each, the last one to arrive (per
+// row counter, zero between launches) folds the keys and writes the token.
+constexpr int ARGMAX_SLICES = 32;
+__global__ void k_argmax_rows(const float* logits, int V, int* out, unsigned long long* keys, unsigned int* counters) {
     __shared__ unsigned long long sb[32];
-    const int m = blockIdx.x, tid = threadIdx.x;
+    __shared__ int is_last;
+    const int m = blockIdx.x, sl = blockIdx.y, tid = threadIdx.x;
     const float* row = logits + (size_t)m * V;
+    const int per = (V + ARGMAX_SLICES - 1) / ARGMAX_SLICES, i0 = sl * per, i1 = min(V, i0 + per);
     unsigned long long best = 0ull;
-    for (int i = tid; i < V; i += blockDim.x) {
+    for (int i = i0 + tid; i < i1; i += blockDim.x) {
         const unsigned long long k = argmax_key(row[i], i);
         best = k > best ? k : best;
     }
@@ -585,7 +592,20 @@ __global__ void k_argmax_rows(const float* logits, int V, int* out) {
     __syncthreads();
     if (tid == 0) {
         for (int i = 1; i < (int)(blockDim.x >> 5); i++) best = sb[i] > best ? sb[i] : best;
-        out[m] = argmax_key_index(best);
+        keys[(size_t)m * ARGMAX_SLICES + sl] = best;
+        __threadfence();
+        const unsigned int old = atomicAdd(counters + m, 1u);
+        is_last = old == ARGMAX_SLICES - 1;
+        if (is_last) {
+            counters[m] = 0u;
+            __threadfence();
+            unsigned long long b = 0ull;
+            for (int i = 0; i < ARGMAX_SLICES; i++) {
+                const unsigned long long k = __ldcg(keys + (size_t)m * ARGMAX_SLICES + i);
+                b = k > b ? k : b;
+            }
+            out[m] = argmax_key_index(b);
+        }
     }
 }
 

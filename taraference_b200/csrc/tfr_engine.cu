@@ -183,6 +183,8 @@ struct tfr_engine {
     float *cx = nullptr, *cq = nullptr, *cattn = nullptr, *ch = nullptr, *cxn = nullptr, *clogits = nullptr, *cpart = nullptr;
     unsigned char* cact = nullptr;
     size_t cact_stride = 0;
+    unsigned long long* ckeys = nullptr;  // per-row, per-slice argmax keys of a verification pass
+    unsigned int* ccount = nullptr;       // per-row arrival counters, zero between launches
 };
 
 struct tfr_kv {
@@ -570,7 +572,7 @@ extern "C" void tfr_destroy(tfr_engine* e) {
     for (auto& kv : e->vecs) cudaFree(kv.second.dev);
     for (auto& L : e->layers) cudaFree(L.bias_qkv);
     void* ws[] = {e->x, e->q, e->attn, e->h, e->logits, e->partial, e->counters, e->st, e->out_tokens, e->prompt,
-                  e->layer_taps, e->tap_attn, e->tap_mid, e->tap_h, e->proj, e->qgate, e->loop_layers, e->loop_bar, e->loop_best, e->loop_vec, e->cx, e->cq, e->cattn, e->ch, e->cxn, e->clogits, e->cpart, e->cact, e->loop_blob, e->loop_head_tasks};
+                  e->layer_taps, e->tap_attn, e->tap_mid, e->tap_h, e->proj, e->qgate, e->loop_layers, e->loop_bar, e->loop_best, e->loop_vec, e->cx, e->cq, e->cattn, e->ch, e->cxn, e->clogits, e->cpart, e->cact, e->ckeys, e->ccount, e->loop_blob, e->loop_head_tasks};
     for (void* p : ws) cudaFree(p);
     if (e->st_host) cudaFreeHost(e->st_host);
     if (e->out_host) cudaFreeHost(e->out_host);
@@ -1586,6 +1588,9 @@ static int chunk_buffers(tfr_engine* e) {
     CU(e, cudaMalloc(&e->ch, (size_t)M * P.ff * 4));
     CU(e, cudaMalloc(&e->cact, (size_t)M * e->cact_stride));
     CU(e, cudaMalloc(&e->clogits, (size_t)CHUNK_VERIFY_MAX * e->head->m.N * 4));
+    CU(e, cudaMalloc(&e->ckeys, (size_t)CHUNK_VERIFY_MAX * ARGMAX_SLICES * 8));
+    CU(e, cudaMalloc(&e->ccount, CHUNK_VERIFY_MAX * 4));
+    CU(e, cudaMemset(e->ccount, 0, CHUNK_VERIFY_MAX * 4));
     CU(e, cudaMalloc(&e->cpart, (size_t)M * P.n_head * CHUNK_ATTN_SPLITS_MAX * (2 + e->cfg.head_dim) * 4));
     return TFR_OK;
 }
@@ -1647,7 +1652,9 @@ static int forward_chunk(tfr_engine* e, const tfr_kv* kv, const int* tok, int M,
             a.M = M, a.n_head = P.n_head, a.n_kv = P.n_kv, a.pos0 = pos0, a.kvdim = nkv, a.ldq = nq;
             a.scale = 1.0f / sqrtf((float)hd);  // forward.rs:389
             const int rep = P.n_head / P.n_kv;
-            a.QT = std::max(1, ATTC_ROWS_MAX / rep);
+            // few tokens (verification batches): one query token per CTA, so that a row's serial walk over the keys is
+            // a warp's only work; prompts: four tokens share every K/V tile
+            a.QT = M <= CHUNK_VERIFY_MAX ? 1 : std::max(1, ATTC_ROWS_MAX / rep);
             const int q_tiles = (M + a.QT - 1) / a.QT;
             // key splits: enough CTAs for every SM, never less than eight key tiles (256 keys) per split
             const int tiles_max = (pos0 + M + ATTC_TK - 1) / ATTC_TK;
@@ -1696,7 +1703,7 @@ static int forward_chunk(tfr_engine* e, const tfr_kv* kv, const int* tok, int M,
         if (launch_gemm_typed(s, cap, e->head->m.type, e->cact, e->cact_stride, nullptr, M, make_job(e->head->m, 2, cap), RowJob{},
                               F32Seg{}, store_epi(e->clogits, V, V, 0), K, e->st) != cudaSuccess)
             return -1;
-        k_argmax_rows<<<M, 1024, 0, s>>>(e->clogits, V, e->out_tokens);
+        k_argmax_rows<<<dim3(M, ARGMAX_SLICES), 256, 0, s>>>(e->clogits, V, e->out_tokens, e->ckeys, e->ccount);
         if (cudaGetLastError() != cudaSuccess) return -1;
         // tfr_current_logits reports the last position's row
         if (cudaMemcpyAsync(e->logits, e->clogits + (size_t)(M - 1) * V, (size_t)V * 4, cudaMemcpyDeviceToDevice, s) != cudaSuccess) return -1;
