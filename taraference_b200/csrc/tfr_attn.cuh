@@ -72,7 +72,9 @@ __device__ __forceinline__ float warp_transpose_reduce32(float (&v)[32], int lan
     return v[0];
 }
 
-template <int HD>
+// STAGED = true compiles in the long-split route (and needs attn_dyn_smem(HD) of dynamic shared memory at launch);
+// the STAGED = false instance is the register route alone, with the registers that route needs and no more.
+template <int HD, bool STAGED = false>
 __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const TokenState* st) {
     prof_mark(0, a.prof_id);
     constexpr int DL = HD / 32;   // dims per lane in the score phase
@@ -136,7 +138,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
     // Rows of earlier positions do not depend on the previous kernel: the first tile's are requested before
     // the grid-dependency wait, so their latency hides behind the kernel boundary.
     // A split with many keys stages its tiles in shared memory instead (below): no register preload then.
-    const bool long_path = a.staged && t1 - t0 > ATTN_LONG_MIN;
+    const bool long_path = STAGED && a.staged && t1 - t0 > ATTN_LONG_MIN;
     if (!long_path) {
         load_k(t0, min(t1, T - 1), false);
         load_v(t0, min(t1, T - 1), false);
@@ -176,7 +178,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
     __syncthreads();
     prof_mark(4, a.prof_id);
 
-    if (long_path) {
+    if constexpr (STAGED) if (long_path) {
         // ---- long splits: K and V tiles travel global -> shared memory as asynchronous 16-byte copies, NST stages
         // deep, so the loads of the next tiles run under the arithmetic of tile i and no register holds cache data.
         extern __shared__ __align__(16) unsigned char attn_dyn[];

@@ -292,9 +292,12 @@ static void configure_kernels_once() {
     configure_kernel(k_attn_decode<64>, false);
     configure_kernel(k_attn_decode<128>, false);
     configure_kernel(k_attn_decode<256>, false);
-    cudaFuncSetAttribute(k_attn_decode<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_dyn_smem(64));
-    cudaFuncSetAttribute(k_attn_decode<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_dyn_smem(128));
-    cudaFuncSetAttribute(k_attn_decode<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_dyn_smem(256));
+    configure_kernel(k_attn_decode<64, true>, false);
+    configure_kernel(k_attn_decode<128, true>, false);
+    configure_kernel(k_attn_decode<256, true>, false);
+    cudaFuncSetAttribute(k_attn_decode<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_dyn_smem(64));
+    cudaFuncSetAttribute(k_attn_decode<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_dyn_smem(128));
+    cudaFuncSetAttribute(k_attn_decode<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_dyn_smem(256));
     configure_kernel(k_gdn_step, false);
     configure_kernel(k_qk_norm_rope_store, false);
     configure_kernel(k_state_advance, false);
@@ -328,9 +331,10 @@ static int attn_max_clusters(int hd) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    cudaError_t r = hd == 64    ? cudaOccupancyMaxActiveClusters(&n, k_attn_decode<64>, &cfg)
-                    : hd == 128 ? cudaOccupancyMaxActiveClusters(&n, k_attn_decode<128>, &cfg)
-                                : cudaOccupancyMaxActiveClusters(&n, k_attn_decode<256>, &cfg);
+    // asked for the instance with the larger footprint (the staged route): the split count then fits both
+    cudaError_t r = hd == 64    ? cudaOccupancyMaxActiveClusters(&n, k_attn_decode<64, true>, &cfg)
+                    : hd == 128 ? cudaOccupancyMaxActiveClusters(&n, k_attn_decode<128, true>, &cfg)
+                                : cudaOccupancyMaxActiveClusters(&n, k_attn_decode<256, true>, &cfg);
     if (r != cudaSuccess) {
         cudaGetLastError();
         n = 0;
@@ -1264,9 +1268,14 @@ static cudaError_t launch_attention(cudaStream_t s, const AttnArgs& a, int hd, c
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = gemv_pdl_enabled() ? 2 : 1;
-    if (hd == 64) return cudaLaunchKernelEx(&cfg, k_attn_decode<64>, a, st);
-    if (hd == 128) return cudaLaunchKernelEx(&cfg, k_attn_decode<128>, a, st);
-    return cudaLaunchKernelEx(&cfg, k_attn_decode<256>, a, st);
+    if (a.staged) {
+        if (hd == 64) return cudaLaunchKernelEx(&cfg, k_attn_decode<64, true>, a, st);
+        if (hd == 128) return cudaLaunchKernelEx(&cfg, k_attn_decode<128, true>, a, st);
+        return cudaLaunchKernelEx(&cfg, k_attn_decode<256, true>, a, st);
+    }
+    if (hd == 64) return cudaLaunchKernelEx(&cfg, k_attn_decode<64, false>, a, st);
+    if (hd == 128) return cudaLaunchKernelEx(&cfg, k_attn_decode<128, false>, a, st);
+    return cudaLaunchKernelEx(&cfg, k_attn_decode<256, false>, a, st);
 }
 
 template <class Epi>
