@@ -429,6 +429,10 @@ def main():
     ap.add_argument("--workload", default="3b", choices=sorted(WORKLOADS))
     ap.add_argument("--skip-32b", action="store_true",
                     help="default workload only: leave out the 32B-shape tensor-parallel side measurement")
+    ap.add_argument("--share-of", type=int, default=1,
+                    help="32b-tp workload on ONE GPU: run the slice of the model a rank of an N-way tensor-parallel engine holds "
+                         "(heads, FFN rows and vocabulary divided by N) as an ordinary engine, i.e. a rank's work without any "
+                         "exchange; the difference to the tensor-parallel figure at N ranks is what the exchange costs")
     ap.add_argument("--roofline-only", action="store_true",
                     help="time only the fused gate+up kernel over 254 MB of weights (the small case used for ncu)")
     args = ap.parse_args()
@@ -453,6 +457,16 @@ def main():
     warmup = max(args.warmup, 3)
     cfg_name, PROMPT_LEN, N_DECODE, CTX, workload_text = WORKLOADS[args.workload]
     cfg = dict(getattr(S, cfg_name))
+    if args.share_of > 1:
+        if args.workload != "32b-tp" or world != 1:
+            raise SystemExit("--share-of applies to --workload 32b-tp on one GPU")
+        n = args.share_of
+        blocks = (cfg["n_ff"] // 256 + n - 1) // n  # the larger FFN slice of the plan (e.g. 14 of 13/14 blocks at n = 8)
+        heads = cfg["n_head"] // n
+        heads += heads % 2  # the stand-alone engine wants whole 256-element blocks of attention width (128-wide heads in pairs)
+        cfg.update(n_head=heads, n_kv=max(1, cfg["n_kv"] // n), n_ff=256 * blocks,
+                   n_vocab=(cfg["n_vocab"] // n + 1) // 2 * 2)
+        workload_text += f" -- the 1/{n} slice of one rank, run alone on one GPU without exchange"
     tp = world if args.workload == "32b-tp" else 1   # the ranks form one engine instead of N replicas
     main_workload = args.workload == "3b"
     want_host = main_workload and rank == 0 and world == 1 and not (args.skip_cpu_baseline and args.skip_reference_gpu)
