@@ -19,10 +19,16 @@
 
 namespace tfr {
 
-constexpr int ATTN_THREADS = 256;
+constexpr int ATTN_THREADS = 256;         // the register-route instance
+constexpr int ATTN_THREADS_STAGED = 512;  // the staged instance: sixteen warps hide the latencies of its tile loop
+__host__ __device__ constexpr int attn_threads(bool staged) { return staged ? ATTN_THREADS_STAGED : ATTN_THREADS; }
 constexpr int ATTN_TILE = 64;     // keys per tile
 constexpr int ATTN_REP_MAX = 8;   // query heads per KV head handled by one CTA
 constexpr int ATTN_CLUSTER = 8;   // CTAs per cluster (the portable maximum); AttnArgs::S is a multiple of it
+// The staged instance (long caches) runs clusters of four: the device holds 14 clusters of eight of that footprint at
+// once (112 of 148 SMs) but enough clusters of four to put a split on nearly every SM.
+constexpr int ATTN_CLUSTER_STAGED = 4;
+__host__ __device__ constexpr int attn_cluster(bool staged) { return staged ? ATTN_CLUSTER_STAGED : ATTN_CLUSTER; }
 constexpr int ATTN_LONG_MIN = 128;  // a split with more keys than this walks them through shared-memory stages
 // Dynamic shared memory of k_attn_decode: a few stages of one K tile (rows padded by 8 halfs: 16-byte reads of 32
 // different rows hit 32 different banks) and one V tile each, then q of the group's heads in fp32.  One tile in
@@ -75,14 +81,16 @@ __device__ __forceinline__ float warp_transpose_reduce32(float (&v)[32], int lan
 // STAGED = true compiles in the long-split route (and needs attn_dyn_smem(HD) of dynamic shared memory at launch);
 // the STAGED = false instance is the register route alone, with the registers that route needs and no more.
 template <int HD, bool STAGED = false>
-__global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const TokenState* st) {
+__global__ void __launch_bounds__(attn_threads(STAGED)) k_attn_decode(AttnArgs a, const TokenState* st) {
+    constexpr int NT = attn_threads(STAGED);
     prof_mark(0, a.prof_id);
     constexpr int DL = HD / 32;   // dims per lane in the score phase
     constexpr int DPT = HD / 64;  // dims per thread in the value phase
     constexpr int VK = ATTN_TILE / 4;  // keys per thread and tile in the value phase
     using KRaw = typename std::conditional<DL == 8, uint4, typename std::conditional<DL == 4, uint2, unsigned int>::type>::type;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = blockIdx.y, s = blockIdx.x;  // grid (S, n_kv), clusters of ATTN_CLUSTER along x
+    constexpr int CL = attn_cluster(STAGED);
+    const int g = blockIdx.y, s = blockIdx.x;  // grid (S, n_kv), clusters of CL along x
     const int rep = a.n_head / a.n_kv;
     const int kvdim = a.n_kv * HD;
     const int kg = tid >> 6, dp = tid & 63;
@@ -92,10 +100,10 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
     const int T = (st ? st->pos : a.pos) + 1;
     int S_eff = (T + a.min_keys - 1) / a.min_keys;
     S_eff = S_eff < 1 ? 1 : (S_eff > a.S ? a.S : S_eff);
-    // up to ATTN_CLUSTER splits: the first cluster of the KV head merges on chip; its idle members
+    // up to CL splits: the first cluster of the KV head merges on chip; its idle members
     // still attend the cluster barriers.  More splits: every CTA for itself, merge through memory.
-    const int n_cl = (S_eff + ATTN_CLUSTER - 1) / ATTN_CLUSTER;  // clusters that have work
-    const bool leave = done || (S_eff == 1 ? s >= 1 : s >= n_cl * ATTN_CLUSTER);
+    const int n_cl = (S_eff + CL - 1) / CL;  // clusters that have work
+    const bool leave = done || (S_eff == 1 ? s >= 1 : s >= n_cl * CL);
     const bool active = s < S_eff;
     const int chunk = (T + S_eff - 1) / S_eff;
     const int t0 = min(T, s * chunk);
@@ -138,37 +146,67 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
     // Rows of earlier positions do not depend on the previous kernel: the first tile's are requested before
     // the grid-dependency wait, so their latency hides behind the kernel boundary.
     // A split with many keys stages its tiles in shared memory instead (below): no register preload then.
-    const bool long_path = STAGED && a.staged && t1 - t0 > ATTN_LONG_MIN;
-    if (!long_path) {
+    const bool long_path = STAGED && t1 > t0;  // the staged instance walks every split through shared memory
+    if constexpr (!STAGED) {
         load_k(t0, min(t1, T - 1), false);
         load_v(t0, min(t1, T - 1), false);
+    }
+    // The staged route does the same with its first NST - 1 tiles, as asynchronous copies; row T - 1 is left out of
+    // them and fetched with plain loads after the wait.
+    extern __shared__ __align__(16) unsigned char attn_dyn[];
+    constexpr int KROW = HD + 8, CPR = HD / 8;  // halfs per staged K row; 16-byte chunks per cache row
+    constexpr int NST = attn_stages(HD);
+    constexpr size_t stage_b = (size_t)ATTN_TILE * KROW * 2 + (size_t)ATTN_TILE * HD * 2;
+    auto k_stage = [&](int st_) { return reinterpret_cast<unsigned short*>(attn_dyn + (size_t)st_ * stage_b); };
+    auto v_stage = [&](int st_) { return reinterpret_cast<unsigned short*>(attn_dyn + (size_t)st_ * stage_b + (size_t)ATTN_TILE * KROW * 2); };
+    auto issue_tile = [&](int tt, int st_, int skip_row) {
+        unsigned short* ks = k_stage(st_);
+        unsigned short* vs = v_stage(st_);
+        if (tt < t1)
+            for (int i = tid; i < ATTN_TILE * CPR; i += NT) {
+                const int row = i / CPR, c8 = i - row * CPR;
+                const bool in = tt + row < t1;
+                if (tt + row == skip_row) continue;
+                const size_t off = (size_t)(in ? tt + row : t1 - 1) * kvdim + (size_t)g * HD + c8 * 8;
+                cp_async16(ks + row * KROW + c8 * 8, a.kc + off, in ? 16 : 0);
+                cp_async16(vs + row * HD + c8 * 8, a.vc + off, in ? 16 : 0);
+            }
+        cp_async_commit();  // a group per tile slot, empty past the end: the wait in the tile loop counts groups
+    };
+    if constexpr (STAGED) if (long_path) {
+#pragma unroll
+        for (int p = 0; p < NST - 1; p++) issue_tile(t0 + p * ATTN_TILE, p, T - 1);
     }
     griddep_wait();  // q and the new K/V row come from the previous kernel
     griddep_launch_dependents();
     prof_mark(1, a.prof_id);
     if (leave) return;
-    if (!long_path) {
+    if constexpr (!STAGED) {
         load_k(t0, 0, true);
         load_v(t0, 0, true);
     }
 
     __shared__ __align__(16) float sc[ATTN_TILE][ATTN_REP_MAX];  // [key][head]: the value phase reads a key's eight weights as two float4
-    __shared__ float m_s[ATTN_REP_MAX], l_s[ATTN_REP_MAX], alpha_s[ATTN_REP_MAX];
+    __shared__ __align__(16) float m_s[ATTN_REP_MAX];
+    __shared__ __align__(16) float l_s[ATTN_REP_MAX];
+    __shared__ __align__(16) float alpha_s[ATTN_REP_MAX];
     __shared__ float ored[4][ATTN_REP_MAX][HD];
     __shared__ int is_last_s;
     // on-chip merge: slice s of every member's O, and every member's (m, l), land here
-    __shared__ float gath[ATTN_CLUSTER][HD];
-    __shared__ float gm[ATTN_CLUSTER][ATTN_REP_MAX], gl[ATTN_CLUSTER][ATTN_REP_MAX];
+    __shared__ float gath[ATTN_REP_MAX * HD];  // [member][per], per = rep * HD / CL
+    __shared__ float gm[CL][ATTN_REP_MAX], gl[CL][ATTN_REP_MAX];
 
-    // q fragment of every head of the group: dims lane*DL .. lane*DL+DL-1
+    // q fragment of every head of the group: dims lane*DL .. lane*DL+DL-1 (the register route's; the staged route
+    // keeps q in shared memory)
     float qr[ATTN_REP_MAX][DL];
 #pragma unroll
     for (int h = 0; h < ATTN_REP_MAX; h++)
 #pragma unroll
-        for (int d = 0; d < DL; d++) qr[h][d] = h < rep ? a.q[(g * rep + h) * HD + lane * DL + d] : 0.f;
+        for (int d = 0; d < DL; d++) qr[h][d] = (h < rep && !STAGED) ? a.q[(g * rep + h) * HD + lane * DL + d] : 0.f;
     if (tid < ATTN_REP_MAX) {
         m_s[tid] = -1e30f;
         l_s[tid] = 0.f;
+        alpha_s[tid] = 1.f;
     }
     float o[ATTN_REP_MAX][DPT];
 #pragma unroll
@@ -178,110 +216,68 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
     __syncthreads();
     prof_mark(4, a.prof_id);
 
-    if constexpr (STAGED) if (long_path) {
-        // ---- long splits: K and V tiles travel global -> shared memory as asynchronous 16-byte copies, NST stages
-        // deep, so the loads of the next tiles run under the arithmetic of tile i and no register holds cache data.
-        extern __shared__ __align__(16) unsigned char attn_dyn[];
-        constexpr int KROW = HD + 8, CPR = HD / 8;  // halfs per staged K row; 16-byte chunks per cache row
-        constexpr int NST = attn_stages(HD);
-        const size_t stage_b = (size_t)ATTN_TILE * KROW * 2 + (size_t)ATTN_TILE * HD * 2;
-        float* q_s = reinterpret_cast<float*>(attn_dyn + NST * stage_b);
-        auto k_stage = [&](int st_) { return reinterpret_cast<unsigned short*>(attn_dyn + (size_t)st_ * stage_b); };
-        auto v_stage = [&](int st_) { return reinterpret_cast<unsigned short*>(attn_dyn + (size_t)st_ * stage_b + (size_t)ATTN_TILE * KROW * 2); };
-        auto issue_tile = [&](int tt, int st_) {
-            unsigned short* ks = k_stage(st_);
-            unsigned short* vs = v_stage(st_);
-            if (tt < t1)
-                for (int i = tid; i < ATTN_TILE * CPR; i += ATTN_THREADS) {
-                    const int row = i / CPR, c8 = i - row * CPR;
-                    const bool in = tt + row < t1;
-                    const size_t off = (size_t)(in ? tt + row : t1 - 1) * kvdim + (size_t)g * HD + c8 * 8;
-                    cp_async16(ks + row * KROW + c8 * 8, a.kc + off, in ? 16 : 0);
-                    cp_async16(vs + row * HD + c8 * 8, a.vc + off, in ? 16 : 0);
+    // The register route (short splits): one tile in flight, K and V rows in registers.  It leaves the sums of its four
+    // key groups in `ored`, like the staged route.
+    auto register_route = [&]() {
+        for (int tt = t0; tt < t1; tt += ATTN_TILE) {
+            const int tn = min(ATTN_TILE, t1 - tt);
+            // ---- scores
+#pragma unroll
+            for (int bt = 0; bt < 2; bt++) {
+                const int kbase = (bt * 8 + warp) * 4;
+                if (kbase >= tn) {
+                    if (kbase + (lane >> 3) < ATTN_TILE && (lane & 7) < ATTN_REP_MAX) sc[kbase + (lane >> 3)][lane & 7] = -1e30f;
+                    continue;
                 }
-            cp_async_commit();  // a group per tile slot, empty past the end: the wait below counts groups
-        };
+                float v[32];
 #pragma unroll
-        for (int p = 0; p < NST - 1; p++) issue_tile(t0 + p * ATTN_TILE, p);
-        for (int i = tid; i < rep * HD; i += ATTN_THREADS) q_s[i] = a.q[g * rep * HD + i];
-        // Both phases are register-blocked so that shared-memory reads stay well below the FMA count (a 16-byte read
-        // costs the load pipe four cycles per warp even when all lanes read the same address).
-        // Scores: a thread takes KPT keys x all heads x one slice of DSL dims: per 8 dims it reads q once for the
-        // eight heads (16 reads) and each key once (KPT reads) for KPT * 64 FMAs; the DS slices of a key group are
-        // DS adjacent lanes, their partial sums meet in a halving butterfly that leaves lane ds with values 2 ds, 2 ds + 1.
-        // Values: warp w takes keys w, w + 8, ... of the tile, lane l the dims l * DV ..: per key 2 reads of the eight
-        // weights and one of V for 8 * DV FMAs.
-        constexpr int DS = HD >= 128 ? 16 : 8;          // dim slices (lanes) per key group
-        constexpr int DSL = HD / DS;                    // dims per slice: 8 or 16
-        constexpr int KPT = DS / 4;                     // keys per thread: 8 warps x (32 / DS) groups x KPT = 64
-        constexpr int NV = KPT * ATTN_REP_MAX;          // partial sums per thread
-        constexpr int DV = HD / 32;                     // value dims per lane
-        const int ds = lane & (DS - 1), kgrp = warp * (32 / DS) + lane / DS;
-        const int key0 = kgrp * KPT;
-        float o2[ATTN_REP_MAX][DV];
+                for (int kk = 0; kk < 4; kk++) {
+                    float kf[DL];
+                    if constexpr (DL == 4) {
+                        const uint2 raw = kraw[bt][kk];
+                        kf[0] = f16_to_f32((unsigned short)(raw.x & 0xffff));
+                        kf[1] = f16_to_f32((unsigned short)(raw.x >> 16));
+                        kf[2] = f16_to_f32((unsigned short)(raw.y & 0xffff));
+                        kf[3] = f16_to_f32((unsigned short)(raw.y >> 16));
+                    } else if constexpr (DL == 8) {
+                        const uint4 raw = kraw[bt][kk];
+                        const unsigned int rw[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-        for (int h = 0; h < ATTN_REP_MAX; h++)
-#pragma unroll
-            for (int d = 0; d < DV; d++) o2[h][d] = 0.f;
-        int it = 0;
-        for (int tt = t0; tt < t1; tt += ATTN_TILE, it++) {
-            const int tn = min(ATTN_TILE, t1 - tt), cur = it % NST;
-            issue_tile(tt + (NST - 1) * ATTN_TILE, (it + NST - 1) % NST);  // the stage tile it - 1 has just left
-            cp_async_wait_group<NST - 1>();
-            __syncthreads();
-            if (it == 0) prof_mark(6, a.prof_id);
-            {
-                float v[NV];
-#pragma unroll
-                for (int i = 0; i < NV; i++) v[i] = 0.f;
-                const unsigned short* kbase = k_stage(cur) + key0 * KROW + ds * DSL;
-#pragma unroll
-                for (int c = 0; c < DSL; c += 8) {
-                    float kf[KPT][8];
-#pragma unroll
-                    for (int kk = 0; kk < KPT; kk++) {
-                        const int4 kw = *reinterpret_cast<const int4*>(kbase + kk * KROW + c);
-                        const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kw.x)), k1 = __half22float2(*reinterpret_cast<const __half2*>(&kw.y));
-                        const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kw.z)), k3 = __half22float2(*reinterpret_cast<const __half2*>(&kw.w));
-                        kf[kk][0] = k0.x, kf[kk][1] = k0.y, kf[kk][2] = k1.x, kf[kk][3] = k1.y;
-                        kf[kk][4] = k2.x, kf[kk][5] = k2.y, kf[kk][6] = k3.x, kf[kk][7] = k3.y;
+                        for (int d = 0; d < 4; d++) {
+                            kf[2 * d] = f16_to_f32((unsigned short)(rw[d] & 0xffff));
+                            kf[2 * d + 1] = f16_to_f32((unsigned short)(rw[d] >> 16));
+                        }
+                    } else if constexpr (DL == 2) {
+                        kf[0] = f16_to_f32((unsigned short)(kraw[bt][kk] & 0xffff));
+                        kf[1] = f16_to_f32((unsigned short)(kraw[bt][kk] >> 16));
+                    } else {
+                        kf[0] = f16_to_f32((unsigned short)kraw[bt][kk]);
                     }
 #pragma unroll
                     for (int h = 0; h < ATTN_REP_MAX; h++) {
-                        if (h < rep) {
-                            const float* qp = q_s + h * HD + ds * DSL + c;
-                            const float4 a0 = *reinterpret_cast<const float4*>(qp), a1 = *reinterpret_cast<const float4*>(qp + 4);
+                        float acc = 0.f;
 #pragma unroll
-                            for (int kk = 0; kk < KPT; kk++)
-                                v[kk * ATTN_REP_MAX + h] += a0.x * kf[kk][0] + a0.y * kf[kk][1] + a0.z * kf[kk][2] + a0.w * kf[kk][3] +
-                                                            a1.x * kf[kk][4] + a1.y * kf[kk][5] + a1.z * kf[kk][6] + a1.w * kf[kk][7];
-                        }
+                        for (int d = 0; d < DL; d++) acc += qr[h][d] * kf[d];
+                        v[kk * 8 + h] = acc;
                     }
                 }
-                // halving butterfly over the DS lanes of the key group
-#pragma unroll
-                for (int off = DS / 2, n = NV; off >= 1; off >>= 1, n >>= 1) {
-                    const bool up = (lane & off) != 0;
-#pragma unroll
-                    for (int i = 0; i < n / 2; i++) {
-                        const float send = up ? v[i] : v[i + n / 2];
-                        const float keep = up ? v[i + n / 2] : v[i];
-                        v[i] = keep + __shfl_xor_sync(TFR_FULL_MASK, send, off);
-                    }
-                }
-                // this lane now holds values 2 ds and 2 ds + 1 of the group's KPT x 8: key 2 ds / 8, heads 2 ds % 8, + 1
-                const int kl = (2 * ds) >> 3, h0 = (2 * ds) & 7, k = key0 + kl;
-                sc[k][h0] = (k < tn && h0 < rep) ? v[0] * a.scale : -1e30f;
-                sc[k][h0 + 1] = (k < tn && h0 + 1 < rep) ? v[1] * a.scale : -1e30f;
+                const float tot = warp_transpose_reduce32(v, lane);
+                const int kk = lane >> 3, h = lane & 7;
+                const int t = tt + kbase + kk;
+                sc[kbase + kk][h] = (t < t1 && h < rep) ? tot * a.scale : -1e30f;
             }
+            // the key registers are free: the next tile's key rows travel during the softmax and the value phase
+            if (tt + ATTN_TILE < t1) load_k(tt + ATTN_TILE, t1, false);
             __syncthreads();
-            if (warp < rep) {  // online softmax bookkeeping: warp h owns head h
+            prof_mark(6, a.prof_id);
+            // ---- online softmax bookkeeping: warp h owns head h
+            if (warp < rep) {
                 const float s0 = sc[lane][warp], s1 = sc[lane + 32][warp];
                 const float tile_m = warp_max(fmaxf(s0, s1));
                 const float m_old = m_s[warp];
                 const float m_new = fmaxf(m_old, tile_m);
-                const float p0 = (lane < tn) ? expf(s0 - m_new) : 0.f;
-                const float p1 = (lane + 32 < tn) ? expf(s1 - m_new) : 0.f;
+                const float p0 = (tt + lane < t1) ? expf(s0 - m_new) : 0.f;
+                const float p1 = (tt + lane + 32 < t1) ? expf(s1 - m_new) : 0.f;
                 const float tile_l = warp_sum(p0 + p1);
                 sc[lane][warp] = p0;
                 sc[lane + 32][warp] = p1;
@@ -293,185 +289,275 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
                 }
             }
             __syncthreads();
+            prof_mark(7, a.prof_id);
+            // ---- values: thread (kg, dp) accumulates keys kg, kg+4, ... for dims dp*DPT..
 #pragma unroll
             for (int h = 0; h < ATTN_REP_MAX; h++) {
                 const float al = h < rep ? alpha_s[h] : 1.f;
 #pragma unroll
-                for (int d = 0; d < DV; d++) o2[h][d] *= al;
+                for (int d = 0; d < DPT; d++) o[h][d] *= al;
             }
-            const unsigned short* vs = v_stage(cur);
-#pragma unroll 2
-            for (int k = warp; k < tn; k += 8) {
-                const float4 pa = *reinterpret_cast<const float4*>(&sc[k][0]), pb = *reinterpret_cast<const float4*>(&sc[k][4]);
-                const float p[ATTN_REP_MAX] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
-                float vf[DV];
-                const unsigned short* vr = vs + k * HD + lane * DV;
-                if constexpr (DV == 8) {
-                    const uint4 raw = *reinterpret_cast<const uint4*>(vr);
-                    const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x)), v1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-                    const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&raw.z)), v3 = __half22float2(*reinterpret_cast<const __half2*>(&raw.w));
-                    vf[0] = v0.x, vf[1] = v0.y, vf[2] = v1.x, vf[3] = v1.y, vf[4] = v2.x, vf[5] = v2.y, vf[6] = v3.x, vf[7] = v3.y;
-                } else if constexpr (DV == 4) {
-                    const uint2 raw = *reinterpret_cast<const uint2*>(vr);
-                    const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x)), v1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-                    vf[0] = v0.x, vf[1] = v0.y, vf[2] = v1.x, vf[3] = v1.y;
-                } else {
-                    const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(vr));
-                    vf[0] = v0.x, vf[1] = v0.y;
+            // Keys past the end of the tile carry weight 0 and value 0, so groups of four keys run without
+            // per-key branches; a group that lies wholly past the end is skipped (uniform over the CTA).
+#pragma unroll
+            for (int i0 = 0; i0 < VK; i0 += 4) {
+                if (4 * i0 >= tn) break;
+                float4 pa[4], pb[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int k = kg + 4 * (i0 + j);
+                    pa[j] = *reinterpret_cast<const float4*>(&sc[k][0]);
+                    pb[j] = *reinterpret_cast<const float4*>(&sc[k][4]);
                 }
 #pragma unroll
-                for (int h = 0; h < ATTN_REP_MAX; h++) {
-                    if (h < rep) {
+                for (int j = 0; j < 4; j++) {
+                    float vf[DPT];
+                    vf[0] = f16_to_f32((unsigned short)(vraw[i0 + j].x & 0xffff));
+                    if constexpr (DPT >= 2) vf[1] = f16_to_f32((unsigned short)(vraw[i0 + j].x >> 16));
+                    if constexpr (DPT == 4) {
+                        vf[2] = f16_to_f32((unsigned short)(vraw[i0 + j].y & 0xffff));
+                        vf[3] = f16_to_f32((unsigned short)(vraw[i0 + j].y >> 16));
+                    }
+                    const float p[ATTN_REP_MAX] = {pa[j].x, pa[j].y, pa[j].z, pa[j].w, pb[j].x, pb[j].y, pb[j].z, pb[j].w};
 #pragma unroll
-                        for (int d = 0; d < DV; d++) o2[h][d] += p[h] * vf[d];
+                    for (int h = 0; h < ATTN_REP_MAX; h++) {
+                        if (h < rep) {
+#pragma unroll
+                            for (int d = 0; d < DPT; d++) o[h][d] += p[h] * vf[d];
+                        }
                     }
                 }
             }
-            __syncthreads();  // the next iteration overwrites sc and refills the stage just used
+            // the next tile's value rows are requested now and used after the next tile's softmax
+            if (tt + ATTN_TILE < t1) load_v(tt + ATTN_TILE, t1, false);
+            __syncthreads();
+        }
+
+#pragma unroll
+        for (int h = 0; h < ATTN_REP_MAX; h++)
+#pragma unroll
+            for (int d = 0; d < DPT; d++) ored[kg][h][dp * DPT + d] = o[h][d];
+    };
+    if constexpr (STAGED) {
+        // ---- the staged route: K and V tiles travel global -> shared memory as asynchronous 16-byte copies, NST stages
+        // deep (the first ones requested before the dependency wait), so the loads of the next tiles run under the
+        // arithmetic of tile i and no register holds cache data.  Sixteen warps.
+        float* q_s = reinterpret_cast<float*>(attn_dyn + NST * stage_b);
+        {
+            // row T - 1, written by the previous kernel, if it lies in one of the tiles requested before the wait
+            const int row = T - 1 - t0;
+            if (T - 1 < t1 && row < (NST - 1) * ATTN_TILE && tid < 2 * CPR) {
+                const int st_ = row / ATTN_TILE, r = row % ATTN_TILE, c8 = tid % CPR;
+                const size_t off = (size_t)(T - 1) * kvdim + (size_t)g * HD + c8 * 8;
+                if (tid < CPR) *reinterpret_cast<int4*>(k_stage(st_) + r * KROW + c8 * 8) = *reinterpret_cast<const int4*>(a.kc + off);
+                else *reinterpret_cast<int4*>(v_stage(st_) + r * HD + c8 * 8) = *reinterpret_cast<const int4*>(a.vc + off);
+            }
+        }
+        // Both phases are register-blocked so that shared-memory reads stay well below the FMA count (a 16-byte read
+        // costs the load pipe four cycles per warp even when all lanes read the same address), and both split the
+        // eight heads in two halves so that a thread's state fits the 128 registers of a 512-thread CTA.
+        // Scores: a thread takes KPT keys x four heads x one slice of DSL dims; the DS slices of a (key group, head half)
+        // are DS adjacent lanes, the two halves of a key group sit in the same warp (one shared-memory read serves
+        // both); the partial sums meet in a halving butterfly that leaves every lane with ONE score.  With 8-dim
+        // slices the thread's q values (four heads x eight dims) stay in registers for the whole split.  Group kgrp
+        // takes keys kgrp, kgrp + NG, ...: a short last tile costs less.
+        // Values: a warp takes KPI keys per round for one head half, HD / 8 lanes per key, a lane eight dims: per key
+        // one read of the four weights and one 16-byte read of V for 32 FMAs.
+        constexpr int HH = ATTN_REP_MAX / 2;            // heads per half
+        constexpr int DS = HD >= 128 ? 16 : 8;          // dim slices (lanes) per group
+        constexpr int DSL = HD / DS;                    // dims per slice: 8 or 16
+        constexpr int NG = NT / DS / 2;                 // key groups
+        constexpr int KPT = ATTN_TILE / NG;             // keys per thread
+        constexpr int NV = KPT * HH;                    // partial sums per thread (= DS)
+        static_assert(NV == DS, "the butterfly leaves one value per lane");
+        constexpr int DV = 8;                           // value dims per lane: one 16-byte read of a V row
+        constexpr int LPK = HD / DV, KPI = 32 / LPK;    // lanes per key and keys per warp and round in the value phase
+        constexpr int KW = NT / 64;                     // warps per head half in the value phase
+        constexpr bool QREG = DSL == 8;
+        const int ds = lane & (DS - 1);
+        const int grp = warp * (32 / DS) + lane / DS, kgrp = grp >> 1, hh = grp & 1;   // scores: key group and head half
+        const int vkl = lane / LPK, vdl = lane % LPK, vkw = warp >> 1, vhh = warp & 1;  // values
+        float qreg[QREG ? HH : 1][8];
+        if constexpr (QREG) {
+#pragma unroll
+            for (int h = 0; h < HH; h++) {
+                const bool on = hh * HH + h < rep;
+                const float* qp = a.q + (size_t)(g * rep + (on ? hh * HH + h : 0)) * HD + ds * DSL;
+                const float4 a0 = *reinterpret_cast<const float4*>(qp), a1 = *reinterpret_cast<const float4*>(qp + 4);
+                qreg[h][0] = on ? a0.x : 0.f, qreg[h][1] = on ? a0.y : 0.f, qreg[h][2] = on ? a0.z : 0.f, qreg[h][3] = on ? a0.w : 0.f;
+                qreg[h][4] = on ? a1.x : 0.f, qreg[h][5] = on ? a1.y : 0.f, qreg[h][6] = on ? a1.z : 0.f, qreg[h][7] = on ? a1.w : 0.f;
+            }
+        } else {
+            for (int i = tid; i < ATTN_REP_MAX * HD; i += NT) q_s[i] = i < rep * HD ? a.q[g * rep * HD + i] : 0.f;
+        }
+        float o2[HH][DV];
+#pragma unroll
+        for (int h = 0; h < HH; h++)
+#pragma unroll
+            for (int d = 0; d < DV; d++) o2[h][d] = 0.f;
+        // Softmax bookkeeping without a serial section.  The tile's row maxima are gathered by warp shuffles and one
+        // shared-memory atomic max per warp and head (maxima do not depend on the order); after a barrier every thread
+        // derives the new running maxima and its rescale factors for itself, the owning lane turns its score into a
+        // weight, and the weight sums go through per-warp slots that eight threads add in a fixed order.
+        __shared__ __align__(16) unsigned int tmax[2][ATTN_REP_MAX];  // ordered-integer image of the tile maxima (read as uint4)
+        __shared__ __align__(16) float tl[NT / 32][ATTN_REP_MAX];     // per-warp sums of the tile's weights
+        auto enc = [](float f) { const unsigned u = __float_as_uint(f); return (u & 0x80000000u) ? ~u : (u | 0x80000000u); };
+        auto dec = [](unsigned k) { return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k); };
+        if (tid < 2 * ATTN_REP_MAX) tmax[tid >> 3][tid & 7] = enc(-1e30f);
+        int it = 0;
+        for (int tt = t0; tt < t1; tt += ATTN_TILE, it++) {
+            const int tn = min(ATTN_TILE, t1 - tt), cur = it % NST, par = it & 1;
+            cp_async_wait_group<NST - 2>();  // this thread's pieces of tile `it`
+            __syncthreads();                 // everybody's pieces, and everybody is done with tile it - 1
+            issue_tile(tt + (NST - 1) * ATTN_TILE, (it + NST - 1) % NST, -1);  // into the stage tile it - 1 has just left
+            if (it == 0) prof_mark(6, a.prof_id);
+            float sv = 0.f;  // this lane's score of the tile
+            auto scores = [&](auto kact_tag) {
+                constexpr int KACT = decltype(kact_tag)::value;  // keys per thread that the tile reaches
+                float v[NV];
+#pragma unroll
+                for (int i = 0; i < NV; i++) v[i] = 0.f;
+                const unsigned short* kbase = k_stage(cur) + kgrp * KROW + ds * DSL;
+#pragma unroll
+                for (int c = 0; c < DSL; c += 8) {
+#pragma unroll
+                    for (int kk = 0; kk < KACT; kk++) {
+                        const int4 kw = *reinterpret_cast<const int4*>(kbase + kk * NG * KROW + c);
+                        const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kw.x)), k1 = __half22float2(*reinterpret_cast<const __half2*>(&kw.y));
+                        const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kw.z)), k3 = __half22float2(*reinterpret_cast<const __half2*>(&kw.w));
+#pragma unroll
+                        for (int h = 0; h < HH; h++) {
+                            float4 a0, a1;
+                            if constexpr (QREG) {
+                                a0 = make_float4(qreg[h][0], qreg[h][1], qreg[h][2], qreg[h][3]);
+                                a1 = make_float4(qreg[h][4], qreg[h][5], qreg[h][6], qreg[h][7]);
+                            } else {
+                                const float* qp = q_s + (hh * HH + h) * HD + ds * DSL + c;
+                                a0 = *reinterpret_cast<const float4*>(qp), a1 = *reinterpret_cast<const float4*>(qp + 4);
+                            }
+                            float t = v[kk * HH + h];
+                            t = fmaf(a0.x, k0.x, t), t = fmaf(a0.y, k0.y, t), t = fmaf(a0.z, k1.x, t), t = fmaf(a0.w, k1.y, t);
+                            t = fmaf(a1.x, k2.x, t), t = fmaf(a1.y, k2.y, t), t = fmaf(a1.z, k3.x, t), t = fmaf(a1.w, k3.y, t);
+                            v[kk * HH + h] = t;
+                        }
+                    }
+                }
+                // halving butterfly over the DS lanes of the group
+#pragma unroll
+                for (int off = DS / 2, n = NV; off >= 1; off >>= 1, n >>= 1) {
+                    const bool up = (lane & off) != 0;
+#pragma unroll
+                    for (int i = 0; i < n / 2; i++) {
+                        const float send = up ? v[i] : v[i + n / 2];
+                        const float keep = up ? v[i + n / 2] : v[i];
+                        v[i] = keep + __shfl_xor_sync(TFR_FULL_MASK, send, off);
+                    }
+                }
+                sv = v[0];
+            };
+            // rows past the end of the split arrive as zeros, so the full schedule is right for any tile; a tile that
+            // reaches only the first key of every group (the short tail of a split) runs a quarter of it
+            if (tn > NG) scores(std::integral_constant<int, KPT>{});
+            else scores(std::integral_constant<int, 1>{});
+            // the lane holds value ds of the group's KPT x 4: the group's key number ds / 4, head ds % 4 of its half
+            const int sk = (ds >> 2) * NG + kgrp, sh = hh * HH + (ds & 3);
+            const bool s_on = sk < tn && sh < rep;
+            sv = s_on ? sv * a.scale : -1e30f;
+            {
+                float mx = sv;  // lanes that agree in lane & 3 and in the head-half bit hold the same head
+#pragma unroll
+                for (int off = 4; off <= 16; off <<= 1)
+                    if (off != DS) mx = fmaxf(mx, __shfl_xor_sync(TFR_FULL_MASK, mx, off));
+                if ((lane & (28 & ~DS)) == 0) atomicMax(&tmax[par][sh], enc(mx));
+            }
+            __syncthreads();
+            {
+                const float4 mo0 = *reinterpret_cast<const float4*>(&m_s[0]), mo1 = *reinterpret_cast<const float4*>(&m_s[4]);
+                const uint4 t0v = *reinterpret_cast<const uint4*>(&tmax[par][0]), t1v = *reinterpret_cast<const uint4*>(&tmax[par][4]);
+                const float m_old[ATTN_REP_MAX] = {mo0.x, mo0.y, mo0.z, mo0.w, mo1.x, mo1.y, mo1.z, mo1.w};
+                const unsigned tm[ATTN_REP_MAX] = {t0v.x, t0v.y, t0v.z, t0v.w, t1v.x, t1v.y, t1v.z, t1v.w};
+                float m_new[ATTN_REP_MAX];
+#pragma unroll
+                for (int h = 0; h < ATTN_REP_MAX; h++) m_new[h] = fmaxf(m_old[h], dec(tm[h]));
+                // the running maxima of a long split settle after its first tiles: rescale only when one has moved
+                bool moved = false;
+#pragma unroll
+                for (int h = 0; h < HH; h++) moved |= (vhh ? m_new[HH + h] != m_old[HH + h] : m_new[h] != m_old[h]);
+                if (moved) {
+#pragma unroll
+                    for (int h = 0; h < HH; h++) {
+                        const float al = vhh ? expf(m_old[HH + h] - m_new[HH + h]) : expf(m_old[h] - m_new[h]);
+#pragma unroll
+                        for (int d = 0; d < DV; d++) o2[h][d] *= al;
+                    }
+                }
+                const int sel = lane & 3;
+                const float mlo = sel == 0 ? m_new[0] : sel == 1 ? m_new[1] : sel == 2 ? m_new[2] : m_new[3];
+                const float mhi = sel == 0 ? m_new[4] : sel == 1 ? m_new[5] : sel == 2 ? m_new[6] : m_new[7];
+                const float pw = s_on ? expf(sv - (hh ? mhi : mlo)) : 0.f;
+                sc[sk][sh] = pw;
+                float ls = pw;
+#pragma unroll
+                for (int off = 4; off <= 16; off <<= 1)
+                    if (off != DS) ls += __shfl_xor_sync(TFR_FULL_MASK, ls, off);
+                if ((lane & (28 & ~DS)) == 0) tl[warp][sh] = ls;
+            }
+            __syncthreads();
+            if (tid < ATTN_REP_MAX) {
+                const float m_old = m_s[tid], mn = fmaxf(m_old, dec(tmax[par][tid]));
+                float sum = 0.f;
+#pragma unroll
+                for (int w = 0; w < NT / 32; w++) sum += tl[w][tid];
+                l_s[tid] = l_s[tid] * expf(m_old - mn) + sum;
+                m_s[tid] = mn;
+                tmax[par][tid] = enc(-1e30f);  // free for tile it + 2
+            }
+            const unsigned short* vs = v_stage(cur);
+#pragma unroll 2
+            for (int k = vkw * KPI + vkl; k < tn; k += KW * KPI) {
+                const float4 pa = *reinterpret_cast<const float4*>(&sc[k][vhh * HH]);
+                const float p[HH] = {pa.x, pa.y, pa.z, pa.w};
+                const uint4 raw = *reinterpret_cast<const uint4*>(vs + k * HD + vdl * DV);
+                const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x)), v1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+                const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&raw.z)), v3 = __half22float2(*reinterpret_cast<const __half2*>(&raw.w));
+                const float vf[DV] = {v0.x, v0.y, v1.x, v1.y, v2.x, v2.y, v3.x, v3.y};
+#pragma unroll
+                for (int h = 0; h < HH; h++)
+#pragma unroll
+                    for (int d = 0; d < DV; d++) o2[h][d] = fmaf(p[h], vf[d], o2[h][d]);
+            }
             if (it == 0) prof_mark(7, a.prof_id);
         }
-        // the eight key groups (warps) fold into the four slots the epilogue sums
+        __syncthreads();  // the last tile's weights and the final (m, l) are settled
+        // the key lanes of a warp fold by shuffles, then the eight key warps of a head half fold into the four slots the epilogue sums
 #pragma unroll
-        for (int half = 0; half < 2; half++) {
-            if ((warp >> 2) == half) {
+        for (int off = 16; off >= LPK; off >>= 1)
 #pragma unroll
-                for (int h = 0; h < ATTN_REP_MAX; h++)
+            for (int h = 0; h < HH; h++)
+#pragma unroll
+                for (int d = 0; d < DV; d++) o2[h][d] += __shfl_xor_sync(TFR_FULL_MASK, o2[h][d], off);
+#pragma unroll
+        for (int half = 0; half < KW / 4; half++) {
+            if ((vkw >> 2) == half && lane < LPK) {
+#pragma unroll
+                for (int h = 0; h < HH; h++)
 #pragma unroll
                     for (int d = 0; d < DV; d++) {
-                        float* dst = &ored[warp & 3][h][lane * DV + d];
+                        float* dst = &ored[vkw & 3][vhh * HH + h][lane * DV + d];
                         *dst = half ? *dst + o2[h][d] : o2[h][d];
                     }
             }
             __syncthreads();
         }
+    } else {
+        register_route();
     }
-    for (int tt = t0; tt < t1 && !long_path; tt += ATTN_TILE) {
-        const int tn = min(ATTN_TILE, t1 - tt);
-        // ---- scores
-#pragma unroll
-        for (int bt = 0; bt < 2; bt++) {
-            const int kbase = (bt * 8 + warp) * 4;
-            if (kbase >= tn) {
-                if (kbase + (lane >> 3) < ATTN_TILE && (lane & 7) < ATTN_REP_MAX) sc[kbase + (lane >> 3)][lane & 7] = -1e30f;
-                continue;
-            }
-            float v[32];
-#pragma unroll
-            for (int kk = 0; kk < 4; kk++) {
-                float kf[DL];
-                if constexpr (DL == 4) {
-                    const uint2 raw = kraw[bt][kk];
-                    kf[0] = f16_to_f32((unsigned short)(raw.x & 0xffff));
-                    kf[1] = f16_to_f32((unsigned short)(raw.x >> 16));
-                    kf[2] = f16_to_f32((unsigned short)(raw.y & 0xffff));
-                    kf[3] = f16_to_f32((unsigned short)(raw.y >> 16));
-                } else if constexpr (DL == 8) {
-                    const uint4 raw = kraw[bt][kk];
-                    const unsigned int rw[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-                    for (int d = 0; d < 4; d++) {
-                        kf[2 * d] = f16_to_f32((unsigned short)(rw[d] & 0xffff));
-                        kf[2 * d + 1] = f16_to_f32((unsigned short)(rw[d] >> 16));
-                    }
-                } else if constexpr (DL == 2) {
-                    kf[0] = f16_to_f32((unsigned short)(kraw[bt][kk] & 0xffff));
-                    kf[1] = f16_to_f32((unsigned short)(kraw[bt][kk] >> 16));
-                } else {
-                    kf[0] = f16_to_f32((unsigned short)kraw[bt][kk]);
-                }
-#pragma unroll
-                for (int h = 0; h < ATTN_REP_MAX; h++) {
-                    float acc = 0.f;
-#pragma unroll
-                    for (int d = 0; d < DL; d++) acc += qr[h][d] * kf[d];
-                    v[kk * 8 + h] = acc;
-                }
-            }
-            const float tot = warp_transpose_reduce32(v, lane);
-            const int kk = lane >> 3, h = lane & 7;
-            const int t = tt + kbase + kk;
-            sc[kbase + kk][h] = (t < t1 && h < rep) ? tot * a.scale : -1e30f;
-        }
-        // the key registers are free: the next tile's key rows travel during the softmax and the value phase
-        if (tt + ATTN_TILE < t1) load_k(tt + ATTN_TILE, t1, false);
-        __syncthreads();
-        prof_mark(6, a.prof_id);
-        // ---- online softmax bookkeeping: warp h owns head h
-        if (warp < rep) {
-            const float s0 = sc[lane][warp], s1 = sc[lane + 32][warp];
-            const float tile_m = warp_max(fmaxf(s0, s1));
-            const float m_old = m_s[warp];
-            const float m_new = fmaxf(m_old, tile_m);
-            const float p0 = (tt + lane < t1) ? expf(s0 - m_new) : 0.f;
-            const float p1 = (tt + lane + 32 < t1) ? expf(s1 - m_new) : 0.f;
-            const float tile_l = warp_sum(p0 + p1);
-            sc[lane][warp] = p0;
-            sc[lane + 32][warp] = p1;
-            if (lane == 0) {
-                const float alpha = expf(m_old - m_new);
-                alpha_s[warp] = alpha;
-                l_s[warp] = l_s[warp] * alpha + tile_l;
-                m_s[warp] = m_new;
-            }
-        }
-        __syncthreads();
-        prof_mark(7, a.prof_id);
-        // ---- values: thread (kg, dp) accumulates keys kg, kg+4, ... for dims dp*DPT..
-#pragma unroll
-        for (int h = 0; h < ATTN_REP_MAX; h++) {
-            const float al = h < rep ? alpha_s[h] : 1.f;
-#pragma unroll
-            for (int d = 0; d < DPT; d++) o[h][d] *= al;
-        }
-        // Keys past the end of the tile carry weight 0 and value 0, so groups of four keys run without
-        // per-key branches; a group that lies wholly past the end is skipped (uniform over the CTA).
-#pragma unroll
-        for (int i0 = 0; i0 < VK; i0 += 4) {
-            if (4 * i0 >= tn) break;
-            float4 pa[4], pb[4];
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int k = kg + 4 * (i0 + j);
-                pa[j] = *reinterpret_cast<const float4*>(&sc[k][0]);
-                pb[j] = *reinterpret_cast<const float4*>(&sc[k][4]);
-            }
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                float vf[DPT];
-                vf[0] = f16_to_f32((unsigned short)(vraw[i0 + j].x & 0xffff));
-                if constexpr (DPT >= 2) vf[1] = f16_to_f32((unsigned short)(vraw[i0 + j].x >> 16));
-                if constexpr (DPT == 4) {
-                    vf[2] = f16_to_f32((unsigned short)(vraw[i0 + j].y & 0xffff));
-                    vf[3] = f16_to_f32((unsigned short)(vraw[i0 + j].y >> 16));
-                }
-                const float p[ATTN_REP_MAX] = {pa[j].x, pa[j].y, pa[j].z, pa[j].w, pb[j].x, pb[j].y, pb[j].z, pb[j].w};
-#pragma unroll
-                for (int h = 0; h < ATTN_REP_MAX; h++) {
-                    if (h < rep) {
-#pragma unroll
-                        for (int d = 0; d < DPT; d++) o[h][d] += p[h] * vf[d];
-                    }
-                }
-            }
-        }
-        // the next tile's value rows are requested now and used after the next tile's softmax
-        if (tt + ATTN_TILE < t1) load_v(tt + ATTN_TILE, t1, false);
-        __syncthreads();
-    }
-
     prof_mark(2, a.prof_id);
-    // ---- combine the four key groups and write this split's (m, l, O)
-    if (!long_path) {
-#pragma unroll
-        for (int h = 0; h < ATTN_REP_MAX; h++)
-#pragma unroll
-            for (int d = 0; d < DPT; d++) ored[kg][h][dp * DPT + d] = o[h][d];
-    }
     __syncthreads();
     const int po = 2 + HD;
     if (S_eff == 1) {
         // single split: normalise and store directly (the merge of one partial is the identity)
-        for (int idx = tid; idx < rep * HD; idx += ATTN_THREADS) {
+        for (int idx = tid; idx < rep * HD; idx += NT) {
             const int h = idx / HD, d = idx % HD;
             const int hg = g * rep + h;
             const float tot = ored[0][h][d] + ored[1][h][d] + ored[2][h][d] + ored[3][h][d];
@@ -487,23 +573,23 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
     // where remote loads cost a round trip each.  After one cluster barrier member j merges slice j of the
     // cluster's eight splits from local memory; nothing remote is touched afterwards, so members leave
     // independently.  Members past the last split send zeros that the merge skips, and still own a slice.
-    const int cl = s / ATTN_CLUSTER, rk = s % ATTN_CLUSTER;
-    const int total = rep * HD, per = total / ATTN_CLUSTER;  // per <= HD
-    for (int idx = tid; idx < total; idx += ATTN_THREADS) {
+    const int cl = s / CL, rk = s % CL;
+    const int total = rep * HD, per = total / CL;
+    for (int idx = tid; idx < total; idx += NT) {
         const int h = idx / HD, d = idx % HD;
         const float v = ored[0][h][d] + ored[1][h][d] + ored[2][h][d] + ored[3][h][d];
-        st_dsmem_f32(&gath[rk][idx % per], (unsigned)(idx / per), v);
+        st_dsmem_f32(&gath[rk * per + idx % per], (unsigned)(idx / per), v);
     }
-    if (tid < ATTN_CLUSTER * ATTN_REP_MAX) {
+    if (tid < CL * ATTN_REP_MAX) {
         const int r = tid / ATTN_REP_MAX, h = tid % ATTN_REP_MAX;
         st_dsmem_f32(&gm[rk][h], (unsigned)r, m_s[h]);
         st_dsmem_f32(&gl[rk][h], (unsigned)r, l_s[h]);
     }
     cluster_sync_all();
     prof_mark(3, a.prof_id);
-    const int in_cl = min(ATTN_CLUSTER, S_eff - cl * ATTN_CLUSTER);  // splits of this cluster that had keys
+    const int in_cl = min(CL, S_eff - cl * CL);  // splits of this cluster that had keys
     if (n_cl == 1) {
-        for (int i = tid; i < per; i += ATTN_THREADS) {
+        for (int i = tid; i < per; i += NT) {
             const int idx = rk * per + i;
             const int h = idx / HD, d = idx % HD;
             const int hg = g * rep + h;
@@ -513,7 +599,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
             for (int r = 0; r < in_cl; r++) {
                 const float al = expf(gm[r][h] - m);
                 l += al * gl[r][h];
-                acc += al * gath[r][i];
+                acc += al * gath[r * per + i];
             }
             float res = acc / fmaxf(l, 1e-20f);
             if (a.gate) res *= 1.f / (1.f + expf(-a.gate[hg * HD + d]));
@@ -528,7 +614,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
     // eight slices of a KV head finish independently on eight SMs.
     {
         float* pbase = a.partial;
-        for (int i = tid; i < per; i += ATTN_THREADS) {
+        for (int i = tid; i < per; i += NT) {
             const int idx = rk * per + i;
             const int h = idx / HD, d = idx % HD;
             float m = -1e30f;
@@ -537,7 +623,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
             for (int r = 0; r < in_cl; r++) {
                 const float al = expf(gm[r][h] - m);
                 l += al * gl[r][h];
-                acc += al * gath[r][i];
+                acc += al * gath[r * per + i];
             }
             float* base = pbase + ((size_t)(g * rep + h) * a.S + cl) * po;
             base[2 + d] = acc;
@@ -558,21 +644,36 @@ __global__ void __launch_bounds__(ATTN_THREADS) k_attn_decode(AttnArgs a, const 
     __syncthreads();
     if (!is_last_s) return;
     __threadfence();
-    for (int i = tid; i < per; i += ATTN_THREADS) {
+    for (int i = tid; i < per; i += NT) {
         const int idx = rk * per + i;
         const int h = idx / HD, d = idx % HD;
         const int hg = g * rep + h;
         const float* hb = a.partial + (size_t)hg * a.S * po;
-        float m = -1e30f;
-#pragma unroll 4
-        for (int c = 0; c < n_cl; c++) m = fmaxf(m, __ldcg(hb + (size_t)c * po));
-        float l = 0.f, acc = 0.f;
-#pragma unroll 4
-        for (int c = 0; c < n_cl; c++) {
-            const float* b = hb + (size_t)c * po;
-            const float al = expf(__ldcg(b) - m);
-            l += al * __ldcg(b + 1);
-            acc += al * __ldcg(b + 2 + d);
+        // eight cluster partials per round, all of a round's loads in flight together (one trip to L2 per round)
+        float m = -1e30f, l = 0.f, acc = 0.f;
+        for (int c0 = 0; c0 < n_cl; c0 += 8) {
+            float mm[8], ll[8], aa[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const bool on = c0 + j < n_cl;
+                const float* b = hb + (size_t)(on ? c0 + j : c0) * po;
+                mm[j] = on ? __ldcg(b) : -1e30f;
+                ll[j] = on ? __ldcg(b + 1) : 0.f;
+                aa[j] = on ? __ldcg(b + 2 + d) : 0.f;
+            }
+            float m_new = m;
+#pragma unroll
+            for (int j = 0; j < 8; j++) m_new = fmaxf(m_new, mm[j]);
+            const float keep = expf(m - m_new);
+            l *= keep;
+            acc *= keep;
+            m = m_new;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float al = expf(mm[j] - m);
+                l += al * ll[j];
+                acc += al * aa[j];
+            }
         }
         float r = acc / fmaxf(l, 1e-20f);
         if (a.gate) r *= 1.f / (1.f + expf(-a.gate[hg * HD + d]));

@@ -148,7 +148,7 @@ struct tfr_engine {
     TokenState* st_host = nullptr;  // pinned
     int *out_tokens = nullptr, *out_host = nullptr, *prompt = nullptr;
     int *args_dev = nullptr, *args_host = nullptr;  // per-call scalars: pinned host -> device
-    int attn_S = 1, attn_min_keys = 64;
+    int attn_S = 1, attn_S_staged = 1, attn_min_keys = 64;  // splits per KV head of the two attention instances
     float* layer_taps = nullptr;  // [n_layer][n_embd] residual stream after each layer (test aid)
     // [n_layer][...] the other vectors a dense layer quantises: attention output, residual after o-proj, SiLU*mul (test aid)
     float *tap_attn = nullptr, *tap_mid = nullptr, *tap_h = nullptr;
@@ -306,35 +306,42 @@ static void configure_kernels_once() {
     configure_kernel(k_state_next_prompt, false);
 }
 
-// Clusters of eight attention CTAs the device can hold at once for a head size (a cluster needs eight SMs
-// of one GPC with room for a CTA each); 0 when the query fails.  Cached per head size.
-static int attn_max_clusters(int hd) {
-    static int cache_all[TFR_MAX_DEVICES][3];
+// Clusters of attention CTAs the device can hold at once for a head size and kernel instance (a cluster needs its
+// SMs in one GPC with room for a CTA each); 0 when the query fails.  Cached per head size and instance.
+static int attn_max_clusters(int hd, bool staged) {
+    static int cache_all[TFR_MAX_DEVICES][6];
     static bool cache_init = false;
     if (!cache_init) {
-        for (auto& d : cache_all) d[0] = d[1] = d[2] = -1;
+        for (auto& d : cache_all)
+            for (int& v : d) v = -1;
         cache_init = true;
     }
     configure_kernels_once();  // the query below asks for the kernel's opt-in dynamic shared memory
     int* cache = cache_all[current_device_slot()];
-    const int slot = hd == 64 ? 0 : hd == 128 ? 1 : 2;
+    const int slot = (hd == 64 ? 0 : hd == 128 ? 1 : 2) + (staged ? 3 : 0);
     if (cache[slot] >= 0) return cache[slot];
+    const int cl = attn_cluster(staged);
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(ATTN_CLUSTER * 64, 1);
-    cfg.blockDim = dim3(ATTN_THREADS);
-    cfg.dynamicSmemBytes = attn_dyn_smem(hd);
+    cfg.gridDim = dim3(cl * 64, 1);
+    cfg.blockDim = dim3(attn_threads(staged));
+    cfg.dynamicSmemBytes = staged ? attn_dyn_smem(hd) : 0;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = ATTN_CLUSTER;
+    attr[0].val.clusterDim.x = cl;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    // asked for the instance with the larger footprint (the staged route): the split count then fits both
-    cudaError_t r = hd == 64    ? cudaOccupancyMaxActiveClusters(&n, k_attn_decode<64, true>, &cfg)
-                    : hd == 128 ? cudaOccupancyMaxActiveClusters(&n, k_attn_decode<128, true>, &cfg)
-                                : cudaOccupancyMaxActiveClusters(&n, k_attn_decode<256, true>, &cfg);
+    cudaError_t r;
+    if (staged)
+        r = hd == 64    ? cudaOccupancyMaxActiveClusters(&n, k_attn_decode<64, true>, &cfg)
+            : hd == 128 ? cudaOccupancyMaxActiveClusters(&n, k_attn_decode<128, true>, &cfg)
+                        : cudaOccupancyMaxActiveClusters(&n, k_attn_decode<256, true>, &cfg);
+    else
+        r = hd == 64    ? cudaOccupancyMaxActiveClusters(&n, k_attn_decode<64, false>, &cfg)
+            : hd == 128 ? cudaOccupancyMaxActiveClusters(&n, k_attn_decode<128, false>, &cfg)
+                        : cudaOccupancyMaxActiveClusters(&n, k_attn_decode<256, false>, &cfg);
     if (r != cudaSuccess) {
         cudaGetLastError();
         n = 0;
@@ -343,14 +350,17 @@ static int attn_max_clusters(int hd) {
     return n;
 }
 
-// Splits per KV head: a multiple of the cluster size, about one CTA per SM over all KV heads, and no more
-// clusters than run at the same time (a second wave would double the kernel's duration).
-static int attn_splits(int sms, int n_kv, int hd) {
-    int s = sms / n_kv / ATTN_CLUSTER * ATTN_CLUSTER;
-    const int fit = attn_max_clusters(hd) / n_kv * ATTN_CLUSTER;
-    if (fit >= ATTN_CLUSTER && fit < s) s = fit;
-    return s < ATTN_CLUSTER ? ATTN_CLUSTER : s;
+// Splits per KV head of an instance: a multiple of its cluster size, about one CTA per SM over all KV heads, and no
+// more clusters than run at the same time (a second wave would double the kernel's duration).
+static int attn_splits(int sms, int n_kv, int hd, bool staged) {
+    const int cl = attn_cluster(staged);
+    int s = sms / n_kv / cl * cl;
+    const int fit = attn_max_clusters(hd, staged) / n_kv * cl;
+    if (fit >= cl && fit < s) s = fit;
+    return s < cl ? cl : s;
 }
+// The staged instance is launched for caches (or positions) that reach beyond this many keys.
+static int attn_staged_threshold(int sms, int n_kv, int hd) { return attn_splits(sms, n_kv, hd, false) * ATTN_LONG_MIN; }
 
 static int sm_count_cached() {
     static int count[TFR_MAX_DEVICES] = {};
@@ -1136,7 +1146,8 @@ extern "C" int tfr_finalize_load(tfr_engine* e) {
     e->held.clear();
     // workspaces (load.rs:547-607: everything allocated once)
     const int sms = e->prop.multiProcessorCount;
-    e->attn_S = attn_splits(sms, P.n_kv, hd);
+    e->attn_S = attn_splits(sms, P.n_kv, hd, false);
+    e->attn_S_staged = attn_splits(sms, P.n_kv, hd, true);
     CU(e, cudaMalloc(&e->x, (size_t)K * 4));
     const int vd = c.hybrid ? gdn_val_dim(c) : 0;
     CU(e, cudaMalloc(&e->q, (size_t)nq * 4));
@@ -1150,7 +1161,7 @@ extern "C" int tfr_finalize_load(tfr_engine* e) {
     }
     CU(e, cudaMalloc(&e->h, (size_t)FF * 4));
     CU(e, cudaMalloc(&e->logits, (size_t)Vl * 4));
-    CU(e, cudaMalloc(&e->partial, (size_t)P.n_head * e->attn_S * (2 + hd) * 4));
+    CU(e, cudaMalloc(&e->partial, (size_t)P.n_head * std::max(e->attn_S, e->attn_S_staged) * (2 + hd) * 4));
     CU(e, cudaMalloc(&e->counters, (size_t)P.n_kv * ATTN_CLUSTER * 4));  // one per KV head and output slice
     if (P.tp > 1) {
         e->comm.lay = tp_layout(K);
@@ -1256,12 +1267,12 @@ extern "C" int tfr_zero_recurrent(tfr_engine* e, tfr_kv* kv) {
 static cudaError_t launch_attention(cudaStream_t s, const AttnArgs& a, int hd, const TokenState* st) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(a.S, a.n_kv);
-    cfg.blockDim = dim3(ATTN_THREADS);
+    cfg.blockDim = dim3(attn_threads(a.staged != 0));
     cfg.dynamicSmemBytes = a.staged ? attn_dyn_smem(hd) : 0;
     cfg.stream = s;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = ATTN_CLUSTER;
+    attr[0].val.clusterDim.x = attn_cluster(a.staged != 0);
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -1341,9 +1352,9 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
         a.gate = nullptr;
         a.n_head = P.n_head;
         a.n_kv = P.n_kv;
-        a.S = e->attn_S;
         // short caches never reach the long-split route: launch without its shared memory (a lighter launch)
         a.staged = kv->max_seq > e->attn_S * ATTN_LONG_MIN;
+        a.S = a.staged ? e->attn_S_staged : e->attn_S;
         a.min_keys = e->attn_min_keys;
         a.scale = 1.0f / sqrtf((float)hd);  // forward.rs:389
         a.prof_id = 0;
@@ -2158,7 +2169,12 @@ extern "C" int tfr_debug_set_timeline(unsigned long long* device_buffer) {
 
 #endif  // TFR_TEST_AIDS
 
-static int check(cudaError_t r) { return r == cudaSuccess ? TFR_OK : TFR_E_CUDA; }
+// The operator entry points have no engine to keep a message in: a CUDA error is named on stderr.
+static int check(cudaError_t r) {
+    if (r == cudaSuccess) return TFR_OK;
+    fprintf(stderr, "tarafer_b200: CUDA error: %s\n", cudaGetErrorString(r));
+    return TFR_E_CUDA;
+}
 
 extern "C" int tfr_op_quantize_q8(const float* x, int n, int8_t* q8, float* d8, void* stream) {
     if (!x || !q8 || !d8 || n <= 0 || n % 32) return TFR_E_INVALID;
@@ -2283,7 +2299,8 @@ static int op_attention_impl(const float* q, const uint16_t* kc, const uint16_t*
     unsigned int*& counters = sc.counters;
     size_t& cap = sc.cap;
     AttnArgs a{};
-    a.S = attn_splits(sm_count_cached(), n_kv, head_dim);
+    a.staged = pos + 1 > attn_staged_threshold(sm_count_cached(), n_kv, head_dim);
+    a.S = attn_splits(sm_count_cached(), n_kv, head_dim, a.staged != 0);
     const size_t need = (size_t)n_head * a.S * (2 + head_dim) * 4;
     if (need > cap || !counters) {
         cudaFree(partial);
@@ -2306,7 +2323,6 @@ static int op_attention_impl(const float* q, const uint16_t* kc, const uint16_t*
     a.min_keys = 64;
     a.scale = 1.0f / sqrtf((float)head_dim);
     a.pos = pos;
-    a.staged = pos + 1 > a.S * ATTN_LONG_MIN;
     return check(launch_attention((cudaStream_t)stream, a, head_dim, nullptr));
 }
 
@@ -2394,7 +2410,8 @@ extern "C" int tfr_op_attention_noalloc(const float* q, const uint16_t* kc, cons
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return TFR_E_CUDA;
     configure_kernels_once();  // function attributes only (shared-memory carve-out): nothing is allocated
     AttnArgs a{};
-    a.S = attn_splits(sms, n_kv, head_dim);
+    a.staged = pos + 1 > attn_staged_threshold(sms, n_kv, head_dim);
+    a.S = attn_splits(sms, n_kv, head_dim, a.staged != 0);
     const size_t need = (size_t)n_head * a.S * (2 + head_dim) * sizeof(float);
     if ((size_t)n_kv * ATTN_CLUSTER * sizeof(unsigned int) > TFR_NOALLOC_COUNTER_BYTES || need > TFR_NOALLOC_SCRATCH_BYTES - TFR_NOALLOC_COUNTER_BYTES) {
         fprintf(stderr,
@@ -2425,7 +2442,6 @@ extern "C" int tfr_op_attention_noalloc(const float* q, const uint16_t* kc, cons
     a.min_keys = 64;
     a.scale = 1.0f / sqrtf((float)head_dim);
     a.pos = pos;
-    a.staged = pos + 1 > a.S * ATTN_LONG_MIN;
     return check(launch_attention(s, a, head_dim, nullptr));
 }
 
