@@ -20,8 +20,9 @@
 namespace tfr {
 
 constexpr int ATTN_THREADS = 256;         // the register-route instance
-constexpr int ATTN_THREADS_STAGED = 512;  // the staged instance: sixteen warps hide the latencies of its tile loop
-__host__ __device__ constexpr int attn_threads(bool staged) { return staged ? ATTN_THREADS_STAGED : ATTN_THREADS; }
+constexpr int ATTN_THREADS_STAGED = 512;  // the staged instance on CUDA cores (head size 256): sixteen warps hide the latencies of its tile loop
+__host__ __device__ constexpr bool attn_staged_mma(int hd) { return hd <= 128; }  // staged route on the tensor cores
+__host__ __device__ constexpr int attn_threads(bool staged, int hd) { return staged && !attn_staged_mma(hd) ? ATTN_THREADS_STAGED : ATTN_THREADS; }
 constexpr int ATTN_TILE = 64;     // keys per tile
 constexpr int ATTN_REP_MAX = 8;   // query heads per KV head handled by one CTA
 constexpr int ATTN_CLUSTER = 8;   // CTAs per cluster (the portable maximum); AttnArgs::S is a multiple of it
@@ -30,12 +31,12 @@ constexpr int ATTN_CLUSTER = 8;   // CTAs per cluster (the portable maximum); At
 constexpr int ATTN_CLUSTER_STAGED = 4;
 __host__ __device__ constexpr int attn_cluster(bool staged) { return staged ? ATTN_CLUSTER_STAGED : ATTN_CLUSTER; }
 constexpr int ATTN_LONG_MIN = 128;  // a split with more keys than this walks them through shared-memory stages
-// Dynamic shared memory of k_attn_decode: a few stages of one K tile (rows padded by 8 halfs: 16-byte reads of 32
-// different rows hit 32 different banks) and one V tile each, then q of the group's heads in fp32.  One tile in
+// Dynamic shared memory of k_attn_decode: a few stages of one K tile and one V tile each (rows padded by 8 halfs: 16-byte
+// reads of different rows hit different banks, for plain reads and for ldmatrix), then q of the group's heads in fp32.  One tile in
 // flight per SM is far too little to cover the memory latency (measured: 4 us per 32 KB tile with two stages), so a
 // split keeps as many tiles in flight as shared memory holds.
 __host__ __device__ constexpr int attn_stages(int hd) { return hd == 256 ? 2 : 5; }
-inline size_t attn_stage_bytes(int hd) { return (size_t)ATTN_TILE * (hd + 8) * 2 + (size_t)ATTN_TILE * hd * 2; }
+inline size_t attn_stage_bytes(int hd) { return 2 * (size_t)ATTN_TILE * (hd + 8) * 2; }
 inline size_t attn_dyn_smem(int hd) { return attn_stages(hd) * attn_stage_bytes(hd) + (size_t)ATTN_REP_MAX * hd * 4; }
 
 __device__ __forceinline__ void cluster_sync_all() {
@@ -63,6 +64,34 @@ struct AttnArgs {
     int prof_id;                // timeline probe: which launch of the token this is (test aid)
 };
 
+// Warp-level matrix instructions of the staged route (f16 operands, fp32 accumulators).
+__device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4_trans(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
+}
+// Transposes an 8x8 matrix of 16-bit values held one row pair per lane (lane 4 r + c holds row r, columns 2 c, 2 c + 1).
+__device__ __forceinline__ unsigned movm_trans(unsigned a) {
+    unsigned d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// x, y -> (f16(x), f16(y)) packed, low half first, and the f16 images of what the rounding dropped: an fp32 value
+// travels through the f16 tensor-core path as hi + lo with about 22 bits kept.
+__device__ __forceinline__ void split_f16x2(float x, float y, unsigned& hi, unsigned& lo) {
+    const __half hx = __float2half_rn(x), hy = __float2half_rn(y);
+    const __half2 h = __halves2half2(hx, hy);
+    const __half2 l = __halves2half2(__float2half_rn(x - __half2float(hx)), __float2half_rn(y - __half2float(hy)));
+    hi = *reinterpret_cast<const unsigned*>(&h);
+    lo = *reinterpret_cast<const unsigned*>(&l);
+}
+
 // After the five butterfly steps lane L holds the sum over all lanes of v[L].
 __device__ __forceinline__ float warp_transpose_reduce32(float (&v)[32], int lane) {
 #pragma unroll
@@ -81,8 +110,8 @@ __device__ __forceinline__ float warp_transpose_reduce32(float (&v)[32], int lan
 // STAGED = true compiles in the long-split route (and needs attn_dyn_smem(HD) of dynamic shared memory at launch);
 // the STAGED = false instance is the register route alone, with the registers that route needs and no more.
 template <int HD, bool STAGED = false>
-__global__ void __launch_bounds__(attn_threads(STAGED)) k_attn_decode(AttnArgs a, const TokenState* st) {
-    constexpr int NT = attn_threads(STAGED);
+__global__ void __launch_bounds__(attn_threads(STAGED, HD)) k_attn_decode(AttnArgs a, const TokenState* st) {
+    constexpr int NT = attn_threads(STAGED, HD);
     prof_mark(0, a.prof_id);
     constexpr int DL = HD / 32;   // dims per lane in the score phase
     constexpr int DPT = HD / 64;  // dims per thread in the value phase
@@ -156,7 +185,7 @@ __global__ void __launch_bounds__(attn_threads(STAGED)) k_attn_decode(AttnArgs a
     extern __shared__ __align__(16) unsigned char attn_dyn[];
     constexpr int KROW = HD + 8, CPR = HD / 8;  // halfs per staged K row; 16-byte chunks per cache row
     constexpr int NST = attn_stages(HD);
-    constexpr size_t stage_b = (size_t)ATTN_TILE * KROW * 2 + (size_t)ATTN_TILE * HD * 2;
+    constexpr size_t stage_b = 2 * (size_t)ATTN_TILE * KROW * 2;
     auto k_stage = [&](int st_) { return reinterpret_cast<unsigned short*>(attn_dyn + (size_t)st_ * stage_b); };
     auto v_stage = [&](int st_) { return reinterpret_cast<unsigned short*>(attn_dyn + (size_t)st_ * stage_b + (size_t)ATTN_TILE * KROW * 2); };
     auto issue_tile = [&](int tt, int st_, int skip_row) {
@@ -169,7 +198,7 @@ __global__ void __launch_bounds__(attn_threads(STAGED)) k_attn_decode(AttnArgs a
                 if (tt + row == skip_row) continue;
                 const size_t off = (size_t)(in ? tt + row : t1 - 1) * kvdim + (size_t)g * HD + c8 * 8;
                 cp_async16(ks + row * KROW + c8 * 8, a.kc + off, in ? 16 : 0);
-                cp_async16(vs + row * HD + c8 * 8, a.vc + off, in ? 16 : 0);
+                cp_async16(vs + row * KROW + c8 * 8, a.vc + off, in ? 16 : 0);
             }
         cp_async_commit();  // a group per tile slot, empty past the end: the wait in the tile loop counts groups
     };
@@ -338,8 +367,158 @@ __global__ void __launch_bounds__(attn_threads(STAGED)) k_attn_decode(AttnArgs a
 #pragma unroll
             for (int d = 0; d < DPT; d++) ored[kg][h][dp * DPT + d] = o[h][d];
     };
-    if constexpr (STAGED) {
-        // ---- the staged route: K and V tiles travel global -> shared memory as asynchronous 16-byte copies, NST stages
+    if constexpr (STAGED && attn_staged_mma(HD)) {
+        // ---- the staged route on the tensor cores (head sizes up to 128).  K and V tiles travel global -> shared
+        // memory as asynchronous 16-byte copies, five stages deep (the first four requested before the dependency
+        // wait).  A warp owns 16 keys of a tile: scores S[16 keys x 8 heads] = K[16 x HD] Q^T as HD / 16 m16n8k16 MMAs,
+        // online softmax on the accumulator fragment (a lane holds two keys x two heads; the maxima meet by three
+        // shuffles), the weights transposed in registers (movmatrix) into the B operand of O^T[HD x 8 heads] +=
+        // V^T[HD x 16 keys] P, whose A operand ldmatrix.trans reads straight from the V rows.  K and V are f16
+        // already; q and the weights are fp32 and go through as hi + lo halves (two MMAs each), the products are
+        // exact and the sums fp32.  Every warp keeps its own running (m, l, O); the eight meet once, after the loop.
+        // A step takes two tiles (warps 0-3 the first, 4-7 the second) and costs one barrier.
+        static_assert(attn_stages(HD) == 5, "the issue schedule below is written for five stages");
+        {
+            // row T - 1, written by the previous kernel, if it lies in one of the tiles requested before the wait
+            const int row = T - 1 - t0;
+            if (T - 1 < t1 && row < (NST - 1) * ATTN_TILE && tid < 2 * CPR) {
+                const int st_ = row / ATTN_TILE, r = row % ATTN_TILE, c8 = tid % CPR;
+                const size_t off = (size_t)(T - 1) * kvdim + (size_t)g * HD + c8 * 8;
+                if (tid < CPR) *reinterpret_cast<int4*>(k_stage(st_) + r * KROW + c8 * 8) = *reinterpret_cast<const int4*>(a.kc + off);
+                else *reinterpret_cast<int4*>(v_stage(st_) + r * KROW + c8 * 8) = *reinterpret_cast<const int4*>(a.vc + off);
+            }
+        }
+        constexpr int KS = HD / 16;  // 16-dim steps of the score product = 16-dim blocks of the value product
+        const int gq = lane >> 2, tq = lane & 3;
+        // B fragments of Q^T (k = dims, n = heads): lane (gq, tq) holds q[head gq][dims 16 ks + 2 tq, + 1] and [+ 8, + 9]
+        unsigned qh[KS][2], ql[KS][2];
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++)
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                float2 qv = make_float2(0.f, 0.f);
+                if (gq < rep) qv = *reinterpret_cast<const float2*>(a.q + (size_t)(g * rep + gq) * HD + 16 * ks + 2 * tq + 8 * j);
+                split_f16x2(qv.x, qv.y, qh[ks][j], ql[ks][j]);
+            }
+        float oacc[KS][4];  // O^T fragments: [0], [1] = dim 16 mb + gq, heads 2 tq, 2 tq + 1; [2], [3] = dim 16 mb + gq + 8
+#pragma unroll
+        for (int mb = 0; mb < KS; mb++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) oacc[mb][i] = 0.f;
+        float m_run[2] = {-1e30f, -1e30f}, l_run[2] = {0.f, 0.f};  // heads 2 tq, 2 tq + 1 (l: this lane's keys only)
+        const int n_tiles = (t1 - t0 + ATTN_TILE - 1) / ATTN_TILE, n_steps = (n_tiles + 1) >> 1;
+        const int kb = warp & 3;
+        // lane addresses of the ldmatrix reads inside a 16-key block (matrix mi = lane / 8, row lane % 8)
+        const int mi = lane >> 3, mr = lane & 7;
+        const int k_off = ((mi & 1) * 8 + mr) * KROW + (mi >> 1) * 8;  // K: keys 0-7 / 8-15 by mi & 1, dims + 0 / + 8 by mi >> 1
+        const int v_off = ((mi >> 1) * 8 + mr) * KROW + (mi & 1) * 8;  // V: dims + 0 / + 8 by mi & 1, keys 0-7 / 8-15 by mi >> 1
+        for (int j = 0; j < n_steps; j++) {
+            // tiles 2 j and 2 j + 1 must have landed: four tiles were requested before the loop, one in step 0 and two
+            // in every later step, one copy group per tile in order
+            if (j == 0) cp_async_wait_group<2>();
+            else cp_async_wait_group<1>();
+            __syncthreads();  // everybody's pieces, and everybody is done with the tiles of step j - 1
+            if (j == 0) {
+                issue_tile(t0 + 4 * ATTN_TILE, 4, -1);
+            } else {
+                issue_tile(t0 + (2 * j + 3) * ATTN_TILE, (2 * j + 3) % NST, -1);
+                issue_tile(t0 + (2 * j + 4) * ATTN_TILE, (2 * j + 4) % NST, -1);
+            }
+            if (j == 0) prof_mark(6, a.prof_id);
+            const int ti = 2 * j + (warp >> 2), key0 = t0 + ti * ATTN_TILE + kb * 16;
+            if (key0 < t1) {  // the same for the whole warp
+                const int stg = ti % NST;
+                float sacc[4] = {0.f, 0.f, 0.f, 0.f};  // S[key gq][heads 2 tq, 2 tq + 1], S[key gq + 8][the same heads]
+                {
+                    const unsigned kaddr = smem_u32(k_stage(stg) + kb * 16 * KROW + k_off);
+#pragma unroll
+                    for (int ks = 0; ks < KS; ks++) {
+                        unsigned af[4];
+                        ldsm_x4(af, kaddr + ks * 32);
+                        mma_16816(sacc, af, ql[ks][0], ql[ks][1]);
+                        mma_16816(sacc, af, qh[ks][0], qh[ks][1]);
+                    }
+                }
+                const bool on_a = key0 + gq < t1, on_b = key0 + gq + 8 < t1;
+                float pw[4], al[2];
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    const float sa = on_a ? sacc[c] * a.scale : -1e30f, sb = on_b ? sacc[2 + c] * a.scale : -1e30f;
+                    float mx = fmaxf(sa, sb);
+#pragma unroll
+                    for (int off = 4; off <= 16; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(TFR_FULL_MASK, mx, off));
+                    const float mn = fmaxf(m_run[c], mx);
+                    al[c] = expf(m_run[c] - mn);
+                    pw[c] = on_a ? expf(sa - mn) : 0.f;
+                    pw[2 + c] = on_b ? expf(sb - mn) : 0.f;
+                    l_run[c] = l_run[c] * al[c] + pw[c] + pw[2 + c];
+                    m_run[c] = mn;
+                }
+                if (__any_sync(TFR_FULL_MASK, al[0] != 1.f || al[1] != 1.f)) {
+#pragma unroll
+                    for (int mb = 0; mb < KS; mb++) {
+                        oacc[mb][0] *= al[0], oacc[mb][1] *= al[1];
+                        oacc[mb][2] *= al[0], oacc[mb][3] *= al[1];
+                    }
+                }
+                // weights as B operand (k = keys, n = heads): transpose the [key][head pair] fragments
+                unsigned ph_a, pl_a, ph_b, pl_b;
+                split_f16x2(pw[0], pw[1], ph_a, pl_a);
+                split_f16x2(pw[2], pw[3], ph_b, pl_b);
+                const unsigned b0h = movm_trans(ph_a), b1h = movm_trans(ph_b), b0l = movm_trans(pl_a), b1l = movm_trans(pl_b);
+                const unsigned vaddr = smem_u32(v_stage(stg) + kb * 16 * KROW + v_off);
+#pragma unroll
+                for (int mb = 0; mb < KS; mb++) {
+                    unsigned vf[4];
+                    ldsm_x4_trans(vf, vaddr + mb * 32);
+                    mma_16816(oacc[mb], vf, b0l, b1l);
+                    mma_16816(oacc[mb], vf, b0h, b1h);
+                }
+            }
+            if (j == 0) prof_mark(7, a.prof_id);
+        }
+        // ---- the eight warps' (m, l, O) meet in shared memory (over the tile stages, which nobody reads any more)
+#pragma unroll
+        for (int c = 0; c < 2; c++)
+#pragma unroll
+            for (int off = 4; off <= 16; off <<= 1) l_run[c] += __shfl_xor_sync(TFR_FULL_MASK, l_run[c], off);
+        cp_async_wait_all();
+        __syncthreads();
+        float* wO = reinterpret_cast<float*>(attn_dyn);                 // [warp][head][HD]
+        float* wm = wO + (NT / 32) * ATTN_REP_MAX * HD;                 // [warp][head]
+        float* wl = wm + (NT / 32) * ATTN_REP_MAX;
+        if (gq == 0) {
+            wm[warp * ATTN_REP_MAX + 2 * tq] = m_run[0], wm[warp * ATTN_REP_MAX + 2 * tq + 1] = m_run[1];
+            wl[warp * ATTN_REP_MAX + 2 * tq] = l_run[0], wl[warp * ATTN_REP_MAX + 2 * tq + 1] = l_run[1];
+        }
+#pragma unroll
+        for (int mb = 0; mb < KS; mb++) {
+            float* o0 = wO + ((size_t)warp * ATTN_REP_MAX + 2 * tq) * HD + 16 * mb + gq;
+            o0[0] = oacc[mb][0], o0[HD] = oacc[mb][1], o0[8] = oacc[mb][2], o0[HD + 8] = oacc[mb][3];
+        }
+        __syncthreads();
+        for (int idx = tid; idx < ATTN_REP_MAX * HD; idx += NT) {
+            const int h = idx / HD, d = idx % HD;
+            float m = -1e30f;
+#pragma unroll
+            for (int w = 0; w < NT / 32; w++) m = fmaxf(m, wm[w * ATTN_REP_MAX + h]);
+            float acc = 0.f;
+#pragma unroll
+            for (int w = 0; w < NT / 32; w++) acc += expf(wm[w * ATTN_REP_MAX + h] - m) * wO[((size_t)w * ATTN_REP_MAX + h) * HD + d];
+            ored[0][h][d] = acc;
+            ored[1][h][d] = 0.f, ored[2][h][d] = 0.f, ored[3][h][d] = 0.f;
+        }
+        if (tid < ATTN_REP_MAX) {
+            float m = -1e30f, l = 0.f;
+#pragma unroll
+            for (int w = 0; w < NT / 32; w++) m = fmaxf(m, wm[w * ATTN_REP_MAX + tid]);
+#pragma unroll
+            for (int w = 0; w < NT / 32; w++) l += expf(wm[w * ATTN_REP_MAX + tid] - m) * wl[w * ATTN_REP_MAX + tid];
+            m_s[tid] = m;
+            l_s[tid] = l;
+        }
+    } else if constexpr (STAGED) {
+        // ---- the staged route on CUDA cores (head size 256): K and V tiles travel global -> shared memory as asynchronous 16-byte copies, NST stages
         // deep (the first ones requested before the dependency wait), so the loads of the next tiles run under the
         // arithmetic of tile i and no register holds cache data.  Sixteen warps.
         float* q_s = reinterpret_cast<float*>(attn_dyn + NST * stage_b);
@@ -350,7 +529,7 @@ __global__ void __launch_bounds__(attn_threads(STAGED)) k_attn_decode(AttnArgs a
                 const int st_ = row / ATTN_TILE, r = row % ATTN_TILE, c8 = tid % CPR;
                 const size_t off = (size_t)(T - 1) * kvdim + (size_t)g * HD + c8 * 8;
                 if (tid < CPR) *reinterpret_cast<int4*>(k_stage(st_) + r * KROW + c8 * 8) = *reinterpret_cast<const int4*>(a.kc + off);
-                else *reinterpret_cast<int4*>(v_stage(st_) + r * HD + c8 * 8) = *reinterpret_cast<const int4*>(a.vc + off);
+                else *reinterpret_cast<int4*>(v_stage(st_) + r * KROW + c8 * 8) = *reinterpret_cast<const int4*>(a.vc + off);
             }
         }
         // Both phases are register-blocked so that shared-memory reads stay well below the FMA count (a 16-byte read
@@ -517,7 +696,7 @@ __global__ void __launch_bounds__(attn_threads(STAGED)) k_attn_decode(AttnArgs a
             for (int k = vkw * KPI + vkl; k < tn; k += KW * KPI) {
                 const float4 pa = *reinterpret_cast<const float4*>(&sc[k][vhh * HH]);
                 const float p[HH] = {pa.x, pa.y, pa.z, pa.w};
-                const uint4 raw = *reinterpret_cast<const uint4*>(vs + k * HD + vdl * DV);
+                const uint4 raw = *reinterpret_cast<const uint4*>(vs + k * KROW + vdl * DV);
                 const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x)), v1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
                 const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&raw.z)), v3 = __half22float2(*reinterpret_cast<const __half2*>(&raw.w));
                 const float vf[DV] = {v0.x, v0.y, v1.x, v1.y, v2.x, v2.y, v3.x, v3.y};
@@ -633,28 +812,32 @@ __global__ void __launch_bounds__(attn_threads(STAGED)) k_attn_decode(AttnArgs a
             }
         }
     }
-    __threadfence();
+    // release: the CTA's stores are ordered before thread 0's fence by the barrier, and the fence is cumulative
     __syncthreads();
     if (tid == 0) {
+        __threadfence();
         unsigned int* ctr = a.counters + g * ATTN_CLUSTER + rk;
         const unsigned int old = atomicAdd(ctr, 1u);
         is_last_s = (old == (unsigned int)(n_cl - 1));
-        if (is_last_s) *ctr = 0u;
+        if (is_last_s) {
+            *ctr = 0u;
+            __threadfence();  // acquire side: the other clusters' partials, read below with L2 loads
+        }
     }
     __syncthreads();
     if (!is_last_s) return;
-    __threadfence();
     for (int i = tid; i < per; i += NT) {
         const int idx = rk * per + i;
         const int h = idx / HD, d = idx % HD;
         const int hg = g * rep + h;
         const float* hb = a.partial + (size_t)hg * a.S * po;
-        // eight cluster partials per round, all of a round's loads in flight together (one trip to L2 per round)
+        // RC cluster partials per round, all of a round's loads in flight together (one trip to L2 per round)
+        constexpr int RC = STAGED ? 16 : 8;
         float m = -1e30f, l = 0.f, acc = 0.f;
-        for (int c0 = 0; c0 < n_cl; c0 += 8) {
-            float mm[8], ll[8], aa[8];
+        for (int c0 = 0; c0 < n_cl; c0 += RC) {
+            float mm[RC], ll[RC], aa[RC];
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
+            for (int j = 0; j < RC; j++) {
                 const bool on = c0 + j < n_cl;
                 const float* b = hb + (size_t)(on ? c0 + j : c0) * po;
                 mm[j] = on ? __ldcg(b) : -1e30f;
@@ -663,13 +846,13 @@ __global__ void __launch_bounds__(attn_threads(STAGED)) k_attn_decode(AttnArgs a
             }
             float m_new = m;
 #pragma unroll
-            for (int j = 0; j < 8; j++) m_new = fmaxf(m_new, mm[j]);
+            for (int j = 0; j < RC; j++) m_new = fmaxf(m_new, mm[j]);
             const float keep = expf(m - m_new);
             l *= keep;
             acc *= keep;
             m = m_new;
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
+            for (int j = 0; j < RC; j++) {
                 const float al = expf(mm[j] - m);
                 l += al * ll[j];
                 acc += al * aa[j];

@@ -323,7 +323,7 @@ static int attn_max_clusters(int hd, bool staged) {
     const int cl = attn_cluster(staged);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(cl * 64, 1);
-    cfg.blockDim = dim3(attn_threads(staged));
+    cfg.blockDim = dim3(attn_threads(staged, hd));
     cfg.dynamicSmemBytes = staged ? attn_dyn_smem(hd) : 0;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1267,7 +1267,7 @@ extern "C" int tfr_zero_recurrent(tfr_engine* e, tfr_kv* kv) {
 static cudaError_t launch_attention(cudaStream_t s, const AttnArgs& a, int hd, const TokenState* st) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(a.S, a.n_kv);
-    cfg.blockDim = dim3(attn_threads(a.staged != 0));
+    cfg.blockDim = dim3(attn_threads(a.staged != 0, hd));
     cfg.dynamicSmemBytes = a.staged ? attn_dyn_smem(hd) : 0;
     cfg.stream = s;
     cudaLaunchAttribute attr[2];
