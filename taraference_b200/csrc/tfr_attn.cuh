@@ -492,45 +492,68 @@ __global__ void __launch_bounds__(attn_threads(STAGED, HD)) k_attn_decode(AttnAr
             }
             if (j == 0) prof_mark(7, a.prof_id);
         }
-        // ---- the eight warps' (m, l, O) meet in shared memory (over the tile stages, which nobody reads any more)
+        // ---- the eight warps' (m, l, O) meet in shared memory (over the tile stages, which nobody reads any more).
+        // A warp that had no keys leaves only its (m, l) = (-1e30, 0) and is skipped by the readers.
 #pragma unroll
         for (int c = 0; c < 2; c++)
 #pragma unroll
             for (int off = 4; off <= 16; off <<= 1) l_run[c] += __shfl_xor_sync(TFR_FULL_MASK, l_run[c], off);
         cp_async_wait_all();
         __syncthreads();
-        float* wO = reinterpret_cast<float*>(attn_dyn);                 // [warp][head][HD]
-        float* wm = wO + (NT / 32) * ATTN_REP_MAX * HD;                 // [warp][head]
+        constexpr int WOS = HD + 4;                                     // floats per head in wO: the four head pairs of a store hit different banks
+        float* wO = reinterpret_cast<float*>(attn_dyn);                 // [warp][head][WOS]
+        float* wm = wO + (NT / 32) * ATTN_REP_MAX * WOS;                // [warp][head]
         float* wl = wm + (NT / 32) * ATTN_REP_MAX;
         if (gq == 0) {
             wm[warp * ATTN_REP_MAX + 2 * tq] = m_run[0], wm[warp * ATTN_REP_MAX + 2 * tq + 1] = m_run[1];
             wl[warp * ATTN_REP_MAX + 2 * tq] = l_run[0], wl[warp * ATTN_REP_MAX + 2 * tq + 1] = l_run[1];
         }
+        const bool had_keys = t0 + (warp >> 2) * ATTN_TILE + kb * 16 < t1;  // the warp's first block exists
+        if (had_keys) {
 #pragma unroll
-        for (int mb = 0; mb < KS; mb++) {
-            float* o0 = wO + ((size_t)warp * ATTN_REP_MAX + 2 * tq) * HD + 16 * mb + gq;
-            o0[0] = oacc[mb][0], o0[HD] = oacc[mb][1], o0[8] = oacc[mb][2], o0[HD + 8] = oacc[mb][3];
+            for (int mb = 0; mb < KS; mb++) {
+                float* o0 = wO + ((size_t)warp * ATTN_REP_MAX + 2 * tq) * WOS + 16 * mb + gq;
+                o0[0] = oacc[mb][0], o0[WOS] = oacc[mb][1], o0[8] = oacc[mb][2], o0[WOS + 8] = oacc[mb][3];
+            }
         }
         __syncthreads();
-        for (int idx = tid; idx < ATTN_REP_MAX * HD; idx += NT) {
-            const int h = idx / HD, d = idx % HD;
-            float m = -1e30f;
+        {
+            // warp h folds head h: a lane takes HD / 32 adjacent dims, the weights exp(m_w - m) once per thread
+            constexpr int DPL = HD / 32;
+            const int h = warp;
+            float mw[NT / 32], m = -1e30f;
 #pragma unroll
-            for (int w = 0; w < NT / 32; w++) m = fmaxf(m, wm[w * ATTN_REP_MAX + h]);
-            float acc = 0.f;
+            for (int w = 0; w < NT / 32; w++) {
+                mw[w] = wm[w * ATTN_REP_MAX + h];
+                m = fmaxf(m, mw[w]);
+            }
+            float acc[DPL], l = 0.f;
 #pragma unroll
-            for (int w = 0; w < NT / 32; w++) acc += expf(wm[w * ATTN_REP_MAX + h] - m) * wO[((size_t)w * ATTN_REP_MAX + h) * HD + d];
-            ored[0][h][d] = acc;
-            ored[1][h][d] = 0.f, ored[2][h][d] = 0.f, ored[3][h][d] = 0.f;
-        }
-        if (tid < ATTN_REP_MAX) {
-            float m = -1e30f, l = 0.f;
+            for (int d = 0; d < DPL; d++) acc[d] = 0.f;
 #pragma unroll
-            for (int w = 0; w < NT / 32; w++) m = fmaxf(m, wm[w * ATTN_REP_MAX + tid]);
+            for (int w = 0; w < NT / 32; w++) {
+                if (mw[w] > -1e29f) {  // the same for the whole warp
+                    const float wgt = expf(mw[w] - m);
+                    l += wgt * wl[w * ATTN_REP_MAX + h];
+                    const float* src = wO + ((size_t)w * ATTN_REP_MAX + h) * WOS + lane * DPL;
+                    if constexpr (DPL == 4) {
+                        const float4 v = *reinterpret_cast<const float4*>(src);
+                        acc[0] += wgt * v.x, acc[1] += wgt * v.y, acc[2] += wgt * v.z, acc[3] += wgt * v.w;
+                    } else {
+                        const float2 v = *reinterpret_cast<const float2*>(src);
+                        acc[0] += wgt * v.x, acc[1] += wgt * v.y;
+                    }
+                }
+            }
 #pragma unroll
-            for (int w = 0; w < NT / 32; w++) l += expf(wm[w * ATTN_REP_MAX + tid] - m) * wl[w * ATTN_REP_MAX + tid];
-            m_s[tid] = m;
-            l_s[tid] = l;
+            for (int d = 0; d < DPL; d++) {
+                ored[0][h][lane * DPL + d] = acc[d];
+                ored[1][h][lane * DPL + d] = 0.f, ored[2][h][lane * DPL + d] = 0.f, ored[3][h][lane * DPL + d] = 0.f;
+            }
+            if (lane == 0) {
+                m_s[h] = m;
+                l_s[h] = l;
+            }
         }
     } else if constexpr (STAGED) {
         // ---- the staged route on CUDA cores (head size 256): K and V tiles travel global -> shared memory as asynchronous 16-byte copies, NST stages
