@@ -359,8 +359,21 @@ static int attn_splits(int sms, int n_kv, int hd, bool staged) {
     if (fit >= cl && fit < s) s = fit;
     return s < cl ? cl : s;
 }
-// The staged instance is launched for caches (or positions) that reach beyond this many keys.
-static int attn_staged_threshold(int sms, int n_kv, int hd) { return attn_splits(sms, n_kv, hd, false) * ATTN_LONG_MIN; }
+// Which instance a launch takes and with how much shared memory, from the head size and the largest number of keys the
+// launch can meet (the cache's capacity in the engine, pos + 1 in the operator entry points).
+// Head sizes up to 128 always take the staged instance (scores and values on the tensor cores): a step of it covers 128
+// keys, so splits are cut at 128 keys, and when no split can exceed 128 keys two tile stages replace the five.  Head
+// size 256 takes the staged instance only where a split can exceed ATTN_LONG_MIN keys.  TFR_ATTN_REGISTER_ROUTE=1 in
+// the environment keeps short caches on the register route for every head size (a test and measurement aid).
+static void attn_route(AttnArgs& a, int hd, int max_keys, int s_short, int s_staged, int min_keys_short) {
+    const bool long_cache = max_keys > s_short * ATTN_LONG_MIN;
+    const bool mma_route = attn_staged_mma(hd) && !getenv("TFR_ATTN_REGISTER_ROUTE");
+    a.staged = long_cache || mma_route;
+    a.S = a.staged ? s_staged : s_short;
+    const bool mma = a.staged && attn_staged_mma(hd);
+    a.stages = (mma && max_keys <= s_staged * 2 * ATTN_TILE) ? 2 : 0;
+    a.min_keys = mma ? 2 * ATTN_TILE : min_keys_short;
+}
 
 static int sm_count_cached() {
     static int count[TFR_MAX_DEVICES] = {};
@@ -1353,15 +1366,7 @@ static int record_token(tfr_engine* e, const tfr_kv* kv, bool with_head) {
         a.n_head = P.n_head;
         a.n_kv = P.n_kv;
         // short caches never reach the long-split route: launch without its shared memory (a lighter launch)
-        // Head sizes up to 128 always take the staged instance (scores and values on the tensor cores): a step of it
-        // covers 128 keys, so splits are cut at 128 keys and a cache that cannot reach beyond 128 keys per split gets
-        // two tile stages instead of five.  Head size 256 takes it for long caches only.
-        const bool long_cache = kv->max_seq > e->attn_S * ATTN_LONG_MIN;
-        const bool mma_route = attn_staged_mma(hd) && !getenv("TFR_ATTN_REGISTER_ROUTE");
-        a.staged = long_cache || mma_route;
-        a.S = a.staged ? e->attn_S_staged : e->attn_S;
-        a.stages = (mma_route && kv->max_seq <= e->attn_S_staged * 2 * ATTN_TILE) ? 2 : 0;
-        a.min_keys = mma_route ? 2 * ATTN_TILE : e->attn_min_keys;
+        attn_route(a, hd, kv->max_seq, e->attn_S, e->attn_S_staged, e->attn_min_keys);
         a.scale = 1.0f / sqrtf((float)hd);  // forward.rs:389
         a.prof_id = 0;
         int mix_width = P.attn_width;       // width of the vector the output projection consumes
@@ -2305,8 +2310,7 @@ static int op_attention_impl(const float* q, const uint16_t* kc, const uint16_t*
     unsigned int*& counters = sc.counters;
     size_t& cap = sc.cap;
     AttnArgs a{};
-    a.staged = pos + 1 > attn_staged_threshold(sm_count_cached(), n_kv, head_dim);
-    a.S = attn_splits(sm_count_cached(), n_kv, head_dim, a.staged != 0);
+    attn_route(a, head_dim, pos + 1, attn_splits(sm_count_cached(), n_kv, head_dim, false), attn_splits(sm_count_cached(), n_kv, head_dim, true), 64);
     const size_t need = (size_t)n_head * a.S * (2 + head_dim) * 4;
     if (need > cap || !counters) {
         cudaFree(partial);
@@ -2326,7 +2330,6 @@ static int op_attention_impl(const float* q, const uint16_t* kc, const uint16_t*
     a.n_head = n_head;
     a.n_kv = n_kv;
     a.gate = gate;
-    a.min_keys = 64;
     a.scale = 1.0f / sqrtf((float)head_dim);
     a.pos = pos;
     return check(launch_attention((cudaStream_t)stream, a, head_dim, nullptr));
@@ -2416,8 +2419,7 @@ extern "C" int tfr_op_attention_noalloc(const float* q, const uint16_t* kc, cons
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return TFR_E_CUDA;
     configure_kernels_once();  // function attributes only (shared-memory carve-out): nothing is allocated
     AttnArgs a{};
-    a.staged = pos + 1 > attn_staged_threshold(sms, n_kv, head_dim);
-    a.S = attn_splits(sms, n_kv, head_dim, a.staged != 0);
+    attn_route(a, head_dim, pos + 1, attn_splits(sms, n_kv, head_dim, false), attn_splits(sms, n_kv, head_dim, true), 64);
     const size_t need = (size_t)n_head * a.S * (2 + head_dim) * sizeof(float);
     if ((size_t)n_kv * ATTN_CLUSTER * sizeof(unsigned int) > TFR_NOALLOC_COUNTER_BYTES || need > TFR_NOALLOC_SCRATCH_BYTES - TFR_NOALLOC_COUNTER_BYTES) {
         fprintf(stderr,
@@ -2445,7 +2447,6 @@ extern "C" int tfr_op_attention_noalloc(const float* q, const uint16_t* kc, cons
     a.out = out;
     a.n_head = n_head;
     a.n_kv = n_kv;
-    a.min_keys = 64;
     a.scale = 1.0f / sqrtf((float)head_dim);
     a.pos = pos;
     return check(launch_attention(s, a, head_dim, nullptr));

@@ -246,7 +246,12 @@ def test_ffn_block_config1_shape(E, oracle, R):
                                         (16, 2, 128, 64), (16, 2, 128, 65), (16, 2, 128, 512), (16, 2, 128, 513),
                                         (16, 2, 128, 4608), (16, 2, 128, 16896), (40, 8, 128, 9000), (16, 4, 256, 2500),
                                         (6, 2, 64, 5000)])
-def test_flash_decode_vs_oracle_and_reference(E, oracle, H, Hkv, hd, T):
+@pytest.mark.parametrize("route", ["default", "register"])
+def test_flash_decode_vs_oracle_and_reference(E, oracle, H, Hkv, hd, T, route, monkeypatch):
+    # default: head sizes up to 128 run scores and values on the tensor cores at every length; "register" keeps
+    # short contexts on the CUDA-core register route (the library reads the variable at every call)
+    if route == "register":
+        monkeypatch.setenv("TFR_ATTN_REGISTER_ROUTE", "1")
     rng = np.random.default_rng(H * 1000 + T)
     q = rng.normal(0, 1, H * hd).astype(np.float32)
     kc = rng.normal(0, 1, (T + 3, Hkv * hd)).astype(np.float16).view(np.uint16)
