@@ -16,6 +16,7 @@
 // prefill arithmetic (fp32 activations against dequantised weights): a prompt fed in chunks then leaves the same
 // K/V rows and residual stream as the same prompt fed token by token, up to the summation order inside attention.
 #pragma once
+#include "tfr_attn.cuh"
 #include "tfr_kernels.cuh"
 
 namespace tfr {
@@ -543,6 +544,204 @@ __global__ void __launch_bounds__(ATTC_THREADS) k_attn_chunk(AttnChunkArgs a) {
             }
 #pragma unroll
             for (int d = 0; d < DPL; d++) dst[2 + lane * DPL + d] = o[rr][d];
+        }
+    }
+}
+
+// The same CTA shape on the tensor cores (head sizes up to 128, prompt chunks): a warp owns 16 rows — (query token,
+// query head) pairs of one KV head — and walks every key of the split, eight warps share the staged tiles.  Scores
+// S[16 rows x 64 keys] = Q K^T and O[16 rows x HD] += P V run as m16n8k16 MMAs (f16 operands, fp32 accumulators) the
+// way k_attn_decode's staged route does: K and V are f16 in the cache (exact), q and the softmax weights are fp32 and
+// travel as two f16 terms (split2_f16x2), every 16-term product sum starts from zero and joins the running sum by a
+// round-to-nearest add.  The softmax runs on the accumulator fragments (a lane holds two rows x two keys of every 8-key block), whose
+// layout is also that of the A operand of P V, so the weights never leave registers.
+constexpr int ATTM_TK = 64, ATTM_STAGES = 4, ATTM_ROWS = 128;
+inline size_t attn_chunk_mma_smem(int hd) { return (size_t)ATTM_STAGES * 2 * ATTM_TK * (hd + 8) * 2; }
+
+template <int HD>
+__global__ void __launch_bounds__(ATTC_THREADS) k_attn_chunk_mma(AttnChunkArgs a) {
+    constexpr int KROW = HD + 8, CPR = HD / 8, KS = HD / 16, NB = HD / 8, KB = ATTM_TK / 16;
+    extern __shared__ __align__(128) unsigned char attc_smem[];
+    constexpr size_t STAGE_B = 2 * (size_t)ATTM_TK * KROW * 2;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gq = lane >> 2, tq = lane & 3;
+    const int g = blockIdx.x, rep = a.n_head / a.n_kv, sp = blockIdx.z;
+    const int m_first = blockIdx.y * a.QT, qt = min(a.QT, a.M - m_first);
+    const int n_rows = qt * rep;
+    const int T = a.pos0 + m_first + qt;  // keys the tile's last token sees
+    const int n_tiles = (T + ATTM_TK - 1) / ATTM_TK, per = (n_tiles + a.S - 1) / a.S;
+    const int k0 = min(T, sp * per * ATTM_TK), k1 = min(T, (sp + 1) * per * ATTM_TK);
+    auto k_stage = [&](int st_) { return reinterpret_cast<unsigned short*>(attc_smem + (size_t)st_ * STAGE_B); };
+    auto v_stage = [&](int st_) { return k_stage(st_) + ATTM_TK * KROW; };
+    auto issue_tile = [&](int tt, int st_) {
+        unsigned short* ks = k_stage(st_);
+        unsigned short* vs = v_stage(st_);
+        if (tt < k1)
+            for (int i = tid; i < ATTM_TK * CPR; i += ATTC_THREADS) {
+                const int row = i / CPR, c8 = i - row * CPR;
+                const bool in = tt + row < k1;
+                const size_t off = (size_t)(in ? tt + row : k1 - 1) * a.kvdim + (size_t)g * HD + c8 * 8;
+                cp_async16(ks + row * KROW + c8 * 8, a.kc + off, in ? 16 : 0);  // rows past the split arrive as zeros
+                cp_async16(vs + row * KROW + c8 * 8, a.vc + off, in ? 16 : 0);
+            }
+        cp_async_commit();
+    };
+    griddep_wait();
+    griddep_launch_dependents();
+#pragma unroll
+    for (int p = 0; p < ATTM_STAGES - 1; p++) issue_tile(k0 + p * ATTM_TK, p);
+    // rows gq and gq + 8 of this warp's 16; a row past the tile's last one repeats row 0 and is never written back
+    const int r_a = warp * 16 + gq, r_b = r_a + 8;
+    const bool row_a = r_a < n_rows, row_b = r_b < n_rows, warp_on = warp * 16 < n_rows;
+    const int ra = row_a ? r_a : 0, rb = row_b ? r_b : 0;
+    const int last_a = a.pos0 + m_first + ra / rep, last_b = a.pos0 + m_first + rb / rep;  // causal limits
+    // the warp's rows are in token order: its last valid row sees the most keys
+    const int last_w = a.pos0 + m_first + (min(n_rows, warp * 16 + 16) - 1) / rep;
+    // A fragments of Q (16 rows x 16 dims per step): [0] row gq dims 2 tq, + 1; [1] row gq + 8; [2], [3] the same, dims + 8
+    unsigned qh[KS][4], ql[KS][4];
+    {
+        const float* qa = a.q + (size_t)(m_first + ra / rep) * a.ldq + (size_t)(g * rep + ra % rep) * HD;
+        const float* qb = a.q + (size_t)(m_first + rb / rep) * a.ldq + (size_t)(g * rep + rb % rep) * HD;
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++)
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const float2 va = warp_on ? *reinterpret_cast<const float2*>(qa + 16 * ks + 2 * tq + 8 * j) : make_float2(0.f, 0.f);
+                const float2 vb = warp_on ? *reinterpret_cast<const float2*>(qb + 16 * ks + 2 * tq + 8 * j) : make_float2(0.f, 0.f);
+                split2_f16x2(va.x, va.y, qh[ks][2 * j], ql[ks][2 * j]);
+                split2_f16x2(vb.x, vb.y, qh[ks][2 * j + 1], ql[ks][2 * j + 1]);
+            }
+    }
+    float oacc[NB][4];  // [0], [1] = row gq, dims 8 nb + 2 tq, + 1; [2], [3] = row gq + 8
+#pragma unroll
+    for (int nb = 0; nb < NB; nb++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) oacc[nb][i] = 0.f;
+    float m_run[2] = {-1e30f, -1e30f}, l_run[2] = {0.f, 0.f};  // rows gq, gq + 8 (l: this lane's keys only)
+    // lane addresses of the ldmatrix reads inside a 16-key block (matrix mi = lane / 8, row lane % 8)
+    const int mi = lane >> 3, mr = lane & 7;
+    const int k_off = ((mi >> 1) * 8 + mr) * KROW + (mi & 1) * 8;  // K as B operand: dims + 0 / + 8 by mi & 1, keys 0-7 / 8-15 by mi >> 1
+    const int v_off = ((mi & 1) * 8 + mr) * KROW + (mi >> 1) * 8;  // V as B operand (transposed read): keys by mi & 1, dims + 0 / + 8 by mi >> 1
+    int it = 0;
+    for (int tt = k0; tt < k1; tt += ATTM_TK, it++) {
+        cp_async_wait_group<ATTM_STAGES - 2>();  // this thread's pieces of tile `it`
+        __syncthreads();                         // everybody's pieces, and everybody is done with tile it - 1
+        issue_tile(tt + (ATTM_STAGES - 1) * ATTM_TK, (it + ATTM_STAGES - 1) % ATTM_STAGES);
+        if (!warp_on || tt > last_w) continue;  // the same for the whole warp; barriers are outside
+        const int stg = it % ATTM_STAGES;
+        // ---- scores of the 64 keys: eight 8-key blocks, fragments [0], [1] = row gq keys 2 tq, + 1; [2], [3] = row gq + 8
+        float sacc[2 * KB][4];
+#pragma unroll
+        for (int nb = 0; nb < 2 * KB; nb++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) sacc[nb][i] = 0.f;
+#pragma unroll
+        for (int kb = 0; kb < KB; kb++) {
+            const unsigned kaddr = smem_u32(k_stage(stg) + kb * 16 * KROW + k_off);
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++) {
+                unsigned bf[4];  // [0], [1]: keys 0-7 of the block, dims + 0 / + 8; [2], [3]: keys 8-15
+                ldsm_x4(bf, kaddr + ks * 32);
+                float p0[4] = {0.f, 0.f, 0.f, 0.f}, p1[4] = {0.f, 0.f, 0.f, 0.f}, l0[4] = {0.f, 0.f, 0.f, 0.f}, l1[4] = {0.f, 0.f, 0.f, 0.f};
+                mma_16816(p0, qh[ks], bf[0], bf[1]);
+                mma_16816(l0, ql[ks], bf[0], bf[1]);
+                mma_16816(p1, qh[ks], bf[2], bf[3]);
+                mma_16816(l1, ql[ks], bf[2], bf[3]);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    sacc[2 * kb][i] += p0[i] + l0[i] * SPLIT_DOWN;
+                    sacc[2 * kb + 1][i] += p1[i] + l1[i] * SPLIT_DOWN;
+                }
+            }
+        }
+        // ---- online softmax on the fragments
+        float mx_a = -1e30f, mx_b = -1e30f;
+#pragma unroll
+        for (int nb = 0; nb < 2 * KB; nb++)
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                const int key = tt + nb * 8 + 2 * tq + c;
+                const bool in = key < k1;
+                sacc[nb][c] = (in && key <= last_a) ? sacc[nb][c] * a.scale : -1e30f;
+                sacc[nb][2 + c] = (in && key <= last_b) ? sacc[nb][2 + c] * a.scale : -1e30f;
+                mx_a = fmaxf(mx_a, sacc[nb][c]);
+                mx_b = fmaxf(mx_b, sacc[nb][2 + c]);
+            }
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(TFR_FULL_MASK, mx_a, 1)), mx_a = fmaxf(mx_a, __shfl_xor_sync(TFR_FULL_MASK, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(TFR_FULL_MASK, mx_b, 1)), mx_b = fmaxf(mx_b, __shfl_xor_sync(TFR_FULL_MASK, mx_b, 2));
+        const float mn_a = fmaxf(m_run[0], mx_a), mn_b = fmaxf(m_run[1], mx_b);
+        const float al_a = expf(m_run[0] - mn_a), al_b = expf(m_run[1] - mn_b);
+        m_run[0] = mn_a, m_run[1] = mn_b;
+        float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+        for (int nb = 0; nb < 2 * KB; nb++)
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                // a masked score is -1e30: its weight must be zero even while the row's maximum is still -1e30
+                const float pa = sacc[nb][c] > -1e29f ? expf(sacc[nb][c] - mn_a) : 0.f;
+                const float pb = sacc[nb][2 + c] > -1e29f ? expf(sacc[nb][2 + c] - mn_b) : 0.f;
+                sacc[nb][c] = pa, sacc[nb][2 + c] = pb;
+                sum_a += pa, sum_b += pb;
+            }
+        l_run[0] = l_run[0] * al_a + sum_a;
+        l_run[1] = l_run[1] * al_b + sum_b;
+        if (__any_sync(TFR_FULL_MASK, al_a != 1.f || al_b != 1.f)) {
+#pragma unroll
+            for (int nb = 0; nb < NB; nb++) {
+                oacc[nb][0] *= al_a, oacc[nb][1] *= al_a;
+                oacc[nb][2] *= al_b, oacc[nb][3] *= al_b;
+            }
+        }
+        // ---- O += P V: the score fragments of two adjacent 8-key blocks are the A fragment of a 16-key step
+#pragma unroll
+        for (int kb = 0; kb < KB; kb++) {
+            unsigned ph[4], pl[4];
+            split2_f16x2(sacc[2 * kb][0], sacc[2 * kb][1], ph[0], pl[0]);
+            split2_f16x2(sacc[2 * kb][2], sacc[2 * kb][3], ph[1], pl[1]);
+            split2_f16x2(sacc[2 * kb + 1][0], sacc[2 * kb + 1][1], ph[2], pl[2]);
+            split2_f16x2(sacc[2 * kb + 1][2], sacc[2 * kb + 1][3], ph[3], pl[3]);
+            const unsigned vaddr = smem_u32(v_stage(stg) + kb * 16 * KROW + v_off);
+#pragma unroll
+            for (int nb = 0; nb < NB; nb += 2) {
+                unsigned bf[4];  // [0], [1]: dims 8 nb .. + 7, keys 0-7 / 8-15; [2], [3]: dims 8 (nb + 1) ..
+                ldsm_x4_trans(bf, vaddr + nb * 16);
+                float p0[4] = {0.f, 0.f, 0.f, 0.f}, p1[4] = {0.f, 0.f, 0.f, 0.f}, l0[4] = {0.f, 0.f, 0.f, 0.f}, l1[4] = {0.f, 0.f, 0.f, 0.f};
+                mma_16816(p0, ph, bf[0], bf[1]);
+                mma_16816(l0, pl, bf[0], bf[1]);
+                mma_16816(p1, ph, bf[2], bf[3]);
+                mma_16816(l1, pl, bf[2], bf[3]);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    oacc[nb][i] += p0[i] + l0[i] * SPLIT_DOWN;
+                    oacc[nb + 1][i] += p1[i] + l1[i] * SPLIT_DOWN;
+                }
+            }
+        }
+    }
+    cp_async_wait_all();
+    if (!warp_on) return;
+#pragma unroll
+    for (int c = 0; c < 2; c++) {
+        l_run[c] += __shfl_xor_sync(TFR_FULL_MASK, l_run[c], 1);
+        l_run[c] += __shfl_xor_sync(TFR_FULL_MASK, l_run[c], 2);
+    }
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+        if (!(half ? row_b : row_a)) continue;
+        const int r = half ? r_b : r_a;
+        const int m = m_first + r / rep, h = g * rep + r % rep;
+        if (a.S == 1) {
+            const float inv = 1.f / fmaxf(l_run[half], 1e-20f);
+            float* dst = a.out + (size_t)m * a.ldq + (size_t)h * HD + 2 * tq;
+#pragma unroll
+            for (int nb = 0; nb < NB; nb++) *reinterpret_cast<float2*>(dst + 8 * nb) = make_float2(oacc[nb][2 * half] * inv, oacc[nb][2 * half + 1] * inv);
+        } else {
+            float* dst = a.partial + (((size_t)m * a.n_head + h) * a.S + sp) * (2 + HD);
+            if (tq == 0) {
+                dst[0] = m_run[half];
+                dst[1] = l_run[half];
+            }
+#pragma unroll
+            for (int nb = 0; nb < NB; nb++) *reinterpret_cast<float2*>(dst + 2 + 8 * nb + 2 * tq) = make_float2(oacc[nb][2 * half], oacc[nb][2 * half + 1]);
         }
     }
 }

@@ -286,6 +286,8 @@ static void configure_kernels_once() {
     configure_kernel(k_attn_chunk<64>, true);
     configure_kernel(k_attn_chunk<128>, true);
     configure_kernel(k_attn_chunk<256>, true);
+    configure_kernel(k_attn_chunk_mma<64>, true);
+    configure_kernel(k_attn_chunk_mma<128>, true);
     configure_kernel(k_prep_rows, false);
     configure_kernel(k_attn_chunk_merge, false);
     // the attention kernel also has static shared memory: ask for exactly the dynamic part it uses
@@ -1685,15 +1687,19 @@ static int forward_chunk(tfr_engine* e, const tfr_kv* kv, const int* tok, int M,
             const int rep = P.n_head / P.n_kv;
             // few tokens (verification batches): one query token per CTA, so that a row's serial walk over the keys is
             // a warp's only work; prompts: four tokens share every K/V tile
-            a.QT = M <= CHUNK_VERIFY_MAX ? 1 : std::max(1, ATTC_ROWS_MAX / rep);
+            // prompt chunks with head sizes up to 128 run on the tensor cores: 128 (token, head) rows per CTA
+            const bool mma = M > CHUNK_VERIFY_MAX && attn_staged_mma(hd) && !getenv("TFR_ATTN_REGISTER_ROUTE");
+            a.QT = M <= CHUNK_VERIFY_MAX ? 1 : std::max(1, (mma ? ATTM_ROWS : ATTC_ROWS_MAX) / rep);
             const int q_tiles = (M + a.QT - 1) / a.QT;
-            // key splits: enough CTAs for every SM, never less than eight key tiles (256 keys) per split
-            const int tiles_max = (pos0 + M + ATTC_TK - 1) / ATTC_TK;
-            a.S = std::max(1, std::min(std::min(CHUNK_ATTN_SPLITS_MAX, tiles_max / 8), (2 * cap + P.n_kv * q_tiles - 1) / (P.n_kv * q_tiles)));
+            // key splits: enough CTAs for every SM, never less than 256 keys per split
+            const int blocks256 = (pos0 + M + 255) / 256;
+            a.S = std::max(1, std::min(std::min(CHUNK_ATTN_SPLITS_MAX, blocks256), (2 * cap + P.n_kv * q_tiles - 1) / (P.n_kv * q_tiles)));
             a.partial = e->cpart;
             const dim3 grid(P.n_kv, q_tiles, a.S);
-            const size_t smem = attn_chunk_smem(hd);
-            cudaError_t r = hd == 64    ? launch_pdl(k_attn_chunk<64>, grid, dim3(ATTC_THREADS), smem, s, a)
+            const size_t smem = mma ? attn_chunk_mma_smem(hd) : attn_chunk_smem(hd);
+            cudaError_t r = mma ? (hd == 64 ? launch_pdl(k_attn_chunk_mma<64>, grid, dim3(ATTC_THREADS), smem, s, a)
+                                            : launch_pdl(k_attn_chunk_mma<128>, grid, dim3(ATTC_THREADS), smem, s, a))
+                            : hd == 64  ? launch_pdl(k_attn_chunk<64>, grid, dim3(ATTC_THREADS), smem, s, a)
                             : hd == 128 ? launch_pdl(k_attn_chunk<128>, grid, dim3(ATTC_THREADS), smem, s, a)
                                         : launch_pdl(k_attn_chunk<256>, grid, dim3(ATTC_THREADS), smem, s, a);
             if (r != cudaSuccess) return -1;
