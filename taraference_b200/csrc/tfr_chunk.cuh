@@ -278,15 +278,16 @@ k_gemm_q8(const unsigned char* act_g, const float* xn, RowJob ja, RowJob jb, F32
             const int per_row = 16 * nb, ppp = max(1, g.pbuf_floats / (2 * per_row));  // row pairs per pass
             for (int p0 = 0; p0 < np; p0 += ppp) {
                 const int pn = min(ppp, np - p0), tn = pn * 2 * per_row;
-                for (int t = tid; t < tn; t += GEMV_THREADS) {
+                // (task, token) pairs over all threads: a CTA holds one or two row pairs, and a thread that walked its
+                // task through the tokens one after the other stood on a trip to L2 per token
+                for (int tt = tid; tt < tn * mt; tt += GEMV_THREADS) {
+                    const int m = tt / tn, t = tt - m * tn;
                     const int row_l = t / per_row, rem = t - row_l * per_row;
                     const int row_g = 2 * (pbase + p0) + row_l;
-                    for (int m = 0; m < mt; m++) {
-                        float v = 0.f;
-                        if (row_g < fseg.m.N)
-                            v = q6k_run_dot_f32_g(fseg.m, (long long)row_g * nb + (rem >> 4), rem >> 4, rem & 15, xn + (size_t)(m0 + m) * K);
-                        pbuf[(size_t)m * g.pbuf_floats + t] = v;
-                    }
+                    float v = 0.f;
+                    if (row_g < fseg.m.N)
+                        v = q6k_run_dot_f32_g(fseg.m, (long long)row_g * nb + (rem >> 4), rem >> 4, rem & 15, xn + (size_t)(m0 + m) * K);
+                    pbuf[(size_t)m * g.pbuf_floats + t] = v;
                 }
                 __syncthreads();
                 for (int item = warp; item < pn * mt; item += GEMV_WARPS) {
@@ -398,6 +399,213 @@ inline cudaError_t launch_gemm(cudaStream_t stream, int grid, const unsigned cha
     if (!L.fits) return cudaErrorInvalidValue;
     L.g.act_stride = act_stride;
     return launch_pdl(k_gemm_q8<BLK>, dim3(grid), dim3(GEMV_THREADS), L.smem, stream, act_g, xn, ja, jb, fseg, epi, L.g, st);
+}
+
+// ------------------------------------------------------------------ the chunk GEMM on the tensor cores (Q4_K)
+
+// CTA tile = 16 * RG rows x 64 tokens, k-loop over the 256-weight blocks, both operands double-buffered in shared
+// memory by 16-byte asynchronous copies: the 144-byte block of (row r, block b) is nine pieces of the tiled layout, the
+// tokens' int8 groups of block b are sixteen pieces of their activation record, their group scales and scaled sums four
+// more.  A warp owns 16 rows and NBW blocks of eight tokens.  The sub-block dots I_j = sum nibble * q8 (kernels/gemv.cu:
+// 71-130) run as m16n8k32 u8 x s8 MMAs — the low nibbles of a 32-byte stretch are sub-block 2 t, the high nibbles, left
+// in place and shifted out of the sum afterwards, sub-block 2 t + 1 — and are the exact integers of block_dot; the scale
+// arithmetic runs on the accumulator fragments (a lane holds two rows x two tokens), block partials d * acc - dmin *
+// accm are summed along k in registers.  That order of a row's sum differs from reduce_rows' butterfly: results agree
+// with the decode kernels' to fp32 rounding, not bit for bit.
+constexpr int GM_MT = 64;         // tokens per CTA tile
+constexpr int GM_ASTRIDE = 176;   // bytes per staged weight block: eight rows' four words hit 32 different banks
+constexpr int GM_BSTRIDE = 272;   // bytes per staged token (256 int8 + 16)
+constexpr int GM_THREADS = 256;
+constexpr int GEMM_MMA_MIN_TOKENS = 17;  // smaller batches (verification) keep the dp4a kernel
+inline size_t gemm_mma_stage_bytes(int rg, bool zip) { return (size_t)rg * 16 * GM_ASTRIDE * (zip ? 2 : 1) + (size_t)GM_MT * GM_BSTRIDE + (size_t)GM_MT * 64; }
+inline size_t gemm_mma_smem(int rg, bool zip) { return 2 * gemm_mma_stage_bytes(rg, zip); }
+
+__device__ __forceinline__ void mma_16832_u8s8(int (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// ZIP: two matrices of the same shape (gate, up), epilogue apply(row, gate, up); otherwise one matrix and the
+// pair-ordered epilogues (store / Q, K rows with RoPE), whose two rows meet by a shuffle.
+template <int RG, bool ZIP>
+__global__ void __launch_bounds__(GM_THREADS, 2)
+k_gemm_mma_q4(const unsigned char* act_g, size_t act_stride, Mat A, Mat B2, int id_base, ChunkEpi epi, int M, int m_base) {
+    constexpr int NBW = RG;                      // 8-token blocks per warp: 8 warps = RG row groups x (8 / RG) token parts
+    constexpr int NMAT = ZIP ? 2 : 1;
+    constexpr int TB = Q4_TILE_BYTES;
+    extern __shared__ __align__(128) unsigned char gm_smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gq = lane >> 2, tq = lane & 3;
+    const int K = A.K, nb = A.nb;
+    const int row0 = blockIdx.x * RG * 16;
+    const size_t a_bytes = (size_t)RG * 16 * GM_ASTRIDE, stage_b = a_bytes * NMAT + (size_t)GM_MT * GM_BSTRIDE + (size_t)GM_MT * 64;
+    const int mt = min(GM_MT, M - m_base);       // tokens of this launch's token tile
+    const unsigned char* act_t = act_g + (size_t)m_base * act_stride;
+    auto stage_a = [&](int st_, int mat) { return gm_smem + (size_t)st_ * stage_b + (size_t)mat * a_bytes; };
+    auto stage_q = [&](int st_) { return gm_smem + (size_t)st_ * stage_b + a_bytes * NMAT; };
+    auto stage_s = [&](int st_) { return reinterpret_cast<float*>(gm_smem + (size_t)st_ * stage_b + a_bytes * NMAT + (size_t)GM_MT * GM_BSTRIDE); };
+    auto issue = [&](int b, int st_) {
+#pragma unroll
+        for (int mat = 0; mat < NMAT; mat++) {
+            const uint8_t* data = mat ? B2.data : A.data;
+            unsigned char* dst = stage_a(st_, mat);
+            for (int i = tid; i < RG * 16 * 9; i += GM_THREADS) {
+                const int r = i / 9, piece = i - r * 9;
+                const long long f = (long long)min(row0 + r, A.N - 1) * nb + b;  // rows past the matrix repeat its last row
+                cp_async16(dst + r * GM_ASTRIDE + piece * 16, data + (f >> 5) * TB + piece * 512 + (f & 31) * 16, 16);
+            }
+        }
+        unsigned char* q = stage_q(st_);
+        for (int i = tid; i < GM_MT * 16; i += GM_THREADS) {
+            const int t = i >> 4, c = i & 15;
+            const bool in = t < mt;
+            cp_async16(q + t * GM_BSTRIDE + c * 16, act_t + (size_t)(in ? t : 0) * act_stride + ((size_t)c * nb + b) * 16, in ? 16 : 0);
+        }
+        float* sc = stage_s(st_);
+        for (int i = tid; i < GM_MT * 4; i += GM_THREADS) {
+            const int t = i >> 2, part = i & 3;  // parts 0, 1: group scales d8[8 b ..]; 2, 3: scaled sums ds[8 b ..]
+            const bool in = t < mt;
+            const unsigned char* rec = act_t + (size_t)(in ? t : 0) * act_stride + K + (part >> 1) * (K / 32) * 4;
+            cp_async16(sc + t * 16 + part * 4, rec + (size_t)(8 * b + 4 * (part & 1)) * 4, in ? 16 : 0);
+        }
+        cp_async_commit();
+    };
+    griddep_wait();
+    griddep_launch_dependents();
+    const int rg = warp % RG, tpart = warp / RG;  // row group and token part of this warp
+    float total[NMAT][NBW][4];
+#pragma unroll
+    for (int mat = 0; mat < NMAT; mat++)
+#pragma unroll
+        for (int n = 0; n < NBW; n++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) total[mat][n][i] = 0.f;
+    issue(0, 0);
+    for (int b = 0; b < nb; b++) {
+        const int st_ = b & 1;
+        if (b + 1 < nb) {
+            issue(b + 1, st_ ^ 1);
+            cp_async_wait_group<1>();
+        } else {
+            cp_async_wait_all();
+        }
+        __syncthreads();
+        const unsigned char* qs = stage_q(st_);
+        const float* scs = stage_s(st_);
+#pragma unroll
+        for (int mat = 0; mat < NMAT; mat++) {
+            const unsigned char* ar = stage_a(st_, mat) + (size_t)(rg * 16 + gq) * GM_ASTRIDE;  // row gq of the group; row gq + 8 is 8 strides on
+            // d, dmin and the 6-bit scales and mins of the two rows (kernels/common.cu:40-50, as in block_dot)
+            unsigned sc_lo[2], sc_hi[2], m_lo[2], m_hi[2];
+            float2 dd[2];
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const int4 wh = *reinterpret_cast<const int4*>(ar + r * 8 * GM_ASTRIDE);
+                const unsigned s0 = (unsigned)wh.y, s1 = (unsigned)wh.z, s2 = (unsigned)wh.w;
+                sc_lo[r] = s0 & 0x3f3f3f3fu, sc_hi[r] = (s2 & 0x0f0f0f0fu) | (((s0 >> 6) & 0x03030303u) << 4);
+                m_lo[r] = s1 & 0x3f3f3f3fu, m_hi[r] = ((s2 >> 4) & 0x0f0f0f0fu) | (((s1 >> 6) & 0x03030303u) << 4);
+                dd[r] = __half22float2(*reinterpret_cast<const __half2*>(&wh.x));
+            }
+#pragma unroll
+            for (int n = 0; n < NBW; n++) {
+                const int tok0 = (tpart * NBW + n) * 8;
+                if (tok0 >= mt) continue;  // the same for the whole warp
+                // group scales (d8) and scaled sums (ds) of tokens tok0 + 2 tq, + 1 for the eight sub-blocks
+                float d8[2][8], ds[2][8];
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    const float4* sp = reinterpret_cast<const float4*>(scs + (tok0 + 2 * tq + c) * 16);
+                    const float4 x0 = sp[0], x1 = sp[1], y0 = sp[2], y1 = sp[3];
+                    d8[c][0] = x0.x, d8[c][1] = x0.y, d8[c][2] = x0.z, d8[c][3] = x0.w, d8[c][4] = x1.x, d8[c][5] = x1.y, d8[c][6] = x1.z, d8[c][7] = x1.w;
+                    ds[c][0] = y0.x, ds[c][1] = y0.y, ds[c][2] = y0.z, ds[c][3] = y0.w, ds[c][4] = y1.x, ds[c][5] = y1.y, ds[c][6] = y1.z, ds[c][7] = y1.w;
+                }
+                const unsigned char* qt = qs + (size_t)(tok0 + gq) * GM_BSTRIDE + 4 * tq;  // B operand: token tok0 + gq
+                float acc[4] = {0.f, 0.f, 0.f, 0.f}, accm[4] = {0.f, 0.f, 0.f, 0.f};  // [0], [1]: row gq, tokens 2 tq, + 1; [2], [3]: row gq + 8
+#pragma unroll
+                for (int t = 0; t < 4; t++) {
+                    unsigned w[4];
+                    w[0] = *reinterpret_cast<const unsigned*>(ar + (1 + 2 * t) * 16 + tq * 4);
+                    w[1] = *reinterpret_cast<const unsigned*>(ar + 8 * GM_ASTRIDE + (1 + 2 * t) * 16 + tq * 4);
+                    w[2] = *reinterpret_cast<const unsigned*>(ar + (2 + 2 * t) * 16 + tq * 4);
+                    w[3] = *reinterpret_cast<const unsigned*>(ar + 8 * GM_ASTRIDE + (2 + 2 * t) * 16 + tq * 4);
+#pragma unroll
+                    for (int half = 0; half < 2; half++) {
+                        const int j = 2 * t + half;
+                        const unsigned mask = half ? 0xf0f0f0f0u : 0x0f0f0f0fu;
+                        const unsigned af[4] = {w[0] & mask, w[1] & mask, w[2] & mask, w[3] & mask};
+                        const unsigned b0 = *reinterpret_cast<const unsigned*>(qt + j * 32), b1 = *reinterpret_cast<const unsigned*>(qt + j * 32 + 16);
+                        int c[4] = {0, 0, 0, 0};
+                        mma_16832_u8s8(c, af, b0, b1);
+                        if (half) {
+#pragma unroll
+                            for (int i = 0; i < 4; i++) c[i] >>= 4;  // the high nibbles were multiplied as nibble * 16
+                        }
+#pragma unroll
+                        for (int r = 0; r < 2; r++) {
+                            const int scj = ((j < 4 ? sc_lo[r] : sc_hi[r]) >> (8 * (j & 3))) & 0xff;
+                            const float mj = i2f_small((int)(((j < 4 ? m_lo[r] : m_hi[r]) >> (8 * (j & 3))) & 0xff));
+#pragma unroll
+                            for (int cc = 0; cc < 2; cc++) {
+                                acc[2 * r + cc] = fmaf(d8[cc][j], i2f_small(c[2 * r + cc] * scj), acc[2 * r + cc]);
+                                accm[2 * r + cc] = fmaf(ds[cc][j], mj, accm[2 * r + cc]);
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < 2; r++)
+#pragma unroll
+                    for (int cc = 0; cc < 2; cc++) total[mat][n][2 * r + cc] += dd[r].x * acc[2 * r + cc] - dd[r].y * accm[2 * r + cc];
+            }
+        }
+        __syncthreads();  // the stage is refilled at the top of the next iteration but one
+    }
+    // ---- epilogue: a lane holds rows gq, gq + 8 of its group x tokens 2 tq, 2 tq + 1 of its token blocks
+#pragma unroll
+    for (int n = 0; n < NBW; n++) {
+        const int tok0 = (tpart * NBW + n) * 8;
+        if (tok0 >= mt) continue;
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const int row = row0 + rg * 16 + gq + 8 * r;
+            if (ZIP) {
+#pragma unroll
+                for (int cc = 0; cc < 2; cc++) {
+                    const int t = tok0 + 2 * tq + cc;
+                    if (row < A.N && t < mt) ChunkEpiTok{&epi, m_base + t}.apply(id_base + row, total[0][n][2 * r + cc], total[NMAT - 1][n][2 * r + cc]);
+                }
+            } else {
+                // rows 2 p and 2 p + 1 sit in lanes gq and gq ^ 1: the even lane takes token 2 tq, the odd one 2 tq + 1
+                const float mine0 = total[0][n][2 * r], mine1 = total[0][n][2 * r + 1];
+                const float other0 = __shfl_xor_sync(TFR_FULL_MASK, mine0, 4), other1 = __shfl_xor_sync(TFR_FULL_MASK, mine1, 4);
+                const bool odd = gq & 1;
+                const int t = tok0 + 2 * tq + (odd ? 1 : 0), row_even = row & ~1;
+                const float x0 = odd ? other1 : mine0, x1 = odd ? mine1 : other0;
+                if (row_even < A.N && t < mt) ChunkEpiTok{&epi, m_base + t}.apply(id_base + (row_even >> 1), x0, x1);
+            }
+        }
+    }
+}
+
+// Launches k_gemm_mma_q4 for one matrix (pair-ordered epilogues) or a gate / up pair (ZIP).  Row tiles of 64 when
+// that still gives every SM a CTA, of 16 otherwise (the output and down projections have 2 048 rows).
+inline cudaError_t launch_gemm_mma_q4(cudaStream_t stream, int sms, const unsigned char* act_g, size_t act_stride, int M, const RowJob& ja,
+                                      const RowJob& jb, const ChunkEpi& epi) {
+    const bool zip = epi.kind == CEPI_SILU;
+    const int rows = ja.m.N;
+    const bool big = (rows + 63) / 64 >= sms;
+    const int rg = big ? 4 : 1;
+    const dim3 grid((rows + 16 * rg - 1) / (16 * rg)), block(GM_THREADS);
+    const size_t smem = gemm_mma_smem(rg, zip);
+    for (int m_base = 0; m_base < M; m_base += GM_MT) {
+        cudaError_t r;
+        if (zip) r = big ? launch_pdl(k_gemm_mma_q4<4, true>, grid, block, smem, stream, act_g, act_stride, ja.m, jb.m, ja.id_base, epi, M, m_base)
+                         : launch_pdl(k_gemm_mma_q4<1, true>, grid, block, smem, stream, act_g, act_stride, ja.m, jb.m, ja.id_base, epi, M, m_base);
+        else r = big ? launch_pdl(k_gemm_mma_q4<4, false>, grid, block, smem, stream, act_g, act_stride, ja.m, Mat{}, ja.id_base, epi, M, m_base)
+                     : launch_pdl(k_gemm_mma_q4<1, false>, grid, block, smem, stream, act_g, act_stride, ja.m, Mat{}, ja.id_base, epi, M, m_base);
+        if (r != cudaSuccess) return r;
+    }
+    return cudaSuccess;
 }
 
 // ------------------------------------------------------------------ causal attention of a chunk

@@ -283,6 +283,10 @@ static void configure_kernels_once() {
     configure_kernel(k_gemm_q8<BlockQ4>, true);
     configure_kernel(k_gemm_q8<BlockQ6>, true);
     configure_kernel(k_gemm_q8<BlockQ8>, true);
+    configure_kernel(k_gemm_mma_q4<4, true>, true);
+    configure_kernel(k_gemm_mma_q4<1, true>, true);
+    configure_kernel(k_gemm_mma_q4<4, false>, true);
+    configure_kernel(k_gemm_mma_q4<1, false>, true);
     configure_kernel(k_attn_chunk<64>, true);
     configure_kernel(k_attn_chunk<128>, true);
     configure_kernel(k_attn_chunk<256>, true);
@@ -1630,6 +1634,10 @@ static int chunk_buffers(tfr_engine* e) {
 
 static cudaError_t launch_gemm_typed(cudaStream_t s, int grid, int type, const unsigned char* act, size_t stride, const float* xn, int M,
                                      const RowJob& ja, const RowJob& jb, const F32Seg& fseg, const ChunkEpi& epi, int K, TokenState* st) {
+    // Q4_K projections of prompt chunks run their sub-block dots on the tensor cores (one matrix with a pair-ordered
+    // epilogue, or the gate / up pair); TFR_GEMM_DP4A=1 in the environment keeps them on the dp4a kernel (a test aid)
+    if (type == TFR_Q4_K && M >= GEMM_MMA_MIN_TOKENS && !fseg.m.data && (!jb.m.data || epi.kind == CEPI_SILU) && !getenv("TFR_GEMM_DP4A"))
+        return launch_gemm_mma_q4(s, grid, act, stride, M, ja, jb, epi);
     if (type == TFR_Q4_K) return launch_gemm<BlockQ4>(s, grid, act, stride, xn, M, ja, jb, fseg, epi, K, st);
     if (type == TFR_Q8_0) return launch_gemm<BlockQ8>(s, grid, act, stride, xn, M, ja, jb, fseg, epi, K, st);
     return launch_gemm<BlockQ6>(s, grid, act, stride, xn, M, ja, jb, fseg, epi, K, st);
@@ -1675,7 +1683,15 @@ static int forward_chunk(tfr_engine* e, const tfr_kv* kv, const int* tok, int M,
             ep.out = e->cq, ep.ldo = nq, ep.bias = L.bias_qkv;
             ep.kc = kv_k(kv, li), ep.vc = kv_v(kv, li);
             ep.nq = nq, ep.nk = nkv, ep.hd = hd, ep.kvdim = nkv, ep.pos0 = pos0, ep.theta = c.rope_theta;
-            if (launch_gemm<BlockQ4>(s, cap, e->cact, e->cact_stride, e->cxn, M, jq, jk, fseg, ep, K, e->st) != cudaSuccess) return -1;
+            if (M >= GEMM_MMA_MIN_TOKENS && !getenv("TFR_GEMM_DP4A")) {
+                // prompt chunks: the Q rows (eight ninths of the launch's Q4_K weights) on the tensor cores; the K rows and
+                // the fp32-route V rows, which fill the cache, keep the decode kernels' arithmetic bit for bit
+                if (launch_gemm_mma_q4(s, cap, e->cact, e->cact_stride, M, jq, RowJob{}, ep) != cudaSuccess) return -1;
+                n++;
+                if (launch_gemm<BlockQ4>(s, cap, e->cact, e->cact_stride, e->cxn, M, jk, RowJob{}, fseg, ep, K, e->st) != cudaSuccess) return -1;
+            } else if (launch_gemm<BlockQ4>(s, cap, e->cact, e->cact_stride, e->cxn, M, jq, jk, fseg, ep, K, e->st) != cudaSuccess) {
+                return -1;
+            }
             n++;
         }
         // 2. causal attention over the cache (rows of this chunk included)
@@ -1723,8 +1739,8 @@ static int forward_chunk(tfr_engine* e, const tfr_kv* kv, const int* tok, int M,
             ChunkEpi ep{};
             ep.kind = CEPI_SILU;
             ep.out = e->ch, ep.ldo = FF;
-            if (launch_gemm<BlockQ4>(s, cap, e->cact, e->cact_stride, nullptr, M, make_job(L.gate->m, 1, cap), make_job(L.up->m, 1, cap),
-                                     F32Seg{}, ep, K, e->st) != cudaSuccess)
+            if (launch_gemm_typed(s, cap, L.gate->m.type, e->cact, e->cact_stride, nullptr, M, make_job(L.gate->m, 1, cap), make_job(L.up->m, 1, cap),
+                                  F32Seg{}, ep, K, e->st) != cudaSuccess)
                 return -1;
             n++;
         }
