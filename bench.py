@@ -48,6 +48,9 @@ WORKLOADS = {
     "3b-long": ("QWEN25_3B", 16384, 512, 32768,
                 "qwen2.5-3b-shape Q4_K_M, long-context flash-decode: 16384-token prompt in the fp16 KV cache, 512 decoded "
                 "tokens per step at positions 16384..16895, ctx 32768 (BASELINE configuration 3)"),
+    "3b-prompt": ("QWEN25_3B", 2048, 64, 4096,
+                  "qwen2.5-3b-shape Q4_K_M, 2048-token prompt through the chunk kernels (the `prefill` object), then 64 "
+                  "decoded tokens per step at positions 2048..2111"),
     "hybrid-4b": ("QWEN35_4B", 64, 256, 4096,
                   "qwen3.5-4b-style hybrid Q4_K_M (3 Gated-DeltaNet layers : 1 gated full-attention layer), 64-token prompt, "
                   "256 decoded tokens per step (BASELINE configuration 4)"),

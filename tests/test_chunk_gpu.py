@@ -121,6 +121,39 @@ def test_long_chunked_prompt_with_key_splits(E, cfg):
     m.destroy()
 
 
+@pytest.mark.parametrize("cfg", [SMALL, SMALL_128, ODD], ids=["small64", "small128", "odd"])
+def test_tensor_core_projections_match_the_dp4a_projections(E, cfg, monkeypatch):
+    """Prompt chunks run their Q4_K projections as int8 MMAs (k_gemm_mma_q4); TFR_GEMM_DP4A=1 keeps them on the dp4a
+    kernel, which the tests above hold against the oracle and the reference.  One layer, so that what is compared is
+    one pass through the projections: the integer sub-block sums are the same numbers on both routes, the fp32 sums
+    differ in order (fp32 rounding level, at most an int8 flip in the layer)."""
+    cfg = dict(cfg, n_layer=1)
+    tens = S.make_dense_model(cfg, seed=25)
+    rng = np.random.default_rng(11)
+    m = E.CudaModel.load_with(cfg, tens)
+    m.set_prefill_chunk(64)
+    rels = []
+    for n in (18, 45, 65, 130):
+        prompt = [int(t) for t in rng.integers(0, cfg["n_vocab"], n)]
+        kv_a, kv_b = m.alloc_kv(160), m.alloc_kv(160)
+        monkeypatch.setenv("TFR_GEMM_DP4A", "1")
+        tok_a = m.forward_greedy(prompt, kv_a)
+        logits_a = m.current_logits()
+        monkeypatch.delenv("TFR_GEMM_DP4A")
+        tok_b = m.forward_greedy(prompt, kv_b)
+        logits_b = m.current_logits()
+        ka, va = _cache_rows(m, kv_a, cfg, 0, n)
+        kb, vb = _cache_rows(m, kv_b, cfg, 0, n)
+        assert np.array_equal(ka, kb) and np.array_equal(va, vb)  # K and V rows keep the decode arithmetic on both routes
+        rels.append(_rel(logits_b, logits_a))
+        assert rels[-1] < TF_WORST, (n, rels)
+        assert tok_a == tok_b or _margin(logits_a) <= 1e-2
+        kv_a.free()
+        kv_b.free()
+    assert np.median(rels) < 1e-4, rels  # without a flip the routes agree to fp32 rounding
+    m.destroy()
+
+
 @pytest.mark.parametrize("cfg", CFGS, ids=IDS)
 def test_chunked_prompt_vs_cpu_oracle(E, oracle, cfg):
     tens = S.make_dense_model(cfg, seed=22)
