@@ -608,6 +608,211 @@ inline cudaError_t launch_gemm_mma_q4(cudaStream_t stream, int sms, const unsign
     return cudaSuccess;
 }
 
+// ------------------------------------------------------------------ the chunk GEMM on the tensor cores (Q6_K)
+
+// The same frame for Q6_K matrices (down, the head): 64 rows x 64 tokens per CTA, eight warps = four row groups x two
+// token halves, and optionally a part of the k range (grid.y parts: a matrix of 2 048 rows has only 32 row tiles).
+// A block's sixteen scale groups are one m16n8k16 s8 x s8 MMA each: the 6-bit values are assembled from the ql nibbles
+// and qh bit pairs as in block_dot(BlockQ6) (kernels/gemv.cu:302-337), the accumulators start at -32 * sum(q8) of the
+// group, so the MMA leaves the exact J = sum (q6 - 32) * q8.  With k parts the CTA stores its partial sums and
+// k_gemm_splitk_finish adds the parts in a fixed order and runs the epilogue.
+constexpr int GM6_ASTRIDE = 240;  // 13 pieces + the d pair + padding: eight rows' words hit 32 different banks
+inline size_t gemm_mma_q6_smem() { return 2 * ((size_t)64 * GM6_ASTRIDE + (size_t)GM_MT * GM_BSTRIDE + (size_t)GM_MT * 96); }
+
+__device__ __forceinline__ void mma_16816_s8(int (&c)[4], unsigned a0, unsigned a1, unsigned b0) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(b0));
+}
+
+__global__ void __launch_bounds__(GM_THREADS, 2)
+k_gemm_mma_q6(const unsigned char* act_g, size_t act_stride, Mat A, int id_base, ChunkEpi epi, int M, float* partial) {
+    constexpr int RG = 4, NBW = 4, TB = Q6_TILE_BYTES;
+    extern __shared__ __align__(128) unsigned char gm_smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gq = lane >> 2, tq = lane & 3;
+    const int K = A.K, nb = A.nb;
+    const int row0 = blockIdx.x * RG * 16;
+    const int kparts = gridDim.y, kp = blockIdx.y;
+    const int b_begin = (int)((long long)nb * kp / kparts), b_end = (int)((long long)nb * (kp + 1) / kparts);
+    constexpr size_t a_bytes = (size_t)RG * 16 * GM6_ASTRIDE, q_bytes = (size_t)GM_MT * GM_BSTRIDE, stage_b = a_bytes + q_bytes + (size_t)GM_MT * 96;
+    const int mt = min(GM_MT, M);
+    auto stage_a = [&](int st_) { return gm_smem + (size_t)st_ * stage_b; };
+    auto stage_q = [&](int st_) { return gm_smem + (size_t)st_ * stage_b + a_bytes; };
+    auto stage_x = [&](int st_) { return gm_smem + (size_t)st_ * stage_b + a_bytes + q_bytes; };  // per token: 8 floats d8, 16 ints -32 * S16
+    auto issue = [&](int b, int st_) {
+        unsigned char* dst = stage_a(st_);
+        for (int i = tid; i < RG * 16 * 14; i += GM_THREADS) {
+            const int r = i / 14, piece = i - r * 14;
+            const long long f = (long long)min(row0 + r, A.N - 1) * nb + b;  // rows past the matrix repeat its last row
+            const uint8_t* tile = A.data + (f >> 5) * TB;
+            if (piece < 13) cp_async16(dst + r * GM6_ASTRIDE + piece * 16, tile + piece * 512 + (f & 31) * 16, 16);
+            else cp_async4(dst + r * GM6_ASTRIDE + 208, tile + Q6_PIECES * 512 + ((f & 31) & ~1) * 2);  // d of this block and its neighbour
+        }
+        unsigned char* q = stage_q(st_);
+        for (int i = tid; i < GM_MT * 16; i += GM_THREADS) {
+            const int t = i >> 4, c = i & 15;
+            const bool in = t < mt;
+            cp_async16(q + t * GM_BSTRIDE + c * 16, act_g + (size_t)(in ? t : 0) * act_stride + ((size_t)c * nb + b) * 16, in ? 16 : 0);
+        }
+        unsigned char* x = stage_x(st_);
+        for (int i = tid; i < GM_MT * 6; i += GM_THREADS) {
+            const int t = i / 6, part = i - t * 6;  // parts 0, 1: d8[8 b ..]; 2 .. 5: s16n[16 b ..]
+            const bool in = t < mt;
+            const unsigned char* rec = act_g + (size_t)(in ? t : 0) * act_stride + K;
+            const unsigned char* src = part < 2 ? rec + (size_t)(8 * b + 4 * part) * 4 : rec + (size_t)(K / 32) * 8 + (size_t)(16 * b + 4 * (part - 2)) * 4;
+            cp_async16(x + t * 96 + part * 16, src, in ? 16 : 0);
+        }
+        cp_async_commit();
+    };
+    griddep_wait();
+    griddep_launch_dependents();
+    const int rg = warp & 3, tpart = warp >> 2;
+    float total[NBW][4];
+#pragma unroll
+    for (int n = 0; n < NBW; n++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) total[n][i] = 0.f;
+    if (b_begin < b_end) issue(b_begin, 0);
+    for (int b = b_begin; b < b_end; b++) {
+        const int st_ = (b - b_begin) & 1;
+        if (b + 1 < b_end) {
+            issue(b + 1, st_ ^ 1);
+            cp_async_wait_group<1>();
+        } else {
+            cp_async_wait_all();
+        }
+        __syncthreads();
+        const unsigned char* qs = stage_q(st_);
+        const unsigned char* xs = stage_x(st_);
+        const unsigned char* ar = stage_a(st_) + (size_t)(rg * 16 + gq) * GM6_ASTRIDE;  // row gq of the group; row gq + 8 is 8 strides on
+        int4 wsc[2];
+        float dw[2];
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            wsc[r] = *reinterpret_cast<const int4*>(ar + r * 8 * GM6_ASTRIDE + 12 * 16);
+            const unsigned dpair = *reinterpret_cast<const unsigned*>(ar + r * 8 * GM6_ASTRIDE + 208);
+            const long long f = (long long)min(row0 + rg * 16 + gq + 8 * r, A.N - 1) * nb + b;
+            dw[r] = f16_to_f32((unsigned short)((f & 1) ? dpair >> 16 : dpair & 0xffffu));
+        }
+#pragma unroll
+        for (int n = 0; n < NBW; n++) {
+            const int tok0 = (tpart * NBW + n) * 8;
+            if (tok0 >= mt) continue;  // the same for the whole warp
+            float d8[2][8];
+            int s16[2][16];
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                const int4* xp = reinterpret_cast<const int4*>(xs + (size_t)(tok0 + 2 * tq + c) * 96);
+                const int4 x0 = xp[0], x1 = xp[1];
+                d8[c][0] = __int_as_float(x0.x), d8[c][1] = __int_as_float(x0.y), d8[c][2] = __int_as_float(x0.z), d8[c][3] = __int_as_float(x0.w);
+                d8[c][4] = __int_as_float(x1.x), d8[c][5] = __int_as_float(x1.y), d8[c][6] = __int_as_float(x1.z), d8[c][7] = __int_as_float(x1.w);
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const int4 y = xp[2 + k];
+                    s16[c][4 * k] = y.x, s16[c][4 * k + 1] = y.y, s16[c][4 * k + 2] = y.z, s16[c][4 * k + 3] = y.w;
+                }
+            }
+            const unsigned char* qt = qs + (size_t)(tok0 + gq) * GM_BSTRIDE + 4 * tq;  // B operand: token tok0 + gq
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};  // [0], [1]: row gq, tokens 2 tq, + 1; [2], [3]: row gq + 8
+#pragma unroll
+            for (int nn = 0; nn < 2; nn++)
+#pragma unroll
+                for (int is = 0; is < 2; is++) {
+                    unsigned la[2], lb[2], hw[2];
+#pragma unroll
+                    for (int r = 0; r < 2; r++) {
+                        const unsigned char* rowp = ar + r * 8 * GM6_ASTRIDE + tq * 4;
+                        la[r] = *reinterpret_cast<const unsigned*>(rowp + (4 * nn + is) * 16);
+                        lb[r] = *reinterpret_cast<const unsigned*>(rowp + (4 * nn + 2 + is) * 16);
+                        hw[r] = *reinterpret_cast<const unsigned*>(rowp + (8 + 2 * nn + is) * 16);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const int c = 8 * nn + 2 * j + is;  // the scale group: elements 16 c .. 16 c + 15 of the block
+                        unsigned af[2];
+#pragma unroll
+                        for (int r = 0; r < 2; r++) {
+                            const unsigned nibw = (j & 1) ? lb[r] : la[r];
+                            af[r] = ((nibw >> (4 * (j >> 1))) & 0x0f0f0f0fu) | (((hw[r] >> (2 * j)) << 4) & 0x30303030u);
+                        }
+                        const unsigned b0 = *reinterpret_cast<const unsigned*>(qt + c * 16);
+                        int cj[4] = {s16[0][c], s16[1][c], s16[0][c], s16[1][c]};
+                        mma_16816_s8(cj, af[0], af[1], b0);
+#pragma unroll
+                        for (int r = 0; r < 2; r++) {
+                            const int w = r ? (c < 4 ? wsc[1].x : c < 8 ? wsc[1].y : c < 12 ? wsc[1].z : wsc[1].w)
+                                            : (c < 4 ? wsc[0].x : c < 8 ? wsc[0].y : c < 12 ? wsc[0].z : wsc[0].w);
+                            const float cf = i2f_small((int)(signed char)((w >> (8 * (c & 3))) & 0xff));
+#pragma unroll
+                            for (int cc = 0; cc < 2; cc++) acc[2 * r + cc] = fmaf(cf * d8[cc][c >> 1], i2f_small(cj[2 * r + cc]), acc[2 * r + cc]);
+                        }
+                    }
+                }
+#pragma unroll
+            for (int r = 0; r < 2; r++)
+#pragma unroll
+                for (int cc = 0; cc < 2; cc++) total[n][2 * r + cc] += dw[r] * acc[2 * r + cc];
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int n = 0; n < NBW; n++) {
+        const int tok0 = (tpart * NBW + n) * 8;
+        if (tok0 >= mt) continue;
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const int row = row0 + rg * 16 + gq + 8 * r;
+            if (kparts > 1) {
+#pragma unroll
+                for (int cc = 0; cc < 2; cc++) {
+                    const int t = tok0 + 2 * tq + cc;
+                    if (row < A.N && t < mt) partial[((size_t)kp * M + t) * A.N + row] = total[n][2 * r + cc];
+                }
+            } else {
+                const float mine0 = total[n][2 * r], mine1 = total[n][2 * r + 1];
+                const float other0 = __shfl_xor_sync(TFR_FULL_MASK, mine0, 4), other1 = __shfl_xor_sync(TFR_FULL_MASK, mine1, 4);
+                const bool odd = gq & 1;
+                const int t = tok0 + 2 * tq + (odd ? 1 : 0), row_even = row & ~1;
+                const float x0 = odd ? other1 : mine0, x1 = odd ? mine1 : other0;
+                if (row_even < A.N && t < mt) ChunkEpiTok{&epi, t}.apply(id_base + (row_even >> 1), x0, x1);
+            }
+        }
+    }
+}
+
+// Adds the k parts of k_gemm_mma_q6 in their order and runs the pair-ordered epilogue: one thread per (token, row pair).
+__global__ void k_gemm_splitk_finish(const float* partial, int kparts, int M, int N, int id_base, ChunkEpi epi) {
+    griddep_wait();
+    griddep_launch_dependents();
+    const int pairs = (N + 1) >> 1;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= M * pairs) return;
+    const int t = i / pairs, p = i - t * pairs;
+    float x0 = 0.f, x1 = 0.f;
+    for (int k = 0; k < kparts; k++) {
+        const float* src = partial + ((size_t)k * M + t) * N + 2 * p;
+        x0 += src[0];
+        if (2 * p + 1 < N) x1 += src[1];
+    }
+    ChunkEpiTok{&epi, t}.apply(id_base + p, x0, x1);
+}
+
+// ws: scratch for the k parts (ws_floats floats; nullptr: no split).
+inline cudaError_t launch_gemm_mma_q6(cudaStream_t stream, int sms, const unsigned char* act_g, size_t act_stride, int M, const RowJob& ja,
+                                      const ChunkEpi& epi, float* ws, size_t ws_floats) {
+    const int rows = ja.m.N, tiles = (rows + 63) / 64;
+    int kparts = 1;
+    if (ws && tiles < sms) {
+        kparts = std::min(std::min(4, ja.m.nb), std::max(1, sms / tiles));
+        if ((size_t)kparts * M * rows > ws_floats) kparts = 1;
+    }
+    cudaError_t r = launch_pdl(k_gemm_mma_q6, dim3(tiles, kparts), dim3(GM_THREADS), gemm_mma_q6_smem(), stream, act_g, act_stride, ja.m,
+                               ja.id_base, epi, M, ws);
+    if (r != cudaSuccess || kparts == 1) return r;
+    const int items = M * ((rows + 1) / 2);
+    return launch_pdl(k_gemm_splitk_finish, dim3((items + 255) / 256), dim3(256), (size_t)0, stream, (const float*)ws, kparts, M, rows, ja.id_base, epi);
+}
+
 // ------------------------------------------------------------------ causal attention of a chunk
 
 // CTA = (KV head g, tile of QT query tokens, split s of the keys); its rows are the QT x rep (query token, query head

@@ -113,6 +113,10 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, unsigned i
                  : "memory");
 }
 
+// 4-byte asynchronous copy global -> shared.
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
 // 16-byte asynchronous copy global -> shared (LDGSTS); n_src = 0 fills the destination with zeros.
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, int n_src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(n_src) : "memory");

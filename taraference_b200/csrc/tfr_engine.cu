@@ -181,6 +181,7 @@ struct tfr_engine {
     bool chunk_ok = false;
     std::string chunk_why;
     float *cx = nullptr, *cq = nullptr, *cattn = nullptr, *ch = nullptr, *cxn = nullptr, *clogits = nullptr, *cpart = nullptr;
+    size_t cpart_floats = 0;
     unsigned char* cact = nullptr;
     size_t cact_stride = 0;
     unsigned long long* ckeys = nullptr;  // per-row, per-slice argmax keys of a verification pass
@@ -283,6 +284,8 @@ static void configure_kernels_once() {
     configure_kernel(k_gemm_q8<BlockQ4>, true);
     configure_kernel(k_gemm_q8<BlockQ6>, true);
     configure_kernel(k_gemm_q8<BlockQ8>, true);
+    configure_kernel(k_gemm_mma_q6, true);
+    configure_kernel(k_gemm_splitk_finish, false);
     configure_kernel(k_gemm_mma_q4<4, true>, true);
     configure_kernel(k_gemm_mma_q4<1, true>, true);
     configure_kernel(k_gemm_mma_q4<4, false>, true);
@@ -1628,16 +1631,22 @@ static int chunk_buffers(tfr_engine* e) {
     CU(e, cudaMalloc(&e->ckeys, (size_t)CHUNK_VERIFY_MAX * ARGMAX_SLICES * 8));
     CU(e, cudaMalloc(&e->ccount, CHUNK_VERIFY_MAX * 4));
     CU(e, cudaMemset(e->ccount, 0, CHUNK_VERIFY_MAX * 4));
-    CU(e, cudaMalloc(&e->cpart, (size_t)M * P.n_head * CHUNK_ATTN_SPLITS_MAX * (2 + e->cfg.head_dim) * 4));
+    e->cpart_floats = (size_t)M * P.n_head * CHUNK_ATTN_SPLITS_MAX * (2 + e->cfg.head_dim);
+    CU(e, cudaMalloc(&e->cpart, e->cpart_floats * 4));
     return TFR_OK;
 }
 
+// ws / ws_floats: scratch a launch may use for partial sums (the attention partials' buffer: free between the attention
+// of a layer and the next one's).
 static cudaError_t launch_gemm_typed(cudaStream_t s, int grid, int type, const unsigned char* act, size_t stride, const float* xn, int M,
-                                     const RowJob& ja, const RowJob& jb, const F32Seg& fseg, const ChunkEpi& epi, int K, TokenState* st) {
+                                     const RowJob& ja, const RowJob& jb, const F32Seg& fseg, const ChunkEpi& epi, int K, TokenState* st,
+                                     float* ws = nullptr, size_t ws_floats = 0) {
     // Q4_K projections of prompt chunks run their sub-block dots on the tensor cores (one matrix with a pair-ordered
     // epilogue, or the gate / up pair); TFR_GEMM_DP4A=1 in the environment keeps them on the dp4a kernel (a test aid)
     if (type == TFR_Q4_K && M >= GEMM_MMA_MIN_TOKENS && !fseg.m.data && (!jb.m.data || epi.kind == CEPI_SILU) && !getenv("TFR_GEMM_DP4A"))
         return launch_gemm_mma_q4(s, grid, act, stride, M, ja, jb, epi);
+    if (type == TFR_Q6_K && M >= GEMM_MMA_MIN_TOKENS && !fseg.m.data && !jb.m.data && epi.kind != CEPI_SILU && !getenv("TFR_GEMM_DP4A"))
+        return launch_gemm_mma_q6(s, grid, act, stride, M, ja, epi, ws, ws_floats);
     if (type == TFR_Q4_K) return launch_gemm<BlockQ4>(s, grid, act, stride, xn, M, ja, jb, fseg, epi, K, st);
     if (type == TFR_Q8_0) return launch_gemm<BlockQ8>(s, grid, act, stride, xn, M, ja, jb, fseg, epi, K, st);
     return launch_gemm<BlockQ6>(s, grid, act, stride, xn, M, ja, jb, fseg, epi, K, st);
@@ -1747,7 +1756,7 @@ static int forward_chunk(tfr_engine* e, const tfr_kv* kv, const int* tok, int M,
         // 5. Q8 + down + residual
         if (prep(e->ch, FF, FF, nullptr, nullptr) != cudaSuccess) return -1;
         if (launch_gemm_typed(s, cap, L.down->m.type, e->cact, e->cact_stride, nullptr, M, make_job(L.down->m, 2, cap), RowJob{}, F32Seg{},
-                              store_epi(e->cx, K, K, 2), FF, e->st) != cudaSuccess)
+                              store_epi(e->cx, K, K, 2), FF, e->st, e->cpart, e->cpart_floats) != cudaSuccess)
             return -1;
         n++;
     }
