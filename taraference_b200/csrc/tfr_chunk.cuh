@@ -259,6 +259,49 @@ k_gemm_q8(const unsigned char* act_g, const float* xn, RowJob ja, RowJob jb, F32
     bool ok = true, dead = false;  // dead: this warp saw a copy time out and takes no further tiles
     int late_slot = -1;
     unsigned late_parity = 0;
+    // Rows on the fp32 activation route whose tasks fit one pass of the CTA (the usual case: one or two V row pairs per
+    // CTA): a thread unpacks the sixteen weights of its task ONCE, keeps them in registers and walks the tokens of the
+    // whole launch, every token's normalised vector straight from global memory; with fewer tasks than threads the
+    // tokens of a group are shared out among the threads of a task.  Same operations in the same order as
+    // q6k_run_dot_f32_g, hence the same bits.
+    bool f32_done = false;
+    if (fseg.m.data) {
+        const int np = fseg.sh.count(cta), pbase = fseg.sh.begin(cta);
+        const int per_row = 16 * nb, tn = np * 2 * per_row;
+        if (tn <= GEMV_THREADS && tn <= g.pbuf_floats) {
+            f32_done = true;
+            if (np > 0) {
+                const int TG = GEMV_THREADS / tn;  // threads per task
+                const int t = tid % tn, tsel = tid / tn;
+                const bool on = tid < TG * tn;
+                const int row_l = t / per_row, rem = t - row_l * per_row, row_g = 2 * pbase + row_l;
+                float w[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) w[i] = 0.f;
+                if (on && row_g < fseg.m.N) q6k_run_weights_f32(fseg.m, (long long)row_g * nb + (rem >> 4), rem & 15, w);
+                for (int m0 = 0; m0 < g.M; m0 += Mt) {
+                    const int mt = min(Mt, g.M - m0);
+                    if (on)
+                        for (int m = tsel; m < mt; m += TG)
+                            pbuf[(size_t)m * g.pbuf_floats + t] = q6k_run_dot_weights(w, xn + (size_t)(m0 + m) * K + 256 * (rem >> 4) + 16 * (rem & 15));
+                    __syncthreads();
+                    for (int item = warp; item < np * mt; item += GEMV_WARPS) {
+                        const int m = item / np, rr = item - m * np;
+                        const float* a = pbuf + (size_t)m * g.pbuf_floats + (2 * rr) * per_row;
+                        float s0 = 0.f, s1 = 0.f;
+                        for (int i = lane; i < per_row; i += 32) {
+                            s0 += a[i];
+                            s1 += a[per_row + i];
+                        }
+                        s0 = warp_sum(s0);
+                        s1 = warp_sum(s1);
+                        if (lane == 0) ChunkEpiTok{&epi, m0 + m}.apply(fseg.id_base + pbase + rr, s0, s1);
+                    }
+                    __syncthreads();
+                }
+            }
+        }
+    }
     for (int grp_i = 0; grp_i < n_groups; grp_i++) {
         const int m0 = grp_i * Mt, mt = min(Mt, g.M - m0);
         // the Q8 activations of tokens m0 .. m0 + mt - 1
@@ -271,15 +314,13 @@ k_gemm_q8(const unsigned char* act_g, const float* xn, RowJob ja, RowJob jb, F32
             }
         }
         __syncthreads();
-        // rows on the fp32 activation route (kernels/gemv.cu:233-264): a task = (row, block, run of 16) reads its
-        // weights once and walks the tokens of the group, each token's normalised vector straight from global memory
-        if (fseg.m.data) {
+        // rows on the fp32 activation route (kernels/gemv.cu:233-264), when their tasks do not fit one pass of the CTA
+        // (otherwise they ran before this loop): a task = (row, block, run of 16) and a token per thread and turn
+        if (fseg.m.data && !f32_done) {
             const int np = fseg.sh.count(cta), pbase = fseg.sh.begin(cta);
             const int per_row = 16 * nb, ppp = max(1, g.pbuf_floats / (2 * per_row));  // row pairs per pass
             for (int p0 = 0; p0 < np; p0 += ppp) {
                 const int pn = min(ppp, np - p0), tn = pn * 2 * per_row;
-                // (task, token) pairs over all threads: a CTA holds one or two row pairs, and a thread that walked its
-                // task through the tokens one after the other stood on a trip to L2 per token
                 for (int tt = tid; tt < tn * mt; tt += GEMV_THREADS) {
                     const int m = tt / tn, t = tt - m * tn;
                     const int row_l = t / per_row, rem = t - row_l * per_row;
@@ -305,7 +346,36 @@ k_gemm_q8(const unsigned char* act_g, const float* xn, RowJob ja, RowJob jb, F32
                 __syncthreads();
             }
         }
-        // phase A: per-block partials of every token out of the tiles
+        // phase A: per-block partials of every token out of the tiles.
+        // A CTA with few tiles (the K rows of a prompt chunk, the projections of a verification batch on 2 048 rows)
+        // would leave most warps idle while a tile's owner walks it through the tokens one block dot after the other:
+        // when every tile sits in a slot of its own for the whole launch (no refills), the warps without a tile help —
+        // warp w takes tile w % n_jobs and every H-th token of the group, each (tile, token) pair is still one
+        // block_dot into the same partial-sum slot, so the results are the same bits.
+        const int H = n_jobs > 0 ? GEMV_WARPS / n_jobs : 0;
+        const bool helpers = H >= 2 && n_jobs <= wa && n_groups <= nsw;
+        if (helpers) {
+            if (warp < H * n_jobs) {
+                const int j = warp % n_jobs, q = warp / n_jobs, s = grp_i % nsw;  // the owner (warp j) has one tile: its use grp_i sits in slot grp_i
+                const bool is_b = j >= tiles_a;
+                const long long f = (long long)(is_b ? tb0 + (j - tiles_a) : ta0 + j) * 32 + lane;
+                const bool mine = is_b ? (f >= fb0 && f < fb1) : (f >= fa0 && f < fa1);
+                const bool landed = mbar_wait(full + j * nsw + s, 0u);
+                if (!landed) {
+                    ok = false;
+                    if (q == 0) late_slot = s, late_parity = 0u;
+                }
+                if (mine) {
+                    const int off = is_b ? rows_a * nb + (int)(f - fb0) : (int)(f - fa0);
+                    const int b = (int)(f % nb);
+                    const unsigned char* tile = ring + (size_t)(j * nsw + s) * TB;
+                    for (int m = q; m < mt; m += H) {
+                        const Act act = act_carve(act_s + (size_t)m * g.act_b16, K, false, false);
+                        pbuf[(size_t)m * g.pbuf_floats + off] = landed ? block_dot<true>(BLK{}, tile, lane, act, b, nb, nullptr) : 0.f;
+                    }
+                }
+            }
+        } else
         for (int i = 0; i < ntw && !dead; i++) {
             const int k = grp_i * ntw + i, j = warp + wa * i, s = k % nsw;
             const bool is_b = j >= tiles_a;

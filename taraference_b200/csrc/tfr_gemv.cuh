@@ -453,6 +453,41 @@ __device__ __forceinline__ float q6k_run_dot_f32_g(const Mat& m, long long f, in
     return acc;
 }
 
+// The sixteen weights of that run as the factors q6k_run_dot_f32_g multiplies x by, d * scale * (q - 32) in its order of
+// operations, and the dot with a vector piece in its order of additions: weights kept in registers serve many tokens.
+__device__ __forceinline__ void q6k_run_weights_f32(const Mat& m, long long f, int c, float (&w)[16]) {
+    const int n = c >> 3, j = (c >> 1) & 3, is = c & 1;
+    const int4 ql = __ldg(reinterpret_cast<const int4*>(block_byte(m, f, 64 * n + 32 * (j & 1) + 16 * is)));
+    const int4 qh = __ldg(reinterpret_cast<const int4*>(block_byte(m, f, 128 + 32 * n + 16 * is)));
+    const float sc = (float)(int)*reinterpret_cast<const signed char*>(block_byte(m, f, 192 + 8 * n + is + 2 * j));
+    const float d = f16_to_f32(__ldg(reinterpret_cast<const unsigned short*>(block_byte(m, f, 208))));
+    const float dsc = d * sc;
+    const int qlw[4] = {ql.x, ql.y, ql.z, ql.w};
+    const int qhw[4] = {qh.x, qh.y, qh.z, qh.w};
+    const int nsh = 4 * (j >> 1), hsh = 2 * j;
+#pragma unroll
+    for (int k = 0; k < 4; k++)
+#pragma unroll
+        for (int by = 0; by < 4; by++) {
+            const int nib = (qlw[k] >> (8 * by + nsh)) & 0xF;
+            const int hb = (qhw[k] >> (8 * by + hsh)) & 3;
+            w[4 * k + by] = dsc * (float)((nib | (hb << 4)) - 32);
+        }
+}
+__device__ __forceinline__ float q6k_run_dot_weights(const float (&w)[16], const float* x16) {
+    const float4* x4 = reinterpret_cast<const float4*>(x16);
+    float acc = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const float4 xq = x4[k];
+        acc += w[4 * k] * xq.x;
+        acc += w[4 * k + 1] * xq.y;
+        acc += w[4 * k + 2] * xq.z;
+        acc += w[4 * k + 3] * xq.w;
+    }
+    return acc;
+}
+
 // ------------------------------------------------------------------ shares
 
 // Contiguous share of n items for CTA c of C, with n = C*quot + rem split on the host so that
