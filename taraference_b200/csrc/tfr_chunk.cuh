@@ -482,13 +482,13 @@ inline cudaError_t launch_gemm(cudaStream_t stream, int grid, const unsigned cha
 // arithmetic runs on the accumulator fragments (a lane holds two rows x two tokens), block partials d * acc - dmin *
 // accm are summed along k in registers.  That order of a row's sum differs from reduce_rows' butterfly: results agree
 // with the decode kernels' to fp32 rounding, not bit for bit.
-constexpr int GM_MT = 64;         // tokens per CTA tile
+constexpr int GM_MT = 64;         // tokens per CTA tile (16 for batches of up to 16 tokens)
 constexpr int GM_ASTRIDE = 176;   // bytes per staged weight block: eight rows' four words hit 32 different banks
 constexpr int GM_BSTRIDE = 272;   // bytes per staged token (256 int8 + 16)
 constexpr int GM_THREADS = 256;
-constexpr int GEMM_MMA_MIN_TOKENS = 17;  // smaller batches (verification) keep the dp4a kernel
-inline size_t gemm_mma_stage_bytes(int rg, bool zip) { return (size_t)rg * 16 * GM_ASTRIDE * (zip ? 2 : 1) + (size_t)GM_MT * GM_BSTRIDE + (size_t)GM_MT * 64; }
-inline size_t gemm_mma_smem(int rg, bool zip) { return 2 * gemm_mma_stage_bytes(rg, zip); }
+constexpr int GEMM_MMA_MIN_TOKENS = 5;   // smaller batches keep the dp4a kernel
+inline size_t gemm_mma_stage_bytes(int rg, bool zip, int mt) { return (size_t)rg * 16 * GM_ASTRIDE * (zip ? 2 : 1) + (size_t)mt * GM_BSTRIDE + (size_t)mt * 64; }
+inline size_t gemm_mma_smem(int rg, bool zip, int mt) { return 2 * gemm_mma_stage_bytes(rg, zip, mt); }
 
 __device__ __forceinline__ void mma_16832_u8s8(int (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -498,22 +498,23 @@ __device__ __forceinline__ void mma_16832_u8s8(int (&c)[4], const unsigned (&a)[
 
 // ZIP: two matrices of the same shape (gate, up), epilogue apply(row, gate, up); otherwise one matrix and the
 // pair-ordered epilogues (store / Q, K rows with RoPE), whose two rows meet by a shuffle.
-template <int RG, bool ZIP>
+template <int RG, bool ZIP, int MT>
 __global__ void __launch_bounds__(GM_THREADS, 2)
 k_gemm_mma_q4(const unsigned char* act_g, size_t act_stride, Mat A, Mat B2, int id_base, ChunkEpi epi, int M, int m_base) {
-    constexpr int NBW = RG;                      // 8-token blocks per warp: 8 warps = RG row groups x (8 / RG) token parts
+    constexpr int NBW = MT * RG / 64;            // 8-token blocks per warp: 8 warps = RG row groups x (8 / RG) token parts of MT * RG / 8 tokens
+    static_assert(NBW >= 1, "a token part holds at least one block of eight tokens");
     constexpr int NMAT = ZIP ? 2 : 1;
     constexpr int TB = Q4_TILE_BYTES;
     extern __shared__ __align__(128) unsigned char gm_smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gq = lane >> 2, tq = lane & 3;
     const int K = A.K, nb = A.nb;
     const int row0 = blockIdx.x * RG * 16;
-    const size_t a_bytes = (size_t)RG * 16 * GM_ASTRIDE, stage_b = a_bytes * NMAT + (size_t)GM_MT * GM_BSTRIDE + (size_t)GM_MT * 64;
-    const int mt = min(GM_MT, M - m_base);       // tokens of this launch's token tile
+    const size_t a_bytes = (size_t)RG * 16 * GM_ASTRIDE, stage_b = a_bytes * NMAT + (size_t)MT * GM_BSTRIDE + (size_t)MT * 64;
+    const int mt = min(MT, M - m_base);       // tokens of this launch's token tile
     const unsigned char* act_t = act_g + (size_t)m_base * act_stride;
     auto stage_a = [&](int st_, int mat) { return gm_smem + (size_t)st_ * stage_b + (size_t)mat * a_bytes; };
     auto stage_q = [&](int st_) { return gm_smem + (size_t)st_ * stage_b + a_bytes * NMAT; };
-    auto stage_s = [&](int st_) { return reinterpret_cast<float*>(gm_smem + (size_t)st_ * stage_b + a_bytes * NMAT + (size_t)GM_MT * GM_BSTRIDE); };
+    auto stage_s = [&](int st_) { return reinterpret_cast<float*>(gm_smem + (size_t)st_ * stage_b + a_bytes * NMAT + (size_t)MT * GM_BSTRIDE); };
     auto issue = [&](int b, int st_) {
 #pragma unroll
         for (int mat = 0; mat < NMAT; mat++) {
@@ -526,13 +527,13 @@ k_gemm_mma_q4(const unsigned char* act_g, size_t act_stride, Mat A, Mat B2, int 
             }
         }
         unsigned char* q = stage_q(st_);
-        for (int i = tid; i < GM_MT * 16; i += GM_THREADS) {
+        for (int i = tid; i < MT * 16; i += GM_THREADS) {
             const int t = i >> 4, c = i & 15;
             const bool in = t < mt;
             cp_async16(q + t * GM_BSTRIDE + c * 16, act_t + (size_t)(in ? t : 0) * act_stride + ((size_t)c * nb + b) * 16, in ? 16 : 0);
         }
         float* sc = stage_s(st_);
-        for (int i = tid; i < GM_MT * 4; i += GM_THREADS) {
+        for (int i = tid; i < MT * 4; i += GM_THREADS) {
             const int t = i >> 2, part = i & 3;  // parts 0, 1: group scales d8[8 b ..]; 2, 3: scaled sums ds[8 b ..]
             const bool in = t < mt;
             const unsigned char* rec = act_t + (size_t)(in ? t : 0) * act_stride + K + (part >> 1) * (K / 32) * 4;
@@ -664,15 +665,18 @@ inline cudaError_t launch_gemm_mma_q4(cudaStream_t stream, int sms, const unsign
     const bool zip = epi.kind == CEPI_SILU;
     const int rows = ja.m.N;
     const bool big = (rows + 63) / 64 >= sms;
-    const int rg = big ? 4 : 1;
+    const bool few = M <= 16 && big;  // a token tile of 16: every warp of a 64-row CTA has a token block
+    const int rg = big ? 4 : 1, mt_tile = few ? 16 : GM_MT;
     const dim3 grid((rows + 16 * rg - 1) / (16 * rg)), block(GM_THREADS);
-    const size_t smem = gemm_mma_smem(rg, zip);
-    for (int m_base = 0; m_base < M; m_base += GM_MT) {
+    const size_t smem = gemm_mma_smem(rg, zip, mt_tile);
+    for (int m_base = 0; m_base < M; m_base += mt_tile) {
         cudaError_t r;
-        if (zip) r = big ? launch_pdl(k_gemm_mma_q4<4, true>, grid, block, smem, stream, act_g, act_stride, ja.m, jb.m, ja.id_base, epi, M, m_base)
-                         : launch_pdl(k_gemm_mma_q4<1, true>, grid, block, smem, stream, act_g, act_stride, ja.m, jb.m, ja.id_base, epi, M, m_base);
-        else r = big ? launch_pdl(k_gemm_mma_q4<4, false>, grid, block, smem, stream, act_g, act_stride, ja.m, Mat{}, ja.id_base, epi, M, m_base)
-                     : launch_pdl(k_gemm_mma_q4<1, false>, grid, block, smem, stream, act_g, act_stride, ja.m, Mat{}, ja.id_base, epi, M, m_base);
+        if (zip) r = few   ? launch_pdl(k_gemm_mma_q4<4, true, 16>, grid, block, smem, stream, act_g, act_stride, ja.m, jb.m, ja.id_base, epi, M, m_base)
+                     : big ? launch_pdl(k_gemm_mma_q4<4, true, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, jb.m, ja.id_base, epi, M, m_base)
+                           : launch_pdl(k_gemm_mma_q4<1, true, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, jb.m, ja.id_base, epi, M, m_base);
+        else r = few   ? launch_pdl(k_gemm_mma_q4<4, false, 16>, grid, block, smem, stream, act_g, act_stride, ja.m, Mat{}, ja.id_base, epi, M, m_base)
+                 : big ? launch_pdl(k_gemm_mma_q4<4, false, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, Mat{}, ja.id_base, epi, M, m_base)
+                       : launch_pdl(k_gemm_mma_q4<1, false, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, Mat{}, ja.id_base, epi, M, m_base);
         if (r != cudaSuccess) return r;
     }
     return cudaSuccess;
@@ -687,7 +691,7 @@ inline cudaError_t launch_gemm_mma_q4(cudaStream_t stream, int sms, const unsign
 // group, so the MMA leaves the exact J = sum (q6 - 32) * q8.  With k parts the CTA stores its partial sums and
 // k_gemm_splitk_finish adds the parts in a fixed order and runs the epilogue.
 constexpr int GM6_ASTRIDE = 240;  // 13 pieces + the d pair + padding: eight rows' words hit 32 different banks
-inline size_t gemm_mma_q6_smem() { return 2 * ((size_t)64 * GM6_ASTRIDE + (size_t)GM_MT * GM_BSTRIDE + (size_t)GM_MT * 96); }
+inline size_t gemm_mma_q6_smem(int mt) { return 2 * ((size_t)64 * GM6_ASTRIDE + (size_t)mt * GM_BSTRIDE + (size_t)mt * 96); }
 
 __device__ __forceinline__ void mma_16816_s8(int (&c)[4], unsigned a0, unsigned a1, unsigned b0) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
@@ -695,17 +699,18 @@ __device__ __forceinline__ void mma_16816_s8(int (&c)[4], unsigned a0, unsigned 
                  : "r"(a0), "r"(a1), "r"(b0));
 }
 
+template <int MT>
 __global__ void __launch_bounds__(GM_THREADS, 2)
 k_gemm_mma_q6(const unsigned char* act_g, size_t act_stride, Mat A, int id_base, ChunkEpi epi, int M, float* partial) {
-    constexpr int RG = 4, NBW = 4, TB = Q6_TILE_BYTES;
+    constexpr int RG = 4, NBW = MT / 16, TB = Q6_TILE_BYTES;  // eight warps = four row groups x two token halves of MT / 2 tokens
     extern __shared__ __align__(128) unsigned char gm_smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gq = lane >> 2, tq = lane & 3;
     const int K = A.K, nb = A.nb;
     const int row0 = blockIdx.x * RG * 16;
     const int kparts = gridDim.y, kp = blockIdx.y;
     const int b_begin = (int)((long long)nb * kp / kparts), b_end = (int)((long long)nb * (kp + 1) / kparts);
-    constexpr size_t a_bytes = (size_t)RG * 16 * GM6_ASTRIDE, q_bytes = (size_t)GM_MT * GM_BSTRIDE, stage_b = a_bytes + q_bytes + (size_t)GM_MT * 96;
-    const int mt = min(GM_MT, M);
+    constexpr size_t a_bytes = (size_t)RG * 16 * GM6_ASTRIDE, q_bytes = (size_t)MT * GM_BSTRIDE, stage_b = a_bytes + q_bytes + (size_t)MT * 96;
+    const int mt = min(MT, M);
     auto stage_a = [&](int st_) { return gm_smem + (size_t)st_ * stage_b; };
     auto stage_q = [&](int st_) { return gm_smem + (size_t)st_ * stage_b + a_bytes; };
     auto stage_x = [&](int st_) { return gm_smem + (size_t)st_ * stage_b + a_bytes + q_bytes; };  // per token: 8 floats d8, 16 ints -32 * S16
@@ -719,13 +724,13 @@ k_gemm_mma_q6(const unsigned char* act_g, size_t act_stride, Mat A, int id_base,
             else cp_async4(dst + r * GM6_ASTRIDE + 208, tile + Q6_PIECES * 512 + ((f & 31) & ~1) * 2);  // d of this block and its neighbour
         }
         unsigned char* q = stage_q(st_);
-        for (int i = tid; i < GM_MT * 16; i += GM_THREADS) {
+        for (int i = tid; i < MT * 16; i += GM_THREADS) {
             const int t = i >> 4, c = i & 15;
             const bool in = t < mt;
             cp_async16(q + t * GM_BSTRIDE + c * 16, act_g + (size_t)(in ? t : 0) * act_stride + ((size_t)c * nb + b) * 16, in ? 16 : 0);
         }
         unsigned char* x = stage_x(st_);
-        for (int i = tid; i < GM_MT * 6; i += GM_THREADS) {
+        for (int i = tid; i < MT * 6; i += GM_THREADS) {
             const int t = i / 6, part = i - t * 6;  // parts 0, 1: d8[8 b ..]; 2 .. 5: s16n[16 b ..]
             const bool in = t < mt;
             const unsigned char* rec = act_g + (size_t)(in ? t : 0) * act_stride + K;
@@ -876,8 +881,10 @@ inline cudaError_t launch_gemm_mma_q6(cudaStream_t stream, int sms, const unsign
         kparts = std::min(std::min(4, ja.m.nb), std::max(1, sms / tiles));
         if ((size_t)kparts * M * rows > ws_floats) kparts = 1;
     }
-    cudaError_t r = launch_pdl(k_gemm_mma_q6, dim3(tiles, kparts), dim3(GM_THREADS), gemm_mma_q6_smem(), stream, act_g, act_stride, ja.m,
-                               ja.id_base, epi, M, ws);
+    cudaError_t r = M <= 16 ? launch_pdl(k_gemm_mma_q6<16>, dim3(tiles, kparts), dim3(GM_THREADS), gemm_mma_q6_smem(16), stream, act_g, act_stride,
+                                         ja.m, ja.id_base, epi, M, ws)
+                            : launch_pdl(k_gemm_mma_q6<64>, dim3(tiles, kparts), dim3(GM_THREADS), gemm_mma_q6_smem(64), stream, act_g, act_stride,
+                                         ja.m, ja.id_base, epi, M, ws);
     if (r != cudaSuccess || kparts == 1) return r;
     const int items = M * ((rows + 1) / 2);
     return launch_pdl(k_gemm_splitk_finish, dim3((items + 255) / 256), dim3(256), (size_t)0, stream, (const float*)ws, kparts, M, rows, ja.id_base, epi);

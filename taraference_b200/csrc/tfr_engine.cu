@@ -284,12 +284,15 @@ static void configure_kernels_once() {
     configure_kernel(k_gemm_q8<BlockQ4>, true);
     configure_kernel(k_gemm_q8<BlockQ6>, true);
     configure_kernel(k_gemm_q8<BlockQ8>, true);
-    configure_kernel(k_gemm_mma_q6, true);
+    configure_kernel(k_gemm_mma_q6<64>, true);
+    configure_kernel(k_gemm_mma_q6<16>, true);
     configure_kernel(k_gemm_splitk_finish, false);
-    configure_kernel(k_gemm_mma_q4<4, true>, true);
-    configure_kernel(k_gemm_mma_q4<1, true>, true);
-    configure_kernel(k_gemm_mma_q4<4, false>, true);
-    configure_kernel(k_gemm_mma_q4<1, false>, true);
+    configure_kernel(k_gemm_mma_q4<4, true, 64>, true);
+    configure_kernel(k_gemm_mma_q4<1, true, 64>, true);
+    configure_kernel(k_gemm_mma_q4<4, false, 64>, true);
+    configure_kernel(k_gemm_mma_q4<1, false, 64>, true);
+    configure_kernel(k_gemm_mma_q4<4, true, 16>, true);
+    configure_kernel(k_gemm_mma_q4<4, false, 16>, true);
     configure_kernel(k_attn_chunk<64>, true);
     configure_kernel(k_attn_chunk<128>, true);
     configure_kernel(k_attn_chunk<256>, true);
