@@ -1715,9 +1715,9 @@ static int forward_chunk(tfr_engine* e, const tfr_kv* kv, const int* tok, int M,
             const int rep = P.n_head / P.n_kv;
             // few tokens (verification batches): one query token per CTA, so that a row's serial walk over the keys is
             // a warp's only work; prompts: four tokens share every K/V tile
-            // prompt chunks with head sizes up to 128 run on the tensor cores: 128 (token, head) rows per CTA
-            const bool mma = M > CHUNK_VERIFY_MAX && attn_staged_mma(hd) && !getenv("TFR_ATTN_REGISTER_ROUTE");
-            a.QT = M <= CHUNK_VERIFY_MAX ? 1 : std::max(1, (mma ? ATTM_ROWS : ATTC_ROWS_MAX) / rep);
+            // batches from five tokens on with head sizes up to 128 run on the tensor cores: 128 (token, head) rows per CTA
+            const bool mma = M >= GEMM_MMA_MIN_TOKENS && attn_staged_mma(hd) && !getenv("TFR_ATTN_REGISTER_ROUTE");
+            a.QT = mma ? std::max(1, ATTM_ROWS / rep) : M <= CHUNK_VERIFY_MAX ? 1 : std::max(1, ATTC_ROWS_MAX / rep);
             const int q_tiles = (M + a.QT - 1) / a.QT;
             // key splits: enough CTAs for every SM, never less than 256 keys per split
             const int blocks256 = (pos0 + M + 255) / 256;
