@@ -9,12 +9,17 @@
 //   k_prep_rows      per token: RMSNorm (kernels/ops.cu:4-34) + Q8 quantiser (kernels/gemv.cu:16-65) -> global
 //   k_gemm_q8        every weight tile is brought on chip once per launch and dotted with the activations of up
 //                    to Mt tokens at a time; same block dots, row sums and epilogues as the batch-1 kernels
-//   k_attn_chunk     causal attention of a tile of query tokens x the query heads of one KV head over the f16 cache
+//                    (K rows, fp32-route V rows, Q8_0 matrices, batches of fewer than five tokens)
+//   k_gemm_mma_q4 / k_gemm_mma_q6   the other projections: the same integer sub-block dots as int8 tensor-core MMAs
+//                    over CTA tiles of rows x tokens, scale arithmetic on the accumulator fragments
+//   k_attn_chunk / k_attn_chunk_mma   causal attention of a tile of query tokens x the query heads of one KV head
+//                    over the f16 cache, on CUDA cores / on the tensor cores (head sizes up to 128)
 //   k_argmax_rows    greedy token of every row                                        (kernels/ops.cu:601-629)
 //
 // The projections use the arithmetic of the decode path (Q8 activations, integer block dots), not the reference's
 // prefill arithmetic (fp32 activations against dequantised weights): a prompt fed in chunks then leaves the same
-// K/V rows and residual stream as the same prompt fed token by token, up to the summation order inside attention.
+// K/V rows of layer 0, bit for bit, and below that the same cache and residual stream up to the summation order of
+// attention and of the tensor-core projections' row sums (fp32 rounding, now and then an int8 flip).
 #pragma once
 #include "tfr_attn.cuh"
 #include "tfr_kernels.cuh"
