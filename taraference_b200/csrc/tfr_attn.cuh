@@ -92,13 +92,11 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const unsigned (&a)[4],
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// An fp32 value travels through the f16 tensor-core path as a sum of two f16 terms: x = h1 + h2 / 2^12, where h2 is the
-// f16 image of 2^12 times what the first rounding dropped (the scaling keeps the small term out of the f16 subnormals):
-// 22 bits.  The products of the two terms are summed separately and joined with the power of two.  Measured against a
-// float64 evaluation the route is as accurate as the fp32 CUDA-core routes (1.3e-7 ... 2.6e-7 of the largest output
-// on seven shapes, against 1.3e-7 ... 2.2e-7); a third term changed neither figure and cost 3 % of a decode token.
-// x, y -> packed pairs, low half first.
-constexpr float SPLIT_UP = 4096.f, SPLIT_DOWN = 1.f / 4096.f;
+// An fp32 value travels through the f16 tensor-core path as a sum of two f16 terms, x = h1 + h2 with h2 the f16 image of
+// what the first rounding dropped: about 22 bits.  Measured against a float64 evaluation the route is as accurate as the
+// fp32 CUDA-core routes (1.0e-7 ... 2.9e-7 of the largest output on seven shapes, against 1.3e-7 ... 2.2e-7).  Scaling
+// the second term by 2^12 to keep it out of the f16 subnormals, or a third term, changed neither figure and cost 0.5 %
+// and 3 % of a decode token.  x, y -> packed pairs, low half first.
 __device__ __forceinline__ unsigned pack_f16x2(__half a, __half b) {
     const __half2 h = __halves2half2(a, b);
     return *reinterpret_cast<const unsigned*>(&h);
@@ -106,7 +104,7 @@ __device__ __forceinline__ unsigned pack_f16x2(__half a, __half b) {
 __device__ __forceinline__ void split2_f16x2(float x, float y, unsigned& t1, unsigned& t2) {
     const __half hx = __float2half_rn(x), hy = __float2half_rn(y);
     t1 = pack_f16x2(hx, hy);
-    t2 = pack_f16x2(__float2half_rn((x - __half2float(hx)) * SPLIT_UP), __float2half_rn((y - __half2float(hy)) * SPLIT_UP));
+    t2 = pack_f16x2(__float2half_rn(x - __half2float(hx)), __float2half_rn(y - __half2float(hy)));
 }
 
 // After the five butterfly steps lane L holds the sum over all lanes of v[L].
@@ -454,11 +452,11 @@ __global__ void __launch_bounds__(attn_threads(STAGED, HD)) k_attn_decode(AttnAr
                         ldsm_x4(af, kaddr + ks * 32);
                         // The tensor core adds into its accumulator with truncation: every 16-term product sum starts
                         // from zero and joins the running sum by a round-to-nearest add, which keeps fp32-level accuracy.
-                        float p1[4] = {0.f, 0.f, 0.f, 0.f}, p2[4] = {0.f, 0.f, 0.f, 0.f};
-                        mma_16816(p1, af, q1[ks][0], q1[ks][1]);
-                        mma_16816(p2, af, q2[ks][0], q2[ks][1]);
+                        float part[4] = {0.f, 0.f, 0.f, 0.f};
+                        mma_16816(part, af, q2[ks][0], q2[ks][1]);
+                        mma_16816(part, af, q1[ks][0], q1[ks][1]);
 #pragma unroll
-                        for (int i = 0; i < 4; i++) sacc[i] += p1[i] + p2[i] * SPLIT_DOWN;
+                        for (int i = 0; i < 4; i++) sacc[i] += part[i];
                     }
                 }
                 const bool on_a = key0 + gq < t1, on_b = key0 + gq + 8 < t1;
@@ -493,11 +491,11 @@ __global__ void __launch_bounds__(attn_threads(STAGED, HD)) k_attn_decode(AttnAr
                 for (int mb = 0; mb < KS; mb++) {
                     unsigned vf[4];
                     ldsm_x4_trans(vf, vaddr + mb * 32);
-                    float p1[4] = {0.f, 0.f, 0.f, 0.f}, p2[4] = {0.f, 0.f, 0.f, 0.f};
-                    mma_16816(p1, vf, b0h, b1h);
-                    mma_16816(p2, vf, b0l, b1l);
+                    float part[4] = {0.f, 0.f, 0.f, 0.f};
+                    mma_16816(part, vf, b0l, b1l);
+                    mma_16816(part, vf, b0h, b1h);
 #pragma unroll
-                    for (int i = 0; i < 4; i++) oacc[mb][i] += p1[i] + p2[i] * SPLIT_DOWN;
+                    for (int i = 0; i < 4; i++) oacc[mb][i] += part[i];
                 }
             }
             if (j == 0) prof_mark(7, a.prof_id);

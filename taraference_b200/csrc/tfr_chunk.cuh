@@ -1136,15 +1136,15 @@ __global__ void __launch_bounds__(ATTC_THREADS) k_attn_chunk_mma(AttnChunkArgs a
             for (int ks = 0; ks < KS; ks++) {
                 unsigned bf[4];  // [0], [1]: keys 0-7 of the block, dims + 0 / + 8; [2], [3]: keys 8-15
                 ldsm_x4(bf, kaddr + ks * 32);
-                float p0[4] = {0.f, 0.f, 0.f, 0.f}, p1[4] = {0.f, 0.f, 0.f, 0.f}, l0[4] = {0.f, 0.f, 0.f, 0.f}, l1[4] = {0.f, 0.f, 0.f, 0.f};
+                float p0[4] = {0.f, 0.f, 0.f, 0.f}, p1[4] = {0.f, 0.f, 0.f, 0.f};
+                mma_16816(p0, ql[ks], bf[0], bf[1]);
                 mma_16816(p0, qh[ks], bf[0], bf[1]);
-                mma_16816(l0, ql[ks], bf[0], bf[1]);
+                mma_16816(p1, ql[ks], bf[2], bf[3]);
                 mma_16816(p1, qh[ks], bf[2], bf[3]);
-                mma_16816(l1, ql[ks], bf[2], bf[3]);
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    sacc[2 * kb][i] += p0[i] + l0[i] * SPLIT_DOWN;
-                    sacc[2 * kb + 1][i] += p1[i] + l1[i] * SPLIT_DOWN;
+                    sacc[2 * kb][i] += p0[i];
+                    sacc[2 * kb + 1][i] += p1[i];
                 }
             }
         }
@@ -1199,15 +1199,15 @@ __global__ void __launch_bounds__(ATTC_THREADS) k_attn_chunk_mma(AttnChunkArgs a
             for (int nb = 0; nb < NB; nb += 2) {
                 unsigned bf[4];  // [0], [1]: dims 8 nb .. + 7, keys 0-7 / 8-15; [2], [3]: dims 8 (nb + 1) ..
                 ldsm_x4_trans(bf, vaddr + nb * 16);
-                float p0[4] = {0.f, 0.f, 0.f, 0.f}, p1[4] = {0.f, 0.f, 0.f, 0.f}, l0[4] = {0.f, 0.f, 0.f, 0.f}, l1[4] = {0.f, 0.f, 0.f, 0.f};
+                float p0[4] = {0.f, 0.f, 0.f, 0.f}, p1[4] = {0.f, 0.f, 0.f, 0.f};
+                mma_16816(p0, pl, bf[0], bf[1]);
                 mma_16816(p0, ph, bf[0], bf[1]);
-                mma_16816(l0, pl, bf[0], bf[1]);
+                mma_16816(p1, pl, bf[2], bf[3]);
                 mma_16816(p1, ph, bf[2], bf[3]);
-                mma_16816(l1, pl, bf[2], bf[3]);
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    oacc[nb][i] += p0[i] + l0[i] * SPLIT_DOWN;
-                    oacc[nb + 1][i] += p1[i] + l1[i] * SPLIT_DOWN;
+                    oacc[nb][i] += p0[i];
+                    oacc[nb + 1][i] += p1[i];
                 }
             }
         }
