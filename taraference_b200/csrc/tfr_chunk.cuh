@@ -671,15 +671,21 @@ inline cudaError_t launch_gemm_mma_q4(cudaStream_t stream, int sms, const unsign
     const int rows = ja.m.N;
     const bool big = (rows + 63) / 64 >= sms;
     const bool few = M <= 16 && big;  // a token tile of 16: every warp of a 64-row CTA has a token block
-    const int rg = big ? 4 : 1, mt_tile = few ? 16 : GM_MT;
+    // 64-row tiles that do not divide evenly over the SMs leave some SMs twice the rows of the others (11 008 rows: 172
+    // tiles on 148 SMs): 32-row tiles then even the load out at a little more unpacking per MMA
+    const int t64 = (rows + 63) / 64, t32 = (rows + 31) / 32;
+    const bool mid = big && !few && ((t32 + sms - 1) / sms) * 32 < ((t64 + sms - 1) / sms) * 64;
+    const int rg = mid ? 2 : big ? 4 : 1, mt_tile = few ? 16 : GM_MT;
     const dim3 grid((rows + 16 * rg - 1) / (16 * rg)), block(GM_THREADS);
     const size_t smem = gemm_mma_smem(rg, zip, mt_tile);
     for (int m_base = 0; m_base < M; m_base += mt_tile) {
         cudaError_t r;
         if (zip) r = few   ? launch_pdl(k_gemm_mma_q4<4, true, 16>, grid, block, smem, stream, act_g, act_stride, ja.m, jb.m, ja.id_base, epi, M, m_base)
+                     : mid ? launch_pdl(k_gemm_mma_q4<2, true, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, jb.m, ja.id_base, epi, M, m_base)
                      : big ? launch_pdl(k_gemm_mma_q4<4, true, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, jb.m, ja.id_base, epi, M, m_base)
                            : launch_pdl(k_gemm_mma_q4<1, true, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, jb.m, ja.id_base, epi, M, m_base);
         else r = few   ? launch_pdl(k_gemm_mma_q4<4, false, 16>, grid, block, smem, stream, act_g, act_stride, ja.m, Mat{}, ja.id_base, epi, M, m_base)
+                 : mid ? launch_pdl(k_gemm_mma_q4<2, false, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, Mat{}, ja.id_base, epi, M, m_base)
                  : big ? launch_pdl(k_gemm_mma_q4<4, false, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, Mat{}, ja.id_base, epi, M, m_base)
                        : launch_pdl(k_gemm_mma_q4<1, false, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, Mat{}, ja.id_base, epi, M, m_base);
         if (r != cudaSuccess) return r;

@@ -292,6 +292,8 @@ static void configure_kernels_once() {
     configure_kernel(k_gemm_mma_q4<4, false, 64>, true);
     configure_kernel(k_gemm_mma_q4<1, false, 64>, true);
     configure_kernel(k_gemm_mma_q4<4, true, 16>, true);
+    configure_kernel(k_gemm_mma_q4<2, true, 64>, true);
+    configure_kernel(k_gemm_mma_q4<2, false, 64>, true);
     configure_kernel(k_gemm_mma_q4<4, false, 16>, true);
     configure_kernel(k_attn_chunk<64>, true);
     configure_kernel(k_attn_chunk<128>, true);
