@@ -24,7 +24,15 @@
  * operators and the read-only taps (tfr_debug_read).  libtarafer_b200_aids.so (-DTFR_TEST_AIDS) adds what only tests,
  * the timeline tool and the benchmark's model builder need: in-kernel timeline probes, the integer-contract taps, the
  * KV-store rounding as an operator and the synthetic K-quant quantiser.  Declarations of the second kind sit inside
- * #ifdef TFR_TEST_AIDS below. */
+ * #ifdef TFR_TEST_AIDS below.
+ *
+ * Environment variables the library reads (test and measurement aids; unset in normal use):
+ *   TFR_ATTN_REGISTER_ROUTE=1   decode attention on short caches and the attention of prompt chunks stay on the CUDA-core
+ *                               kernels for every head size (default: tensor cores for head sizes up to 128);
+ *   TFR_GEMM_DP4A=1             the projections of prompt chunks and verification batches stay on the dp4a kernel
+ *                               (default: int8 tensor-core MMAs for Q4_K / Q6_K matrices from five tokens on);
+ *   TFR_LOOP_SLOTS, TFR_LOOP_LPB, TFR_LOOP_PBUF, TFR_LOOP_ATTN_KEYS, TFR_LOOP_ATTN_INLINE
+ *                               sizes of the opt-in persistent decode loop (tfr_set_decode_path). */
 #ifdef __cplusplus
 extern "C" {
 #endif
