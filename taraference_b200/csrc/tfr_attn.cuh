@@ -553,6 +553,20 @@ __global__ void __launch_bounds__(attn_threads(STAGED, HD)) k_attn_decode(AttnAr
                     }
                 }
             }
+            if (S_eff == 1) {
+                // single split: the folded head is the output (the merge of one partial is the identity)
+                if (h < rep) {
+                    const int hg = g * rep + h;
+#pragma unroll
+                    for (int d = 0; d < DPL; d++) {
+                        float r = acc[d] / fmaxf(l, 1e-20f);
+                        if (a.gate) r *= 1.f / (1.f + expf(-a.gate[hg * HD + lane * DPL + d]));
+                        a.out[hg * HD + lane * DPL + d] = r;
+                    }
+                }
+                prof_mark(5, a.prof_id);
+                return;
+            }
 #pragma unroll
             for (int d = 0; d < DPL; d++) {
                 ored[0][h][lane * DPL + d] = acc[d];
