@@ -488,11 +488,12 @@ inline cudaError_t launch_gemm(cudaStream_t stream, int grid, const unsigned cha
 // accm are summed along k in registers.  That order of a row's sum differs from reduce_rows' butterfly: results agree
 // with the decode kernels' to fp32 rounding, not bit for bit.
 constexpr int GM_MT = 64;         // tokens per CTA tile (16 for batches of up to 16 tokens)
-constexpr int GM_ASTRIDE = 176;   // bytes per staged weight block: eight rows' four words hit 32 different banks
-constexpr int GM_BSTRIDE = 272;   // bytes per staged token (256 int8 + 16)
+constexpr int GM_ASTRIDE = 160;   // bytes per staged Q4_K block (144 + 16): 8 words modulo 32, four rows' 8-byte reads of four lanes each fill the banks
+constexpr int GM4_BSTRIDE = 288;  // bytes per staged token in the Q4_K kernel (256 int8 + 32): 8 words modulo 32 as well
+constexpr int GM_BSTRIDE = 272;   // bytes per staged token in the Q6_K kernel (256 int8 + 16): 4 words modulo 32 for its 4-byte reads
 constexpr int GM_THREADS = 256;
 constexpr int GEMM_MMA_MIN_TOKENS = 5;   // smaller batches keep the dp4a kernel
-inline size_t gemm_mma_stage_bytes(int rg, bool zip, int mt) { return (size_t)rg * 16 * GM_ASTRIDE * (zip ? 2 : 1) + (size_t)mt * GM_BSTRIDE + (size_t)mt * 64; }
+inline size_t gemm_mma_stage_bytes(int rg, bool zip, int mt) { return (size_t)rg * 16 * GM_ASTRIDE * (zip ? 2 : 1) + (size_t)mt * GM4_BSTRIDE + (size_t)mt * 64; }
 inline size_t gemm_mma_smem(int rg, bool zip, int mt) { return 2 * gemm_mma_stage_bytes(rg, zip, mt); }
 
 __device__ __forceinline__ void mma_16832_u8s8(int (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
@@ -514,12 +515,12 @@ k_gemm_mma_q4(const unsigned char* act_g, size_t act_stride, Mat A, Mat B2, int 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gq = lane >> 2, tq = lane & 3;
     const int K = A.K, nb = A.nb;
     const int row0 = blockIdx.x * RG * 16;
-    const size_t a_bytes = (size_t)RG * 16 * GM_ASTRIDE, stage_b = a_bytes * NMAT + (size_t)MT * GM_BSTRIDE + (size_t)MT * 64;
+    const size_t a_bytes = (size_t)RG * 16 * GM_ASTRIDE, stage_b = a_bytes * NMAT + (size_t)MT * GM4_BSTRIDE + (size_t)MT * 64;
     const int mt = min(MT, M - m_base);       // tokens of this launch's token tile
     const unsigned char* act_t = act_g + (size_t)m_base * act_stride;
     auto stage_a = [&](int st_, int mat) { return gm_smem + (size_t)st_ * stage_b + (size_t)mat * a_bytes; };
     auto stage_q = [&](int st_) { return gm_smem + (size_t)st_ * stage_b + a_bytes * NMAT; };
-    auto stage_s = [&](int st_) { return reinterpret_cast<float*>(gm_smem + (size_t)st_ * stage_b + a_bytes * NMAT + (size_t)MT * GM_BSTRIDE); };
+    auto stage_s = [&](int st_) { return reinterpret_cast<float*>(gm_smem + (size_t)st_ * stage_b + a_bytes * NMAT + (size_t)MT * GM4_BSTRIDE); };
     auto issue = [&](int b, int st_) {
 #pragma unroll
         for (int mat = 0; mat < NMAT; mat++) {
@@ -535,7 +536,7 @@ k_gemm_mma_q4(const unsigned char* act_g, size_t act_stride, Mat A, Mat B2, int 
         for (int i = tid; i < MT * 16; i += GM_THREADS) {
             const int t = i >> 4, c = i & 15;
             const bool in = t < mt;
-            cp_async16(q + t * GM_BSTRIDE + c * 16, act_t + (size_t)(in ? t : 0) * act_stride + ((size_t)c * nb + b) * 16, in ? 16 : 0);
+            cp_async16(q + t * GM4_BSTRIDE + c * 16, act_t + (size_t)(in ? t : 0) * act_stride + ((size_t)c * nb + b) * 16, in ? 16 : 0);
         }
         float* sc = stage_s(st_);
         for (int i = tid; i < MT * 4; i += GM_THREADS) {
@@ -595,21 +596,23 @@ k_gemm_mma_q4(const unsigned char* act_g, size_t act_stride, Mat A, Mat B2, int 
                     d8[c][0] = x0.x, d8[c][1] = x0.y, d8[c][2] = x0.z, d8[c][3] = x0.w, d8[c][4] = x1.x, d8[c][5] = x1.y, d8[c][6] = x1.z, d8[c][7] = x1.w;
                     ds[c][0] = y0.x, ds[c][1] = y0.y, ds[c][2] = y0.z, ds[c][3] = y0.w, ds[c][4] = y1.x, ds[c][5] = y1.y, ds[c][6] = y1.z, ds[c][7] = y1.w;
                 }
-                const unsigned char* qt = qs + (size_t)(tok0 + gq) * GM_BSTRIDE + 4 * tq;  // B operand: token tok0 + gq
+                // The order of a sub-block's 32 products is free: MMA k slots 4 tq .. and 16 + 4 tq .. take elements
+                // 8 tq .. 8 tq + 3 and 8 tq + 4 .. 8 tq + 7, so a lane's two weight words and two activation words are
+                // one 8-byte read each.
+                const unsigned char* qt = qs + (size_t)(tok0 + gq) * GM4_BSTRIDE + 8 * tq;  // B operand: token tok0 + gq
                 float acc[4] = {0.f, 0.f, 0.f, 0.f}, accm[4] = {0.f, 0.f, 0.f, 0.f};  // [0], [1]: row gq, tokens 2 tq, + 1; [2], [3]: row gq + 8
 #pragma unroll
                 for (int t = 0; t < 4; t++) {
-                    unsigned w[4];
-                    w[0] = *reinterpret_cast<const unsigned*>(ar + (1 + 2 * t) * 16 + tq * 4);
-                    w[1] = *reinterpret_cast<const unsigned*>(ar + 8 * GM_ASTRIDE + (1 + 2 * t) * 16 + tq * 4);
-                    w[2] = *reinterpret_cast<const unsigned*>(ar + (2 + 2 * t) * 16 + tq * 4);
-                    w[3] = *reinterpret_cast<const unsigned*>(ar + 8 * GM_ASTRIDE + (2 + 2 * t) * 16 + tq * 4);
+                    const uint2 wa = *reinterpret_cast<const uint2*>(ar + (1 + 2 * t) * 16 + tq * 8);                   // row gq
+                    const uint2 wb = *reinterpret_cast<const uint2*>(ar + 8 * GM_ASTRIDE + (1 + 2 * t) * 16 + tq * 8);  // row gq + 8
+                    const unsigned w[4] = {wa.x, wb.x, wa.y, wb.y};
 #pragma unroll
                     for (int half = 0; half < 2; half++) {
                         const int j = 2 * t + half;
                         const unsigned mask = half ? 0xf0f0f0f0u : 0x0f0f0f0fu;
                         const unsigned af[4] = {w[0] & mask, w[1] & mask, w[2] & mask, w[3] & mask};
-                        const unsigned b0 = *reinterpret_cast<const unsigned*>(qt + j * 32), b1 = *reinterpret_cast<const unsigned*>(qt + j * 32 + 16);
+                        const uint2 bw = *reinterpret_cast<const uint2*>(qt + j * 32);
+                        const unsigned b0 = bw.x, b1 = bw.y;
                         int c[4] = {0, 0, 0, 0};
                         mma_16832_u8s8(c, af, b0, b1);
                         if (half) {
