@@ -307,10 +307,12 @@ k_gemm_q8(const unsigned char* act_g, const float* xn, RowJob ja, RowJob jb, F32
             }
         }
     }
+    if (n_jobs == 0 && (f32_done || !fseg.m.data)) return;  // nothing on the Q8 route in this CTA, and no copy was requested
     for (int grp_i = 0; grp_i < n_groups; grp_i++) {
         const int m0 = grp_i * Mt, mt = min(Mt, g.M - m0);
-        // the Q8 activations of tokens m0 .. m0 + mt - 1
-        {
+        // the Q8 activations of tokens m0 .. m0 + mt - 1 (a CTA without tiles, e.g. in a launch of fp32-route rows alone,
+        // has no use for them)
+        if (n_jobs > 0) {
             const int per = g.act_b16 >> 4;
             for (int i = tid; i < mt * per; i += GEMV_THREADS) {
                 const int m = i / per, r = i - m * per;

@@ -29,6 +29,17 @@ def _free_running(cfg):
     return min(cfg["n_layer"], 5) * TF_WORST
 
 
+def _k_rows_agree(ka, kb):
+    """K rows of layer 0 from two routes of which one ran the K projection on the tensor cores: the integer sub-block
+    sums are the same, the fp32 row sums differ in order, so a value now and then lands on the other side of an f16
+    rounding boundary (where RoPE subtracts two close products, a few steps of a small value).  Measured on the four
+    shapes: 0.1 - 0.4 % of the values move, by at most 2.1e-4 of the largest value (one f16 step of it is 4.9e-4)."""
+    if np.array_equal(ka, kb):
+        return True
+    f = lambda a: a.view(np.float16).astype(np.float32)
+    return (ka != kb).mean() < 1e-2 and _rel(f(kb), f(ka)) < 5e-4
+
+
 def _margin(logits):
     top = np.sort(logits)[-2:]
     return float(top[1] - top[0])
@@ -45,8 +56,9 @@ def _cache_rows(m, kv, cfg, layer, n_pos):
 @pytest.mark.parametrize("chunk", [5, 16, 64])
 def test_chunked_prompt_equals_step_by_step(E, cfg, chunk):
     """A prompt fed in chunks leaves the cache and the next-token logits of the same prompt fed token by token.
-    The projections are the same arithmetic, so layer 0 (no attention upstream) is bit-identical; deeper layers
-    differ by the summation order inside attention (fp32 rounding level, now and then an int8 flip)."""
+    The projections compute the same integer sub-block sums, so layer 0 (no attention upstream) leaves the same V rows
+    bit for bit and the same K rows up to an f16 step now and then; deeper layers differ by the summation order inside
+    attention and the tensor-core projections (fp32 rounding level, now and then an int8 flip)."""
     tens = S.make_dense_model(cfg, seed=21)
     rng = np.random.default_rng(7)
     n = 45
@@ -70,7 +82,9 @@ def test_chunked_prompt_equals_step_by_step(E, cfg, chunk):
         assert launches_chunk < launches_step / 2, (launches_chunk, launches_step)
     k0a, v0a = _cache_rows(m, kv_a, cfg, 0, n)
     k0b, v0b = _cache_rows(m, kv_b, cfg, 0, n)
-    assert np.array_equal(k0a, k0b) and np.array_equal(v0a, v0b)
+    # layer 0 has no attention upstream: the fp32-route V rows keep the decode arithmetic bit for bit, the K rows run on
+    # the tensor cores from five tokens on
+    assert np.array_equal(v0a, v0b) and _k_rows_agree(k0a, k0b)
     last = cfg["n_layer"] - 1
     kla, vla = _cache_rows(m, kv_a, cfg, last, n)
     klb, vlb = _cache_rows(m, kv_b, cfg, last, n)
@@ -111,7 +125,7 @@ def test_long_chunked_prompt_with_key_splits(E, cfg):
         logits_b = m.current_logits()
         k0a, v0a = _cache_rows(m, kv_a, cfg, 0, n)
         k0b, v0b = _cache_rows(m, kv_b, cfg, 0, n)
-        assert np.array_equal(k0a, k0b) and np.array_equal(v0a, v0b)  # layer 0 has no attention upstream
+        assert np.array_equal(v0a, v0b) and _k_rows_agree(k0a, k0b)  # layer 0 has no attention upstream
         klb, vlb = _cache_rows(m, kv_b, cfg, last, n)
         assert _rel(f16(klb), f16(kla)) < _free_running(cfg) and _rel(f16(vlb), f16(vla)) < _free_running(cfg), chunk
         assert _rel(logits_b, logits_a) < _free_running(cfg), chunk
@@ -144,7 +158,7 @@ def test_tensor_core_projections_match_the_dp4a_projections(E, cfg, monkeypatch)
         logits_b = m.current_logits()
         ka, va = _cache_rows(m, kv_a, cfg, 0, n)
         kb, vb = _cache_rows(m, kv_b, cfg, 0, n)
-        assert np.array_equal(ka, kb) and np.array_equal(va, vb)  # K and V rows keep the decode arithmetic on both routes
+        assert np.array_equal(va, vb) and _k_rows_agree(ka, kb)  # V rows keep the decode arithmetic on both routes
         rels.append(_rel(logits_b, logits_a))
         assert rels[-1] < TF_WORST, (n, rels)
         assert tok_a == tok_b or _margin(logits_a) <= 1e-2
