@@ -508,15 +508,21 @@ __device__ __forceinline__ void mma_16832_u8s8(int (&c)[4], const unsigned (&a)[
 // pair-ordered epilogues (store / Q, K rows with RoPE), whose two rows meet by a shuffle.
 template <int RG, bool ZIP, int MT>
 __global__ void __launch_bounds__(GM_THREADS, 2)
-k_gemm_mma_q4(const unsigned char* act_g, size_t act_stride, Mat A, Mat B2, int id_base, ChunkEpi epi, int M, int m_base) {
+k_gemm_mma_q4(const unsigned char* act_g, size_t act_stride, Mat A1, Mat B2, int id_base1, int id_base2, ChunkEpi epi, int M, int m_base) {
     constexpr int NBW = MT * RG / 64;            // 8-token blocks per warp: 8 warps = RG row groups x (8 / RG) token parts of MT * RG / 8 tokens
     static_assert(NBW >= 1, "a token part holds at least one block of eight tokens");
     constexpr int NMAT = ZIP ? 2 : 1;
     constexpr int TB = Q4_TILE_BYTES;
     extern __shared__ __align__(128) unsigned char gm_smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gq = lane >> 2, tq = lane & 3;
+    // Without ZIP a second matrix of the same K may follow the first in the grid (the K rows behind the Q rows: one launch
+    // instead of two): a CTA's rows lie in one of them.
+    const int tiles1 = (A1.N + RG * 16 - 1) / (RG * 16);
+    const bool second = !ZIP && B2.data != nullptr && (int)blockIdx.x >= tiles1;
+    const Mat A = second ? B2 : A1;
+    const int id_base = second ? id_base2 : id_base1;
     const int K = A.K, nb = A.nb;
-    const int row0 = blockIdx.x * RG * 16;
+    const int row0 = (second ? (int)blockIdx.x - tiles1 : (int)blockIdx.x) * RG * 16;
     const size_t a_bytes = (size_t)RG * 16 * GM_ASTRIDE, stage_b = a_bytes * NMAT + (size_t)MT * GM4_BSTRIDE + (size_t)MT * 64;
     const int mt = min(MT, M - m_base);       // tokens of this launch's token tile
     const unsigned char* act_t = act_g + (size_t)m_base * act_stride;
@@ -668,12 +674,13 @@ k_gemm_mma_q4(const unsigned char* act_g, size_t act_stride, Mat A, Mat B2, int 
     }
 }
 
-// Launches k_gemm_mma_q4 for one matrix (pair-ordered epilogues) or a gate / up pair (ZIP).  Row tiles of 64 when
+// Launches k_gemm_mma_q4 for one matrix or two in a row (pair-ordered epilogues) or a gate / up pair (ZIP).  Row tiles of 64 when
 // that still gives every SM a CTA, of 16 otherwise (the output and down projections have 2 048 rows).
 inline cudaError_t launch_gemm_mma_q4(cudaStream_t stream, int sms, const unsigned char* act_g, size_t act_stride, int M, const RowJob& ja,
                                       const RowJob& jb, const ChunkEpi& epi) {
     const bool zip = epi.kind == CEPI_SILU;
-    const int rows = ja.m.N;
+    const bool two = !zip && jb.m.data != nullptr;  // a second matrix behind the first (Q rows, then K rows)
+    const int rows = ja.m.N + (two ? jb.m.N : 0);
     const bool big = (rows + 63) / 64 >= sms;
     const bool few = M <= 16 && big;  // a token tile of 16: every warp of a 64-row CTA has a token block
     // 64-row tiles that do not divide evenly over the SMs leave some SMs twice the rows of the others (11 008 rows: 172
@@ -681,18 +688,21 @@ inline cudaError_t launch_gemm_mma_q4(cudaStream_t stream, int sms, const unsign
     const int t64 = (rows + 63) / 64, t32 = (rows + 31) / 32;
     const bool mid = big && !few && ((t32 + sms - 1) / sms) * 32 < ((t64 + sms - 1) / sms) * 64;
     const int rg = mid ? 2 : big ? 4 : 1, mt_tile = few ? 16 : GM_MT;
-    const dim3 grid((rows + 16 * rg - 1) / (16 * rg)), block(GM_THREADS);
+    const int tile_rows = 16 * rg;
+    const dim3 grid((ja.m.N + tile_rows - 1) / tile_rows + (two ? (jb.m.N + tile_rows - 1) / tile_rows : 0)), block(GM_THREADS);
     const size_t smem = gemm_mma_smem(rg, zip, mt_tile);
+    const Mat m2 = (zip || two) ? jb.m : Mat{};
+    const int id1 = ja.id_base, id2 = two ? jb.id_base : 0;
     for (int m_base = 0; m_base < M; m_base += mt_tile) {
         cudaError_t r;
-        if (zip) r = few   ? launch_pdl(k_gemm_mma_q4<4, true, 16>, grid, block, smem, stream, act_g, act_stride, ja.m, jb.m, ja.id_base, epi, M, m_base)
-                     : mid ? launch_pdl(k_gemm_mma_q4<2, true, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, jb.m, ja.id_base, epi, M, m_base)
-                     : big ? launch_pdl(k_gemm_mma_q4<4, true, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, jb.m, ja.id_base, epi, M, m_base)
-                           : launch_pdl(k_gemm_mma_q4<1, true, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, jb.m, ja.id_base, epi, M, m_base);
-        else r = few   ? launch_pdl(k_gemm_mma_q4<4, false, 16>, grid, block, smem, stream, act_g, act_stride, ja.m, Mat{}, ja.id_base, epi, M, m_base)
-                 : mid ? launch_pdl(k_gemm_mma_q4<2, false, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, Mat{}, ja.id_base, epi, M, m_base)
-                 : big ? launch_pdl(k_gemm_mma_q4<4, false, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, Mat{}, ja.id_base, epi, M, m_base)
-                       : launch_pdl(k_gemm_mma_q4<1, false, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, Mat{}, ja.id_base, epi, M, m_base);
+        if (zip) r = few   ? launch_pdl(k_gemm_mma_q4<4, true, 16>, grid, block, smem, stream, act_g, act_stride, ja.m, m2, id1, id2, epi, M, m_base)
+                     : mid ? launch_pdl(k_gemm_mma_q4<2, true, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, m2, id1, id2, epi, M, m_base)
+                     : big ? launch_pdl(k_gemm_mma_q4<4, true, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, m2, id1, id2, epi, M, m_base)
+                           : launch_pdl(k_gemm_mma_q4<1, true, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, m2, id1, id2, epi, M, m_base);
+        else r = few   ? launch_pdl(k_gemm_mma_q4<4, false, 16>, grid, block, smem, stream, act_g, act_stride, ja.m, m2, id1, id2, epi, M, m_base)
+                 : mid ? launch_pdl(k_gemm_mma_q4<2, false, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, m2, id1, id2, epi, M, m_base)
+                 : big ? launch_pdl(k_gemm_mma_q4<4, false, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, m2, id1, id2, epi, M, m_base)
+                       : launch_pdl(k_gemm_mma_q4<1, false, 64>, grid, block, smem, stream, act_g, act_stride, ja.m, m2, id1, id2, epi, M, m_base);
         if (r != cudaSuccess) return r;
     }
     return cudaSuccess;

@@ -1700,9 +1700,7 @@ static int forward_chunk(tfr_engine* e, const tfr_kv* kv, const int* tok, int M,
             if (M >= GEMM_MMA_MIN_TOKENS && !getenv("TFR_GEMM_DP4A")) {
                 // batches from five tokens on: the Q and K rows on the tensor cores (same integer sub-block sums, row sums
                 // along k); the fp32-route V rows keep the decode kernels' arithmetic bit for bit
-                if (launch_gemm_mma_q4(s, cap, e->cact, e->cact_stride, M, jq, RowJob{}, ep) != cudaSuccess) return -1;
-                n++;
-                if (launch_gemm_mma_q4(s, cap, e->cact, e->cact_stride, M, jk, RowJob{}, ep) != cudaSuccess) return -1;
+                if (launch_gemm_mma_q4(s, cap, e->cact, e->cact_stride, M, jq, jk, ep) != cudaSuccess) return -1;
                 n++;
                 if (launch_gemm<BlockQ4>(s, cap, e->cact, e->cact_stride, e->cxn, M, RowJob{}, RowJob{}, fseg, ep, K, e->st) != cudaSuccess) return -1;
             } else if (launch_gemm<BlockQ4>(s, cap, e->cact, e->cact_stride, e->cxn, M, jq, jk, fseg, ep, K, e->st) != cudaSuccess) {
