@@ -480,8 +480,8 @@ inline cudaError_t launch_gemm(cudaStream_t stream, int grid, const unsigned cha
 
 // ------------------------------------------------------------------ the chunk GEMM on the tensor cores (Q4_K)
 
-// CTA tile = 16 * RG rows x 64 tokens, k-loop over the 256-weight blocks, both operands double-buffered in shared
-// memory by 16-byte asynchronous copies: the 144-byte block of (row r, block b) is nine pieces of the tiled layout, the
+// CTA tile = 16 * RG rows x 64 tokens, k-loop over the 256-weight blocks, both operands staged in shared memory three
+// or four k steps deep by 16-byte asynchronous copies: the 144-byte block of (row r, block b) is nine pieces of the tiled layout, the
 // tokens' int8 groups of block b are sixteen pieces of their activation record, their group scales and scaled sums four
 // more.  A warp owns 16 rows and NBW blocks of eight tokens.  The sub-block dots I_j = sum nibble * q8 (kernels/gemv.cu:
 // 71-130) run as m16n8k32 u8 x s8 MMAs — the low nibbles of a 32-byte stretch are sub-block 2 t, the high nibbles, left
@@ -496,7 +496,10 @@ constexpr int GM_BSTRIDE = 272;   // bytes per staged token in the Q6_K kernel (
 constexpr int GM_THREADS = 256;
 constexpr int GEMM_MMA_MIN_TOKENS = 5;   // smaller batches keep the dp4a kernel
 inline size_t gemm_mma_stage_bytes(int rg, bool zip, int mt) { return (size_t)rg * 16 * GM_ASTRIDE * (zip ? 2 : 1) + (size_t)mt * GM4_BSTRIDE + (size_t)mt * 64; }
-inline size_t gemm_mma_smem(int rg, bool zip, int mt) { return 2 * gemm_mma_stage_bytes(rg, zip, mt); }
+// Stages of the copy pipeline: the 16-row tiles do little per k step and need the copies of three steps in flight to hide
+// a trip to L2; the others take three stages (one barrier per k step).
+__host__ __device__ constexpr int gemm_mma_stages(int rg) { return rg == 1 ? 4 : 3; }
+inline size_t gemm_mma_smem(int rg, bool zip, int mt) { return gemm_mma_stages(rg) * gemm_mma_stage_bytes(rg, zip, mt); }
 
 __device__ __forceinline__ void mma_16832_u8s8(int (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -529,7 +532,12 @@ k_gemm_mma_q4(const unsigned char* act_g, size_t act_stride, Mat A1, Mat B2, int
     auto stage_a = [&](int st_, int mat) { return gm_smem + (size_t)st_ * stage_b + (size_t)mat * a_bytes; };
     auto stage_q = [&](int st_) { return gm_smem + (size_t)st_ * stage_b + a_bytes * NMAT; };
     auto stage_s = [&](int st_) { return reinterpret_cast<float*>(gm_smem + (size_t)st_ * stage_b + a_bytes * NMAT + (size_t)MT * GM4_BSTRIDE); };
+    constexpr int NST = gemm_mma_stages(RG);
     auto issue = [&](int b, int st_) {
+        if (b >= nb) {
+            cp_async_commit();  // an empty group keeps the count of the wait below
+            return;
+        }
 #pragma unroll
         for (int mat = 0; mat < NMAT; mat++) {
             const uint8_t* data = mat ? B2.data : A.data;
@@ -565,16 +573,13 @@ k_gemm_mma_q4(const unsigned char* act_g, size_t act_stride, Mat A1, Mat B2, int
         for (int n = 0; n < NBW; n++)
 #pragma unroll
             for (int i = 0; i < 4; i++) total[mat][n][i] = 0.f;
-    issue(0, 0);
+#pragma unroll
+    for (int p = 0; p < NST - 1; p++) issue(p, p);
     for (int b = 0; b < nb; b++) {
-        const int st_ = b & 1;
-        if (b + 1 < nb) {
-            issue(b + 1, st_ ^ 1);
-            cp_async_wait_group<1>();
-        } else {
-            cp_async_wait_all();
-        }
-        __syncthreads();
+        const int st_ = b % NST;
+        cp_async_wait_group<NST - 2>();  // this thread's pieces of step b
+        __syncthreads();                 // everybody's pieces, and everybody is done with step b - 1
+        issue(b + NST - 1, (b + NST - 1) % NST);  // into the stage step b - 1 has just left
         const unsigned char* qs = stage_q(st_);
         const float* scs = stage_s(st_);
 #pragma unroll
@@ -645,8 +650,8 @@ k_gemm_mma_q4(const unsigned char* act_g, size_t act_stride, Mat A1, Mat B2, int
                     for (int cc = 0; cc < 2; cc++) total[mat][n][2 * r + cc] += dd[r].x * acc[2 * r + cc] - dd[r].y * accm[2 * r + cc];
             }
         }
-        __syncthreads();  // the stage is refilled at the top of the next iteration but one
     }
+    cp_async_wait_all();
     // ---- epilogue: a lane holds rows gq, gq + 8 of its group x tokens 2 tq, 2 tq + 1 of its token blocks
 #pragma unroll
     for (int n = 0; n < NBW; n++) {
