@@ -168,6 +168,52 @@ def test_tensor_core_projections_match_the_dp4a_projections(E, cfg, monkeypatch)
     m.destroy()
 
 
+def test_tensor_core_projections_on_a_wide_ffn(E, monkeypatch):
+    """The tile shapes only wide matrices reach: n_ff = 11 008 gives gate / up more 64-row tiles than SMs (32-row tiles
+    for a prompt chunk, 64-row tiles x 16-token tiles for a verification batch) and a down projection of 43 blocks per
+    row whose k range is cut in four parts.  One layer, against the dp4a route and against feeding token by token."""
+    cfg = dict(arch="qwen2", n_layer=1, n_embd=512, n_head=8, n_kv=2, head_dim=64, n_ff=11008, n_vocab=1000,
+               rope_theta=1e6, eps=1e-6, tied=True, qkv_bias=True)
+    tens = S.make_dense_model(cfg, seed=26)
+    rng = np.random.default_rng(12)
+    m = E.CudaModel.load_with(cfg, tens)
+    n = 45
+    prompt = [int(t) for t in rng.integers(0, cfg["n_vocab"], n)]
+    kv = m.alloc_kv(64)
+    m.set_prefill_chunk(0)
+    tok_step = m.forward_greedy(prompt, kv)
+    logits_step = m.current_logits()
+    rels = []
+    for chunk in (64, 16):
+        m.set_prefill_chunk(chunk)
+        monkeypatch.setenv("TFR_GEMM_DP4A", "1")
+        kv.len = 0
+        m.forward_greedy(prompt, kv)
+        logits_dp4a = m.current_logits()
+        monkeypatch.delenv("TFR_GEMM_DP4A")
+        kv.len = 0
+        tok = m.forward_greedy(prompt, kv)
+        logits = m.current_logits()
+        rels.append((_rel(logits, logits_dp4a), _rel(logits, logits_step)))
+        assert rels[-1][0] < TF_WORST and rels[-1][1] < TF_WORST, (chunk, rels)
+        assert tok == tok_step or _margin(logits_step) <= 1e-2
+    assert min(r[0] for r in rels) < 1e-4, rels  # without a flip the routes agree to fp32 rounding
+    # a verification batch of nine tokens (16-token tiles) against the same tokens one by one
+    v = [int(t) for t in rng.integers(0, cfg["n_vocab"], 9)]
+    m.set_prefill_chunk(64)
+    kv.len = n
+    got = m.forward_greedy_all(v, kv)
+    lg = m.current_logits()
+    m.set_prefill_chunk(0)
+    kv.len = n
+    want = m.forward_greedy_all(v, kv)
+    lw = m.current_logits()
+    assert _rel(lg, lw) < TF_WORST
+    assert got[-1] == want[-1] or _margin(lw) <= 1e-2
+    kv.free()
+    m.destroy()
+
+
 @pytest.mark.parametrize("cfg", CFGS, ids=IDS)
 def test_chunked_prompt_vs_cpu_oracle(E, oracle, cfg):
     tens = S.make_dense_model(cfg, seed=22)
