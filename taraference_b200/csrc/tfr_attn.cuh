@@ -70,7 +70,7 @@ struct AttnArgs {
     float scale;
     int pos;                    // used when st == nullptr
     int staged;                 // 1: the staged instance (the launch carries its dynamic shared memory, attn_dyn_smem)
-    int stages;                 // host side: tile stages the launch provides (0 = all); two serve splits of up to 128 keys
+    int stages;                 // host side: tile stages the launch provides (0 = all); n serve splits of up to 64 n keys
     int prof_id;                // timeline probe: which launch of the token this is (test aid)
 };
 

@@ -376,7 +376,8 @@ static int attn_splits(int sms, int n_kv, int hd, bool staged) {
 // Which instance a launch takes and with how much shared memory, from the head size and the largest number of keys the
 // launch can meet (the cache's capacity in the engine, pos + 1 in the operator entry points).
 // Head sizes up to 128 always take the staged instance (scores and values on the tensor cores): a step of it covers 128
-// keys, so splits are cut at 128 keys, and when no split can exceed 128 keys two tile stages replace the five.  Head
+// keys; splits are cut at 256 keys (a second step costs less than the cluster merge a second split needs), and when no
+// split can exceed 256 keys four tile stages replace the five.  Head
 // size 256 takes the staged instance only where a split can exceed ATTN_LONG_MIN keys.  TFR_ATTN_REGISTER_ROUTE=1 in
 // the environment keeps short caches on the register route for every head size (a test and measurement aid).
 static void attn_route(AttnArgs& a, int hd, int max_keys, int s_short, int s_staged, int min_keys_short) {
@@ -385,8 +386,9 @@ static void attn_route(AttnArgs& a, int hd, int max_keys, int s_short, int s_sta
     a.staged = long_cache || mma_route;
     a.S = a.staged ? s_staged : s_short;
     const bool mma = a.staged && attn_staged_mma(hd);
-    a.stages = (mma && max_keys <= s_staged * 2 * ATTN_TILE) ? 2 : 0;
-    a.min_keys = mma ? 2 * ATTN_TILE : min_keys_short;
+    constexpr int tiles_per_split = 4;  // measured on one box: 2 tiles 718.6 tok/s, 3 715.3, 4 722.9, 5 719.0 - 723.9
+    a.stages = (mma && max_keys <= s_staged * tiles_per_split * ATTN_TILE) ? tiles_per_split : 0;
+    a.min_keys = mma ? tiles_per_split * ATTN_TILE : min_keys_short;
 }
 
 static int sm_count_cached() {
